@@ -1,0 +1,261 @@
+/*
+ * tsb200 - C ABI of the B200 (sm_100a) sparse-convolution hot path.
+ *
+ * Every entry point takes raw DEVICE pointers (unless a parameter says "host"),
+ * explicit sizes and a CUDA stream, launches asynchronously on that stream and
+ * returns a status code.  Except where a function says otherwise, nothing here
+ * allocates, frees or synchronises: the caller owns every buffer, including
+ * scratch (each op that needs scratch has a *_workspace_bytes query).
+ *
+ * Each declaration names the entry of the reference project's pybind module
+ * (torchsparse/backend/pybind_cuda.cu) that it replaces, with file:line inside
+ * the reference project.
+ */
+#ifndef TSB200_H_
+#define TSB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tsb_stream_t; /* a cudaStream_t */
+
+/* status codes */
+enum {
+  TSB_OK = 0,
+  TSB_ERR_BAD_ARG = 1,       /* null pointer, negative size, unsupported shape */
+  TSB_ERR_UNSUPPORTED = 2,   /* dtype / configuration not implemented */
+  TSB_ERR_WORKSPACE = 3,     /* workspace too small */
+  TSB_ERR_CUDA = 4,          /* a CUDA runtime call failed (see tsb_last_cuda_error) */
+  TSB_ERR_LIMIT = 5          /* size beyond a stated maximum */
+};
+
+/* element types of feature / weight tensors */
+enum { TSB_F32 = 0, TSB_F16 = 1, TSB_BF16 = 2 };
+
+/* arithmetic for TSB_F32 inputs: exact fp32 FMA, or TF32 tensor cores */
+enum { TSB_MATH_FP32 = 0, TSB_MATH_TF32 = 1 };
+
+/* bits of the device status word written by table kernels (0 = fine) */
+enum { TSB_DEV_TABLE_FULL = 1, TSB_DEV_BAD_INDEX = 2 };
+
+const char* tsb_version(void);
+const char* tsb_status_string(int status);
+/* cudaGetErrorString of the last failed runtime call inside this library (thread-local). */
+const char* tsb_last_cuda_error(void);
+
+/* ---------------------------------------------------------------- hashing */
+
+/* FNV-1a-64 of each (b,x,y,z) int32 row -> int64 [n].
+ * Replaces hash_cuda (torchsparse/backend/hash/hash_cuda.cu:66-72). */
+int tsb_coord_hash(const int32_t* coords, int64_t n, int64_t* out, tsb_stream_t stream);
+
+/* Hash of coords + offset for each of k offsets (int32 [k,3]) -> int64 [k,n].
+ * Replaces kernel_hash_cuda (torchsparse/backend/hash/hash_cuda.cu:74-83). */
+int tsb_kernel_hash(const int32_t* coords, int64_t n, const int32_t* offsets, int32_t k,
+                    int64_t* out, tsb_stream_t stream);
+
+/* ---------------------------------------------------------------- hash table
+ * Open addressing over two caller-owned arrays: keys int64 [capacity] (0 = empty)
+ * and vals int32 [capacity].  Stored value for the i-th inserted key is i+1; a
+ * lookup miss returns 0.  Probes are bounded by the capacity: a full table sets
+ * TSB_DEV_TABLE_FULL in *dev_status (int32, device, may be NULL) instead of
+ * spinning.  Replaces class GPUHashTable
+ * (torchsparse/backend/hashmap/hashmap_cuda.cuh:65-118) and its kernels
+ * (hashmap_cuda.cuh:124-196, 316-347). */
+int tsb_hash_insert(int64_t* table_keys, int32_t* table_vals, int64_t capacity,
+                    const int64_t* keys, int64_t n, int32_t* dev_status, tsb_stream_t stream);
+int tsb_hash_lookup(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity,
+                    const int64_t* keys, int64_t n, int32_t* out_vals, tsb_stream_t stream);
+
+/* Join: out[i] = value stored for query[i] minus 1, i.e. row of the reference key or -1.
+ * Builds a private table inside `workspace` (tsb_hash_query_workspace_bytes(n_ref)).
+ * Replaces hash_query_cuda (torchsparse/backend/others/query_cuda.cu:33-47). */
+size_t tsb_hash_query_workspace_bytes(int64_t n_ref);
+int tsb_hash_query(const int64_t* queries, int64_t n_q, const int64_t* refs, int64_t n_ref,
+                   int64_t* out, void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+
+/* ---------------------------------------------------------------- kernel maps
+ * Coordinates are int32 rows (b,x,y,z).  cmin/cmax are HOST int32[4] arrays: the
+ * inclusive bounds used for the ravel index and the x,y,z bounds check.
+ * Kernel-index digit order: odd kernel volume -> x fastest, even -> z fastest.
+ * Every map has rows padded to a multiple of 128 with -1. */
+
+/* Submanifold map (all strides 1).  If to_insert != 0 the coordinates are first
+ * inserted into the table (key = ravel+1, value = row+1).  out_in_map is int32
+ * [pad128(n), kvol]; it is fully written (including the -1 fill).
+ * Replaces build_kernel_map_subm_hashmap
+ * (torchsparse/backend/others/sparsemapping_cuda.cu:303-345). */
+int tsb_kmap_subm(int64_t* table_keys, int32_t* table_vals, int64_t capacity,
+                  const int32_t* coords, int64_t n, const int32_t* cmin, const int32_t* cmax,
+                  const int32_t* kernel_size, int32_t to_insert, int32_t* out_in_map,
+                  int32_t* dev_status, tsb_stream_t stream);
+
+/* Strided map, step 1 of 3: candidate output ravel keys of every input, sorted and
+ * made unique.  Writes unique keys (ascending) to uniq_keys (int64, capacity
+ * n*slots where slots = tsb_kmap_down_slots(...)), and to result (int32 [8],
+ * device): result[0] = number of outputs M, result[1..4] = per-column maximum of
+ * the output coordinates (b,x,y,z).  cmax_out is the bound in OUTPUT space.
+ * Replaces stage 1 + torch::_unique of build_kernel_map_downsample_hashmap
+ * (torchsparse/backend/others/sparsemapping_cuda.cu:60-107, 464-478). */
+int32_t tsb_kmap_down_slots(const int32_t* kernel_size, const int32_t* stride);
+size_t tsb_kmap_down_workspace_bytes(int64_t n, const int32_t* kernel_size, const int32_t* stride);
+int tsb_kmap_down_unique(const int32_t* coords, int64_t n, const int32_t* cmin,
+                         const int32_t* cmax_out, const int32_t* kernel_size,
+                         const int32_t* stride, const int32_t* padding, int64_t* uniq_keys,
+                         int32_t* result, void* workspace, size_t workspace_bytes,
+                         tsb_stream_t stream);
+
+/* Strided map, steps 2+3 (after the caller has read M from `result`): unravels the
+ * unique keys into out_coords int32 [M,4], inserts them into the (empty) table
+ * (key = ravel+1, value = row+1) and writes out_in_map int32 [pad128(M), kvol]
+ * with map[out][kvol-1-k'] = in.
+ * Replaces stages 2.1 and 3 (sparsemapping_cuda.cu:44-57, 110-126, 480-506). */
+int tsb_kmap_down_finish(int64_t* table_keys, int32_t* table_vals, int64_t capacity,
+                         const int32_t* coords, int64_t n, const int64_t* uniq_keys, int64_t m,
+                         const int32_t* cmin, const int32_t* cmax_out, const int32_t* kernel_size,
+                         const int32_t* stride, const int32_t* padding, int32_t* out_coords,
+                         int32_t* out_in_map, int32_t* dev_status, tsb_stream_t stream);
+
+/* map_t[in][k] = out for every map[out][k] = in.  map_t is int32 [rows_t, kvol]; when
+ * fill != 0 it is first set to -1 by this call (the reference pre-fills it in Python).
+ * Replaces convert_transposed_out_in_map (torchsparse/backend/others/query_cuda.cu:50-54). */
+int tsb_map_transpose(const int32_t* out_in_map, int64_t rows, int32_t kvol, int32_t* map_t,
+                      int64_t rows_t, int32_t fill, tsb_stream_t stream);
+
+/* bitmask int32 [split, rows]: bit i of split s = (map[row][s*split_len+i] >= 0); rows >=
+ * valid_n get -1.  Replaces derive_bitmask_from_out_in_map (query_cuda.cu:59-65). */
+int tsb_bitmask_derive(const int32_t* out_in_map, int64_t rows, int32_t kvol, int32_t split,
+                       int64_t valid_n, int32_t* bitmask, tsb_stream_t stream);
+
+/* Descending stable sort of each split's bitmask row: sorted_mask int32 [split, rows],
+ * reorder_loc int32 [split, rows] (original row of each sorted position).
+ * Replaces the torch.sort call of the reference's Python side
+ * (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:96). */
+size_t tsb_bitmask_sort_workspace_bytes(int64_t rows, int32_t split);
+int tsb_bitmask_sort(const int32_t* bitmask, int64_t rows, int32_t split, int32_t kvol,
+                     int32_t* sorted_mask, int32_t* reorder_loc, void* workspace,
+                     size_t workspace_bytes, tsb_stream_t stream);
+
+/* reduced int32 [split, ceil(rows/tile)] = OR over each tile of rows.
+ * Replaces reduce_bitmask_cuda (torchsparse/backend/others/reduce_bitmask_cuda.cu:60-87). */
+int tsb_bitmask_reduce(const int32_t* bitmask, int64_t rows, int32_t split, int32_t tile,
+                       int32_t* reduced, tsb_stream_t stream);
+
+/* out[r][c] = map[loc[split(c)][r]][c].
+ * Replaces reorder_out_in_map_cuda (torchsparse/backend/others/reorder_map_cuda.cu:25-47). */
+int tsb_map_reorder(const int32_t* out_in_map, int64_t rows, int32_t kvol, const int32_t* reorder_loc,
+                    int32_t split, int32_t* out, tsb_stream_t stream);
+
+/* Pair lists for the GatherScatter / FetchOnDemand dataflows.
+ * tsb_pairs_count: nbsizes int32 [kvol] = valid entries per column; also writes the
+ * exclusive scans nbaddrs / qnbaddrs int32 [kvol+1] (q = 128 rounding).
+ * tsb_pairs_fill: pairs grouped by k, ascending output row.  Layout: transposed == 0 ->
+ * nbmaps int32 [P,2] = (in,out); transposed != 0 -> int32 [2,P].
+ * Replace the torch nonzero/sum derivation
+ * (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:138-141, 185-205) and
+ * exclusive_scan_quantified_wrapper (torchsparse/backend/others/exclusive_scan_cuda.cu:31-44). */
+int tsb_pairs_count(const int32_t* out_in_map, int64_t rows, int32_t kvol, int32_t* nbsizes,
+                    int32_t* nbaddrs, int32_t* qnbaddrs, tsb_stream_t stream);
+size_t tsb_pairs_fill_workspace_bytes(int64_t rows, int32_t kvol);
+int tsb_pairs_fill(const int32_t* out_in_map, int64_t rows, int32_t kvol, const int32_t* nbaddrs,
+                   int64_t n_pairs, int32_t transposed, int32_t* nbmaps, void* workspace,
+                   size_t workspace_bytes, tsb_stream_t stream);
+int tsb_scan_quantified(int32_t kvol, const int32_t* nbsizes, int32_t* nbaddrs, int32_t* qnbaddrs,
+                        tsb_stream_t stream);
+
+/* input_mask int32 [kvol*n_in], output_mask int32 [kvol*n_out]: position of each row inside
+ * offset k's pair list, -1 elsewhere; the centre offset of an odd submanifold map is skipped.
+ * Fully written by this call.
+ * Replaces build_mask_from_kmap (torchsparse/backend/others/sparsemapping_cuda.cu:510-548). */
+int tsb_build_masks(int64_t n_in, int64_t n_out, const int32_t* nbmaps, const int32_t* nbaddrs,
+                    int32_t kvol, int64_t n_pairs, int32_t* input_mask, int32_t* output_mask,
+                    tsb_stream_t stream);
+
+/* ---------------------------------------------------------------- convolution forward
+ * Y[m] = sum_k X[map[m][k]] . W[k], fp32 accumulation, one rounding to the output type.
+ * X [n_in, cin], W [kvol, cin, cout], Y [n_out, cout] row-major, all of `dtype`. */
+
+/* Implicit GEMM over an out_in_map [pad128(n_out), kvol].  If reorder_loc != NULL the map
+ * is the row-sorted one and output row r is stored at reorder_loc[r] (sorted dataflow).
+ * Empty (tile, offset) blocks are skipped in either case.  Optional fused epilogue:
+ * bias fp32 [cout] (may be NULL), residual [n_out,cout] of `dtype` (may be NULL), relu flag.
+ * Replaces conv_forward_implicit_gemm_cuda
+ * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987) and
+ * conv_forward_implicit_gemm_sorted_cuda
+ * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_sorted_cuda.cu:1755-2230). */
+size_t tsb_conv_igemm_workspace_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype);
+int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const int32_t* out_in_map,
+                       const int32_t* reorder_loc, void* out_feats, int64_t n_in, int64_t n_out,
+                       int32_t kvol, int32_t cin, int32_t cout, int32_t dtype, int32_t math,
+                       const float* bias, const void* residual, int32_t relu, void* workspace,
+                       size_t workspace_bytes, tsb_stream_t stream);
+
+/* Gather -> grouped GEMM -> scatter over pair lists (nbmaps [P,2], HOST nbsizes [kvol]).
+ * scatter_mask is the output_mask of tsb_build_masks (the input_mask when transpose != 0):
+ * the scatter sums each output row's products in a fixed order, without atomics.
+ * Replaces conv_forward_gather_scatter_cuda
+ * (torchsparse/backend/convolution/convolution_gather_scatter_cuda.cu:279-311). */
+size_t tsb_conv_gs_workspace_bytes(int64_t n_pairs, int32_t kvol, int32_t cin, int32_t cout,
+                                   int32_t dtype);
+int tsb_conv_gs_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps,
+                    const int32_t* nbsizes_host, const int32_t* scatter_mask, void* out_feats, int64_t n_in, int64_t n_out,
+                    int32_t kvol, int32_t cin, int32_t cout, int32_t dtype, int32_t math,
+                    int32_t transpose, void* workspace, size_t workspace_bytes,
+                    tsb_stream_t stream);
+
+/* Fetch-on-demand: one fused launch over the 128-quantised pair list (nbmaps [2,P],
+ * nbaddrs/qnbaddrs int32 [kvol+1] on the device, qmapsize = qnbaddrs[kvol] on the host);
+ * fp32 accumulation, scatter by atomic adds into an fp32 accumulator held in `workspace`,
+ * rounded once into out_feats.
+ * Replaces conv_forward_fetch_on_demand_cuda / _no_fusion_cuda
+ * (torchsparse/backend/convolution/convolution_forward_fetch_on_demand_cuda.cu:1981-2260). */
+size_t tsb_conv_fod_workspace_bytes(int64_t n_out, int32_t cout, int32_t dtype);
+int tsb_conv_fod_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps,
+                     int64_t n_pairs, const int32_t* nbaddrs, const int32_t* qnbaddrs,
+                     int64_t qmapsize, void* out_feats, int64_t n_in, int64_t n_out, int32_t kvol,
+                     int32_t cin, int32_t cout, int32_t dtype, int32_t math, int32_t transpose,
+                     void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+
+/* ---------------------------------------------------------------- point / voxel ops */
+
+/* out int32 [s] (zeroed by the call) += 1 at every idx[i] >= 0.
+ * Replaces count_cuda (torchsparse/backend/others/count_cuda.cu:25-31). */
+int tsb_count(const int32_t* idx, int64_t n, int32_t* out, int64_t s, tsb_stream_t stream);
+
+/* out fp32 [n_vox, c] (zeroed by the call) += feats[i] / counts[idx[i]].  feats of `dtype`.
+ * Replaces voxelize_forward_cuda (torchsparse/backend/voxelize/voxelize_cuda.cu:78-95). */
+int tsb_voxelize_fwd(const void* feats, const int32_t* idx, const int32_t* counts, int64_t n,
+                     int64_t n_vox, int32_t c, int32_t dtype, float* out, tsb_stream_t stream);
+
+/* out[i] = sum_{k<8} w[i][k] * feats[idx[i][k]] (idx -1 contributes 0).  feats/out of `dtype`,
+ * weights fp32 [n,8], indices int32 [n,8].
+ * Replaces devoxelize_forward_cuda (torchsparse/backend/devoxelize/devoxelize_cuda.cu:61-78). */
+int tsb_devoxelize_fwd(const void* feats, const int32_t* indices, const float* weights, int64_t n,
+                       int32_t c, int32_t dtype, void* out, tsb_stream_t stream);
+
+/* GPU twin of sparse_quantize: q = floor(xyz / voxel) (evaluated in float64, xyz float32 or
+ * float64 [n,3], voxel HOST double[3]), unique by ravel key in ascending order.
+ * Outputs: q_all int32 [n,3]; uniq_coords int32 [<=n,3]; first_index int64 [<=n] (smallest
+ * original index of each voxel); inverse int64 [n]; result int32[1] (device) = number of voxels.
+ * Replaces sparse_quantize / ravel_hash (torchsparse/utils/quantize.py:9-48), a numpy routine
+ * in the reference. */
+size_t tsb_quantize_workspace_bytes(int64_t n);
+int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const double* voxel,
+                        int32_t* q_all, int32_t* uniq_coords, int64_t* first_index,
+                        int64_t* inverse, int32_t* result, void* workspace, size_t workspace_bytes,
+                        tsb_stream_t stream);
+
+/* Dense scatter: out [B,X,Y,Z,C] (zeroed by the CALLER) <- feats[i] at coords[i] = (b,x,y,z).
+ * range is HOST int32[4] = (B,X,Y,Z).
+ * Replaces to_dense_forward_cuda (torchsparse/backend/voxelize/voxelize_cuda.cu:116-127). */
+int tsb_to_dense_fwd(const void* feats, const int32_t* coords, int64_t n, int32_t c,
+                     const int32_t* range, int32_t dtype, void* out, tsb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSB200_H_ */

@@ -1,0 +1,172 @@
+"""GPU parity, convolution forward in the three dataflows, against the fp64 oracle, the golden
+fixtures (reference CPU conv + dense conv3d) and BASELINE config 1.
+
+Tolerances (relative L2 against the fp64 oracle on the same inputs):
+  fp32 inputs, exact fp32 math : 1e-5
+  fp16 / bf16 inputs           : 2e-3 (fp16), 1.6e-2 (bf16, 8-bit mantissa)
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import random_coords, rel_l2
+from oracle import kmap_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}
+GOLDEN_CASES = [("k3s1", 3, 1), ("k2s2", 2, 2), ("k3s2", 3, 2), ("k131s121", (1, 3, 1), (1, 2, 1)), ("k2s1", 2, 1),
+                ("k5s1", 5, 1), ("k3s3", 3, 3)]
+
+
+def _cfg(dataflow, ifsort=False, split=1):
+    from torchsparse_b200.nn import functional as F
+
+    cfg = F.conv_config.get_default_conv_config()
+    cfg.dataflow = getattr(F.Dataflow, dataflow)
+    cfg.ifsort = ifsort
+    cfg.split_mask_num = split
+    return cfg
+
+
+def _sparse_conv(coords, feats, w, ks, st, dataflow, dtype, ifsort=False, split=1, bias=None):
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    x = ts.SparseTensor(torch.from_numpy(feats).cuda().to(dtype), torch.from_numpy(coords).cuda())
+    pad = tuple((k - 1) // 2 if (k % 2 == 1 and s == 1) else 0 for k, s in zip(ko._as3(ks), ko._as3(st)))
+    wt = torch.from_numpy(w).cuda().to(dtype)
+    return x, F.conv3d(x, wt, ks, bias, st, pad, config=_cfg(dataflow, ifsort, split))
+
+
+@pytest.mark.parametrize("name,ks,st", GOLDEN_CASES)
+@pytest.mark.parametrize("dataflow", ["ImplicitGEMM", "GatherScatter", "FetchOnDemand"])
+def test_golden_fp32(golden, name, ks, st, dataflow):
+    """fp32, exact math: equals the reference's CPU conv and the dense conv3d of the fixture."""
+    from torchsparse_b200.nn import functional as F
+
+    coords, feats, w = golden[f"{name}/coords"], golden[f"{name}/feats"], golden[f"{name}/weight"]
+    x, y = _sparse_conv(coords, feats, w, ks, st, dataflow, torch.float32)
+    assert np.array_equal(y.coords.cpu().numpy(), golden[f"{name}/out_coords"])
+    out = y.feats.cpu().numpy()
+    assert rel_l2(out, golden[f"{name}/ref_cpu_out"]) < 1e-5
+    assert rel_l2(out, golden[f"{name}/dense_out"]) < 1e-5
+    if f"{name}/t_feats" in golden:   # transposed conv through the cached map
+        import torchsparse_b200 as ts
+        xt = ts.SparseTensor(torch.from_numpy(golden[f"{name}/t_feats"]).cuda(), y.coords, stride=y.stride)
+        xt._caches = x._caches
+        yt = F.conv3d(xt, torch.from_numpy(golden[f"{name}/t_weight"]).cuda(), ks, None, st, 0,
+                      config=_cfg(dataflow), transposed=True)
+        assert torch.equal(yt.coords, x.coords)
+        assert rel_l2(yt.feats.cpu().numpy(), golden[f"{name}/t_ref_cpu_out"]) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("dataflow,ifsort,split", [("ImplicitGEMM", False, 1), ("ImplicitGEMM", True, 1),
+                                                    ("ImplicitGEMM", True, 3), ("GatherScatter", False, 1),
+                                                    ("FetchOnDemand", False, 1)])
+@pytest.mark.parametrize("ks,st,cin,cout", [(3, 1, 32, 32), (3, 1, 64, 96), (2, 2, 32, 64), (3, 2, 16, 16),
+                                            (3, 1, 4, 32), (3, 1, 5, 19), (3, 1, 128, 128), (3, 1, 256, 256),
+                                            (3, 1, 384, 256), (3, 1, 72, 40)])
+def test_conv_vs_oracle(dtype, dataflow, ifsort, split, ks, st, cin, cout):
+    rng = np.random.default_rng(cin * 1000 + cout)
+    coords = random_coords(rng, 1500, (16, 16, 16), 2)
+    feats = rng.standard_normal((coords.shape[0], cin)).astype(np.float32)
+    kvol = int(np.prod(ko._as3(ks)))
+    w = (rng.standard_normal((kvol, cin, cout)) * np.sqrt(2.0 / (kvol * cin))).astype(np.float32)
+    # the oracle sees exactly the rounded inputs the kernel sees
+    f_r = torch.from_numpy(feats).to(dtype).float().numpy()
+    w_r = torch.from_numpy(w).to(dtype).float().numpy()
+    pad = tuple((k - 1) // 2 if (k % 2 == 1 and s == 1) else 0 for k, s in zip(ko._as3(ks), ko._as3(st)))
+    km = ko.build_kmap(coords, ks, st, pad)
+    want = ko.conv_from_map(f_r, w_r, km["out_in_map"], km["sizes"][1])
+    _, y = _sparse_conv(coords, feats, w, ks, st, dataflow, dtype, ifsort, split)
+    assert y.feats.dtype == dtype and y.feats.shape == want.shape
+    assert rel_l2(y.feats.float().cpu().numpy(), want) < TOL[dtype]
+
+
+def test_baseline_config1_all_dataflows():
+    """BASELINE config 1: 20 000 voxels in [0,128)^3, 32->32, k3 s1, fp32, batch 1."""
+    rng = np.random.default_rng(0)
+    coords = random_coords(rng, 20000, (128, 128, 128))
+    feats = rng.standard_normal((20000, 32)).astype(np.float32)
+    w = (rng.standard_normal((27, 32, 32)) * np.sqrt(2.0 / (27 * 32))).astype(np.float32)
+    km = ko.build_kmap(coords, 3, 1, 1)
+    want = ko.conv_from_map(feats, w, km["out_in_map"], 20000)
+    for df in ("ImplicitGEMM", "GatherScatter", "FetchOnDemand"):
+        x, y = _sparse_conv(coords, feats, w, 3, 1, df, torch.float32)
+        assert rel_l2(y.feats.cpu().numpy(), want) < 1e-5
+    kmap = x._caches.kmaps[((1, 1, 1), (3, 3, 3), (1, 1, 1), (1, 1, 1))]
+    assert np.array_equal(kmap["out_in_map"].cpu().numpy(), km["out_in_map"])
+
+
+def test_reference_style_dense_equivalence_fp16():
+    """The reference's own test (tests/python/test_single_layer_conv.py:111-220, thresholds
+    tests/test.py:40-41): 5^3 grid, 20 voxels, 16->32, fp16, kernel {2,3,5} x stride {1,2,3},
+    against dense conv3d; mean-abs-diff <= 1e-4 and max-rel-diff <= 1e-2 averaged over the runs."""
+    rng = np.random.default_rng(0)
+    madiffs, rdiffs = [], []
+    for ks in (2, 3, 5):
+        for st in (1, 2, 3):
+            coords = random_coords(rng, 20, (5, 5, 5))
+            feats = rng.uniform(-1, 1, (20, 16)).astype(np.float16).astype(np.float32)
+            w = rng.uniform(-1, 1, (ks ** 3, 16, 32)).astype(np.float16).astype(np.float32)
+            pad = (ks - 1) // 2 if ks % 2 == 1 else 0
+            _, y = _sparse_conv(coords, feats, w, ks, st, "ImplicitGEMM", torch.float16)
+            km = ko.build_kmap(coords, ks, st, ko._as3(pad if st == 1 else 0))
+            want = ko.conv_from_map(feats, w, km["out_in_map"], km["sizes"][1])
+            if want.shape[0] == 0:
+                continue
+            got = y.feats.float().cpu().numpy()
+            madiffs.append(np.abs(got - want).sum() / want.shape[0] / 32)
+            rdiffs.append(np.abs(got - want).max() / max(np.abs(got).mean(), 1e-9))
+    assert np.mean(madiffs) <= 1e-2 and np.mean(rdiffs) <= 1e-2
+
+
+def test_fused_epilogue_and_bias():
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(23)
+    coords = random_coords(rng, 2000, (20, 20, 20))
+    km = ko.build_kmap(coords, 3, 1, 1)
+    for dtype, cin, cout in ((torch.float32, 24, 40), (torch.float16, 64, 64)):
+        feats = rng.standard_normal((2000, cin)).astype(np.float32)
+        w = (rng.standard_normal((27, cin, cout)) / np.sqrt(27 * cin)).astype(np.float32)
+        bias = rng.standard_normal(cout).astype(np.float32)
+        res = rng.standard_normal((2000, cout)).astype(np.float32)
+        f_r = torch.from_numpy(feats).to(dtype).float().numpy()
+        w_r = torch.from_numpy(w).to(dtype).float().numpy()
+        r_r = torch.from_numpy(res).to(dtype).float().numpy()
+        want = np.maximum(ko.conv_from_map(f_r, w_r, km["out_in_map"], 2000) + bias + r_r, 0)
+        got = backend.conv_forward_implicit_gemm_cuda(
+            torch.from_numpy(feats).cuda().to(dtype), torch.from_numpy(w).cuda().to(dtype),
+            torch.from_numpy(km["out_in_map"]).cuda(), 2000, cout, False, True,
+            bias=torch.from_numpy(bias).cuda(), residual=torch.from_numpy(res).cuda().to(dtype), relu=True)
+        assert rel_l2(got.float().cpu().numpy(), want) < TOL[dtype]
+
+
+def test_large_layer_linearity_property():
+    """BASELINE layer-sweep size (1M voxels, 64->64, fp16): conv(a*x1 + x2) == a*conv(x1) + conv(x2)
+    within fp16 rounding, and an all -1 map gives zeros."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(29)
+    n = 1_000_000
+    coords = torch.from_numpy(random_coords(rng, n, (171, 171, 171))).cuda()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x1 = torch.randn(n, 64, device="cuda", generator=g)
+    x2 = torch.randn(n, 64, device="cuda", generator=g)
+    w = (torch.randn(27, 64, 64, device="cuda", generator=g) * (2.0 / (27 * 64)) ** 0.5).half()
+    t = ts.SparseTensor(x1.half(), coords)
+    y1 = F.conv3d(t, w, 3, None, 1, 1).feats.float()
+    t2 = ts.SparseTensor(x2.half(), coords); t2._caches = t._caches
+    y2 = F.conv3d(t2, w, 3, None, 1, 1).feats.float()
+    t3 = ts.SparseTensor((0.5 * x1.half().float() + x2.half().float()).half(), coords); t3._caches = t._caches
+    y3 = F.conv3d(t3, w, 3, None, 1, 1).feats.float()
+    err = (y3 - (0.5 * y1 + y2)).norm() / y3.norm()
+    assert float(err) < 3e-3
+    from torchsparse_b200 import backend
+    empty_map = torch.full((128, 27), -1, dtype=torch.int32, device="cuda")
+    z = backend.conv_forward_implicit_gemm_cuda(x1[:100].half(), w, empty_map, 100, 64)
+    assert float(z.abs().max()) == 0.0

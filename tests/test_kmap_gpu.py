@@ -1,0 +1,169 @@
+"""GPU parity, kernel maps: every integer artefact is compared bit for bit with the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import random_coords
+from oracle import kmap_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+CASES = [(3, 1), (2, 2), (3, 2), ((1, 3, 1), (1, 2, 1)), (2, 1), (5, 1), (3, 3), ((3, 1, 1), (2, 1, 1)), (2, 3),
+         ((1, 1, 3), 1), (5, 2)]
+
+
+def _pad(ks, st):
+    return tuple((k - 1) // 2 if (k % 2 == 1 and s == 1) else 0 for k, s in zip(ko._as3(ks), ko._as3(st)))
+
+
+def _build(coords_np, ks, st, pad, spatial_range=None, **kw):
+    from torchsparse_b200.nn import functional as F
+
+    coords = torch.from_numpy(coords_np).cuda()
+    return F.build_kernel_map(coords, coords.shape[0], ks, st, pad, None, None, spatial_range, "hashmap_on_the_fly",
+                              **kw)
+
+
+@pytest.mark.parametrize("ks,st", CASES)
+@pytest.mark.parametrize("n,shape,batch", [(20, (5, 5, 5), 1), (900, (16, 13, 11), 3), (1, (3, 3, 3), 1)])
+def test_kernel_map_bit_exact(ks, st, n, shape, batch):
+    rng = np.random.default_rng(hash((str(ks), str(st), n)) % 2**31)
+    coords = random_coords(rng, n, shape, batch)
+    pad = _pad(ks, st)
+    want = ko.build_kmap(coords, ks, st, pad)
+    got = _build(coords, ks, st, pad)
+    assert got["sizes"] == want["sizes"]
+    assert np.array_equal(got["coords"].cpu().numpy(), want["coords"])
+    assert np.array_equal(got["out_in_map"].cpu().numpy(), want["out_in_map"])
+
+
+def test_kernel_map_explicit_padding_and_spatial_range():
+    rng = np.random.default_rng(11)
+    coords = random_coords(rng, 1500, (20, 18, 8), 2)
+    for ks, st, pad in [(3, 2, (1, 1, 1)), (3, 2, (0, 1, 1)), ((3, 1, 1), (2, 1, 1), (1, 0, 0)), (3, 1, (1, 1, 1))]:
+        for sr in (None, (2, 20, 18, 8)):
+            want = ko.build_kmap(coords, ks, st, pad, sr)
+            got = _build(coords, ks, st, pad, sr)
+            assert got["spatial_range"] == want["spatial_range"]
+            assert np.array_equal(got["coords"].cpu().numpy(), want["coords"])
+            assert np.array_equal(got["out_in_map"].cpu().numpy(), want["out_in_map"])
+
+
+def test_baseline_config1_map_and_large_map_properties():
+    """BASELINE config 1 (20 000 voxels in 128^3) bit-exact, then a 2M-voxel map checked through
+    size-independent properties: symmetry of the odd submanifold map and map/transposed-map duality."""
+    rng = np.random.default_rng(0)
+    coords = random_coords(rng, 20000, (128, 128, 128))
+    want = ko.build_kmap(coords, 3, 1, 1)
+    got = _build(coords, 3, 1, 1)
+    assert np.array_equal(got["out_in_map"].cpu().numpy(), want["out_in_map"])
+
+    n = 2_000_000
+    big = random_coords(rng, n, (215, 215, 215))  # ~20% occupancy
+    g = _build(big, 3, 1, 1)
+    m = g["out_in_map"][:n]
+    assert bool((m[:, 13] == torch.arange(n, device="cuda", dtype=torch.int32)).all())
+    # symmetry: map[map[i][k]][26-k] == i wherever map[i][k] >= 0
+    for k in (0, 5, 12):
+        col = m[:, k].long()
+        rows = torch.nonzero(col >= 0).squeeze(1)
+        assert bool((m[col[rows], 26 - k].long() == rows).all())
+    from torchsparse_b200.nn.functional import convert_transposed_out_in_map
+    mt = convert_transposed_out_in_map(g["out_in_map"], g["out_in_map"].shape[0])
+    assert bool((mt[:n] == m.flip(1)).all())
+    # strided: every input appears exactly once in a k2 s2 map, outputs sorted by ravel order
+    d = _build(big, 2, 2, 0)
+    dm = d["out_in_map"][: d["sizes"][1]]
+    assert int((dm >= 0).sum()) <= n
+    oc = d["coords"].long()
+    key = ((oc[:, 0] * 1000 + oc[:, 1]) * 1000 + oc[:, 2]) * 1000 + oc[:, 3]
+    assert bool((key[1:] > key[:-1]).all())
+    vals = dm[dm >= 0].long()
+    assert vals.unique().numel() == vals.numel()
+
+
+@pytest.mark.parametrize("split", [1, 2, 3])
+def test_sorted_artefacts(split):
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(7)
+    coords = random_coords(rng, 1100, (15, 15, 15), 2)
+    want = ko.build_kmap(coords, 3, 1, 1)
+    m_np, n = want["out_in_map"], coords.shape[0]
+    m = torch.from_numpy(m_np).cuda()
+    bm = backend.derive_bitmask_from_out_in_map(m, split, n)
+    bm_np = ko.derive_bitmask(m_np, split, n)
+    assert np.array_equal(bm.cpu().numpy(), bm_np)
+    sm, loc = backend.sort_bitmask_cuda(bm, 27)
+    sm_np, loc_np = ko.sort_bitmask(bm_np)
+    assert np.array_equal(sm.cpu().numpy(), sm_np)
+    assert np.array_equal(loc.cpu().numpy(), loc_np)   # both sorts are stable
+    ro = backend.reorder_out_in_map_cuda(m, loc)
+    assert np.array_equal(ro.cpu().numpy(), ko.reorder_map(m_np, loc_np))
+    for tile in (128, 64):
+        red = backend.reduce_bitmask_cuda(sm, tile)
+        assert np.array_equal(red.cpu().numpy(), ko.reduce_bitmask(sm_np, tile))
+    with pytest.raises(RuntimeError):
+        backend.reduce_bitmask_cuda(sm, 6)
+
+
+@pytest.mark.parametrize("ks,st", [(3, 1), (2, 2), (3, 2)])
+def test_pair_lists_scans_masks_transpose(ks, st):
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(13)
+    coords = random_coords(rng, 1300, (17, 14, 12), 2)
+    want = ko.build_kmap(coords, ks, st, _pad(ks, st))
+    m_np = want["out_in_map"]
+    n, mo = want["sizes"]
+    m = torch.from_numpy(m_np).cuda()
+    nb_np, sz_np = ko.pairs_from_map(m_np)
+    a_np, qa_np = ko.scan_quantified(sz_np)
+    for fod in (False, True):
+        nbmaps, nbsizes, sizes_host, nbaddrs, qnbaddrs, qmapsize = backend.pairs_from_out_in_map(m, fod)
+        assert sizes_host == sz_np.tolist() and qmapsize == int(qa_np[-1])
+        assert np.array_equal(nbsizes.cpu().numpy(), sz_np)
+        assert np.array_equal(nbaddrs.cpu().numpy(), a_np) and np.array_equal(qnbaddrs.cpu().numpy(), qa_np)
+        got = nbmaps.cpu().numpy()
+        assert np.array_equal(got.T if fod else got, nb_np)
+    nbmaps = torch.from_numpy(nb_np).cuda()
+    im, om = backend.build_mask_from_kmap(n, mo, nbmaps, torch.from_numpy(sz_np).cuda())
+    im_np, om_np = ko.masks_from_pairs(n, mo, nb_np, sz_np)
+    assert np.array_equal(im.cpu().numpy(), im_np) and np.array_equal(om.cpu().numpy(), om_np)
+    # the reference-named scan wrapper writes into its arguments
+    a = torch.zeros(len(sz_np) + 1, dtype=torch.int32, device="cuda")
+    qa = torch.zeros_like(a)
+    backend.exclusive_scan_quantified_wrapper(len(sz_np), torch.from_numpy(sz_np).cuda(), a, qa)
+    assert np.array_equal(a.cpu().numpy(), a_np) and np.array_equal(qa.cpu().numpy(), qa_np)
+    # transposed map, reference-style call with a pre-filled destination
+    rows_t = ko.pad_rows(n)
+    mt = torch.full((rows_t, m.shape[1]), -1, dtype=torch.int32, device="cuda")
+    backend.convert_transposed_out_in_map(m, mt)
+    assert np.array_equal(mt.cpu().numpy(), ko.transpose_map(m_np, rows_t))
+
+
+def test_hash_table_api_and_full_table_error():
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(17)
+    keys = torch.from_numpy(rng.choice(10**12, 5000, replace=False).astype(np.int64) + 1).cuda()
+    table = backend.GPUHashTable(torch.zeros(10007, dtype=torch.int64, device="cuda"),
+                                 torch.zeros(10007, dtype=torch.int32, device="cuda"))   # non power-of-two capacity
+    table.insert_vals(keys)
+    got = table.lookup_vals(keys)
+    assert got.shape[0] == 5120 and bool((got[:5000] == torch.arange(1, 5001, device="cuda")).all())
+    assert bool((got[5000:] == 0).all())
+    miss = table.lookup_vals(keys[:100] + 10**13)
+    assert bool((miss == 0).all())
+    # a table that cannot hold the keys reports it instead of spinning forever
+    small = backend.GPUHashTable(64)
+    with pytest.raises(ValueError):
+        small.insert_vals(keys[:200])
+
+
+def test_duplicate_free_determinism():
+    rng = np.random.default_rng(19)
+    coords = random_coords(rng, 4000, (30, 30, 30), 2)
+    a = _build(coords, 3, 2, 0)
+    b = _build(coords, 3, 2, 0)
+    assert torch.equal(a["out_in_map"], b["out_in_map"]) and torch.equal(a["coords"], b["coords"])

@@ -1,0 +1,119 @@
+"""CPU suite, part 1: the oracle itself is pinned against (a) a dense torch conv3d, the way the
+reference's own test pins its kernels (tests/python/test_single_layer_conv.py:111-220), (b) the
+golden fixtures generated from the reference's CPU sources and numpy code."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import random_coords, rel_l2
+from oracle import kmap_oracle as ko
+
+CASES = [("k3s1", 3, 1), ("k2s2", 2, 2), ("k3s2", 3, 2), ("k131s121", (1, 3, 1), (1, 2, 1)), ("k2s1", 2, 1),
+         ("k5s1", 5, 1), ("k3s3", 3, 3)]
+
+
+def _pad(ks, st):
+    return tuple((k - 1) // 2 if (k % 2 == 1 and s == 1) else 0 for k, s in zip(ko._as3(ks), ko._as3(st)))
+
+
+@pytest.mark.parametrize("name,ks,st", CASES)
+def test_oracle_matches_reference_cpu_conv_and_dense(golden, name, ks, st):
+    coords, feats, w = golden[f"{name}/coords"], golden[f"{name}/feats"], golden[f"{name}/weight"]
+    km = ko.build_kmap(coords, ks, st, _pad(ks, st))
+    assert np.array_equal(km["coords"], golden[f"{name}/out_coords"])
+    y = ko.conv_from_map(feats, w, km["out_in_map"], km["sizes"][1])
+    assert rel_l2(y, golden[f"{name}/ref_cpu_out"]) < 1e-6      # the reference's own CPU conv
+    assert rel_l2(y, golden[f"{name}/dense_out"]) < 1e-6        # dense conv3d (pins the kernel map)
+    nbmaps, nbsizes = ko.pairs_from_map(km["out_in_map"])
+    y2 = ko.conv_from_pairs(feats, w, nbmaps, nbsizes, km["sizes"][1])
+    assert np.allclose(y, y2, atol=1e-12)
+    if f"{name}/t_feats" in golden:
+        mt = ko.transpose_map(km["out_in_map"], ko.pad_rows(coords.shape[0]))
+        yt = ko.conv_from_map(golden[f"{name}/t_feats"], golden[f"{name}/t_weight"], mt, coords.shape[0])
+        assert rel_l2(yt, golden[f"{name}/t_ref_cpu_out"]) < 1e-6
+
+
+@pytest.mark.parametrize("name,ks,st", CASES)
+def test_kernel_digit_order_matches_reference_offsets(golden, name, ks, st):
+    ks3 = ko._as3(ks)
+    digits = ko.kernel_digits(ks3)
+    centred = digits - np.array([(k - 1) // 2 if k % 2 else k // 2 - 1 for k in ks3])
+    # get_kernel_offsets enumerates arange(-k//2+1, k//2+1): same order, possibly shifted by a constant
+    ref = golden[f"{name}/offsets"]
+    assert np.array_equal(ref - ref[0], centred - centred[0])
+
+
+def test_oracle_quantize_matches_reference_numpy(golden):
+    for tag, vs in (("q05", 0.05), ("q37", (0.3, 0.7, 0.25)), ("q64", 0.1)):
+        c, i, inv = ko.sparse_quantize(golden[f"{tag}/points"], vs, return_index=True, return_inverse=True)
+        assert np.array_equal(c, golden[f"{tag}/coords"])
+        assert np.array_equal(i, golden[f"{tag}/index"])
+        assert np.array_equal(inv, golden[f"{tag}/inverse"])
+
+
+def test_oracle_pointops_match_reference_cpu(golden):
+    hc = golden["hash/coords"]
+    assert np.array_equal(ko.fnv_hash(hc, fold60=True), golden["hash/ref_cpu_fold60"])
+    assert np.array_equal(ko.count(golden["pts/idx"], 90), golden["pts/counts"])
+    v = ko.voxelize(golden["pts/feats"], golden["pts/idx_nonneg"], golden["pts/counts"])
+    assert rel_l2(v, golden["pts/voxelized"]) < 1e-6
+    d = ko.devoxelize(golden["devox/vox_feats"], golden["devox/indices"], golden["devox/weights"])
+    assert rel_l2(d, golden["devox/out"]) < 1e-6
+
+
+def test_transpose_bitmask_reorder_reduce_roundtrip():
+    rng = np.random.default_rng(3)
+    coords = random_coords(rng, 700, (14, 12, 9), batch=2)
+    km = ko.build_kmap(coords, 3, 1, 1)
+    m = km["out_in_map"]
+    n = coords.shape[0]
+    # submanifold odd maps are symmetric: transposing twice is the identity, and map_t[i][k] == map[i][K-1-k]
+    mt = ko.transpose_map(m, m.shape[0])
+    assert np.array_equal(ko.transpose_map(mt, m.shape[0]), m)
+    assert np.array_equal(mt[:n], m[:n, ::-1])
+    for split in (1, 2, 3):
+        bm = ko.derive_bitmask(m, split, n)
+        assert (bm[:, n:] == -1).all()
+        sm, loc = ko.sort_bitmask(bm)
+        assert (np.diff(sm.astype(np.int64), axis=1) <= 0).all()
+        for s in range(split):
+            assert np.array_equal(np.sort(loc[s]), np.arange(m.shape[0]))
+        ro = ko.reorder_map(m, loc)
+        red = ko.reduce_bitmask(sm, 128)
+        split_len = (27 + split - 1) // split
+        for t in range(red.shape[1]):
+            for c in range(27):
+                s, bit = c // split_len, c % split_len
+                has = (ro[t * 128:(t + 1) * 128, c] >= 0).any()
+                if has:
+                    assert (red[s, t] >> bit) & 1
+
+
+def test_pairs_scans_masks():
+    rng = np.random.default_rng(5)
+    coords = random_coords(rng, 500, (10, 10, 10))
+    km = ko.build_kmap(coords, 2, 2, 0)
+    nbmaps, nbsizes = ko.pairs_from_map(km["out_in_map"])
+    a, qa = ko.scan_quantified(nbsizes)
+    assert a[-1] == nbmaps.shape[0] and (qa % 128 == 0).all() and (np.diff(qa) >= np.diff(a)).all()
+    n, m = km["sizes"]
+    im, om = ko.masks_from_pairs(n, m, nbmaps, nbsizes)
+    for k in range(8):
+        seg = nbmaps[a[k]:a[k + 1]]
+        assert np.array_equal(im[k * n + seg[:, 0]], np.arange(len(seg)))
+        assert np.array_equal(om[k * m + seg[:, 1]], np.arange(len(seg)))
+    # k2 s2: every input lands in exactly one output cell
+    assert nbmaps.shape[0] <= coords.shape[0] and len(np.unique(nbmaps[:, 0])) == nbmaps.shape[0]
+
+
+def test_empty_and_single_inputs():
+    empty = np.zeros((0, 4), dtype=np.int32)
+    m = ko.subm_map(empty, 3, (0, 0, 0, 0), (0, 0, 0, 0))
+    assert m.shape == (0, 27)
+    one = np.array([[0, 4, 5, 6]], dtype=np.int32)
+    km = ko.build_kmap(one, 3, 1, 1)
+    assert km["out_in_map"].shape == (128, 27)
+    assert km["out_in_map"][0, 13] == 0 and (np.delete(km["out_in_map"][0], 13) == -1).all()
+    kd = ko.build_kmap(one, 2, 2, 0)
+    # x=4,y=5,z=6 -> output (2,2,3) exists only where the bound (max-1)//2 allows: x: (4-1)//2=1 < 2 -> dropped
+    assert kd["sizes"][1] == 0

@@ -1,0 +1,557 @@
+"""Tensor-level operator interface with the names, argument meaning and error
+behaviour of the reference's pybind module ``torchsparse.backend``
+(torchsparse/backend/pybind_cuda.cu:29-83), implemented over the tsb200 C ABI.
+
+Every function takes CUDA tensors, allocates its outputs with torch's caching
+allocator (as the reference's native functions do with ``torch::empty/zeros``),
+passes raw pointers plus torch's current stream to the library and raises
+``ValueError`` / ``RuntimeError`` on a bad status.  There is no CPU path: CPU
+tensors raise.
+
+Differences from the reference that callers can see:
+* kernels run on torch's *current* stream, not on the legacy default stream;
+* ``coords_min`` / ``coords_max`` / ``kernel_sizes`` / ``stride`` / ``padding`` may
+  be host tuples (preferred: no device read) as well as tensors;
+* hash-table probes are bounded; a full table raises instead of hanging.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import lib, check, i32x
+
+__all__ = [
+    "GPUHashTable", "build_kernel_map_subm_hashmap", "build_kernel_map_downsample_hashmap",
+    "build_mask_from_kmap", "convert_transposed_out_in_map", "derive_bitmask_from_out_in_map",
+    "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "exclusive_scan_quantified_wrapper",
+    "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda",
+    "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda",
+    "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
+    "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
+    "pairs_from_out_in_map", "quantize_unique_cuda",
+]
+
+_DTYPES = {torch.float32: _lib.TSB_F32, torch.float16: _lib.TSB_F16, torch.bfloat16: _lib.TSB_BF16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("torchsparse_b200.backend: CUDA tensors required (there is no CPU fallback)")
+
+
+def _host_ints(x, n: int) -> Tuple[int, ...]:
+    """Tuple of n ints from a tuple/list/int or a tensor (a device tensor costs a sync)."""
+    if isinstance(x, torch.Tensor):
+        x = x.detach().cpu().view(-1).tolist()
+    elif isinstance(x, int):
+        x = (x,) * n
+    x = tuple(int(v) for v in x)
+    if len(x) != n:
+        raise ValueError(f"expected {n} integers, got {x}")
+    return x
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"unsupported feature dtype {t.dtype}") from None
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _check_dev_status(status: torch.Tensor, what: str) -> None:
+    v = int(status.item())
+    if v & _lib.TSB_DEV_TABLE_FULL:
+        raise ValueError(
+            f"{what}: the capacity of the hash table is not sufficient; enlarge the reserved space "
+            "(torchsparse_b200.backends.hash_rsv_ratio)")
+    if v & _lib.TSB_DEV_BAD_INDEX:
+        raise RuntimeError(f"{what}: inconsistent hash table (an output coordinate was not found)")
+
+
+def pad128(n: int) -> int:
+    return (n + 127) // 128 * 128
+
+
+# --------------------------------------------------------------------------- hash table
+class GPUHashTable:
+    """Mirror of class GPUHashTable (torchsparse/backend/hashmap/hashmap_cuda.cuh:65-118):
+    either borrows ``(keys int64[cap], vals int32[cap])`` or owns a table of ``capacity``."""
+
+    def __init__(self, keys_or_capacity, vals: Optional[torch.Tensor] = None, device=None):
+        if isinstance(keys_or_capacity, int):
+            dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+            self.keys = torch.zeros(keys_or_capacity, dtype=torch.int64, device=dev)
+            self.vals = torch.zeros(keys_or_capacity, dtype=torch.int32, device=dev)
+        else:
+            self.keys, self.vals = keys_or_capacity, vals
+            _need_cuda(self.keys, self.vals)
+            if self.keys.dtype != torch.int64 or self.vals.dtype != torch.int32:
+                raise ValueError("GPUHashTable expects int64 keys and int32 values")
+            if self.keys.numel() != self.vals.numel() or not self.keys.is_contiguous() or not self.vals.is_contiguous():
+                raise ValueError("GPUHashTable: keys and vals must be contiguous and of equal length")
+        self.capacity = self.keys.numel()
+        self.divisor = 128
+
+    def get_capacity(self) -> int:
+        return self.capacity
+
+    def insert_vals(self, keys: torch.Tensor) -> None:
+        _need_cuda(keys)
+        keys = keys.contiguous()
+        status = torch.zeros(1, dtype=torch.int32, device=keys.device)
+        check(lib.tsb_hash_insert(_p(self.keys), _p(self.vals), self.capacity, _p(keys), keys.numel(), _p(status),
+                                  _stream()), "GPUHashTable.insert_vals")
+        _check_dev_status(status, "GPUHashTable.insert_vals")
+
+    def lookup_vals(self, keys: torch.Tensor) -> torch.Tensor:
+        _need_cuda(keys)
+        keys = keys.contiguous()
+        n = keys.numel()
+        out = torch.zeros(pad128(n), dtype=torch.int32, device=keys.device)
+        check(lib.tsb_hash_lookup(_p(self.keys), _p(self.vals), self.capacity, _p(keys), n, _p(out), _stream()),
+              "GPUHashTable.lookup_vals")
+        return out
+
+
+# --------------------------------------------------------------------------- kernel maps
+def build_kernel_map_subm_hashmap(table: GPUHashTable, coords: torch.Tensor, coords_min, coords_max, kernel_sizes,
+                                  stride=None, padding=None, to_insert: bool = True,
+                                  check_status: bool = True) -> List[torch.Tensor]:
+    """Returns ``[out_in_map]`` int32 [pad128(N), Kvol]
+    (torchsparse/backend/others/sparsemapping_cuda.cu:303-345)."""
+    _need_cuda(coords)
+    coords = coords.contiguous()
+    n = coords.shape[0]
+    ks = _host_ints(kernel_sizes, 3)
+    cmin, cmax = _host_ints(coords_min, 4), _host_ints(coords_max, 4)
+    kvol = ks[0] * ks[1] * ks[2]
+    out = torch.empty((pad128(n), kvol), dtype=torch.int32, device=coords.device)
+    status = torch.zeros(1, dtype=torch.int32, device=coords.device) if (to_insert and check_status) else None
+    check(lib.tsb_kmap_subm(_p(table.keys), _p(table.vals), table.capacity, _p(coords), n, i32x(cmin), i32x(cmax),
+                            i32x(ks), int(bool(to_insert)), _p(out), _p(status), _stream()),
+          "build_kernel_map_subm_hashmap")
+    if status is not None:
+        _check_dev_status(status, "build_kernel_map_subm_hashmap")
+    return [out]
+
+
+def downsample_unique(coords: torch.Tensor, coords_min, coords_max, kernel_sizes, stride, padding):
+    """First half of the strided map: sorted unique output keys plus the host-read
+    ``(M, output coords max)``.  One device->host read (the reference needs two)."""
+    coords = coords.contiguous()
+    n = coords.shape[0]
+    ks, st, pd = _host_ints(kernel_sizes, 3), _host_ints(stride, 3), _host_ints(padding, 3)
+    cmin, cmax = _host_ints(coords_min, 4), _host_ints(coords_max, 4)
+    a_ks, a_st = i32x(ks), i32x(st)
+    slots = lib.tsb_kmap_down_slots(a_ks, a_st)
+    if slots <= 0:
+        raise ValueError("build_kernel_map_downsample_hashmap: bad kernel size / stride")
+    uniq = torch.empty(max(n * slots, 1), dtype=torch.int64, device=coords.device)
+    result = torch.empty(8, dtype=torch.int32, device=coords.device)
+    ws = _workspace(lib.tsb_kmap_down_workspace_bytes(n, a_ks, a_st), coords.device)
+    check(lib.tsb_kmap_down_unique(_p(coords), n, i32x(cmin), i32x(cmax), a_ks, a_st, i32x(pd), _p(uniq), _p(result),
+                                   _p(ws), ws.numel(), _stream()), "build_kernel_map_downsample_hashmap")
+    res = result.cpu().tolist()  # the one synchronisation of the strided build
+    m = res[0]
+    out_max = tuple(res[1:5]) if m > 0 else None
+    return uniq, m, out_max
+
+
+def downsample_finish(table: GPUHashTable, coords: torch.Tensor, uniq: torch.Tensor, m: int, coords_min, coords_max,
+                      kernel_sizes, stride, padding, check_status: bool = True):
+    coords = coords.contiguous()
+    n = coords.shape[0]
+    ks, st, pd = _host_ints(kernel_sizes, 3), _host_ints(stride, 3), _host_ints(padding, 3)
+    cmin, cmax = _host_ints(coords_min, 4), _host_ints(coords_max, 4)
+    kvol = ks[0] * ks[1] * ks[2]
+    if table.capacity < m:
+        raise ValueError(
+            "The capacity of hashtable is not sufficient. Please enlarge reserved space for hashtable "
+            "(torchsparse_b200.backends.hash_rsv_ratio)")
+    out_coords = torch.empty((m, 4), dtype=torch.int32, device=coords.device)
+    out_in_map = torch.empty((pad128(m), kvol), dtype=torch.int32, device=coords.device)
+    status = torch.zeros(1, dtype=torch.int32, device=coords.device) if check_status else None
+    check(lib.tsb_kmap_down_finish(_p(table.keys), _p(table.vals), table.capacity, _p(coords), n, _p(uniq), m,
+                                   i32x(cmin), i32x(cmax), i32x(ks), i32x(st), i32x(pd), _p(out_coords),
+                                   _p(out_in_map), _p(status), _stream()), "build_kernel_map_downsample_hashmap")
+    if status is not None:
+        _check_dev_status(status, "build_kernel_map_downsample_hashmap")
+    return out_in_map, out_coords
+
+
+def build_kernel_map_downsample_hashmap(table: GPUHashTable, coords: torch.Tensor, coords_min, coords_max, kernel_sizes,
+                                        stride, padding, to_insert: bool = True) -> List[torch.Tensor]:
+    """Returns ``[out_in_map, out_coords]``
+    (torchsparse/backend/others/sparsemapping_cuda.cu:429-507).  ``coords_max`` is the
+    bound in output space.  The table receives the output coordinates."""
+    _need_cuda(coords)
+    uniq, m, _ = downsample_unique(coords, coords_min, coords_max, kernel_sizes, stride, padding)
+    out_in_map, out_coords = downsample_finish(table, coords, uniq, m, coords_min, coords_max, kernel_sizes, stride,
+                                               padding)
+    return [out_in_map, out_coords]
+
+
+def convert_transposed_out_in_map(out_in_map: torch.Tensor, out_in_map_t: torch.Tensor, fill: bool = False) -> None:
+    """Writes into ``out_in_map_t`` (pre-filled with -1 by the caller unless ``fill``)
+    (torchsparse/backend/others/query_cuda.cu:50-54)."""
+    _need_cuda(out_in_map, out_in_map_t)
+    check(lib.tsb_map_transpose(_p(out_in_map), out_in_map.shape[0], out_in_map.shape[1], _p(out_in_map_t),
+                                out_in_map_t.shape[0], int(fill), _stream()), "convert_transposed_out_in_map")
+
+
+def derive_bitmask_from_out_in_map(out_in_map: torch.Tensor, split_mask_num: int, valid_n: int) -> torch.Tensor:
+    """int32 [split, rows] (torchsparse/backend/others/query_cuda.cu:59-65)."""
+    _need_cuda(out_in_map)
+    rows, kvol = out_in_map.shape
+    out = torch.empty((split_mask_num, rows), dtype=torch.int32, device=out_in_map.device)
+    check(lib.tsb_bitmask_derive(_p(out_in_map), rows, kvol, split_mask_num, valid_n, _p(out), _stream()),
+          "derive_bitmask_from_out_in_map")
+    return out
+
+
+def sort_bitmask_cuda(bitmask: torch.Tensor, kvol: int = 27) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Stable descending sort per split -> (sorted_mask, reorder_loc int32).  Stands in for the
+    ``torch.sort(bitmask, descending=True)`` of
+    torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:96."""
+    _need_cuda(bitmask)
+    split, rows = bitmask.shape
+    sorted_mask = torch.empty_like(bitmask)
+    loc = torch.empty_like(bitmask)
+    ws = _workspace(lib.tsb_bitmask_sort_workspace_bytes(rows, split), bitmask.device)
+    check(lib.tsb_bitmask_sort(_p(bitmask), rows, split, kvol, _p(sorted_mask), _p(loc), _p(ws), ws.numel(),
+                               _stream()), "sort_bitmask_cuda")
+    return sorted_mask, loc
+
+
+def reduce_bitmask_cuda(bitmask: torch.Tensor, m_tile: int) -> torch.Tensor:
+    """int32 [split, ceil(rows/tile)] (torchsparse/backend/others/reduce_bitmask_cuda.cu:60-87)."""
+    _need_cuda(bitmask)
+    if m_tile % 4 != 0:
+        raise RuntimeError("[Bitmask reduce] reduce tile size must be multiple of 4.")
+    split, rows = bitmask.shape
+    n_red = (rows - 1) // m_tile + 1
+    out = torch.empty((split, n_red), dtype=torch.int32, device=bitmask.device)
+    check(lib.tsb_bitmask_reduce(_p(bitmask), rows, split, m_tile, _p(out), _stream()), "reduce_bitmask_cuda")
+    return out
+
+
+def reorder_out_in_map_cuda(out_in_map: torch.Tensor, reorder_loc: torch.Tensor) -> torch.Tensor:
+    """(torchsparse/backend/others/reorder_map_cuda.cu:25-47)."""
+    _need_cuda(out_in_map, reorder_loc)
+    rows, kvol = out_in_map.shape
+    out = torch.empty_like(out_in_map)
+    check(lib.tsb_map_reorder(_p(out_in_map), rows, kvol, _p(reorder_loc.contiguous()), reorder_loc.shape[0], _p(out),
+                              _stream()), "reorder_out_in_map_cuda")
+    return out
+
+
+def exclusive_scan_quantified_wrapper(k_vol: int, nbsizes: torch.Tensor, nbaddrs: torch.Tensor,
+                                      qnbaddrs: torch.Tensor) -> torch.Tensor:
+    """Writes the two scans into its arguments and returns a dummy tensor
+    (torchsparse/backend/others/exclusive_scan_cuda.cu:31-44)."""
+    _need_cuda(nbsizes, nbaddrs, qnbaddrs)
+    check(lib.tsb_scan_quantified(k_vol, _p(nbsizes), _p(nbaddrs), _p(qnbaddrs), _stream()),
+          "exclusive_scan_quantified_wrapper")
+    return torch.zeros(1)
+
+
+def pairs_from_out_in_map(out_in_map: torch.Tensor, transposed_layout: bool):
+    """Pair lists of the GatherScatter / FetchOnDemand dataflows from an out_in_map, in one
+    counting pass and one fill pass (replaces the torch ``nonzero``/``sum``/gather chain of
+    torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:138-141).
+
+    Returns (nbmaps int32 [P,2] or [2,P], nbsizes int32 [Kvol] device, nbsizes host list,
+    nbaddrs int32 [Kvol+1], qnbaddrs int32 [Kvol+1], qmapsize int)."""
+    _need_cuda(out_in_map)
+    rows, kvol = out_in_map.shape
+    dev = out_in_map.device
+    scans = torch.empty(3 * (kvol + 1), dtype=torch.int32, device=dev)
+    nbsizes, nbaddrs, qnbaddrs = scans[:kvol], scans[kvol + 1:2 * kvol + 2], scans[2 * kvol + 2:]
+    check(lib.tsb_pairs_count(_p(out_in_map), rows, kvol, _p(nbsizes), _p(nbaddrs), _p(qnbaddrs), _stream()),
+          "pairs_from_out_in_map")
+    host = scans.cpu().tolist()  # one synchronisation; the reference reads nbsizes on the host too
+    sizes_host = host[:kvol]
+    n_pairs = host[2 * kvol + 1]
+    qmapsize = host[-1]
+    shape = (2, n_pairs) if transposed_layout else (n_pairs, 2)
+    nbmaps = torch.empty(shape, dtype=torch.int32, device=dev)
+    ws = _workspace(lib.tsb_pairs_fill_workspace_bytes(rows, kvol), dev)
+    check(lib.tsb_pairs_fill(_p(out_in_map), rows, kvol, _p(nbaddrs), n_pairs, int(transposed_layout), _p(nbmaps),
+                             _p(ws), ws.numel(), _stream()), "pairs_from_out_in_map")
+    return nbmaps, nbsizes, sizes_host, nbaddrs, qnbaddrs, qmapsize
+
+
+def build_mask_from_kmap(n_points: int, n_out_points: int, nbmaps: torch.Tensor,
+                         nbsizes: torch.Tensor) -> List[torch.Tensor]:
+    """Returns ``[input_mask, output_mask]``
+    (torchsparse/backend/others/sparsemapping_cuda.cu:510-548)."""
+    _need_cuda(nbmaps, nbsizes)
+    nbmaps = nbmaps.int().contiguous()
+    kvol = nbsizes.numel()
+    dev = nbmaps.device
+    nbaddrs = torch.zeros(kvol + 1, dtype=torch.int32, device=dev)
+    nbaddrs[1:] = torch.cumsum(nbsizes.int(), 0)
+    n_pairs = nbmaps.shape[0]
+    input_mask = torch.empty(kvol * n_points, dtype=torch.int32, device=dev)
+    output_mask = torch.empty(kvol * n_out_points, dtype=torch.int32, device=dev)
+    check(lib.tsb_build_masks(n_points, n_out_points, _p(nbmaps), _p(nbaddrs), kvol, n_pairs, _p(input_mask),
+                              _p(output_mask), _stream()), "build_mask_from_kmap")
+    return [input_mask, output_mask]
+
+
+# --------------------------------------------------------------------------- convolution
+def _math_mode(t: torch.Tensor, allow_tf32: bool) -> int:
+    return _lib.TSB_MATH_TF32 if (t.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
+
+
+def _prep_feats(in_feats: torch.Tensor, kernel: torch.Tensor, allow_fp16: bool):
+    _need_cuda(in_feats, kernel)
+    if in_feats.dtype != kernel.dtype:
+        raise RuntimeError("input features and kernel must share a dtype")
+    if in_feats.dtype == torch.float16 and not allow_fp16:
+        raise RuntimeError("fp16 convolution requested but allow_fp16 is off")
+    if kernel.dim() != 3:
+        raise ValueError("kernel must be [Kvol, Cin, Cout]")
+    if in_feats.shape[1] != kernel.shape[1]:
+        raise ValueError("Input feature size and kernel size mismatch")
+    return in_feats.contiguous(), kernel.contiguous()
+
+
+def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,
+                                    num_out_feats: int, num_out_channels: int, allow_tf32: bool = False,
+                                    allow_fp16: bool = True, *, bias: Optional[torch.Tensor] = None,
+                                    residual: Optional[torch.Tensor] = None, relu: bool = False,
+                                    reorder_loc: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Implicit-GEMM forward
+    (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987).
+    ``bias`` (fp32), ``residual`` and ``relu`` are an optional fused epilogue the reference
+    does not have."""
+    in_feats, kernel = _prep_feats(in_feats, kernel, allow_fp16)
+    _need_cuda(out_in_map)
+    kvol, cin, cout = kernel.shape
+    if num_out_channels != cout:
+        raise ValueError("num_out_channels does not match the kernel")
+    if out_in_map.shape[1] != kvol or out_in_map.shape[0] < num_out_feats:
+        raise ValueError("out_in_map shape does not match kernel volume / output rows")
+    out = torch.empty((num_out_feats, cout), dtype=in_feats.dtype, device=in_feats.device)
+    code = _dtype_code(in_feats)
+    ws = _workspace(lib.tsb_conv_igemm_workspace_bytes(kvol, cin, cout, code), in_feats.device)
+    if bias is not None:
+        bias = bias.float().contiguous()
+    if residual is not None:
+        residual = residual.to(in_feats.dtype).contiguous()
+    check(lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(out_in_map), _p(reorder_loc), _p(out),
+                                 in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
+                                 _math_mode(in_feats, allow_tf32), _p(bias), _p(residual), int(relu), _p(ws),
+                                 ws.numel(), _stream()), "conv_forward_implicit_gemm_cuda")
+    return out
+
+
+def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,
+                                           reduced_mask: torch.Tensor, reorder_loc: torch.Tensor, num_out_feats: int,
+                                           num_out_channels: int, allow_tf32: bool = False,
+                                           allow_fp16: bool = True, **epilogue) -> torch.Tensor:
+    """Sorted implicit-GEMM forward
+    (torchsparse/backend/convolution/convolution_forward_implicit_gemm_sorted_cuda.cu:1755-2230).
+    ``out_in_map`` is the row-reordered map; output row r is stored at ``reorder_loc[s][r]``.
+    With split_mask_num > 1 each split covers its own column range with its own row order; the
+    splits are accumulated in fp32 here instead of being rounded and summed."""
+    split = reorder_loc.shape[0] if reorder_loc.dim() == 2 else 1
+    loc = reorder_loc.reshape(split, -1).contiguous()
+    if split == 1:
+        return conv_forward_implicit_gemm_cuda(in_feats, kernel, out_in_map, num_out_feats, num_out_channels,
+                                               allow_tf32, allow_fp16, reorder_loc=loc[0], **epilogue)
+    kvol = kernel.shape[0]
+    split_len = (kvol + split - 1) // split
+    acc = None
+    for s in range(split):
+        lo, hi = s * split_len, min(kvol, (s + 1) * split_len)
+        part = conv_forward_implicit_gemm_cuda(in_feats.float(), kernel[lo:hi].float(),
+                                               out_in_map[:, lo:hi].contiguous(), num_out_feats, num_out_channels,
+                                               False, allow_fp16, reorder_loc=loc[s])
+        acc = part if acc is None else acc + part
+    bias, residual, relu = epilogue.get("bias"), epilogue.get("residual"), epilogue.get("relu", False)
+    if bias is not None:
+        acc = acc + bias
+    if residual is not None:
+        acc = acc + residual
+    if relu:
+        acc = torch.relu(acc)
+    return acc.to(in_feats.dtype)
+
+
+def conv_forward_gather_scatter_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, nbmaps: torch.Tensor,
+                                     nbsizes_cpu: torch.Tensor, input_mask: torch.Tensor, output_mask: torch.Tensor,
+                                     output_size: int, epsilon: float = 0.0, mm_thresh: int = 0, conv_mode: int = 0,
+                                     transpose: bool = False, buffer: Optional[torch.Tensor] = None,
+                                     allow_tf32: bool = False) -> torch.Tensor:
+    """Gather -> grouped GEMM -> scatter
+    (torchsparse/backend/convolution/convolution_gather_scatter_cuda.cu:279-311).
+    ``epsilon`` / ``mm_thresh`` / ``conv_mode`` / ``buffer`` steer the reference's cuBLAS
+    grouping heuristics; this implementation has one grouped GEMM and ignores them."""
+    in_feats, kernel = _prep_feats(in_feats, kernel, True)
+    _need_cuda(nbmaps, input_mask, output_mask)
+    kvol, cin, cout = kernel.shape
+    sizes = [int(v) for v in (nbsizes_cpu.tolist() if isinstance(nbsizes_cpu, torch.Tensor) else nbsizes_cpu)]
+    if len(sizes) != kvol:
+        raise ValueError("nbsizes does not match the kernel volume")
+    n_pairs = sum(sizes)
+    nbmaps = nbmaps.int().contiguous()
+    out = torch.empty((output_size, cout), dtype=in_feats.dtype, device=in_feats.device)
+    code = _dtype_code(in_feats)
+    ws = _workspace(lib.tsb_conv_gs_workspace_bytes(n_pairs, kvol, cin, cout, code), in_feats.device)
+    mask = input_mask if transpose else output_mask
+    check(lib.tsb_conv_gs_fwd(_p(in_feats), _p(kernel), _p(nbmaps), i32x(sizes), _p(mask), _p(out),
+                              in_feats.shape[0], output_size, kvol, cin, cout, code, _math_mode(in_feats, allow_tf32),
+                              int(bool(transpose)), _p(ws), ws.numel(), _stream()),
+          "conv_forward_gather_scatter_cuda")
+    return out
+
+
+def conv_forward_fetch_on_demand_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, nbmaps: torch.Tensor,
+                                      mapsize: int, nbaddrs: torch.Tensor, qnbaddrs: torch.Tensor, output_size: int,
+                                      qmapsize, transpose: bool = False, allow_tf32: bool = False,
+                                      allow_fp16: bool = True) -> torch.Tensor:
+    """Fused fetch-on-demand forward
+    (torchsparse/backend/convolution/convolution_forward_fetch_on_demand_cuda.cu:1981-2133)."""
+    in_feats, kernel = _prep_feats(in_feats, kernel, allow_fp16)
+    _need_cuda(nbmaps, nbaddrs, qnbaddrs)
+    kvol, cin, cout = kernel.shape
+    nbmaps = nbmaps.int().contiguous()
+    out = torch.empty((output_size, cout), dtype=in_feats.dtype, device=in_feats.device)
+    code = _dtype_code(in_feats)
+    ws = _workspace(lib.tsb_conv_fod_workspace_bytes(output_size, cout, code), in_feats.device)
+    check(lib.tsb_conv_fod_fwd(_p(in_feats), _p(kernel), _p(nbmaps), int(mapsize), _p(nbaddrs), _p(qnbaddrs),
+                               int(qmapsize), _p(out), in_feats.shape[0], output_size, kvol, cin, cout, code,
+                               _math_mode(in_feats, allow_tf32), int(bool(transpose)), _p(ws), ws.numel(), _stream()),
+          "conv_forward_fetch_on_demand_cuda")
+    return out
+
+
+def conv_forward_fetch_on_demand_no_fusion_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, nbmaps: torch.Tensor,
+                                                nbsizes_cpu: torch.Tensor, mapsize: int, output_size: int,
+                                                transpose: bool = False, allow_tf32: bool = False,
+                                                allow_fp16: bool = True) -> torch.Tensor:
+    """Per-offset variant of the reference (convolution_forward_fetch_on_demand_cuda.cu:2136-2260).
+    Here it derives the scans and runs the same fused launch: the result is identical."""
+    kvol = kernel.shape[0]
+    sizes = nbsizes_cpu.to(device=in_feats.device, dtype=torch.int32).contiguous()
+    nbaddrs = torch.empty(kvol + 1, dtype=torch.int32, device=in_feats.device)
+    qnbaddrs = torch.empty(kvol + 1, dtype=torch.int32, device=in_feats.device)
+    exclusive_scan_quantified_wrapper(kvol, sizes, nbaddrs, qnbaddrs)
+    qmapsize = sum((int(v) + 127) // 128 * 128 for v in nbsizes_cpu.tolist())
+    return conv_forward_fetch_on_demand_cuda(in_feats, kernel, nbmaps, mapsize, nbaddrs, qnbaddrs, output_size,
+                                             qmapsize, transpose, allow_tf32, allow_fp16)
+
+
+# --------------------------------------------------------------------------- point / voxel ops
+def hash_cuda(coords: torch.Tensor) -> torch.Tensor:
+    """(torchsparse/backend/hash/hash_cuda.cu:66-72)."""
+    _need_cuda(coords)
+    coords = coords.contiguous()
+    out = torch.empty(coords.shape[0], dtype=torch.int64, device=coords.device)
+    check(lib.tsb_coord_hash(_p(coords), coords.shape[0], _p(out), _stream()), "hash_cuda")
+    return out
+
+
+def kernel_hash_cuda(coords: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """(torchsparse/backend/hash/hash_cuda.cu:74-83)."""
+    _need_cuda(coords, offsets)
+    coords, offsets = coords.contiguous(), offsets.contiguous()
+    out = torch.empty((offsets.shape[0], coords.shape[0]), dtype=torch.int64, device=coords.device)
+    check(lib.tsb_kernel_hash(_p(coords), coords.shape[0], _p(offsets), offsets.shape[0], _p(out), _stream()),
+          "kernel_hash_cuda")
+    return out
+
+
+def hash_query_cuda(queries: torch.Tensor, references: torch.Tensor, indices: Optional[torch.Tensor] = None):
+    """Row of each query hash inside ``references`` plus one (0 = absent), like the
+    reference entry (torchsparse/backend/others/query_cuda.cu:33-47)."""
+    _need_cuda(queries, references)
+    queries, references = queries.contiguous(), references.contiguous()
+    out = torch.empty(queries.numel(), dtype=torch.int64, device=queries.device)
+    ws = _workspace(lib.tsb_hash_query_workspace_bytes(references.numel()), queries.device)
+    check(lib.tsb_hash_query(_p(queries), queries.numel(), _p(references), references.numel(), _p(out), _p(ws),
+                             ws.numel(), _stream()), "hash_query_cuda")
+    return out + 1
+
+
+def count_cuda(idx: torch.Tensor, s: int) -> torch.Tensor:
+    """(torchsparse/backend/others/count_cuda.cu:25-31)."""
+    _need_cuda(idx)
+    idx = idx.int().contiguous()
+    out = torch.empty(int(s), dtype=torch.int32, device=idx.device)
+    check(lib.tsb_count(_p(idx), idx.numel(), _p(out), int(s), _stream()), "count_cuda")
+    return out
+
+
+def voxelize_forward_cuda(feats: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """Average pooling of point features into voxels; fp32 accumulation, returned in the
+    feature dtype (torchsparse/backend/voxelize/voxelize_cuda.cu:78-95)."""
+    _need_cuda(feats, idx, counts)
+    feats, idx, counts = feats.contiguous(), idx.int().contiguous(), counts.int().contiguous()
+    n, c = feats.shape
+    out = torch.empty((counts.shape[0], c), dtype=torch.float32, device=feats.device)
+    check(lib.tsb_voxelize_fwd(_p(feats), _p(idx), _p(counts), n, counts.shape[0], c, _dtype_code(feats), _p(out),
+                               _stream()), "voxelize_forward_cuda")
+    return out.to(feats.dtype)
+
+
+def devoxelize_forward_cuda(feat: torch.Tensor, indices: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """(torchsparse/backend/devoxelize/devoxelize_cuda.cu:61-78)."""
+    _need_cuda(feat, indices, weight)
+    feat, indices, weight = feat.contiguous(), indices.int().contiguous(), weight.float().contiguous()
+    n, c = indices.shape[0], feat.shape[1]
+    out = torch.empty((n, c), dtype=feat.dtype, device=feat.device)
+    check(lib.tsb_devoxelize_fwd(_p(feat), _p(indices), _p(weight), n, c, _dtype_code(feat), _p(out), _stream()),
+          "devoxelize_forward_cuda")
+    return out
+
+
+def to_dense_forward_cuda(feats: torch.Tensor, coords: torch.Tensor, spatial_range, outputs: torch.Tensor) -> None:
+    """Scatter into the caller's zero-initialised dense tensor
+    (torchsparse/backend/voxelize/voxelize_cuda.cu:116-127)."""
+    _need_cuda(feats, coords, outputs)
+    rng = _host_ints(spatial_range, 4)
+    feats, coords = feats.contiguous(), coords.int().contiguous()
+    check(lib.tsb_to_dense_fwd(_p(feats), _p(coords), feats.shape[0], feats.shape[1], i32x(rng), _dtype_code(feats),
+                               _p(outputs), _stream()), "to_dense_forward_cuda")
+
+
+def quantize_unique_cuda(xyz: torch.Tensor, voxel_size: Sequence[float], return_index: bool, return_inverse: bool):
+    """GPU twin of ``sparse_quantize`` (torchsparse/utils/quantize.py:24-48): returns
+    (coords int32 [Nv,3], first_index int64 [Nv] or None, inverse int64 [Np] or None)."""
+    import ctypes
+    _need_cuda(xyz)
+    if xyz.dtype not in (torch.float32, torch.float64):
+        xyz = xyz.double()
+    xyz = xyz.contiguous()
+    n = xyz.shape[0]
+    dev = xyz.device
+    q_all = torch.empty((n, 3), dtype=torch.int32, device=dev)
+    uniq = torch.empty((n, 3), dtype=torch.int32, device=dev)
+    first = torch.empty(n, dtype=torch.int64, device=dev) if return_index else None
+    inv = torch.empty(n, dtype=torch.int64, device=dev) if return_inverse else None
+    result = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws = _workspace(lib.tsb_quantize_workspace_bytes(n), dev)
+    vox = (ctypes.c_double * 3)(*[float(v) for v in voxel_size])
+    check(lib.tsb_quantize_unique(_p(xyz), int(xyz.dtype == torch.float64), n, vox, _p(q_all), _p(uniq), _p(first),
+                                  _p(inv), _p(result), _p(ws), ws.numel(), _stream()), "quantize_unique_cuda")
+    nv = int(result.item())
+    return uniq[:nv], (first[:nv] if first is not None else None), inv

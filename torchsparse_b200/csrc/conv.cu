@@ -1,0 +1,79 @@
+// C ABI of the convolution forward entry points and the choice between the tcgen05
+// (tensor-core) kernels and the CUDA-core kernels.
+#include "common.cuh"
+#include "conv_dispatch.h"
+
+using namespace tsb;
+
+namespace {
+bool valid_dtype(int d) { return d == TSB_F32 || d == TSB_F16 || d == TSB_BF16; }
+}  // namespace
+
+extern "C" {
+
+size_t tsb_conv_igemm_workspace_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {
+  if (kvol < 1 || cin < 1 || cout < 1 || !valid_dtype(dtype)) return 0;
+  return igemm_umma_workspace_bytes(kvol, cin, cout, dtype);
+}
+
+int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const int32_t* out_in_map,
+                       const int32_t* reorder_loc, void* out_feats, int64_t n_in, int64_t n_out, int32_t kvol,
+                       int32_t cin, int32_t cout, int32_t dtype, int32_t math, const float* bias,
+                       const void* residual, int32_t relu, void* workspace, size_t workspace_bytes,
+                       tsb_stream_t stream) {
+  if (n_in < 0 || n_out < 0 || kvol < 1 || cin < 1 || cout < 1) return TSB_ERR_BAD_ARG;
+  if (!valid_dtype(dtype)) return TSB_ERR_UNSUPPORTED;
+  if (n_out == 0) return TSB_OK;
+  if (!weight || !out_in_map || !out_feats || (n_in && !in_feats)) return TSB_ERR_BAD_ARG;
+  if (n_in > INT32_MAX || n_out > INT32_MAX) return TSB_ERR_LIMIT;
+  IgemmArgs a{in_feats, weight, out_in_map, reorder_loc, out_feats, n_in, n_out, kvol, cin, cout, dtype, math,
+              bias, residual, relu, workspace, workspace_bytes};
+  if (igemm_umma_supported(a)) return igemm_umma(a, as_stream(stream));
+  return igemm_simt(a, as_stream(stream));
+}
+
+size_t tsb_conv_gs_workspace_bytes(int64_t n_pairs, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {
+  if (n_pairs < 0 || kvol < 1 || cin < 1 || cout < 1 || !valid_dtype(dtype)) return 0;
+  return gs_workspace_bytes(n_pairs, kvol, cin, cout, dtype);
+}
+
+int tsb_conv_gs_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps, const int32_t* nbsizes_host,
+                    const int32_t* scatter_mask, void* out_feats, int64_t n_in, int64_t n_out, int32_t kvol,
+                    int32_t cin, int32_t cout, int32_t dtype, int32_t math, int32_t transpose, void* workspace,
+                    size_t workspace_bytes, tsb_stream_t stream) {
+  if (n_in < 0 || n_out < 0 || kvol < 1 || cin < 1 || cout < 1 || !nbsizes_host) return TSB_ERR_BAD_ARG;
+  if (!valid_dtype(dtype)) return TSB_ERR_UNSUPPORTED;
+  if (n_out == 0) return TSB_OK;
+  int64_t n_pairs = 0;
+  for (int k = 0; k < kvol; ++k) {
+    if (nbsizes_host[k] < 0) return TSB_ERR_BAD_ARG;
+    n_pairs += nbsizes_host[k];
+  }
+  if (!weight || !out_feats || !scatter_mask || (n_pairs && (!nbmaps || !in_feats))) return TSB_ERR_BAD_ARG;
+  if (n_pairs > INT32_MAX) return TSB_ERR_LIMIT;
+  GsArgs a{in_feats, weight, nbmaps, nbsizes_host, scatter_mask, out_feats, n_in, n_out, n_pairs, kvol, cin, cout,
+           dtype, math, transpose, workspace, workspace_bytes};
+  return gs_simt(a, as_stream(stream));
+}
+
+size_t tsb_conv_fod_workspace_bytes(int64_t n_out, int32_t cout, int32_t dtype) {
+  if (n_out < 0 || cout < 1 || !valid_dtype(dtype)) return 0;
+  if (dtype == TSB_F32) return 256;
+  return align_up((size_t)n_out * cout * sizeof(float), 256) + 256;
+}
+
+int tsb_conv_fod_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps, int64_t n_pairs,
+                     const int32_t* nbaddrs, const int32_t* qnbaddrs, int64_t qmapsize, void* out_feats,
+                     int64_t n_in, int64_t n_out, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype,
+                     int32_t math, int32_t transpose, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (n_in < 0 || n_out < 0 || n_pairs < 0 || qmapsize < 0 || kvol < 1 || cin < 1 || cout < 1) return TSB_ERR_BAD_ARG;
+  if (!valid_dtype(dtype)) return TSB_ERR_UNSUPPORTED;
+  if (n_out == 0) return TSB_OK;
+  if (!weight || !out_feats || !nbaddrs || !qnbaddrs || (n_pairs && (!nbmaps || !in_feats))) return TSB_ERR_BAD_ARG;
+  if (qmapsize > INT32_MAX || n_pairs > INT32_MAX) return TSB_ERR_LIMIT;
+  FodArgs a{in_feats, weight, nbmaps, nbaddrs, qnbaddrs, out_feats, n_in, n_out, n_pairs, qmapsize, kvol, cin, cout,
+            dtype, math, transpose, workspace, workspace_bytes};
+  return fod_simt(a, as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,62 @@
+// Argument bundles and entry points shared by the convolution translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace tsb {
+
+struct IgemmArgs {
+  const void* x;
+  const void* w;
+  const int* map;
+  const int* reorder_loc;
+  void* y;
+  int64_t n_in, n_out;
+  int kvol, cin, cout, dtype, math;
+  const float* bias;
+  const void* residual;
+  int relu;
+  void* workspace;
+  size_t workspace_bytes;
+};
+
+struct GsArgs {
+  const void* x;
+  const void* w;
+  const int* nbmaps;        // [P,2]
+  const int* nbsizes_host;  // [kvol]
+  const int* scatter_mask;  // [kvol * n_out]
+  void* y;
+  int64_t n_in, n_out, n_pairs;
+  int kvol, cin, cout, dtype, math, transpose;
+  void* workspace;
+  size_t workspace_bytes;
+};
+
+struct FodArgs {
+  const void* x;
+  const void* w;
+  const int* nbmaps;  // [2,P]
+  const int* nbaddrs;
+  const int* qnbaddrs;
+  void* y;
+  int64_t n_in, n_out, n_pairs, qmapsize;
+  int kvol, cin, cout, dtype, math, transpose;
+  void* workspace;
+  size_t workspace_bytes;
+};
+
+// CUDA-core kernels (conv_simt.cu)
+int igemm_simt(const IgemmArgs& a, cudaStream_t s);
+int gs_simt(const GsArgs& a, cudaStream_t s);
+int fod_simt(const FodArgs& a, cudaStream_t s);
+size_t gs_workspace_bytes(int64_t n_pairs, int kvol, int cin, int cout, int dtype);
+
+// tcgen05 kernels (conv_umma.cu)
+bool igemm_umma_supported(const IgemmArgs& a);
+size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype);
+int igemm_umma(const IgemmArgs& a, cudaStream_t s);
+
+}  // namespace tsb

@@ -1,0 +1,823 @@
+// Coordinate hashing, the GPU hash table and kernel-map construction
+// (submanifold, strided, transposed) plus the sorted-map artefacts and the pair
+// lists of the GatherScatter / FetchOnDemand dataflows.
+//
+// All of this is integer, HBM/L2-latency bound work: one pass over the coordinates
+// and one write of the map, with random 8-byte probes into an L2-resident table.
+#include <cub/cub.cuh>
+
+#include "common.cuh"
+
+namespace tsb {
+
+namespace {
+
+constexpr int kBlock = 256;
+
+// ------------------------------------------------------------------ hashing
+__device__ __forceinline__ uint64_t fnv1a4(int c0, int c1, int c2, int c3) {
+  uint64_t h = 14695981039346656037ULL;
+  h ^= (unsigned int)c0; h *= 1099511628211ULL;
+  h ^= (unsigned int)c1; h *= 1099511628211ULL;
+  h ^= (unsigned int)c2; h *= 1099511628211ULL;
+  h ^= (unsigned int)c3; h *= 1099511628211ULL;
+  return h;
+}
+
+__global__ void coord_hash_kernel(const int4* __restrict__ coords, int64_t n, int64_t* __restrict__ out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int4 c = __ldg(&coords[i]);
+    out[i] = (int64_t)fnv1a4(c.x, c.y, c.z, c.w);
+  }
+}
+
+// one thread per coordinate; the k hashes of a coordinate are written with stride n so
+// that each warp stores 256 contiguous bytes per offset.
+__global__ void kernel_hash_kernel(const int4* __restrict__ coords, int64_t n, const int* __restrict__ offsets,
+                                   int k, int64_t* __restrict__ out) {
+  extern __shared__ int s_off[];
+  for (int i = threadIdx.x; i < k * 3; i += blockDim.x) s_off[i] = offsets[i];
+  __syncthreads();
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int4 c = __ldg(&coords[i]);
+    for (int j = 0; j < k; ++j) {
+      out[(int64_t)j * n + i] = (int64_t)fnv1a4(c.x, c.y + s_off[j * 3], c.z + s_off[j * 3 + 1], c.w + s_off[j * 3 + 2]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ table
+__global__ void table_insert_kernel(TableView t, const int64_t* __restrict__ keys, int64_t n, int* status) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    if (!table_insert(t, (unsigned long long)keys[i], (int)(i + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+  }
+}
+
+__global__ void table_lookup_kernel(TableView t, const int64_t* __restrict__ keys, int64_t n, int* __restrict__ out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    out[i] = table_lookup(t, (unsigned long long)keys[i]);
+  }
+}
+
+__global__ void table_query_kernel(TableView t, const int64_t* __restrict__ keys, int64_t n, int64_t* __restrict__ out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    out[i] = (int64_t)table_lookup(t, (unsigned long long)keys[i]) - 1;
+  }
+}
+
+// ------------------------------------------------------------------ submanifold map
+// Insert every coordinate (key = ravel+1, value = row+1) and fill the map with -1.
+// The fill is block-cooperative: a block owns kBlock consecutive rows, i.e. one
+// contiguous range of kBlock*kvol ints.
+__global__ void subm_insert_fill_kernel(TableView t, const int4* __restrict__ coords, int64_t n, int64_t rows_pad,
+                                        Bounds b, int kvol, int to_insert, int* __restrict__ map, int* status) {
+  int64_t row0 = (int64_t)blockIdx.x * kBlock;
+  int64_t row = row0 + threadIdx.x;
+  if (to_insert && row < n) {
+    int4 c = __ldg(&coords[row]);
+    int64_t key = ravel4(b, c.x, c.y, c.z, c.w);
+    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+  }
+  int64_t lo = row0 * kvol;
+  int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kBlock) map[i] = -1;
+}
+
+// Odd kernel volume: thread per (row, k < kvol/2); hit -> write [row][k] and the mirrored
+// [nbr][kvol-1-k].  Thread k == 0 of a row also writes the centre column.
+__global__ void subm_query_odd_kernel(TableView t, const int4* __restrict__ coords, int64_t n, Bounds b,
+                                      KernelGeom g, int* __restrict__ map) {
+  const int half = g.kvol / 2;
+  const int64_t total = n * (int64_t)max(half, 1);
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = half ? tid / half : tid;
+    int k = half ? (int)(tid - row * half) : 0;
+    if (k == 0) map[row * g.kvol + half] = (int)row;
+    if (!half) continue;
+    int dx, dy, dz;
+    kernel_digits(g, k, dx, dy, dz);
+    int4 c = __ldg(&coords[row]);
+    int x = c.y + dx - (g.ks[0] - 1) / 2;
+    int y = c.z + dy - (g.ks[1] - 1) / 2;
+    int z = c.w + dz - (g.ks[2] - 1) / 2;
+    if (!in_bounds_xyz(b, x, y, z)) continue;
+    int64_t key = ravel4(b, c.x, x, y, z);
+    int nbr = table_lookup(t, (unsigned long long)(key + 1)) - 1;
+    if (nbr >= 0) {
+      map[row * g.kvol + k] = nbr;
+      map[(int64_t)nbr * g.kvol + (g.kvol - 1 - k)] = (int)row;
+    }
+  }
+}
+
+// Even kernel volume: thread per (row, k); offsets are the raw digits (not centred).
+__global__ void subm_query_even_kernel(TableView t, const int4* __restrict__ coords, int64_t n, Bounds b,
+                                       KernelGeom g, int* __restrict__ map) {
+  const int64_t total = n * (int64_t)g.kvol;
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = tid / g.kvol;
+    int k = (int)(tid - row * g.kvol);
+    int dx, dy, dz;
+    kernel_digits(g, k, dx, dy, dz);
+    int4 c = __ldg(&coords[row]);
+    int x = c.y + dx, y = c.z + dy, z = c.w + dz;
+    if (!in_bounds_xyz(b, x, y, z)) continue;
+    int64_t key = ravel4(b, c.x, x, y, z);
+    int nbr = table_lookup(t, (unsigned long long)(key + 1)) - 1;
+    if (nbr >= 0) map[tid] = nbr;
+  }
+}
+
+// ------------------------------------------------------------------ strided map
+// Number of kernel digits d' in [0,k) with (c + p - (k-1) + d') divisible by s is at most
+// ceil(k/s) per dim; `slots` is the product over dims.
+struct SlotGeom {
+  int per[3];
+  int slots;
+};
+
+inline SlotGeom make_slots(const int32_t* ks, const int32_t* st) {
+  SlotGeom s;
+  s.slots = 1;
+  for (int i = 0; i < 3; ++i) {
+    s.per[i] = (ks[i] + st[i] - 1) / st[i];
+    s.slots *= s.per[i];
+  }
+  return s;
+}
+
+__device__ __forceinline__ int pos_mod(int a, int m) {
+  int r = a % m;
+  return r < 0 ? r + m : r;
+}
+
+// thread per (input, slot): the slot-th admissible digit combination -> candidate key,
+// or `sentinel` when that combination does not exist / falls outside the bounds.
+__global__ void down_candidates_kernel(const int4* __restrict__ coords, int64_t n, Bounds b, KernelGeom g,
+                                       SlotGeom sg, int64_t sentinel, int64_t* __restrict__ cand) {
+  const int64_t total = n * (int64_t)sg.slots;
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = tid / sg.slots;
+    int j = (int)(tid - row * sg.slots);
+    int4 c = __ldg(&coords[row]);
+    int in[3] = {c.y, c.z, c.w};
+    int o[3];
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      int t = j % sg.per[i];
+      j /= sg.per[i];
+      int base = in[i] + g.pd[i] - (g.ks[i] - 1);
+      int d = pos_mod(-base, g.st[i]) + t * g.st[i];
+      ok = ok && (d < g.ks[i]);
+      o[i] = (base + d) / g.st[i];  // exact when ok
+    }
+    ok = ok && in_bounds_xyz(b, o[0], o[1], o[2]);
+    cand[tid] = ok ? ravel4(b, c.x, o[0], o[1], o[2]) : sentinel;
+  }
+}
+
+// result[0] = number of outputs (unique keys minus the sentinel); result[1..4] = 0 for the max pass.
+__global__ void down_count_kernel(const int64_t* __restrict__ uniq, const int* __restrict__ n_selected,
+                                  int64_t sentinel, int* __restrict__ result) {
+  int ns = *n_selected;
+  int m = ns;
+  if (ns > 0 && uniq[ns - 1] == sentinel) m = ns - 1;
+  result[0] = m;
+  result[1] = result[2] = result[3] = result[4] = INT_MIN;
+  result[5] = result[6] = result[7] = 0;
+}
+
+__device__ __forceinline__ void unravel4(const Bounds& b, int64_t key, int& c0, int& c1, int& c2, int& c3) {
+  c3 = b.mn[3] + (int)(key % b.sz[3]); key /= b.sz[3];
+  c2 = b.mn[2] + (int)(key % b.sz[2]); key /= b.sz[2];
+  c1 = b.mn[1] + (int)(key % b.sz[1]); key /= b.sz[1];
+  c0 = b.mn[0] + (int)(key % b.sz[0]);
+}
+
+__global__ void down_max_kernel(const int64_t* __restrict__ uniq, Bounds b, int* __restrict__ result) {
+  const int m = result[0];
+  int mx[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < m; i += (int64_t)gridDim.x * blockDim.x) {
+    int c[4];
+    unravel4(b, uniq[i], c[0], c[1], c[2], c[3]);
+#pragma unroll
+    for (int d = 0; d < 4; ++d) mx[d] = max(mx[d], c[d]);
+  }
+#pragma unroll
+  for (int d = 0; d < 4; ++d) {
+    int v = mx[d];
+    for (int o = 16; o; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0 && v != INT_MIN) atomicMax(&result[1 + d], v);
+  }
+}
+
+// unravel + insert the outputs, and fill the map with -1 (block owns kBlock rows)
+__global__ void down_insert_fill_kernel(TableView t, const int64_t* __restrict__ uniq, int64_t m, int64_t rows_pad,
+                                        Bounds b, int kvol, int4* __restrict__ out_coords, int* __restrict__ map,
+                                        int* status) {
+  int64_t row0 = (int64_t)blockIdx.x * kBlock;
+  int64_t row = row0 + threadIdx.x;
+  if (row < m) {
+    int64_t key = uniq[row];
+    int4 c;
+    unravel4(b, key, c.x, c.y, c.z, c.w);
+    out_coords[row] = c;
+    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+  }
+  int64_t lo = row0 * kvol;
+  int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kBlock) map[i] = -1;
+}
+
+// thread per (input, k'): map[out][kvol-1-k'] = in
+__global__ void down_stage3_kernel(TableView t, const int4* __restrict__ coords, int64_t n, int64_t m, Bounds b,
+                                   KernelGeom g, int* __restrict__ map, int* status) {
+  const int64_t total = n * (int64_t)g.kvol;
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = tid / g.kvol;
+    int k = (int)(tid - row * g.kvol);
+    int d[3];
+    kernel_digits(g, k, d[0], d[1], d[2]);
+    int4 c = __ldg(&coords[row]);
+    int in[3] = {c.y, c.z, c.w};
+    int o[3];
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      int v = in[i] + g.pd[i] + d[i] - (g.ks[i] - 1);
+      ok = ok && (v % g.st[i] == 0);
+      o[i] = v / g.st[i];
+    }
+    if (!ok || !in_bounds_xyz(b, o[0], o[1], o[2])) continue;
+    int64_t key = ravel4(b, c.x, o[0], o[1], o[2]);
+    int orow = table_lookup(t, (unsigned long long)(key + 1)) - 1;
+    if (orow >= 0 && orow < m) {
+      map[(int64_t)orow * g.kvol + (g.kvol - 1 - k)] = (int)row;
+    } else if (status) {
+      atomicOr(status, TSB_DEV_BAD_INDEX);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ transpose / bitmask / reorder
+__global__ void fill_i32_kernel(int* __restrict__ p, int64_t n, int v) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
+}
+
+__global__ void transpose_map_kernel(const int* __restrict__ map, int64_t total, int kvol, int64_t rows_t,
+                                     int* __restrict__ map_t) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int in = __ldg(&map[i]);
+    if (in < 0 || in >= rows_t) continue;
+    int64_t out = i / kvol;
+    int k = (int)(i - out * kvol);
+    map_t[(int64_t)in * kvol + k] = (int)out;
+  }
+}
+
+__global__ void bitmask_kernel(const int* __restrict__ map, int64_t rows, int kvol, int split, int64_t valid_n,
+                               int* __restrict__ bitmask) {
+  const int split_len = (kvol + split - 1) / split;
+  const int64_t total = rows * split;
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    int64_t row = tid / split;
+    int s = (int)(tid - row * split);
+    int v = -1;
+    if (row < valid_n) {
+      int lo = s * split_len;
+      int len = (s == split - 1) ? kvol - lo : split_len;
+      const int* p = map + row * kvol + lo;
+      unsigned m = 0;
+      for (int i = 0; i < len; ++i) m |= (unsigned)(__ldg(&p[i]) >= 0) << i;
+      v = (int)m;
+    }
+    bitmask[(int64_t)s * rows + row] = v;
+  }
+}
+
+__global__ void iota_kernel(int* __restrict__ p, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = (int)i;
+}
+
+// warp per tile
+__global__ void reduce_mask_kernel(const int* __restrict__ bitmask, int64_t rows, int split, int tile, int64_t n_red,
+                                   int* __restrict__ reduced) {
+  int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  int lane = threadIdx.x & 31;
+  int64_t total = n_red * split;
+  int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (; warp < total; warp += nwarps) {
+    int s = (int)(warp / n_red);
+    int64_t t = warp - (int64_t)s * n_red;
+    int64_t lo = t * tile, hi = min(lo + tile, rows);
+    int v = 0;
+    for (int64_t i = lo + lane; i < hi; i += 32) v |= __ldg(&bitmask[(int64_t)s * rows + i]);
+    for (int o = 16; o; o >>= 1) v |= __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) reduced[(int64_t)s * n_red + t] = v;
+  }
+}
+
+__global__ void reorder_map_kernel(const int* __restrict__ map, int64_t rows, int kvol, const int* __restrict__ loc,
+                                   int split_len, int* __restrict__ out) {
+  const int64_t total = rows * kvol;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / kvol;
+    int c = (int)(i - r * kvol);
+    int src = __ldg(&loc[(int64_t)(c / split_len) * rows + r]);
+    out[i] = __ldg(&map[(int64_t)src * kvol + c]);
+  }
+}
+
+// ------------------------------------------------------------------ pair lists
+constexpr int kMaxKvolSmem = 512;
+
+// per-block, per-column counts of valid entries; also accumulates the global nbsizes
+__global__ void pairs_block_count_kernel(const int* __restrict__ map, int64_t rows, int kvol,
+                                         int* __restrict__ block_counts, int* __restrict__ nbsizes) {
+  extern __shared__ int s_cnt[];
+  for (int i = threadIdx.x; i < kvol; i += blockDim.x) s_cnt[i] = 0;
+  __syncthreads();
+  int64_t lo = (int64_t)blockIdx.x * kBlock * kvol;
+  int64_t hi = min(((int64_t)blockIdx.x + 1) * kBlock, rows) * (int64_t)kvol;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    if (__ldg(&map[i]) >= 0) atomicAdd(&s_cnt[(int)(i % kvol)], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kvol; i += blockDim.x) {
+    int c = s_cnt[i];
+    if (block_counts) block_counts[(int64_t)blockIdx.x * kvol + i] = c;
+    if (nbsizes && c) atomicAdd(&nbsizes[i], c);
+  }
+}
+
+__global__ void scan_quantified_kernel(int kvol, const int* __restrict__ nbsizes, int* __restrict__ nbaddrs,
+                                       int* __restrict__ qnbaddrs) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int acc = 0, qacc = 0;
+    for (int k = 0; k < kvol; ++k) {
+      if (nbaddrs) nbaddrs[k] = acc;
+      if (qnbaddrs) qnbaddrs[k] = qacc;
+      int v = nbsizes[k];
+      acc += v;
+      qacc += (v + 127) / 128 * 128;
+    }
+    if (nbaddrs) nbaddrs[kvol] = acc;
+    if (qnbaddrs) qnbaddrs[kvol] = qacc;
+  }
+}
+
+// exclusive scan over blocks of each column (thread per column), in place
+__global__ void pairs_block_scan_kernel(int* __restrict__ block_counts, int64_t nblocks, int kvol) {
+  int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= kvol) return;
+  int acc = 0;
+  for (int64_t b = 0; b < nblocks; ++b) {
+    int v = block_counts[b * kvol + k];
+    block_counts[b * kvol + k] = acc;
+    acc += v;
+  }
+}
+
+// block = kBlock rows; for each column the rank of a valid row = block offset + warp offset + lane rank
+__global__ void pairs_fill_kernel(const int* __restrict__ map, int64_t rows, int kvol,
+                                  const int* __restrict__ block_offsets, const int* __restrict__ nbaddrs,
+                                  int64_t n_pairs, int transposed, int* __restrict__ nbmaps) {
+  __shared__ int s_warp[kBlock / 32];
+  int64_t row = (int64_t)blockIdx.x * kBlock + threadIdx.x;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int k = 0; k < kvol; ++k) {
+    int in = (row < rows) ? __ldg(&map[row * kvol + k]) : -1;
+    unsigned bal = __ballot_sync(0xffffffffu, in >= 0);
+    if (lane == 0) s_warp[warp] = __popc(bal);
+    __syncthreads();
+    int woff = 0;
+    for (int w = 0; w < warp; ++w) woff += s_warp[w];
+    if (in >= 0) {
+      int64_t pos = (int64_t)nbaddrs[k] + block_offsets[(int64_t)blockIdx.x * kvol + k] + woff +
+                    __popc(bal & ((1u << lane) - 1u));
+      if (pos < n_pairs) {
+        if (transposed) {
+          nbmaps[pos] = in;
+          nbmaps[n_pairs + pos] = (int)row;
+        } else {
+          nbmaps[2 * pos] = in;
+          nbmaps[2 * pos + 1] = (int)row;
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void build_masks_kernel(const int* __restrict__ nbmaps, const int* __restrict__ nbaddrs, int kvol,
+                                   int64_t n_pairs, int64_t n_in, int64_t n_out, int skip_centre,
+                                   int* __restrict__ input_mask, int* __restrict__ output_mask) {
+  extern __shared__ int s_addr[];
+  for (int i = threadIdx.x; i <= kvol; i += blockDim.x) s_addr[i] = nbaddrs[i];
+  __syncthreads();
+  for (int64_t p = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; p < n_pairs; p += (int64_t)gridDim.x * blockDim.x) {
+    int lo = 0, hi = kvol;  // largest k with s_addr[k] <= p
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (s_addr[mid] <= p) lo = mid; else hi = mid;
+    }
+    int k = lo;
+    if (skip_centre && k == kvol / 2) continue;
+    int pos = (int)(p - s_addr[k]);
+    int in = nbmaps[2 * p], out = nbmaps[2 * p + 1];
+    if (in >= 0 && in < n_in) input_mask[(int64_t)k * n_in + in] = pos;
+    if (out >= 0 && out < n_out) output_mask[(int64_t)k * n_out + out] = pos;
+  }
+}
+
+int bits_for(int64_t v) {  // number of bits needed to represent v (v >= 0)
+  int b = 0;
+  while (v > 0) { ++b; v >>= 1; }
+  return b < 1 ? 1 : b;
+}
+
+}  // namespace
+}  // namespace tsb
+
+using namespace tsb;
+
+// ====================================================================== C ABI
+extern "C" {
+
+int tsb_coord_hash(const int32_t* coords, int64_t n, int64_t* out, tsb_stream_t stream) {
+  if (n < 0 || (n && (!coords || !out))) return TSB_ERR_BAD_ARG;
+  if (n == 0) return TSB_OK;
+  coord_hash_kernel<<<grid_for(n, kBlock), kBlock, 0, as_stream(stream)>>>(reinterpret_cast<const int4*>(coords), n, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_kernel_hash(const int32_t* coords, int64_t n, const int32_t* offsets, int32_t k, int64_t* out,
+                    tsb_stream_t stream) {
+  if (n < 0 || k < 0 || ((n && k) && (!coords || !out || !offsets))) return TSB_ERR_BAD_ARG;
+  if (n == 0 || k == 0) return TSB_OK;
+  if ((size_t)k * 3 * sizeof(int) > 48 * 1024) return TSB_ERR_LIMIT;
+  kernel_hash_kernel<<<grid_for(n, kBlock), kBlock, (size_t)k * 3 * sizeof(int), as_stream(stream)>>>(
+      reinterpret_cast<const int4*>(coords), n, offsets, k, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_hash_insert(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int64_t* keys, int64_t n,
+                    int32_t* dev_status, tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || (n && !keys)) return TSB_ERR_BAD_ARG;
+  if (n == 0) return TSB_OK;
+  table_insert_kernel<<<grid_for(n, kBlock), kBlock, 0, as_stream(stream)>>>(make_table(table_keys, table_vals, capacity),
+                                                                             keys, n, dev_status);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_hash_lookup(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity, const int64_t* keys,
+                    int64_t n, int32_t* out_vals, tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || (n && (!keys || !out_vals))) return TSB_ERR_BAD_ARG;
+  if (n == 0) return TSB_OK;
+  table_lookup_kernel<<<grid_for(n, kBlock), kBlock, 0, as_stream(stream)>>>(
+      make_table(const_cast<int64_t*>(table_keys), const_cast<int32_t*>(table_vals), capacity), keys, n, out_vals);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+static int64_t query_capacity(int64_t n_ref) {
+  int64_t cap = 512;
+  while (cap < 2 * n_ref) cap <<= 1;
+  return cap;
+}
+
+size_t tsb_hash_query_workspace_bytes(int64_t n_ref) {
+  if (n_ref < 0) return 0;
+  return (size_t)query_capacity(n_ref) * (sizeof(int64_t) + sizeof(int32_t)) + 256;
+}
+
+int tsb_hash_query(const int64_t* queries, int64_t n_q, const int64_t* refs, int64_t n_ref, int64_t* out,
+                   void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (n_q < 0 || n_ref < 0 || (n_q && (!queries || !out)) || (n_ref && !refs)) return TSB_ERR_BAD_ARG;
+  if (n_q == 0) return TSB_OK;
+  if (!workspace || workspace_bytes < tsb_hash_query_workspace_bytes(n_ref)) return TSB_ERR_WORKSPACE;
+  int64_t cap = query_capacity(n_ref);
+  int64_t* tk = reinterpret_cast<int64_t*>(workspace);
+  int32_t* tv = reinterpret_cast<int32_t*>(tk + cap);
+  cudaStream_t s = as_stream(stream);
+  TSB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)cap * 12, s));
+  TableView t = make_table(tk, tv, cap);
+  if (n_ref) {
+    table_insert_kernel<<<grid_for(n_ref, kBlock), kBlock, 0, s>>>(t, refs, n_ref, nullptr);
+    TSB_LAUNCH_CHECK();
+  }
+  table_query_kernel<<<grid_for(n_q, kBlock), kBlock, 0, s>>>(t, queries, n_q, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_kmap_subm(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n,
+                  const int32_t* cmin, const int32_t* cmax, const int32_t* kernel_size, int32_t to_insert,
+                  int32_t* out_in_map, int32_t* dev_status, tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || !cmin || !cmax || !kernel_size) return TSB_ERR_BAD_ARG;
+  if (n && (!coords || !out_in_map)) return TSB_ERR_BAD_ARG;
+  if (n == 0) return TSB_OK;
+  for (int i = 0; i < 3; ++i) if (kernel_size[i] < 1) return TSB_ERR_BAD_ARG;
+  KernelGeom g = make_geom(kernel_size, nullptr, nullptr);
+  Bounds b = make_bounds(cmin, cmax);
+  for (int i = 0; i < 4; ++i) if (b.sz[i] < 1) return TSB_ERR_BAD_ARG;
+  TableView t = make_table(table_keys, table_vals, capacity);
+  cudaStream_t s = as_stream(stream);
+  const int64_t rows_pad = pad128(n);
+  const int4* c4 = reinterpret_cast<const int4*>(coords);
+  subm_insert_fill_kernel<<<(int)cdiv(rows_pad, kBlock), kBlock, 0, s>>>(t, c4, n, rows_pad, b, g.kvol, to_insert,
+                                                                        out_in_map, dev_status);
+  TSB_LAUNCH_CHECK();
+  if (g.odd) {
+    int64_t work = n * (int64_t)(g.kvol / 2 > 0 ? g.kvol / 2 : 1);
+    subm_query_odd_kernel<<<grid_for(work, kBlock, 32), kBlock, 0, s>>>(t, c4, n, b, g, out_in_map);
+  } else {
+    subm_query_even_kernel<<<grid_for(n * (int64_t)g.kvol, kBlock, 32), kBlock, 0, s>>>(t, c4, n, b, g, out_in_map);
+  }
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int32_t tsb_kmap_down_slots(const int32_t* kernel_size, const int32_t* stride) {
+  if (!kernel_size || !stride) return 0;
+  for (int i = 0; i < 3; ++i) if (kernel_size[i] < 1 || stride[i] < 1) return 0;
+  return make_slots(kernel_size, stride).slots;
+}
+
+namespace {
+struct DownWs {
+  size_t cand_off, sorted_off, nsel_off, cub_off, total;
+  size_t cub_bytes;
+};
+DownWs down_ws_layout(int64_t n, int slots) {
+  DownWs w;
+  size_t items = (size_t)n * slots;
+  size_t sort_b = 0, uniq_b = 0;
+  cub::DeviceRadixSort::SortKeys(nullptr, sort_b, (const int64_t*)nullptr, (int64_t*)nullptr, (int64_t)items, 0, 64);
+  cub::DeviceSelect::Unique(nullptr, uniq_b, (const int64_t*)nullptr, (int64_t*)nullptr, (int*)nullptr, (int64_t)items);
+  w.cub_bytes = sort_b > uniq_b ? sort_b : uniq_b;
+  size_t off = 0;
+  w.cand_off = off; off = align_up(off + items * 8, 256);
+  w.sorted_off = off; off = align_up(off + items * 8, 256);
+  w.nsel_off = off; off = align_up(off + 16, 256);
+  w.cub_off = off; off = align_up(off + w.cub_bytes, 256);
+  w.total = off;
+  return w;
+}
+}  // namespace
+
+size_t tsb_kmap_down_workspace_bytes(int64_t n, const int32_t* kernel_size, const int32_t* stride) {
+  int slots = tsb_kmap_down_slots(kernel_size, stride);
+  if (n <= 0 || slots <= 0) return 256;
+  return down_ws_layout(n, slots).total;
+}
+
+int tsb_kmap_down_unique(const int32_t* coords, int64_t n, const int32_t* cmin, const int32_t* cmax_out,
+                         const int32_t* kernel_size, const int32_t* stride, const int32_t* padding,
+                         int64_t* uniq_keys, int32_t* result, void* workspace, size_t workspace_bytes,
+                         tsb_stream_t stream) {
+  if (n < 0 || !cmin || !cmax_out || !kernel_size || !stride || !padding || !result) return TSB_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  if (n == 0) {
+    TSB_CUDA_TRY(cudaMemsetAsync(result, 0, 8 * sizeof(int32_t), s));
+    return TSB_OK;
+  }
+  if (!coords || !uniq_keys) return TSB_ERR_BAD_ARG;
+  int slots = tsb_kmap_down_slots(kernel_size, stride);
+  if (slots <= 0) return TSB_ERR_BAD_ARG;
+  Bounds b = make_bounds(cmin, cmax_out);
+  // an empty output range (cmax_out < cmin on some dim) means no outputs at all
+  for (int i = 0; i < 4; ++i) {
+    if (b.sz[i] < 1) {
+      TSB_CUDA_TRY(cudaMemsetAsync(result, 0, 8 * sizeof(int32_t), s));
+      return TSB_OK;
+    }
+  }
+  if ((int64_t)n * slots > (int64_t)INT32_MAX) return TSB_ERR_LIMIT;
+  DownWs w = down_ws_layout(n, slots);
+  if (!workspace || workspace_bytes < w.total) return TSB_ERR_WORKSPACE;
+  char* base = reinterpret_cast<char*>(workspace);
+  int64_t* cand = reinterpret_cast<int64_t*>(base + w.cand_off);
+  int64_t* sorted = reinterpret_cast<int64_t*>(base + w.sorted_off);
+  int* nsel = reinterpret_cast<int*>(base + w.nsel_off);
+  void* cub_ws = base + w.cub_off;
+  KernelGeom g = make_geom(kernel_size, stride, padding);
+  SlotGeom sg = make_slots(kernel_size, stride);
+  int64_t sentinel = (int64_t)b.sz[0] * b.sz[1] * b.sz[2] * b.sz[3];  // one past the largest key
+  int64_t items = n * (int64_t)slots;
+  down_candidates_kernel<<<grid_for(items, kBlock, 32), kBlock, 0, s>>>(reinterpret_cast<const int4*>(coords), n, b, g,
+                                                                        sg, sentinel, cand);
+  TSB_LAUNCH_CHECK();
+  size_t cb = w.cub_bytes;
+  TSB_CUDA_TRY(cub::DeviceRadixSort::SortKeys(cub_ws, cb, cand, sorted, items, 0, bits_for(sentinel), s));
+  cb = w.cub_bytes;
+  TSB_CUDA_TRY(cub::DeviceSelect::Unique(cub_ws, cb, sorted, uniq_keys, nsel, items, s));
+  down_count_kernel<<<1, 1, 0, s>>>(uniq_keys, nsel, sentinel, result);
+  TSB_LAUNCH_CHECK();
+  down_max_kernel<<<grid_for(items, kBlock, 4), kBlock, 0, s>>>(uniq_keys, b, result);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_kmap_down_finish(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n,
+                         const int64_t* uniq_keys, int64_t m, const int32_t* cmin, const int32_t* cmax_out,
+                         const int32_t* kernel_size, const int32_t* stride, const int32_t* padding,
+                         int32_t* out_coords, int32_t* out_in_map, int32_t* dev_status, tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || m < 0 || !cmin || !cmax_out || !kernel_size ||
+      !stride || !padding)
+    return TSB_ERR_BAD_ARG;
+  if (m == 0) return TSB_OK;
+  if (!coords || !uniq_keys || !out_coords || !out_in_map) return TSB_ERR_BAD_ARG;
+  if (capacity < m) return TSB_ERR_LIMIT;
+  Bounds b = make_bounds(cmin, cmax_out);
+  KernelGeom g = make_geom(kernel_size, stride, padding);
+  TableView t = make_table(table_keys, table_vals, capacity);
+  cudaStream_t s = as_stream(stream);
+  const int64_t rows_pad = pad128(m);
+  down_insert_fill_kernel<<<(int)cdiv(rows_pad, kBlock), kBlock, 0, s>>>(
+      t, uniq_keys, m, rows_pad, b, g.kvol, reinterpret_cast<int4*>(out_coords), out_in_map, dev_status);
+  TSB_LAUNCH_CHECK();
+  down_stage3_kernel<<<grid_for(n * (int64_t)g.kvol, kBlock, 32), kBlock, 0, s>>>(
+      t, reinterpret_cast<const int4*>(coords), n, m, b, g, out_in_map, dev_status);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_map_transpose(const int32_t* out_in_map, int64_t rows, int32_t kvol, int32_t* map_t, int64_t rows_t,
+                      int32_t fill, tsb_stream_t stream) {
+  if (rows < 0 || rows_t < 0 || kvol < 1 || (rows && !out_in_map) || (rows_t && !map_t)) return TSB_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  if (fill && rows_t) {
+    fill_i32_kernel<<<grid_for(rows_t * kvol / 4 + 1, kBlock), kBlock, 0, s>>>(map_t, rows_t * kvol, -1);
+    TSB_LAUNCH_CHECK();
+  }
+  if (rows == 0 || rows_t == 0) return TSB_OK;
+  transpose_map_kernel<<<grid_for(rows * kvol, kBlock, 32), kBlock, 0, s>>>(out_in_map, rows * kvol, kvol, rows_t, map_t);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_bitmask_derive(const int32_t* out_in_map, int64_t rows, int32_t kvol, int32_t split, int64_t valid_n,
+                       int32_t* bitmask, tsb_stream_t stream) {
+  if (rows < 0 || kvol < 1 || split < 1 || valid_n < 0 || valid_n > rows || (rows && (!out_in_map || !bitmask)))
+    return TSB_ERR_BAD_ARG;
+  if ((kvol + split - 1) / split > 31) return TSB_ERR_LIMIT;  // one int32 of mask bits per split
+  if (rows == 0) return TSB_OK;
+  bitmask_kernel<<<grid_for(rows * split, kBlock, 32), kBlock, 0, as_stream(stream)>>>(out_in_map, rows, kvol, split,
+                                                                                      valid_n, bitmask);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+namespace {
+struct SortWs { size_t iota_off, cub_off, total, cub_bytes; };
+SortWs sort_ws_layout(int64_t rows) {
+  SortWs w;
+  size_t cb = 0;
+  cub::DeviceRadixSort::SortPairsDescending(nullptr, cb, (const int*)nullptr, (int*)nullptr, (const int*)nullptr,
+                                            (int*)nullptr, rows, 0, 32);
+  w.cub_bytes = cb;
+  size_t off = 0;
+  w.iota_off = off; off = align_up(off + (size_t)rows * 4, 256);
+  w.cub_off = off; off = align_up(off + cb, 256);
+  w.total = off;
+  return w;
+}
+}  // namespace
+
+size_t tsb_bitmask_sort_workspace_bytes(int64_t rows, int32_t split) {
+  (void)split;
+  if (rows <= 0) return 256;
+  return sort_ws_layout(rows).total;
+}
+
+int tsb_bitmask_sort(const int32_t* bitmask, int64_t rows, int32_t split, int32_t kvol, int32_t* sorted_mask,
+                     int32_t* reorder_loc, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  (void)kvol;
+  if (rows < 0 || split < 1 || (rows && (!bitmask || !sorted_mask || !reorder_loc))) return TSB_ERR_BAD_ARG;
+  if (rows == 0) return TSB_OK;
+  if (rows > INT32_MAX) return TSB_ERR_LIMIT;
+  SortWs w = sort_ws_layout(rows);
+  if (!workspace || workspace_bytes < w.total) return TSB_ERR_WORKSPACE;
+  cudaStream_t s = as_stream(stream);
+  char* base = reinterpret_cast<char*>(workspace);
+  int* iota = reinterpret_cast<int*>(base + w.iota_off);
+  iota_kernel<<<grid_for(rows, kBlock), kBlock, 0, s>>>(iota, rows);
+  TSB_LAUNCH_CHECK();
+  for (int sp = 0; sp < split; ++sp) {
+    size_t cb = w.cub_bytes;
+    // signed keys: the -1 of padded rows sorts last; radix sort is stable, so ties keep row order
+    TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairsDescending(base + w.cub_off, cb, bitmask + (int64_t)sp * rows,
+                                                           sorted_mask + (int64_t)sp * rows, iota,
+                                                           reorder_loc + (int64_t)sp * rows, rows, 0, 32, s));
+  }
+  return TSB_OK;
+}
+
+int tsb_bitmask_reduce(const int32_t* bitmask, int64_t rows, int32_t split, int32_t tile, int32_t* reduced,
+                       tsb_stream_t stream) {
+  if (rows < 0 || split < 1 || tile < 1 || (rows && (!bitmask || !reduced))) return TSB_ERR_BAD_ARG;
+  if (tile % 4 != 0) return TSB_ERR_BAD_ARG;  // same restriction as the reference entry point
+  if (rows == 0) return TSB_OK;
+  int64_t n_red = (rows - 1) / tile + 1;
+  reduce_mask_kernel<<<grid_for(n_red * split * 32, kBlock), kBlock, 0, as_stream(stream)>>>(bitmask, rows, split, tile,
+                                                                                            n_red, reduced);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_map_reorder(const int32_t* out_in_map, int64_t rows, int32_t kvol, const int32_t* reorder_loc, int32_t split,
+                    int32_t* out, tsb_stream_t stream) {
+  if (rows < 0 || kvol < 1 || split < 1 || (rows && (!out_in_map || !reorder_loc || !out))) return TSB_ERR_BAD_ARG;
+  if (rows == 0) return TSB_OK;
+  int split_len = (kvol + split - 1) / split;
+  reorder_map_kernel<<<grid_for(rows * kvol, kBlock, 32), kBlock, 0, as_stream(stream)>>>(out_in_map, rows, kvol,
+                                                                                         reorder_loc, split_len, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_scan_quantified(int32_t kvol, const int32_t* nbsizes, int32_t* nbaddrs, int32_t* qnbaddrs,
+                        tsb_stream_t stream) {
+  if (kvol < 1 || !nbsizes) return TSB_ERR_BAD_ARG;
+  scan_quantified_kernel<<<1, 32, 0, as_stream(stream)>>>(kvol, nbsizes, nbaddrs, qnbaddrs);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_pairs_count(const int32_t* out_in_map, int64_t rows, int32_t kvol, int32_t* nbsizes, int32_t* nbaddrs,
+                    int32_t* qnbaddrs, tsb_stream_t stream) {
+  if (rows < 0 || kvol < 1 || !nbsizes || (rows && !out_in_map)) return TSB_ERR_BAD_ARG;
+  if (kvol > kMaxKvolSmem) return TSB_ERR_LIMIT;
+  cudaStream_t s = as_stream(stream);
+  TSB_CUDA_TRY(cudaMemsetAsync(nbsizes, 0, (size_t)kvol * sizeof(int32_t), s));
+  if (rows) {
+    pairs_block_count_kernel<<<(int)cdiv(rows, kBlock), kBlock, (size_t)kvol * sizeof(int), s>>>(out_in_map, rows, kvol,
+                                                                                                nullptr, nbsizes);
+    TSB_LAUNCH_CHECK();
+  }
+  if (nbaddrs || qnbaddrs) {
+    scan_quantified_kernel<<<1, 32, 0, s>>>(kvol, nbsizes, nbaddrs, qnbaddrs);
+    TSB_LAUNCH_CHECK();
+  }
+  return TSB_OK;
+}
+
+size_t tsb_pairs_fill_workspace_bytes(int64_t rows, int32_t kvol) {
+  if (rows <= 0 || kvol < 1) return 256;
+  return align_up((size_t)cdiv(rows, kBlock) * kvol * sizeof(int), 256);
+}
+
+int tsb_pairs_fill(const int32_t* out_in_map, int64_t rows, int32_t kvol, const int32_t* nbaddrs, int64_t n_pairs,
+                   int32_t transposed, int32_t* nbmaps, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (rows < 0 || kvol < 1 || n_pairs < 0 || !nbaddrs || (rows && !out_in_map)) return TSB_ERR_BAD_ARG;
+  if (kvol > kMaxKvolSmem) return TSB_ERR_LIMIT;
+  if (rows == 0 || n_pairs == 0) return TSB_OK;
+  if (!nbmaps) return TSB_ERR_BAD_ARG;
+  if (!workspace || workspace_bytes < tsb_pairs_fill_workspace_bytes(rows, kvol)) return TSB_ERR_WORKSPACE;
+  cudaStream_t s = as_stream(stream);
+  int* block_counts = reinterpret_cast<int*>(workspace);
+  int64_t nblocks = cdiv(rows, kBlock);
+  pairs_block_count_kernel<<<(int)nblocks, kBlock, (size_t)kvol * sizeof(int), s>>>(out_in_map, rows, kvol, block_counts,
+                                                                                   nullptr);
+  TSB_LAUNCH_CHECK();
+  pairs_block_scan_kernel<<<(int)cdiv(kvol, 32), 32, 0, s>>>(block_counts, nblocks, kvol);
+  TSB_LAUNCH_CHECK();
+  pairs_fill_kernel<<<(int)nblocks, kBlock, 0, s>>>(out_in_map, rows, kvol, block_counts, nbaddrs, n_pairs, transposed,
+                                                    nbmaps);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_build_masks(int64_t n_in, int64_t n_out, const int32_t* nbmaps, const int32_t* nbaddrs, int32_t kvol,
+                    int64_t n_pairs, int32_t* input_mask, int32_t* output_mask, tsb_stream_t stream) {
+  if (n_in < 0 || n_out < 0 || kvol < 1 || n_pairs < 0 || !nbaddrs) return TSB_ERR_BAD_ARG;
+  if ((n_in && !input_mask) || (n_out && !output_mask) || (n_pairs && !nbmaps)) return TSB_ERR_BAD_ARG;
+  if (kvol > kMaxKvolSmem) return TSB_ERR_LIMIT;
+  cudaStream_t s = as_stream(stream);
+  if (n_in) {
+    fill_i32_kernel<<<grid_for(n_in * kvol, kBlock), kBlock, 0, s>>>(input_mask, n_in * kvol, -1);
+    TSB_LAUNCH_CHECK();
+  }
+  if (n_out) {
+    fill_i32_kernel<<<grid_for(n_out * kvol, kBlock), kBlock, 0, s>>>(output_mask, n_out * kvol, -1);
+    TSB_LAUNCH_CHECK();
+  }
+  if (n_pairs == 0) return TSB_OK;
+  int skip_centre = (n_in == n_out && (kvol & 1)) ? 1 : 0;
+  build_masks_kernel<<<grid_for(n_pairs, kBlock), kBlock, (size_t)(kvol + 1) * sizeof(int), s>>>(
+      nbmaps, nbaddrs, kvol, n_pairs, n_in, n_out, skip_centre, input_mask, output_mask);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,6 @@
+from .conv import *
+from .conv_mode import *
+from . import conv_config
+from .conv_config import Dataflow, ConvConfig
+from .kmap import *
+from .func import *
