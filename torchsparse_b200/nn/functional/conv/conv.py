@@ -53,6 +53,8 @@ def conv3d(
         config["ifsort"] = False  # row sorting only exists for the implicit-GEMM dataflow
     fn = _FUNCS[dataflow]
     caches = input._caches
+    # the input's own coordinates are the target of a later transposed conv back to this stride
+    caches.cmaps.setdefault(input.stride, (coords, input.spatial_range))
 
     if kernel_size == (1, 1, 1) and stride == (1, 1, 1) and dilation == (1, 1, 1):
         out_feats = feats.matmul(weight.to(feats.dtype))
