@@ -1,0 +1,392 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-convolution hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2, the one the metric is quoted on): a MinkUNet-class residual sparse
+U-Net (the reference's own SparseResUNet42, width 1.0, plus a 19-way linear head) in fp16 inference
+on one synthetic LiDAR-like scan per GPU per step (64 rings x 2048 azimuths, 120k rays + 20% box
+points, 0.05 m voxels).  One step = voxelisation (sparse_quantize on the GPU) -> 9 kernel maps ->
+42 sparse convolutions (+ BN/ReLU/skip) -> logits.  With N GPUs every rank runs its own scan (weak
+scaling, scans are independent) and the logits are all-gathered over NCCL once per step.
+
+Prints ONE JSON line (rank 0).  `value` = scans/s with the points already resident in HBM;
+`e2e` = the same through the public API from pinned host memory (H2D of the points and D2H of the
+logits inside the timed region).  `roofline` describes the dominant kernel (the implicit-GEMM conv
+forward of the layer shape with the largest total time), timed with CUDA events on its own stream
+inside the timed region.  `cpu_baseline` = the reference project's own CPU convolution (oracle/_ref)
+driving the same network on a spatial crop of the same scan, scaled by voxel count.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+VOXEL = 0.05
+NUM_CLASSES = 19
+METRIC = "minkunet_fp16_scans_per_sec"
+SCAN_POOL = 4          # distinct scans rotated through the timed steps
+L2_FLUSH_BYTES = 256 << 20
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tensor_tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured (MEASURED_PEAKS.json; sustained 16-bit GEMM, copy bandwidth)"}
+    return {"hbm_gbs": 6650.0, "tensor_tflops": 1400.0, "source": "fallback (6.65 TB/s, 1.4 PFLOP/s sustained)"}
+
+
+# --------------------------------------------------------------------------------------- model
+class SegNet(torch.nn.Module):
+    """SparseResUNet42 + linear classifier on the finest decoder output."""
+
+    def __init__(self):
+        super().__init__()
+        from torchsparse_b200.backbones import SparseResUNet42
+
+        self.backbone = SparseResUNet42(in_channels=4, width_multiplier=1.0)
+        self.head = torch.nn.Linear(96, NUM_CLASSES)
+
+    def forward(self, x):
+        return self.head(self.backbone(x)[-1].feats)
+
+
+def make_model(device=None, half=True):
+    torch.manual_seed(0)
+    model = SegNet()
+    for m in model.modules():   # random Kaiming-style init, non-trivial BN statistics
+        if hasattr(m, "kernel"):
+            fan_in = m.kernel.shape[-2] * (m.kernel.shape[0] if m.kernel.dim() == 3 else 1)
+            torch.nn.init.normal_(m.kernel, std=(2.0 / fan_in) ** 0.5)
+        if isinstance(m, torch.nn.BatchNorm1d):
+            torch.nn.init.uniform_(m.weight, 0.8, 1.2)
+            torch.nn.init.uniform_(m.bias, -0.1, 0.1)
+            m.running_mean.uniform_(-0.1, 0.1)
+            m.running_var.uniform_(0.8, 1.2)
+    model.eval()
+    if device is not None:
+        model = model.to(device)
+        if half:
+            model = model.half()
+    return model
+
+
+def scan_points(seed: int) -> np.ndarray:
+    from torchsparse_b200.utils.synthetic import lidar_scan
+
+    pts = lidar_scan(seed)
+    pts[:, :3] -= pts[:, :3].min(0, keepdims=True)
+    return pts
+
+
+# --------------------------------------------------------------------------------------- our arm
+def forward_scan(model, pts_dev: torch.Tensor):
+    """points [Np,4] on the device -> logits [Nv, 19] (the public-API path a user runs)."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.utils import sparse_quantize
+
+    vox, idx = sparse_quantize(pts_dev[:, :3], VOXEL, return_index=True)
+    coords = torch.cat([torch.zeros((vox.shape[0], 1), dtype=torch.int32, device=vox.device), vox], 1)
+    feats = pts_dev[idx].half()
+    return model(ts.SparseTensor(feats, coords))
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        self.idx = gpu_index
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(gpu_index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(names, f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.remove(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def conv_algorithmic(dims, pairs: int):
+    """Algorithmic work of one conv launch: useful FLOPs and bytes (features, weights, map once)."""
+    n_in, n_out, kvol, cin, cout, code, _ = dims
+    e = 4 if code == 0 else 2
+    flops = 2.0 * pairs * cin * cout
+    m_pad = (n_out + 127) // 128 * 128
+    byts = n_in * cin * e + n_out * cout * e + kvol * cin * cout * e + m_pad * kvol * 4
+    return flops, byts
+
+
+def run_ours(args, rank: int, world: int, device: torch.device):
+    import torch.distributed as dist
+    import torchsparse_b200  # noqa: F401  (fails loudly when libtsb200.so is missing)
+    from torchsparse_b200 import backend
+    from torchsparse_b200.sharding import gather_rows
+
+    model = make_model(device)
+    scans = [scan_points(1000 * rank + i) for i in range(SCAN_POOL)]
+    host = [torch.from_numpy(s).pin_memory() for s in scans]
+    resident = [h.to(device) for h in host]
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i, e2e: bool):
+        h = host[i % SCAN_POOL]
+        pts = h.to(device, non_blocking=True) if e2e else resident[i % SCAN_POOL]
+        logits = forward_scan(model, pts)
+        if world > 1:
+            logits, _ = gather_rows(logits)
+        out = logits.cpu() if e2e else logits
+        return out, h.numel() * h.element_size(), (logits.numel() * logits.element_size() if e2e else 0)
+
+    records = []
+
+    def observer(name, dims, ev0, ev1):
+        records.append((dims, ev0, ev1))
+
+    def timed(e2e: bool, observe: bool):
+        with torch.no_grad():
+            for i in range(args.warmup):
+                step(i, e2e)
+            barrier()
+            evs = []
+            launches0 = backend.launch_count()
+            backend.set_launch_observer(observer if observe else None)
+            h2d = d2h = 0
+            for i in range(args.steps):
+                flush.fill_(i & 0xFF)       # evict L2 between steps (outside the timed events)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                _, bi, bo = step(i, e2e)
+                e1.record(stream)
+                h2d, d2h = bi, bo
+                evs.append((e0, e1))
+            backend.set_launch_observer(None)
+            barrier()
+            launches = backend.launch_count() - launches0
+        total_ms = sum(a.elapsed_time(b) for a, b in evs)
+        t = torch.tensor([total_ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), launches, h2d, d2h
+
+    sampler = ClockSampler(device.index or 0) if rank == 0 else None
+    ms_total, launches, _, _ = timed(False, True)
+    clocks = sampler.stop() if sampler else None
+    e2e_ms, _, h2d, d2h = timed(True, False)
+
+    if rank != 0:
+        return None
+    scans_per_step = world
+    value = scans_per_step * args.steps / (ms_total / 1e3)
+    e2e_value = scans_per_step * args.steps / (e2e_ms / 1e3)
+
+    # ---- roofline of the dominant kernel (largest total time among conv layer shapes)
+    pk = peaks()
+    by_shape = {}
+    pair_cache = {}
+    for dims, ev0, ev1 in records:
+        key = dims[:6]
+        m = dims[6]
+        pk_key = (m.data_ptr(), tuple(m.shape))
+        if pk_key not in pair_cache:
+            pair_cache[pk_key] = int((m[: dims[1]] >= 0).sum().item())
+        d = by_shape.setdefault(key, {"ms": 0.0, "n": 0, "flops": 0.0, "bytes": 0.0})
+        fl, by = conv_algorithmic(dims, pair_cache[pk_key])
+        d["ms"] += ev0.elapsed_time(ev1); d["n"] += 1; d["flops"] += fl; d["bytes"] += by
+    roof = None
+    conv_ms = sum(d["ms"] for d in by_shape.values())
+    if by_shape:
+        key, d = max(by_shape.items(), key=lambda kv: kv[1]["ms"])
+        sec = d["ms"] / 1e3
+        tf, gb = d["flops"] / sec / 1e12, d["bytes"] / sec / 1e9
+        t_tensor, t_hbm = d["flops"] / (pk["tensor_tflops"] * 1e12), d["bytes"] / (pk["hbm_gbs"] * 1e9)
+        if t_tensor >= t_hbm:
+            roof = {"bound": "tensor", "achieved": round(tf, 3), "peak": pk["tensor_tflops"], "unit": "TFLOP/s",
+                    "frac": round(tf / pk["tensor_tflops"], 4)}
+        else:
+            roof = {"bound": "hbm", "achieved": round(gb, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(gb / pk["hbm_gbs"], 4)}
+        roof.update({"traffic": None, "kernel": "igemm conv forward",
+                     "layer": {"n_in": key[0], "n_out": key[1], "kvol": key[2], "cin": key[3], "cout": key[4]},
+                     "launches": d["n"], "avg_us": round(d["ms"] * 1e3 / d["n"], 2),
+                     "useful_flops_per_launch": d["flops"] / d["n"], "algorithmic_bytes_per_launch": d["bytes"] / d["n"],
+                     "share_of_step": round(d["ms"] / ms_total, 4), "all_conv_share_of_step": round(conv_ms / ms_total, 4),
+                     "peak_source": pk["source"]})
+
+    out = {
+        "metric": METRIC, "value": round(value, 3), "unit": "scans/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "BASELINE config 2: SparseResUNet42 (MinkUNet-class, cr=1.0) + 19-class head, fp16 "
+                               "inference, one synthetic 64-ring LiDAR scan (144k points, 0.05 m voxels) per GPU per step",
+                   "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": scans_per_step,
+                   "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps; {SCAN_POOL} scans rotated",
+                   "parallelism": f"scan-sharded x{world}, NCCL all-gather of logits" if world > 1 else "single GPU"},
+        "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roof,
+    }
+    if world == 1:
+        out["cpu_baseline"] = cpu_baseline(budget_s=20.0)
+    return out
+
+
+def forward_voxels(pts: np.ndarray) -> int:
+    q = np.floor(pts[:, :3] / VOXEL).astype(np.int64)
+    return len(np.unique((q[:, 0] * 100003 + q[:, 1]) * 100003 + q[:, 2]))
+
+
+# --------------------------------------------------------------------------------------- CPU arm
+def _crop(pts: np.ndarray, n_target: int):
+    """Spatial crop around the sensor holding about n_target voxels; returns (coords, feats, n_vox, n_full)."""
+    from oracle import kmap_oracle as ko
+
+    vox, idx = ko.sparse_quantize(pts[:, :3], VOXEL, return_index=True)
+    n_full = vox.shape[0]
+    centre = np.median(vox, axis=0)
+    d = np.abs(vox - centre).max(axis=1)
+    order = np.argsort(d, kind="stable")
+    keep = np.sort(order[: min(n_target, n_full)])
+    coords = np.concatenate([np.zeros((len(keep), 1), np.int32), vox[keep]], 1).astype(np.int32)
+    return coords, pts[idx[keep]], len(keep), n_full
+
+
+def cpu_forward_seconds(model, coords, feats, threads):
+    from oracle import net_cpu
+
+    t0 = time.perf_counter()
+    net_cpu.forward_cpu(model, coords, feats, threads)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(budget_s: float = 20.0, steps: int = 1, warmup: int = 0):
+    """The network on the host cores through the reference's own CPU convolution (oracle/_ref),
+    on a crop of the scan sized for about `budget_s` seconds per pass; scans/s scaled by voxel count."""
+    from oracle import net_cpu
+
+    threads = net_cpu.host_threads()
+    kind = "reference" if net_cpu.reference_conv_module() is not None else "port"
+    model = make_model(None)
+    pts = scan_points(0)
+    c, f, n, n_full = _crop(pts, 8000)
+    cpu_forward_seconds(model, c, f, threads)            # warm caches / thread pools
+    probe = cpu_forward_seconds(model, c, f, threads)
+    n_target = int(max(3000, min(n_full, 0.7 * n * budget_s / max(probe, 1e-3))))
+    c, f, n, n_full = _crop(pts, n_target)
+    for _ in range(warmup):
+        cpu_forward_seconds(model, c, f, threads)
+    times = [cpu_forward_seconds(model, c, f, threads) for _ in range(max(steps, 1))]
+    per_pass = sum(times) / len(times)
+    value = 1.0 / (per_pass * n_full / n)
+    return {"value": round(value, 5), "unit": "scans/s", "cores": threads, "kind": kind,
+            "sample": f"full network forward (fp32) on a {n}-voxel crop of the {n_full}-voxel scan, "
+                      f"{per_pass:.2f} s per pass, scaled by voxel count",
+            "seconds_per_pass": round(per_pass, 3), "crop_voxels": n, "scan_voxels": n_full}
+
+
+def run_reference(args):
+    total_budget = 150.0
+    per_step = max(2.0, total_budget / max(args.steps + args.warmup, 1))
+    b = cpu_baseline(budget_s=per_step, steps=args.steps, warmup=args.warmup)
+    return {
+        "impl": "reference", "metric": METRIC, "value": b["value"], "unit": "scans/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(b["seconds_per_pass"] * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "BASELINE config 2 network on the host CPU through the reference's CPU convolution "
+                               "(fp32 gather-matmul-scatter; the reference has no fp16 / implicit-GEMM CPU path)"},
+        "cpu_baseline": b,
+        "e2e": {"value": b["value"], "unit": "scans/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args)), flush=True)
+        return
+
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    try:
+        out = run_ours(args, rank, world, device)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -46,6 +46,9 @@ const char* tsb_version(void);
 const char* tsb_status_string(int status);
 /* cudaGetErrorString of the last failed runtime call inside this library (thread-local). */
 const char* tsb_last_cuda_error(void);
+/* Number of kernels this library has launched in this process so far (library sort / scan /
+ * select passes count as one launch each).  No counterpart in the reference. */
+long long tsb_launch_count(void);
 
 /* ---------------------------------------------------------------- hashing */
 

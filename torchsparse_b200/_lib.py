@@ -21,6 +21,7 @@ SIGNATURES = {
     "tsb_version": (C.c_char_p, []),
     "tsb_status_string": (C.c_char_p, [C.c_int]),
     "tsb_last_cuda_error": (C.c_char_p, []),
+    "tsb_launch_count": (C.c_longlong, []),
     "tsb_coord_hash": (C.c_int, [P, I64, P, P]),
     "tsb_kernel_hash": (C.c_int, [P, I64, P, I32, P, P]),
     "tsb_hash_insert": (C.c_int, [P, P, I64, P, I64, P, P]),

@@ -37,6 +37,21 @@ __all__ = [
 _DTYPES = {torch.float32: _lib.TSB_F32, torch.float16: _lib.TSB_F16, torch.bfloat16: _lib.TSB_BF16}
 
 
+_observer = None
+
+
+def set_launch_observer(fn) -> None:
+    """Install (or clear with None) a callback ``fn(name, dims, start_event, end_event)`` invoked
+    around every convolution launch; used by the benchmark to time kernels on their own stream."""
+    global _observer
+    _observer = fn
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib.tsb_launch_count())
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -356,10 +371,16 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
         bias = bias.float().contiguous()
     if residual is not None:
         residual = residual.to(in_feats.dtype).contiguous()
+    if _observer is not None:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
     check(lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(out_in_map), _p(reorder_loc), _p(out),
                                  in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
                                  _math_mode(in_feats, allow_tf32), _p(bias), _p(residual), int(relu), _p(ws),
                                  ws.numel(), _stream()), "conv_forward_implicit_gemm_cuda")
+    if _observer is not None:
+        ev1.record()
+        _observer("igemm", (in_feats.shape[0], num_out_feats, kvol, cin, cout, code, out_in_map), ev0, ev1)
     return out
 
 

@@ -24,7 +24,13 @@ inline cudaStream_t as_stream(tsb_stream_t s) { return reinterpret_cast<cudaStre
     }                                      \
   } while (0)
 
-#define TSB_LAUNCH_CHECK() TSB_CUDA_TRY(cudaPeekAtLastError())
+void count_launch(int n = 1);  // bumps the counter read by tsb_launch_count()
+
+#define TSB_LAUNCH_CHECK()                  \
+  do {                                      \
+    ::tsb::count_launch();                  \
+    TSB_CUDA_TRY(cudaPeekAtLastError());    \
+  } while (0)
 
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t pad128(int64_t n) { return cdiv(n, 128) * 128; }

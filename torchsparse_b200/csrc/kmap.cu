@@ -619,8 +619,10 @@ int tsb_kmap_down_unique(const int32_t* coords, int64_t n, const int32_t* cmin, 
   TSB_LAUNCH_CHECK();
   size_t cb = w.cub_bytes;
   TSB_CUDA_TRY(cub::DeviceRadixSort::SortKeys(cub_ws, cb, cand, sorted, items, 0, bits_for(sentinel), s));
+  count_launch();
   cb = w.cub_bytes;
   TSB_CUDA_TRY(cub::DeviceSelect::Unique(cub_ws, cb, sorted, uniq_keys, nsel, items, s));
+  count_launch();
   down_count_kernel<<<1, 1, 0, s>>>(uniq_keys, nsel, sentinel, result);
   TSB_LAUNCH_CHECK();
   down_max_kernel<<<grid_for(items, kBlock, 4), kBlock, 0, s>>>(uniq_keys, b, result);
@@ -719,6 +721,7 @@ int tsb_bitmask_sort(const int32_t* bitmask, int64_t rows, int32_t split, int32_
     TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairsDescending(base + w.cub_off, cb, bitmask + (int64_t)sp * rows,
                                                            sorted_mask + (int64_t)sp * rows, iota,
                                                            reorder_loc + (int64_t)sp * rows, rows, 0, 32, s));
+    count_launch();
   }
   return TSB_OK;
 }

@@ -3,10 +3,14 @@
 
 #include "common.cuh"
 
+#include <atomic>
+
 namespace tsb {
 namespace {
 thread_local std::string g_last_error;
+std::atomic<long long> g_launches{0};
 }
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 void set_cuda_error(cudaError_t e) {
   g_last_error = cudaGetErrorString(e);
   (void)cudaGetLastError();  // clear the sticky-less error so later calls start clean
@@ -30,5 +34,7 @@ const char* tsb_status_string(int status) {
 }
 
 const char* tsb_last_cuda_error(void) { return tsb::g_last_error.c_str(); }
+
+long long tsb_launch_count(void) { return tsb::g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

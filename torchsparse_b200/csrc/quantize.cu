@@ -151,11 +151,13 @@ int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const do
   // radix sort is stable: inside a run the original indices stay ascending, so the head of a
   // run is the first occurrence
   TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairs(base + w.cub, cb, keys_in, keys_out, idx_in, idx_out, n, 0, 64, s));
+  count_launch();
   int* flags = idx_in;  // idx_in is free after the sort
   head_flags_kernel<<<grid, kBlock, 0, s>>>(keys_out, n, flags);
   TSB_LAUNCH_CHECK();
   cb = w.cub_bytes;
   TSB_CUDA_TRY(cub::DeviceScan::InclusiveSum(base + w.cub, cb, flags, scan, n, s));
+  count_launch();
   emit_kernel<<<grid, kBlock, 0, s>>>(keys_out, idx_out, scan, n, q_all, uniq_coords, first_index, inverse, result);
   TSB_LAUNCH_CHECK();
   return TSB_OK;

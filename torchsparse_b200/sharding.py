@@ -1,0 +1,56 @@
+"""Scan-level data parallelism: scans are independent (the batch index is part of every
+coordinate key and normalisation runs on stored statistics), so a batch is split by scan across
+the GPUs of one box, every rank holds a full copy of the weights and runs its shard on its own
+stream, and the only communication is one gather of the outputs per batch.  The reference has no
+multi-GPU code at all; this module is what a caller of it would have to add."""
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+__all__ = ["shard_range", "balanced_assignment", "gather_rows"]
+
+
+def shard_range(n_items: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous [lo, hi) slice of n_items for `rank`; the first n_items % world_size ranks get
+    one extra item."""
+    if world_size < 1 or not (0 <= rank < world_size):
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    base, extra = divmod(n_items, world_size)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def balanced_assignment(sizes: Sequence[int], world_size: int) -> List[List[int]]:
+    """Greedy longest-first assignment of items (e.g. scans by voxel count) to ranks; returns the
+    item indices of every rank.  Deterministic for equal inputs on every rank."""
+    order = sorted(range(len(sizes)), key=lambda i: (-sizes[i], i))
+    loads = [0] * world_size
+    out: List[List[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda k: (loads[k], k))
+        out[r].append(i)
+        loads[r] += sizes[i]
+    return [sorted(v) for v in out]
+
+
+def gather_rows(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> Tuple[torch.Tensor, List[int]]:
+    """All-gather of row-major [n_r, C] tensors with a different row count per rank.
+    Returns (rows of all ranks concatenated in rank order, list of per-rank row counts).
+    Two collectives: the counts (world_size int64) and the rows padded to the largest count."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return local, [local.shape[0]]
+    world = dist.get_world_size(group)
+    n = torch.tensor([local.shape[0]], dtype=torch.int64, device=local.device)
+    counts = torch.empty(world, dtype=torch.int64, device=local.device)
+    dist.all_gather_into_tensor(counts, n, group=group)
+    counts_host = counts.cpu().tolist()
+    mx = max(counts_host)
+    padded = local
+    if local.shape[0] != mx:
+        padded = torch.zeros((mx,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        padded[: local.shape[0]] = local
+    buf = torch.empty((world * mx,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(buf, padded.contiguous(), group=group)
+    parts = [buf[r * mx: r * mx + counts_host[r]] for r in range(world)]
+    return torch.cat(parts, 0), counts_host
