@@ -191,11 +191,21 @@ int tsb_build_masks(int64_t n_in, int64_t n_out, const int32_t* nbmaps, const in
  * conv_forward_implicit_gemm_sorted_cuda
  * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_sorted_cuda.cu:1755-2230). */
 size_t tsb_conv_igemm_workspace_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype);
-int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const int32_t* out_in_map,
-                       const int32_t* reorder_loc, void* out_feats, int64_t n_in, int64_t n_out,
-                       int32_t kvol, int32_t cin, int32_t cout, int32_t dtype, int32_t math,
-                       const float* bias, const void* residual, int32_t relu, void* workspace,
-                       size_t workspace_bytes, tsb_stream_t stream);
+int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* packed_weight,
+                       const int32_t* out_in_map, const int32_t* reorder_loc, void* out_feats,
+                       int64_t n_in, int64_t n_out, int32_t kvol, int32_t cin, int32_t cout,
+                       int32_t dtype, int32_t math, const float* bias, const void* residual,
+                       int32_t relu, int32_t* dev_status, void* workspace, size_t workspace_bytes,
+                       tsb_stream_t stream);
+
+/* The tensor-core kernel reads the weights K-major ([kvol, cout, cin]).  A caller whose weights
+ * do not change between calls (inference) packs them once and passes the result as
+ * packed_weight above; with packed_weight == NULL every call packs into its workspace.
+ * dev_status (int32, device, nullable) receives a non-zero code if a bounded wait inside the
+ * kernel ran out (the output is then undefined).  No counterpart in the reference. */
+size_t tsb_conv_packed_weight_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype);
+int tsb_conv_pack_weight(const void* weight, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype,
+                         void* packed, tsb_stream_t stream);
 
 /* Gather -> grouped GEMM -> scatter over pair lists (nbmaps [P,2], HOST nbsizes [kvol]).
  * scatter_mask is the output_mask of tsb_build_masks (the input_mask when transpose != 0):

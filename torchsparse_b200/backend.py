@@ -331,6 +331,32 @@ def build_mask_from_kmap(n_points: int, n_out_points: int, nbmaps: torch.Tensor,
 
 
 # --------------------------------------------------------------------------- convolution
+# Weights packed K-major for the tensor-core kernel are cached ON the weight tensor object, tagged
+# with its version counter, so an inference loop packs each layer once and an in-place update
+# through torch invalidates the copy.  Turn off for weights rewritten through raw pointers.
+cache_packed_weights = True
+# When True every tensor-core launch is followed by a read of its device status word (a sync).
+check_kernel_status = False
+
+
+def _packed_weight(kernel: torch.Tensor, code: int) -> Optional[torch.Tensor]:
+    if code == _lib.TSB_F32:
+        return None
+    tag = (kernel._version, kernel.data_ptr())
+    hit = getattr(kernel, "_tsb_packed", None)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    kvol, cin, cout = kernel.shape
+    packed = torch.empty(lib.tsb_conv_packed_weight_bytes(kvol, cin, cout, code), dtype=torch.uint8,
+                         device=kernel.device)
+    check(lib.tsb_conv_pack_weight(_p(kernel), kvol, cin, cout, code, _p(packed), _stream()), "pack_weight")
+    try:
+        kernel._tsb_packed = (tag, packed)
+    except (AttributeError, RuntimeError):
+        pass
+    return packed
+
+
 def _math_mode(t: torch.Tensor, allow_tf32: bool) -> int:
     return _lib.TSB_MATH_TF32 if (t.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
 
@@ -371,16 +397,21 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
         bias = bias.float().contiguous()
     if residual is not None:
         residual = residual.to(in_feats.dtype).contiguous()
+    packed = _packed_weight(kernel, code) if cache_packed_weights else None
+    status = torch.zeros(1, dtype=torch.int32, device=in_feats.device) if check_kernel_status else None
     if _observer is not None:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
-    check(lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(out_in_map), _p(reorder_loc), _p(out),
+    check(lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(packed), _p(out_in_map), _p(reorder_loc), _p(out),
                                  in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
-                                 _math_mode(in_feats, allow_tf32), _p(bias), _p(residual), int(relu), _p(ws),
-                                 ws.numel(), _stream()), "conv_forward_implicit_gemm_cuda")
+                                 _math_mode(in_feats, allow_tf32), _p(bias), _p(residual), int(relu), _p(status),
+                                 _p(ws), ws.numel(), _stream()), "conv_forward_implicit_gemm_cuda")
     if _observer is not None:
         ev1.record()
         _observer("igemm", (in_feats.shape[0], num_out_feats, kvol, cin, cout, code, out_in_map), ev0, ev1)
+    if status is not None and int(status.item()) != 0:
+        raise RuntimeError(f"conv_forward_implicit_gemm_cuda: a bounded wait inside the kernel ran out "
+                           f"(code {int(status.item())}); the output is undefined")
     return out
 
 

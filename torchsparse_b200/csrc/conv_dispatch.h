@@ -10,6 +10,7 @@ namespace tsb {
 struct IgemmArgs {
   const void* x;
   const void* w;
+  const void* packed_w;  // nullable: weights already in [kvol, cout, cin] order
   const int* map;
   const int* reorder_loc;
   void* y;
@@ -18,6 +19,7 @@ struct IgemmArgs {
   const float* bias;
   const void* residual;
   int relu;
+  int* dev_status;  // nullable
   void* workspace;
   size_t workspace_bytes;
 };
@@ -58,5 +60,7 @@ size_t gs_workspace_bytes(int64_t n_pairs, int kvol, int cin, int cout, int dtyp
 bool igemm_umma_supported(const IgemmArgs& a);
 size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype);
 int igemm_umma(const IgemmArgs& a, cudaStream_t s);
+size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype);
+int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* packed, cudaStream_t s);
 
 }  // namespace tsb

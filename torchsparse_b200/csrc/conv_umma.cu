@@ -1,8 +1,515 @@
-// placeholder until the tcgen05 kernel lands
+// Implicit-GEMM sparse convolution forward on the 5th-generation tensor cores (tcgen05 / TMEM).
+//
+//   Y[m, :] = sum_k  X[map[m][k], :] . W[k]         (fp16 or bf16 operands, fp32 accumulation)
+//
+// One CTA owns 128 consecutive output rows (the rows of one map tile) and an N-tile of at most
+// 256 output channels.  The reduction runs over "K blocks": one kernel offset k x one 64-channel
+// chunk of Cin.  K blocks whose offset has no neighbour in the whole tile are skipped (the tile's
+// 128 x Kvol map slice is staged in shared memory first and OR-reduced into an offset mask), so
+// the issued MMA work follows the sparsity of the map; with a row-sorted map the skipping gets
+// coarser-grained and the output rows are scattered through reorder_loc.
+//
+// Roles (160 threads):
+//   warps 0-3  producers: gather the 128 A rows (each a 128-byte slice of a feature row, or zeros
+//              for a missing neighbour) and the N_tile weight rows of the K block into a
+//              128B-swizzled K-major stage with 16-byte cp.async; completion is signalled with
+//              cp.async.mbarrier.arrive on the stage's "full" barrier.  Afterwards the same
+//              warps run the epilogue: tcgen05.ld of their 32 TMEM lanes, bias / residual / ReLU,
+//              rounding and 16-byte stores.
+//   warp 4     allocates TMEM; its lane 0 issues tcgen05.mma (M=128, N=N_tile, K=16, 4 per stage)
+//              and releases stages / publishes the accumulator with tcgen05.commit.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records an error
+// code, and the CTA drains its copies, frees its TMEM and returns.
 #include "common.cuh"
 #include "conv_dispatch.h"
+
 namespace tsb {
-bool igemm_umma_supported(const IgemmArgs&) { return false; }
-size_t igemm_umma_workspace_bytes(int, int, int, int) { return 256; }
-int igemm_umma(const IgemmArgs&, cudaStream_t) { return TSB_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kChunkK = 64;                 // 16-bit elements per stage row = 128 bytes
+constexpr int kRowBytes = 128;
+constexpr int kABytes = kTileM * kRowBytes; // 16 KiB
+constexpr int kProducerThreads = 128;
+constexpr int kThreads = 160;
+constexpr int kMaxStages = 8;
+constexpr int kMaxKvolUmma = 32;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait; false after kSpinLimit polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 1023u) == 1023u) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+#if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM101_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
+#define TSB_TCGEN05 1
+#endif
+
+__device__ __forceinline__ void tc_fence_before() {
+#ifdef TSB_TCGEN05
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void tc_fence_after() {
+#ifdef TSB_TCGEN05
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+#ifdef TSB_TCGEN05
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+#ifdef TSB_TCGEN05
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+#endif
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+#ifdef TSB_TCGEN05
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+#endif
+}
+// arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+#ifdef TSB_TCGEN05
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+#endif
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+#ifdef TSB_TCGEN05
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#endif
+}
+
+// K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);          // start address, leading byte offset (unused) = 1
+  uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);         // stride byte offset 1024, version 1, SWIZZLE_128B
+  return ((uint64_t)hi << 32) | lo;
+}
+
+// instruction descriptor: D fp32, A/B fp16 (0) or bf16 (1), both K-major, M = 128, N = n
+__host__ __device__ inline uint32_t make_idesc(int ab_format, int n) {
+  return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kTileM >> 4) << 24);
+}
+
+struct UmmaParams {
+  const void* x;        // [n_in, cin]
+  const void* wt;       // packed weights [kvol, cout, cin] (K-major)
+  const int* map;       // [pad128(n_out), kvol]
+  const int* reorder;   // nullable
+  void* y;              // [n_out, cout]
+  const float* bias;    // nullable
+  const void* residual; // nullable, [n_out, cout]
+  int* error;           // device error word (0 = fine)
+  int n_in, n_out, kvol, cin, cout;
+  int n_tile;           // UMMA N of a full tile (multiple of 16, <= 256)
+  int stages;
+  int relu;
+  int ab_format;        // 0 fp16, 1 bf16
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t s_full[kMaxStages];
+  __shared__ uint64_t s_empty[kMaxStages];
+  __shared__ uint64_t s_acc;
+  __shared__ uint32_t s_tmem;
+  __shared__ uint32_t s_mask;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = blockIdx.x * kTileM;
+  const int n0 = blockIdx.y * p.n_tile;
+  const int n_valid = min(p.n_tile, p.cout - n0);          // real output channels of this N tile
+  const int n_mma = (n_valid + 15) & ~15;                   // UMMA N (zero rows beyond n_valid)
+  const int b_bytes = p.n_tile * kRowBytes;
+  const int stage_bytes = kABytes + b_bytes;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t map_smem = smem_base + (uint32_t)p.stages * stage_bytes;
+  int* s_map = reinterpret_cast<int*>(smem_raw + (map_smem - smem_u32(smem_raw)));
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < n_mma) tmem_cols <<= 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), kProducerThreads);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_acc), 1);
+    s_mask = 0;
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4) tmem_alloc(smem_u32(&s_tmem), tmem_cols);
+  // stage the tile's slice of the map (contiguous: 128 rows x kvol ints)
+  {
+    const int* src = p.map + (int64_t)row0 * p.kvol;
+    for (int i = tid; i < kTileM * p.kvol; i += kThreads) s_map[i] = __ldg(&src[i]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem;
+  // offset mask: bit k set when some row of the tile has a neighbour at offset k
+  if (tid < kProducerThreads) {
+    uint32_t mine = 0;
+    for (int k = 0; k < p.kvol; ++k) {
+      int v = s_map[tid * p.kvol + k];
+      if (v >= p.n_in) { v = -1; s_map[tid * p.kvol + k] = -1; }
+      mine |= (uint32_t)(v >= 0) << k;
+    }
+    for (int o = 16; o; o >>= 1) mine |= __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0 && mine) atomicOr(&s_mask, mine);
+  }
+  __syncthreads();
+  const uint32_t kmask = s_mask;
+  const int chunks = (p.cin + kChunkK - 1) / kChunkK;
+  const int n_blocks = __popc(kmask) * chunks;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------ producers
+    const T* x = reinterpret_cast<const T*>(p.x);
+    const T* wt = reinterpret_cast<const T*>(p.wt);
+    const int sub = lane >> 3;       // row within a group of 4 rows per warp instruction
+    const int gran = lane & 7;       // 16-byte granule within the 128-byte row
+    int it = 0;
+    bool ok = true;
+    for (int k = 0; k < p.kvol && ok; ++k) {
+      if (!((kmask >> k) & 1u)) continue;
+      for (int c = 0; c < chunks && ok; ++c, ++it) {
+        const int stage = it % p.stages;
+        if (it >= p.stages) {
+          if (!mbar_wait(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1)) {
+            atomicExch(p.error, kErrEmptyWait);
+            s_abort = 1;
+            ok = false;
+            break;
+          }
+        }
+        const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
+        const uint32_t b_base = a_base + kABytes;
+        const int c0 = c * kChunkK;
+        const int col = c0 + gran * 8;                       // first channel of this thread's granule
+        const uint32_t col_ok = (col < p.cin) ? 16u : 0u;   // cin % 8 == 0: a granule is all-in or all-out
+        // A: 128 rows, 4 rows per warp instruction, 8 instructions per warp
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = warp * 32 + j * 4 + sub;
+          const int src = s_map[r * p.kvol + k];
+          const uint32_t dst = a_base + (uint32_t)r * kRowBytes + (uint32_t)((gran ^ (r & 7)) << 4);
+          const T* g = x + ((src >= 0) ? ((int64_t)src * p.cin + col) : 0);
+          cp_async16(dst, (src >= 0 && col_ok) ? (const void*)g : (const void*)x, (src >= 0) ? col_ok : 0u);
+        }
+        // B: n_mma weight rows of offset k (rows >= n_valid are zero)
+        const T* wk = wt + ((int64_t)k * p.cout + n0) * p.cin;
+        for (int r = warp * 4 + sub; r < n_mma; r += 16) {
+          const uint32_t dst = b_base + (uint32_t)r * kRowBytes + (uint32_t)((gran ^ (r & 7)) << 4);
+          const bool live = (r < n_valid) && col_ok;
+          cp_async16(dst, live ? (const void*)(wk + (int64_t)r * p.cin + col) : (const void*)wt, live ? 16u : 0u);
+        }
+        cp_async_arrive_noinc(smem_u32(&s_full[stage]));
+      }
+    }
+    cp_async_wait_all();
+
+    // ------------------------------------------------------------ epilogue
+    bool have_acc = false;
+    if (ok && n_blocks > 0) {
+      have_acc = mbar_wait(smem_u32(&s_acc), 0);
+      if (!have_acc) {
+        atomicExch(p.error, kErrAccWait);
+        s_abort = 1;
+      }
+    }
+    tc_fence_after();
+    const int r = warp * 32 + lane;
+    const int64_t grow = (int64_t)row0 + r;
+    int64_t dst_row = -1;
+    if (grow < p.n_out) {
+      dst_row = p.reorder ? (int64_t)__ldg(&p.reorder[grow]) : grow;
+      if (dst_row >= p.n_out) dst_row = -1;
+    }
+    T* y = reinterpret_cast<T*>(p.y);
+    const T* res = reinterpret_cast<const T*>(p.residual);
+    const bool store = (ok && (have_acc || n_blocks == 0));
+    for (int j = 0; j < n_mma; j += 16) {
+      uint32_t v[16];
+      if (have_acc) {
+        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)j, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0u;
+      }
+      if (!store || dst_row < 0) continue;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int n = n0 + j + h * 8;
+        if (n >= p.cout) continue;        // cout % 8 == 0: 8-channel groups are all-in or all-out
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[h * 8 + i]);
+        if (p.bias) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] += __ldg(&p.bias[n + i]);
+        }
+        if (res) {
+          uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n));
+          const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 t = unpack2<T>(rw[i]);
+            f[2 * i] += t.x;
+            f[2 * i + 1] += t.y;
+          }
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = fmaxf(f[i], 0.f);
+        }
+        uint4 o;
+        o.x = pack2<T>(f[0], f[1]);
+        o.y = pack2<T>(f[2], f[3]);
+        o.z = pack2<T>(f[4], f[5]);
+        o.w = pack2<T>(f[6], f[7]);
+        *reinterpret_cast<uint4*>(y + dst_row * p.cout + n) = o;
+      }
+    }
+    tc_fence_before();
+  } else {
+    // ------------------------------------------------------------ MMA issuer (warp 4)
+    if (lane == 0 && n_blocks > 0) {
+      const uint32_t idesc = make_idesc(p.ab_format, n_mma);
+      bool ok = true;
+      int it = 0;
+      for (int k = 0; k < p.kvol && ok; ++k) {
+        if (!((kmask >> k) & 1u)) continue;
+        for (int c = 0; c < chunks; ++c, ++it) {
+          const int stage = it % p.stages;
+          if (!mbar_wait(smem_u32(&s_full[stage]), (it / p.stages) & 1)) {
+            atomicExch(p.error, kErrFullWait);
+            s_abort = 1;
+            ok = false;
+            break;
+          }
+          fence_proxy_async();
+          tc_fence_after();
+          const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
+          const uint64_t a_desc = make_smem_desc(a_base);
+          const uint64_t b_desc = make_smem_desc(a_base + kABytes);
+          const int kc = min(kChunkK, p.cin - c * kChunkK);
+          const int steps = (kc + 15) >> 4;
+          for (int s = 0; s < steps; ++s) {
+            // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
+            umma_f16(tmem_base, a_desc + (uint64_t)(2 * s), b_desc + (uint64_t)(2 * s), idesc, (it | s) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&s_empty[stage]));
+        }
+      }
+      umma_commit(smem_u32(&s_acc));   // also on the error path: lets the epilogue's bounded wait end early
+    }
+    __syncwarp();
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// W [kvol, cin, cout] -> Wt [kvol, cout, cin]
+template <typename T>
+__global__ void pack_weight_kernel(const T* __restrict__ w, T* __restrict__ wt, int cin, int cout) {
+  __shared__ T tile[32][33];
+  const int k = blockIdx.z;
+  const int c0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  const T* src = w + (int64_t)k * cin * cout;
+  T* dst = wt + (int64_t)k * cin * cout;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    int c = c0 + i, n = n0 + threadIdx.x;
+    if (c < cin && n < cout) tile[i][threadIdx.x] = src[(int64_t)c * cout + n];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    int n = n0 + i, c = c0 + threadIdx.x;
+    if (c < cin && n < cout) dst[(int64_t)n * cin + c] = tile[threadIdx.x][i];
+  }
+}
+
+size_t smem_bytes_for(int n_tile, int stages, int kvol) {
+  return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)kTileM * kvol * sizeof(int);
+}
+
+// stages so that two CTAs fit one SM when possible (about 113 KiB each), else one CTA
+int pick_stages(int n_tile, int kvol) {
+  const size_t two_cta = 112 * 1024, one_cta = 226 * 1024;
+  int best = 0;
+  for (int s = 2; s <= 6; ++s)
+    if (smem_bytes_for(n_tile, s, kvol) <= two_cta) best = s;
+  if (best >= 2) return best;
+  for (int s = 2; s <= 4; ++s)
+    if (smem_bytes_for(n_tile, s, kvol) <= one_cta) best = s;
+  return best;
+}
+
+int pick_n_tile(int cout) {
+  int n = (cout + 15) & ~15;
+  return n > 256 ? 256 : n;
+}
+
+}  // namespace
+
+bool igemm_umma_supported(const IgemmArgs& a) {
+  if (a.dtype != TSB_F16 && a.dtype != TSB_BF16) return false;
+  if (a.cin % 8 || a.cout % 8) return false;        // 16-byte granules of rows
+  if (a.kvol > kMaxKvolUmma) return false;
+  if (((uintptr_t)a.x | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual | (uintptr_t)a.packed_w) & 15)
+    return false;
+  return pick_stages(pick_n_tile(a.cout), a.kvol) >= 2;
+}
+
+size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype) {
+  return align_up((size_t)kvol * cin * cout * dtype_size(dtype), 256);
+}
+
+size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype) {
+  if (dtype == TSB_F32) return 256;
+  return packed_weight_bytes(kvol, cin, cout, dtype) + 256;   // packed weights + error word
+}
+
+template <typename T>
+static int pack_launch(const void* w, int kvol, int cin, int cout, void* packed, cudaStream_t s) {
+  dim3 pgrid((unsigned)cdiv(cout, 32), (unsigned)cdiv(cin, 32), (unsigned)kvol);
+  pack_weight_kernel<T><<<pgrid, dim3(32, 8), 0, s>>>((const T*)w, (T*)packed, cin, cout);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* packed, cudaStream_t s) {
+  if (dtype == TSB_F32) return pack_launch<float>(w, kvol, cin, cout, packed, s);
+  if (dtype == TSB_F16) return pack_launch<__half>(w, kvol, cin, cout, packed, s);
+  return pack_launch<__nv_bfloat16>(w, kvol, cin, cout, packed, s);
+}
+
+template <typename T>
+static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
+  const size_t w_bytes = packed_weight_bytes(a.kvol, a.cin, a.cout, a.dtype);
+  const T* wt = reinterpret_cast<const T*>(a.packed_w);
+  int* err = a.dev_status;
+  if (!wt || !err) {
+    if (!a.workspace || a.workspace_bytes < w_bytes + 256) return TSB_ERR_WORKSPACE;
+  }
+  if (!err) {
+    err = reinterpret_cast<int*>(reinterpret_cast<char*>(a.workspace) + w_bytes);
+    TSB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), s));
+  }
+  if (!wt) {
+    int rc = pack_launch<T>(a.w, a.kvol, a.cin, a.cout, a.workspace, s);
+    if (rc != TSB_OK) return rc;
+    wt = reinterpret_cast<const T*>(a.workspace);
+  }
+  UmmaParams p;
+  p.x = a.x; p.wt = wt; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias;
+  p.residual = a.residual; p.error = err;
+  p.n_in = (int)a.n_in; p.n_out = (int)a.n_out; p.kvol = a.kvol; p.cin = a.cin; p.cout = a.cout;
+  p.n_tile = pick_n_tile(a.cout);
+  p.stages = pick_stages(p.n_tile, a.kvol);
+  p.relu = a.relu;
+  p.ab_format = (a.dtype == TSB_BF16) ? 1 : 0;
+  const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol);
+  static bool attr_set[2] = {false, false};
+  const int ti = (a.dtype == TSB_BF16) ? 1 : 0;
+  if (!attr_set[ti]) {
+    TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    attr_set[ti] = true;
+  }
+  dim3 grid((unsigned)cdiv(a.n_out, kTileM), (unsigned)cdiv(a.cout, p.n_tile));
+  igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int igemm_umma(const IgemmArgs& a, cudaStream_t s) {
+  if (a.dtype == TSB_F16) return umma_launch<__half>(a, s);
+  if (a.dtype == TSB_BF16) return umma_launch<__nv_bfloat16>(a, s);
+  return TSB_ERR_UNSUPPORTED;
+}
+
 }  // namespace tsb
