@@ -81,6 +81,24 @@ size_t tsb_hash_query_workspace_bytes(int64_t n_ref);
 int tsb_hash_query(const int64_t* queries, int64_t n_q, const int64_t* refs, int64_t n_ref,
                    int64_t* out, void* workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* The same join for callers that are not allowed to allocate device memory and have no scratch
+ * buffer to lend: for example a plug-in that a host application calls with nothing but its input
+ * and output buffers, or a real-time perception loop whose device memory is carved up once at
+ * start-up and where a cudaMalloc in the loop (it synchronises the device and can fail) is ruled
+ * out.  This entry point has no counterpart in the reference.
+ *
+ * The private table lives in a 6 MiB array compiled into the library (every GPU that loads the
+ * library holds it until the process exits), so n_ref is limited to
+ * tsb_hash_query_static_max_refs() = 262144 keys; a larger n_ref returns TSB_ERR_LIMIT and does
+ * nothing.  The call allocates and frees nothing.  The first call on each device looks up the
+ * array's device address (a host-side runtime query, not a launch): make that first call before
+ * starting any stream capture.  All calls share the one array and each call clears it first, so
+ * two calls whose work overlaps on the GPU (different streams, no dependency) race; calls issued
+ * to one stream are safe.  Results equal tsb_hash_query's. */
+int64_t tsb_hash_query_static_max_refs(void);
+int tsb_hash_query_static(const int64_t* queries, int64_t n_q, const int64_t* refs, int64_t n_ref,
+                          int64_t* out, tsb_stream_t stream);
+
 /* ---------------------------------------------------------------- kernel maps
  * Coordinates are int32 rows (b,x,y,z).  cmin/cmax are HOST int32[4] arrays: the
  * inclusive bounds used for the ravel index and the x,y,z bounds check.

@@ -28,6 +28,8 @@ SIGNATURES = {
     "tsb_hash_lookup": (C.c_int, [P, P, I64, P, I64, P, P]),
     "tsb_hash_query_workspace_bytes": (SZ, [I64]),
     "tsb_hash_query": (C.c_int, [P, I64, P, I64, P, P, SZ, P]),
+    "tsb_hash_query_static_max_refs": (I64, []),
+    "tsb_hash_query_static": (C.c_int, [P, I64, P, I64, P, P]),
     "tsb_kmap_subm": (C.c_int, [P, P, I64, P, I64, P, P, P, I32, P, P, P]),
     "tsb_kmap_down_slots": (I32, [P, P]),
     "tsb_kmap_down_workspace_bytes": (SZ, [I64, P, P]),

@@ -6,6 +6,8 @@
 // and one write of the map, with random 8-byte probes into an L2-resident table.
 #include <cub/cub.cuh>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace tsb {
@@ -511,6 +513,63 @@ int tsb_hash_query(const int64_t* queries, int64_t n_q, const int64_t* refs, int
   cudaStream_t s = as_stream(stream);
   TSB_CUDA_TRY(cudaMemsetAsync(workspace, 0, (size_t)cap * 12, s));
   TableView t = make_table(tk, tv, cap);
+  if (n_ref) {
+    table_insert_kernel<<<grid_for(n_ref, kBlock), kBlock, 0, s>>>(t, refs, n_ref, nullptr);
+    TSB_LAUNCH_CHECK();
+  }
+  table_query_kernel<<<grid_for(n_q, kBlock), kBlock, 0, s>>>(t, queries, n_q, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// tsb_hash_query_static: the same join as tsb_hash_query, for callers that may not allocate.
+// The private table lives in a file-scope device array instead of a caller workspace.
+namespace {
+constexpr int64_t kStaticQueryMaxRefs = 262144;                    // documented limit of the entry point
+constexpr int64_t kStaticQueryCap = 2 * kStaticQueryMaxRefs;       // power of two, load factor <= 0.5
+constexpr size_t kStaticQueryBytes = (size_t)kStaticQueryCap * (sizeof(int64_t) + sizeof(int32_t));  // 6 MiB
+// Resident on every GPU that loads this library, from load to exit.
+static __device__ __align__(256) unsigned char g_static_query_table[kStaticQueryBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_query_ptr[kMaxDevices] = {};   // device address of the array, per device ordinal
+std::mutex g_static_query_mutex;
+
+// In host code the array's name is only a handle; the device address has to be asked for, once
+// per device, with that device current.
+int static_query_table(void** out) {
+  int dev = -1;
+  TSB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TSB_ERR_LIMIT;
+  std::lock_guard<std::mutex> lock(g_static_query_mutex);
+  if (!g_static_query_ptr[dev]) {
+    void* p = nullptr;
+    TSB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_query_table));
+    if (!p) return TSB_ERR_CUDA;
+    g_static_query_ptr[dev] = p;
+  }
+  *out = g_static_query_ptr[dev];
+  return TSB_OK;
+}
+}  // namespace
+
+int64_t tsb_hash_query_static_max_refs(void) { return kStaticQueryMaxRefs; }
+
+int tsb_hash_query_static(const int64_t* queries, int64_t n_q, const int64_t* refs, int64_t n_ref, int64_t* out,
+                          tsb_stream_t stream) {
+  if (n_q < 0 || n_ref < 0 || (n_q && (!queries || !out)) || (n_ref && !refs)) return TSB_ERR_BAD_ARG;
+  if (n_ref > kStaticQueryMaxRefs) return TSB_ERR_LIMIT;   // the fixed table cannot hold more keys
+  if (n_q == 0) return TSB_OK;
+  void* base = nullptr;
+  int rc = static_query_table(&base);
+  if (rc != TSB_OK) return rc;
+  int64_t* tk = reinterpret_cast<int64_t*>(base);
+  int32_t* tv = reinterpret_cast<int32_t*>(tk + kStaticQueryCap);
+  cudaStream_t s = as_stream(stream);
+  // the array keeps whatever the previous call left: empty it first
+  TSB_CUDA_TRY(cudaMemsetAsync(base, 0, kStaticQueryBytes, s));
+  TableView t = make_table(tk, tv, kStaticQueryCap);
   if (n_ref) {
     table_insert_kernel<<<grid_for(n_ref, kBlock), kBlock, 0, s>>>(t, refs, n_ref, nullptr);
     TSB_LAUNCH_CHECK();
