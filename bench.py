@@ -119,7 +119,7 @@ class ClockSampler:
         self.idx = gpu_index
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(gpu_index)],
+                                          "-lms", "250", "-i", str(gpu_index)],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -170,6 +170,8 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     from torchsparse_b200 import backend
     from torchsparse_b200.sharding import gather_rows
 
+    from torchsparse_b200.nn import functional as F
+    F.set_conv_mode(args.conv_mode)
     model = make_model(device)
     scans = [scan_points(1000 * rank + i) for i in range(SCAN_POOL)]
     host = [torch.from_numpy(s).pin_memory() for s in scans]
@@ -191,10 +193,25 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         out = logits.cpu() if e2e else logits
         return out, h.numel() * h.element_size(), (logits.numel() * logits.element_size() if e2e else 0)
 
+    # useful-FLOP bookkeeping: the number of valid (row, offset) pairs of every conv launch of every
+    # pooled scan, taken in an untimed pass (the timed pass must not keep maps alive or sync)
+    pairs_of_scan = []
+    with torch.no_grad():
+        for i in range(SCAN_POOL):
+            plist = []
+            backend.set_launch_observer(
+                lambda name, dims, e0, e1, plist=plist: plist.append(int((dims[6][: dims[1]] >= 0).sum().item())))
+            forward_scan(model, resident[i])
+            backend.set_launch_observer(None)
+            pairs_of_scan.append(plist)
+    torch.cuda.synchronize()
+
     records = []
+    cur = {"step": 0, "k": 0}
 
     def observer(name, dims, ev0, ev1):
-        records.append((dims, ev0, ev1))
+        records.append((cur["step"], cur["k"], dims[:6], ev0, ev1))
+        cur["k"] += 1
 
     def timed(e2e: bool, observe: bool):
         with torch.no_grad():
@@ -209,6 +226,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                 flush.fill_(i & 0xFF)       # evict L2 between steps (outside the timed events)
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
+                cur["step"], cur["k"] = i, 0
                 _, bi, bo = step(i, e2e)
                 e1.record(stream)
                 h2d, d2h = bi, bo
@@ -225,7 +243,9 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     sampler = ClockSampler(device.index or 0) if rank == 0 else None
     ms_total, launches, _, _ = timed(False, True)
     clocks = sampler.stop() if sampler else None
-    e2e_ms, _, h2d, d2h = timed(True, False)
+    e2e_ms, h2d, d2h = float("nan"), 0, 0
+    if not args.no_e2e:
+        e2e_ms, _, h2d, d2h = timed(True, False)
 
     if rank != 0:
         return None
@@ -236,15 +256,10 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     # ---- roofline of the dominant kernel (largest total time among conv layer shapes)
     pk = peaks()
     by_shape = {}
-    pair_cache = {}
-    for dims, ev0, ev1 in records:
-        key = dims[:6]
-        m = dims[6]
-        pk_key = (m.data_ptr(), tuple(m.shape))
-        if pk_key not in pair_cache:
-            pair_cache[pk_key] = int((m[: dims[1]] >= 0).sum().item())
+    for step_i, k_i, key, ev0, ev1 in records:
+        pairs = pairs_of_scan[step_i % SCAN_POOL][k_i]
         d = by_shape.setdefault(key, {"ms": 0.0, "n": 0, "flops": 0.0, "bytes": 0.0})
-        fl, by = conv_algorithmic(dims, pair_cache[pk_key])
+        fl, by = conv_algorithmic(key + (None,), pairs)
         d["ms"] += ev0.elapsed_time(ev1); d["n"] += 1; d["flops"] += fl; d["bytes"] += by
     roof = None
     conv_ms = sum(d["ms"] for d in by_shape.values())
@@ -274,6 +289,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                                "inference, one synthetic 64-ring LiDAR scan (144k points, 0.05 m voxels) per GPU per step",
                    "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": scans_per_step,
                    "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps; {SCAN_POOL} scans rotated",
+                   "conv_mode": args.conv_mode,
                    "parallelism": f"scan-sharded x{world}, NCCL all-gather of logits" if world > 1 else "single GPU"},
         "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
@@ -281,7 +297,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         "clocks": clocks,
         "roofline": roof,
     }
-    if world == 1:
+    if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(budget_s=20.0)
     return out
 
@@ -354,12 +370,74 @@ def run_reference(args):
     }
 
 
+def run_layer(args, device):
+    """Single sparse Conv3d layer (BASELINE config 5 cell): --layer N,Cin,Cout,kernel,stride,occupancy
+    [--dataflow ImplicitGEMM|GatherScatter|FetchOnDemand] [--dtype f16|bf16|f32] [--sorted].
+    Prints one JSON line with time, useful TFLOP/s and algorithmic GB/s of the conv launch."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200 import backend
+    from torchsparse_b200.nn import functional as F
+    from torchsparse_b200.utils.synthetic import uniform_voxels
+
+    n, cin, cout, ks, st = [int(v) for v in args.layer.split(",")[:5]]
+    occ = float(args.layer.split(",")[5]) if len(args.layer.split(",")) > 5 else 0.05
+    dtype = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[args.dtype]
+    coords_np, side = uniform_voxels(0, n, occ)
+    coords = torch.from_numpy(coords_np).to(device)
+    g = torch.Generator(device=device).manual_seed(0)
+    feats = torch.randn(n, cin, device=device, generator=g).to(dtype)
+    kvol = ks ** 3
+    w = (torch.randn(kvol, cin, cout, device=device, generator=g) * (2.0 / (kvol * cin)) ** 0.5).to(dtype)
+    cfg = F.conv_config.get_default_conv_config()
+    cfg.dataflow = getattr(F.Dataflow, args.dataflow)
+    cfg.ifsort = bool(args.sorted)
+    pad = (ks - 1) // 2 if (ks % 2 == 1 and st == 1) else 0
+    x = ts.SparseTensor(feats, coords)
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(); y = F.conv3d(x, w, ks, None, st, pad, config=cfg); t1.record()
+    torch.cuda.synchronize()
+    first_ms = t0.elapsed_time(t1)          # includes the kernel-map build
+    kmap = x._caches.kmaps[((1, 1, 1), (ks,) * 3, (st,) * 3, (1, 1, 1))]
+    n_out = kmap["sizes"][1]
+    pairs = int((kmap["out_in_map"][:n_out] >= 0).sum().item())
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    times = []
+    with torch.no_grad():
+        for i in range(args.warmup + args.steps):
+            flush.fill_(i & 0xFF)
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(); F.conv3d(x, w, ks, None, st, pad, config=cfg); e1.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+    fl, by = conv_algorithmic((n, n_out, kvol, cin, cout, code, None), pairs)
+    pk = peaks()
+    return {"metric": "sparse_conv3d_layer_ms", "value": round(ms, 4), "unit": "ms", "higher_is_better": False,
+            "config": {"workload": f"single Conv3d N={n} {cin}->{cout} k{ks} s{st} occupancy {occ} (grid side {side})",
+                       "dataflow": args.dataflow, "sorted": bool(args.sorted), "dtype": args.dtype},
+            "n_out": n_out, "pairs": pairs, "neighbours_per_row": round(pairs / max(n_out, 1), 2),
+            "useful_tflops": round(fl / ms / 1e9, 2), "algorithmic_gbs": round(by / ms / 1e6, 1),
+            "frac_tensor_peak": round(fl / ms / 1e9 / pk["tensor_tflops"], 4),
+            "frac_hbm_peak": round(by / ms / 1e6 / pk["hbm_gbs"], 4),
+            "first_call_ms_incl_kmap": round(first_ms, 3), "steps": args.steps, "warmup": args.warmup}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--layer", default=None, help="N,Cin,Cout,kernel,stride[,occupancy]: single-layer mode")
+    ap.add_argument("--dataflow", default="ImplicitGEMM")
+    ap.add_argument("--dtype", default="f16")
+    ap.add_argument("--sorted", action="store_true")
+    ap.add_argument("--conv-mode", type=int, default=0, choices=[0, 1, 2],
+                    help="0 unsorted, 1 row-sorted maps, 2 sorted with 3 mask splits (F.set_conv_mode)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -376,6 +454,10 @@ def main():
 
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    if args.layer:
+        if rank == 0:
+            print(json.dumps(run_layer(args, device)), flush=True)
+        return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)

@@ -202,8 +202,10 @@ int tsb_build_masks(int64_t n_in, int64_t n_out, const int32_t* nbmaps, const in
 
 /* Implicit GEMM over an out_in_map [pad128(n_out), kvol].  If reorder_loc != NULL the map
  * is the row-sorted one and output row r is stored at reorder_loc[r] (sorted dataflow).
- * Empty (tile, offset) blocks are skipped in either case.  Optional fused epilogue:
- * bias fp32 [cout] (may be NULL), residual [n_out,cout] of `dtype` (may be NULL), relu flag.
+ * Empty (tile, offset) blocks are skipped in either case.  Optional fused epilogue, applied to the
+ * fp32 accumulator before the single rounding: y = acc * scale[n] + bias[n] + residual[m][n], then
+ * ReLU; scale / bias fp32 [cout], residual [n_out,cout] of `dtype`, each may be NULL (an
+ * inference-mode BatchNorm folds into scale and bias).
  * Replaces conv_forward_implicit_gemm_cuda
  * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987) and
  * conv_forward_implicit_gemm_sorted_cuda
@@ -212,9 +214,9 @@ size_t tsb_conv_igemm_workspace_bytes(int32_t kvol, int32_t cin, int32_t cout, i
 int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* packed_weight,
                        const int32_t* out_in_map, const int32_t* reorder_loc, void* out_feats,
                        int64_t n_in, int64_t n_out, int32_t kvol, int32_t cin, int32_t cout,
-                       int32_t dtype, int32_t math, const float* bias, const void* residual,
-                       int32_t relu, int32_t* dev_status, void* workspace, size_t workspace_bytes,
-                       tsb_stream_t stream);
+                       int32_t dtype, int32_t math, const float* scale, const float* bias,
+                       const void* residual, int32_t relu, int32_t* dev_status, void* workspace,
+                       size_t workspace_bytes, tsb_stream_t stream);
 
 /* The tensor-core kernel reads the weights K-major ([kvol, cout, cin]).  A caller whose weights
  * do not change between calls (inference) packs them once and passes the result as

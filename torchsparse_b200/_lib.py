@@ -47,7 +47,7 @@ SIGNATURES = {
     "tsb_scan_quantified": (C.c_int, [I32, P, P, P, P]),
     "tsb_build_masks": (C.c_int, [I64, I64, P, P, I32, I64, P, P, P]),
     "tsb_conv_igemm_workspace_bytes": (SZ, [I32, I32, I32, I32]),
-    "tsb_conv_igemm_fwd": (C.c_int, [P, P, P, P, P, P, I64, I64, I32, I32, I32, I32, I32, P, P, I32, P, P, SZ, P]),
+    "tsb_conv_igemm_fwd": (C.c_int, [P, P, P, P, P, P, I64, I64, I32, I32, I32, I32, I32, P, P, P, I32, P, P, SZ, P]),
     "tsb_conv_packed_weight_bytes": (SZ, [I32, I32, I32, I32]),
     "tsb_conv_pack_weight": (C.c_int, [P, I32, I32, I32, I32, P, P]),
     "tsb_conv_gs_workspace_bytes": (SZ, [I64, I32, I32, I32, I32]),

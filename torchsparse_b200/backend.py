@@ -376,13 +376,14 @@ def _prep_feats(in_feats: torch.Tensor, kernel: torch.Tensor, allow_fp16: bool):
 
 def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,
                                     num_out_feats: int, num_out_channels: int, allow_tf32: bool = False,
-                                    allow_fp16: bool = True, *, bias: Optional[torch.Tensor] = None,
+                                    allow_fp16: bool = True, *, scale: Optional[torch.Tensor] = None,
+                                    bias: Optional[torch.Tensor] = None,
                                     residual: Optional[torch.Tensor] = None, relu: bool = False,
                                     reorder_loc: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Implicit-GEMM forward
     (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987).
-    ``bias`` (fp32), ``residual`` and ``relu`` are an optional fused epilogue the reference
-    does not have."""
+    ``scale`` / ``bias`` (fp32 [Cout]), ``residual`` and ``relu`` are an optional fused epilogue
+    (y = relu(acc * scale + bias + residual), one rounding) that the reference does not have."""
     in_feats, kernel = _prep_feats(in_feats, kernel, allow_fp16)
     _need_cuda(out_in_map)
     kvol, cin, cout = kernel.shape
@@ -395,6 +396,8 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     ws = _workspace(lib.tsb_conv_igemm_workspace_bytes(kvol, cin, cout, code), in_feats.device)
     if bias is not None:
         bias = bias.float().contiguous()
+    if scale is not None:
+        scale = scale.float().contiguous()
     if residual is not None:
         residual = residual.to(in_feats.dtype).contiguous()
     packed = _packed_weight(kernel, code) if cache_packed_weights else None
@@ -404,7 +407,8 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
         ev0.record()
     check(lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(packed), _p(out_in_map), _p(reorder_loc), _p(out),
                                  in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
-                                 _math_mode(in_feats, allow_tf32), _p(bias), _p(residual), int(relu), _p(status),
+                                 _math_mode(in_feats, allow_tf32), _p(scale), _p(bias), _p(residual), int(relu),
+                                 _p(status),
                                  _p(ws), ws.numel(), _stream()), "conv_forward_implicit_gemm_cuda")
     if _observer is not None:
         ev1.record()
@@ -439,6 +443,8 @@ def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch
                                                False, allow_fp16, reorder_loc=loc[s])
         acc = part if acc is None else acc + part
     bias, residual, relu = epilogue.get("bias"), epilogue.get("residual"), epilogue.get("relu", False)
+    if epilogue.get("scale") is not None:
+        acc = acc * epilogue["scale"]
     if bias is not None:
         acc = acc + bias
     if residual is not None:

@@ -31,15 +31,15 @@ int tsb_conv_pack_weight(const void* weight, int32_t kvol, int32_t cin, int32_t 
 int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* packed_weight,
                        const int32_t* out_in_map, const int32_t* reorder_loc, void* out_feats, int64_t n_in,
                        int64_t n_out, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype, int32_t math,
-                       const float* bias, const void* residual, int32_t relu, int32_t* dev_status, void* workspace,
-                       size_t workspace_bytes, tsb_stream_t stream) {
+                       const float* scale, const float* bias, const void* residual, int32_t relu,
+                       int32_t* dev_status, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
   if (n_in < 0 || n_out < 0 || kvol < 1 || cin < 1 || cout < 1) return TSB_ERR_BAD_ARG;
   if (!valid_dtype(dtype)) return TSB_ERR_UNSUPPORTED;
   if (n_out == 0) return TSB_OK;
   if (!weight || !out_in_map || !out_feats || (n_in && !in_feats)) return TSB_ERR_BAD_ARG;
   if (n_in > INT32_MAX || n_out > INT32_MAX) return TSB_ERR_LIMIT;
   IgemmArgs a{in_feats, weight, packed_weight, out_in_map, reorder_loc, out_feats, n_in, n_out, kvol, cin, cout,
-              dtype, math, bias, residual, relu, dev_status, workspace, workspace_bytes};
+              dtype, math, scale, bias, residual, relu, dev_status, workspace, workspace_bytes};
   if (igemm_umma_supported(a)) return igemm_umma(a, as_stream(stream));
   return igemm_simt(a, as_stream(stream));
 }

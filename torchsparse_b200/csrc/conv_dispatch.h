@@ -16,6 +16,7 @@ struct IgemmArgs {
   void* y;
   int64_t n_in, n_out;
   int kvol, cin, cout, dtype, math;
+  const float* scale;  // nullable: y = acc * scale[n] + bias[n] (+ residual), then ReLU
   const float* bias;
   const void* residual;
   int relu;

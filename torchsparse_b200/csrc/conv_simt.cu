@@ -72,7 +72,8 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 igemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* __restrict__ map,
                   const int* __restrict__ reorder_loc, T* __restrict__ y, int64_t n_in, int64_t n_out, int kvol,
-                  int cin, int cout, const float* __restrict__ bias, const T* __restrict__ residual, int relu) {
+                  int cin, int cout, const float* __restrict__ scale, const float* __restrict__ bias,
+                  const T* __restrict__ residual, int relu) {
   __shared__ TileSmem sm;
   __shared__ int s_rows[BM];
   const int64_t row0 = (int64_t)blockIdx.x * BM;
@@ -112,6 +113,7 @@ igemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* _
       int n = n0 + tx * 4 + j;
       if (n >= cout) continue;
       float v = acc[i][j];
+      if (scale) v *= __ldg(&scale[n]);
       if (bias) v += __ldg(&bias[n]);
       if (residual) v += to_f32(__ldg(&residual[dst * cout + n]));
       if (relu) v = fmaxf(v, 0.f);
@@ -278,7 +280,7 @@ template <typename T>
 int igemm_simt_launch(const IgemmArgs& a, cudaStream_t s) {
   dim3 grid((unsigned)cdiv(a.n_out, BM), (unsigned)cdiv(a.cout, BN));
   igemm_simt_kernel<T><<<grid, kThreads, 0, s>>>((const T*)a.x, (const T*)a.w, a.map, a.reorder_loc, (T*)a.y, a.n_in,
-                                                 a.n_out, a.kvol, a.cin, a.cout, a.bias, (const T*)a.residual, a.relu);
+                                                 a.n_out, a.kvol, a.cin, a.cout, a.scale, a.bias, (const T*)a.residual, a.relu);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }

@@ -9,18 +9,23 @@
 // the issued MMA work follows the sparsity of the map; with a row-sorted map the skipping gets
 // coarser-grained and the output rows are scattered through reorder_loc.
 //
-// Roles (160 threads):
-//   warps 0-3  producers: gather the 128 A rows (each a 128-byte slice of a feature row, or zeros
-//              for a missing neighbour) and the N_tile weight rows of the K block into a
-//              128B-swizzled K-major stage with 16-byte cp.async; completion is signalled with
-//              cp.async.mbarrier.arrive on the stage's "full" barrier.  Afterwards the same
-//              warps run the epilogue: tcgen05.ld of their 32 TMEM lanes, bias / residual / ReLU,
-//              rounding and 16-byte stores.
-//   warp 4     allocates TMEM; its lane 0 issues tcgen05.mma (M=128, N=N_tile, K=16, 4 per stage)
+// Roles (320 threads):
+//   warps 0-7  gather the 128 A rows of a K block (each a 128-byte slice of a feature row, or
+//              zeros for a missing neighbour) into a 128B-swizzled K-major stage with 16-byte
+//              cp.async, a commit group per block; a landed block is fenced for the tensor-core
+//              proxy and one lane per warp arrives on the stage's "full" barrier.  Afterwards the
+//              same warps run the epilogue: tcgen05.ld of their TMEM lanes, scale / bias /
+//              residual / ReLU, rounding and 16-byte stores.
+//   warp 8     one thread loads the weight block of each K block (64 channels x N_tile rows of
+//              the K-major packed weights) with a TMA tile copy that counts bytes on the same
+//              "full" barrier.
+//   warp 9     allocates TMEM; one thread issues tcgen05.mma (M=128, N=N_tile, K=16, 4 per stage)
 //              and releases stages / publishes the accumulator with tcgen05.commit.
 //
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records an error
 // code, and the CTA drains its copies, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "conv_dispatch.h"
 
@@ -31,11 +36,14 @@ constexpr int kTileM = 128;
 constexpr int kChunkK = 64;                 // 16-bit elements per stage row = 128 bytes
 constexpr int kRowBytes = 128;
 constexpr int kABytes = kTileM * kRowBytes; // 16 KiB
-constexpr int kProducerThreads = 128;
-constexpr int kThreads = 160;
+constexpr int kGatherWarps = 8;
+constexpr int kTmaWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
 constexpr int kMaxStages = 8;
 constexpr int kMaxKvolUmma = 32;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 
 enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 
@@ -59,13 +67,39 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// bounded wait; false after kSpinLimit polls
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: try_wait parks the thread in hardware instead of spinning on shared memory (a
+// spinning warp competes with the copies for the load/store pipe).  Gives up after kWaitLimitNs.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_test(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if ((i & 1023u) == 1023u) __nanosleep(64);
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 63u) == 63u && global_ns() - t0 > kWaitLimitNs) return false;
   }
   return false;
+}
+// one lane waits for the warp; the others are released by __syncwarp
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane) {
+  uint32_t ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -74,6 +108,18 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most `pending` of this thread's committed groups are still in flight
+__device__ __forceinline__ void cp_async_wait_pending(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+  }
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
@@ -151,6 +197,7 @@ struct UmmaParams {
   const int* map;       // [pad128(n_out), kvol]
   const int* reorder;   // nullable
   void* y;              // [n_out, cout]
+  const float* scale;   // nullable, fp32 [cout]: y = acc * scale + bias (+ residual), then ReLU
   const float* bias;    // nullable
   const void* residual; // nullable, [n_out, cout]
   int* error;           // device error word (0 = fine)
@@ -184,21 +231,34 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
 
+// TMA tile load of the weight block: box = 64 channels x n_tile rows of the packed weights,
+// written 128B-swizzled; completion is counted in bytes on the mbarrier.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t s_full[kMaxStages];
   __shared__ uint64_t s_empty[kMaxStages];
   __shared__ uint64_t s_acc;
   __shared__ uint32_t s_tmem;
   __shared__ uint32_t s_mask;
-  __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * kTileM;
   const int n0 = blockIdx.y * p.n_tile;
   const int n_valid = min(p.n_tile, p.cout - n0);          // real output channels of this N tile
-  const int n_mma = (n_valid + 15) & ~15;                   // UMMA N (zero rows beyond n_valid)
+  const int n_mma = (n_valid + 15) & ~15;                   // UMMA N
   const int b_bytes = p.n_tile * kRowBytes;
   const int stage_bytes = kABytes + b_bytes;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -209,26 +269,26 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&s_full[s]), kProducerThreads);
+      mbar_init(smem_u32(&s_full[s]), kGatherWarps + 1);   // 8 gather warps + the TMA thread (with byte count)
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     mbar_init(smem_u32(&s_acc), 1);
     s_mask = 0;
-    s_abort = 0;
     fence_barrier_init();
   }
-  if (warp == 4) tmem_alloc(smem_u32(&s_tmem), tmem_cols);
-  // stage the tile's slice of the map (contiguous: 128 rows x kvol ints)
+  if (warp == kMmaWarp) tmem_alloc(smem_u32(&s_tmem), tmem_cols);
+  // stage the tile's slice of the map (contiguous: 128 rows x kvol ints, 16-byte loads)
   {
-    const int* src = p.map + (int64_t)row0 * p.kvol;
-    for (int i = tid; i < kTileM * p.kvol; i += kThreads) s_map[i] = __ldg(&src[i]);
+    const int4* src = reinterpret_cast<const int4*>(p.map + (int64_t)row0 * p.kvol);
+    int4* dst = reinterpret_cast<int4*>(s_map);
+    for (int i = tid; i < kTileM * p.kvol / 4; i += kThreads) dst[i] = __ldg(&src[i]);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
   // offset mask: bit k set when some row of the tile has a neighbour at offset k
-  if (tid < kProducerThreads) {
+  if (tid < kTileM) {
     uint32_t mine = 0;
     for (int k = 0; k < p.kvol; ++k) {
       int v = s_map[tid * p.kvol + k];
@@ -243,63 +303,72 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
   const int chunks = (p.cin + kChunkK - 1) / kChunkK;
   const int n_blocks = __popc(kmask) * chunks;
 
-  if (warp < 4) {
-    // ------------------------------------------------------------ producers
+  if (warp < kGatherWarps) {
+    // ------------------------------------------------------------ gather warps (A operand)
+    // thread -> granule (tid & 7) of rows (tid >> 3) + 32 j, j = 0..3: a warp instruction covers four
+    // whole 128-byte row slices.  Each warp keeps `ahead` K blocks in flight (one commit group per
+    // block); when a block has landed the warp fences its writes for the tensor-core proxy and one
+    // lane arrives on the stage's full barrier.
     const T* x = reinterpret_cast<const T*>(p.x);
-    const T* wt = reinterpret_cast<const T*>(p.wt);
-    const int sub = lane >> 3;       // row within a group of 4 rows per warp instruction
-    const int gran = lane & 7;       // 16-byte granule within the 128-byte row
+    const int gran = tid & 7;
+    const int rbase = tid >> 3;                                   // 0..31
+    const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
+    const int ahead = p.stages - 1;
     int it = 0;
     bool ok = true;
     for (int k = 0; k < p.kvol && ok; ++k) {
       if (!((kmask >> k) & 1u)) continue;
+      const T* rowp[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int src = s_map[(rbase + 32 * j) * p.kvol + k];
+        rowp[j] = (src >= 0) ? x + (int64_t)src * p.cin + gran * 8 : nullptr;
+      }
       for (int c = 0; c < chunks && ok; ++c, ++it) {
         const int stage = it % p.stages;
         if (it >= p.stages) {
-          if (!mbar_wait(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1)) {
+          if (!mbar_wait_warp(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1, lane)) {
             atomicExch(p.error, kErrEmptyWait);
-            s_abort = 1;
             ok = false;
             break;
           }
         }
-        const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
-        const uint32_t b_base = a_base + kABytes;
-        const int c0 = c * kChunkK;
-        const int col = c0 + gran * 8;                       // first channel of this thread's granule
-        const uint32_t col_ok = (col < p.cin) ? 16u : 0u;   // cin % 8 == 0: a granule is all-in or all-out
-        // A: 128 rows, 4 rows per warp instruction, 8 instructions per warp
+        const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes + dst_off;
+        const bool col_ok = (c * kChunkK + gran * 8) < p.cin;     // cin % 8 == 0: all-in or all-out
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int r = warp * 32 + j * 4 + sub;
-          const int src = s_map[r * p.kvol + k];
-          const uint32_t dst = a_base + (uint32_t)r * kRowBytes + (uint32_t)((gran ^ (r & 7)) << 4);
-          const T* g = x + ((src >= 0) ? ((int64_t)src * p.cin + col) : 0);
-          cp_async16(dst, (src >= 0 && col_ok) ? (const void*)g : (const void*)x, (src >= 0) ? col_ok : 0u);
+        for (int j = 0; j < 4; ++j) {
+          const bool live = col_ok && rowp[j] != nullptr;
+          cp_async16(a_dst + (uint32_t)j * (32 * kRowBytes), live ? (const void*)(rowp[j] + c * kChunkK) : (const void*)x,
+                     live ? 16u : 0u);
         }
-        // B: n_mma weight rows of offset k (rows >= n_valid are zero)
-        const T* wk = wt + ((int64_t)k * p.cout + n0) * p.cin;
-        for (int r = warp * 4 + sub; r < n_mma; r += 16) {
-          const uint32_t dst = b_base + (uint32_t)r * kRowBytes + (uint32_t)((gran ^ (r & 7)) << 4);
-          const bool live = (r < n_valid) && col_ok;
-          cp_async16(dst, live ? (const void*)(wk + (int64_t)r * p.cin + col) : (const void*)wt, live ? 16u : 0u);
+        cp_async_commit();
+        if (it >= ahead) {
+          cp_async_wait_pending(ahead);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&s_full[(it - ahead) % p.stages]));
         }
-        cp_async_arrive_noinc(smem_u32(&s_full[stage]));
       }
     }
     cp_async_wait_all();
-
-    // ------------------------------------------------------------ epilogue
-    bool have_acc = false;
-    if (ok && n_blocks > 0) {
-      have_acc = mbar_wait(smem_u32(&s_acc), 0);
-      if (!have_acc) {
-        atomicExch(p.error, kErrAccWait);
-        s_abort = 1;
+    if (ok) {   // publish the last `ahead` blocks
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        for (int j = max(it - ahead, 0); j < it; ++j) mbar_arrive(smem_u32(&s_full[j % p.stages]));
       }
     }
+
+    // ------------------------------------------------------------ epilogue (same 8 warps)
+    // warp w reads TMEM lanes 32 (w & 3) .. +31 (its 32 output rows) and every second 16-column chunk
+    bool have_acc = false;
+    if (ok && n_blocks > 0) {
+      have_acc = mbar_wait_warp(smem_u32(&s_acc), 0, lane);
+      if (!have_acc) atomicExch(p.error, kErrAccWait);
+    }
     tc_fence_after();
-    const int r = warp * 32 + lane;
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;
     const int64_t grow = (int64_t)row0 + r;
     int64_t dst_row = -1;
     if (grow < p.n_out) {
@@ -309,10 +378,10 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
     T* y = reinterpret_cast<T*>(p.y);
     const T* res = reinterpret_cast<const T*>(p.residual);
     const bool store = (ok && (have_acc || n_blocks == 0));
-    for (int j = 0; j < n_mma; j += 16) {
+    for (int j = half * 16; j < n_mma; j += 32) {
       uint32_t v[16];
       if (have_acc) {
-        tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)j, v);
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)j, v);
       } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0u;
@@ -325,6 +394,10 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[h * 8 + i]);
+        if (p.scale) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] *= __ldg(&p.scale[n + i]);
+        }
         if (p.bias) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] += __ldg(&p.bias[n + i]);
@@ -352,8 +425,31 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
       }
     }
     tc_fence_before();
+  } else if (warp == kTmaWarp) {
+    // ------------------------------------------------------------ weight loader (B operand, one thread)
+    if (lane == 0 && n_blocks > 0) {
+      const uint32_t bytes = (uint32_t)b_bytes;
+      int it = 0;
+      bool ok = true;
+      for (int k = 0; k < p.kvol && ok; ++k) {
+        if (!((kmask >> k) & 1u)) continue;
+        for (int c = 0; c < chunks; ++c, ++it) {
+          const int stage = it % p.stages;
+          if (it >= p.stages && !mbar_wait(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1)) {
+            atomicExch(p.error, kErrEmptyWait);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&s_full[stage]);
+          mbar_arrive_expect_tx(bar, bytes);
+          tma_load_2d(smem_base + (uint32_t)stage * stage_bytes + kABytes, &w_map, bar, c * kChunkK,
+                      k * p.cout + n0);
+        }
+      }
+    }
+    __syncwarp();
   } else {
-    // ------------------------------------------------------------ MMA issuer (warp 4)
+    // ------------------------------------------------------------ MMA issuer (one thread)
     if (lane == 0 && n_blocks > 0) {
       const uint32_t idesc = make_idesc(p.ab_format, n_mma);
       bool ok = true;
@@ -364,11 +460,9 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
           const int stage = it % p.stages;
           if (!mbar_wait(smem_u32(&s_full[stage]), (it / p.stages) & 1)) {
             atomicExch(p.error, kErrFullWait);
-            s_abort = 1;
             ok = false;
             break;
           }
-          fence_proxy_async();
           tc_fence_after();
           const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
           const uint64_t a_desc = make_smem_desc(a_base);
@@ -388,7 +482,7 @@ __global__ void __launch_bounds__(kThreads, 1) igemm_umma_kernel(const UmmaParam
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
@@ -411,6 +505,22 @@ __global__ void pack_weight_kernel(const T* __restrict__ w, T* __restrict__ wt, 
     int n = n0 + i, c = c0 + threadIdx.x;
     if (c < cin && n < cout) dst[(int64_t)n * cin + c] = tile[threadIdx.x][i];
   }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn tensor_map_encoder() {
+  static EncodeFn fn = []() -> EncodeFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeFn>(ptr);
+  }();
+  return fn;
 }
 
 size_t smem_bytes_for(int n_tile, int stages, int kvol) {
@@ -437,6 +547,8 @@ int pick_n_tile(int cout) {
 }  // namespace
 
 bool igemm_umma_supported(const IgemmArgs& a) {
+  if (!tensor_map_encoder()) return false;
+  if ((a.kvol * kTileM) % 4 || ((uintptr_t)a.map & 15)) return false;
   if (a.dtype != TSB_F16 && a.dtype != TSB_BF16) return false;
   if (a.cin % 8 || a.cout % 8) return false;        // 16-byte granules of rows
   if (a.kvol > kMaxKvolUmma) return false;
@@ -486,7 +598,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     wt = reinterpret_cast<const T*>(a.workspace);
   }
   UmmaParams p;
-  p.x = a.x; p.wt = wt; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias;
+  p.x = a.x; p.wt = wt; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
   p.residual = a.residual; p.error = err;
   p.n_in = (int)a.n_in; p.n_out = (int)a.n_out; p.kvol = a.kvol; p.cin = a.cin; p.cout = a.cout;
   p.n_tile = pick_n_tile(a.cout);
@@ -500,8 +612,23 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr_set[ti] = true;
   }
+  CUtensorMap w_map;
+  {
+    // packed weights as a 2-D tensor [kvol * cout rows, cin columns]; box = 64 columns x n_tile rows
+    auto encode = tensor_map_encoder();
+    if (!encode) return TSB_ERR_UNSUPPORTED;
+    cuuint64_t gdim[2] = {(cuuint64_t)a.cin, (cuuint64_t)a.kvol * (cuuint64_t)a.cout};
+    cuuint64_t gstride[1] = {(cuuint64_t)a.cin * sizeof(T)};
+    cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)p.n_tile};
+    cuuint32_t estride[2] = {1, 1};
+    CUresult r = encode(&w_map, a.dtype == TSB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        2, const_cast<T*>(wt), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
+  }
   dim3 grid((unsigned)cdiv(a.n_out, kTileM), (unsigned)cdiv(a.cout, p.n_tile));
-  igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p);
+  igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p, w_map);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }
