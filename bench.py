@@ -66,7 +66,7 @@ class SegNet(torch.nn.Module):
         return self.head(self.backbone(x)[-1].feats)
 
 
-def make_model(device=None, half=True):
+def make_model(device=None, half=True, engine=True):
     torch.manual_seed(0)
     model = SegNet()
     for m in model.modules():   # random Kaiming-style init, non-trivial BN statistics
@@ -83,6 +83,9 @@ def make_model(device=None, half=True):
         model = model.to(device)
         if half:
             model = model.half()
+        if engine:
+            from torchsparse_b200.nn import InferenceEngine
+            model.backbone = InferenceEngine(model.backbone)
     return model
 
 
@@ -172,7 +175,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
 
     from torchsparse_b200.nn import functional as F
     F.set_conv_mode(args.conv_mode)
-    model = make_model(device)
+    model = make_model(device, engine=not args.unfused)
     scans = [scan_points(1000 * rank + i) for i in range(SCAN_POOL)]
     host = [torch.from_numpy(s).pin_memory() for s in scans]
     resident = [h.to(device) for h in host]
@@ -289,7 +292,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                                "inference, one synthetic 64-ring LiDAR scan (144k points, 0.05 m voxels) per GPU per step",
                    "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": scans_per_step,
                    "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps; {SCAN_POOL} scans rotated",
-                   "conv_mode": args.conv_mode,
+                   "conv_mode": args.conv_mode, "fused_inference_engine": not args.unfused,
                    "parallelism": f"scan-sharded x{world}, NCCL all-gather of logits" if world > 1 else "single GPU"},
         "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
@@ -436,6 +439,7 @@ def main():
     ap.add_argument("--dataflow", default="ImplicitGEMM")
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
+    ap.add_argument("--unfused", action="store_true", help="run the module graph as written (no InferenceEngine)")
     ap.add_argument("--conv-mode", type=int, default=0, choices=[0, 1, 2],
                     help="0 unsorted, 1 row-sorted maps, 2 sorted with 3 mask splits (F.set_conv_mode)")
     args = ap.parse_args()

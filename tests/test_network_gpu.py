@@ -1,0 +1,134 @@
+"""GPU parity of whole networks (the callers of the hot path) against the CPU oracle executor:
+the package's own modules evaluated on CPU through oracle kernel maps + the reference CPU conv.
+
+Tolerances are relative L2 of the final feature matrix / logits: fp32 1e-5 (stated in BASELINE for
+network outputs), fp16 2e-3 per the same statement; the fp16 runs compare against an fp32 CPU run of
+the SAME fp16-rounded weights, so what is measured is the arithmetic of the 42-layer chain."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2
+from oracle import kmap_oracle as ko
+from oracle import net_cpu
+
+pytestmark = pytest.mark.gpu
+
+
+def _scan_crop(n_target=6000, seed=0):
+    from torchsparse_b200.utils.synthetic import lidar_scan
+
+    pts = lidar_scan(seed)
+    pts[:, :3] -= pts[:, :3].min(0, keepdims=True)
+    vox, idx = ko.sparse_quantize(pts[:, :3], 0.05, return_index=True)
+    centre = np.median(vox, axis=0)
+    order = np.argsort(np.abs(vox - centre).max(axis=1), kind="stable")
+    keep = np.sort(order[:n_target])
+    coords = np.concatenate([np.zeros((len(keep), 1), np.int32), vox[keep]], 1).astype(np.int32)
+    return coords, pts[idx[keep]].astype(np.float32)
+
+
+def _randomise_bn(model):
+    g = torch.Generator().manual_seed(1)
+    for m in model.modules():
+        if isinstance(m, torch.nn.BatchNorm1d):
+            m.weight.data.uniform_(0.8, 1.2, generator=g)
+            m.bias.data.uniform_(-0.1, 0.1, generator=g)
+            m.running_mean.uniform_(-0.1, 0.1, generator=g)
+            m.running_var.uniform_(0.8, 1.2, generator=g)
+
+
+def _gpu_forward(model, coords, feats, dtype, engine):
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import InferenceEngine
+
+    m = model.cuda().to(dtype).eval()
+    if engine:
+        m = InferenceEngine(m)
+    x = ts.SparseTensor(torch.from_numpy(feats).cuda().to(dtype), torch.from_numpy(coords).cuda())
+    with torch.no_grad():
+        out = m(x)
+        if engine:   # second call goes through the pre-built strided maps
+            x2 = ts.SparseTensor(torch.from_numpy(feats).cuda().to(dtype), torch.from_numpy(coords).cuda())
+            out2 = m(x2)
+            assert torch.equal(out[-1].feats, out2[-1].feats)
+    return out
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3)])
+@pytest.mark.parametrize("engine", [False, True])
+def test_unet_matches_cpu_oracle(dtype, tol, engine):
+    import copy
+    from torchsparse_b200.backbones import SparseResUNet42
+
+    torch.manual_seed(0)
+    model = SparseResUNet42(in_channels=4, width_multiplier=0.5 if dtype == torch.float32 else 1.0)
+    _randomise_bn(model)
+    model.eval()
+    coords, feats = _scan_crop()
+    ref_model = copy.deepcopy(model).to(dtype).float()      # the rounded weights, evaluated in fp32 on CPU
+    f_r = torch.from_numpy(feats).to(dtype).float().numpy()
+    want = net_cpu.forward_cpu(ref_model, coords, f_r)
+    got = _gpu_forward(copy.deepcopy(model), coords, feats, dtype, engine)
+    assert len(got) == len(want) == 9
+    for g, w in zip(got, want):
+        assert np.array_equal(g.coords.cpu().numpy(), w.coords.numpy())     # coordinates bit-exact at every level
+        assert g.stride == w.stride
+    err = rel_l2(got[-1].feats.float().cpu().numpy(), want[-1].feats.numpy())
+    assert err < tol, err
+    err_mid = rel_l2(got[4].feats.float().cpu().numpy(), want[4].feats.numpy())   # bottleneck (stride 16)
+    assert err_mid < tol, err_mid
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3)])
+def test_resnet21d_matches_cpu_oracle(dtype, tol):
+    import copy
+    from torchsparse_b200.backbones import SparseResNet21D
+    from torchsparse_b200.utils.synthetic import multisweep_scan
+
+    torch.manual_seed(0)
+    model = SparseResNet21D(in_channels=5)
+    _randomise_bn(model)
+    model.eval()
+    pts = multisweep_scan(0, sweeps=3, n_rays=6000)
+    xyz = pts[:, :3] - np.array([-54.0, -54.0, -5.0])
+    q = np.floor(xyz / np.array([0.1, 0.1, 0.2])).astype(np.int64)
+    _, idx = np.unique((q[:, 0] * 2000 + q[:, 1]) * 2000 + q[:, 2], return_index=True)
+    coords = np.concatenate([np.zeros((len(idx), 1), np.int64), q[idx]], 1).astype(np.int32)
+    feats = pts[idx].astype(np.float32)
+    ref_model = copy.deepcopy(model).to(dtype).float()
+    f_r = torch.from_numpy(feats).to(dtype).float().numpy()
+    want = net_cpu.forward_cpu(ref_model, coords, f_r)
+    for engine in (False, True):
+        got = _gpu_forward(copy.deepcopy(model), coords, feats, dtype, engine)
+        assert len(got) == len(want) == 5
+        for g, w in zip(got, want):
+            assert np.array_equal(g.coords.cpu().numpy(), w.coords.numpy())
+            assert rel_l2(g.feats.float().cpu().numpy(), w.feats.numpy()) < tol
+
+
+def test_batched_scans_equal_single_scans():
+    """Scans in one batch do not interact: a 2-scan batch gives the concatenation of the single-scan
+    results (what makes scan-sharding across GPUs exact)."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.backbones import SparseResUNet42
+    from torchsparse_b200.utils.collate import sparse_collate
+
+    torch.manual_seed(0)
+    model = SparseResUNet42(in_channels=4, width_multiplier=0.5).cuda().eval()
+    outs, tensors = [], []
+    for seed in (0, 1):
+        coords, feats = _scan_crop(3000, seed)
+        t = ts.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords[:, 1:]).cuda())
+        tensors.append(t)
+        single = ts.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda())
+        with torch.no_grad():
+            outs.append(model(single)[-1])
+    batch = sparse_collate(tensors)
+    with torch.no_grad():
+        y = model(batch)[-1]
+    n0 = outs[0].feats.shape[0]
+    assert torch.equal(y.coords[:n0, 1:], outs[0].coords[:, 1:]) and torch.equal(y.coords[n0:, 1:], outs[1].coords[:, 1:])
+    assert bool((y.coords[n0:, 0] == 1).all())
+    assert rel_l2(y.feats[:n0].cpu().numpy(), outs[0].feats.cpu().numpy()) < 1e-5
+    assert rel_l2(y.feats[n0:].cpu().numpy(), outs[1].feats.cpu().numpy()) < 1e-5

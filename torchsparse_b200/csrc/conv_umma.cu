@@ -26,6 +26,8 @@
 // code, and the CTA drains its copies, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "conv_dispatch.h"
 
@@ -78,6 +80,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ long long clk() {
+  long long t;
+  asm volatile("mov.u64 %0, %clock64;" : "=l"(t));
+  return t;
+}
+// trace layout: [it][8] = {gather: after empty wait, after issue, after landing; tma: after issue;
+//                          mma: after full wait, after commit; spare, spare}
+#define TSB_TRACE(slot, it_)                                                         \
+  do {                                                                               \
+    if (p.trace && (int)blockIdx.x == p.trace_cta && (it_) < 256) p.trace[(it_) * 8 + (slot)] = clk(); \
+  } while (0)
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -201,6 +214,8 @@ struct UmmaParams {
   const float* bias;    // nullable
   const void* residual; // nullable, [n_out, cout]
   int* error;           // device error word (0 = fine)
+  long long* trace;     // debugging aid: per-block timestamps of CTA `trace_cta` (null = off)
+  int trace_cta;
   int n_in, n_out, kvol, cin, cout;
   int n_tile;           // UMMA N of a full tile (multiple of 16, <= 256)
   int stages;
@@ -255,6 +270,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   __shared__ uint32_t s_mask;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) TSB_TRACE(6, 0);
   const int row0 = blockIdx.x * kTileM;
   const int n0 = blockIdx.y * p.n_tile;
   const int n_valid = min(p.n_tile, p.cout - n0);          // real output channels of this N tile
@@ -302,6 +318,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   const uint32_t kmask = s_mask;
   const int chunks = (p.cin + kChunkK - 1) / kChunkK;
   const int n_blocks = __popc(kmask) * chunks;
+  if (tid == 0) TSB_TRACE(7, 0);
 
   if (warp < kGatherWarps) {
     // ------------------------------------------------------------ gather warps (A operand)
@@ -333,6 +350,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             break;
           }
         }
+        if (tid == 0) TSB_TRACE(0, it);
         const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes + dst_off;
         const bool col_ok = (c * kChunkK + gran * 8) < p.cin;     // cin % 8 == 0: all-in or all-out
 #pragma unroll
@@ -342,11 +360,13 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
                      live ? 16u : 0u);
         }
         cp_async_commit();
+        if (tid == 0) TSB_TRACE(1, it);
         if (it >= ahead) {
           cp_async_wait_pending(ahead);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&s_full[(it - ahead) % p.stages]));
+          if (tid == 0) TSB_TRACE(2, it - ahead);
         }
       }
     }
@@ -367,6 +387,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       if (!have_acc) atomicExch(p.error, kErrAccWait);
     }
     tc_fence_after();
+    if (tid == 0) TSB_TRACE(6, 1);
     const int quarter = warp & 3, half = warp >> 2;
     const int r = quarter * 32 + lane;
     const int64_t grow = (int64_t)row0 + r;
@@ -425,6 +446,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       }
     }
     tc_fence_before();
+    if (tid == 0) TSB_TRACE(7, 1);
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------ weight loader (B operand, one thread)
     if (lane == 0 && n_blocks > 0) {
@@ -444,6 +466,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           mbar_arrive_expect_tx(bar, bytes);
           tma_load_2d(smem_base + (uint32_t)stage * stage_bytes + kABytes, &w_map, bar, c * kChunkK,
                       k * p.cout + n0);
+          TSB_TRACE(3, it);
         }
       }
     }
@@ -464,6 +487,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             break;
           }
           tc_fence_after();
+          TSB_TRACE(4, it);
           const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
           const uint64_t a_desc = make_smem_desc(a_base);
           const uint64_t b_desc = make_smem_desc(a_base + kABytes);
@@ -474,6 +498,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             umma_f16(tmem_base, a_desc + (uint64_t)(2 * s), b_desc + (uint64_t)(2 * s), idesc, (it | s) ? 1u : 0u);
           }
           umma_commit(smem_u32(&s_empty[stage]));
+          TSB_TRACE(5, it);
         }
       }
       umma_commit(smem_u32(&s_acc));   // also on the error path: lets the epilogue's bounded wait end early
@@ -600,6 +625,11 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   UmmaParams p;
   p.x = a.x; p.wt = wt; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
   p.residual = a.residual; p.error = err;
+  p.trace = nullptr; p.trace_cta = 0;
+  if (const char* tr = getenv("TSB_UMMA_TRACE")) {   // debugging aid: address of a 256x8 int64 device buffer
+    p.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
+    if (const char* tc = getenv("TSB_UMMA_TRACE_CTA")) p.trace_cta = atoi(tc);
+  }
   p.n_in = (int)a.n_in; p.n_out = (int)a.n_out; p.kvol = a.kvol; p.cin = a.cin; p.cout = a.cout;
   p.n_tile = pick_n_tile(a.cout);
   p.stages = pick_stages(p.n_tile, a.kvol);

@@ -1,2 +1,3 @@
 from . import functional
 from .modules import *
+from .fused import *

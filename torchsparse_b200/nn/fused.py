@@ -1,0 +1,190 @@
+"""Inference-time fusion: conv + BatchNorm (stored statistics) + ReLU (+ residual add) become one
+kernel launch, and the strided kernel maps of a network are built before its first convolution.
+
+The reference runs BatchNorm, ReLU and the residual add as separate torch kernels over the feature
+matrix after every convolution (torchsparse/nn/modules/norm.py:15-17, activation.py,
+torchsparse/backbones/modules/blocks.py:53-85).  At batch 1 those launches cost more than the
+convolutions, so `fuse_for_inference` rewrites a trained model:
+
+* ``Conv3d -> BatchNorm [-> ReLU]`` inside any ``nn.Sequential``  ->  :class:`FusedConv`
+  (BatchNorm folded into a per-channel fp32 scale and shift applied to the fp32 accumulator);
+* ``SparseResBlock``  ->  :class:`FusedResBlock` (the shortcut is added and the final ReLU applied in
+  the second convolution's epilogue).
+
+The rewritten model computes the same function (one rounding instead of three per layer).
+:class:`InferenceEngine` additionally remembers, from its first forward, which strided convolutions
+the network runs and builds their kernel maps up front on later calls, so that the only
+device-to-host reads of a forward (one per strided map) happen before the convolutions are queued.
+"""
+from typing import Dict, Optional
+
+import torch
+from torch import nn
+
+from ..tensor import SparseTensor
+from . import functional as F
+from .functional.conv import conv as _conv_impl
+from .modules.activation import ReLU
+from .modules.conv import Conv3d
+from .modules.norm import BatchNorm
+
+__all__ = ["FusedConv", "FusedResBlock", "fuse_for_inference", "InferenceEngine"]
+
+
+def _fold_bn(conv: Conv3d, bn: Optional[nn.BatchNorm1d]):
+    cout = conv.out_channels
+    dev = conv.kernel.device
+    if bn is None:
+        scale = torch.ones(cout, dtype=torch.float32, device=dev)
+        shift = torch.zeros(cout, dtype=torch.float32, device=dev)
+    else:
+        var = bn.running_var.float()
+        mean = bn.running_mean.float()
+        gamma = bn.weight.float() if bn.weight is not None else torch.ones_like(var)
+        beta = bn.bias.float() if bn.bias is not None else torch.zeros_like(var)
+        scale = gamma / torch.sqrt(var + bn.eps)
+        shift = beta - mean * scale
+    if conv.bias is not None:
+        shift = shift + conv.bias.float() * scale
+    return scale.detach().contiguous(), shift.detach().contiguous()
+
+
+class FusedConv(nn.Module):
+    """conv (+ folded BatchNorm) (+ ReLU); ``forward(x, residual=None)`` adds a residual feature
+    matrix before the ReLU."""
+
+    def __init__(self, conv: Conv3d, bn: Optional[nn.BatchNorm1d] = None, relu: bool = False) -> None:
+        super().__init__()
+        assert not conv.generative
+        self.kernel_size, self.stride, self.padding = conv.kernel_size, conv.stride, conv.padding
+        self.dilation, self.transposed, self._config = conv.dilation, conv.transposed, conv._config
+        self.in_channels, self.out_channels = conv.in_channels, conv.out_channels
+        self.relu = relu
+        self.kernel = nn.Parameter(conv.kernel.detach(), requires_grad=False)
+        scale, shift = _fold_bn(conv, bn)
+        self.pointwise = self.kernel.dim() == 2
+        if self.pointwise:
+            # 1x1x1: a dense matmul; the scale goes into the weights (fp32 product, then one rounding)
+            self.kernel = nn.Parameter((self.kernel.float() * scale[None, :]).to(self.kernel.dtype),
+                                       requires_grad=False)
+            self.register_buffer("shift_lp", shift.to(self.kernel.dtype))
+        self.register_buffer("scale", scale)
+        self.register_buffer("shift", shift)
+
+    def _apply(self, fn, recurse=True):
+        # keep the folded scale / shift in fp32 under .half() / .to(dtype)
+        scale, shift = self.scale, self.shift
+        super()._apply(fn, recurse)
+        self.scale = scale.to(self.kernel.device).float()
+        self.shift = shift.to(self.kernel.device).float()
+        return self
+
+    def forward(self, x: SparseTensor, residual: Optional[torch.Tensor] = None) -> SparseTensor:
+        if self.pointwise:
+            out = torch.addmm(self.shift_lp, x.feats, self.kernel)
+            if residual is not None:
+                out = out + residual
+            if self.relu:
+                out = torch.relu_(out)
+            y = SparseTensor(out, x.coords, x.stride, x.spatial_range)
+            y._caches = x._caches
+            return y
+        return F.conv3d(x, self.kernel, self.kernel_size, None, self.stride, self.padding, self.dilation,
+                        self._config, self.transposed, False, False,
+                        epilogue={"scale": self.scale, "bias": self.shift, "residual": residual, "relu": self.relu})
+
+    def extra_repr(self) -> str:
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}, "
+                f"relu={self.relu}, transposed={self.transposed}")
+
+
+class FusedResBlock(nn.Module):
+    """relu(conv2(relu(conv1(x))) + shortcut(x)) with both BatchNorms folded and the add + ReLU in the
+    second convolution's epilogue."""
+
+    def __init__(self, block) -> None:
+        super().__init__()
+        main = list(block.main)
+        self.conv1 = FusedConv(main[0], main[1], relu=True)
+        self.conv2 = FusedConv(main[3], main[4], relu=True)
+        if isinstance(block.shortcut, nn.Identity):
+            self.shortcut = None
+        else:
+            sc = list(block.shortcut)
+            self.shortcut = FusedConv(sc[0], sc[1], relu=False)
+
+    def forward(self, x: SparseTensor) -> SparseTensor:
+        res = x.feats if self.shortcut is None else self.shortcut(x).feats
+        return self.conv2(self.conv1(x), residual=res)
+
+
+def _fuse_sequential(seq: nn.Sequential) -> nn.Sequential:
+    mods = list(seq)
+    out = []
+    i = 0
+    while i < len(mods):
+        m = mods[i]
+        if isinstance(m, Conv3d) and not m.generative:
+            bn = mods[i + 1] if i + 1 < len(mods) and isinstance(mods[i + 1], nn.BatchNorm1d) else None
+            j = i + (2 if bn is not None else 1)
+            relu = j < len(mods) and isinstance(mods[j], (ReLU, nn.ReLU))
+            out.append(FusedConv(m, bn, relu))
+            i = j + (1 if relu else 0)
+        else:
+            out.append(fuse_for_inference(m))
+            i += 1
+    return nn.Sequential(*out)
+
+
+def fuse_for_inference(model: nn.Module) -> nn.Module:
+    """Returns a rewritten copy-free view of `model` (parameters are shared, BatchNorm statistics
+    are folded at call time) for eval-mode inference.  Modules it does not recognise are kept."""
+    from ..backbones.blocks import SparseResBlock
+
+    if isinstance(model, SparseResBlock):
+        return FusedResBlock(model)
+    if isinstance(model, Conv3d) and not model.generative:
+        return FusedConv(model, None, False)
+    if isinstance(model, nn.Sequential):
+        return _fuse_sequential(model)
+    for name, child in list(model.named_children()):
+        fused = fuse_for_inference(child)
+        if fused is not child:
+            model._modules[name] = fused
+    return model
+
+
+class InferenceEngine(nn.Module):
+    """Eval-mode wrapper: fused modules, no autograd, strided kernel maps built ahead of the convs."""
+
+    def __init__(self, model: nn.Module) -> None:
+        super().__init__()
+        if model.training:
+            raise ValueError("InferenceEngine needs a model in eval() mode (BatchNorm statistics are folded)")
+        self.model = fuse_for_inference(model)
+        self._plan = None   # strided conv keys in execution order, learnt on the first call
+
+    def _prebuild(self, x: SparseTensor) -> None:
+        caches = x._caches
+        caches.cmaps.setdefault(x.stride, (x.coords, x.spatial_range))
+        for tensor_stride, ks, st, pad, dil, config in self._plan:
+            cm = caches.cmaps.get(tensor_stride)
+            if cm is None:
+                return   # the plan no longer matches this input; fall back to building on demand
+            coords, srange = cm
+            _conv_impl.acquire_kernel_map(caches, coords, coords.shape[0], tensor_stride, srange, ks, st, pad, dil,
+                                          config, False)
+
+    @torch.no_grad()
+    def forward(self, x: SparseTensor):
+        if self._plan is None:
+            _conv_impl.strided_build_log = []
+            try:
+                out = self.model(x)
+            finally:
+                log, _conv_impl.strided_build_log = _conv_impl.strided_build_log, None
+            cfg = _conv_impl.resolve_config(None)
+            self._plan = [entry + (cfg,) for entry in log]
+            return out
+        self._prebuild(x)
+        return self.model(x)
