@@ -119,6 +119,8 @@ def coords_bounds(coords, kernel_size, stride, padding, subm, spatial_range=None
     pd = np.array(_as3(padding), dtype=np.int64)
     if spatial_range is not None:
         cmax = np.array([v - 1 for v in spatial_range], dtype=np.int64)
+    elif coords.shape[0] == 0:
+        cmax = np.zeros(4, dtype=np.int64)
     else:
         cmax = coords.astype(np.int64).max(axis=0)
         if not subm:

@@ -167,3 +167,21 @@ def test_duplicate_free_determinism():
     a = _build(coords, 3, 2, 0)
     b = _build(coords, 3, 2, 0)
     assert torch.equal(a["out_in_map"], b["out_in_map"]) and torch.equal(a["coords"], b["coords"])
+
+
+def test_empty_and_vanishing_inputs():
+    """No voxels in, or a strided conv that keeps none: empty tensors, no error."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    empty = torch.zeros((0, 4), dtype=torch.int32, device="cuda")
+    g = F.build_kernel_map(empty, 0, 3, 1, 1, None, None, None, "hashmap_on_the_fly")
+    assert g["out_in_map"].shape == (0, 27) and g["sizes"] == (0, 0)
+    # one voxel at even max coordinate: k2 s2 drops it (bound (max-1)//2), as the oracle says
+    one = torch.tensor([[0, 4, 4, 4]], dtype=torch.int32, device="cuda")
+    x = ts.SparseTensor(torch.ones(1, 8, device="cuda"), one)
+    w = torch.ones(8, 8, 16, device="cuda")
+    y = F.conv3d(x, w, 2, None, 2, 0)
+    assert y.coords.shape == (0, 4) and y.feats.shape == (0, 16)
+    z = F.conv3d(y, torch.ones(27, 16, 16, device="cuda"), 3, None, 1, 1)
+    assert z.feats.shape == (0, 16)

@@ -39,15 +39,18 @@ constexpr int kChunkK = 64;                 // 16-bit elements per stage row = 1
 constexpr int kRowBytes = 128;
 constexpr int kABytes = kTileM * kRowBytes; // 16 KiB
 constexpr int kGatherWarps = 8;
-constexpr int kTmaWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kEpilogueWarps = 4;      // warps 8..11: warp % 4 = TMEM lane quarter
+constexpr int kTmaWarp = 12;
+constexpr int kMmaWarp = 13;
+constexpr int kSchedWarp = 14;
+constexpr int kThreads = 480;
+constexpr int kMaxRing = 4;            // tile ring: map slices + offset masks staged ahead of the gather warps
 constexpr int kMaxStages = 8;
 constexpr int kMaxKvolUmma = 32;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 
-enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
+enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3, kErrSchedWait = 4 };
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -218,6 +221,8 @@ struct UmmaParams {
   int trace_cta;
   int n_in, n_out, kvol, cin, cout;
   int n_tile;           // UMMA N of a full tile (multiple of 16, <= 256)
+  int acc_cols;         // TMEM columns of one accumulator buffer (power of two >= n_tile, >= 32)
+  int ring;             // tile ring depth (2..kMaxRing)
   int stages;
   int relu;
   int ab_format;        // 0 fp16, 1 bf16
@@ -259,249 +264,341 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// Persistent kernel: one CTA per SM walks the (row tile, N tile) work list with a fixed stride.
+// Three rings decouple the roles so that the copies of the next tile are in flight while the
+// current tile is multiplied and the previous one is written out:
+//   stage ring   (p.stages)  A+B operands of one K block         full[] / empty[]
+//   tile ring    (2)         map slice + offset mask of a tile   sched_full[] / sched_empty[]
+//   accumulator  (2)         TMEM column ranges                   acc_full[] / acc_empty[]
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t s_full[kMaxStages];
   __shared__ uint64_t s_empty[kMaxStages];
-  __shared__ uint64_t s_acc;
+  __shared__ uint64_t s_sched_full[kMaxRing];
+  __shared__ uint64_t s_sched_empty[kMaxRing];
+  __shared__ uint64_t s_acc_full[2];
+  __shared__ uint64_t s_acc_empty[2];
+  __shared__ uint32_t s_kmask[kMaxRing];
   __shared__ uint32_t s_tmem;
-  __shared__ uint32_t s_mask;
+  __shared__ volatile int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) TSB_TRACE(6, 0);
-  const int row0 = blockIdx.x * kTileM;
-  const int n0 = blockIdx.y * p.n_tile;
-  const int n_valid = min(p.n_tile, p.cout - n0);          // real output channels of this N tile
-  const int n_mma = (n_valid + 15) & ~15;                   // UMMA N
+  const int tiles_n = (p.cout + p.n_tile - 1) / p.n_tile;
+  const int tiles_m = (p.n_out + kTileM - 1) / kTileM;
+  const int n_work = tiles_m * tiles_n;
   const int b_bytes = p.n_tile * kRowBytes;
   const int stage_bytes = kABytes + b_bytes;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t map_smem = smem_base + (uint32_t)p.stages * stage_bytes;
-  int* s_map = reinterpret_cast<int*>(smem_raw + (map_smem - smem_u32(smem_raw)));
-  uint32_t tmem_cols = 32;
-  while ((int)tmem_cols < n_mma) tmem_cols <<= 1;
+  const int map_ints = kTileM * p.kvol;
+  int* s_map0 = reinterpret_cast<int*>(smem_raw + (map_smem - smem_u32(smem_raw)));
+  const uint32_t acc_cols = p.acc_cols;            // TMEM columns of one accumulator (power of two)
+  const int chunks = (p.cin + kChunkK - 1) / kChunkK;
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&s_full[s]), kGatherWarps + 1);   // 8 gather warps + the TMA thread (with byte count)
+      mbar_init(smem_u32(&s_full[s]), kGatherWarps * 32 + 1);   // every gather thread + the TMA thread (byte count)
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
-    mbar_init(smem_u32(&s_acc), 1);
-    s_mask = 0;
+    for (int b = 0; b < p.ring; ++b) {
+      mbar_init(smem_u32(&s_sched_full[b]), 1);
+      // readers of a ring slot: gather warps, TMA thread, MMA thread, epilogue warps
+      mbar_init(smem_u32(&s_sched_empty[b]), kGatherWarps + 2 + kEpilogueWarps);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&s_acc_full[b]), 1);
+      mbar_init(smem_u32(&s_acc_empty[b]), kEpilogueWarps);
+    }
+    s_abort = 0;
     fence_barrier_init();
   }
-  if (warp == kMmaWarp) tmem_alloc(smem_u32(&s_tmem), tmem_cols);
-  // stage the tile's slice of the map (contiguous: 128 rows x kvol ints, 16-byte loads)
-  {
-    const int4* src = reinterpret_cast<const int4*>(p.map + (int64_t)row0 * p.kvol);
-    int4* dst = reinterpret_cast<int4*>(s_map);
-    for (int i = tid; i < kTileM * p.kvol / 4; i += kThreads) dst[i] = __ldg(&src[i]);
-  }
+  if (warp == kMmaWarp) tmem_alloc(smem_u32(&s_tmem), 2 * acc_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
-  // offset mask: bit k set when some row of the tile has a neighbour at offset k
-  if (tid < kTileM) {
-    uint32_t mine = 0;
-    for (int k = 0; k < p.kvol; ++k) {
-      int v = s_map[tid * p.kvol + k];
-      if (v >= p.n_in) { v = -1; s_map[tid * p.kvol + k] = -1; }
-      mine |= (uint32_t)(v >= 0) << k;
-    }
-    for (int o = 16; o; o >>= 1) mine |= __shfl_xor_sync(0xffffffffu, mine, o);
-    if (lane == 0 && mine) atomicOr(&s_mask, mine);
-  }
-  __syncthreads();
-  const uint32_t kmask = s_mask;
-  const int chunks = (p.cin + kChunkK - 1) / kChunkK;
-  const int n_blocks = __popc(kmask) * chunks;
-  if (tid == 0) TSB_TRACE(7, 0);
 
   if (warp < kGatherWarps) {
-    // ------------------------------------------------------------ gather warps (A operand)
-    // thread -> granule (tid & 7) of rows (tid >> 3) + 32 j, j = 0..3: a warp instruction covers four
-    // whole 128-byte row slices.  Each warp keeps `ahead` K blocks in flight (one commit group per
-    // block); when a block has landed the warp fences its writes for the tensor-core proxy and one
-    // lane arrives on the stage's full barrier.
+    // ------------------------------------------------------------ gather warps (map staging + A operand)
     const T* x = reinterpret_cast<const T*>(p.x);
     const int gran = tid & 7;
     const int rbase = tid >> 3;                                   // 0..31
     const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
-    const int ahead = p.stages - 1;
-    int it = 0;
+    int it = 0;          // K blocks issued so far (all tiles)
     bool ok = true;
-    for (int k = 0; k < p.kvol && ok; ++k) {
-      if (!((kmask >> k) & 1u)) continue;
-      const T* rowp[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int src = s_map[(rbase + 32 * j) * p.kvol + k];
-        rowp[j] = (src >= 0) ? x + (int64_t)src * p.cin + gran * 8 : nullptr;
+    int i = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
+      const int buf = i % p.ring;
+      const uint32_t use_parity = (uint32_t)(i / p.ring) & 1u;
+      int* s_map = s_map0 + buf * map_ints;
+      if (ok && !mbar_wait_warp(smem_u32(&s_sched_full[buf]), use_parity, lane)) {
+        atomicExch(p.error, kErrSchedWait);
+        s_abort = 1;
+        ok = false;
       }
-      for (int c = 0; c < chunks && ok; ++c, ++it) {
-        const int stage = it % p.stages;
-        if (it >= p.stages) {
-          if (!mbar_wait_warp(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1, lane)) {
-            atomicExch(p.error, kErrEmptyWait);
-            ok = false;
-            break;
-          }
-        }
-        if (tid == 0) TSB_TRACE(0, it);
-        const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes + dst_off;
-        const bool col_ok = (c * kChunkK + gran * 8) < p.cin;     // cin % 8 == 0: all-in or all-out
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const bool live = col_ok && rowp[j] != nullptr;
-          cp_async16(a_dst + (uint32_t)j * (32 * kRowBytes), live ? (const void*)(rowp[j] + c * kChunkK) : (const void*)x,
-                     live ? 16u : 0u);
-        }
-        cp_async_commit();
-        if (tid == 0) TSB_TRACE(1, it);
-        if (it >= ahead) {
-          cp_async_wait_pending(ahead);
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&s_full[(it - ahead) % p.stages]));
-          if (tid == 0) TSB_TRACE(2, it - ahead);
-        }
-      }
-    }
-    cp_async_wait_all();
-    if (ok) {   // publish the last `ahead` blocks
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) {
-        for (int j = max(it - ahead, 0); j < it; ++j) mbar_arrive(smem_u32(&s_full[j % p.stages]));
-      }
-    }
-
-    // ------------------------------------------------------------ epilogue (same 8 warps)
-    // warp w reads TMEM lanes 32 (w & 3) .. +31 (its 32 output rows) and every second 16-column chunk
-    bool have_acc = false;
-    if (ok && n_blocks > 0) {
-      have_acc = mbar_wait_warp(smem_u32(&s_acc), 0, lane);
-      if (!have_acc) atomicExch(p.error, kErrAccWait);
-    }
-    tc_fence_after();
-    if (tid == 0) TSB_TRACE(6, 1);
-    const int quarter = warp & 3, half = warp >> 2;
-    const int r = quarter * 32 + lane;
-    const int64_t grow = (int64_t)row0 + r;
-    int64_t dst_row = -1;
-    if (grow < p.n_out) {
-      dst_row = p.reorder ? (int64_t)__ldg(&p.reorder[grow]) : grow;
-      if (dst_row >= p.n_out) dst_row = -1;
-    }
-    T* y = reinterpret_cast<T*>(p.y);
-    const T* res = reinterpret_cast<const T*>(p.residual);
-    const bool store = (ok && (have_acc || n_blocks == 0));
-    for (int j = half * 16; j < n_mma; j += 32) {
-      uint32_t v[16];
-      if (have_acc) {
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)j, v);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = 0u;
-      }
-      if (!store || dst_row < 0) continue;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int n = n0 + j + h * 8;
-        if (n >= p.cout) continue;        // cout % 8 == 0: 8-channel groups are all-in or all-out
-        float f[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[h * 8 + i]);
-        if (p.scale) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] *= __ldg(&p.scale[n + i]);
-        }
-        if (p.bias) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] += __ldg(&p.bias[n + i]);
-        }
-        if (res) {
-          uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n));
-          const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float2 t = unpack2<T>(rw[i]);
-            f[2 * i] += t.x;
-            f[2 * i + 1] += t.y;
-          }
-        }
-        if (p.relu) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = fmaxf(f[i], 0.f);
-        }
-        uint4 o;
-        o.x = pack2<T>(f[0], f[1]);
-        o.y = pack2<T>(f[2], f[3]);
-        o.z = pack2<T>(f[4], f[5]);
-        o.w = pack2<T>(f[6], f[7]);
-        *reinterpret_cast<uint4*>(y + dst_row * p.cout + n) = o;
-      }
-    }
-    tc_fence_before();
-    if (tid == 0) TSB_TRACE(7, 1);
-  } else if (warp == kTmaWarp) {
-    // ------------------------------------------------------------ weight loader (B operand, one thread)
-    if (lane == 0 && n_blocks > 0) {
-      const uint32_t bytes = (uint32_t)b_bytes;
-      int it = 0;
-      bool ok = true;
+      const uint32_t kmask = (ok && !s_abort) ? s_kmask[buf] : 0u;
+      if (!ok || s_abort) ok = false;
       for (int k = 0; k < p.kvol && ok; ++k) {
         if (!((kmask >> k) & 1u)) continue;
+        const T* rowp[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int src = s_map[(rbase + 32 * j) * p.kvol + k];
+          rowp[j] = (src >= 0) ? x + (int64_t)src * p.cin + gran * 8 : nullptr;
+        }
         for (int c = 0; c < chunks; ++c, ++it) {
           const int stage = it % p.stages;
-          if (it >= p.stages && !mbar_wait(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1)) {
-            atomicExch(p.error, kErrEmptyWait);
-            ok = false;
-            break;
+          if (it >= p.stages) {
+            if (!mbar_wait_warp(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1, lane)) {
+              atomicExch(p.error, kErrEmptyWait);
+              s_abort = 1;
+              ok = false;
+              break;
+            }
           }
-          const uint32_t bar = smem_u32(&s_full[stage]);
-          mbar_arrive_expect_tx(bar, bytes);
-          tma_load_2d(smem_base + (uint32_t)stage * stage_bytes + kABytes, &w_map, bar, c * kChunkK,
-                      k * p.cout + n0);
-          TSB_TRACE(3, it);
+          const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes + dst_off;
+          const bool col_ok = (c * kChunkK + gran * 8) < p.cin;     // cin % 8 == 0: all-in or all-out
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const bool live = col_ok && rowp[j] != nullptr;
+            cp_async16(a_dst + (uint32_t)j * (32 * kRowBytes),
+                       live ? (const void*)(rowp[j] + c * kChunkK) : (const void*)x, live ? 16u : 0u);
+          }
+          // arrives on the stage's full barrier when this thread's copies have landed; the warp does
+          // not wait and goes on to the next K block (back-pressure comes from empty[] only)
+          cp_async_arrive_noinc(smem_u32(&s_full[stage]));
+        }
+      }
+      __syncwarp();   // every lane has read its rows of the slice
+      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
+    }
+    cp_async_wait_all();   // nothing of this CTA may still be writing shared memory at exit
+  } else if (warp < kGatherWarps + kEpilogueWarps) {
+    // ------------------------------------------------------------ epilogue warps
+    // warp q reads TMEM lanes 32 q .. 32 q + 31 = its 32 output rows, all columns of the tile
+    const int quarter = warp & 3;
+    T* y = reinterpret_cast<T*>(p.y);
+    const T* res = reinterpret_cast<const T*>(p.residual);
+    int i = 0;
+    int acc_count = 0;   // tiles that used an accumulator so far (tiles with an empty mask use none)
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
+      const int buf = i % p.ring;
+      const int row0 = (w / tiles_n) * kTileM;
+      const int n0 = (w % tiles_n) * p.n_tile;
+      const int n_valid = min(p.n_tile, p.cout - n0);
+      const int n_mma = (n_valid + 15) & ~15;
+      if (ok && !mbar_wait_warp(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u, lane)) {
+        atomicExch(p.error, kErrSchedWait);
+        s_abort = 1;
+        ok = false;
+      }
+      const uint32_t kmask = s_kmask[buf];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
+      if (!ok || s_abort) { ok = false; continue; }
+      const bool have_acc = kmask != 0;
+      const int ab = acc_count & 1;
+      if (have_acc && !mbar_wait_warp(smem_u32(&s_acc_full[ab]), (acc_count >> 1) & 1, lane)) {
+        atomicExch(p.error, kErrAccWait);
+        s_abort = 1;
+        ok = false;
+        continue;
+      }
+      tc_fence_after();
+      const int r = quarter * 32 + lane;
+      const int64_t grow = (int64_t)row0 + r;
+      int64_t dst_row = -1;
+      if (grow < p.n_out) {
+        dst_row = p.reorder ? (int64_t)__ldg(&p.reorder[grow]) : grow;
+        if (dst_row >= p.n_out) dst_row = -1;
+      }
+      const uint32_t acc_addr = tmem_base + (uint32_t)ab * acc_cols + ((uint32_t)(quarter * 32) << 16);
+      for (int j = 0; j < n_mma; j += 16) {
+        uint32_t v[16];
+        if (have_acc) {
+          tmem_ld16(acc_addr + (uint32_t)j, v);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = 0u;
+        }
+        if (dst_row < 0) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int n = n0 + j + h * 8;
+          if (n >= p.cout) continue;        // cout % 8 == 0: 8-channel groups are all-in or all-out
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[h * 8 + e]);
+          if (p.scale) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] *= __ldg(&p.scale[n + e]);
+          }
+          if (p.bias) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] += __ldg(&p.bias[n + e]);
+          }
+          if (res) {
+            uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n));
+            const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 t = unpack2<T>(rw[e]);
+              f[2 * e] += t.x;
+              f[2 * e + 1] += t.y;
+            }
+          }
+          if (p.relu) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
+          }
+          uint4 o;
+          o.x = pack2<T>(f[0], f[1]);
+          o.y = pack2<T>(f[2], f[3]);
+          o.z = pack2<T>(f[4], f[5]);
+          o.w = pack2<T>(f[6], f[7]);
+          *reinterpret_cast<uint4*>(y + dst_row * p.cout + n) = o;
+        }
+      }
+      // this warp is done with the accumulator buffer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0 && have_acc) mbar_arrive(smem_u32(&s_acc_empty[ab]));
+      if (have_acc) ++acc_count;
+    }
+  } else if (warp == kSchedWarp) {
+    // ------------------------------------------------------------ scheduler warp
+    // stages the map slice of each tile (128 rows x kvol ints, contiguous, 16-byte loads) into the
+    // tile ring and publishes its offset mask, up to `ring` tiles ahead of the other roles
+    const int n4 = map_ints / 4;
+    int i = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
+      const int buf = i % p.ring;
+      const int row0 = (w / tiles_n) * kTileM;
+      if (i >= p.ring && !mbar_wait_warp(smem_u32(&s_sched_empty[buf]), ((uint32_t)(i / p.ring) + 1u) & 1u, lane)) {
+        atomicExch(p.error, kErrSchedWait);
+        s_abort = 1;
+        break;
+      }
+      if (s_abort) break;
+      const int4* src = reinterpret_cast<const int4*>(p.map + (int64_t)row0 * p.kvol);
+      int4* dst = reinterpret_cast<int4*>(s_map0 + buf * map_ints);
+      uint32_t mine = 0;
+      int kk = (lane * 4) % p.kvol;                 // kernel offset of the first int of this lane's int4
+      const int kstep = 128 % p.kvol;               // advance of that offset per loop trip (32 lanes x 4 ints)
+      for (int e = lane; e < n4; e += 32) {
+        int4 v = __ldg(&src[e]);
+        int* c = reinterpret_cast<int*>(&v);
+        int k = kk;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (c[j] >= p.n_in) c[j] = -1;
+          if (c[j] >= 0) mine |= 1u << k;
+          k = (k + 1 == p.kvol) ? 0 : k + 1;
+        }
+        dst[e] = v;
+        kk += kstep;
+        if (kk >= p.kvol) kk -= p.kvol;
+      }
+      for (int o = 16; o; o >>= 1) mine |= __shfl_xor_sync(0xffffffffu, mine, o);
+      __syncwarp();
+      if (lane == 0) {
+        s_kmask[buf] = mine;
+        mbar_arrive(smem_u32(&s_sched_full[buf]));
+      }
+    }
+  } else if (warp == kTmaWarp) {
+    // ------------------------------------------------------------ weight loader (B operand, one thread)
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)b_bytes;
+      int it = 0, i = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
+        const int buf = i % p.ring;
+        const int n0 = (w % tiles_n) * p.n_tile;
+        if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
+          atomicExch(p.error, kErrSchedWait);
+          s_abort = 1;
+          break;
+        }
+        const uint32_t kmask = s_kmask[buf];
+        mbar_arrive(smem_u32(&s_sched_empty[buf]));
+        for (int k = 0; k < p.kvol && ok; ++k) {
+          if (!((kmask >> k) & 1u)) continue;
+          for (int c = 0; c < chunks; ++c, ++it) {
+            const int stage = it % p.stages;
+            if (s_abort || (it >= p.stages && !mbar_wait(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1))) {
+              if (!s_abort) atomicExch(p.error, kErrEmptyWait);
+              s_abort = 1;
+              ok = false;
+              break;
+            }
+            const uint32_t bar = smem_u32(&s_full[stage]);
+            mbar_arrive_expect_tx(bar, bytes);
+            tma_load_2d(smem_base + (uint32_t)stage * stage_bytes + kABytes, &w_map, bar, c * kChunkK,
+                        k * p.cout + n0);
+          }
         }
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------ MMA issuer (one thread)
-    if (lane == 0 && n_blocks > 0) {
-      const uint32_t idesc = make_idesc(p.ab_format, n_mma);
+    if (lane == 0) {
+      int it = 0, i = 0, acc_count = 0;
       bool ok = true;
-      int it = 0;
-      for (int k = 0; k < p.kvol && ok; ++k) {
-        if (!((kmask >> k) & 1u)) continue;
-        for (int c = 0; c < chunks; ++c, ++it) {
-          const int stage = it % p.stages;
-          if (!mbar_wait(smem_u32(&s_full[stage]), (it / p.stages) & 1)) {
-            atomicExch(p.error, kErrFullWait);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          TSB_TRACE(4, it);
-          const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
-          const uint64_t a_desc = make_smem_desc(a_base);
-          const uint64_t b_desc = make_smem_desc(a_base + kABytes);
-          const int kc = min(kChunkK, p.cin - c * kChunkK);
-          const int steps = (kc + 15) >> 4;
-          for (int s = 0; s < steps; ++s) {
-            // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
-            umma_f16(tmem_base, a_desc + (uint64_t)(2 * s), b_desc + (uint64_t)(2 * s), idesc, (it | s) ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&s_empty[stage]));
-          TSB_TRACE(5, it);
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
+        const int buf = i % p.ring;
+        const int n0 = (w % tiles_n) * p.n_tile;
+        const int n_mma = (min(p.n_tile, p.cout - n0) + 15) & ~15;
+        const uint32_t idesc = make_idesc(p.ab_format, n_mma);
+        if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
+          atomicExch(p.error, kErrSchedWait);
+          s_abort = 1;
+          break;
         }
+        const uint32_t kmask = s_kmask[buf];
+        mbar_arrive(smem_u32(&s_sched_empty[buf]));
+        if (!kmask) continue;                                      // nothing to multiply: the epilogue writes zeros
+        // the epilogue must have drained this accumulator buffer (its previous use)
+        const int ab = acc_count & 1;
+        if (acc_count >= 2 && !mbar_wait(smem_u32(&s_acc_empty[ab]), ((acc_count >> 1) + 1) & 1)) {
+          atomicExch(p.error, kErrAccWait);
+          s_abort = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + (uint32_t)ab * acc_cols;
+        int first = 1;
+        for (int k = 0; k < p.kvol && ok; ++k) {
+          if (!((kmask >> k) & 1u)) continue;
+          for (int c = 0; c < chunks; ++c, ++it) {
+            const int stage = it % p.stages;
+            if (s_abort || !mbar_wait(smem_u32(&s_full[stage]), (it / p.stages) & 1)) {
+              if (!s_abort) atomicExch(p.error, kErrFullWait);
+              s_abort = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
+            const uint64_t a_desc = make_smem_desc(a_base);
+            const uint64_t b_desc = make_smem_desc(a_base + kABytes);
+            const int kc = min(kChunkK, p.cin - c * kChunkK);
+            const int steps = (kc + 15) >> 4;
+            for (int s = 0; s < steps; ++s) {
+              // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
+              umma_f16(acc, a_desc + (uint64_t)(2 * s), b_desc + (uint64_t)(2 * s), idesc, first ? 0u : 1u);
+              first = 0;
+            }
+            umma_commit(smem_u32(&s_empty[stage]));
+          }
+        }
+        umma_commit(smem_u32(&s_acc_full[ab]));   // also on the error path: ends the epilogue's bounded wait early
+        ++acc_count;
       }
-      umma_commit(smem_u32(&s_acc));   // also on the error path: lets the epilogue's bounded wait end early
     }
     __syncwarp();
     tc_fence_before();
@@ -509,7 +606,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
+    tmem_dealloc(tmem_base, 2 * acc_cols);
   }
 }
 
@@ -548,20 +645,29 @@ EncodeFn tensor_map_encoder() {
   return fn;
 }
 
-size_t smem_bytes_for(int n_tile, int stages, int kvol) {
-  return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)kTileM * kvol * sizeof(int);
+size_t smem_bytes_for(int n_tile, int stages, int kvol, int ring) {
+  return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)ring * kTileM * kvol * sizeof(int);
 }
 
-// stages so that two CTAs fit one SM when possible (about 113 KiB each), else one CTA
-int pick_stages(int n_tile, int kvol) {
-  const size_t two_cta = 112 * 1024, one_cta = 226 * 1024;
-  int best = 0;
-  for (int s = 2; s <= 6; ++s)
-    if (smem_bytes_for(n_tile, s, kvol) <= two_cta) best = s;
-  if (best >= 2) return best;
-  for (int s = 2; s <= 4; ++s)
-    if (smem_bytes_for(n_tile, s, kvol) <= one_cta) best = s;
-  return best;
+// as many stages as fit next to the tile ring (one persistent CTA per SM); a ring of 3 unless
+// giving up one slot buys a stage for a shallow pipeline
+void pick_config(int n_tile, int kvol, int* stages, int* ring) {
+  const size_t budget = 226 * 1024;
+  int best[2] = {0, 0};
+  for (int r = 2; r <= 3; ++r)
+    for (int s = 2; s <= kMaxStages; ++s)
+      if (smem_bytes_for(n_tile, s, kvol, r) <= budget) best[r - 2] = s;
+  if (best[0] > best[1] && best[1] < 4) { *stages = best[0]; *ring = 2; }
+  else { *stages = best[1]; *ring = 3; }
+}
+
+int num_sms() {
+  static int n = []() {
+    int dev = 0, v = kSmCount;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : kSmCount;
+  }();
+  return n;
 }
 
 int pick_n_tile(int cout) {
@@ -579,7 +685,9 @@ bool igemm_umma_supported(const IgemmArgs& a) {
   if (a.kvol > kMaxKvolUmma) return false;
   if (((uintptr_t)a.x | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual | (uintptr_t)a.packed_w) & 15)
     return false;
-  return pick_stages(pick_n_tile(a.cout), a.kvol) >= 2;
+  int st = 0, rg = 0;
+  pick_config(pick_n_tile(a.cout), a.kvol, &st, &rg);
+  return st >= 2;
 }
 
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype) {
@@ -632,10 +740,10 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   }
   p.n_in = (int)a.n_in; p.n_out = (int)a.n_out; p.kvol = a.kvol; p.cin = a.cin; p.cout = a.cout;
   p.n_tile = pick_n_tile(a.cout);
-  p.stages = pick_stages(p.n_tile, a.kvol);
+  pick_config(p.n_tile, a.kvol, &p.stages, &p.ring);
   p.relu = a.relu;
   p.ab_format = (a.dtype == TSB_BF16) ? 1 : 0;
-  const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol);
+  const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol, p.ring);
   static bool attr_set[2] = {false, false};
   const int ti = (a.dtype == TSB_BF16) ? 1 : 0;
   if (!attr_set[ti]) {
@@ -657,7 +765,10 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
   }
-  dim3 grid((unsigned)cdiv(a.n_out, kTileM), (unsigned)cdiv(a.cout, p.n_tile));
+  p.acc_cols = 32;
+  while (p.acc_cols < p.n_tile) p.acc_cols <<= 1;
+  const int64_t n_work = cdiv(a.n_out, kTileM) * cdiv(a.cout, p.n_tile);
+  const int grid = (int)(n_work < num_sms() ? n_work : num_sms());
   igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p, w_map);
   TSB_LAUNCH_CHECK();
   return TSB_OK;

@@ -38,16 +38,23 @@ def lidar_scan(seed: int, n_rays: int = 120_000, box_fraction: float = 0.2, n_bo
     return np.concatenate([xyz, inten], 1).astype(np.float32)
 
 
-def multisweep_scan(seed: int, sweeps: int = 10, n_rays: int = 25_000) -> np.ndarray:
-    """Detection-style input: `sweeps` ring scans with small ego offsets merged, cropped to
-    [-54,54]^2 x [-5,3] m; float32 [~sweeps*n_rays, 5] = (x, y, z, intensity, time in [0,0.5])."""
+def multisweep_scan(seed: int, sweeps: int = 10, n_rays: int = 25_000, box_fraction: float = 0.2,
+                    n_boxes: int = 30) -> np.ndarray:
+    """Detection-style input: `sweeps` copies of the scan generator (rings + the same boxes seen from
+    a moving sensor) with small ego offsets merged, cropped to [-54,54]^2 x [-5,3] m; float32
+    [~sweeps*n_rays*(1+box_fraction), 5] = (x, y, z, intensity, time in [0,0.5])."""
     rng = np.random.default_rng(seed)
+    centres = np.stack([rng.uniform(-40, 40, n_boxes), rng.uniform(-40, 40, n_boxes), rng.uniform(-1.7, 0.5, n_boxes)], 1)
+    sides = rng.uniform(1.0, 4.0, (n_boxes, 3))
+    n_box_pts = int(n_rays * box_fraction)
     out = []
     for s in range(sweeps):
         origin = (0.4 * s * rng.uniform(0.8, 1.2), 0.05 * rng.standard_normal(), 0.0)
-        xyz = _ring_points(rng, n_rays, origin)
-        t = np.full((n_rays, 1), 0.5 * s / max(sweeps - 1, 1))
-        out.append(np.concatenate([xyz, rng.uniform(0, 1, (n_rays, 1)), t], 1))
+        which = rng.integers(0, n_boxes, n_box_pts)
+        boxes = centres[which] + (rng.uniform(0, 1, (n_box_pts, 3)) - 0.5) * sides[which]
+        xyz = np.concatenate([_ring_points(rng, n_rays, origin), boxes], 0)
+        t = np.full((xyz.shape[0], 1), 0.5 * s / max(sweeps - 1, 1))
+        out.append(np.concatenate([xyz, rng.uniform(0, 1, (xyz.shape[0], 1)), t], 1))
     p = np.concatenate(out, 0)
     keep = (np.abs(p[:, 0]) < 54) & (np.abs(p[:, 1]) < 54) & (p[:, 2] > -5) & (p[:, 2] < 3)
     return p[keep].astype(np.float32)
