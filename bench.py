@@ -266,6 +266,12 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         d["ms"] += ev0.elapsed_time(ev1); d["n"] += 1; d["flops"] += fl; d["bytes"] += by
     roof = None
     conv_ms = sum(d["ms"] for d in by_shape.values())
+    if args.dump_layers:
+        for key, d in sorted(by_shape.items(), key=lambda kv: -kv[1]["ms"]):
+            sys.stderr.write(f"layer n_in={key[0]:7d} n_out={key[1]:7d} kvol={key[2]:2d} {key[3]:3d}->{key[4]:3d}  "
+                             f"launches/step={d['n'] / args.steps:4.1f} avg_us={d['ms'] * 1e3 / d['n']:8.1f} "
+                             f"total_us/step={d['ms'] * 1e3 / args.steps:8.1f} useful_TF={d['flops'] / d['ms'] / 1e9:7.1f} "
+                             f"GB/s={d['bytes'] / d['ms'] / 1e6:7.1f}\n")
     if by_shape:
         key, d = max(by_shape.items(), key=lambda kv: kv[1]["ms"])
         sec = d["ms"] / 1e3
@@ -435,6 +441,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
+    ap.add_argument("--dump-layers", action="store_true", help="per-layer-shape conv timings to stderr")
     ap.add_argument("--layer", default=None, help="N,Cin,Cout,kernel,stride[,occupancy]: single-layer mode")
     ap.add_argument("--dataflow", default="ImplicitGEMM")
     ap.add_argument("--dtype", default="f16")

@@ -108,26 +108,32 @@ def test_resnet21d_matches_cpu_oracle(dtype, tol):
 
 
 def test_batched_scans_equal_single_scans():
-    """Scans in one batch do not interact: a 2-scan batch gives the concatenation of the single-scan
-    results (what makes scan-sharding across GPUs exact)."""
+    """Scans in one batch do not interact, given a common spatial range: a 2-scan batch gives the
+    concatenation of the single-scan results (what makes scan-sharding across GPUs exact).  Without a
+    stated range the strided-conv output bound comes from the largest coordinate present in the whole
+    batch (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:33-37), so voxels on the
+    upper boundary of one scan can depend on another scan; the range removes that coupling."""
     import torchsparse_b200 as ts
     from torchsparse_b200.backbones import SparseResUNet42
-    from torchsparse_b200.utils.collate import sparse_collate
 
     torch.manual_seed(0)
     model = SparseResUNet42(in_channels=4, width_multiplier=0.5).cuda().eval()
-    outs, tensors = [], []
-    for seed in (0, 1):
-        coords, feats = _scan_crop(3000, seed)
-        t = ts.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords[:, 1:]).cuda())
-        tensors.append(t)
-        single = ts.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda())
+    scans = [_scan_crop(3000, seed) for seed in (0, 1)]
+    ext = np.max([c[:, 1:].max(0) for c, _ in scans], axis=0) + 1
+    ext = tuple(int(v + (16 - v % 16) % 16) for v in ext)          # divisible by the total stride
+    outs = []
+    for coords, feats in scans:
+        single = ts.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda(),
+                                 spatial_range=(1,) + ext)
         with torch.no_grad():
             outs.append(model(single)[-1])
-    batch = sparse_collate(tensors)
+    bc = np.concatenate([scans[0][0], scans[1][0] + np.array([1, 0, 0, 0], np.int32)])
+    bf = np.concatenate([scans[0][1], scans[1][1]])
+    batch = ts.SparseTensor(torch.from_numpy(bf).cuda(), torch.from_numpy(bc).cuda(), spatial_range=(2,) + ext)
     with torch.no_grad():
         y = model(batch)[-1]
     n0 = outs[0].feats.shape[0]
+    assert y.feats.shape[0] == n0 + outs[1].feats.shape[0]
     assert torch.equal(y.coords[:n0, 1:], outs[0].coords[:, 1:]) and torch.equal(y.coords[n0:, 1:], outs[1].coords[:, 1:])
     assert bool((y.coords[n0:, 0] == 1).all())
     assert rel_l2(y.feats[:n0].cpu().numpy(), outs[0].feats.cpu().numpy()) < 1e-5
