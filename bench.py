@@ -66,7 +66,7 @@ class SegNet(torch.nn.Module):
         return self.head(self.backbone(x)[-1].feats)
 
 
-def make_model(device=None, half=True, engine=True):
+def make_model(device=None, half=True, engine=True, sort_max_stride=0):
     torch.manual_seed(0)
     model = SegNet()
     for m in model.modules():   # random Kaiming-style init, non-trivial BN statistics
@@ -85,7 +85,7 @@ def make_model(device=None, half=True, engine=True):
             model = model.half()
         if engine:
             from torchsparse_b200.nn import InferenceEngine
-            model.backbone = InferenceEngine(model.backbone)
+            model.backbone = InferenceEngine(model.backbone, sort_max_stride=sort_max_stride)
     return model
 
 
@@ -175,7 +175,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
 
     from torchsparse_b200.nn import functional as F
     F.set_conv_mode(args.conv_mode)
-    model = make_model(device, engine=not args.unfused)
+    model = make_model(device, engine=not args.unfused, sort_max_stride=args.sort_max_stride)
     scans = [scan_points(1000 * rank + i) for i in range(SCAN_POOL)]
     host = [torch.from_numpy(s).pin_memory() for s in scans]
     resident = [h.to(device) for h in host]
@@ -299,6 +299,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                    "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": scans_per_step,
                    "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps; {SCAN_POOL} scans rotated",
                    "conv_mode": args.conv_mode, "fused_inference_engine": not args.unfused,
+                   "sort_max_stride": args.sort_max_stride,
                    "parallelism": f"scan-sharded x{world}, NCCL all-gather of logits" if world > 1 else "single GPU"},
         "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
@@ -447,6 +448,8 @@ def main():
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
     ap.add_argument("--unfused", action="store_true", help="run the module graph as written (no InferenceEngine)")
+    ap.add_argument("--sort-max-stride", type=int, default=0,
+                    help="row-sorted kernel maps for convolutions at tensor strides <= this value (0 = none)")
     ap.add_argument("--conv-mode", type=int, default=0, choices=[0, 1, 2],
                     help="0 unsorted, 1 row-sorted maps, 2 sorted with 3 mask splits (F.set_conv_mode)")
     args = ap.parse_args()

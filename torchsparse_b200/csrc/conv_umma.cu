@@ -271,7 +271,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 //   tile ring    (2)         map slice + offset mask of a tile   sched_full[] / sched_empty[]
 //   accumulator  (2)         TMEM column ranges                   acc_full[] / acc_empty[]
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t s_full[kMaxStages];
@@ -649,14 +649,25 @@ size_t smem_bytes_for(int n_tile, int stages, int kvol, int ring) {
   return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)ring * kTileM * kvol * sizeof(int);
 }
 
-// as many stages as fit next to the tile ring (one persistent CTA per SM); a ring of 3 unless
-// giving up one slot buys a stage for a shallow pipeline
-void pick_config(int n_tile, int kvol, int* stages, int* ring) {
+// Two persistent CTAs per SM when two double-buffered accumulators fit TMEM (N tile <= 128 columns)
+// and three stages fit half the shared memory: two MMA issuers and 16 gather warps per SM hide the
+// per-block latency of the narrow layers.  Otherwise one CTA per SM with as many stages as fit.
+void pick_config(int n_tile, int kvol, int* stages, int* ring, int* ctas) {
+  int acc_cols = 32;
+  while (acc_cols < n_tile) acc_cols <<= 1;
+  if (acc_cols <= 128) {
+    const size_t half = 112 * 1024;
+    int best = 0;
+    for (int s = 2; s <= kMaxStages; ++s)
+      if (smem_bytes_for(n_tile, s, kvol, 2) <= half) best = s;
+    if (best >= 3) { *stages = best; *ring = 2; *ctas = 2; return; }
+  }
   const size_t budget = 226 * 1024;
   int best[2] = {0, 0};
   for (int r = 2; r <= 3; ++r)
     for (int s = 2; s <= kMaxStages; ++s)
       if (smem_bytes_for(n_tile, s, kvol, r) <= budget) best[r - 2] = s;
+  *ctas = 1;
   if (best[0] > best[1] && best[1] < 4) { *stages = best[0]; *ring = 2; }
   else { *stages = best[1]; *ring = 3; }
 }
@@ -685,8 +696,8 @@ bool igemm_umma_supported(const IgemmArgs& a) {
   if (a.kvol > kMaxKvolUmma) return false;
   if (((uintptr_t)a.x | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual | (uintptr_t)a.packed_w) & 15)
     return false;
-  int st = 0, rg = 0;
-  pick_config(pick_n_tile(a.cout), a.kvol, &st, &rg);
+  int st = 0, rg = 0, ct = 0;
+  pick_config(pick_n_tile(a.cout), a.kvol, &st, &rg, &ct);
   return st >= 2;
 }
 
@@ -740,7 +751,8 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   }
   p.n_in = (int)a.n_in; p.n_out = (int)a.n_out; p.kvol = a.kvol; p.cin = a.cin; p.cout = a.cout;
   p.n_tile = pick_n_tile(a.cout);
-  pick_config(p.n_tile, a.kvol, &p.stages, &p.ring);
+  int ctas = 1;
+  pick_config(p.n_tile, a.kvol, &p.stages, &p.ring, &ctas);
   p.relu = a.relu;
   p.ab_format = (a.dtype == TSB_BF16) ? 1 : 0;
   const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol, p.ring);
@@ -768,7 +780,8 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   p.acc_cols = 32;
   while (p.acc_cols < p.n_tile) p.acc_cols <<= 1;
   const int64_t n_work = cdiv(a.n_out, kTileM) * cdiv(a.cout, p.n_tile);
-  const int grid = (int)(n_work < num_sms() ? n_work : num_sms());
+  const int64_t slots = (int64_t)ctas * num_sms();
+  const int grid = (int)(n_work < slots ? n_work : slots);
   igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p, w_map);
   TSB_LAUNCH_CHECK();
   return TSB_OK;

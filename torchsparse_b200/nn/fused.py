@@ -79,6 +79,23 @@ class FusedConv(nn.Module):
         self.shift = shift.to(self.kernel.device).float()
         return self
 
+    # set by InferenceEngine: layers whose input (output, for transposed convs) tensor stride is at most
+    # this value run on row-sorted kernel maps (fewer issued K blocks where the map is very sparse)
+    sort_max_stride = 0
+
+    def _layer_config(self, x: SparseTensor):
+        if self._config is not None or self.sort_max_stride <= 0:
+            return self._config
+        s = max(x.stride)
+        if self.transposed:
+            s = s // max(self.stride)
+        if s > self.sort_max_stride:
+            return None
+        cfg = _conv_impl.resolve_config(None).copy()
+        cfg["ifsort"] = True
+        cfg["split_mask_num"] = 1
+        return cfg
+
     def forward(self, x: SparseTensor, residual: Optional[torch.Tensor] = None) -> SparseTensor:
         if self.pointwise:
             out = torch.addmm(self.shift_lp, x.feats, self.kernel)
@@ -90,7 +107,7 @@ class FusedConv(nn.Module):
             y._caches = x._caches
             return y
         return F.conv3d(x, self.kernel, self.kernel_size, None, self.stride, self.padding, self.dilation,
-                        self._config, self.transposed, False, False,
+                        self._layer_config(x), self.transposed, False, False,
                         epilogue={"scale": self.scale, "bias": self.shift, "residual": residual, "relu": self.relu})
 
     def extra_repr(self) -> str:
@@ -157,11 +174,16 @@ def fuse_for_inference(model: nn.Module) -> nn.Module:
 class InferenceEngine(nn.Module):
     """Eval-mode wrapper: fused modules, no autograd, strided kernel maps built ahead of the convs."""
 
-    def __init__(self, model: nn.Module) -> None:
+    def __init__(self, model: nn.Module, sort_max_stride: int = 0) -> None:
+        """`sort_max_stride` > 0: convolutions at tensor strides up to that value use row-sorted kernel
+        maps (the reference's sorted implicit GEMM, chosen per resolution level instead of globally)."""
         super().__init__()
         if model.training:
             raise ValueError("InferenceEngine needs a model in eval() mode (BatchNorm statistics are folded)")
         self.model = fuse_for_inference(model)
+        for m in self.model.modules():
+            if isinstance(m, FusedConv):
+                m.sort_max_stride = sort_max_stride
         self._plan = None   # strided conv keys in execution order, learnt on the first call
 
     def _prebuild(self, x: SparseTensor) -> None:
