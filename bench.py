@@ -216,23 +216,48 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         records.append((cur["step"], cur["k"], dims[:6], ev0, ev1))
         cur["k"] += 1
 
+    n_streams = max(1, args.streams)
+    side = [torch.cuda.Stream(device) for _ in range(n_streams)] if n_streams > 1 else [stream]
+
     def timed(e2e: bool, observe: bool):
         with torch.no_grad():
             for i in range(args.warmup):
-                step(i, e2e)
+                with torch.cuda.stream(side[i % n_streams]):
+                    step(i, e2e)
             barrier()
             evs = []
             launches0 = backend.launch_count()
             backend.set_launch_observer(observer if observe else None)
             h2d = d2h = 0
-            for i in range(args.steps):
-                flush.fill_(i & 0xFF)       # evict L2 between steps (outside the timed events)
+            if n_streams == 1:
+                for i in range(args.steps):
+                    flush.fill_(i & 0xFF)       # evict L2 between steps (outside the timed events)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    cur["step"], cur["k"] = i, 0
+                    _, bi, bo = step(i, e2e)
+                    e1.record(stream)
+                    h2d, d2h = bi, bo
+                    evs.append((e0, e1))
+            else:
+                # consecutive scans alternate between CUDA streams, so the host-side part of one scan
+                # (kernel-map readbacks, launches) overlaps the convolutions of the previous one; the whole
+                # K-step region is timed with one event pair and the L2 flushes are INSIDE it
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
-                cur["step"], cur["k"] = i, 0
-                _, bi, bo = step(i, e2e)
+                for s in side:
+                    s.wait_event(e0)
+                for i in range(args.steps):
+                    with torch.cuda.stream(side[i % n_streams]):
+                        flush.fill_(i & 0xFF)
+                        cur["step"], cur["k"] = i, 0
+                        _, bi, bo = step(i, e2e)
+                        h2d, d2h = bi, bo
+                for s in side:
+                    done = torch.cuda.Event()
+                    done.record(s)
+                    stream.wait_event(done)
                 e1.record(stream)
-                h2d, d2h = bi, bo
                 evs.append((e0, e1))
             backend.set_launch_observer(None)
             barrier()
@@ -297,7 +322,10 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         "config": {"workload": "BASELINE config 2: SparseResUNet42 (MinkUNet-class, cr=1.0) + 19-class head, fp16 "
                                "inference, one synthetic 64-ring LiDAR scan (144k points, 0.05 m voxels) per GPU per step",
                    "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": scans_per_step,
-                   "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps; {SCAN_POOL} scans rotated",
+                   "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps"
+                         + (" (inside the timed region)" if n_streams > 1 else " (outside the timed events)")
+                         + f"; {SCAN_POOL} scans rotated",
+                   "streams": n_streams,
                    "conv_mode": args.conv_mode, "fused_inference_engine": not args.unfused,
                    "sort_max_stride": args.sort_max_stride,
                    "parallelism": f"scan-sharded x{world}, NCCL all-gather of logits" if world > 1 else "single GPU"},
@@ -434,6 +462,55 @@ def run_layer(args, device):
             "first_call_ms_incl_kmap": round(first_ms, 3), "steps": args.steps, "warmup": args.warmup}
 
 
+def run_kmap(args, device):
+    """Kernel-map build timing (--kmap N,kernel,stride[,occupancy|lidar]): median ms of a cold build (caches
+    cleared every iteration, as torchsparse/utils/tune.py:67-71 does), algorithmic bytes and GB/s."""
+    from torchsparse_b200.nn import functional as F
+    from torchsparse_b200.utils.synthetic import uniform_voxels
+
+    parts = args.kmap.split(",")
+    n, ks, st = int(parts[0]), int(parts[1]), int(parts[2])
+    occ = parts[3] if len(parts) > 3 else "0.05"
+    if occ == "lidar":
+        from torchsparse_b200.utils import sparse_quantize
+        pts = torch.from_numpy(scan_points(0)).to(device)
+        vox = sparse_quantize(pts[:, :3], VOXEL)
+        coords = torch.cat([torch.zeros((vox.shape[0], 1), dtype=torch.int32, device=device), vox], 1)
+        n = coords.shape[0]
+    else:
+        coords = torch.from_numpy(uniform_voxels(0, n, float(occ))[0]).to(device)
+    pad = (ks - 1) // 2 if (ks % 2 == 1 and st == 1) else 0
+    kvol = ks ** 3
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    times, m = [], 0
+    for i in range(args.warmup + args.steps):
+        flush.fill_(i & 0xFF)
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        km = F.build_kernel_map(coords, n, ks, st, pad, None, None, None, "hashmap_on_the_fly")
+        e1.record()
+        torch.cuda.synchronize()
+        m = km["sizes"][1]
+        if i >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    cap = 512
+    while cap < 2 * max(n, m):
+        cap *= 2
+    m_pad = (m + 127) // 128 * 128
+    if st == 1:   # coords + table write + coords re-read + map write + probe reads
+        byts = n * 16 + cap * 12 + n * 16 + m_pad * kvol * 4 + (kvol // 2 if kvol % 2 else kvol) * n * 8
+    else:         # + candidate keys written, sorted (read+write), unique; outputs; stage-3 probes
+        slots = ((ks + st - 1) // st) ** 3
+        byts = n * 16 + 4 * n * slots * 8 + m * 24 + cap * 12 + n * 16 + m_pad * kvol * 4 + n * 8
+    pk = peaks()
+    return {"metric": "kmap_build_ms", "value": round(ms, 4), "unit": "ms", "higher_is_better": False,
+            "config": {"workload": f"kernel map N={n} k{ks} s{st} ({occ})", "n_out": m},
+            "algorithmic_bytes": byts, "algorithmic_gbs": round(byts / ms / 1e6, 1),
+            "frac_hbm_peak": round(byts / ms / 1e6 / pk["hbm_gbs"], 4), "min_ms": round(min(times), 4),
+            "steps": args.steps, "warmup": args.warmup}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -444,9 +521,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--dump-layers", action="store_true", help="per-layer-shape conv timings to stderr")
     ap.add_argument("--layer", default=None, help="N,Cin,Cout,kernel,stride[,occupancy]: single-layer mode")
+    ap.add_argument("--kmap", default=None, help="N,kernel,stride[,occupancy|lidar]: kernel-map build timing")
     ap.add_argument("--dataflow", default="ImplicitGEMM")
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
+    ap.add_argument("--streams", type=int, default=2,
+                    help="CUDA streams the scans of consecutive steps alternate between (1 = strictly serial steps)")
     ap.add_argument("--unfused", action="store_true", help="run the module graph as written (no InferenceEngine)")
     ap.add_argument("--sort-max-stride", type=int, default=0,
                     help="row-sorted kernel maps for convolutions at tensor strides <= this value (0 = none)")
@@ -468,9 +548,9 @@ def main():
 
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if args.layer:
+    if args.layer or args.kmap:
         if rank == 0:
-            print(json.dumps(run_layer(args, device)), flush=True)
+            print(json.dumps(run_layer(args, device) if args.layer else run_kmap(args, device)), flush=True)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -223,6 +223,7 @@ struct UmmaParams {
   int n_tile;           // UMMA N of a full tile (multiple of 16, <= 256)
   int acc_cols;         // TMEM columns of one accumulator buffer (power of two >= n_tile, >= 32)
   int ring;             // tile ring depth (2..kMaxRing)
+  int groups;           // gather groups (divides `stages`; 8 / groups warps each)
   int stages;
   int relu;
   int ab_format;        // 0 fp16, 1 bf16
@@ -299,7 +300,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(smem_u32(&s_full[s]), kGatherWarps * 32 + 1);   // every gather thread + the TMA thread (byte count)
+      // the threads of the block's gather group + the TMA thread (which also posts the byte count)
+      mbar_init(smem_u32(&s_full[s]), (kGatherWarps / p.groups) * 32 + 1);
       mbar_init(smem_u32(&s_empty[s]), 1);
     }
     for (int b = 0; b < p.ring; ++b) {
@@ -321,18 +323,36 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   const uint32_t tmem_base = s_tmem;
 
   if (warp < kGatherWarps) {
-    // ------------------------------------------------------------ gather warps (map staging + A operand)
+    // ------------------------------------------------------------ gather warps (A operand)
+    // The gather warps form p.groups groups; K blocks are dealt round-robin to the groups, and the
+    // number of groups divides the number of stages, so a group always refills the same stages and
+    // sees every use of them (a parity wait cannot tell "released once" from "released twice").
+    // A group's T = 32 * warps_per_group threads load the whole 128-row A tile of their block:
+    // thread -> 16-byte granule (t & 7) of rows (t >> 3) + (T/8) j, so every warp instruction covers
+    // four whole 128-byte row slices.  Each thread arrives asynchronously on the stage's full barrier
+    // when its copies have landed (cp.async.mbarrier.arrive.noinc) and goes on to its next block.
+    // Stage index and barrier phase are carried incrementally: this loop is latency-bound on its own
+    // instruction stream, and a division per block is a large part of it.
     const T* x = reinterpret_cast<const T*>(p.x);
-    const int gran = tid & 7;
-    const int rbase = tid >> 3;                                   // 0..31
+    const int wpg = kGatherWarps / p.groups;                      // warps per group
+    const int group = warp / wpg;                                  // >= p.groups: spare warp, loads nothing
+    const int tpg = wpg * 32;                                      // threads per group
+    const int tg = tid - group * tpg;
+    const int gran = tg & 7;
+    const int rbase = tg >> 3;
+    const int rstep = tpg >> 3;                                    // rows between a thread's copies (8 or 16)
+    const int ncopy = kTileM / rstep;                              // copies per thread per block (16 or 8)
     const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
-    int it = 0;          // K blocks issued so far (all tiles)
+    const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+    uint32_t stage = 0, phase = 0;      // stage of the current block; phase = parity of its use count
+    int owner = 0;                       // group that owns the current block
+    bool first_pass = true;              // the first use of a stage needs no release
     bool ok = true;
     int i = 0;
     for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
       const int buf = i % p.ring;
       const uint32_t use_parity = (uint32_t)(i / p.ring) & 1u;
-      int* s_map = s_map0 + buf * map_ints;
+      const int* s_map = s_map0 + buf * map_ints;
       if (ok && !mbar_wait_warp(smem_u32(&s_sched_full[buf]), use_parity, lane)) {
         atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
@@ -342,33 +362,30 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       if (!ok || s_abort) ok = false;
       for (int k = 0; k < p.kvol && ok; ++k) {
         if (!((kmask >> k) & 1u)) continue;
-        const T* rowp[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int src = s_map[(rbase + 32 * j) * p.kvol + k];
-          rowp[j] = (src >= 0) ? x + (int64_t)src * p.cin + gran * 8 : nullptr;
-        }
-        for (int c = 0; c < chunks; ++c, ++it) {
-          const int stage = it % p.stages;
-          if (it >= p.stages) {
-            if (!mbar_wait_warp(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1, lane)) {
+        for (int c = 0; c < chunks && ok; ++c) {
+          if (owner == group) {
+            if (!first_pass && !mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, lane)) {
               atomicExch(p.error, kErrEmptyWait);
               s_abort = 1;
               ok = false;
               break;
             }
+            const uint32_t a_dst = smem_base + stage * (uint32_t)stage_bytes + dst_off;
+            const int col = c * kChunkK + gran * 8;
+            const bool col_ok = col < p.cin;                        // cin % 8 == 0: all-in or all-out
+            const int* mp = s_map + rbase * p.kvol + k;
+            const int mstep = rstep * p.kvol;
+#pragma unroll 8
+            for (int j = 0; j < ncopy; ++j) {
+              const int src = mp[j * mstep];
+              const bool live = col_ok && src >= 0;
+              cp_async16(a_dst + (uint32_t)(j * rstep) * kRowBytes,
+                         live ? (const void*)(x + (int64_t)src * p.cin + col) : (const void*)x, live ? 16u : 0u);
+            }
+            cp_async_arrive_noinc(full0 + stage * 8);
           }
-          const uint32_t a_dst = smem_base + (uint32_t)stage * stage_bytes + dst_off;
-          const bool col_ok = (c * kChunkK + gran * 8) < p.cin;     // cin % 8 == 0: all-in or all-out
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const bool live = col_ok && rowp[j] != nullptr;
-            cp_async16(a_dst + (uint32_t)j * (32 * kRowBytes),
-                       live ? (const void*)(rowp[j] + c * kChunkK) : (const void*)x, live ? 16u : 0u);
-          }
-          // arrives on the stage's full barrier when this thread's copies have landed; the warp does
-          // not wait and goes on to the next K block (back-pressure comes from empty[] only)
-          cp_async_arrive_noinc(smem_u32(&s_full[stage]));
+          if (++owner == p.groups) owner = 0;
+          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
         }
       }
       __syncwarp();   // every lane has read its rows of the slice
@@ -513,7 +530,10 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     // ------------------------------------------------------------ weight loader (B operand, one thread)
     if (lane == 0) {
       const uint32_t bytes = (uint32_t)b_bytes;
-      int it = 0, i = 0;
+      const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+      uint32_t stage = 0, phase = 0;
+      bool first_pass = true;
+      int i = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
         const int buf = i % p.ring;
@@ -527,18 +547,18 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         mbar_arrive(smem_u32(&s_sched_empty[buf]));
         for (int k = 0; k < p.kvol && ok; ++k) {
           if (!((kmask >> k) & 1u)) continue;
-          for (int c = 0; c < chunks; ++c, ++it) {
-            const int stage = it % p.stages;
-            if (s_abort || (it >= p.stages && !mbar_wait(smem_u32(&s_empty[stage]), ((it / p.stages) + 1) & 1))) {
-              if (!s_abort) atomicExch(p.error, kErrEmptyWait);
+          const int wrow = k * p.cout + n0;
+          for (int c = 0; c < chunks; ++c) {
+            if (!first_pass && !mbar_wait(empty0 + stage * 8, phase ^ 1u)) {
+              atomicExch(p.error, kErrEmptyWait);
               s_abort = 1;
               ok = false;
               break;
             }
-            const uint32_t bar = smem_u32(&s_full[stage]);
+            const uint32_t bar = full0 + stage * 8;
             mbar_arrive_expect_tx(bar, bytes);
-            tma_load_2d(smem_base + (uint32_t)stage * stage_bytes + kABytes, &w_map, bar, c * kChunkK,
-                        k * p.cout + n0);
+            tma_load_2d(smem_base + stage * (uint32_t)stage_bytes + kABytes, &w_map, bar, c * kChunkK, wrow);
+            if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
           }
         }
       }
@@ -546,8 +566,17 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     __syncwarp();
   } else {
     // ------------------------------------------------------------ MMA issuer (one thread)
+    // This thread's instruction stream is the critical path of the whole CTA: stage index, barrier
+    // phase and descriptors are carried incrementally (no division, no 64-bit arithmetic per block).
     if (lane == 0) {
-      int it = 0, i = 0, acc_count = 0;
+      const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, SWIZZLE_128B
+      const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);  // stage 0, A operand
+      const uint32_t stage_units = (uint32_t)stage_bytes >> 4;
+      const uint32_t b_units = (uint32_t)kABytes >> 4;
+      const int last_steps = ((p.cin - (chunks - 1) * kChunkK) + 15) >> 4;
+      uint32_t stage = 0, phase = 0, a_lo = a_lo0;
+      int i = 0, acc_count = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
         const int buf = i % p.ring;
@@ -571,29 +600,28 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         }
         tc_fence_after();
         const uint32_t acc = tmem_base + (uint32_t)ab * acc_cols;
-        int first = 1;
+        uint32_t accumulate = 0;
         for (int k = 0; k < p.kvol && ok; ++k) {
           if (!((kmask >> k) & 1u)) continue;
-          for (int c = 0; c < chunks; ++c, ++it) {
-            const int stage = it % p.stages;
-            if (s_abort || !mbar_wait(smem_u32(&s_full[stage]), (it / p.stages) & 1)) {
-              if (!s_abort) atomicExch(p.error, kErrFullWait);
+          for (int c = 0; c < chunks; ++c) {
+            if (!mbar_wait(full0 + stage * 8, phase)) {
+              atomicExch(p.error, kErrFullWait);
               s_abort = 1;
               ok = false;
               break;
             }
             tc_fence_after();
-            const uint32_t a_base = smem_base + (uint32_t)stage * stage_bytes;
-            const uint64_t a_desc = make_smem_desc(a_base);
-            const uint64_t b_desc = make_smem_desc(a_base + kABytes);
-            const int kc = min(kChunkK, p.cin - c * kChunkK);
-            const int steps = (kc + 15) >> 4;
-            for (int s = 0; s < steps; ++s) {
-              // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
-              umma_f16(acc, a_desc + (uint64_t)(2 * s), b_desc + (uint64_t)(2 * s), idesc, first ? 0u : 1u);
-              first = 0;
+            const int steps = (c == chunks - 1) ? last_steps : (kChunkK >> 4);
+            // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
+            for (int st = 0; st < steps; ++st) {
+              const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_lo + 2u * st);
+              const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (a_lo + b_units + 2u * st);
+              umma_f16(acc, a_desc, b_desc, idesc, accumulate);
+              accumulate = 1;
             }
-            umma_commit(smem_u32(&s_empty[stage]));
+            umma_commit(empty0 + stage * 8);
+            a_lo += stage_units;
+            if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
           }
         }
         umma_commit(smem_u32(&s_acc_full[ab]));   // also on the error path: ends the epilogue's bounded wait early
@@ -649,6 +677,11 @@ size_t smem_bytes_for(int n_tile, int stages, int kvol, int ring) {
   return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)ring * kTileM * kvol * sizeof(int);
 }
 
+// Stage counts are restricted to {2,3,4,6,8} so that the number of gather groups (2,3,4,3,4) divides
+// them: a group then always refills the same stages.
+int usable_stages(int s) { return s >= 8 ? 8 : s >= 6 ? 6 : s >= 4 ? 4 : s; }
+int groups_for(int stages) { return stages == 2 ? 2 : (stages == 3 || stages == 6) ? 3 : 4; }
+
 // Two persistent CTAs per SM when two double-buffered accumulators fit TMEM (N tile <= 128 columns)
 // and three stages fit half the shared memory: two MMA issuers and 16 gather warps per SM hide the
 // per-block latency of the narrow layers.  Otherwise one CTA per SM with as many stages as fit.
@@ -660,15 +693,15 @@ void pick_config(int n_tile, int kvol, int* stages, int* ring, int* ctas) {
     int best = 0;
     for (int s = 2; s <= kMaxStages; ++s)
       if (smem_bytes_for(n_tile, s, kvol, 2) <= half) best = s;
-    if (best >= 3) { *stages = best; *ring = 2; *ctas = 2; return; }
+    if (best >= 3) { *stages = usable_stages(best); *ring = 2; *ctas = 2; return; }
   }
   const size_t budget = 226 * 1024;
   int best[2] = {0, 0};
   for (int r = 2; r <= 3; ++r)
     for (int s = 2; s <= kMaxStages; ++s)
-      if (smem_bytes_for(n_tile, s, kvol, r) <= budget) best[r - 2] = s;
+      if (smem_bytes_for(n_tile, s, kvol, r) <= budget) best[r - 2] = usable_stages(s);
   *ctas = 1;
-  if (best[0] > best[1] && best[1] < 4) { *stages = best[0]; *ring = 2; }
+  if (best[0] > best[1]) { *stages = best[0]; *ring = 2; }
   else { *stages = best[1]; *ring = 3; }
 }
 
@@ -753,6 +786,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   p.n_tile = pick_n_tile(a.cout);
   int ctas = 1;
   pick_config(p.n_tile, a.kvol, &p.stages, &p.ring, &ctas);
+  p.groups = groups_for(p.stages);
   p.relu = a.relu;
   p.ab_format = (a.dtype == TSB_BF16) ? 1 : 0;
   const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol, p.ring);
