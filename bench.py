@@ -103,10 +103,11 @@ def forward_scan(model, pts_dev: torch.Tensor):
     import torchsparse_b200 as ts
     from torchsparse_b200.utils import sparse_quantize
 
-    vox, idx = sparse_quantize(pts_dev[:, :3], VOXEL, return_index=True)
-    coords = torch.cat([torch.zeros((vox.shape[0], 1), dtype=torch.int32, device=vox.device), vox], 1)
+    vox, idx, (vmin, vmax) = sparse_quantize(pts_dev[:, :3], VOXEL, return_index=True, return_bounds=True)
+    coords = torch.nn.functional.pad(vox, (1, 0))              # batch index 0 in front
     feats = pts_dev[idx].half()
-    return model(ts.SparseTensor(feats, coords))
+    bounds = ((0, 0, 0, 0), (0,) + tuple(vmax))                # the points were shifted to start at the origin
+    return model(ts.SparseTensor(feats, coords, coord_bounds=bounds))
 
 
 class ClockSampler:

@@ -273,7 +273,8 @@ int tsb_devoxelize_fwd(const void* feats, const int32_t* indices, const float* w
 /* GPU twin of sparse_quantize: q = floor(xyz / voxel) (evaluated in float64, xyz float32 or
  * float64 [n,3], voxel HOST double[3]), unique by ravel key in ascending order.
  * Outputs: q_all int32 [n,3]; uniq_coords int32 [<=n,3]; first_index int64 [<=n] (smallest
- * original index of each voxel); inverse int64 [n]; result int32[1] (device) = number of voxels.
+ * original index of each voxel); inverse int64 [n]; result int32[8] (device): [0] = number of
+ * voxels, [1..3] = minimum and [4..6] = maximum voxel coordinate per axis.
  * Replaces sparse_quantize / ravel_hash (torchsparse/utils/quantize.py:9-48), a numpy routine
  * in the reference. */
 size_t tsb_quantize_workspace_bytes(int64_t n);

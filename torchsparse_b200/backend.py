@@ -357,6 +357,21 @@ def _packed_weight(kernel: torch.Tensor, code: int) -> Optional[torch.Tensor]:
     return packed
 
 
+def _padded_kernel(kernel: torch.Tensor) -> torch.Tensor:
+    """[Kvol, Cin, Cout] with Cin zero-padded to a multiple of 8; cached on the weight tensor."""
+    tag = (kernel._version, kernel.data_ptr())
+    hit = getattr(kernel, "_tsb_padded", None)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    cin = kernel.shape[1]
+    padded = torch.nn.functional.pad(kernel, (0, 0, 0, (-cin) % 8)).contiguous()
+    try:
+        kernel._tsb_padded = (tag, padded)
+    except (AttributeError, RuntimeError):
+        pass
+    return padded
+
+
 def _math_mode(t: torch.Tensor, allow_tf32: bool) -> int:
     return _lib.TSB_MATH_TF32 if (t.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
 
@@ -389,6 +404,12 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     kvol, cin, cout = kernel.shape
     if num_out_channels != cout:
         raise ValueError("num_out_channels does not match the kernel")
+    if in_feats.dtype != torch.float32 and cin % 8 != 0 and cout % 8 == 0 and kvol <= 32:
+        # rows that are not 16-byte multiples (the 4- or 5-channel input layer): zero-pad the channels
+        # once so that the layer takes the tensor-core kernel instead of the CUDA-core one
+        kernel = _padded_kernel(kernel)
+        in_feats = torch.nn.functional.pad(in_feats, (0, kernel.shape[1] - cin))
+        cin = kernel.shape[1]
     if out_in_map.shape[1] != kvol or out_in_map.shape[0] < num_out_feats:
         raise ValueError("out_in_map shape does not match kernel volume / output rows")
     out = torch.empty((num_out_feats, cout), dtype=in_feats.dtype, device=in_feats.device)
@@ -606,10 +627,12 @@ def quantize_unique_cuda(xyz: torch.Tensor, voxel_size: Sequence[float], return_
     uniq = torch.empty((n, 3), dtype=torch.int32, device=dev)
     first = torch.empty(n, dtype=torch.int64, device=dev) if return_index else None
     inv = torch.empty(n, dtype=torch.int64, device=dev) if return_inverse else None
-    result = torch.zeros(1, dtype=torch.int32, device=dev)
+    result = torch.zeros(8, dtype=torch.int32, device=dev)
     ws = _workspace(lib.tsb_quantize_workspace_bytes(n), dev)
     vox = (ctypes.c_double * 3)(*[float(v) for v in voxel_size])
     check(lib.tsb_quantize_unique(_p(xyz), int(xyz.dtype == torch.float64), n, vox, _p(q_all), _p(uniq), _p(first),
                                   _p(inv), _p(result), _p(ws), ws.numel(), _stream()), "quantize_unique_cuda")
-    nv = int(result.item())
-    return uniq[:nv], (first[:nv] if first is not None else None), inv
+    res = result.cpu().tolist()        # the one synchronisation: voxel count + coordinate bounds
+    nv = res[0]
+    bounds = (tuple(res[1:4]), tuple(res[4:7])) if nv else ((0, 0, 0), (0, 0, 0))
+    return uniq[:nv], (first[:nv] if first is not None else None), inv, bounds

@@ -66,7 +66,8 @@ __global__ void head_flags_kernel(const unsigned long long* __restrict__ keys, i
 __global__ void emit_kernel(const unsigned long long* __restrict__ keys, const int* __restrict__ sorted_idx,
                             const int* __restrict__ scan, int64_t n, const int* __restrict__ q_all,
                             int* __restrict__ uniq_coords, int64_t* __restrict__ first_index,
-                            int64_t* __restrict__ inverse, int* __restrict__ result) {
+                            int64_t* __restrict__ inverse, const int* __restrict__ minmax,
+                            int* __restrict__ result) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     int run = scan[i] - 1;
     int src = sorted_idx[i];
@@ -78,7 +79,11 @@ __global__ void emit_kernel(const unsigned long long* __restrict__ keys, const i
       uniq_coords[run * 3 + 2] = q_all[(int64_t)src * 3 + 2];
       if (first_index) first_index[run] = src;
     }
-    if (i == n - 1) result[0] = run + 1;
+    if (i == n - 1) {
+      result[0] = run + 1;
+#pragma unroll
+      for (int d = 0; d < 6; ++d) result[1 + d] = minmax[d];   // min x,y,z then max x,y,z of the voxel coordinates
+    }
   }
 }
 
@@ -122,7 +127,7 @@ int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const do
   if (n < 0 || !voxel || !result) return TSB_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
   if (n == 0) {
-    TSB_CUDA_TRY(cudaMemsetAsync(result, 0, sizeof(int32_t), s));
+    TSB_CUDA_TRY(cudaMemsetAsync(result, 0, 8 * sizeof(int32_t), s));
     return TSB_OK;
   }
   if (!xyz || !q_all || !uniq_coords) return TSB_ERR_BAD_ARG;
@@ -158,7 +163,8 @@ int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const do
   cb = w.cub_bytes;
   TSB_CUDA_TRY(cub::DeviceScan::InclusiveSum(base + w.cub, cb, flags, scan, n, s));
   count_launch();
-  emit_kernel<<<grid, kBlock, 0, s>>>(keys_out, idx_out, scan, n, q_all, uniq_coords, first_index, inverse, result);
+  emit_kernel<<<grid, kBlock, 0, s>>>(keys_out, idx_out, scan, n, q_all, uniq_coords, first_index, inverse, minmax,
+                                      result);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }

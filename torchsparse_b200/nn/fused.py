@@ -86,10 +86,9 @@ class FusedConv(nn.Module):
     def _layer_config(self, x: SparseTensor):
         if self._config is not None or self.sort_max_stride <= 0:
             return self._config
-        s = max(x.stride)
-        if self.transposed:
-            s = s // max(self.stride)
-        if s > self.sort_max_stride:
+        # only submanifold convolutions: their map is shared by every layer of the resolution level, so
+        # one sort serves many launches; a strided or transposed map is used once and not worth sorting
+        if self.transposed or any(s != 1 for s in self.stride) or max(x.stride) > self.sort_max_stride:
             return None
         cfg = _conv_impl.resolve_config(None).copy()
         cfg["ifsort"] = True

@@ -26,7 +26,7 @@ class SparseTensor:
     with a cache of kernel maps shared along the network (torchsparse/tensor.py:29-114)."""
 
     def __init__(self, feats: torch.Tensor, coords: torch.Tensor, stride: Union[int, Tuple[int, ...]] = 1,
-                 spatial_range: Union[int, Tuple[int, ...]] = None) -> None:
+                 spatial_range: Union[int, Tuple[int, ...]] = None, coord_bounds=None) -> None:
         self.feats = feats
         self.coords = coords
         self.stride = make_ntuple(stride, ndim=3)
@@ -39,6 +39,11 @@ class SparseTensor:
             self._caches = caches
         else:
             self._caches = TensorCache()
+        if coord_bounds is not None:
+            # ((min b,x,y,z), (max b,x,y,z)) known on the host (e.g. from sparse_quantize): kernel-map
+            # builds then need no device reduction of the coordinates
+            self._caches.cbounds[self.stride] = (tuple(int(v) for v in coord_bounds[0]),
+                                                 tuple(int(v) for v in coord_bounds[1]))
 
     @property
     def F(self) -> torch.Tensor:
