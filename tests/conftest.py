@@ -41,8 +41,11 @@ def _check_kernel_status(request):
     if request.node.get_closest_marker("gpu") is None:
         yield
         return
-    from torchsparse_b200 import backend
+    from torchsparse_b200 import backend, backends
     old = backend.check_kernel_status
+    old_tf32 = backends.allow_tf32
     backend.check_kernel_status = True
+    backends.allow_tf32 = False      # fp32 parity is exact fp32; the TF32 tests switch it on themselves
     yield
     backend.check_kernel_status = old
+    backends.allow_tf32 = old_tf32

@@ -3,6 +3,7 @@ fixtures (reference CPU conv + dense conv3d) and BASELINE config 1.
 
 Tolerances (relative L2 against the fp64 oracle on the same inputs):
   fp32 inputs, exact fp32 math : 1e-5
+  fp32 inputs, TF32 multiply    : 2e-3 (10-bit mantissa operands, fp32 accumulation)
   fp16 / bf16 inputs           : 2e-3 (fp16), 1.6e-2 (bf16, 8-bit mantissa)
 """
 import numpy as np
@@ -83,6 +84,31 @@ def test_conv_vs_oracle(dtype, dataflow, ifsort, split, ks, st, cin, cout):
     _, y = _sparse_conv(coords, feats, w, ks, st, dataflow, dtype, ifsort, split)
     assert y.feats.dtype == dtype and y.feats.shape == want.shape
     assert rel_l2(y.feats.float().cpu().numpy(), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("ifsort", [False, True])
+@pytest.mark.parametrize("ks,st,cin,cout", [(3, 1, 32, 32), (3, 1, 64, 96), (2, 2, 32, 64), (3, 1, 36, 40),
+                                            (3, 1, 256, 256), (3, 1, 4, 32)])
+def test_conv_tf32_vs_oracle(ifsort, ks, st, cin, cout):
+    """fp32 tensors with backends.allow_tf32 (the reference's default on Ampere and newer): the
+    implicit GEMM multiplies on the tensor cores as TF32 and accumulates in fp32."""
+    from torchsparse_b200 import backends
+
+    rng = np.random.default_rng(cin * 1000 + cout + 7)
+    coords = random_coords(rng, 1500, (16, 16, 16), 2)
+    feats = rng.standard_normal((coords.shape[0], cin)).astype(np.float32)
+    kvol = int(np.prod(ko._as3(ks)))
+    w = (rng.standard_normal((kvol, cin, cout)) * np.sqrt(2.0 / (kvol * cin))).astype(np.float32)
+    pad = tuple((k - 1) // 2 if (k % 2 == 1 and s == 1) else 0 for k, s in zip(ko._as3(ks), ko._as3(st)))
+    km = ko.build_kmap(coords, ks, st, pad)
+    want = ko.conv_from_map(feats, w, km["out_in_map"], km["sizes"][1])
+    backends.allow_tf32 = True       # restored by the autouse fixture
+    _, y = _sparse_conv(coords, feats, w, ks, st, "ImplicitGEMM", torch.float32, ifsort)
+    assert y.feats.dtype == torch.float32 and y.feats.shape == want.shape
+    err = rel_l2(y.feats.cpu().numpy(), want)
+    assert err < 2e-3
+    if cin % 4 == 0 and cout % 8 == 0:
+        assert err > 1e-6            # the tensor-core path ran (exact fp32 would be ~1e-7)
 
 
 def test_baseline_config1_all_dataflows():

@@ -339,9 +339,9 @@ cache_packed_weights = True
 check_kernel_status = False
 
 
-def _packed_weight(kernel: torch.Tensor, code: int) -> Optional[torch.Tensor]:
-    if code == _lib.TSB_F32:
-        return None
+def _packed_weight(kernel: torch.Tensor, code: int, tf32: bool = False) -> Optional[torch.Tensor]:
+    if code == _lib.TSB_F32 and not tf32:
+        return None          # exact fp32 runs on the CUDA cores, which read the weights as they are
     tag = (kernel._version, kernel.data_ptr())
     hit = getattr(kernel, "_tsb_packed", None)
     if hit is not None and hit[0] == tag:
@@ -421,7 +421,7 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
         scale = scale.float().contiguous()
     if residual is not None:
         residual = residual.to(in_feats.dtype).contiguous()
-    packed = _packed_weight(kernel, code) if cache_packed_weights else None
+    packed = _packed_weight(kernel, code, bool(allow_tf32)) if cache_packed_weights else None
     status = torch.zeros(1, dtype=torch.int32, device=in_feats.device) if check_kernel_status else None
     if _observer is not None:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -19,8 +19,8 @@ def init():
         device_capability = cap[0] * 100 + cap[1] * 10
     else:
         device_capability = 0
-    # fp32 inputs stay exact fp32 unless the user opts into TF32 (the reference turns TF32 on
-    # for every Ampere-or-newer device, which silently changes fp32 results)
-    allow_tf32 = False
+    # as in the reference: fp32 convolutions multiply as TF32 (fp32 accumulation) on Ampere and newer;
+    # set allow_tf32 = False for exact fp32 arithmetic on the CUDA cores
+    allow_tf32 = device_capability >= 800
     allow_fp16 = True
     hash_rsv_ratio = 2

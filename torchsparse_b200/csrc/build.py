@@ -37,7 +37,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def cc(job):
         s, o = job
-        r = subprocess.run([nvcc, *NVCC_FLAGS, "-c", s, "-o", o], capture_output=True, text=True)
+        extra = os.environ.get("TSB_NVCC_EXTRA", "").split()   # e.g. -DTSB_TRACE_BUILD for a debugging build
+        r = subprocess.run([nvcc, *NVCC_FLAGS, *extra, "-c", s, "-o", o], capture_output=True, text=True)
         log = o.replace(".o", ".ptxas.log")
         with open(log, "w") as f:
             f.write(r.stderr)

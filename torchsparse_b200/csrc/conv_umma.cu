@@ -1,29 +1,38 @@
 // Implicit-GEMM sparse convolution forward on the 5th-generation tensor cores (tcgen05 / TMEM).
 //
-//   Y[m, :] = sum_k  X[map[m][k], :] . W[k]         (fp16 or bf16 operands, fp32 accumulation)
+//   Y[m, :] = sum_k  X[map[m][k], :] . W[k]      (fp16 / bf16 operands, or fp32 operands multiplied
+//                                                  as TF32; fp32 accumulation in every case)
 //
 // One CTA owns 128 consecutive output rows (the rows of one map tile) and an N-tile of at most
-// 256 output channels.  The reduction runs over "K blocks": one kernel offset k x one 64-channel
-// chunk of Cin.  K blocks whose offset has no neighbour in the whole tile are skipped (the tile's
-// 128 x Kvol map slice is staged in shared memory first and OR-reduced into an offset mask), so
-// the issued MMA work follows the sparsity of the map; with a row-sorted map the skipping gets
-// coarser-grained and the output rows are scattered through reorder_loc.
+// 256 output channels.  The reduction runs over "K blocks": one kernel offset k x one 128-byte
+// chunk of Cin (64 16-bit or 32 32-bit channels).  K blocks whose offset has no neighbour in the
+// whole tile are skipped (the tile's 128 x Kvol map slice is staged in shared memory first and
+// OR-reduced into an offset mask), so the issued MMA work follows the sparsity of the map; with a
+// row-sorted map the skipping gets coarser-grained and the output rows are scattered through
+// reorder_loc.
 //
-// Roles (320 threads):
-//   warps 0-7  gather the 128 A rows of a K block (each a 128-byte slice of a feature row, or
-//              zeros for a missing neighbour) into a 128B-swizzled K-major stage with 16-byte
-//              cp.async, a commit group per block; a landed block is fenced for the tensor-core
-//              proxy and one lane per warp arrives on the stage's "full" barrier.  Afterwards the
-//              same warps run the epilogue: tcgen05.ld of their TMEM lanes, scale / bias /
-//              residual / ReLU, rounding and 16-byte stores.
-//   warp 8     one thread loads the weight block of each K block (64 channels x N_tile rows of
-//              the K-major packed weights) with a TMA tile copy that counts bytes on the same
-//              "full" barrier.
-//   warp 9     allocates TMEM; one thread issues tcgen05.mma (M=128, N=N_tile, K=16, 4 per stage)
-//              and releases stages / publishes the accumulator with tcgen05.commit.
+// Operands of a K block (one pipeline stage, both 128B-swizzled K-major tiles):
+//   A  128 gathered feature-row slices of 128 bytes (zeros for a missing neighbour), copied by
+//      all eight gather warps with 16-byte cp.async, four per thread; each thread's arrival on the
+//      stage's "full" barrier is attached to its copies (cp.async.mbarrier.arrive.noinc), so no
+//      thread ever blocks on data.  The map entries are read into registers before the wait for
+//      the stage, so the copies go out back to back once it is released.
+//   B  one TMA tile copy of N_tile rows of the K-major packed weights, counted in bytes on the
+//      same barrier.
 //
-// Every wait on an mbarrier is bounded: after kSpinLimit polls the thread records an error
-// code, and the CTA drains its copies, frees its TMEM and returns.
+// Roles (480 threads, persistent CTAs, one or two per SM):
+//   warps 0-7   gather (A operand)
+//   warps 8-11  epilogue: tcgen05.ld of their TMEM lane quarter, scale / bias / residual / ReLU,
+//               rounding and 16-byte stores
+//   warp 12     weight loader: one elected thread issues the TMA copies
+//   warp 13     allocates TMEM; one elected thread issues tcgen05.mma (M=128, N=N_tile, 32 bytes of K
+//               per instruction, 4 per stage) and releases stages / publishes accumulators with
+//               tcgen05.commit.  Warps 12 and 13 run their loops converged and elect the issuing
+//               lane per instruction, so that descriptors and coordinates stay warp-uniform.
+//   warp 14     scheduler: stages the map slices of the coming tiles and their offset masks
+//
+// Every wait on an mbarrier is bounded: when it runs out the thread records an error code and the
+// CTA stops issuing work, gives its copies in flight time to land, frees its TMEM and returns.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -35,22 +44,25 @@ namespace tsb {
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kChunkK = 64;                 // 16-bit elements per stage row = 128 bytes
-constexpr int kRowBytes = 128;
+constexpr int kRowBytes = 128;              // bytes of K per stage row = one swizzle span
 constexpr int kABytes = kTileM * kRowBytes; // 16 KiB
 constexpr int kGatherWarps = 8;
+constexpr int kGatherThreads = kGatherWarps * 32;
+constexpr int kRowsPerPass = kGatherThreads / 8;   // rows covered by one copy of every gather thread (32)
+constexpr int kCopies = kTileM / kRowsPerPass;     // copies per gather thread per K block (4)
 constexpr int kEpilogueWarps = 4;      // warps 8..11: warp % 4 = TMEM lane quarter
 constexpr int kTmaWarp = 12;
 constexpr int kMmaWarp = 13;
 constexpr int kSchedWarp = 14;
 constexpr int kThreads = 480;
-constexpr int kMaxRing = 4;            // tile ring: map slices + offset masks staged ahead of the gather warps
+constexpr int kMaxRing = 4;            // tile ring: map slices + offset masks staged ahead of the other roles
 constexpr int kMaxStages = 8;
 constexpr int kMaxKvolUmma = 32;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 
 enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3, kErrSchedWait = 4 };
+enum { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -88,29 +100,40 @@ __device__ __forceinline__ long long clk() {
   asm volatile("mov.u64 %0, %clock64;" : "=l"(t));
   return t;
 }
-// trace layout: [it][8] = {gather: after empty wait, after issue, after landing; tma: after issue;
-//                          mma: after full wait, after commit; spare, spare}
-#define TSB_TRACE(slot, it_)                                                         \
-  do {                                                                               \
+// Debugging aid, compiled in only with -DTSB_TRACE_BUILD: per-block timestamps of one CTA.
+// trace layout: [block][8] = {producer: at the block, after the empty wait, after issue; spare;
+//                             mma: at the block, after the full wait, after commit; spare}
+// (producer = thread 0 of the gather warps)
+#ifdef TSB_TRACE_BUILD
+#define TSB_TRACE_HOT(slot, it_)                                                                     \
+  do {                                                                                               \
     if (p.trace && (int)blockIdx.x == p.trace_cta && (it_) < 256) p.trace[(it_) * 8 + (slot)] = clk(); \
   } while (0)
+#else
+#define TSB_TRACE_HOT(slot, it_) do { } while (0)
+#endif
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: try_wait parks the thread in hardware instead of spinning on shared memory (a
-// spinning warp competes with the copies for the load/store pipe).  Gives up after kWaitLimitNs.
+// Bounded wait: try_wait parks the thread in hardware instead of spinning on shared memory.  The
+// wall clock is read only after the first 64 failed tries (reading it costs hundreds of cycles);
+// the wait gives up kWaitLimitNs after that.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_test(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try(bar, parity)) return true;
-    if ((i & 63u) == 63u && global_ns() - t0 > kWaitLimitNs) return false;
+    if ((i & 63u) == 63u) {
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) return false;
+    }
   }
   return false;
 }
-// one lane waits for the warp; the others are released by __syncwarp
+// one lane waits for the warp; the others are released by the shuffle
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane) {
   uint32_t ok = 1;
   if (lane == 0) ok = mbar_wait(bar, parity) ? 1u : 0u;
@@ -124,19 +147,16 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// waits until at most `pending` of this thread's committed groups are still in flight
-__device__ __forceinline__ void cp_async_wait_pending(int pending) {
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-  }
+// true in exactly one lane of a converged warp (the same lane every time)
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 
 #if defined(__CUDA_ARCH_FEAT_SM100_ALL) || defined(__CUDA_ARCH_FEAT_SM101_ALL) || defined(__CUDA_ARCH_FEAT_SM103_ALL)
@@ -164,16 +184,28 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 #endif
 }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// D[tmem] (+)= A[smem] . B[smem]; kind::f16 for fp16 / bf16 operands, kind::tf32 for fp32 operands
+template <bool TF32>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
 #ifdef TSB_TCGEN05
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if constexpr (TF32) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
 #endif
 }
 // arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed
@@ -194,14 +226,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 #endif
 }
 
-// K-major, 128-byte-swizzled operand tile: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);          // start address, leading byte offset (unused) = 1
-  uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);         // stride byte offset 1024, version 1, SWIZZLE_128B
-  return ((uint64_t)hi << 32) | lo;
-}
-
-// instruction descriptor: D fp32, A/B fp16 (0) or bf16 (1), both K-major, M = 128, N = n
+// instruction descriptor: D fp32, A/B format (0 fp16, 1 bf16, 2 tf32), both K-major, M = 128, N = n
 __host__ __device__ inline uint32_t make_idesc(int ab_format, int n) {
   return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(kTileM >> 4) << 24);
@@ -209,7 +234,6 @@ __host__ __device__ inline uint32_t make_idesc(int ab_format, int n) {
 
 struct UmmaParams {
   const void* x;        // [n_in, cin]
-  const void* wt;       // packed weights [kvol, cout, cin] (K-major)
   const int* map;       // [pad128(n_out), kvol]
   const int* reorder;   // nullable
   void* y;              // [n_out, cout]
@@ -217,16 +241,15 @@ struct UmmaParams {
   const float* bias;    // nullable
   const void* residual; // nullable, [n_out, cout]
   int* error;           // device error word (0 = fine)
-  long long* trace;     // debugging aid: per-block timestamps of CTA `trace_cta` (null = off)
+  long long* trace;     // debugging aid (trace builds only)
   int trace_cta;
   int n_in, n_out, kvol, cin, cout;
   int n_tile;           // UMMA N of a full tile (multiple of 16, <= 256)
   int acc_cols;         // TMEM columns of one accumulator buffer (power of two >= n_tile, >= 32)
   int ring;             // tile ring depth (2..kMaxRing)
-  int groups;           // gather groups (divides `stages`; 8 / groups warps each)
   int stages;
   int relu;
-  int ab_format;        // 0 fp16, 1 bf16
+  int ab_format;        // kFmtF16 / kFmtBF16 / kFmtTF32
 };
 
 template <typename T>
@@ -252,8 +275,8 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
 
-// TMA tile load of the weight block: box = 64 channels x n_tile rows of the packed weights,
-// written 128B-swizzled; completion is counted in bytes on the mbarrier.
+// TMA tile load of the weight block: box = 128 bytes of channels x n_tile rows of the packed
+// weights, written 128B-swizzled; completion is counted in bytes on the mbarrier.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -265,15 +288,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// Persistent kernel: one CTA per SM walks the (row tile, N tile) work list with a fixed stride.
+// Persistent kernel: each CTA walks the (row tile, N tile) work list with a fixed stride.
 // Three rings decouple the roles so that the copies of the next tile are in flight while the
 // current tile is multiplied and the previous one is written out:
 //   stage ring   (p.stages)  A+B operands of one K block         full[] / empty[]
-//   tile ring    (2)         map slice + offset mask of a tile   sched_full[] / sched_empty[]
+//   tile ring    (p.ring)    map slice + offset mask of a tile   sched_full[] / sched_empty[]
 //   accumulator  (2)         TMEM column ranges                   acc_full[] / acc_empty[]
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
 igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map) {
+  constexpr bool kTF32 = sizeof(T) == 4;
+  constexpr int kChunk = kRowBytes / (int)sizeof(T);     // channels per stage row
+  constexpr int kStepK = 32 / (int)sizeof(T);            // channels per MMA instruction (32 bytes of K)
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t s_full[kMaxStages];
   __shared__ uint64_t s_empty[kMaxStages];
@@ -296,17 +322,17 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   const int map_ints = kTileM * p.kvol;
   int* s_map0 = reinterpret_cast<int*>(smem_raw + (map_smem - smem_u32(smem_raw)));
   const uint32_t acc_cols = p.acc_cols;            // TMEM columns of one accumulator (power of two)
-  const int chunks = (p.cin + kChunkK - 1) / kChunkK;
+  const int chunks = (p.cin + kChunk - 1) / kChunk;
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      // the threads of the block's gather group + the TMA thread (which also posts the byte count)
-      mbar_init(smem_u32(&s_full[s]), (kGatherWarps / p.groups) * 32 + 1);
-      mbar_init(smem_u32(&s_empty[s]), 1);
+      // every gather thread (attached to its copies) + the weight loader's arrive.expect_tx
+      mbar_init(smem_u32(&s_full[s]), kGatherThreads + 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);   // tcgen05.commit
     }
     for (int b = 0; b < p.ring; ++b) {
       mbar_init(smem_u32(&s_sched_full[b]), 1);
-      // readers of a ring slot: gather warps, TMA thread, MMA thread, epilogue warps
+      // readers of a ring slot: gather warps, weight loader, MMA warp, epilogue warps
       mbar_init(smem_u32(&s_sched_empty[b]), kGatherWarps + 2 + kEpilogueWarps);
     }
     for (int b = 0; b < 2; ++b) {
@@ -324,74 +350,70 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 
   if (warp < kGatherWarps) {
     // ------------------------------------------------------------ gather warps (A operand)
-    // The gather warps form p.groups groups; K blocks are dealt round-robin to the groups, and the
-    // number of groups divides the number of stages, so a group always refills the same stages and
-    // sees every use of them (a parity wait cannot tell "released once" from "released twice").
-    // A group's T = 32 * warps_per_group threads load the whole 128-row A tile of their block:
-    // thread -> 16-byte granule (t & 7) of rows (t >> 3) + (T/8) j, so every warp instruction covers
-    // four whole 128-byte row slices.  Each thread arrives asynchronously on the stage's full barrier
-    // when its copies have landed (cp.async.mbarrier.arrive.noinc) and goes on to its next block.
-    // Stage index and barrier phase are carried incrementally: this loop is latency-bound on its own
-    // instruction stream, and a division per block is a large part of it.
+    // Thread t copies the 16-byte granule (t & 7) of rows (t >> 3) + 32 j, j = 0..3, of every K block:
+    // a warp instruction covers four whole 128-byte row slices.  The four map entries of an offset
+    // are read once, before the wait for the stage, and serve all channel chunks of that offset.
+    constexpr int kGran = 16 / (int)sizeof(T);                     // channels per 16-byte granule
     const T* x = reinterpret_cast<const T*>(p.x);
-    const int wpg = kGatherWarps / p.groups;                      // warps per group
-    const int group = warp / wpg;                                  // >= p.groups: spare warp, loads nothing
-    const int tpg = wpg * 32;                                      // threads per group
-    const int tg = tid - group * tpg;
-    const int gran = tg & 7;
-    const int rbase = tg >> 3;
-    const int rstep = tpg >> 3;                                    // rows between a thread's copies (8 or 16)
-    const int ncopy = kTileM / rstep;                              // copies per thread per block (16 or 8)
+    const int gran = tid & 7;
+    const int rbase = tid >> 3;
     const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+    const int mrow = kRowsPerPass * p.kvol;                        // map ints between a thread's rows
     uint32_t stage = 0, phase = 0;      // stage of the current block; phase = parity of its use count
-    int owner = 0;                       // group that owns the current block
     bool first_pass = true;              // the first use of a stage needs no release
     bool ok = true;
     int i = 0;
+#ifdef TSB_TRACE_BUILD
+    int blk = 0;
+#endif
     for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
       const int buf = i % p.ring;
       const uint32_t use_parity = (uint32_t)(i / p.ring) & 1u;
-      const int* s_map = s_map0 + buf * map_ints;
+      const int* mp = s_map0 + buf * map_ints + rbase * p.kvol;
       if (ok && !mbar_wait_warp(smem_u32(&s_sched_full[buf]), use_parity, lane)) {
         atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         ok = false;
       }
-      const uint32_t kmask = (ok && !s_abort) ? s_kmask[buf] : 0u;
-      if (!ok || s_abort) ok = false;
+      if (s_abort) ok = false;
+      const uint32_t kmask = ok ? s_kmask[buf] : 0u;
       for (int k = 0; k < p.kvol && ok; ++k) {
         if (!((kmask >> k) & 1u)) continue;
-        for (int c = 0; c < chunks && ok; ++c) {
-          if (owner == group) {
-            if (!first_pass && !mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, lane)) {
-              atomicExch(p.error, kErrEmptyWait);
-              s_abort = 1;
-              ok = false;
-              break;
-            }
-            const uint32_t a_dst = smem_base + stage * (uint32_t)stage_bytes + dst_off;
-            const int col = c * kChunkK + gran * 8;
-            const bool col_ok = col < p.cin;                        // cin % 8 == 0: all-in or all-out
-            const int* mp = s_map + rbase * p.kvol + k;
-            const int mstep = rstep * p.kvol;
-#pragma unroll 8
-            for (int j = 0; j < ncopy; ++j) {
-              const int src = mp[j * mstep];
-              const bool live = col_ok && src >= 0;
-              cp_async16(a_dst + (uint32_t)(j * rstep) * kRowBytes,
-                         live ? (const void*)(x + (int64_t)src * p.cin + col) : (const void*)x, live ? 16u : 0u);
-            }
-            cp_async_arrive_noinc(full0 + stage * 8);
+        int src[kCopies];
+#pragma unroll
+        for (int j = 0; j < kCopies; ++j) src[j] = mp[j * mrow + k];
+        for (int c = 0; c < chunks; ++c) {
+          const int col = c * kChunk + gran * kGran;
+          const bool col_ok = col < p.cin;                          // rows are 16-byte multiples: all-in or all-out
+          const T* xc = x + col;
+          if (tid == 0) TSB_TRACE_HOT(0, blk);
+          if (!first_pass && !mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, lane)) {
+            atomicExch(p.error, kErrEmptyWait);
+            s_abort = 1;
+            ok = false;
+            break;
           }
-          if (++owner == p.groups) owner = 0;
+          if (tid == 0) TSB_TRACE_HOT(1, blk);
+          const uint32_t a_dst = smem_base + stage * (uint32_t)stage_bytes + dst_off;
+#pragma unroll
+          for (int j = 0; j < kCopies; ++j) {
+            const bool live = col_ok && src[j] >= 0;
+            cp_async16(a_dst + (uint32_t)(j * kRowsPerPass) * kRowBytes,
+                       live ? (const void*)(xc + (int64_t)src[j] * p.cin) : (const void*)x, live ? 16u : 0u);
+          }
+          cp_async_arrive_noinc(full0 + stage * 8);
+          if (tid == 0) TSB_TRACE_HOT(2, blk);
+#ifdef TSB_TRACE_BUILD
+          ++blk;
+#endif
           if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
         }
       }
       __syncwarp();   // every lane has read its rows of the slice
       if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
     }
-    cp_async_wait_all();   // nothing of this CTA may still be writing shared memory at exit
+    cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
   } else if (warp < kGatherWarps + kEpilogueWarps) {
     // ------------------------------------------------------------ epilogue warps
     // warp q reads TMEM lanes 32 q .. 32 q + 31 = its 32 output rows, all columns of the tile
@@ -457,26 +479,43 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 #pragma unroll
             for (int e = 0; e < 8; ++e) f[e] += __ldg(&p.bias[n + e]);
           }
-          if (res) {
-            uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n));
-            const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float2 t = unpack2<T>(rw[e]);
-              f[2 * e] += t.x;
-              f[2 * e + 1] += t.y;
+          if constexpr (kTF32) {
+            float* yo = reinterpret_cast<float*>(y) + dst_row * p.cout + n;
+            if (res) {
+              const float* rp = reinterpret_cast<const float*>(res) + dst_row * p.cout + n;
+              const float4 ra = __ldg(reinterpret_cast<const float4*>(rp));
+              const float4 rb = __ldg(reinterpret_cast<const float4*>(rp) + 1);
+              f[0] += ra.x; f[1] += ra.y; f[2] += ra.z; f[3] += ra.w;
+              f[4] += rb.x; f[5] += rb.y; f[6] += rb.z; f[7] += rb.w;
             }
-          }
-          if (p.relu) {
+            if (p.relu) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
+              for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
+            }
+            reinterpret_cast<float4*>(yo)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(yo)[1] = make_float4(f[4], f[5], f[6], f[7]);
+          } else {
+            if (res) {
+              uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n));
+              const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float2 t = unpack2<T>(rw[e]);
+                f[2 * e] += t.x;
+                f[2 * e + 1] += t.y;
+              }
+            }
+            if (p.relu) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
+            }
+            uint4 o;
+            o.x = pack2<T>(f[0], f[1]);
+            o.y = pack2<T>(f[2], f[3]);
+            o.z = pack2<T>(f[4], f[5]);
+            o.w = pack2<T>(f[6], f[7]);
+            *reinterpret_cast<uint4*>(y + dst_row * p.cout + n) = o;
           }
-          uint4 o;
-          o.x = pack2<T>(f[0], f[1]);
-          o.y = pack2<T>(f[2], f[3]);
-          o.z = pack2<T>(f[4], f[5]);
-          o.w = pack2<T>(f[6], f[7]);
-          *reinterpret_cast<uint4*>(y + dst_row * p.cout + n) = o;
         }
       }
       // this warp is done with the accumulator buffer
@@ -505,6 +544,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       uint32_t mine = 0;
       int kk = (lane * 4) % p.kvol;                 // kernel offset of the first int of this lane's int4
       const int kstep = 128 % p.kvol;               // advance of that offset per loop trip (32 lanes x 4 ints)
+#pragma unroll 4
       for (int e = lane; e < n4; e += 32) {
         int4 v = __ldg(&src[e]);
         int* c = reinterpret_cast<int*>(&v);
@@ -527,109 +567,133 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       }
     }
   } else if (warp == kTmaWarp) {
-    // ------------------------------------------------------------ weight loader (B operand, one thread)
-    if (lane == 0) {
-      const uint32_t bytes = (uint32_t)b_bytes;
-      const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
-      uint32_t stage = 0, phase = 0;
-      bool first_pass = true;
-      int i = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
-        const int buf = i % p.ring;
-        const int n0 = (w % tiles_n) * p.n_tile;
-        if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
-          atomicExch(p.error, kErrSchedWait);
-          s_abort = 1;
-          break;
-        }
-        const uint32_t kmask = s_kmask[buf];
-        mbar_arrive(smem_u32(&s_sched_empty[buf]));
-        for (int k = 0; k < p.kvol && ok; ++k) {
-          if (!((kmask >> k) & 1u)) continue;
-          const int wrow = k * p.cout + n0;
-          for (int c = 0; c < chunks; ++c) {
-            if (!first_pass && !mbar_wait(empty0 + stage * 8, phase ^ 1u)) {
-              atomicExch(p.error, kErrEmptyWait);
-              s_abort = 1;
-              ok = false;
-              break;
-            }
-            const uint32_t bar = full0 + stage * 8;
-            mbar_arrive_expect_tx(bar, bytes);
-            tma_load_2d(smem_base + stage * (uint32_t)stage_bytes + kABytes, &w_map, bar, c * kChunkK, wrow);
-            if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+    // ------------------------------------------------------------ weight loader (B operand)
+    // the whole warp walks the blocks converged; one elected lane posts the byte count and issues the copy
+    const uint32_t bytes = (uint32_t)b_bytes;
+    const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+    uint32_t stage = 0, phase = 0;
+    bool first_pass = true;
+    int i = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
+      const int buf = i % p.ring;
+      const int n0 = (w % tiles_n) * p.n_tile;
+      if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
+        if (lane == 0) atomicExch(p.error, kErrSchedWait);
+        s_abort = 1;
+        break;
+      }
+      const uint32_t kmask = s_kmask[buf];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
+      if (s_abort) break;
+      for (int k = 0; k < p.kvol && ok; ++k) {
+        if (!((kmask >> k) & 1u)) continue;
+        const int wrow = k * p.cout + n0;
+        for (int c = 0; c < chunks; ++c) {
+          if (!first_pass && !mbar_wait(empty0 + stage * 8, phase ^ 1u)) {
+            if (lane == 0) atomicExch(p.error, kErrEmptyWait);
+            s_abort = 1;
+            ok = false;
+            break;
           }
+          const uint32_t bar = full0 + stage * 8;
+          if (elect_one()) {
+            mbar_arrive_expect_tx(bar, bytes);
+            tma_load_2d(smem_base + stage * (uint32_t)stage_bytes + kABytes, &w_map, bar, c * kChunk, wrow);
+          }
+          __syncwarp();
+          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
         }
       }
     }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------ MMA issuer (one thread)
-    // This thread's instruction stream is the critical path of the whole CTA: stage index, barrier
-    // phase and descriptors are carried incrementally (no division, no 64-bit arithmetic per block).
-    if (lane == 0) {
-      const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
-      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, SWIZZLE_128B
-      const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);  // stage 0, A operand
-      const uint32_t stage_units = (uint32_t)stage_bytes >> 4;
-      const uint32_t b_units = (uint32_t)kABytes >> 4;
-      const int last_steps = ((p.cin - (chunks - 1) * kChunkK) + 15) >> 4;
-      uint32_t stage = 0, phase = 0, a_lo = a_lo0;
-      int i = 0, acc_count = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
-        const int buf = i % p.ring;
-        const int n0 = (w % tiles_n) * p.n_tile;
-        const int n_mma = (min(p.n_tile, p.cout - n0) + 15) & ~15;
-        const uint32_t idesc = make_idesc(p.ab_format, n_mma);
-        if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
-          atomicExch(p.error, kErrSchedWait);
-          s_abort = 1;
-          break;
-        }
-        const uint32_t kmask = s_kmask[buf];
-        mbar_arrive(smem_u32(&s_sched_empty[buf]));
-        if (!kmask) continue;                                      // nothing to multiply: the epilogue writes zeros
-        // the epilogue must have drained this accumulator buffer (its previous use)
-        const int ab = acc_count & 1;
-        if (acc_count >= 2 && !mbar_wait(smem_u32(&s_acc_empty[ab]), ((acc_count >> 1) + 1) & 1)) {
-          atomicExch(p.error, kErrAccWait);
-          s_abort = 1;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t acc = tmem_base + (uint32_t)ab * acc_cols;
-        uint32_t accumulate = 0;
-        for (int k = 0; k < p.kvol && ok; ++k) {
-          if (!((kmask >> k) & 1u)) continue;
-          for (int c = 0; c < chunks; ++c) {
-            if (!mbar_wait(full0 + stage * 8, phase)) {
-              atomicExch(p.error, kErrFullWait);
-              s_abort = 1;
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const int steps = (c == chunks - 1) ? last_steps : (kChunkK >> 4);
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------ MMA issuer
+    // The instruction stream of this warp is on the critical path of the whole CTA: stage index,
+    // barrier phase and descriptors are carried incrementally (no division, no 64-bit arithmetic per
+    // block), and the warp stays converged so that they are warp-uniform values.
+    const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+    const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, SWIZZLE_128B
+    const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);  // stage 0, A operand
+    const uint32_t stage_units = (uint32_t)stage_bytes >> 4;
+    const uint32_t b_units = (uint32_t)kABytes >> 4;
+    const int last_steps = ((p.cin - (chunks - 1) * kChunk) + kStepK - 1) / kStepK;
+    uint32_t stage = 0, phase = 0, a_lo = a_lo0;
+    int i = 0, acc_count = 0;
+    bool ok = true;
+#ifdef TSB_TRACE_BUILD
+    int blk = 0;
+#endif
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
+      const int buf = i % p.ring;
+      const int n0 = (w % tiles_n) * p.n_tile;
+      const int n_mma = (min(p.n_tile, p.cout - n0) + 15) & ~15;
+      const uint32_t idesc = make_idesc(p.ab_format, n_mma);
+      if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
+        if (lane == 0) atomicExch(p.error, kErrSchedWait);
+        s_abort = 1;
+        break;
+      }
+      const uint32_t kmask = s_kmask[buf];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
+      if (s_abort) break;
+      if (!kmask) continue;                                      // nothing to multiply: the epilogue writes zeros
+      // the epilogue must have drained this accumulator buffer (its previous use)
+      const int ab = acc_count & 1;
+      if (acc_count >= 2 && !mbar_wait(smem_u32(&s_acc_empty[ab]), ((acc_count >> 1) + 1) & 1)) {
+        if (lane == 0) atomicExch(p.error, kErrAccWait);
+        s_abort = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t acc = tmem_base + (uint32_t)ab * acc_cols;
+      uint32_t accumulate = 0;
+      for (uint32_t km = kmask; km && ok; km &= km - 1) {       // one trip per offset present in the tile
+        for (int c = 0; c < chunks; ++c) {
+          if (lane == 0) TSB_TRACE_HOT(4, blk);
+          if (!mbar_wait(full0 + stage * 8, phase)) {
+            if (lane == 0) atomicExch(p.error, kErrFullWait);
+            s_abort = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (lane == 0) TSB_TRACE_HOT(5, blk);
+          const int steps = (c == chunks - 1) ? last_steps : 4;
+          if (elect_one()) {
             // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
-            for (int st = 0; st < steps; ++st) {
-              const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_lo + 2u * st);
-              const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (a_lo + b_units + 2u * st);
-              umma_f16(acc, a_desc, b_desc, idesc, accumulate);
-              accumulate = 1;
+#pragma unroll
+            for (int st = 0; st < 4; ++st) {
+              if (st < steps) {
+                const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_lo + 2u * st);
+                const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (a_lo + b_units + 2u * st);
+                umma<kTF32>(acc, a_desc, b_desc, idesc, (st == 0) ? accumulate : 1u);
+              }
             }
             umma_commit(empty0 + stage * 8);
-            a_lo += stage_units;
-            if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
           }
+          __syncwarp();
+          accumulate = 1;
+#ifdef TSB_TRACE_BUILD
+          if (lane == 0) TSB_TRACE_HOT(6, blk);
+          ++blk;
+#endif
+          a_lo += stage_units;
+          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
         }
-        umma_commit(smem_u32(&s_acc_full[ab]));   // also on the error path: ends the epilogue's bounded wait early
-        ++acc_count;
       }
+      // also on the error path: ends the epilogue's bounded wait early
+      if (elect_one()) umma_commit(smem_u32(&s_acc_full[ab]));
+      __syncwarp();
+      ++acc_count;
     }
-    __syncwarp();
     tc_fence_before();
+  }
+  // A CTA that gave up may still have copies in flight towards its shared memory: give them time
+  // to land (bounded) before the CTA's resources are released.
+  if (s_abort) {
+    for (int t = 0; t < 1000; ++t) __nanosleep(1000);
   }
   __syncthreads();
   if (warp == kMmaWarp) {
@@ -677,14 +741,11 @@ size_t smem_bytes_for(int n_tile, int stages, int kvol, int ring) {
   return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)ring * kTileM * kvol * sizeof(int);
 }
 
-// Stage counts are restricted to {2,3,4,6,8} so that the number of gather groups (2,3,4,3,4) divides
-// them: a group then always refills the same stages.
-int usable_stages(int s) { return s >= 8 ? 8 : s >= 6 ? 6 : s >= 4 ? 4 : s; }
-int groups_for(int stages) { return stages == 2 ? 2 : (stages == 3 || stages == 6) ? 3 : 4; }
+int usable_stages(int s) { return s > kMaxStages ? kMaxStages : s; }
 
 // Two persistent CTAs per SM when two double-buffered accumulators fit TMEM (N tile <= 128 columns)
-// and three stages fit half the shared memory: two MMA issuers and 16 gather warps per SM hide the
-// per-block latency of the narrow layers.  Otherwise one CTA per SM with as many stages as fit.
+// and three stages fit half the shared memory: two MMA issuers per SM hide the per-block latency
+// of the narrow layers.  Otherwise one CTA per SM with as many stages as fit.
 void pick_config(int n_tile, int kvol, int* stages, int* ring, int* ctas) {
   int acc_cols = 32;
   while (acc_cols < n_tile) acc_cols <<= 1;
@@ -724,8 +785,14 @@ int pick_n_tile(int cout) {
 bool igemm_umma_supported(const IgemmArgs& a) {
   if (!tensor_map_encoder()) return false;
   if ((a.kvol * kTileM) % 4 || ((uintptr_t)a.map & 15)) return false;
-  if (a.dtype != TSB_F16 && a.dtype != TSB_BF16) return false;
-  if (a.cin % 8 || a.cout % 8) return false;        // 16-byte granules of rows
+  if (a.dtype == TSB_F32) {
+    if (a.math != TSB_MATH_TF32) return false;       // exact fp32 stays on the CUDA cores
+  } else if (a.dtype != TSB_F16 && a.dtype != TSB_BF16) {
+    return false;
+  }
+  // feature rows must be 16-byte multiples (tensor-map stride); outputs are written in 8-channel groups
+  if ((a.cin * (int)dtype_size(a.dtype)) % 16 || a.cout % 8) return false;
+  if (a.n_in >= (int64_t)INT32_MAX || a.n_out >= (int64_t)INT32_MAX) return false;
   if (a.kvol > kMaxKvolUmma) return false;
   if (((uintptr_t)a.x | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual | (uintptr_t)a.packed_w) & 15)
     return false;
@@ -739,7 +806,6 @@ size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype) {
 }
 
 size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype) {
-  if (dtype == TSB_F32) return 256;
   return packed_weight_bytes(kvol, cin, cout, dtype) + 256;   // packed weights + error word
 }
 
@@ -775,7 +841,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     wt = reinterpret_cast<const T*>(a.workspace);
   }
   UmmaParams p;
-  p.x = a.x; p.wt = wt; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
+  p.x = a.x; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
   p.residual = a.residual; p.error = err;
   p.trace = nullptr; p.trace_cta = 0;
   if (const char* tr = getenv("TSB_UMMA_TRACE")) {   // debugging aid: address of a 256x8 int64 device buffer
@@ -786,27 +852,29 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   p.n_tile = pick_n_tile(a.cout);
   int ctas = 1;
   pick_config(p.n_tile, a.kvol, &p.stages, &p.ring, &ctas);
-  p.groups = groups_for(p.stages);
   p.relu = a.relu;
-  p.ab_format = (a.dtype == TSB_BF16) ? 1 : 0;
+  p.ab_format = (a.dtype == TSB_BF16) ? kFmtBF16 : (a.dtype == TSB_F32) ? kFmtTF32 : kFmtF16;
   const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol, p.ring);
-  static bool attr_set[2] = {false, false};
-  const int ti = (a.dtype == TSB_BF16) ? 1 : 0;
+  static bool attr_set[3] = {false, false, false};
+  const int ti = p.ab_format;
   if (!attr_set[ti]) {
     TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr_set[ti] = true;
   }
   CUtensorMap w_map;
   {
-    // packed weights as a 2-D tensor [kvol * cout rows, cin columns]; box = 64 columns x n_tile rows
     auto encode = tensor_map_encoder();
     if (!encode) return TSB_ERR_UNSUPPORTED;
+    const CUtensorMapDataType dt = a.dtype == TSB_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                   : a.dtype == TSB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const cuuint32_t chunk = (cuuint32_t)(kRowBytes / sizeof(T));
+    cuuint32_t estride[2] = {1, 1};
+    // packed weights as a 2-D tensor [kvol * cout rows, cin columns]; box = 128 bytes of columns x n_tile rows
     cuuint64_t gdim[2] = {(cuuint64_t)a.cin, (cuuint64_t)a.kvol * (cuuint64_t)a.cout};
     cuuint64_t gstride[1] = {(cuuint64_t)a.cin * sizeof(T)};
-    cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)p.n_tile};
-    cuuint32_t estride[2] = {1, 1};
-    CUresult r = encode(&w_map, a.dtype == TSB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                        2, const_cast<T*>(wt), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    cuuint32_t box[2] = {chunk, (cuuint32_t)p.n_tile};
+    CUresult r = encode(&w_map, dt, 2, const_cast<T*>(wt), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
@@ -824,6 +892,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
 int igemm_umma(const IgemmArgs& a, cudaStream_t s) {
   if (a.dtype == TSB_F16) return umma_launch<__half>(a, s);
   if (a.dtype == TSB_BF16) return umma_launch<__nv_bfloat16>(a, s);
+  if (a.dtype == TSB_F32 && a.math == TSB_MATH_TF32) return umma_launch<float>(a, s);
   return TSB_ERR_UNSUPPORTED;
 }
 
