@@ -220,6 +220,8 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     n_streams = max(1, args.streams)
     side = [torch.cuda.Stream(device) for _ in range(n_streams)] if n_streams > 1 else [stream]
 
+    host_ms = {"issue": float("nan")}   # host wall time per step spent issuing the step (no final sync)
+
     def timed(e2e: bool, observe: bool):
         with torch.no_grad():
             for i in range(args.warmup):
@@ -230,6 +232,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
             launches0 = backend.launch_count()
             backend.set_launch_observer(observer if observe else None)
             h2d = d2h = 0
+            t_host0 = time.perf_counter()
             if n_streams == 1:
                 for i in range(args.steps):
                     flush.fill_(i & 0xFF)       # evict L2 between steps (outside the timed events)
@@ -260,6 +263,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                     stream.wait_event(done)
                 e1.record(stream)
                 evs.append((e0, e1))
+            host_ms["issue"] = (time.perf_counter() - t_host0) * 1e3 / max(1, args.steps)
             backend.set_launch_observer(None)
             barrier()
             launches = backend.launch_count() - launches0
@@ -271,6 +275,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
 
     sampler = ClockSampler(device.index or 0) if rank == 0 else None
     ms_total, launches, _, _ = timed(False, True)
+    host_issue_ms = host_ms["issue"]
     clocks = sampler.stop() if sampler else None
     e2e_ms, h2d, d2h = float("nan"), 0, 0
     if not args.no_e2e:
@@ -333,6 +338,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(launches),
+        "host_issue_ms_per_step": round(host_issue_ms, 4),
         "clocks": clocks,
         "roofline": roof,
     }

@@ -53,7 +53,21 @@ def launch_count() -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    # raw handle of torch's current stream on the current device (torch.cuda.current_stream() builds a
+    # Stream object and costs ~15 us per call, which adds up over the launches of a network)
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
+
+
+_status_words = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """One persistent int32 status word per device for launches whose status nobody reads back
+    (the kernels only ever write non-zero error codes into it)."""
+    w = _status_words.get(device)
+    if w is None:
+        w = _status_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return w
 
 
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -414,7 +428,6 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
         raise ValueError("out_in_map shape does not match kernel volume / output rows")
     out = torch.empty((num_out_feats, cout), dtype=in_feats.dtype, device=in_feats.device)
     code = _dtype_code(in_feats)
-    ws = _workspace(lib.tsb_conv_igemm_workspace_bytes(kvol, cin, cout, code), in_feats.device)
     if bias is not None:
         bias = bias.float().contiguous()
     if scale is not None:
@@ -422,7 +435,13 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     if residual is not None:
         residual = residual.to(in_feats.dtype).contiguous()
     packed = _packed_weight(kernel, code, bool(allow_tf32)) if cache_packed_weights else None
-    status = torch.zeros(1, dtype=torch.int32, device=in_feats.device) if check_kernel_status else None
+    if check_kernel_status:
+        status = torch.zeros(1, dtype=torch.int32, device=in_feats.device)
+    else:
+        status = _status_word(in_feats.device)
+    # with packed weights and a status word supplied the kernel needs no workspace
+    ws = None if packed is not None else _workspace(lib.tsb_conv_igemm_workspace_bytes(kvol, cin, cout, code),
+                                                    in_feats.device)
     if _observer is not None:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
@@ -430,11 +449,12 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
                                  in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
                                  _math_mode(in_feats, allow_tf32), _p(scale), _p(bias), _p(residual), int(relu),
                                  _p(status),
-                                 _p(ws), ws.numel(), _stream()), "conv_forward_implicit_gemm_cuda")
+                                 _p(ws), 0 if ws is None else ws.numel(), _stream()),
+          "conv_forward_implicit_gemm_cuda")
     if _observer is not None:
         ev1.record()
         _observer("igemm", (in_feats.shape[0], num_out_feats, kvol, cin, cout, code, out_in_map), ev0, ev1)
-    if status is not None and int(status.item()) != 0:
+    if check_kernel_status and int(status.item()) != 0:
         raise RuntimeError(f"conv_forward_implicit_gemm_cuda: a bounded wait inside the kernel ran out "
                            f"(code {int(status.item())}); the output is undefined")
     return out

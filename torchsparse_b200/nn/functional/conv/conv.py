@@ -153,9 +153,8 @@ def conv3d(
         out_feats += bias
     if epilogue is not None and not fused:
         out_feats = _epilogue_torch(out_feats, epilogue)
-    output = SparseTensor(coords=out_coords, feats=out_feats, stride=out_stride, spatial_range=out_range)
-    output._caches = caches
-    caches.cmaps.setdefault(output.stride, (output.coords, output.spatial_range))
+    output = SparseTensor._from_parts(out_feats, out_coords, out_stride, out_range, caches)
+    caches.cmaps.setdefault(out_stride, (out_coords, out_range))
     return output
 
 

@@ -21,7 +21,9 @@ from typing import Dict, Optional
 import torch
 from torch import nn
 
+from .. import backend, backends
 from ..tensor import SparseTensor
+from ..utils.utils import make_ntuple
 from . import functional as F
 from .functional.conv import conv as _conv_impl
 from .modules.activation import ReLU
@@ -56,8 +58,9 @@ class FusedConv(nn.Module):
     def __init__(self, conv: Conv3d, bn: Optional[nn.BatchNorm1d] = None, relu: bool = False) -> None:
         super().__init__()
         assert not conv.generative
-        self.kernel_size, self.stride, self.padding = conv.kernel_size, conv.stride, conv.padding
-        self.dilation, self.transposed, self._config = conv.dilation, conv.transposed, conv._config
+        self.kernel_size, self.stride = make_ntuple(conv.kernel_size, 3), make_ntuple(conv.stride, 3)
+        self.padding, self.dilation = conv.padding, make_ntuple(conv.dilation, 3)
+        self.transposed, self._config = conv.transposed, conv._config
         self.in_channels, self.out_channels = conv.in_channels, conv.out_channels
         self.relu = relu
         self.kernel = nn.Parameter(conv.kernel.detach(), requires_grad=False)
@@ -102,12 +105,47 @@ class FusedConv(nn.Module):
                 out = out + residual
             if self.relu:
                 out = torch.relu_(out)
-            y = SparseTensor(out, x.coords, x.stride, x.spatial_range)
-            y._caches = x._caches
+            return SparseTensor._from_parts(out, x.coords, x.stride, x.spatial_range, x._caches)
+        layer_config = self._layer_config(x)
+        y = self._forward_cached_map(x, residual, layer_config)
+        if y is not None:
             return y
         return F.conv3d(x, self.kernel, self.kernel_size, None, self.stride, self.padding, self.dilation,
-                        self._layer_config(x), self.transposed, False, False,
+                        layer_config, self.transposed, False, False,
                         epilogue={"scale": self.scale, "bias": self.shift, "residual": residual, "relu": self.relu})
+
+    def _forward_cached_map(self, x: SparseTensor, residual, layer_config) -> Optional[SparseTensor]:
+        """Short path for the common case of a network's inner layers: unsorted implicit GEMM on a
+        kernel map that is already in the tensor's cache (built by an earlier layer of the level or by
+        the engine's prebuild).  Same launch as F.conv3d makes, without its per-call bookkeeping;
+        returns None when the case does not apply."""
+        config = _conv_impl.resolve_config(layer_config)
+        if config["dataflow"] != F.Dataflow.ImplicitGEMM or config["ifsort"]:
+            return None
+        feats = x.feats
+        if feats.dtype != self.kernel.dtype or not feats.is_cuda:
+            return None
+        caches = x._caches
+        if self.transposed:
+            out_stride = tuple(a // b for a, b in zip(x.stride, self.stride))
+            kmap = caches.kmaps.get((out_stride, self.kernel_size, self.stride, self.dilation))
+            target = caches.cmaps.get(out_stride)
+            if kmap is None or target is None or kmap.get("out_in_map_t") is None:
+                return None
+            out_in_map, n_out = kmap["out_in_map_t"], kmap["sizes"][0]
+            out_coords, out_range = target
+        else:
+            kmap = caches.kmaps.get((x.stride, self.kernel_size, self.stride, self.dilation))
+            if kmap is None:
+                return None
+            out_in_map, n_out = kmap["out_in_map"], kmap["sizes"][1]
+            out_coords, out_range = kmap["coords"], kmap["spatial_range"]
+            out_stride = tuple(a * b for a, b in zip(x.stride, self.stride))
+        out = backend.conv_forward_implicit_gemm_cuda(
+            feats, self.kernel, out_in_map, n_out, self.out_channels, backends.allow_tf32, backends.allow_fp16,
+            scale=self.scale, bias=self.shift, residual=residual, relu=self.relu)
+        caches.cmaps.setdefault(out_stride, (out_coords, out_range))
+        return SparseTensor._from_parts(out, out_coords, out_stride, out_range, caches)
 
     def extra_repr(self) -> str:
         return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, stride={self.stride}, "

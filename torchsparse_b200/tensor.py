@@ -45,6 +45,16 @@ class SparseTensor:
             self._caches.cbounds[self.stride] = (tuple(int(v) for v in coord_bounds[0]),
                                                  tuple(int(v) for v in coord_bounds[1]))
 
+    @classmethod
+    def _from_parts(cls, feats: torch.Tensor, coords: torch.Tensor, stride: Tuple[int, ...], spatial_range,
+                    caches) -> "SparseTensor":
+        """The output of a layer: stride and range are already canonical tuples and the cache is the
+        input's, so nothing is validated or created."""
+        self = cls.__new__(cls)
+        self.feats, self.coords, self.stride, self.spatial_range, self._caches = (feats, coords, stride,
+                                                                                 spatial_range, caches)
+        return self
+
     @property
     def F(self) -> torch.Tensor:
         return self.feats

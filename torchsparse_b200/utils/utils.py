@@ -9,6 +9,8 @@ __all__ = ["make_ntuple", "make_tensor", "make_divisible"]
 
 def make_ntuple(x: Union[int, List[int], Tuple[int, ...], torch.Tensor], ndim: int) -> Tuple[int, ...]:
     """int / list / tuple / tensor -> tuple of ``ndim`` ints (torchsparse/utils/utils.py:9-21)."""
+    if type(x) is tuple and len(x) == ndim and all(type(v) is int for v in x):
+        return x
     if isinstance(x, int):
         x = tuple(repeat(x, ndim))
     elif isinstance(x, torch.Tensor):
