@@ -460,6 +460,61 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     return out
 
 
+class IgemmLayerPlan:
+    """The arguments of tsb_conv_igemm_fwd that do not change between calls of one inference layer
+    (weights, packed weights, fp32 scale / shift, sizes), resolved once.  ``launch`` then costs one
+    output allocation and one foreign call; argument checks happened when the plan was made.  The
+    plan keeps the tensors alive and is remade when the weights are replaced or modified."""
+
+    __slots__ = ("kernel", "packed", "scale", "bias", "tag", "args_head", "args_tail", "cout", "dtype", "device")
+
+    def __init__(self, kernel: torch.Tensor, scale: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                 relu: bool, allow_tf32: bool):
+        _need_cuda(kernel)
+        if kernel.dim() != 3:
+            raise ValueError("kernel must be [Kvol, Cin, Cout]")
+        kernel = kernel.contiguous()
+        kvol, cin, cout = kernel.shape
+        code = _dtype_code(kernel)
+        if kernel.dtype != torch.float32 and cin % 8 != 0:
+            raise ValueError("IgemmLayerPlan needs feature rows that are 16-byte multiples")
+        self.tag = (kernel._version, kernel.data_ptr(), bool(allow_tf32))
+        self.kernel = kernel
+        self.packed = _packed_weight(kernel, code, bool(allow_tf32))
+        self.scale = None if scale is None else scale.float().contiguous()
+        self.bias = None if bias is None else bias.float().contiguous()
+        self.cout, self.dtype, self.device = cout, kernel.dtype, kernel.device
+        math = _lib.TSB_MATH_TF32 if (kernel.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
+        self.args_head = (kernel.data_ptr(), _p(self.packed))
+        self.args_tail = (kvol, cin, cout, code, math, _p(self.scale), _p(self.bias))
+
+    def valid_for(self, kernel: torch.Tensor, allow_tf32: bool) -> bool:
+        return self.tag == (kernel._version, kernel.data_ptr(), bool(allow_tf32))
+
+
+def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: torch.Tensor, num_out_feats: int,
+                      residual: Optional[torch.Tensor], relu: bool) -> torch.Tensor:
+    """conv_forward_implicit_gemm_cuda for a layer with an :class:`IgemmLayerPlan` (same kernel launch).
+    Falls back to the checked entry point when launches are being observed or their status read back."""
+    if _observer is not None or check_kernel_status or plan.packed is None:
+        return conv_forward_implicit_gemm_cuda(in_feats, plan.kernel, out_in_map, num_out_feats, plan.cout,
+                                               plan.tag[2], True, scale=plan.scale, bias=plan.bias,
+                                               residual=residual, relu=relu)
+    if in_feats.dtype != plan.dtype or not in_feats.is_contiguous() or in_feats.shape[1] != plan.args_tail[1]:
+        raise ValueError("input features do not match the layer plan (dtype, layout or channel count)")
+    if residual is not None and (residual.dtype != plan.dtype or not residual.is_contiguous()):
+        residual = residual.to(plan.dtype).contiguous()
+    out = torch.empty((num_out_feats, plan.cout), dtype=plan.dtype, device=plan.device)
+    rc = lib.tsb_conv_igemm_fwd(in_feats.data_ptr(), plan.args_head[0], plan.args_head[1], out_in_map.data_ptr(),
+                                None, out.data_ptr(), in_feats.shape[0], num_out_feats, *plan.args_tail,
+                                None if residual is None else residual.data_ptr(), int(relu),
+                                _status_word(plan.device).data_ptr(), None, 0,
+                                torch._C._cuda_getCurrentRawStream(plan.device.index))
+    if rc != 0:
+        check(rc, "conv_forward_implicit_gemm_cuda")
+    return out
+
+
 def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,
                                            reduced_mask: torch.Tensor, reorder_loc: torch.Tensor, num_out_feats: int,
                                            num_out_channels: int, allow_tf32: bool = False,

@@ -73,6 +73,7 @@ class FusedConv(nn.Module):
             self.register_buffer("shift_lp", shift.to(self.kernel.dtype))
         self.register_buffer("scale", scale)
         self.register_buffer("shift", shift)
+        self._plan = None      # per-layer constant launch arguments, made on first use
 
     def _apply(self, fn, recurse=True):
         # keep the folded scale / shift in fp32 under .half() / .to(dtype)
@@ -80,6 +81,7 @@ class FusedConv(nn.Module):
         super()._apply(fn, recurse)
         self.scale = scale.to(self.kernel.device).float()
         self.shift = shift.to(self.kernel.device).float()
+        self._plan = None
         return self
 
     # set by InferenceEngine: layers whose input (output, for transposed convs) tensor stride is at most
@@ -141,9 +143,13 @@ class FusedConv(nn.Module):
             out_in_map, n_out = kmap["out_in_map"], kmap["sizes"][1]
             out_coords, out_range = kmap["coords"], kmap["spatial_range"]
             out_stride = tuple(a * b for a, b in zip(x.stride, self.stride))
-        out = backend.conv_forward_implicit_gemm_cuda(
-            feats, self.kernel, out_in_map, n_out, self.out_channels, backends.allow_tf32, backends.allow_fp16,
-            scale=self.scale, bias=self.shift, residual=residual, relu=self.relu)
+        if feats.shape[1] % 8 != 0 or not feats.is_contiguous():
+            return None     # the 4-channel input layer is padded by the general entry point
+        plan = self._plan
+        if plan is None or not plan.valid_for(self.kernel, backends.allow_tf32):
+            plan = self._plan = backend.IgemmLayerPlan(self.kernel, self.scale, self.shift, self.relu,
+                                                       backends.allow_tf32)
+        out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu)
         caches.cmaps.setdefault(out_stride, (out_coords, out_range))
         return SparseTensor._from_parts(out, out_coords, out_stride, out_range, caches)
 
@@ -168,8 +174,19 @@ class FusedResBlock(nn.Module):
             self.shortcut = FusedConv(sc[0], sc[1], relu=False)
 
     def forward(self, x: SparseTensor) -> SparseTensor:
-        res = x.feats if self.shortcut is None else self.shortcut(x).feats
-        return self.conv2(self.conv1(x), residual=res)
+        # the fused modules carry no hooks: their forward methods are called directly
+        res = x.feats if self.shortcut is None else self.shortcut.forward(x).feats
+        return self.conv2.forward(self.conv1.forward(x), residual=res)
+
+
+class _FusedSequential(nn.Sequential):
+    """nn.Sequential whose fused members are run through their forward methods directly (no hook
+    dispatch per layer: at batch 1 the host, not the GPU, paces a forward pass)."""
+
+    def forward(self, x):
+        for m in self._modules.values():
+            x = m.forward(x) if type(m) in _DIRECT else m(x)
+        return x
 
 
 def _fuse_sequential(seq: nn.Sequential) -> nn.Sequential:
@@ -187,7 +204,10 @@ def _fuse_sequential(seq: nn.Sequential) -> nn.Sequential:
         else:
             out.append(fuse_for_inference(m))
             i += 1
-    return nn.Sequential(*out)
+    return _FusedSequential(*out)
+
+
+_DIRECT = (FusedConv, FusedResBlock)
 
 
 def fuse_for_inference(model: nn.Module) -> nn.Module:
