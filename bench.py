@@ -40,6 +40,7 @@ VOXEL = 0.05
 NUM_CLASSES = 19
 METRIC = "minkunet_fp16_scans_per_sec"
 SCAN_POOL = 4          # distinct scans rotated through the timed steps
+MAX_VOXELS = 144_000   # upper bound of the voxels of one scan (every point its own voxel): row bound of the output gather
 L2_FLUSH_BYTES = 256 << 20
 
 
@@ -173,6 +174,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     import torch.distributed as dist
     import torchsparse_b200  # noqa: F401  (fails loudly when libtsb200.so is missing)
     from torchsparse_b200 import backend
+    from torchsparse_b200.sharding import gather_rows_padded
 
     from torchsparse_b200.nn import functional as F
     F.set_conv_mode(args.conv_mode)
@@ -188,12 +190,14 @@ def run_ours(args, rank: int, world: int, device: torch.device):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step(i, e2e: bool):
+    def step(i, e2e: bool, gather_inline: bool = True):
         h = host[i % SCAN_POOL]
         pts = h.to(device, non_blocking=True) if e2e else resident[i % SCAN_POOL]
-        logits = forward_scan(model, pts)      # scans are independent: ranks exchange nothing on the data path
+        logits = forward_scan(model, pts)      # scans are independent: the only exchange is the gather of outputs
+        if world > 1 and gather_inline:
+            gather_rows_padded(logits, MAX_VOXELS)
         out = logits.cpu() if e2e else logits
-        return out, h.numel() * h.element_size(), (logits.numel() * logits.element_size() if e2e else 0)
+        return logits, h.numel() * h.element_size(), (logits.numel() * logits.element_size() if e2e else 0)
 
     # useful-FLOP bookkeeping: the number of valid (row, offset) pairs of every conv launch of every
     # pooled scan, taken in an untimed pass (the timed pass must not keep maps alive or sync)
@@ -219,6 +223,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     # host threads that issue scans (each on its own stream); collectives of a sharded run stay on one thread
     n_threads = max(1, min(args.host_threads, n_streams))
     side = [torch.cuda.Stream(device) for _ in range(n_streams)] if n_streams > 1 else [stream]
+    comm_stream = torch.cuda.Stream(device) if world > 1 else None
 
     host_ms = {"issue": float("nan")}   # host wall time per step spent issuing the step (no final sync)
 
@@ -226,7 +231,12 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         with torch.no_grad():
             for i in range(args.warmup):
                 with torch.cuda.stream(side[i % n_streams]):
-                    step(i, e2e)
+                    logits, _, _ = step(i, e2e, gather_inline=False)
+                if world > 1:       # the gather runs where the timed loop runs it
+                    comm_stream.wait_stream(side[i % n_streams])
+                    with torch.cuda.stream(comm_stream):
+                        logits.record_stream(comm_stream)
+                        gather_rows_padded(logits, MAX_VOXELS)
             barrier()
             evs = []
             launches0 = backend.launch_count()
@@ -252,28 +262,57 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                 for s in side:
                     s.wait_event(e0)
                 io_bytes = {}
+                # sharded runs: the issuing threads hand each step's logits to this (main) thread, which
+                # alone talks to NCCL, in step order on every rank, on a stream of its own
+                outputs = [None] * args.steps
+                ready = [threading.Event() for _ in range(args.steps)]
 
                 def issue(first, stride):
+                    torch.cuda.set_device(device)    # the current device is per thread (a new thread starts on 0)
                     with torch.no_grad():
                         for i in range(first, args.steps, stride):
                             with torch.cuda.stream(side[i % n_streams]):
                                 flush.fill_(i & 0xFF)
                                 cur.step, cur.k = i, 0
-                                _, bi, bo = step(i, e2e)
+                                logits, bi, bo = step(i, e2e, gather_inline=False)
                                 io_bytes["h2d"], io_bytes["d2h"] = bi, bo
+                                if world > 1:
+                                    produced = torch.cuda.Event()
+                                    produced.record()
+                                    outputs[i] = (logits, produced)
+                            ready[i].set()
+                            if os.environ.get("TSB_BENCH_DEBUG"):
+                                sys.stderr.write(f"[dbg rank {rank}] issued step {i} at {(time.perf_counter() - t_host0) * 1e3:.2f} ms\n")
+
+                def gather_outputs():
+                    for i in range(args.steps):
+                        if not ready[i].wait(timeout=300) or outputs[i] is None:
+                            raise RuntimeError(f"step {i} produced no output (an issuing thread failed)")
+                        logits, produced = outputs[i]
+                        outputs[i] = None
+                        comm_stream.wait_event(produced)
+                        with torch.cuda.stream(comm_stream):
+                            logits.record_stream(comm_stream)
+                            gather_rows_padded(logits, MAX_VOXELS)
+                        if os.environ.get("TSB_BENCH_DEBUG"):
+                            sys.stderr.write(f"[dbg rank {rank}] gathered step {i} at {(time.perf_counter() - t_host0) * 1e3:.2f} ms\n")
 
                 if n_threads == 1:
                     issue(0, 1)
+                    if world > 1:
+                        gather_outputs()
                 else:
                     # thread t issues scans t, t + T, ... on stream t: the Python part of one scan overlaps
                     # the native part (launch calls, allocator) of another
                     workers = [threading.Thread(target=issue, args=(t, n_threads)) for t in range(n_threads)]
                     for wk in workers:
                         wk.start()
+                    if world > 1:
+                        gather_outputs()
                     for wk in workers:
                         wk.join()
                 h2d, d2h = io_bytes.get("h2d", 0), io_bytes.get("d2h", 0)
-                for s in side:
+                for s in side + ([comm_stream] if world > 1 else []):
                     done = torch.cuda.Event()
                     done.record(s)
                     stream.wait_event(done)
@@ -357,7 +396,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                    "streams": n_streams, "host_threads": n_threads,
                    "conv_mode": args.conv_mode, "fused_inference_engine": not args.unfused,
                    "sort_max_stride": args.sort_max_stride,
-                   "parallelism": f"scan-sharded x{world}, no data-path collective" if world > 1 else "single GPU"},
+                   "parallelism": f"scan-sharded x{world}, NCCL all-gather of the logits of every step" if world > 1 else "single GPU"},
         "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(launches),

@@ -6,7 +6,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from torchsparse_b200.sharding import balanced_assignment, gather_rows, shard_range
+from torchsparse_b200.sharding import balanced_assignment, gather_rows, gather_rows_padded, shard_range
 
 
 def test_shard_range_covers_everything_once():
@@ -51,6 +51,9 @@ def _worker(rank, world, port, q):
         local2 = torch.zeros((0 if rank == 0 else 2, 4))
         out2, counts2 = gather_rows(local2)
         q.put((rank, out2.clone(), counts2, None))
+        # the variant with a known row bound: same rows, counts stay a tensor, no host read inside
+        buf, cnt = gather_rows_padded(local, 8)
+        q.put((rank, buf.clone(), cnt.tolist(), "padded"))
     finally:
         dist.destroy_process_group()
 
@@ -63,10 +66,12 @@ def test_gather_rows_two_gloo_ranks():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=120) for _ in range(2 * world)]
+    results = [q.get(timeout=120) for _ in range(3 * world)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
+    padded = [r for r in results if r[3] == "padded"]
+    results = [r for r in results if r[3] != "padded"]
     first = [r for r in results if r[3] is not None]
     second = [r for r in results if r[3] is None]
     expect = torch.cat([torch.arange(12, dtype=torch.float32).reshape(3, 4),
@@ -77,3 +82,7 @@ def test_gather_rows_two_gloo_ranks():
         assert rng == ((0, 5) if rank == 0 else (5, 10))
     for rank, out, counts, _ in second:
         assert counts == [0, 2] and out.shape == (2, 4)
+    assert len(padded) == world
+    for rank, buf, counts, _ in padded:
+        assert counts == [3, 5] and buf.shape == (2, 8, 4)
+        assert torch.equal(torch.cat([buf[0, :3], buf[1, :5]]), expect)

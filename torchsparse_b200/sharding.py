@@ -8,7 +8,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "balanced_assignment", "gather_rows"]
+__all__ = ["shard_range", "balanced_assignment", "gather_rows", "gather_rows_padded"]
 
 
 def shard_range(n_items: int, world_size: int, rank: int) -> Tuple[int, int]:
@@ -54,3 +54,26 @@ def gather_rows(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) 
     dist.all_gather_into_tensor(buf, padded.contiguous(), group=group)
     parts = [buf[r * mx: r * mx + counts_host[r]] for r in range(world)]
     return torch.cat(parts, 0), counts_host
+
+
+def gather_rows_padded(local: torch.Tensor, max_rows: int, group: Optional[dist.ProcessGroup] = None
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """All-gather for a caller that knows an upper bound of the per-rank row count: no host read.
+    Returns (buffer [world, max_rows, C] whose slice [r, :counts[r]] holds rank r's rows, counts as
+    an int64 device tensor [world]).  Rows beyond a rank's count are unspecified.  Two collectives
+    queued on the current stream; nothing waits for the device."""
+    if local.shape[0] > max_rows:
+        raise ValueError(f"{local.shape[0]} rows exceed max_rows={max_rows}")
+    n = torch.tensor([local.shape[0]], dtype=torch.int64).to(local.device, non_blocking=True)
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        buf = torch.empty((1, max_rows) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        buf[0, : local.shape[0]] = local
+        return buf, n
+    world = dist.get_world_size(group)
+    counts = torch.empty(world, dtype=torch.int64, device=local.device)
+    dist.all_gather_into_tensor(counts, n, group=group)
+    padded = torch.empty((max_rows,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    padded[: local.shape[0]] = local
+    buf = torch.empty((world, max_rows) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(buf.view((world * max_rows,) + tuple(local.shape[1:])), padded, group=group)
+    return buf, counts
