@@ -227,16 +227,67 @@ def run_ours(args, rank: int, world: int, device: torch.device):
 
     host_ms = {"issue": float("nan")}   # host wall time per step spent issuing the step (no final sync)
 
+    def pipelined(n_steps: int, e2e: bool, n_streams: int, n_threads: int):
+        """n_steps scans, consecutive ones on alternating streams, issued by n_threads host threads (thread t
+        issues scans t, t + T, ... : the Python part of one scan overlaps the native part -- launch calls,
+        allocator, readbacks -- of another).  In a sharded run the issuing threads hand each step's logits to
+        the calling (main) thread, which alone talks to NCCL, in step order on every rank, on its own stream."""
+        io_bytes = {}
+        outputs = [None] * n_steps
+        ready = [threading.Event() for _ in range(n_steps)]
+        t0 = time.perf_counter()
+
+        def issue(first, stride):
+            torch.cuda.set_device(device)    # the current device is per thread (a new thread starts on 0)
+            with torch.no_grad():
+                for i in range(first, n_steps, stride):
+                    with torch.cuda.stream(side[i % n_streams]):
+                        flush.fill_(i & 0xFF)
+                        cur.step, cur.k = i, 0
+                        logits, bi, bo = step(i, e2e, gather_inline=False)
+                        io_bytes["h2d"], io_bytes["d2h"] = bi, bo
+                        if world > 1:
+                            produced = torch.cuda.Event()
+                            produced.record()
+                            outputs[i] = (logits, produced)
+                    ready[i].set()
+                    if os.environ.get("TSB_BENCH_DEBUG"):
+                        sys.stderr.write(f"[dbg rank {rank}] issued step {i} at {(time.perf_counter() - t0) * 1e3:.2f} ms\n")
+
+        def gather_outputs():
+            for i in range(n_steps):
+                if not ready[i].wait(timeout=300) or outputs[i] is None:
+                    raise RuntimeError(f"step {i} produced no output (an issuing thread failed)")
+                logits, produced = outputs[i]
+                outputs[i] = None
+                comm_stream.wait_event(produced)
+                with torch.cuda.stream(comm_stream):
+                    logits.record_stream(comm_stream)
+                    gather_rows_padded(logits, MAX_VOXELS)
+
+        if n_threads == 1:
+            issue(0, 1)
+            if world > 1:
+                gather_outputs()
+        else:
+            workers = [threading.Thread(target=issue, args=(t, n_threads)) for t in range(n_threads)]
+            for wk in workers:
+                wk.start()
+            if world > 1:
+                gather_outputs()
+            for wk in workers:
+                wk.join()
+        return io_bytes.get("h2d", 0), io_bytes.get("d2h", 0)
+
     def timed(e2e: bool, observe: bool, n_streams: int = n_streams, n_threads: int = n_threads):
         with torch.no_grad():
-            for i in range(args.warmup):
-                with torch.cuda.stream(side[i % n_streams]):
-                    logits, _, _ = step(i, e2e, gather_inline=False)
-                if world > 1:       # the gather runs where the timed loop runs it
-                    comm_stream.wait_stream(side[i % n_streams])
-                    with torch.cuda.stream(comm_stream):
-                        logits.record_stream(comm_stream)
-                        gather_rows_padded(logits, MAX_VOXELS)
+            if n_streams == 1:
+                for i in range(args.warmup):
+                    step(i, e2e)
+            else:
+                # warm-up through the same threads-and-streams path as the timed steps (a thread's first
+                # library calls create per-thread handles)
+                pipelined(args.warmup, e2e, n_streams, n_threads)
             barrier()
             evs = []
             launches0 = backend.launch_count()
@@ -254,64 +305,12 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                     h2d, d2h = bi, bo
                     evs.append((e0, e1))
             else:
-                # consecutive scans alternate between CUDA streams, so the host-side part of one scan
-                # (kernel-map readbacks, launches) overlaps the convolutions of the previous one; the whole
-                # K-step region is timed with one event pair and the L2 flushes are INSIDE it
+                # the whole K-step region is timed with one event pair and the L2 flushes are INSIDE it
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
                 for s in side:
                     s.wait_event(e0)
-                io_bytes = {}
-                # sharded runs: the issuing threads hand each step's logits to this (main) thread, which
-                # alone talks to NCCL, in step order on every rank, on a stream of its own
-                outputs = [None] * args.steps
-                ready = [threading.Event() for _ in range(args.steps)]
-
-                def issue(first, stride):
-                    torch.cuda.set_device(device)    # the current device is per thread (a new thread starts on 0)
-                    with torch.no_grad():
-                        for i in range(first, args.steps, stride):
-                            with torch.cuda.stream(side[i % n_streams]):
-                                flush.fill_(i & 0xFF)
-                                cur.step, cur.k = i, 0
-                                logits, bi, bo = step(i, e2e, gather_inline=False)
-                                io_bytes["h2d"], io_bytes["d2h"] = bi, bo
-                                if world > 1:
-                                    produced = torch.cuda.Event()
-                                    produced.record()
-                                    outputs[i] = (logits, produced)
-                            ready[i].set()
-                            if os.environ.get("TSB_BENCH_DEBUG"):
-                                sys.stderr.write(f"[dbg rank {rank}] issued step {i} at {(time.perf_counter() - t_host0) * 1e3:.2f} ms\n")
-
-                def gather_outputs():
-                    for i in range(args.steps):
-                        if not ready[i].wait(timeout=300) or outputs[i] is None:
-                            raise RuntimeError(f"step {i} produced no output (an issuing thread failed)")
-                        logits, produced = outputs[i]
-                        outputs[i] = None
-                        comm_stream.wait_event(produced)
-                        with torch.cuda.stream(comm_stream):
-                            logits.record_stream(comm_stream)
-                            gather_rows_padded(logits, MAX_VOXELS)
-                        if os.environ.get("TSB_BENCH_DEBUG"):
-                            sys.stderr.write(f"[dbg rank {rank}] gathered step {i} at {(time.perf_counter() - t_host0) * 1e3:.2f} ms\n")
-
-                if n_threads == 1:
-                    issue(0, 1)
-                    if world > 1:
-                        gather_outputs()
-                else:
-                    # thread t issues scans t, t + T, ... on stream t: the Python part of one scan overlaps
-                    # the native part (launch calls, allocator) of another
-                    workers = [threading.Thread(target=issue, args=(t, n_threads)) for t in range(n_threads)]
-                    for wk in workers:
-                        wk.start()
-                    if world > 1:
-                        gather_outputs()
-                    for wk in workers:
-                        wk.join()
-                h2d, d2h = io_bytes.get("h2d", 0), io_bytes.get("d2h", 0)
+                h2d, d2h = pipelined(args.steps, e2e, n_streams, n_threads)
                 for s in side + ([comm_stream] if world > 1 else []):
                     done = torch.cuda.Event()
                     done.record(s)

@@ -29,13 +29,17 @@
 //               per instruction, 4 per stage) and releases stages / publishes accumulators with
 //               tcgen05.commit.  Warps 12 and 13 run their loops converged and elect the issuing
 //               lane per instruction, so that descriptors and coordinates stay warp-uniform.
-//   warp 14     scheduler: stages the map slices of the coming tiles and their offset masks
+//   warp 14     scheduler: takes the CTA's next work item from a global counter (tiles differ in how
+//               many offsets they hold, so a fixed assignment would leave CTAs idle at the end), stages
+//               its map slice and offset mask for the other roles
 //
 // Every wait on an mbarrier is bounded: when it runs out the thread records an error code and the
 // CTA stops issuing work, gives its copies in flight time to land, frees its TMEM and returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "conv_dispatch.h"
@@ -241,6 +245,7 @@ struct UmmaParams {
   const float* bias;    // nullable
   const void* residual; // nullable, [n_out, cout]
   int* error;           // device error word (0 = fine)
+  int* sched;           // {next work item, CTAs finished}: both zero at launch, reset by the last CTA
   long long* trace;     // debugging aid (trace builds only)
   int trace_cta;
   int n_in, n_out, kvol, cin, cout;
@@ -288,11 +293,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-// Persistent kernel: each CTA walks the (row tile, N tile) work list with a fixed stride.
+// Persistent kernel: each CTA takes (row tile, N tile) work items from a shared counter until none is left.
 // Three rings decouple the roles so that the copies of the next tile are in flight while the
 // current tile is multiplied and the previous one is written out:
 //   stage ring   (p.stages)  A+B operands of one K block         full[] / empty[]
-//   tile ring    (p.ring)    map slice + offset mask of a tile   sched_full[] / sched_empty[]
+//   tile ring    (p.ring)    work item, map slice + offset mask  sched_full[] / sched_empty[]
 //   accumulator  (2)         TMEM column ranges                   acc_full[] / acc_empty[]
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -308,6 +313,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   __shared__ uint64_t s_acc_full[2];
   __shared__ uint64_t s_acc_empty[2];
   __shared__ uint32_t s_kmask[kMaxRing];
+  __shared__ int s_tile[kMaxRing];       // work item of the ring slot; -1 = no more work
   __shared__ uint32_t s_tmem;
   __shared__ volatile int s_abort;
 
@@ -367,17 +373,17 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 #ifdef TSB_TRACE_BUILD
     int blk = 0;
 #endif
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
+    for (;; ++i) {
       const int buf = i % p.ring;
       const uint32_t use_parity = (uint32_t)(i / p.ring) & 1u;
       const int* mp = s_map0 + buf * map_ints + rbase * p.kvol;
-      if (ok && !mbar_wait_warp(smem_u32(&s_sched_full[buf]), use_parity, lane)) {
+      if (!mbar_wait_warp(smem_u32(&s_sched_full[buf]), use_parity, lane)) {
         atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
-        ok = false;
+        break;
       }
-      if (s_abort) ok = false;
-      const uint32_t kmask = ok ? s_kmask[buf] : 0u;
+      if (s_abort || s_tile[buf] < 0) break;
+      const uint32_t kmask = s_kmask[buf];
       for (int k = 0; k < p.kvol && ok; ++k) {
         if (!((kmask >> k) & 1u)) continue;
         int src[kCopies];
@@ -410,6 +416,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
         }
       }
+      if (!ok) break;
       __syncwarp();   // every lane has read its rows of the slice
       if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
     }
@@ -423,28 +430,28 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     int i = 0;
     int acc_count = 0;   // tiles that used an accumulator so far (tiles with an empty mask use none)
     bool ok = true;
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
+    for (;; ++i) {
       const int buf = i % p.ring;
+      if (!mbar_wait_warp(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u, lane)) {
+        atomicExch(p.error, kErrSchedWait);
+        s_abort = 1;
+        break;
+      }
+      const int w = s_tile[buf];
+      if (s_abort || w < 0) break;
+      const uint32_t kmask = s_kmask[buf];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
       const int row0 = (w / tiles_n) * kTileM;
       const int n0 = (w % tiles_n) * p.n_tile;
       const int n_valid = min(p.n_tile, p.cout - n0);
       const int n_mma = (n_valid + 15) & ~15;
-      if (ok && !mbar_wait_warp(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u, lane)) {
-        atomicExch(p.error, kErrSchedWait);
-        s_abort = 1;
-        ok = false;
-      }
-      const uint32_t kmask = s_kmask[buf];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
-      if (!ok || s_abort) { ok = false; continue; }
       const bool have_acc = kmask != 0;
       const int ab = acc_count & 1;
       if (have_acc && !mbar_wait_warp(smem_u32(&s_acc_full[ab]), (acc_count >> 1) & 1, lane)) {
         atomicExch(p.error, kErrAccWait);
         s_abort = 1;
-        ok = false;
-        continue;
+        break;
       }
       tc_fence_after();
       const int r = quarter * 32 + lane;
@@ -530,15 +537,25 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     // tile ring and publishes its offset mask, up to `ring` tiles ahead of the other roles
     const int n4 = map_ints / 4;
     int i = 0;
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++i) {
+    for (;; ++i) {
       const int buf = i % p.ring;
-      const int row0 = (w / tiles_n) * kTileM;
       if (i >= p.ring && !mbar_wait_warp(smem_u32(&s_sched_empty[buf]), ((uint32_t)(i / p.ring) + 1u) & 1u, lane)) {
         atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
-      if (s_abort) break;
+      int w = 0;
+      if (lane == 0) w = atomicAdd(p.sched, 1);
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (w >= n_work || s_abort) {
+        // tell the other roles that the CTA is done
+        if (lane == 0) {
+          s_tile[buf] = -1;
+          mbar_arrive(smem_u32(&s_sched_full[buf]));
+        }
+        break;
+      }
+      const int row0 = (w / tiles_n) * kTileM;
       const int4* src = reinterpret_cast<const int4*>(p.map + (int64_t)row0 * p.kvol);
       int4* dst = reinterpret_cast<int4*>(s_map0 + buf * map_ints);
       uint32_t mine = 0;
@@ -563,6 +580,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       __syncwarp();
       if (lane == 0) {
         s_kmask[buf] = mine;
+        s_tile[buf] = w;
         mbar_arrive(smem_u32(&s_sched_full[buf]));
       }
     }
@@ -575,18 +593,19 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     bool first_pass = true;
     int i = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
+    for (; ok; ++i) {
       const int buf = i % p.ring;
-      const int n0 = (w % tiles_n) * p.n_tile;
       if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
         if (lane == 0) atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
+      const int w = s_tile[buf];
+      if (s_abort || w < 0) break;
       const uint32_t kmask = s_kmask[buf];
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
-      if (s_abort) break;
+      const int n0 = (w % tiles_n) * p.n_tile;
       for (int k = 0; k < p.kvol && ok; ++k) {
         if (!((kmask >> k) & 1u)) continue;
         const int wrow = k * p.cout + n0;
@@ -624,20 +643,21 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 #ifdef TSB_TRACE_BUILD
     int blk = 0;
 #endif
-    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++i) {
+    for (; ok; ++i) {
       const int buf = i % p.ring;
-      const int n0 = (w % tiles_n) * p.n_tile;
-      const int n_mma = (min(p.n_tile, p.cout - n0) + 15) & ~15;
-      const uint32_t idesc = make_idesc(p.ab_format, n_mma);
       if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
         if (lane == 0) atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
+      const int w = s_tile[buf];
+      if (s_abort || w < 0) break;
       const uint32_t kmask = s_kmask[buf];
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
-      if (s_abort) break;
+      const int n0 = (w % tiles_n) * p.n_tile;
+      const int n_mma = (min(p.n_tile, p.cout - n0) + 15) & ~15;
+      const uint32_t idesc = make_idesc(p.ab_format, n_mma);
       if (!kmask) continue;                                      // nothing to multiply: the epilogue writes zeros
       // the epilogue must have drained this accumulator buffer (its previous use)
       const int ab = acc_count & 1;
@@ -700,7 +720,22 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * acc_cols);
   }
+  // the last CTA to finish puts the scheduling words back to zero for a later launch
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1) == (int)gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+      __threadfence();
+    }
+  }
 }
+
+// Scheduling words of the launches in flight: slot = launch sequence number modulo kSchedSlots.  A slot is
+// zero whenever no launch uses it (zero-initialised, and every launch zeroes its slot when its last CTA
+// leaves), and kernels that run at the same time (different streams) are at most a few launches apart.
+constexpr int kSchedSlots = 1024;
+__device__ int g_sched_slots[kSchedSlots * 2];
 
 // W [kvol, cin, cout] -> Wt [kvol, cout, cin]
 template <typename T>
@@ -764,6 +799,21 @@ void pick_config(int n_tile, int kvol, int* stages, int* ring, int* ctas) {
   *ctas = 1;
   if (best[0] > best[1]) { *stages = best[0]; *ring = 2; }
   else { *stages = best[1]; *ring = 3; }
+}
+
+// device address of g_sched_slots on the current device (looked up once per device)
+int* sched_slots() {
+  static std::mutex mu;
+  static int* addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_sched_slots) != cudaSuccess) return nullptr;
+    addr[dev] = reinterpret_cast<int*>(ptr);
+  }
+  return addr[dev];
 }
 
 int num_sms() {
@@ -843,6 +893,12 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   UmmaParams p;
   p.x = a.x; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
   p.residual = a.residual; p.error = err;
+  {
+    int* slots = sched_slots();
+    if (!slots) return TSB_ERR_CUDA;
+    static std::atomic<unsigned> seq{0};
+    p.sched = slots + 2 * (seq.fetch_add(1) % kSchedSlots);
+  }
   p.trace = nullptr; p.trace_cta = 0;
   if (const char* tr = getenv("TSB_UMMA_TRACE")) {   // debugging aid: address of a 256x8 int64 device buffer
     p.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
