@@ -318,6 +318,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   __shared__ volatile int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) TSB_TRACE_HOT(7, 0);     // CTA entry
   const int tiles_n = (p.cout + p.n_tile - 1) / p.n_tile;
   const int tiles_m = (p.n_out + kTileM - 1) / kTileM;
   const int n_work = tiles_m * tiles_n;
@@ -525,6 +526,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           }
         }
       }
+      if (warp == kGatherWarps && lane == 0) TSB_TRACE_HOT(7, i + 1);   // tile i written out (first epilogue warp)
       // this warp is done with the accumulator buffer
       tc_fence_before();
       __syncwarp();
@@ -556,23 +558,30 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         break;
       }
       const int row0 = (w / tiles_n) * kTileM;
+      // all 16-byte copies of the slice go out before any of them is waited for: the slice costs one
+      // memory round trip, not one per few loads
       const int4* src = reinterpret_cast<const int4*>(p.map + (int64_t)row0 * p.kvol);
       int4* dst = reinterpret_cast<int4*>(s_map0 + buf * map_ints);
+      const uint32_t dst_s = map_smem + (uint32_t)(buf * map_ints) * 4u;
+      for (int e = lane; e < n4; e += 32) cp_async16(dst_s + (uint32_t)e * 16u, src + e, 16u);
+      cp_async_wait_all();
+      __syncwarp();
       uint32_t mine = 0;
       int kk = (lane * 4) % p.kvol;                 // kernel offset of the first int of this lane's int4
       const int kstep = 128 % p.kvol;               // advance of that offset per loop trip (32 lanes x 4 ints)
 #pragma unroll 4
       for (int e = lane; e < n4; e += 32) {
-        int4 v = __ldg(&src[e]);
+        int4 v = dst[e];
         int* c = reinterpret_cast<int*>(&v);
         int k = kk;
+        bool changed = false;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if (c[j] >= p.n_in) c[j] = -1;
+          if (c[j] >= p.n_in) { c[j] = -1; changed = true; }   // defensive: an index beyond the features reads nothing
           if (c[j] >= 0) mine |= 1u << k;
           k = (k + 1 == p.kvol) ? 0 : k + 1;
         }
-        dst[e] = v;
+        if (changed) dst[e] = v;
         kk += kstep;
         if (kk >= p.kvol) kk -= p.kvol;
       }
@@ -720,6 +729,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * acc_cols);
   }
+  if (tid == 0) TSB_TRACE_HOT(3, 0);     // CTA exit
   // the last CTA to finish puts the scheduling words back to zero for a later launch
   if (tid == 0) {
     __threadfence();
