@@ -218,6 +218,7 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 #endif
 }
+// issues the load of 16 consecutive accumulator columns of this warp's 32 lanes; tmem_ld_wait16 completes it
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 #ifdef TSB_TCGEN05
   asm volatile(
@@ -226,7 +227,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#endif
+}
+// Waits for the tcgen05.ld issued before it.  The loaded registers pass through the statement as
+// in/out operands so that no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t (&v)[16]) {
+#ifdef TSB_TCGEN05
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
 #endif
 }
 
@@ -464,6 +475,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       }
       const uint32_t acc_addr = tmem_base + (uint32_t)ab * acc_cols + ((uint32_t)(quarter * 32) << 16);
       for (int j = 0; j < n_mma; j += 16) {
+        // the accumulator load is in flight while the per-channel constants and the residual are fetched
         uint32_t v[16];
         if (have_acc) {
           tmem_ld16(acc_addr + (uint32_t)j, v);
@@ -471,26 +483,41 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 #pragma unroll
           for (int e = 0; e < 16; ++e) v[e] = 0u;
         }
-        if (dst_row < 0) continue;
+        const int n = n0 + j;
+        const bool ok8[2] = {dst_row >= 0 && n < p.cout, dst_row >= 0 && n + 8 < p.cout};   // cout % 8 == 0
+        // residual of the 16 channels, still packed (fp32: fetched per half below)
+        uint4 rv[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+        if constexpr (!kTF32) {
+          if (res) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              if (ok8[h]) rv[h] = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n) + h);
+          }
+        }
+        if (have_acc) tmem_ld_wait16(v);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int n = n0 + j + h * 8;
-          if (n >= p.cout) continue;        // cout % 8 == 0: 8-channel groups are all-in or all-out
+          if (!ok8[h]) continue;
+          const int nh = n + 8 * h;
           float f[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[h * 8 + e]);
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * h + e]);
           if (p.scale) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] *= __ldg(&p.scale[n + e]);
+            const float4 a = __ldg(reinterpret_cast<const float4*>(p.scale + nh));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.scale + nh) + 1);
+            f[0] *= a.x; f[1] *= a.y; f[2] *= a.z; f[3] *= a.w;
+            f[4] *= b.x; f[5] *= b.y; f[6] *= b.z; f[7] *= b.w;
           }
           if (p.bias) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] += __ldg(&p.bias[n + e]);
+            const float4 a = __ldg(reinterpret_cast<const float4*>(p.bias + nh));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + nh) + 1);
+            f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+            f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
           }
           if constexpr (kTF32) {
-            float* yo = reinterpret_cast<float*>(y) + dst_row * p.cout + n;
+            float* yo = reinterpret_cast<float*>(y) + dst_row * p.cout + nh;
             if (res) {
-              const float* rp = reinterpret_cast<const float*>(res) + dst_row * p.cout + n;
+              const float* rp = reinterpret_cast<const float*>(res) + dst_row * p.cout + nh;
               const float4 ra = __ldg(reinterpret_cast<const float4*>(rp));
               const float4 rb = __ldg(reinterpret_cast<const float4*>(rp) + 1);
               f[0] += ra.x; f[1] += ra.y; f[2] += ra.z; f[3] += ra.w;
@@ -504,11 +531,10 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             reinterpret_cast<float4*>(yo)[1] = make_float4(f[4], f[5], f[6], f[7]);
           } else {
             if (res) {
-              uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n));
-              const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
+              const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv[h]);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                float2 t = unpack2<T>(rw[e]);
+                const float2 t = unpack2<T>(rw[e]);
                 f[2 * e] += t.x;
                 f[2 * e + 1] += t.y;
               }
@@ -517,12 +543,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
             }
-            uint4 o;
-            o.x = pack2<T>(f[0], f[1]);
-            o.y = pack2<T>(f[2], f[3]);
-            o.z = pack2<T>(f[4], f[5]);
-            o.w = pack2<T>(f[6], f[7]);
-            *reinterpret_cast<uint4*>(y + dst_row * p.cout + n) = o;
+            *reinterpret_cast<uint4*>(y + dst_row * p.cout + nh) =
+                make_uint4(pack2<T>(f[0], f[1]), pack2<T>(f[2], f[3]), pack2<T>(f[4], f[5]), pack2<T>(f[6], f[7]));
           }
         }
       }
