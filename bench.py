@@ -170,6 +170,13 @@ def conv_algorithmic(dims, pairs: int):
     return flops, byts
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one conv launch from the ncu captures
+# summarised under profiles/ (igemm_umma_256x256_31k_rows.md, igemm_umma_96x96_110k_rows.md):
+# (kvol, cin, cout) -> (bytes, output rows of the captured launch).  Feature, output and map bytes grow with
+# the rows and the weights are small beside them, so the figure is scaled by the row count.
+NCU_TRAFFIC = {(27, 256, 256): (23.3e6, 31788), (27, 96, 96): (33.6e6, 110000)}
+
+
 def map_counts(dims):
     """(valid (row, offset) pairs, issued (128-row tile, offset) blocks) of one conv launch's map."""
     m = dims[6]
@@ -382,7 +389,11 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         else:
             roof = {"bound": "hbm", "achieved": round(gb, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": round(gb / pk["hbm_gbs"], 4)}
-        roof.update({"traffic": None, "kernel": "igemm conv forward",
+        cap = NCU_TRAFFIC.get((key[2], key[3], key[4]))
+        roof.update({"traffic": None if cap is None else round(cap[0] * key[1] / cap[1]),
+                     "traffic_source": None if cap is None else
+                     f"ncu capture of the same kernel on {cap[1]} rows (profiles/), scaled by rows; bytes per launch",
+                     "kernel": "igemm conv forward",
                      "layer": {"n_in": key[0], "n_out": key[1], "kvol": key[2], "cin": key[3], "cout": key[4]},
                      "launches": d["n"], "avg_us": round(d["ms"] * 1e3 / d["n"], 2),
                      "useful_flops_per_launch": d["flops"] / d["n"], "algorithmic_bytes_per_launch": d["bytes"] / d["n"],
