@@ -228,6 +228,8 @@ int tsb_conv_pack_weight(const void* weight, int32_t kvol, int32_t cin, int32_t 
                          void* packed, tsb_stream_t stream);
 
 /* Gather -> grouped GEMM -> scatter over pair lists (nbmaps [P,2], HOST nbsizes [kvol]).
+ * 16-bit tensors (and fp32 under TSB_MATH_TF32) whose rows are 16-byte multiples run the GEMM on the
+ * tensor cores over the 128-padded pair list, fetching the input rows straight from in_feats.
  * scatter_mask is the output_mask of tsb_build_masks (the input_mask when transpose != 0):
  * the scatter sums each output row's products in a fixed order, without atomics.
  * Replaces conv_forward_gather_scatter_cuda
@@ -240,13 +242,15 @@ int tsb_conv_gs_fwd(const void* in_feats, const void* weight, const int32_t* nbm
                     int32_t transpose, void* workspace, size_t workspace_bytes,
                     tsb_stream_t stream);
 
-/* Fetch-on-demand: one fused launch over the 128-quantised pair list (nbmaps [2,P],
+/* Fetch-on-demand: one fused launch over the 128-quantised pair list (tensor cores where the shape
+ * allows, as for tsb_conv_gs_fwd) (nbmaps [2,P],
  * nbaddrs/qnbaddrs int32 [kvol+1] on the device, qmapsize = qnbaddrs[kvol] on the host);
  * fp32 accumulation, scatter by atomic adds into an fp32 accumulator held in `workspace`,
  * rounded once into out_feats.
  * Replaces conv_forward_fetch_on_demand_cuda / _no_fusion_cuda
  * (torchsparse/backend/convolution/convolution_forward_fetch_on_demand_cuda.cu:1981-2260). */
-size_t tsb_conv_fod_workspace_bytes(int64_t n_out, int32_t cout, int32_t dtype);
+size_t tsb_conv_fod_workspace_bytes(int64_t n_out, int64_t qmapsize, int32_t kvol, int32_t cin, int32_t cout,
+                                    int32_t dtype);
 int tsb_conv_fod_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps,
                      int64_t n_pairs, const int32_t* nbaddrs, const int32_t* qnbaddrs,
                      int64_t qmapsize, void* out_feats, int64_t n_in, int64_t n_out, int32_t kvol,

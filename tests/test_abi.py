@@ -39,7 +39,7 @@ def test_status_strings_and_argument_checks():
     assert lib.tsb_kmap_down_slots(i32x((3, 3, 3)), i32x((2, 2, 2))) == 8
     assert lib.tsb_kmap_down_slots(i32x((1, 3, 1)), i32x((1, 2, 1))) == 2
     assert lib.tsb_kmap_down_slots(i32x((3, 3, 3)), i32x((0, 2, 2))) == 0
-    assert lib.tsb_conv_fod_workspace_bytes(100, 32, 1) >= 100 * 32 * 4
+    assert lib.tsb_conv_fod_workspace_bytes(100, 256, 27, 32, 32, 1) >= 100 * 32 * 4
 
 
 def test_product_has_no_oracle_or_cpu_fallback():

@@ -52,7 +52,7 @@ SIGNATURES = {
     "tsb_conv_pack_weight": (C.c_int, [P, I32, I32, I32, I32, P, P]),
     "tsb_conv_gs_workspace_bytes": (SZ, [I64, I32, I32, I32, I32]),
     "tsb_conv_gs_fwd": (C.c_int, [P, P, P, P, P, P, I64, I64, I32, I32, I32, I32, I32, I32, P, SZ, P]),
-    "tsb_conv_fod_workspace_bytes": (SZ, [I64, I32, I32]),
+    "tsb_conv_fod_workspace_bytes": (SZ, [I64, I64, I32, I32, I32, I32]),
     "tsb_conv_fod_fwd": (C.c_int, [P, P, P, I64, P, P, I64, P, I64, I64, I32, I32, I32, I32, I32, I32, P, SZ, P]),
     "tsb_count": (C.c_int, [P, I64, P, I64, P]),
     "tsb_voxelize_fwd": (C.c_int, [P, P, P, I64, I64, I32, I32, P, P]),

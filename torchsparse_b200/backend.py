@@ -590,7 +590,8 @@ def conv_forward_fetch_on_demand_cuda(in_feats: torch.Tensor, kernel: torch.Tens
     nbmaps = nbmaps.int().contiguous()
     out = torch.empty((output_size, cout), dtype=in_feats.dtype, device=in_feats.device)
     code = _dtype_code(in_feats)
-    ws = _workspace(lib.tsb_conv_fod_workspace_bytes(output_size, cout, code), in_feats.device)
+    ws = _workspace(lib.tsb_conv_fod_workspace_bytes(output_size, int(qmapsize), kvol, cin, cout, code),
+                    in_feats.device)
     check(lib.tsb_conv_fod_fwd(_p(in_feats), _p(kernel), _p(nbmaps), int(mapsize), _p(nbaddrs), _p(qnbaddrs),
                                int(qmapsize), _p(out), in_feats.shape[0], output_size, kvol, cin, cout, code,
                                _math_mode(in_feats, allow_tf32), int(bool(transpose)), _p(ws), ws.numel(), _stream()),

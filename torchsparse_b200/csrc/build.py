@@ -11,7 +11,8 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libtsb200.so")
-SOURCES = ["lib.cu", "kmap.cu", "conv.cu", "conv_simt.cu", "conv_umma.cu", "pointops.cu", "quantize.cu"]
+SOURCES = ["lib.cu", "kmap.cu", "conv.cu", "conv_simt.cu", "conv_umma.cu", "conv_pairs.cu", "pointops.cu",
+           "quantize.cu"]
 HEADERS = ["common.cuh", "conv_dispatch.h", os.path.join("..", "..", "include", "tsb200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

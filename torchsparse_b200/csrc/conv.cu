@@ -1,5 +1,7 @@
 // C ABI of the convolution forward entry points and the choice between the tcgen05
 // (tensor-core) kernels and the CUDA-core kernels.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "conv_dispatch.h"
 
@@ -46,7 +48,9 @@ int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* pac
 
 size_t tsb_conv_gs_workspace_bytes(int64_t n_pairs, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {
   if (n_pairs < 0 || kvol < 1 || cin < 1 || cout < 1 || !valid_dtype(dtype)) return 0;
-  return gs_workspace_bytes(n_pairs, kvol, cin, cout, dtype);
+  const size_t simt = gs_workspace_bytes(n_pairs, kvol, cin, cout, dtype);
+  const size_t umma = gs_umma_workspace_bytes(n_pairs, kvol, cin, cout, dtype);
+  return simt > umma ? simt : umma;
 }
 
 int tsb_conv_gs_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps, const int32_t* nbsizes_host,
@@ -65,13 +69,19 @@ int tsb_conv_gs_fwd(const void* in_feats, const void* weight, const int32_t* nbm
   if (n_pairs > INT32_MAX) return TSB_ERR_LIMIT;
   GsArgs a{in_feats, weight, nbmaps, nbsizes_host, scatter_mask, out_feats, n_in, n_out, n_pairs, kvol, cin, cout,
            dtype, math, transpose, workspace, workspace_bytes};
+  // tensor cores when the shape allows (16-bit tensors, or fp32 under TF32 math); else the CUDA cores
+  if (pairs_umma_usable(in_feats, weight, n_in, kvol, cin, cout, dtype, math) &&
+      workspace_bytes >= gs_umma_workspace_bytes(n_pairs, kvol, cin, cout, dtype))
+    return gs_umma(a, as_stream(stream));
   return gs_simt(a, as_stream(stream));
 }
 
-size_t tsb_conv_fod_workspace_bytes(int64_t n_out, int32_t cout, int32_t dtype) {
-  if (n_out < 0 || cout < 1 || !valid_dtype(dtype)) return 0;
-  if (dtype == TSB_F32) return 256;
-  return align_up((size_t)n_out * cout * sizeof(float), 256) + 256;
+size_t tsb_conv_fod_workspace_bytes(int64_t n_out, int64_t qmapsize, int32_t kvol, int32_t cin, int32_t cout,
+                                    int32_t dtype) {
+  if (n_out < 0 || qmapsize < 0 || kvol < 1 || cin < 1 || cout < 1 || !valid_dtype(dtype)) return 0;
+  const size_t simt = dtype == TSB_F32 ? 256 : align_up((size_t)n_out * cout * sizeof(float), 256) + 256;
+  const size_t umma = fod_umma_workspace_bytes(n_out, qmapsize, kvol, cin, cout, dtype);
+  return simt > umma ? simt : umma;
 }
 
 int tsb_conv_fod_fwd(const void* in_feats, const void* weight, const int32_t* nbmaps, int64_t n_pairs,
@@ -85,6 +95,12 @@ int tsb_conv_fod_fwd(const void* in_feats, const void* weight, const int32_t* nb
   if (qmapsize > INT32_MAX || n_pairs > INT32_MAX) return TSB_ERR_LIMIT;
   FodArgs a{in_feats, weight, nbmaps, nbaddrs, qnbaddrs, out_feats, n_in, n_out, n_pairs, qmapsize, kvol, cin, cout,
             dtype, math, transpose, workspace, workspace_bytes};
+  // The tensor-core path adds its products to the output with vector atomics from the epilogue; below
+  // 128 x 128 channels a launch is bound by those atomics and the CUDA-core kernel (whose lanes add to
+  // consecutive floats of a row) is as fast or faster, so it keeps the narrow layers.
+  if ((int64_t)cin * cout >= 128 * 128 && pairs_umma_usable(in_feats, weight, n_in, kvol, cin, cout, dtype, math) &&
+      workspace_bytes >= fod_umma_workspace_bytes(n_out, qmapsize, kvol, cin, cout, dtype))
+    return fod_umma(a, as_stream(stream));
   return fod_simt(a, as_stream(stream));
 }
 

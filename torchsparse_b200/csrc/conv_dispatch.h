@@ -23,6 +23,13 @@ struct IgemmArgs {
   int* dev_status;  // nullable
   void* workspace;
   size_t workspace_bytes;
+  // pair-list mode of the tensor-core kernel (zero / null otherwise): `map` is one column of input rows,
+  // 128-row tile t multiplies with weight offset tile_k[t] of a [kvol_w, cin, cout] weight tensor
+  const int* tile_k;
+  int kvol_w;
+  int out_fp32;     // 16-bit operands, fp32 output rows
+  int atomic_out;   // fp32 output rows accumulated with atomic adds
+  int64_t dst_rows; // rows of y when they are addressed through reorder_loc (0: n_out)
 };
 
 struct GsArgs {
@@ -63,5 +70,13 @@ size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype);
 int igemm_umma(const IgemmArgs& a, cudaStream_t s);
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype);
 int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* packed, cudaStream_t s);
+
+
+// tensor-core pair-list paths of the other two dataflows (conv_pairs.cu)
+bool pairs_umma_usable(const void* x, const void* w, int64_t n_in, int kvol, int cin, int cout, int dtype, int math);
+size_t gs_umma_workspace_bytes(int64_t n_pairs, int kvol, int cin, int cout, int dtype);
+size_t fod_umma_workspace_bytes(int64_t n_out, int64_t qmapsize, int kvol, int cin, int cout, int dtype);
+int gs_umma(const GsArgs& a, cudaStream_t s);
+int fod_umma(const FodArgs& a, cudaStream_t s);
 
 }  // namespace tsb

@@ -257,6 +257,10 @@ struct UmmaParams {
   const void* residual; // nullable, [n_out, cout]
   int* error;           // device error word (0 = fine)
   int* sched;           // {next work item, CTAs finished}: both zero at launch, reset by the last CTA
+  const int* tile_k;    // nullable ("pair list" mode): weight offset of each 128-row tile; the map is one column
+  int dst_rows;         // rows of y (bound of the reorder scatter)
+  int out_fp32;         // 16-bit operands, fp32 output rows (no residual)
+  int atomic_out;       // fp32 output accumulated with atomic adds (rows may repeat between tiles)
   long long* trace;     // debugging aid (trace builds only)
   int trace_cta;
   int n_in, n_out, kvol, cin, cout;
@@ -471,7 +475,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       int64_t dst_row = -1;
       if (grow < p.n_out) {
         dst_row = p.reorder ? (int64_t)__ldg(&p.reorder[grow]) : grow;
-        if (dst_row >= p.n_out) dst_row = -1;
+        if (dst_row >= p.dst_rows) dst_row = -1;
       }
       const uint32_t acc_addr = tmem_base + (uint32_t)ab * acc_cols + ((uint32_t)(quarter * 32) << 16);
       for (int j = 0; j < n_mma; j += 16) {
@@ -514,9 +518,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
             f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
           }
-          if constexpr (kTF32) {
-            float* yo = reinterpret_cast<float*>(y) + dst_row * p.cout + nh;
-            if (res) {
+          if (kTF32 || p.out_fp32) {
+            float* yo = reinterpret_cast<float*>(p.y) + dst_row * p.cout + nh;
+            if (kTF32 && res) {
               const float* rp = reinterpret_cast<const float*>(res) + dst_row * p.cout + nh;
               const float4 ra = __ldg(reinterpret_cast<const float4*>(rp));
               const float4 rb = __ldg(reinterpret_cast<const float4*>(rp) + 1);
@@ -527,9 +531,14 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
             }
-            reinterpret_cast<float4*>(yo)[0] = make_float4(f[0], f[1], f[2], f[3]);
-            reinterpret_cast<float4*>(yo)[1] = make_float4(f[4], f[5], f[6], f[7]);
-          } else {
+            if (p.atomic_out) {
+              atomicAdd(reinterpret_cast<float4*>(yo), make_float4(f[0], f[1], f[2], f[3]));
+              atomicAdd(reinterpret_cast<float4*>(yo) + 1, make_float4(f[4], f[5], f[6], f[7]));
+            } else {
+              reinterpret_cast<float4*>(yo)[0] = make_float4(f[0], f[1], f[2], f[3]);
+              reinterpret_cast<float4*>(yo)[1] = make_float4(f[4], f[5], f[6], f[7]);
+            }
+          } else if constexpr (!kTF32) {
             if (res) {
               const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv[h]);
 #pragma unroll
@@ -639,7 +648,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       const int n0 = (w % tiles_n) * p.n_tile;
       for (int k = 0; k < p.kvol && ok; ++k) {
         if (!((kmask >> k) & 1u)) continue;
-        const int wrow = k * p.cout + n0;
+        // pair-list mode: the tile's rows all belong to one kernel offset, named by tile_k
+        const int wrow = (p.tile_k ? __ldg(&p.tile_k[w / tiles_n]) : k) * p.cout + n0;
         for (int c = 0; c < chunks; ++c) {
           if (!first_pass && !mbar_wait(empty0 + stage * 8, phase ^ 1u)) {
             if (lane == 0) atomicExch(p.error, kErrEmptyWait);
@@ -875,7 +885,9 @@ bool igemm_umma_supported(const IgemmArgs& a) {
   // feature rows must be 16-byte multiples (tensor-map stride); outputs are written in 8-channel groups
   if ((a.cin * (int)dtype_size(a.dtype)) % 16 || a.cout % 8) return false;
   if (a.n_in >= (int64_t)INT32_MAX || a.n_out >= (int64_t)INT32_MAX) return false;
-  if (a.kvol > kMaxKvolUmma) return false;
+  if (a.kvol > kMaxKvolUmma) return false;            // one bit per map column in a tile's offset mask
+  if (a.tile_k && a.kvol != 1) return false;          // pair-list mode: one map column, weights chosen per tile
+  if (a.out_fp32 && a.residual) return false;
   if (((uintptr_t)a.x | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual | (uintptr_t)a.packed_w) & 15)
     return false;
   int st = 0, rg = 0, ct = 0;
@@ -907,7 +919,8 @@ int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* pac
 
 template <typename T>
 static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
-  const size_t w_bytes = packed_weight_bytes(a.kvol, a.cin, a.cout, a.dtype);
+  const int kvol_w = a.tile_k ? a.kvol_w : a.kvol;      // kernel offsets of the weight tensor
+  const size_t w_bytes = packed_weight_bytes(kvol_w, a.cin, a.cout, a.dtype);
   const T* wt = reinterpret_cast<const T*>(a.packed_w);
   int* err = a.dev_status;
   if (!wt || !err) {
@@ -918,13 +931,15 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     TSB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), s));
   }
   if (!wt) {
-    int rc = pack_launch<T>(a.w, a.kvol, a.cin, a.cout, a.workspace, s);
+    int rc = pack_launch<T>(a.w, kvol_w, a.cin, a.cout, a.workspace, s);
     if (rc != TSB_OK) return rc;
     wt = reinterpret_cast<const T*>(a.workspace);
   }
   UmmaParams p;
   p.x = a.x; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
   p.residual = a.residual; p.error = err;
+  p.tile_k = a.tile_k; p.out_fp32 = a.out_fp32; p.atomic_out = a.atomic_out;
+  p.dst_rows = (int)(a.dst_rows > 0 ? a.dst_rows : a.n_out);
   {
     int* slots = sched_slots();
     if (!slots) return TSB_ERR_CUDA;
@@ -959,7 +974,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     const cuuint32_t chunk = (cuuint32_t)(kRowBytes / sizeof(T));
     cuuint32_t estride[2] = {1, 1};
     // packed weights as a 2-D tensor [kvol * cout rows, cin columns]; box = 128 bytes of columns x n_tile rows
-    cuuint64_t gdim[2] = {(cuuint64_t)a.cin, (cuuint64_t)a.kvol * (cuuint64_t)a.cout};
+    cuuint64_t gdim[2] = {(cuuint64_t)a.cin, (cuuint64_t)kvol_w * (cuuint64_t)a.cout};
     cuuint64_t gstride[1] = {(cuuint64_t)a.cin * sizeof(T)};
     cuuint32_t box[2] = {chunk, (cuuint32_t)p.n_tile};
     CUresult r = encode(&w_map, dt, 2, const_cast<T*>(wt), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
