@@ -266,6 +266,46 @@ __global__ void down_stage3_kernel(TableView t, const int4* __restrict__ coords,
   }
 }
 
+// The same pass as a block of inputs x offset lanes (32 x 8 or 16 x 16) with the offset digits precomputed (no
+// 64-bit division, no digit arithmetic per thread) and power-of-two strides taken with masks and shifts.
+constexpr int kMaxStage3Offsets = 128;
+struct DownOffsets {
+  signed char d[3][kMaxStage3Offsets];   // digit - (kernel size - 1) + padding, per dimension
+  int shift[3];                           // log2(stride) when the stride is a power of two, else -1
+};
+
+__global__ void __launch_bounds__(256)
+down_stage3_rows_kernel(TableView t, const int4* __restrict__ coords, int64_t n, int64_t m, Bounds b, KernelGeom g,
+                        DownOffsets off, int* __restrict__ map, int* status) {
+  const int64_t row = blockIdx.x * (int64_t)blockDim.y + threadIdx.y;
+  if (row >= n) return;
+  const int4 c = __ldg(&coords[row]);
+  const int in[3] = {c.y, c.z, c.w};
+  for (int k = threadIdx.x; k < g.kvol; k += blockDim.x) {
+    int o[3];
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int v = in[i] + off.d[i][k];
+      if (off.shift[i] >= 0) {
+        ok = ok && ((v & ((1 << off.shift[i]) - 1)) == 0);
+        o[i] = v >> off.shift[i];           // exact for the multiples of the stride that pass the test
+      } else {
+        ok = ok && (v % g.st[i] == 0);
+        o[i] = v / g.st[i];
+      }
+    }
+    if (!ok || !in_bounds_xyz(b, o[0], o[1], o[2])) continue;
+    const int64_t key = ravel4(b, c.x, o[0], o[1], o[2]);
+    const int orow = table_lookup(t, (unsigned long long)(key + 1)) - 1;
+    if (orow >= 0 && orow < m) {
+      map[(int64_t)orow * g.kvol + (g.kvol - 1 - k)] = (int)row;
+    } else if (status) {
+      atomicOr(status, TSB_DEV_BAD_INDEX);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ transpose / bitmask / reorder
 __global__ void fill_i32_kernel(int* __restrict__ p, int64_t n, int v) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
@@ -707,8 +747,27 @@ int tsb_kmap_down_finish(int64_t* table_keys, int32_t* table_vals, int64_t capac
   down_insert_fill_kernel<<<(int)cdiv(rows_pad, kBlock), kBlock, 0, s>>>(
       t, uniq_keys, m, rows_pad, b, g.kvol, reinterpret_cast<int4*>(out_coords), out_in_map, dev_status);
   TSB_LAUNCH_CHECK();
-  down_stage3_kernel<<<grid_for(n * (int64_t)g.kvol, kBlock, 32), kBlock, 0, s>>>(
-      t, reinterpret_cast<const int4*>(coords), n, m, b, g, out_in_map, dev_status);
+  bool small = g.kvol <= kMaxStage3Offsets && cdiv(n, 16) <= INT32_MAX;
+  for (int i = 0; i < 3; ++i) small = small && g.ks[i] <= 64 && g.pd[i] >= 0 && g.pd[i] <= 63;
+  if (small) {
+    DownOffsets off;
+    for (int k = 0; k < g.kvol; ++k) {
+      int d[3];
+      if (g.odd) { d[0] = k % g.ks[0]; d[1] = (k / g.ks[0]) % g.ks[1]; d[2] = k / (g.ks[0] * g.ks[1]); }
+      else { d[2] = k % g.ks[2]; d[1] = (k / g.ks[2]) % g.ks[1]; d[0] = k / (g.ks[2] * g.ks[1]); }
+      for (int i = 0; i < 3; ++i) off.d[i][k] = (signed char)(g.pd[i] + d[i] - (g.ks[i] - 1));
+    }
+    for (int i = 0; i < 3; ++i) {
+      off.shift[i] = -1;
+      for (int sh = 0; sh < 16; ++sh) if (g.st[i] == (1 << sh)) off.shift[i] = sh;
+    }
+    const int lanes = g.kvol <= 8 ? 8 : 16, rows = 256 / lanes;
+    down_stage3_rows_kernel<<<(unsigned)cdiv(n, rows), dim3(lanes, rows), 0, s>>>(
+        t, reinterpret_cast<const int4*>(coords), n, m, b, g, off, out_in_map, dev_status);
+  } else {
+    down_stage3_kernel<<<grid_for(n * (int64_t)g.kvol, kBlock, 32), kBlock, 0, s>>>(
+        t, reinterpret_cast<const int4*>(coords), n, m, b, g, out_in_map, dev_status);
+  }
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }
