@@ -493,20 +493,21 @@ class IgemmLayerPlan:
 
 
 def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: torch.Tensor, num_out_feats: int,
-                      residual: Optional[torch.Tensor], relu: bool) -> torch.Tensor:
+                      residual: Optional[torch.Tensor], relu: bool,
+                      reorder_loc: Optional[torch.Tensor] = None) -> torch.Tensor:
     """conv_forward_implicit_gemm_cuda for a layer with an :class:`IgemmLayerPlan` (same kernel launch).
     Falls back to the checked entry point when launches are being observed or their status read back."""
     if _observer is not None or check_kernel_status or plan.packed is None:
         return conv_forward_implicit_gemm_cuda(in_feats, plan.kernel, out_in_map, num_out_feats, plan.cout,
                                                plan.tag[2], True, scale=plan.scale, bias=plan.bias,
-                                               residual=residual, relu=relu)
+                                               residual=residual, relu=relu, reorder_loc=reorder_loc)
     if in_feats.dtype != plan.dtype or not in_feats.is_contiguous() or in_feats.shape[1] != plan.args_tail[1]:
         raise ValueError("input features do not match the layer plan (dtype, layout or channel count)")
     if residual is not None and (residual.dtype != plan.dtype or not residual.is_contiguous()):
         residual = residual.to(plan.dtype).contiguous()
     out = torch.empty((num_out_feats, plan.cout), dtype=plan.dtype, device=plan.device)
     rc = lib.tsb_conv_igemm_fwd(in_feats.data_ptr(), plan.args_head[0], plan.args_head[1], out_in_map.data_ptr(),
-                                None, out.data_ptr(), in_feats.shape[0], num_out_feats, *plan.args_tail,
+                                None if reorder_loc is None else reorder_loc.data_ptr(), out.data_ptr(), in_feats.shape[0], num_out_feats, *plan.args_tail,
                                 None if residual is None else residual.data_ptr(), int(relu),
                                 _status_word(plan.device).data_ptr(), None, 0,
                                 torch._C._cuda_getCurrentRawStream(plan.device.index))

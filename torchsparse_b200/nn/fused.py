@@ -117,12 +117,15 @@ class FusedConv(nn.Module):
                         epilogue={"scale": self.scale, "bias": self.shift, "residual": residual, "relu": self.relu})
 
     def _forward_cached_map(self, x: SparseTensor, residual, layer_config) -> Optional[SparseTensor]:
-        """Short path for the common case of a network's inner layers: unsorted implicit GEMM on a
+        """Short path for the common case of a network's inner layers: implicit GEMM on a
         kernel map that is already in the tensor's cache (built by an earlier layer of the level or by
         the engine's prebuild).  Same launch as F.conv3d makes, without its per-call bookkeeping;
         returns None when the case does not apply."""
         config = _conv_impl.resolve_config(layer_config)
-        if config["dataflow"] != F.Dataflow.ImplicitGEMM or config["ifsort"]:
+        if config["dataflow"] != F.Dataflow.ImplicitGEMM:
+            return None
+        ifsort = bool(config["ifsort"])
+        if ifsort and config["split_mask_num"] != 1:
             return None
         feats = x.feats
         if feats.dtype != self.kernel.dtype or not feats.is_cuda:
@@ -134,13 +137,19 @@ class FusedConv(nn.Module):
             target = caches.cmaps.get(out_stride)
             if kmap is None or target is None or kmap.get("out_in_map_t") is None:
                 return None
-            out_in_map, n_out = kmap["out_in_map_t"], kmap["sizes"][0]
+            if ifsort and (kmap.get("reorder_out_in_map_t") is None or kmap.get("_split_t") != 1):
+                return None
+            out_in_map, n_out = kmap["reorder_out_in_map_t" if ifsort else "out_in_map_t"], kmap["sizes"][0]
+            reorder_loc = kmap["reorder_loc_t"] if ifsort else None
             out_coords, out_range = target
         else:
             kmap = caches.kmaps.get((x.stride, self.kernel_size, self.stride, self.dilation))
             if kmap is None:
                 return None
-            out_in_map, n_out = kmap["out_in_map"], kmap["sizes"][1]
+            if ifsort and (kmap.get("reorder_out_in_map") is None or kmap.get("_split") != 1):
+                return None
+            out_in_map, n_out = kmap["reorder_out_in_map" if ifsort else "out_in_map"], kmap["sizes"][1]
+            reorder_loc = kmap["reorder_loc"] if ifsort else None
             out_coords, out_range = kmap["coords"], kmap["spatial_range"]
             out_stride = tuple(a * b for a, b in zip(x.stride, self.stride))
         if feats.shape[1] % 8 != 0 or not feats.is_contiguous():
@@ -149,7 +158,7 @@ class FusedConv(nn.Module):
         if plan is None or not plan.valid_for(self.kernel, backends.allow_tf32):
             plan = self._plan = backend.IgemmLayerPlan(self.kernel, self.scale, self.shift, self.relu,
                                                        backends.allow_tf32)
-        out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu)
+        out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu, reorder_loc)
         caches.cmaps.setdefault(out_stride, (out_coords, out_range))
         return SparseTensor._from_parts(out, out_coords, out_stride, out_range, caches)
 
