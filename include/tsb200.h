@@ -171,6 +171,17 @@ int tsb_bitmask_reduce(const int32_t* bitmask, int64_t rows, int32_t split, int3
 int tsb_map_reorder(const int32_t* out_in_map, int64_t rows, int32_t kvol, const int32_t* reorder_loc,
                     int32_t split, int32_t* out, tsb_stream_t stream);
 
+/* The four steps above for one split in one call: bitmask of every row, stable descending sort,
+ * row-reordered map, per-tile OR of the sorted masks.  sorted_mask / reorder_loc int32 [rows],
+ * reordered_map int32 [rows, kvol], reduced_mask int32 [ceil(rows / tile)].  At batch 1 the host cost
+ * of four separate calls exceeds the device time of the steps.  No counterpart in the reference
+ * (its Python side chains derive_bitmask_from_out_in_map, torch.sort, reorder_out_in_map_cuda and
+ * reduce_bitmask_cuda, torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:86-111). */
+size_t tsb_map_sorted_workspace_bytes(int64_t rows);
+int tsb_map_sorted_artefacts(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n, int32_t tile,
+                             int32_t* sorted_mask, int32_t* reorder_loc, int32_t* reordered_map,
+                             int32_t* reduced_mask, void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+
 /* Pair lists for the GatherScatter / FetchOnDemand dataflows.
  * tsb_pairs_count: nbsizes int32 [kvol] = valid entries per column; also writes the
  * exclusive scans nbaddrs / qnbaddrs int32 [kvol+1] (q = 128 rounding).

@@ -57,6 +57,8 @@ SIGNATURES = {
     "tsb_count": (C.c_int, [P, I64, P, I64, P]),
     "tsb_voxelize_fwd": (C.c_int, [P, P, P, I64, I64, I32, I32, P, P]),
     "tsb_devoxelize_fwd": (C.c_int, [P, P, P, I64, I32, I32, P, P]),
+    "tsb_map_sorted_workspace_bytes": (SZ, [I64]),
+    "tsb_map_sorted_artefacts": (C.c_int, [P, I64, I32, I64, I32, P, P, P, P, P, SZ, P]),
     "tsb_quantize_workspace_bytes": (SZ, [I64]),
     "tsb_quantize_unique": (C.c_int, [P, I32, I64, P, P, P, P, P, P, P, SZ, P]),
     "tsb_to_dense_fwd": (C.c_int, [P, P, I64, I32, P, I32, P, P]),

@@ -26,7 +26,8 @@ from ._lib import lib, check, i32x
 __all__ = [
     "GPUHashTable", "build_kernel_map_subm_hashmap", "build_kernel_map_downsample_hashmap",
     "build_mask_from_kmap", "convert_transposed_out_in_map", "derive_bitmask_from_out_in_map",
-    "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "exclusive_scan_quantified_wrapper",
+    "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "sorted_artefacts_cuda",
+    "exclusive_scan_quantified_wrapper",
     "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda",
     "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
@@ -266,6 +267,23 @@ def sort_bitmask_cuda(bitmask: torch.Tensor, kvol: int = 27) -> Tuple[torch.Tens
     check(lib.tsb_bitmask_sort(_p(bitmask), rows, split, kvol, _p(sorted_mask), _p(loc), _p(ws), ws.numel(),
                                _stream()), "sort_bitmask_cuda")
     return sorted_mask, loc
+
+
+def sorted_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, m_tile: int):
+    """One-call form of derive_bitmask -> sort -> reorder -> reduce for a single split.
+    Returns (sorted_mask [1, rows], reorder_loc [1, rows], reordered_map [rows, Kvol],
+    reduced_mask [1, ceil(rows / m_tile)]), the same tensors the four separate calls return."""
+    _need_cuda(out_in_map)
+    rows, kvol = out_in_map.shape
+    dev = out_in_map.device
+    masks = torch.empty((2, 1, rows), dtype=torch.int32, device=dev)
+    reordered = torch.empty_like(out_in_map)
+    reduced = torch.empty((1, (rows - 1) // m_tile + 1 if rows else 0), dtype=torch.int32, device=dev)
+    ws = _workspace(lib.tsb_map_sorted_workspace_bytes(rows), dev)
+    check(lib.tsb_map_sorted_artefacts(_p(out_in_map), rows, kvol, int(valid_n), int(m_tile), _p(masks[0]),
+                                       _p(masks[1]), _p(reordered), _p(reduced), _p(ws), ws.numel(), _stream()),
+          "sorted_artefacts_cuda")
+    return masks[0], masks[1], reordered, reduced
 
 
 def reduce_bitmask_cuda(bitmask: torch.Tensor, m_tile: int) -> torch.Tensor:

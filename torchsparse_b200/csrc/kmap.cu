@@ -867,6 +867,30 @@ int tsb_map_reorder(const int32_t* out_in_map, int64_t rows, int32_t kvol, const
   return TSB_OK;
 }
 
+size_t tsb_map_sorted_workspace_bytes(int64_t rows) {
+  if (rows <= 0) return 256;
+  return align_up((size_t)rows * 4, 256) + sort_ws_layout(rows).total;
+}
+
+int tsb_map_sorted_artefacts(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n, int32_t tile,
+                             int32_t* sorted_mask, int32_t* reorder_loc, int32_t* reordered_map, int32_t* reduced_mask,
+                             void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (rows < 0 || kvol < 1 || valid_n < 0 || valid_n > rows) return TSB_ERR_BAD_ARG;
+  if (rows == 0) return TSB_OK;
+  if (!out_in_map || !sorted_mask || !reorder_loc || !reordered_map || !reduced_mask) return TSB_ERR_BAD_ARG;
+  const size_t mask_bytes = align_up((size_t)rows * 4, 256);
+  if (!workspace || workspace_bytes < mask_bytes + sort_ws_layout(rows).total) return TSB_ERR_WORKSPACE;
+  int32_t* bitmask = reinterpret_cast<int32_t*>(workspace);
+  char* sort_ws = reinterpret_cast<char*>(workspace) + mask_bytes;
+  int rc = tsb_bitmask_derive(out_in_map, rows, kvol, 1, valid_n, bitmask, stream);
+  if (rc != TSB_OK) return rc;
+  rc = tsb_bitmask_sort(bitmask, rows, 1, kvol, sorted_mask, reorder_loc, sort_ws, workspace_bytes - mask_bytes, stream);
+  if (rc != TSB_OK) return rc;
+  rc = tsb_map_reorder(out_in_map, rows, kvol, reorder_loc, 1, reordered_map, stream);
+  if (rc != TSB_OK) return rc;
+  return tsb_bitmask_reduce(sorted_mask, rows, 1, tile, reduced_mask, stream);
+}
+
 int tsb_scan_quantified(int32_t kvol, const int32_t* nbsizes, int32_t* nbaddrs, int32_t* qnbaddrs,
                         tsb_stream_t stream) {
   if (kvol < 1 || !nbsizes) return TSB_ERR_BAD_ARG;

@@ -59,6 +59,8 @@ def convert_transposed_out_in_map(out_in_map: torch.Tensor, size: int) -> torch.
 
 
 def _sorted_artefacts(out_in_map: torch.Tensor, split_mask_num: int, valid_n: int, tile: int = cta_M):
+    if split_mask_num == 1:
+        return backend.sorted_artefacts_cuda(out_in_map, valid_n, tile)
     bitmask = backend.derive_bitmask_from_out_in_map(out_in_map, split_mask_num, valid_n)
     sorted_mask, reorder_loc = backend.sort_bitmask_cuda(bitmask, out_in_map.shape[1])
     reorder_out_in_map = backend.reorder_out_in_map_cuda(out_in_map, reorder_loc)
