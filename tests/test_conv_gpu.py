@@ -68,8 +68,10 @@ def test_golden_fp32(golden, name, ks, st, dataflow):
                                                     ("FetchOnDemand", False, 1)])
 @pytest.mark.parametrize("ks,st,cin,cout", [(3, 1, 32, 32), (3, 1, 64, 96), (2, 2, 32, 64), (3, 2, 16, 16),
                                             (3, 1, 4, 32), (3, 1, 5, 19), (3, 1, 128, 128), (3, 1, 256, 256),
-                                            (3, 1, 384, 256), (3, 1, 72, 40)])
+                                            (3, 1, 384, 256), (3, 1, 72, 40), (5, 1, 16, 32)])
 def test_conv_vs_oracle(dtype, dataflow, ifsort, split, ks, st, cin, cout):
+    if ifsort and -(-int(np.prod(ko._as3(ks))) // split) > 31:
+        pytest.skip("a row's offset bitmask is one int32 per split (as in the reference): 31 offsets per split")
     rng = np.random.default_rng(cin * 1000 + cout)
     coords = random_coords(rng, 1500, (16, 16, 16), 2)
     feats = rng.standard_normal((coords.shape[0], cin)).astype(np.float32)

@@ -39,12 +39,14 @@ def _randomise_bn(model):
 
 
 def _gpu_forward(model, coords, feats, dtype, engine):
+    """engine: False = the module graph as written, True = fused inference engine,
+    "sorted" = the engine with row-sorted kernel maps at every level."""
     import torchsparse_b200 as ts
     from torchsparse_b200.nn import InferenceEngine
 
     m = model.cuda().to(dtype).eval()
     if engine:
-        m = InferenceEngine(m)
+        m = InferenceEngine(m, sort_max_stride=16 if engine == "sorted" else 0)
     x = ts.SparseTensor(torch.from_numpy(feats).cuda().to(dtype), torch.from_numpy(coords).cuda())
     with torch.no_grad():
         out = m(x)
@@ -56,7 +58,7 @@ def _gpu_forward(model, coords, feats, dtype, engine):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3)])
-@pytest.mark.parametrize("engine", [False, True])
+@pytest.mark.parametrize("engine", [False, True, "sorted"])
 def test_unet_matches_cpu_oracle(dtype, tol, engine):
     import copy
     from torchsparse_b200.backbones import SparseResUNet42
@@ -78,6 +80,28 @@ def test_unet_matches_cpu_oracle(dtype, tol, engine):
     assert err < tol, err
     err_mid = rel_l2(got[4].feats.float().cpu().numpy(), want[4].feats.numpy())   # bottleneck (stride 16)
     assert err_mid < tol, err_mid
+
+
+def test_unet_fp32_tensors_under_tf32():
+    """fp32 network with backends.allow_tf32 (the default on this hardware, as in the reference): every
+    convolution multiplies as TF32 on the tensor cores; coordinates stay bit-exact, features within 1e-2
+    of the exact-fp32 CPU evaluation after ~40 layers (10-bit mantissa operands, fp32 accumulation)."""
+    import copy
+    from torchsparse_b200 import backends
+    from torchsparse_b200.backbones import SparseResUNet42
+
+    torch.manual_seed(0)
+    model = SparseResUNet42(in_channels=4, width_multiplier=0.5)
+    _randomise_bn(model)
+    model.eval()
+    coords, feats = _scan_crop()
+    want = net_cpu.forward_cpu(copy.deepcopy(model).float(), coords, feats)
+    backends.allow_tf32 = True        # restored by the autouse fixture
+    got = _gpu_forward(copy.deepcopy(model), coords, feats, torch.float32, True)
+    for g, w in zip(got, want):
+        assert np.array_equal(g.coords.cpu().numpy(), w.coords.numpy())
+    err = rel_l2(got[-1].feats.cpu().numpy(), want[-1].feats.numpy())
+    assert 1e-6 < err < 1e-2, err     # not exact (tensor cores ran), and close
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3)])
