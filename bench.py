@@ -504,7 +504,7 @@ def run_reference(args):
 
 def run_layer(args, device):
     """Single sparse Conv3d layer (BASELINE config 5 cell): --layer N,Cin,Cout,kernel,stride,occupancy
-    [--dataflow ImplicitGEMM|GatherScatter|FetchOnDemand] [--dtype f16|bf16|f32] [--sorted].
+    [--dataflow ImplicitGEMM|GatherScatter|FetchOnDemand] [--dtype f16|bf16|f32|tf32] [--sorted].
     Prints one JSON line with time, useful TFLOP/s and algorithmic GB/s of the conv launch."""
     import torchsparse_b200 as ts
     from torchsparse_b200 import backend
@@ -513,7 +513,9 @@ def run_layer(args, device):
 
     n, cin, cout, ks, st = [int(v) for v in args.layer.split(",")[:5]]
     occ = float(args.layer.split(",")[5]) if len(args.layer.split(",")) > 5 else 0.05
-    dtype = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[args.dtype]
+    dtype = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32, "tf32": torch.float32}[args.dtype]
+    from torchsparse_b200 import backends
+    backends.allow_tf32 = args.dtype == "tf32"     # "f32" = exact fp32 arithmetic on the CUDA cores
     coords_np, side = uniform_voxels(0, n, occ)
     coords = torch.from_numpy(coords_np).to(device)
     g = torch.Generator(device=device).manual_seed(0)
