@@ -107,7 +107,7 @@ def forward_scan(model, pts_dev: torch.Tensor):
 
     vox, idx, (vmin, vmax) = sparse_quantize(pts_dev[:, :3], VOXEL, return_index=True, return_bounds=True)
     coords = torch.nn.functional.pad(vox, (1, 0))              # batch index 0 in front
-    feats = pts_dev[idx].half()
+    feats = torch.index_select(pts_dev, 0, idx).half()
     bounds = ((0, 0, 0, 0), (0,) + tuple(vmax))                # the points were shifted to start at the origin
     return model(ts.SparseTensor(feats, coords, coord_bounds=bounds))
 
