@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory from the REFERENCE project itself.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has a checkout of the reference project (its path is the optional first argument):
 
     python oracle/build_ref.py            # compiles the reference's CPU sources -> oracle/_ref/
     python tests/golden/make_golden.py
