@@ -191,7 +191,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     import torch.distributed as dist
     import torchsparse_b200  # noqa: F401  (fails loudly when libtsb200.so is missing)
     from torchsparse_b200 import backend
-    from torchsparse_b200.sharding import gather_rows_padded
+    from torchsparse_b200.sharding import PaddedGather
 
     from torchsparse_b200.nn import functional as F
     F.set_conv_mode(args.conv_mode)
@@ -212,7 +212,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         pts = h.to(device, non_blocking=True) if e2e else resident[i % SCAN_POOL]
         logits = forward_scan(model, pts)      # scans are independent: the only exchange is the gather of outputs
         if world > 1 and gather_inline:
-            gather_rows_padded(logits, MAX_VOXELS)
+            gather(logits)
         out = logits.cpu() if e2e else logits
         return logits, h.numel() * h.element_size(), (logits.numel() * logits.element_size() if e2e else 0)
 
@@ -240,6 +240,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     n_threads = max(1, min(args.host_threads, n_streams))
     side = [torch.cuda.Stream(device) for _ in range(n_streams)] if n_streams > 1 else [stream]
     comm_stream = torch.cuda.Stream(device) if world > 1 else None
+    gather = PaddedGather(MAX_VOXELS, 19, torch.float16, device) if world > 1 else None   # used on comm_stream only
 
     host_ms = {"issue": float("nan")}   # host wall time per step spent issuing the step (no final sync)
 
@@ -279,7 +280,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                 comm_stream.wait_event(produced)
                 with torch.cuda.stream(comm_stream):
                     logits.record_stream(comm_stream)
-                    gather_rows_padded(logits, MAX_VOXELS)
+                    gather(logits)
 
         if n_threads == 1:
             issue(0, 1)

@@ -6,7 +6,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from torchsparse_b200.sharding import balanced_assignment, gather_rows, gather_rows_padded, shard_range
+from torchsparse_b200.sharding import (PaddedGather, balanced_assignment, gather_rows, gather_rows_padded,
+                                       shard_range)
 
 
 def test_shard_range_covers_everything_once():
@@ -54,6 +55,11 @@ def _worker(rank, world, port, q):
         # the variant with a known row bound: same rows, counts stay a tensor, no host read inside
         buf, cnt = gather_rows_padded(local, 8)
         q.put((rank, buf.clone(), cnt.tolist(), "padded"))
+        # the same with buffers kept between calls: two calls with different row counts
+        pg = PaddedGather(8, 4, torch.float32, "cpu")
+        pg(local[:2])
+        buf, cnt = pg(local)
+        q.put((rank, buf.clone(), cnt.tolist(), "padded"))
     finally:
         dist.destroy_process_group()
 
@@ -66,7 +72,7 @@ def test_gather_rows_two_gloo_ranks():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=120) for _ in range(3 * world)]
+    results = [q.get(timeout=120) for _ in range(4 * world)]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
@@ -82,7 +88,7 @@ def test_gather_rows_two_gloo_ranks():
         assert rng == ((0, 5) if rank == 0 else (5, 10))
     for rank, out, counts, _ in second:
         assert counts == [0, 2] and out.shape == (2, 4)
-    assert len(padded) == world
+    assert len(padded) == 2 * world
     for rank, buf, counts, _ in padded:
         assert counts == [3, 5] and buf.shape == (2, 8, 4)
         assert torch.equal(torch.cat([buf[0, :3], buf[1, :5]]), expect)

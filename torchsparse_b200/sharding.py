@@ -8,7 +8,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "balanced_assignment", "gather_rows", "gather_rows_padded"]
+__all__ = ["shard_range", "balanced_assignment", "gather_rows", "gather_rows_padded", "PaddedGather"]
 
 
 def shard_range(n_items: int, world_size: int, rank: int) -> Tuple[int, int]:
@@ -77,3 +77,37 @@ def gather_rows_padded(local: torch.Tensor, max_rows: int, group: Optional[dist.
     buf = torch.empty((world, max_rows) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf.view((world * max_rows,) + tuple(local.shape[1:])), padded, group=group)
     return buf, counts
+
+
+class PaddedGather:
+    """gather_rows_padded with its buffers allocated once: for a loop that gathers the output of every
+    step, where the per-call allocations and small host calls would otherwise be paid each time.
+    All calls must be made on the same stream (the buffers are reused in stream order).  Returns views
+    of the internal buffers, valid until the next call."""
+
+    def __init__(self, max_rows: int, cols: int, dtype: torch.dtype, device,
+                 group: Optional[dist.ProcessGroup] = None) -> None:
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.max_rows = max_rows
+        self.padded = torch.zeros((max_rows, cols), dtype=dtype, device=device)
+        self.buf = torch.empty((self.world, max_rows, cols), dtype=dtype, device=device)
+        self.n_host = torch.zeros(1, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else \
+            torch.zeros(1, dtype=torch.int64)
+        self.n_dev = torch.zeros(1, dtype=torch.int64, device=device)
+        self.counts = torch.zeros(self.world, dtype=torch.int64, device=device)
+
+    def __call__(self, local: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        rows = local.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed max_rows={self.max_rows}")
+        self.n_host[0] = rows
+        self.n_dev.copy_(self.n_host, non_blocking=True)
+        self.padded[:rows].copy_(local)
+        if self.world == 1:
+            self.counts.copy_(self.n_dev)
+            self.buf[0].copy_(self.padded)
+        else:
+            dist.all_gather_into_tensor(self.counts, self.n_dev, group=self.group)
+            dist.all_gather_into_tensor(self.buf.view(self.world * self.max_rows, -1), self.padded, group=self.group)
+        return self.buf, self.counts
