@@ -33,13 +33,19 @@
 //               many offsets they hold, so a fixed assignment would leave CTAs idle at the end), stages
 //               its map slice and offset mask for the other roles
 //
+// Pair-list mode (the GatherScatter / FetchOnDemand dataflows, conv_pairs.cu): the map is one column of
+// input rows, every 128-row tile belongs to one kernel offset (tile_k[tile] picks its weight block),
+// and the fp32 products are either stored as rows of a buffer or added to the output rows with
+// 16-byte atomic adds.
+//
 // Every wait on an mbarrier is bounded: when it runs out the thread records an error code and the
 // CTA stops issuing work, gives its copies in flight time to land, frees its TMEM and returns.
 #include <cuda.h>
 
-#include <atomic>
 #include <cstdlib>
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "conv_dispatch.h"
@@ -773,9 +779,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   }
 }
 
-// Scheduling words of the launches in flight: slot = launch sequence number modulo kSchedSlots.  A slot is
-// zero whenever no launch uses it (zero-initialised, and every launch zeroes its slot when its last CTA
-// leaves), and kernels that run at the same time (different streams) are at most a few launches apart.
+// Scheduling words, one slot per stream: launches on one stream run one after another, so they can share
+// a slot (zero-initialised, and every launch zeroes it again when its last CTA leaves); launches on
+// different streams may overlap and get different slots.
 constexpr int kSchedSlots = 1024;
 __device__ int g_sched_slots[kSchedSlots * 2];
 
@@ -843,10 +849,13 @@ void pick_config(int n_tile, int kvol, int* stages, int* ring, int* ctas) {
   else { *stages = best[1]; *ring = 3; }
 }
 
-// device address of g_sched_slots on the current device (looked up once per device)
-int* sched_slots() {
+// scheduling words of `stream` on the current device (the array's address is looked up once per device,
+// a stream gets the next free slot the first time it launches a convolution)
+int* sched_slot_of(cudaStream_t stream) {
   static std::mutex mu;
   static int* addr[64] = {nullptr};
+  static std::map<std::pair<int, cudaStream_t>, int> slot_of;
+  static int next_slot[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
@@ -855,7 +864,9 @@ int* sched_slots() {
     if (cudaGetSymbolAddress(&ptr, g_sched_slots) != cudaSuccess) return nullptr;
     addr[dev] = reinterpret_cast<int*>(ptr);
   }
-  return addr[dev];
+  auto it = slot_of.find({dev, stream});
+  if (it == slot_of.end()) it = slot_of.emplace(std::make_pair(dev, stream), next_slot[dev]++ % kSchedSlots).first;
+  return addr[dev] + 2 * it->second;
 }
 
 int num_sms() {
@@ -940,12 +951,8 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   p.residual = a.residual; p.error = err;
   p.tile_k = a.tile_k; p.out_fp32 = a.out_fp32; p.atomic_out = a.atomic_out;
   p.dst_rows = (int)(a.dst_rows > 0 ? a.dst_rows : a.n_out);
-  {
-    int* slots = sched_slots();
-    if (!slots) return TSB_ERR_CUDA;
-    static std::atomic<unsigned> seq{0};
-    p.sched = slots + 2 * (seq.fetch_add(1) % kSchedSlots);
-  }
+  p.sched = sched_slot_of(s);
+  if (!p.sched) return TSB_ERR_CUDA;
   p.trace = nullptr; p.trace_cta = 0;
   if (const char* tr = getenv("TSB_UMMA_TRACE")) {   // debugging aid: address of a 256x8 int64 device buffer
     p.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
