@@ -347,10 +347,10 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     sampler = ClockSampler(device.index or 0) if rank == 0 else None
     ms_total, launches, _, _ = timed(False, False)
     host_issue_ms = host_ms["issue"]
-    clocks = sampler.stop() if sampler else None
     e2e_ms, h2d, d2h = float("nan"), 0, 0
     if not args.no_e2e:
         e2e_ms, _, h2d, d2h = timed(True, False)
+    clocks = sampler.stop() if sampler else None     # sampled over both timed passes
     # per-launch durations for the roofline: the same K steps once more, issued serially on one stream
     # with an event pair around every convolution launch (under concurrent streams an event pair would
     # also time the other stream's kernels)
