@@ -346,6 +346,25 @@ def conv_from_map(feats, weight, out_in_map, n_out, dtype=np.float64):
     return y
 
 
+def conv_backward_from_map(feats, weight, out_in_map, n_out, grad_out, dtype=np.float64):
+    """Gradients of y = conv_from_map(feats, weight, out_in_map, n_out) for an upstream grad_out:
+    dX[map[m][k]] += dY[m] @ W[k]^T and dW[k] += X[map[m][k]]^T @ dY[m]
+    (the sums the reference's dgrad / wgrad kernels compute,
+    torchsparse/nn/functional/conv/func/implicit_gemm.py:108-193)."""
+    x = feats.astype(dtype)
+    w = weight.astype(dtype)
+    dy = grad_out.astype(dtype)
+    dx = np.zeros_like(x)
+    dw = np.zeros_like(w)
+    for k in range(w.shape[0]):
+        col = out_in_map[:n_out, k]
+        rows = np.nonzero(col >= 0)[0]
+        if rows.size:
+            np.add.at(dx, col[rows], dy[rows] @ w[k].T)
+            dw[k] = x[col[rows]].T @ dy[rows]
+    return dx, dw
+
+
 def conv_from_pairs(feats, weight, nbmaps, nbsizes, n_out, transpose=False, dtype=np.float64):
     """Gather -> matmul -> scatter-add per kernel offset
     (torchsparse/backend/convolution/convolution_gather_scatter_cpu.cpp:38-109)."""

@@ -116,6 +116,74 @@ def test_conv_tf32_vs_oracle(dataflow, ifsort, ks, st, cin, cout):
         assert err > 1e-6            # the tensor-core path ran (exact fp32 would be ~1e-7)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 4e-3)])
+@pytest.mark.parametrize("dataflow", ["ImplicitGEMM", "GatherScatter", "FetchOnDemand"])
+@pytest.mark.parametrize("ks,st,cin,cout", [(3, 1, 32, 48), (2, 2, 32, 64), (3, 2, 16, 16), (3, 1, 5, 19)])
+def test_conv_backward_vs_oracle(dtype, tol, dataflow, ks, st, cin, cout):
+    """Input and weight gradients of a single layer against the fp64 oracle (fp16: both gradients are
+    rounded to fp16, the weight gradient after a sum over ~10^3 pairs, hence the wider bound)."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(cin * 100 + cout + 3)
+    coords = random_coords(rng, 1200, (14, 14, 14), 2)
+    n = coords.shape[0]
+    feats = rng.standard_normal((n, cin)).astype(np.float32)
+    kvol = int(np.prod(ko._as3(ks)))
+    w = (rng.standard_normal((kvol, cin, cout)) * np.sqrt(2.0 / (kvol * cin))).astype(np.float32)
+    pad = tuple((k - 1) // 2 if (k % 2 == 1 and s == 1) else 0 for k, s in zip(ko._as3(ks), ko._as3(st)))
+    km = ko.build_kmap(coords, ks, st, pad)
+    m = km["sizes"][1]
+    gy = rng.standard_normal((m, cout)).astype(np.float32)
+    f_r = torch.from_numpy(feats).to(dtype).float().numpy()
+    w_r = torch.from_numpy(w).to(dtype).float().numpy()
+    g_r = torch.from_numpy(gy).to(dtype).float().numpy()
+    want_dx, want_dw = ko.conv_backward_from_map(f_r, w_r, km["out_in_map"], m, g_r)
+
+    x_feats = torch.from_numpy(feats).cuda().to(dtype).requires_grad_(True)
+    wt = torch.from_numpy(w).cuda().to(dtype).requires_grad_(True)
+    x = ts.SparseTensor(x_feats, torch.from_numpy(coords).cuda())
+    y = F.conv3d(x, wt, ks, None, st, pad, config=_cfg(dataflow))
+    assert y.feats.requires_grad and y.feats.shape == (m, cout)
+    y.feats.backward(torch.from_numpy(gy).cuda().to(dtype))
+    assert x_feats.grad.dtype == dtype and wt.grad.dtype == dtype
+    assert rel_l2(x_feats.grad.float().cpu().numpy(), want_dx) < tol
+    assert rel_l2(wt.grad.float().cpu().numpy(), want_dw) < tol
+
+
+def test_transposed_conv_backward_vs_oracle():
+    """Strided conv followed by its transposed conv, gradients through both (fp32, exact arithmetic)."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(77)
+    coords = random_coords(rng, 1000, (12, 12, 12))
+    n = coords.shape[0]
+    feats = rng.standard_normal((n, 16)).astype(np.float32)
+    w1 = (rng.standard_normal((8, 16, 24)) * 0.2).astype(np.float32)
+    w2 = (rng.standard_normal((8, 24, 8)) * 0.2).astype(np.float32)
+    km = ko.build_kmap(coords, 2, 2, 0)
+    m = km["sizes"][1]
+    map_t = ko.transpose_map(km["out_in_map"], (n + 127) // 128 * 128)
+    gy = rng.standard_normal((n, 8)).astype(np.float32)
+    # oracle: h = conv(x, w1, map); y = conv(h, w2, map_t)
+    h = ko.conv_from_map(feats, w1, km["out_in_map"], m)
+    want_dh, want_dw2 = ko.conv_backward_from_map(h, w2, map_t, n, gy)
+    want_dx, want_dw1 = ko.conv_backward_from_map(feats, w1, km["out_in_map"], m, want_dh)
+
+    xf = torch.from_numpy(feats).cuda().requires_grad_(True)
+    t1 = torch.from_numpy(w1).cuda().requires_grad_(True)
+    t2 = torch.from_numpy(w2).cuda().requires_grad_(True)
+    x = ts.SparseTensor(xf, torch.from_numpy(coords).cuda())
+    hh = F.conv3d(x, t1, 2, None, 2, 0)
+    yy = F.conv3d(hh, t2, 2, None, 2, 0, transposed=True)
+    assert yy.feats.shape == (n, 8)
+    yy.feats.backward(torch.from_numpy(gy).cuda())
+    assert rel_l2(xf.grad.cpu().numpy(), want_dx) < 1e-5
+    assert rel_l2(t1.grad.cpu().numpy(), want_dw1) < 1e-5
+    assert rel_l2(t2.grad.cpu().numpy(), want_dw2) < 1e-5
+
+
 def test_baseline_config1_all_dataflows():
     """BASELINE config 1: 20 000 voxels in [0,128)^3, 32->32, k3 s1, fp32, batch 1."""
     rng = np.random.default_rng(0)

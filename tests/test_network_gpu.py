@@ -162,3 +162,30 @@ def test_batched_scans_equal_single_scans():
     assert bool((y.coords[n0:, 0] == 1).all())
     assert rel_l2(y.feats[:n0].cpu().numpy(), outs[0].feats.cpu().numpy()) < 1e-5
     assert rel_l2(y.feats[n0:].cpu().numpy(), outs[1].feats.cpu().numpy()) < 1e-5
+
+
+def test_training_step_through_a_unet():
+    """Forward + backward through the whole module graph (train mode, BatchNorm on batch statistics):
+    every convolution kernel receives a finite, non-zero gradient and an SGD step lowers the loss."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.backbones import SparseResUNet42
+
+    torch.manual_seed(0)
+    model = SparseResUNet42(in_channels=4, width_multiplier=0.25).cuda().train()
+    coords, feats = _scan_crop()
+    c = torch.from_numpy(coords).cuda()
+    f = torch.from_numpy(feats).cuda()
+    target = torch.randn(c.shape[0], model(ts.SparseTensor(f, c))[-1].feats.shape[1], device="cuda")
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        out = model(ts.SparseTensor(f, c))[-1].feats
+        loss = torch.nn.functional.mse_loss(out, target)
+        loss.backward()
+        losses.append(float(loss.detach()))
+        kernels = [p for n, p in model.named_parameters() if n.endswith("kernel")]
+        assert kernels and all(p.grad is not None and torch.isfinite(p.grad).all() for p in kernels)
+        assert all(float(p.grad.abs().max()) > 0 for p in kernels)
+        opt.step()
+    assert losses[-1] < losses[0], losses

@@ -28,7 +28,7 @@ __all__ = [
     "build_mask_from_kmap", "convert_transposed_out_in_map", "derive_bitmask_from_out_in_map",
     "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "sorted_artefacts_cuda",
     "exclusive_scan_quantified_wrapper",
-    "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda",
+    "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda", "conv_backward_wgrad_pairs_cuda",
     "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
     "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
@@ -532,6 +532,31 @@ def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: 
     if rc != 0:
         check(rc, "conv_forward_implicit_gemm_cuda")
     return out
+
+
+def conv_backward_wgrad_pairs_cuda(grad_out: torch.Tensor, in_feats: torch.Tensor, nbmaps: torch.Tensor,
+                                   nbsizes_host, transposed: bool = False) -> torch.Tensor:
+    """Weight gradient dW[k] = X[in_k]^T . dY[out_k] over the pair list of every kernel offset
+    (nbmaps int32 [P,2] = (input row, output row), segments of nbsizes_host[k] pairs; the columns swap
+    roles for a transposed convolution).  Returns [Kvol, Cin, Cout] in the dtype of in_feats.
+    The rows are gathered once and the per-offset products are plain GEMMs on torch's cuBLAS handle,
+    as in the reference's gather-scatter backward
+    (torchsparse/backend/convolution/convolution_gather_scatter_cuda.cu:640-800); the reference's
+    implicit-GEMM wgrad kernels (convolution_backward_wgrad_implicit_gemm_cuda.cu) compute the same sums."""
+    _need_cuda(grad_out, in_feats, nbmaps)
+    kvol = len(nbsizes_host)
+    cin, cout = in_feats.shape[1], grad_out.shape[1]
+    x_col, y_col = (1, 0) if transposed else (0, 1)
+    pairs = nbmaps.long()
+    xg = in_feats.index_select(0, pairs[:, x_col])
+    yg = grad_out.to(in_feats.dtype).index_select(0, pairs[:, y_col])
+    dw = torch.zeros((kvol, cin, cout), dtype=in_feats.dtype, device=in_feats.device)
+    start = 0
+    for k, size in enumerate(nbsizes_host):
+        if size:
+            torch.mm(xg[start:start + size].t(), yg[start:start + size], out=dw[k])
+        start += size
+    return dw
 
 
 def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,

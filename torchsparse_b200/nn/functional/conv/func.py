@@ -1,4 +1,4 @@
-"""The three dataflows as autograd Functions (forward only)
+"""The three dataflows as autograd Functions
 (torchsparse/nn/functional/conv/func/{implicit_gemm,gather_scatter,fetch_on_demand}.py)."""
 from typing import Dict
 
@@ -19,18 +19,54 @@ def _cast_pair(input: torch.Tensor, weight: torch.Tensor):
     return input, weight
 
 
-class _ForwardOnly(Function):
+def _remember(ctx, input: torch.Tensor, weight: torch.Tensor, kmap: Dict, transposed: bool) -> None:
+    """What backward needs (ctx is None when the forward runs outside autograd)."""
+    if ctx is not None:
+        ctx.save_for_backward(input, weight)
+        ctx.kmap, ctx.transposed = kmap, transposed
+
+
+class _SparseConvFunction(Function):
+    """Backward shared by the three dataflows (torchsparse/nn/functional/conv/func/implicit_gemm.py:108-193):
+
+    * dgrad: the implicit-GEMM *forward* kernel run on grad_output with W transposed per offset and the
+      transposed kernel map (input row -> output rows), as the reference does;
+    * wgrad: dW[k] = X[in_k]^T . dY[out_k] over the pair lists (gathers + one GEMM per offset)."""
+
     @staticmethod
-    def backward(ctx, grad_output):
-        raise NotImplementedError("the backward pass (dgrad / wgrad) of the sparse convolution is not built yet")
+    def backward(ctx, grad_output: torch.Tensor):
+        from .kmap import transpose_kernel_map
+
+        input, weight = ctx.saved_tensors
+        kmap, transposed = ctx.kmap, ctx.transposed
+        x, w = _cast_pair(input.contiguous(), weight.contiguous())
+        dy = grad_output.contiguous().to(w.dtype)
+        kvol, cin, cout = w.shape
+        grad_input = grad_weight = None
+        if ctx.needs_input_grad[0]:
+            if transposed:
+                bwd_map = kmap["out_in_map"]               # rows: inputs of the transposed conv
+            else:
+                bwd_map = transpose_kernel_map(kmap)["out_in_map_t"]
+            grad_input = backend.conv_forward_implicit_gemm_cuda(
+                dy, w.transpose(1, 2).contiguous(), bwd_map, x.shape[0], cin, backends.allow_tf32,
+                backends.allow_fp16).to(input.dtype)
+        if ctx.needs_input_grad[1]:
+            pairs = kmap.get("_bwd_pairs")
+            if pairs is None:
+                nbmaps, _, sizes_host, _, _, _ = backend.pairs_from_out_in_map(kmap["out_in_map"], False)
+                pairs = kmap["_bwd_pairs"] = (nbmaps, sizes_host)
+            grad_weight = backend.conv_backward_wgrad_pairs_cuda(dy, x, pairs[0], pairs[1], transposed).to(weight.dtype)
+        return grad_input, grad_weight, None, None, None, None
 
 
-class ImplicitGEMMConvolutionFuntion(_ForwardOnly):
+class ImplicitGEMMConvolutionFuntion(_SparseConvFunction):
     @staticmethod
     def forward(ctx, input: torch.Tensor, weight: torch.Tensor, kmap: Dict, config: Dict,
                 transposed: bool = False, epilogue: Dict = None) -> torch.Tensor:
         if input.device.type != "cuda":
             raise NotImplementedError
+        _remember(ctx, input, weight, kmap, transposed)
         sizes = kmap["sizes"]
         sfx = "_t" if transposed else ""
         input, weight = _cast_pair(input.contiguous(), weight.contiguous())
@@ -48,12 +84,13 @@ class ImplicitGEMMConvolutionFuntion(_ForwardOnly):
         return out.to(weight.dtype)
 
 
-class GatherScatterConvolutionFuntion(_ForwardOnly):
+class GatherScatterConvolutionFuntion(_SparseConvFunction):
     @staticmethod
     def forward(ctx, input: torch.Tensor, weight: torch.Tensor, kmap: Dict, config: Dict,
                 transposed: bool = False, epilogue: Dict = None) -> torch.Tensor:
         if input.device.type != "cuda":
             raise NotImplementedError
+        _remember(ctx, input, weight, kmap, transposed)
         sizes = kmap["sizes"]
         input, weight = _cast_pair(input.contiguous(), weight.contiguous())
         sizes_host = kmap.get("nbsizes_host")
@@ -66,12 +103,13 @@ class GatherScatterConvolutionFuntion(_ForwardOnly):
         return out.to(weight.dtype)
 
 
-class FetchOnDemandConvolutionFuntion(_ForwardOnly):
+class FetchOnDemandConvolutionFuntion(_SparseConvFunction):
     @staticmethod
     def forward(ctx, input: torch.Tensor, weight: torch.Tensor, kmap: Dict, config: Dict,
                 transposed: bool = False, epilogue: Dict = None) -> torch.Tensor:
         if input.device.type != "cuda":
             raise NotImplementedError
+        _remember(ctx, input, weight, kmap, transposed)
         sizes = kmap["sizes"]
         input, weight = _cast_pair(input.contiguous(), weight.contiguous())
         nbmaps = kmap["nbmaps"]
