@@ -108,7 +108,7 @@ def _in_bounds(c: np.ndarray, cmin, cmax) -> np.ndarray:
 
 
 # --------------------------------------------------------------------------- bounds
-def coords_bounds(coords, kernel_size, stride, padding, subm, spatial_range=None):
+def coords_bounds(coords, kernel_size, stride, padding, subm, spatial_range=None, allow_negative=False):
     """coords_min / coords_max as the Python side of the reference derives them
     (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:24-45).
 
@@ -127,6 +127,11 @@ def coords_bounds(coords, kernel_size, stride, padding, subm, spatial_range=None
             # floor division, as torch's ``//`` on integer tensors
             cmax[1:] = np.floor_divide(cmax[1:] + 2 * pd - (ks - 1), st)
     cmin = np.zeros(4, dtype=np.int64)
+    if allow_negative and coords.shape[0]:
+        # torchsparse.tensor.get_allow_negative_coordinates() branch (hashmap_on_the_fly.py:39-43):
+        # torch.div is a true division; storing it into the int tensor truncates toward zero
+        cmin = coords.astype(np.int64).min(axis=0)
+        cmin[1:] = np.trunc((cmin[1:] - 2 * pd + (ks - 1)) / st).astype(np.int64)
     return cmin, cmax
 
 
@@ -466,7 +471,7 @@ def sparse_quantize(coords, voxel_size=1, return_index=False, return_inverse=Fal
 
 
 # --------------------------------------------------------------------------- one-call kernel-map builder
-def build_kmap(coords, kernel_size, stride=1, padding=0, spatial_range=None):
+def build_kmap(coords, kernel_size, stride=1, padding=0, spatial_range=None, allow_negative=False):
     """The ``hashmap_on_the_fly`` kernel map as a dict with the reference's keys
     (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:10-109)."""
     ks, st, pd = _as3(kernel_size), _as3(stride), _as3(padding)
@@ -475,7 +480,7 @@ def build_kmap(coords, kernel_size, stride=1, padding=0, spatial_range=None):
     if spatial_range is not None:
         new_range = (spatial_range[0],) + tuple(
             (spatial_range[i + 1] + 2 * pd[i] - (ks[i] - 1) - 1) // st[i] + 1 for i in range(3))
-    cmin, cmax = coords_bounds(coords, ks, st, pd, subm, new_range)
+    cmin, cmax = coords_bounds(coords, ks, st, pd, subm, new_range, allow_negative)
     if subm:
         m = subm_map(coords, ks, cmin, cmax)
         out_coords = coords

@@ -185,3 +185,29 @@ def test_empty_and_vanishing_inputs():
     assert y.coords.shape == (0, 4) and y.feats.shape == (0, 16)
     z = F.conv3d(y, torch.ones(27, 16, 16, device="cuda"), 3, None, 1, 1)
     assert z.feats.shape == (0, 16)
+
+
+@pytest.mark.parametrize("ks,st,pd", [(3, 1, 1), (2, 2, 0), (3, 2, 1)])
+def test_negative_coordinates(ks, st, pd):
+    """set_allow_negative_coordinates(True): the key space starts at the (padding-adjusted) smallest
+    coordinate instead of 0 (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:39-43);
+    maps and output coordinates bit-exact against the oracle run with the same bound rule."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+    from torchsparse_b200.tensor import set_allow_negative_coordinates
+
+    rng = np.random.default_rng(5)
+    coords = random_coords(rng, 3000, (24, 20, 16), 2)
+    coords[:, 1:] -= np.array([11, 7, 9], dtype=np.int32)          # roughly centred on the origin
+    want = ko.build_kmap(coords, ks, st, pd, allow_negative=True)
+    set_allow_negative_coordinates(True)
+    try:
+        x = ts.SparseTensor(torch.zeros(coords.shape[0], 8, device="cuda"), torch.from_numpy(coords).cuda())
+        w = torch.zeros(ks ** 3, 8, 8, device="cuda")
+        y = F.conv3d(x, w, ks, None, st, pd)
+        kmap = x._caches.kmaps[((1, 1, 1), (ks,) * 3, (st,) * 3, (1, 1, 1))]
+    finally:
+        set_allow_negative_coordinates(False)
+    assert np.array_equal(y.coords.cpu().numpy(), want["coords"])
+    assert np.array_equal(kmap["out_in_map"].cpu().numpy(), want["out_in_map"])
+    assert (want["coords"][:, 1:] < 0).any()

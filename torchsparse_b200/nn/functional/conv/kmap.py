@@ -113,15 +113,24 @@ def build_kernel_map(
     coords = _coords.contiguous()
     n = coords.shape[0]
     cmin_act, cmax_act = _actual_bounds(coords, caches, tensor_stride)
+    from ....tensor import get_allow_negative_coordinates
+    if get_allow_negative_coordinates():
+        # lower bound of the key space as the reference derives it
+        # (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:39-43): a true division whose
+        # result is truncated toward zero when it is stored back into the integer tensor
+        cmin_key = (cmin_act[0],) + tuple(
+            int((cmin_act[1 + i] - 2 * padding[i] + (kernel_size[i] - 1)) / stride[i]) for i in range(3))
+    else:
+        cmin_key = (0, 0, 0, 0)
 
     if subm:
         table_bounds = caches.hash_bounds.get(tensor_stride) if (caches is not None and hashmap_keys is not None) else None
         if table_bounds is not None:
             cmin, cmax = table_bounds
         elif new_range is not None:
-            cmin, cmax = cmin_act, tuple(v - 1 for v in new_range)
+            cmin, cmax = cmin_key, tuple(v - 1 for v in new_range)
         else:
-            cmin, cmax = cmin_act, cmax_act
+            cmin, cmax = cmin_key, cmax_act
         to_insert = hashmap_keys is None or table_bounds is None
         if to_insert:
             cap = _table_capacity(n)
@@ -136,14 +145,10 @@ def build_kernel_map(
     else:
         if new_range is not None:
             cmax_out = tuple(v - 1 for v in new_range)
-            cmin_out = cmin_act
         else:
             cmax_out = (cmax_act[0],) + tuple(
                 (cmax_act[1 + i] + 2 * padding[i] - (kernel_size[i] - 1)) // stride[i] for i in range(3))
-            # (negative-coordinate mode: the reference shifts the lower bound the same way)
-            cmin_out = (cmin_act[0],) + tuple(
-                int((cmin_act[1 + i] - 2 * padding[i] + (kernel_size[i] - 1)) / stride[i]) if cmin_act[1 + i] else 0
-                for i in range(3))
+        cmin_out = cmin_key
         uniq, m, out_max = backend.downsample_unique(coords, cmin_out, cmax_out, kernel_size, stride, padding)
         cap = _table_capacity(max(n, m))
         hashmap_keys = torch.zeros(cap, dtype=torch.int64, device=coords.device)
