@@ -189,3 +189,32 @@ def test_training_step_through_a_unet():
         assert all(float(p.grad.abs().max()) > 0 for p in kernels)
         opt.step()
     assert losses[-1] < losses[0], losses
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_tune_assigns_a_config_per_group_and_keeps_results(fused):
+    """utils.tune.tune: every group of convolutions sharing a kernel map gets one of the candidates,
+    and the tuned model computes the same function."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.backbones import SparseResUNet42
+    from torchsparse_b200.nn import InferenceEngine
+    from torchsparse_b200.utils.tune import default_candidates, tune
+
+    torch.manual_seed(0)
+    model = SparseResUNet42(in_channels=4, width_multiplier=0.5)
+    _randomise_bn(model)
+    model = model.cuda().half().eval()
+    if fused:
+        model = InferenceEngine(model)
+    coords, feats = _scan_crop()
+    c = torch.from_numpy(coords).cuda()
+    f = torch.from_numpy(feats).cuda().half()
+    with torch.no_grad():
+        before = model(ts.SparseTensor(f, c))[-1].feats.float()
+    choice = tune(model, [ts.SparseTensor(f, c)], warmup=1, iters=2)
+    names = {name for name, _ in default_candidates()}
+    assert len(choice) >= 8 and set(choice.values()) <= names
+    assert any(key[3] for key in choice) and any(key[2] != (1, 1, 1) for key in choice)   # transposed, strided groups
+    with torch.no_grad():
+        after = model(ts.SparseTensor(f, c))[-1].feats.float()
+    assert rel_l2(after.cpu().numpy(), before.cpu().numpy()) < 2e-3
