@@ -74,6 +74,16 @@ int tsb_hash_insert(int64_t* table_keys, int32_t* table_vals, int64_t capacity,
 int tsb_hash_lookup(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity,
                     const int64_t* keys, int64_t n, int32_t* out_vals, tsb_stream_t stream);
 
+/* Kernel-map lookup of the "hashmap" mode: the table holds FNV-1a hashes of (x, y, z, b) rows
+ * (tsb_coord_hash + tsb_hash_insert); out int32 [pad128(n), kvol] (zero-filled by the call) gets, for
+ * output row i and kernel index k, the value stored for  coords[i] * stride + digit_k - (kernel - 1) / 2,
+ * i.e. input row + 1, or 0.  coords_xyzb: int32 [n,4] in (x, y, z, batch) order; kernel_size / stride:
+ * host int32 [3].  Replaces GPUHashTable::lookup_coords
+ * (torchsparse/backend/hashmap/hashmap_cuda.cuh:200-254, 307-314). */
+int tsb_hash_lookup_coords(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity,
+                           const int32_t* coords_xyzb, int64_t n, const int32_t* kernel_size,
+                           const int32_t* stride, int32_t* out, tsb_stream_t stream);
+
 /* Join: out[i] = value stored for query[i] minus 1, i.e. row of the reference key or -1.
  * Builds a private table inside `workspace` (tsb_hash_query_workspace_bytes(n_ref)).
  * Replaces hash_query_cuda (torchsparse/backend/others/query_cuda.cu:33-47). */

@@ -471,6 +471,45 @@ def sparse_quantize(coords, voxel_size=1, return_index=False, return_inverse=Fal
 
 
 # --------------------------------------------------------------------------- one-call kernel-map builder
+def build_kmap_hashmap_mode(coords, kernel_size, stride=1, padding=0, spatial_range=None):
+    """The kernel map of ``kmap_mode="hashmap"``
+    (torchsparse/nn/functional/conv/kmap/func/hashmap.py:8-105, kmap/downsample.py:11-79,
+    backend/hashmap/hashmap_cuda.cuh:200-254): output coordinates = unique rows of floor(c / stride) when
+    every stride is 1 or the kernel size, else the natively enumerated strided outputs; for output row i
+    and kernel index k the input at ``out * stride + digit_k - (kernel - 1) // 2`` (x the fastest digit
+    for an odd kernel volume, z for an even one), -1 when there is none.  Padding plays no part in the
+    lookup.  Coordinates are matched exactly (the reference matches 64-bit FNV hashes of them)."""
+    ks, st, pd = _as3(kernel_size), _as3(stride), _as3(padding)
+    subm = not any(s > 1 for s in st)
+    coords = np.asarray(coords, dtype=np.int32)
+    if subm:
+        out_coords = coords
+    elif all(st[i] in (1, ks[i]) for i in range(3)):
+        c = coords.astype(np.int64).copy()
+        c[:, 1:] = np.floor(c[:, 1:] / np.array(st, dtype=np.float64)).astype(np.int64)
+        out_coords = np.unique(c, axis=0).astype(np.int32)
+    else:
+        new_range = None
+        if spatial_range is not None:               # the strided output range, as build_kmap derives it
+            new_range = (spatial_range[0],) + tuple(
+                (spatial_range[i + 1] + 2 * pd[i] - (ks[i] - 1) - 1) // st[i] + 1 for i in range(3))
+        cmin, cmax = coords_bounds(coords, ks, st, pd, False, new_range)
+        out_coords = downsample_map(coords, ks, st, pd, cmin, cmax)[1]
+    index = {tuple(int(v) for v in row): i for i, row in enumerate(coords)}
+    kvol = ks[0] * ks[1] * ks[2]
+    m = out_coords.shape[0]
+    out = np.full(((m + 127) // 128 * 128, kvol), -1, dtype=np.int32)
+    digits = kernel_digits(ks)
+    for i in range(m):
+        b, x, y, z = (int(v) for v in out_coords[i])
+        for k in range(kvol):
+            dx, dy, dz = (int(v) for v in digits[k])
+            key = (b, x * st[0] + dx - (ks[0] - 1) // 2, y * st[1] + dy - (ks[1] - 1) // 2,
+                   z * st[2] + dz - (ks[2] - 1) // 2)
+            out[i, k] = index.get(key, -1)
+    return {"out_in_map": out, "coords": out_coords, "sizes": (coords.shape[0], m)}
+
+
 def build_kmap(coords, kernel_size, stride=1, padding=0, spatial_range=None, allow_negative=False):
     """The ``hashmap_on_the_fly`` kernel map as a dict with the reference's keys
     (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:10-109)."""

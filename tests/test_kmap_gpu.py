@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import random_coords
+from conftest import random_coords, rel_l2
 from oracle import kmap_oracle as ko
 
 pytestmark = pytest.mark.gpu
@@ -211,3 +211,44 @@ def test_negative_coordinates(ks, st, pd):
     assert np.array_equal(y.coords.cpu().numpy(), want["coords"])
     assert np.array_equal(kmap["out_in_map"].cpu().numpy(), want["out_in_map"])
     assert (want["coords"][:, 1:] < 0).any()
+
+
+@pytest.mark.parametrize("ks,st,pd", [(3, 1, 1), (2, 2, 0), (3, 2, 1), (2, 1, 0), ((1, 3, 1), (1, 2, 1), 0)])
+def test_kmap_mode_hashmap(ks, st, pd):
+    """kmap_mode="hashmap": spdownsample output coordinates, FNV-keyed table (GPUHashTable.insert_coords /
+    lookup_coords), map bit-exact against the oracle, and the convolution on that map."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(9)
+    coords = random_coords(rng, 2500, (20, 18, 16), 2)
+    want = ko.build_kmap_hashmap_mode(coords, ks, st, pd)
+    cfg = F.conv_config.get_default_conv_config()
+    cfg.kmap_mode = "hashmap"
+    kvol = int(np.prod(ko._as3(ks)))
+    feats = rng.standard_normal((coords.shape[0], 16)).astype(np.float32)
+    w = (rng.standard_normal((kvol, 16, 24)) * 0.1).astype(np.float32)
+    x = ts.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda())
+    y = F.conv3d(x, torch.from_numpy(w).cuda(), ks, None, st, pd, config=cfg)
+    kmap = x._caches.kmaps[((1, 1, 1), ko._as3(ks), ko._as3(st), (1, 1, 1))]
+    assert np.array_equal(y.coords.cpu().numpy(), want["coords"])
+    assert np.array_equal(kmap["out_in_map"].cpu().numpy(), want["out_in_map"])
+    ref = ko.conv_from_map(feats, w, want["out_in_map"], want["sizes"][1])
+    assert rel_l2(y.feats.cpu().numpy(), ref) < 1e-5
+    # a second convolution at the same stride reuses the table
+    y2 = F.conv3d(x, torch.from_numpy(w).cuda(), ks, None, st, pd, config=cfg)
+    assert torch.equal(y2.feats, y.feats)
+
+
+def test_spdownsample_and_downsample_cuda():
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(10)
+    coords = random_coords(rng, 3000, (24, 24, 12), 2)
+    c = torch.from_numpy(coords).cuda()
+    got = F.spdownsample(c, 2, 2, 0).cpu().numpy()
+    want = np.unique(np.concatenate([coords[:, :1], coords[:, 1:] // 2], 1), axis=0)
+    assert np.array_equal(got, want)
+    got3 = F.spdownsample(c, 2, 3, 1).cpu().numpy()                 # stride != kernel: native enumeration
+    want3 = ko.build_kmap(coords, 3, 2, 1)["coords"]
+    assert np.array_equal(got3, want3)

@@ -26,6 +26,7 @@ SIGNATURES = {
     "tsb_kernel_hash": (C.c_int, [P, I64, P, I32, P, P]),
     "tsb_hash_insert": (C.c_int, [P, P, I64, P, I64, P, P]),
     "tsb_hash_lookup": (C.c_int, [P, P, I64, P, I64, P, P]),
+    "tsb_hash_lookup_coords": (C.c_int, [P, P, I64, P, I64, P, P, P, P]),
     "tsb_hash_query_workspace_bytes": (SZ, [I64]),
     "tsb_hash_query": (C.c_int, [P, I64, P, I64, P, P, SZ, P]),
     "tsb_hash_query_static_max_refs": (I64, []),

@@ -29,7 +29,7 @@ __all__ = [
     "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "sorted_artefacts_cuda",
     "exclusive_scan_quantified_wrapper",
     "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda", "conv_backward_wgrad_pairs_cuda",
-    "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda",
+    "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
     "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
     "pairs_from_out_in_map", "quantize_unique_cuda",
@@ -159,7 +159,48 @@ class GPUHashTable:
         return out
 
 
+    def insert_coords(self, coords: torch.Tensor) -> None:
+        """Rows of int32 [n,4] in (x, y, z, batch) order, keyed by their FNV-1a hash, value = row + 1
+        (torchsparse/backend/hashmap/hashmap_cuda.cuh:150-171, 273-277; the caller permutes the
+        columns, torchsparse/nn/functional/conv/kmap/func/hashmap.py:60)."""
+        self.insert_vals(hash_cuda(coords.int()))
+
+    def lookup_coords(self, coords: torch.Tensor, kernel_sizes, strides, kernel_volume: int) -> torch.Tensor:
+        """int32 [pad128(n), Kvol]: for row i and kernel index k the value stored for
+        ``coords[i] * stride + digit_k - (kernel - 1) // 2`` (input row + 1), 0 when absent
+        (torchsparse/backend/hashmap/hashmap_cuda.cuh:200-254, 307-314).  coords in (x, y, z, batch) order."""
+        _need_cuda(coords)
+        coords = coords.int().contiguous()
+        ks, st = _host_ints(kernel_sizes, 3), _host_ints(strides, 3)
+        kvol = ks[0] * ks[1] * ks[2]
+        if int(kernel_volume) != kvol:
+            raise ValueError("kernel_volume does not match kernel_sizes")
+        n = coords.shape[0]
+        out = torch.empty((pad128(n), kvol), dtype=torch.int32, device=coords.device)
+        check(lib.tsb_hash_lookup_coords(_p(self.keys), _p(self.vals), self.capacity, _p(coords), n, _lib.i32x(ks),
+                                         _lib.i32x(st), _p(out), _stream()), "GPUHashTable.lookup_coords")
+        return out
+
+
 # --------------------------------------------------------------------------- kernel maps
+def downsample_cuda(coords: torch.Tensor, coords_max, coords_min, kernel_sizes, stride, padding) -> torch.Tensor:
+    """Output coordinates of a strided convolution, int32 [M,4] in ascending ravel order
+    (torchsparse/backend/others/downsample_cuda.cu:147-189): every input voxel proposes the outputs
+    its kernel footprint reaches, the proposals are made unique."""
+    _need_cuda(coords)
+    cmin, cmax = _host_ints(coords_min, 4), _host_ints(coords_max, 4)
+    uniq, m, _ = downsample_unique(coords, cmin, cmax, kernel_sizes, stride, padding)
+    keys = uniq[:m]
+    out = torch.empty((m, 4), dtype=torch.int32, device=coords.device)
+    rem = keys
+    for dim in (3, 2, 1):                      # unravel: z fastest, then y, x, batch
+        size = cmax[dim] - cmin[dim] + 1
+        out[:, dim] = (rem % size + cmin[dim]).int()
+        rem = rem // size
+    out[:, 0] = (rem + cmin[0]).int()
+    return out
+
+
 def build_kernel_map_subm_hashmap(table: GPUHashTable, coords: torch.Tensor, coords_min, coords_max, kernel_sizes,
                                   stride=None, padding=None, to_insert: bool = True,
                                   check_status: bool = True) -> List[torch.Tensor]:

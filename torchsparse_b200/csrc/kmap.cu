@@ -113,6 +113,27 @@ __global__ void subm_query_odd_kernel(TableView t, const int4* __restrict__ coor
   }
 }
 
+// "hashmap" kernel-map mode: the table is keyed by the FNV-1a hash of (x, y, z, b); for output row i and
+// kernel index k the neighbour is  out * stride + digit - (kernel - 1) / 2  (x the fastest digit for an
+// odd kernel volume, z for an even one); out[i][k] = stored value (input row + 1) or 0.
+__global__ void lookup_coords_kernel(TableView t, const int4* __restrict__ coords_xyzb, int64_t n, KernelGeom g,
+                                     int* __restrict__ out) {
+  const int64_t total = n * (int64_t)g.kvol;
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = tid / g.kvol;
+    const int k = (int)(tid - row * g.kvol);
+    int d[3];
+    kernel_digits(g, k, d[0], d[1], d[2]);
+    const int4 c = __ldg(&coords_xyzb[row]);
+    const int x = c.x * g.st[0] + d[0] - (g.ks[0] - 1) / 2;
+    const int y = c.y * g.st[1] + d[1] - (g.ks[1] - 1) / 2;
+    const int z = c.z * g.st[2] + d[2] - (g.ks[2] - 1) / 2;
+    const unsigned long long key = fnv1a4(x, y, z, c.w);
+    out[tid] = key ? table_lookup(t, key) : 0;
+  }
+}
+
 // Even kernel volume: thread per (row, k); offsets are the raw digits (not centred).
 __global__ void subm_query_even_kernel(TableView t, const int4* __restrict__ coords, int64_t n, Bounds b,
                                        KernelGeom g, int* __restrict__ map) {
@@ -615,6 +636,24 @@ int tsb_hash_query_static(const int64_t* queries, int64_t n_q, const int64_t* re
     TSB_LAUNCH_CHECK();
   }
   table_query_kernel<<<grid_for(n_q, kBlock), kBlock, 0, s>>>(t, queries, n_q, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_hash_lookup_coords(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity,
+                           const int32_t* coords_xyzb, int64_t n, const int32_t* kernel_size, const int32_t* stride,
+                           int32_t* out, tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || !kernel_size || !stride) return TSB_ERR_BAD_ARG;
+  if (n && (!coords_xyzb || !out)) return TSB_ERR_BAD_ARG;
+  for (int i = 0; i < 3; ++i) if (kernel_size[i] < 1 || stride[i] < 1) return TSB_ERR_BAD_ARG;
+  KernelGeom g = make_geom(kernel_size, stride, nullptr);
+  cudaStream_t s = as_stream(stream);
+  const int64_t rows_pad = pad128(n);
+  if (rows_pad) TSB_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)rows_pad * g.kvol * sizeof(int32_t), s));
+  if (n == 0) return TSB_OK;
+  TableView t = make_table(const_cast<int64_t*>(table_keys), const_cast<int32_t*>(table_vals), capacity);
+  lookup_coords_kernel<<<grid_for(n * (int64_t)g.kvol, kBlock, 32), kBlock, 0, s>>>(
+      t, reinterpret_cast<const int4*>(coords_xyzb), n, g, out);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }

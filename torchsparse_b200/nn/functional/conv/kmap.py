@@ -93,8 +93,10 @@ def build_kernel_map(
     (``out_in_map``, ``coords``, ``sizes``, ``hashmap_keys/vals``, ``spatial_range``, sorted
     artefacts, pair lists ...).  ``caches`` / ``tensor_stride`` let the host-side bounds and
     the ravel bounds of a reused table be looked up instead of recomputed."""
-    if mode != "hashmap_on_the_fly":
-        raise NotImplementedError(f'kmap_mode "{mode}" is not built; use "hashmap_on_the_fly" (the default)')
+    if mode not in ("hashmap_on_the_fly", "hashmap"):
+        raise ValueError(f"unknown kmap_mode {mode!r}")
+    if generative and mode == "hashmap":
+        raise NotImplementedError("generative transposed convolution is not built")
     if generative:
         raise ValueError(
             f"Unsupported kmap_mode: {mode} for generative convolution (please switch to kmap_mode=hashmap).")
@@ -112,6 +114,11 @@ def build_kernel_map(
     subm = not any(s > 1 for s in stride)
     coords = _coords.contiguous()
     n = coords.shape[0]
+    if mode == "hashmap":
+        hashmap_keys, hashmap_vals = _hashmap_mode_map(kmap, coords, kernel_size, stride, padding, new_range,
+                                                       subm, downsample_mode, caches, tensor_stride)
+        return _finish_kernel_map(kmap, n, input_node_num, hashmap_keys, hashmap_vals, dataflow, ifsort,
+                                  split_mask_num)
     cmin_act, cmax_act = _actual_bounds(coords, caches, tensor_stride)
     from ....tensor import get_allow_negative_coordinates
     if get_allow_negative_coordinates():
@@ -125,6 +132,8 @@ def build_kernel_map(
 
     if subm:
         table_bounds = caches.hash_bounds.get(tensor_stride) if (caches is not None and hashmap_keys is not None) else None
+        if table_bounds == _FNV_TABLE:          # a table of the other kmap_mode cannot serve ravel keys
+            table_bounds, hashmap_keys, hashmap_vals = None, None, None
         if table_bounds is not None:
             cmin, cmax = table_bounds
         elif new_range is not None:
@@ -162,6 +171,44 @@ def build_kernel_map(
                                 else tuple(tensor_stride[i] * stride[i] for i in range(3)))
         kmap["table_bounds"] = (cmin_out, cmax_out)
         kmap["out_bounds"] = (cmin_out, out_max if out_max is not None else cmin_out)
+    return _finish_kernel_map(kmap, n, input_node_num, hashmap_keys, hashmap_vals, dataflow, ifsort, split_mask_num)
+
+
+_FNV_TABLE = ("fnv",)    # `table_bounds` marker of a table keyed by coordinate hashes (kmap_mode="hashmap")
+
+
+def _hashmap_mode_map(kmap, coords, kernel_size, stride, padding, spatial_range, subm, downsample_mode, caches,
+                      tensor_stride):
+    """kmap_mode="hashmap" (torchsparse/nn/functional/conv/kmap/func/hashmap.py:8-105): output
+    coordinates from ``spdownsample``, input coordinates inserted into a table keyed by the FNV-1a hash
+    of (x, y, z, b), and one lookup per (output row, kernel offset) at
+    ``out * stride + digit - (kernel - 1) // 2``.  A table built for this tensor stride is reused."""
+    from .downsample import spdownsample
+
+    out_coords = coords if subm else spdownsample(coords, stride, kernel_size, padding, spatial_range,
+                                                  downsample_mode=downsample_mode)
+    keys = vals = None
+    if caches is not None and caches.hash_bounds.get(tensor_stride) == _FNV_TABLE:
+        keys, vals = caches.hashmaps.get(tensor_stride, (None, None))
+    to_insert = keys is None
+    if to_insert:
+        cap = _table_capacity(coords.shape[0])
+        keys = torch.zeros(cap, dtype=torch.int64, device=coords.device)
+        vals = torch.zeros(cap, dtype=torch.int32, device=coords.device)
+    table = backend.GPUHashTable(keys, vals)
+    if to_insert:
+        table.insert_coords(coords[:, [1, 2, 3, 0]])
+    kvol = kernel_size[0] * kernel_size[1] * kernel_size[2]
+    kmap["out_in_map"] = table.lookup_coords(out_coords[:, [1, 2, 3, 0]], kernel_size, stride, kvol) - 1
+    kmap["coords"] = out_coords
+    kmap["table_stride"] = tensor_stride
+    kmap["table_bounds"] = _FNV_TABLE
+    return keys, vals
+
+
+def _finish_kernel_map(kmap, n, input_node_num, hashmap_keys, hashmap_vals, dataflow, ifsort, split_mask_num):
+    """The part of a build that does not depend on how out_in_map was found: sizes, sorted artefacts
+    of the implicit GEMM, pair lists and masks of the other dataflows."""
     kmap["hashmap_keys"], kmap["hashmap_vals"] = hashmap_keys, hashmap_vals
     kmap["sizes"] = (input_node_num, kmap["coords"].shape[0])
     out_in_map = kmap["out_in_map"]
