@@ -263,6 +263,10 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                         cur.step, cur.k = i, 0
                         logits, bi, bo = step(i, e2e, gather_inline=False)
                         io_bytes["h2d"], io_bytes["d2h"] = bi, bo
+                        if not e2e:
+                            # an issuing thread keeps one scan in flight: it waits for its scan's result (as
+                            # the e2e pass does by reading the logits back) before it starts its next one
+                            torch.cuda.current_stream().synchronize()
                         if world > 1:
                             produced = torch.cuda.Event()
                             produced.record()
