@@ -1,0 +1,53 @@
+"""Host-side pieces of the reference's Python surface that need no CUDA kernel of their own: global
+pooling, crop, functional activations (torchsparse/nn/functional/{pooling,crop,activation}.py).
+They run on CPU tensors, so these tests do too."""
+import numpy as np
+import torch
+
+
+def _tensor():
+    import torchsparse_b200 as ts
+
+    rng = np.random.default_rng(3)
+    coords = np.concatenate([rng.integers(0, 3, (200, 1)), rng.integers(0, 12, (200, 3))], 1).astype(np.int32)
+    feats = rng.standard_normal((200, 6)).astype(np.float32)
+    return ts.SparseTensor(torch.from_numpy(feats), torch.from_numpy(coords)), coords, feats
+
+
+def test_global_pooling_matches_a_loop_over_the_batch():
+    from torchsparse_b200 import nn as spnn
+    from torchsparse_b200.nn import functional as F
+
+    x, coords, feats = _tensor()
+    avg, mx = F.global_avg_pool(x).numpy(), F.global_max_pool(x).numpy()
+    for b in range(3):
+        rows = feats[coords[:, 0] == b]
+        assert np.allclose(avg[b], rows.mean(0), atol=1e-6)
+        assert np.array_equal(mx[b], rows.max(0))
+    assert torch.equal(spnn.GlobalAvgPool()(x), F.global_avg_pool(x))
+    assert torch.equal(spnn.GlobalMaxPool()(x), F.global_max_pool(x))
+
+
+def test_spcrop_keeps_the_half_open_box_over_the_first_three_columns():
+    from torchsparse_b200 import nn as spnn
+    from torchsparse_b200.nn import functional as F
+
+    x, coords, feats = _tensor()
+    lo, hi = (0, 2, 3), (2, 9, 10)
+    keep = np.all((coords[:, :3] >= lo) & (coords[:, :3] < hi), axis=1)
+    y = F.spcrop(x, lo, hi)
+    assert np.array_equal(y.coords.numpy(), coords[keep]) and np.array_equal(y.feats.numpy(), feats[keep])
+    assert y.stride == x.stride
+    assert np.array_equal(spnn.SparseCrop(lo, hi)(x).coords.numpy(), coords[keep])
+    assert F.spcrop(x).coords.shape == x.coords.shape          # no bounds: everything stays
+
+
+def test_functional_activations_keep_coords_and_cache():
+    from torchsparse_b200.nn import functional as F
+
+    x, coords, feats = _tensor()
+    for fn, ref in ((F.relu, np.maximum(feats, 0)), (F.leaky_relu, np.where(feats > 0, feats, 0.1 * feats))):
+        x2, _, _ = _tensor()
+        y = fn(x2, inplace=False)
+        assert np.allclose(y.feats.numpy(), ref, atol=1e-6)
+        assert y.coords is x2.coords and y._caches is x2._caches
