@@ -423,6 +423,9 @@ def _packed_weight(kernel: torch.Tensor, code: int, tf32: bool = False) -> Optio
     packed = torch.empty(lib.tsb_conv_packed_weight_bytes(kvol, cin, cout, code), dtype=torch.uint8,
                          device=kernel.device)
     check(lib.tsb_conv_pack_weight(_p(kernel), kvol, cin, cout, code, _p(packed), _stream()), "pack_weight")
+    # the packed copy is published to every later launch, also on other streams: it is complete first
+    # (once per weight tensor and version)
+    torch.cuda.current_stream().synchronize()
     try:
         kernel._tsb_packed = (tag, packed)
     except (AttributeError, RuntimeError):
@@ -438,6 +441,7 @@ def _padded_kernel(kernel: torch.Tensor) -> torch.Tensor:
         return hit[1]
     cin = kernel.shape[1]
     padded = torch.nn.functional.pad(kernel, (0, 0, 0, (-cin) % 8)).contiguous()
+    torch.cuda.current_stream().synchronize()     # published to launches on other streams: complete first
     try:
         kernel._tsb_padded = (tag, padded)
     except (AttributeError, RuntimeError):
