@@ -388,6 +388,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
     const int mrow = kRowsPerPass * p.kvol;                        // map ints between a thread's rows
+    const int cin_mma = (p.cin + kStepK - 1) / kStepK * kStepK;     // K extent the MMAs read
     uint32_t stage = 0, phase = 0;      // stage of the current block; phase = parity of its use count
     bool first_pass = true;              // the first use of a stage needs no release
     bool ok = true;
@@ -424,11 +425,16 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           }
           if (tid == 0) TSB_TRACE_HOT(1, blk);
           const uint32_t a_dst = smem_base + stage * (uint32_t)stage_bytes + dst_off;
+          // granules beyond the K extent of the chunk's last MMA (Cin rounded up to one instruction's K) are
+          // never read: their threads copy nothing and only arrive; granules between Cin and that bound are
+          // zero-filled (the weights there are zero, but stale shared memory could hold NaN patterns)
+          if (col < cin_mma) {
 #pragma unroll
-          for (int j = 0; j < kCopies; ++j) {
-            const bool live = col_ok && src[j] >= 0;
-            cp_async16(a_dst + (uint32_t)(j * kRowsPerPass) * kRowBytes,
-                       live ? (const void*)(xc + (int64_t)src[j] * p.cin) : (const void*)x, live ? 16u : 0u);
+            for (int j = 0; j < kCopies; ++j) {
+              const bool live = col_ok && src[j] >= 0;
+              cp_async16(a_dst + (uint32_t)(j * kRowsPerPass) * kRowBytes,
+                         live ? (const void*)(xc + (int64_t)src[j] * p.cin) : (const void*)x, live ? 16u : 0u);
+            }
           }
           cp_async_arrive_noinc(full0 + stage * 8);
           if (tid == 0) TSB_TRACE_HOT(2, blk);
