@@ -426,7 +426,8 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                    "streams": n_streams, "host_threads": n_threads,
                    "conv_mode": args.conv_mode, "fused_inference_engine": not args.unfused,
                    "sort_max_stride": args.sort_max_stride,
-                   "parallelism": f"scan-sharded x{world}, NCCL all-gather of the logits of every step" if world > 1 else "single GPU"},
+                   "parallelism": (f"scan-sharded x{world}, NCCL all-gather of the logits of every step"
+                                   if world > 1 else "single GPU")},
         "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h)},
         "gpu_launches": int(launches),

@@ -3,7 +3,6 @@ reference's own test pins its kernels (tests/python/test_single_layer_conv.py:11
 golden fixtures generated from the reference's CPU sources and numpy code."""
 import numpy as np
 import pytest
-import torch
 
 from conftest import random_coords, rel_l2
 from oracle import kmap_oracle as ko

@@ -525,14 +525,14 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
 
 class IgemmLayerPlan:
     """The arguments of tsb_conv_igemm_fwd that do not change between calls of one inference layer
-    (weights, packed weights, fp32 scale / shift, sizes), resolved once.  ``launch`` then costs one
-    output allocation and one foreign call; argument checks happened when the plan was made.  The
-    plan keeps the tensors alive and is remade when the weights are replaced or modified."""
+    (weights, packed weights, fp32 scale / shift, sizes), resolved once.  :func:`igemm_plan_launch` then
+    costs one output allocation and one foreign call; argument checks happened when the plan was made.
+    The plan keeps the tensors alive and is remade when the weights are replaced or modified."""
 
     __slots__ = ("kernel", "packed", "scale", "bias", "tag", "args_head", "args_tail", "cout", "dtype", "device")
 
     def __init__(self, kernel: torch.Tensor, scale: Optional[torch.Tensor], bias: Optional[torch.Tensor],
-                 relu: bool, allow_tf32: bool):
+                 allow_tf32: bool):
         _need_cuda(kernel)
         if kernel.dim() != 3:
             raise ValueError("kernel must be [Kvol, Cin, Cout]")
@@ -546,7 +546,8 @@ class IgemmLayerPlan:
         self.packed = _packed_weight(kernel, code, bool(allow_tf32))
         self.scale = None if scale is None else scale.float().contiguous()
         self.bias = None if bias is None else bias.float().contiguous()
-        self.cout, self.dtype, self.device = cout, kernel.dtype, kernel.device
+        self.cout, self.dtype = cout, kernel.dtype
+        self.device = kernel.device if kernel.device.index is not None else torch.device("cuda", kernel.get_device())
         math = _lib.TSB_MATH_TF32 if (kernel.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
         self.args_head = (kernel.data_ptr(), _p(self.packed))
         self.args_tail = (kvol, cin, cout, code, math, _p(self.scale), _p(self.bias))
@@ -570,7 +571,8 @@ def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: 
         residual = residual.to(plan.dtype).contiguous()
     out = torch.empty((num_out_feats, plan.cout), dtype=plan.dtype, device=plan.device)
     rc = lib.tsb_conv_igemm_fwd(in_feats.data_ptr(), plan.args_head[0], plan.args_head[1], out_in_map.data_ptr(),
-                                None if reorder_loc is None else reorder_loc.data_ptr(), out.data_ptr(), in_feats.shape[0], num_out_feats, *plan.args_tail,
+                                None if reorder_loc is None else reorder_loc.data_ptr(), out.data_ptr(),
+                                in_feats.shape[0], num_out_feats, *plan.args_tail,
                                 None if residual is None else residual.data_ptr(), int(relu),
                                 _status_word(plan.device).data_ptr(), None, 0,
                                 torch._C._cuda_getCurrentRawStream(plan.device.index))

@@ -16,7 +16,7 @@ The rewritten model computes the same function (one rounding instead of three pe
 the network runs and builds their kernel maps up front on later calls, so that the only
 device-to-host reads of a forward (one per strided map) happen before the convolutions are queued.
 """
-from typing import Dict, Optional
+from typing import Optional
 
 import torch
 from torch import nn
@@ -28,7 +28,6 @@ from . import functional as F
 from .functional.conv import conv as _conv_impl
 from .modules.activation import ReLU
 from .modules.conv import Conv3d
-from .modules.norm import BatchNorm
 
 __all__ = ["FusedConv", "FusedResBlock", "fuse_for_inference", "InferenceEngine"]
 
@@ -156,8 +155,7 @@ class FusedConv(nn.Module):
             return None     # the 4-channel input layer is padded by the general entry point
         plan = self._plan
         if plan is None or not plan.valid_for(self.kernel, backends.allow_tf32):
-            plan = self._plan = backend.IgemmLayerPlan(self.kernel, self.scale, self.shift, self.relu,
-                                                       backends.allow_tf32)
+            plan = self._plan = backend.IgemmLayerPlan(self.kernel, self.scale, self.shift, backends.allow_tf32)
         out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu, reorder_loc)
         caches.cmaps.setdefault(out_stride, (out_coords, out_range))
         return SparseTensor._from_parts(out, out_coords, out_stride, out_range, caches)

@@ -1,5 +1,5 @@
 from itertools import repeat
-from typing import List, Tuple, Union
+from typing import Tuple, Union
 
 import numpy as np
 import torch

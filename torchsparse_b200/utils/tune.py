@@ -8,7 +8,7 @@ row-sorted map) with CUDA events around every convolution module, the cost of wh
 candidate adds to the kernel-map build (sorting, pair lists) included in the first layer of a
 group that triggers it.  It works on a module graph of :class:`~torchsparse_b200.nn.Conv3d` and on
 the fused inference modules alike."""
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
 from torch import nn
