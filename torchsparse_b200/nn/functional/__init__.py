@@ -1,9 +1,7 @@
-from .activation import *
 from .conv import *
-from .crop import *
-from .pooling import *
 from .count import *
 from .devoxelize import *
 from .hash import *
 from .query import *
 from .voxelize import *
+from .tensor_ops import *

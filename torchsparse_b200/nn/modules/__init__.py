@@ -1,5 +1,4 @@
 from .activation import *
 from .conv import *
 from .norm import *
-from .crop import *
-from .pooling import *
+from .tensor_ops import *
