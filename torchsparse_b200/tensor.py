@@ -1,140 +1,123 @@
-from typing import Tuple, Union
+"""The two tensor containers of the reference's Python surface (torchsparse/tensor.py:29-145).
+
+``SparseTensor`` = features [N, C] + int32 coordinates [N, 4] in (batch, x, y, z) order + the tensor
+stride + an optional spatial range, carrying the cache of coordinate maps, kernel maps and hash
+tables that the layers of a network share.  ``PointTensor`` = point features with float coordinates
+and the voxel queries cached for them."""
+from typing import Callable, Optional, Sequence, Tuple, Union
 
 import torch
 
-from .utils.utils import make_ntuple
+from .utils.tensor_cache import TensorCache, TensorCacheMode, cache_for_new_tensor
 from .utils.to_dense import to_dense
-from .utils.tensor_cache import (TensorCache, TensorCacheMode, get_global_tensor_cache, set_global_tensor_cache,
-                                 get_tensor_cache_mode)
+from .utils.utils import make_ntuple
 
 __all__ = ["SparseTensor", "PointTensor", "get_allow_negative_coordinates", "set_allow_negative_coordinates"]
 
-_allow_negative_coordinates = False
+_negative_coordinates = {"allowed": False}
 
 
-def get_allow_negative_coordinates():
-    return _allow_negative_coordinates
+def set_allow_negative_coordinates(allow_negative_coordinates: bool) -> None:
+    """When on, kernel-map keys start at the smallest coordinate instead of 0."""
+    _negative_coordinates["allowed"] = bool(allow_negative_coordinates)
 
 
-def set_allow_negative_coordinates(allow_negative_coordinates):
-    global _allow_negative_coordinates
-    _allow_negative_coordinates = allow_negative_coordinates
+def get_allow_negative_coordinates() -> bool:
+    return _negative_coordinates["allowed"]
+
+
+class _Alias:
+    """Short attribute name of the reference (``F``, ``C``, ``s``) for a field of this class."""
+
+    def __init__(self, field: str, convert: Optional[Callable] = None) -> None:
+        self.field, self.convert = field, convert
+
+    def __get__(self, obj, owner=None):
+        return self if obj is None else getattr(obj, self.field)
+
+    def __set__(self, obj, value) -> None:
+        setattr(obj, self.field, self.convert(value) if self.convert else value)
 
 
 class SparseTensor:
-    """feats [N,C] + coords int32 [N,4] = (batch,x,y,z) + tensor stride + optional spatial range,
-    with a cache of kernel maps shared along the network (torchsparse/tensor.py:29-114)."""
+    F = _Alias("feats")
+    C = _Alias("coords")
+    s = _Alias("stride", lambda v: make_ntuple(v, ndim=3))
 
     def __init__(self, feats: torch.Tensor, coords: torch.Tensor, stride: Union[int, Tuple[int, ...]] = 1,
-                 spatial_range: Union[int, Tuple[int, ...]] = None, coord_bounds=None) -> None:
-        self.feats = feats
-        self.coords = coords
+                 spatial_range: Optional[Sequence[int]] = None, coord_bounds=None) -> None:
+        """``coord_bounds`` = ((min b, x, y, z), (max b, x, y, z)) when the caller already knows them on
+        the host (``sparse_quantize`` returns them): kernel-map builds then need no device reduction."""
+        self.feats, self.coords = feats, coords
         self.stride = make_ntuple(stride, ndim=3)
         self.spatial_range = None if spatial_range is None else make_ntuple(spatial_range, ndim=len(spatial_range))
-        if get_tensor_cache_mode() == TensorCacheMode.GLOBAL_TENSOR_CACHE:
-            caches = get_global_tensor_cache()
-            if caches is None:
-                caches = TensorCache()
-                set_global_tensor_cache(caches)
-            self._caches = caches
-        else:
-            self._caches = TensorCache()
+        self._caches = cache_for_new_tensor()
         if coord_bounds is not None:
-            # ((min b,x,y,z), (max b,x,y,z)) known on the host (e.g. from sparse_quantize): kernel-map
-            # builds then need no device reduction of the coordinates
-            self._caches.cbounds[self.stride] = (tuple(int(v) for v in coord_bounds[0]),
-                                                 tuple(int(v) for v in coord_bounds[1]))
+            lo, hi = coord_bounds
+            self._caches.cbounds[self.stride] = (tuple(int(v) for v in lo), tuple(int(v) for v in hi))
 
     @classmethod
     def _from_parts(cls, feats: torch.Tensor, coords: torch.Tensor, stride: Tuple[int, ...], spatial_range,
-                    caches) -> "SparseTensor":
+                    caches: TensorCache) -> "SparseTensor":
         """The output of a layer: stride and range are already canonical tuples and the cache is the
         input's, so nothing is validated or created."""
-        self = cls.__new__(cls)
-        self.feats, self.coords, self.stride, self.spatial_range, self._caches = (feats, coords, stride,
-                                                                                 spatial_range, caches)
+        out = cls.__new__(cls)
+        out.feats, out.coords, out.stride, out.spatial_range, out._caches = feats, coords, stride, spatial_range, caches
+        return out
+
+    # ---- in-place movers (each returns self, as the reference's do)
+    def _apply(self, fn: Callable[[torch.Tensor], torch.Tensor], coords_too: bool = True) -> "SparseTensor":
+        self.feats = fn(self.feats)
+        if coords_too:
+            self.coords = fn(self.coords)
         return self
 
-    @property
-    def F(self) -> torch.Tensor:
-        return self.feats
+    def cpu(self) -> "SparseTensor":
+        return self._apply(torch.Tensor.cpu)
 
-    @F.setter
-    def F(self, feats: torch.Tensor) -> None:
-        self.feats = feats
+    def cuda(self) -> "SparseTensor":
+        return self._apply(torch.Tensor.cuda)
 
-    @property
-    def C(self) -> torch.Tensor:
-        return self.coords
+    def detach(self) -> "SparseTensor":
+        return self._apply(torch.Tensor.detach)
 
-    @C.setter
-    def C(self, coords: torch.Tensor) -> None:
-        self.coords = coords
+    def half(self) -> "SparseTensor":
+        return self._apply(torch.Tensor.half, coords_too=False)
 
-    @property
-    def s(self) -> Tuple[int, ...]:
-        return self.stride
+    def to(self, device, non_blocking: bool = True) -> "SparseTensor":
+        return self._apply(lambda t: t.to(device, non_blocking=non_blocking))
 
-    @s.setter
-    def s(self, stride: Union[int, Tuple[int, ...]]) -> None:
-        self.stride = make_ntuple(stride, ndim=3)
-
-    def cpu(self):
-        self.coords, self.feats = self.coords.cpu(), self.feats.cpu()
-        return self
-
-    def cuda(self):
-        self.coords, self.feats = self.coords.cuda(), self.feats.cuda()
-        return self
-
-    def half(self):
-        self.feats = self.feats.half()
-        return self
-
-    def detach(self):
-        self.coords, self.feats = self.coords.detach(), self.feats.detach()
-        return self
-
-    def to(self, device, non_blocking: bool = True):
-        self.coords = self.coords.to(device, non_blocking=non_blocking)
-        self.feats = self.feats.to(device, non_blocking=non_blocking)
-        return self
-
-    def dense(self):
-        assert self.spatial_range is not None
+    def dense(self) -> torch.Tensor:
+        if self.spatial_range is None:
+            raise AssertionError("dense() needs a spatial_range")
         return to_dense(self.feats, self.coords, self.spatial_range)
 
-    def __add__(self, other):
-        output = SparseTensor(coords=self.coords, feats=self.feats + other.feats, stride=self.stride,
-                              spatial_range=self.spatial_range)
-        output._caches = self._caches
-        return output
+    def __add__(self, other: "SparseTensor") -> "SparseTensor":
+        return SparseTensor._from_parts(self.feats + other.feats, self.coords, self.stride, self.spatial_range,
+                                        self._caches)
 
 
 class PointTensor:
-    """Point features with float coordinates and cached voxel queries (torchsparse/tensor.py:116-145)."""
-
     def __init__(self, feats, coords, idx_query=None, weights=None):
-        self.F = feats
-        self.C = coords
-        self.idx_query = idx_query if idx_query is not None else {}
-        self.weights = weights if weights is not None else {}
+        self.F, self.C = feats, coords
+        self.idx_query = {} if idx_query is None else idx_query
+        self.weights = {} if weights is None else weights
         self.additional_features = {"idx_query": {}, "counts": {}}
 
-    def cuda(self):
-        self.F, self.C = self.F.cuda(), self.C.cuda()
+    def _apply(self, fn) -> "PointTensor":
+        self.F, self.C = fn(self.F), fn(self.C)
         return self
 
-    def detach(self):
-        self.F, self.C = self.F.detach(), self.C.detach()
-        return self
+    def cuda(self) -> "PointTensor":
+        return self._apply(torch.Tensor.cuda)
 
-    def to(self, device, non_blocking=True):
-        self.F = self.F.to(device, non_blocking=non_blocking)
-        self.C = self.C.to(device, non_blocking=non_blocking)
-        return self
+    def detach(self) -> "PointTensor":
+        return self._apply(torch.Tensor.detach)
 
-    def __add__(self, other):
-        tensor = PointTensor(self.F + other.F, self.C, self.idx_query, self.weights)
-        tensor.additional_features = self.additional_features
-        return tensor
+    def to(self, device, non_blocking: bool = True) -> "PointTensor":
+        return self._apply(lambda t: t.to(device, non_blocking=non_blocking))
+
+    def __add__(self, other: "PointTensor") -> "PointTensor":
+        out = PointTensor(self.F + other.F, self.C, self.idx_query, self.weights)
+        out.additional_features = self.additional_features
+        return out

@@ -1,11 +1,28 @@
-"""Per-network cache of coordinate maps, kernel maps and hash tables
-(torchsparse/utils/tensor_cache.py:6-60), plus the host-side coordinate bounds this
-implementation keeps so that kernel-map builds need no device read of ``coords.max``."""
+"""The cache a network's layers share (torchsparse/utils/tensor_cache.py:6-60): coordinate maps,
+kernel maps and hash tables, keyed by tensor stride — plus the host-side coordinate bounds this
+implementation keeps so that kernel-map builds need no device read of ``coords.max``.
+
+Two modes, as in the reference: every new SparseTensor starts its own cache (default), or all
+tensors share one process-wide cache until it is cleared."""
+from dataclasses import dataclass, field
 from enum import Enum
-from typing import Any, Dict, Tuple
+from typing import Any, Dict, Optional, Tuple
 
 __all__ = ["TensorCache", "TensorCacheMode", "set_tensor_cache_mode", "get_tensor_cache_mode",
-           "get_global_tensor_cache", "set_global_tensor_cache", "clear_global_tensor_cache"]
+           "get_global_tensor_cache", "set_global_tensor_cache", "clear_global_tensor_cache",
+           "cache_for_new_tensor"]
+
+Stride = Tuple[int, ...]
+Bounds = Tuple[Tuple[int, ...], Tuple[int, ...]]
+
+
+@dataclass
+class TensorCache:
+    cmaps: Dict[Stride, Tuple[Any, Any]] = field(default_factory=dict)       # stride -> (coords, spatial_range)
+    kmaps: Dict[Tuple[Any, ...], Any] = field(default_factory=dict)          # (stride, kernel, conv stride, dilation) -> kmap
+    hashmaps: Dict[Stride, Tuple[Any, ...]] = field(default_factory=dict)    # stride of the coords held -> (keys, vals)
+    cbounds: Dict[Stride, Bounds] = field(default_factory=dict)              # host copy of the actual (min, max)
+    hash_bounds: Dict[Stride, Any] = field(default_factory=dict)             # key space of the table at that stride
 
 
 class TensorCacheMode(Enum):
@@ -13,39 +30,35 @@ class TensorCacheMode(Enum):
     GLOBAL_TENSOR_CACHE = 1
 
 
-_tensor_cache_mode = TensorCacheMode.SEPARATE_TENSOR_CACHE
-_global_tensor_cache = None
-
-
-def set_tensor_cache_mode(mode: TensorCacheMode):
-    assert isinstance(mode, TensorCacheMode), "Input must be an instance of TensorCacheMode"
-    global _tensor_cache_mode
-    _tensor_cache_mode = mode
+_state: Dict[str, Any] = {"mode": TensorCacheMode.SEPARATE_TENSOR_CACHE, "shared": None}
 
 
 def get_tensor_cache_mode() -> TensorCacheMode:
-    return _tensor_cache_mode
+    return _state["mode"]
 
 
-class TensorCache:
-    def __init__(self) -> None:
-        self.cmaps: Dict[Tuple[int, ...], Tuple[Any, Any]] = {}   # stride -> (coords, spatial_range)
-        self.kmaps: Dict[Tuple[Any, ...], Any] = {}               # (stride, kernel, conv stride, dilation) -> kmap
-        self.hashmaps: Dict[Tuple[int, ...], Tuple[Any, ...]] = {}  # stride of the coords held -> (keys, vals)
-        # host-side bounds, keyed by tensor stride
-        self.cbounds: Dict[Tuple[int, ...], Tuple[Tuple[int, ...], Tuple[int, ...]]] = {}   # actual (min, max)
-        self.hash_bounds: Dict[Tuple[int, ...], Tuple[Tuple[int, ...], Tuple[int, ...]]] = {}  # ravel bounds of the table
+def set_tensor_cache_mode(mode: TensorCacheMode) -> None:
+    if not isinstance(mode, TensorCacheMode):
+        raise AssertionError("Input must be an instance of TensorCacheMode")
+    _state["mode"] = mode
 
 
-def get_global_tensor_cache():
-    return _global_tensor_cache
+def get_global_tensor_cache() -> Optional[TensorCache]:
+    return _state["shared"]
 
 
-def set_global_tensor_cache(tensor_cache):
-    global _global_tensor_cache
-    _global_tensor_cache = tensor_cache
+def set_global_tensor_cache(tensor_cache: Optional[TensorCache]) -> None:
+    _state["shared"] = tensor_cache
 
 
-def clear_global_tensor_cache():
-    global _global_tensor_cache
-    _global_tensor_cache = None
+def clear_global_tensor_cache() -> None:
+    _state["shared"] = None
+
+
+def cache_for_new_tensor() -> TensorCache:
+    """The cache a freshly constructed SparseTensor gets under the current mode."""
+    if _state["mode"] is TensorCacheMode.GLOBAL_TENSOR_CACHE:
+        if _state["shared"] is None:
+            _state["shared"] = TensorCache()
+        return _state["shared"]
+    return TensorCache()

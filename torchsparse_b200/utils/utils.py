@@ -1,5 +1,5 @@
+"""Small argument helpers (torchsparse/utils/utils.py:9-33)."""
 from functools import lru_cache
-from itertools import repeat
 from typing import List, Tuple, Union
 
 import torch
@@ -8,23 +8,23 @@ __all__ = ["make_ntuple", "make_tensor", "make_divisible"]
 
 
 def make_ntuple(x: Union[int, List[int], Tuple[int, ...], torch.Tensor], ndim: int) -> Tuple[int, ...]:
-    """int / list / tuple / tensor -> tuple of ``ndim`` ints (torchsparse/utils/utils.py:9-21)."""
+    """``ndim`` ints from an int (repeated), a list / tuple or a tensor (a device tensor costs a read)."""
     if type(x) is tuple and len(x) == ndim and all(type(v) is int for v in x):
-        return x
-    if isinstance(x, int):
-        x = tuple(repeat(x, ndim))
-    elif isinstance(x, torch.Tensor):
-        x = tuple(int(v) for v in x.view(-1).cpu().tolist())
-    elif isinstance(x, (list, tuple)):
-        x = tuple(int(v) for v in x)
-    assert isinstance(x, tuple) and len(x) == ndim, x
-    return x
+        return x                                  # the common case on the hot path: already canonical
+    if isinstance(x, torch.Tensor):
+        x = x.reshape(-1).tolist()
+    values = (int(x),) * ndim if isinstance(x, int) else tuple(int(v) for v in x)
+    if len(values) != ndim:
+        raise AssertionError(f"expected {ndim} values, got {values}")
+    return values
 
 
 @lru_cache()
 def make_tensor(x: Tuple[int, ...], dtype: torch.dtype, device) -> torch.Tensor:
+    """A small constant tensor; one instance per (values, dtype, device)."""
     return torch.tensor(x, dtype=dtype, device=device)
 
 
 def make_divisible(x: int, divisor: int) -> int:
-    return (x + divisor - 1) // divisor * divisor
+    """x rounded up to a multiple of divisor."""
+    return -(-x // divisor) * divisor
