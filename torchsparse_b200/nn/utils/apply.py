@@ -1,3 +1,4 @@
+"""Lifting a dense function to SparseTensor features (torchsparse/nn/utils/apply.py:10-21)."""
 from typing import Callable
 
 import torch
@@ -8,9 +9,7 @@ __all__ = ["fapply"]
 
 
 def fapply(input: SparseTensor, fn: Callable[..., torch.Tensor], *args, **kwargs) -> SparseTensor:
-    """Apply a dense function to the feature matrix, keeping coordinates and caches
-    (torchsparse/nn/utils/apply.py:10-21)."""
-    output = SparseTensor(coords=input.coords, feats=fn(input.feats, *args, **kwargs), stride=input.stride,
-                          spatial_range=input.spatial_range)
-    output._caches = input._caches
-    return output
+    """``fn(input.feats, *args, **kwargs)`` wrapped back into a SparseTensor that shares the input's
+    coordinates, stride, spatial range and kernel-map cache (the geometry does not change)."""
+    mapped = fn(input.feats, *args, **kwargs)
+    return SparseTensor._from_parts(mapped, input.coords, input.stride, input.spatial_range, input._caches)
