@@ -51,3 +51,27 @@ def test_functional_activations_keep_coords_and_cache():
         y = fn(x2, inplace=False)
         assert np.allclose(y.feats.numpy(), ref, atol=1e-6)
         assert y.coords is x2.coords and y._caches is x2._caches
+
+
+def test_spdownsample_stride_equal_kernel_on_cpu():
+    """The branch of spdownsample that is plain tensor arithmetic (every stride 1 or the kernel size)."""
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(4)
+    coords = np.unique(np.concatenate([rng.integers(0, 2, (500, 1)), rng.integers(0, 30, (500, 3))], 1), axis=0)
+    got = F.spdownsample(torch.from_numpy(coords.astype(np.int32)), (2, 2, 1), (2, 2, 1)).numpy()
+    want = np.unique(np.concatenate([coords[:, :1], coords[:, 1:] // np.array([2, 2, 1])], 1), axis=0)
+    assert np.array_equal(got, want) and got.dtype == np.int32
+
+
+def test_sparse_collate_prepends_batch_index():
+    import torchsparse_b200 as ts
+    from torchsparse_b200.utils.collate import sparse_collate, sparse_collate_fn
+
+    a = ts.SparseTensor(torch.ones(3, 2), torch.tensor([[0, 0, 0], [1, 1, 1], [2, 2, 2]], dtype=torch.int32))
+    b = ts.SparseTensor(torch.zeros(2, 2), np.array([[5, 5, 5], [6, 6, 6]], dtype=np.int32))
+    out = sparse_collate([a, b])
+    assert out.coords.tolist() == [[0, 0, 0, 0], [0, 1, 1, 1], [0, 2, 2, 2], [1, 5, 5, 5], [1, 6, 6, 6]]
+    assert out.feats.shape == (5, 2) and out.stride == (1, 1, 1)
+    batch = sparse_collate_fn([{"x": a, "y": np.zeros(2), "meta": {"n": 1}}, {"x": b, "y": np.ones(2), "meta": {"n": 2}}])
+    assert batch["x"].coords.shape == (5, 4) and batch["y"].shape == (2, 2) and batch["meta"]["n"] == [1, 2]
