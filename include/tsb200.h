@@ -227,6 +227,9 @@ int tsb_build_masks(int64_t n_in, int64_t n_out, const int32_t* nbmaps, const in
  * fp32 accumulator before the single rounding: y = acc * scale[n] + bias[n] + residual[m][n], then
  * ReLU; scale / bias fp32 [cout], residual [n_out,cout] of `dtype`, each may be NULL (an
  * inference-mode BatchNorm folds into scale and bias).
+ * fp16 / bf16 tensors, and fp32 tensors with math == TSB_MATH_TF32, run on the tensor cores when the
+ * feature rows are 16-byte multiples, cout is a multiple of 8 and kvol <= 32; every other case
+ * (exact fp32 arithmetic included) runs on the CUDA cores with the same results up to rounding.
  * Replaces conv_forward_implicit_gemm_cuda
  * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987) and
  * conv_forward_implicit_gemm_sorted_cuda
