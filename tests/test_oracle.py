@@ -116,3 +116,40 @@ def test_empty_and_single_inputs():
     kd = ko.build_kmap(one, 2, 2, 0)
     # x=4,y=5,z=6 -> output (2,2,3) exists only where the bound (max-1)//2 allows: x: (4-1)//2=1 < 2 -> dropped
     assert kd["sizes"][1] == 0
+
+
+def test_oracle_backward_matches_autograd():
+    """conv_backward_from_map against torch autograd through the same sum written with dense ops (fp64)."""
+    import torch
+
+    rng = np.random.default_rng(11)
+    coords = random_coords(rng, 300, (9, 9, 9), 2)
+    n = coords.shape[0]
+    for ks, st, pd in ((3, 1, 1), (2, 2, 0), (3, 2, 1)):
+        km = ko.build_kmap(coords, ks, st, pd)
+        m = km["sizes"][1]
+        kvol = km["out_in_map"].shape[1]
+        x, w, gy = rng.standard_normal((n, 5)), rng.standard_normal((kvol, 5, 7)), rng.standard_normal((m, 7))
+        dx, dw = ko.conv_backward_from_map(x, w, km["out_in_map"], m, gy)
+        xt, wt = torch.tensor(x, requires_grad=True), torch.tensor(w, requires_grad=True)
+        omap = torch.tensor(km["out_in_map"][:m]).long()
+        y = torch.zeros(m, 7, dtype=torch.float64)
+        for k in range(kvol):
+            rows = (omap[:, k] >= 0).nonzero()[:, 0]
+            y = y.index_add(0, rows, xt[omap[rows, k]] @ wt[k])
+        assert np.allclose(y.detach().numpy(), ko.conv_from_map(x, w, km["out_in_map"], m), atol=1e-12)
+        y.backward(torch.tensor(gy))
+        assert np.abs(dx - xt.grad.numpy()).max() < 1e-12 and np.abs(dw - wt.grad.numpy()).max() < 1e-12
+
+
+def test_oracle_hashmap_mode_agrees_with_on_the_fly_mode_where_both_are_defined():
+    """Submanifold maps and stride = kernel maps without padding are the same in the two kernel-map
+    modes of the reference (same output coordinates, same neighbours); the hashmap-mode restatement is
+    checked against the on-the-fly one, which is pinned by the dense-convolution equivalence above."""
+    rng = np.random.default_rng(12)
+    coords = random_coords(rng, 1500, (16, 14, 12), 2)
+    for ks, st, pd in ((3, 1, 1), (5, 1, 2), (2, 2, 0), ((1, 2, 2), (1, 2, 2), 0)):
+        a = ko.build_kmap(coords, ks, st, pd)
+        b = ko.build_kmap_hashmap_mode(coords, ks, st, pd)
+        assert np.array_equal(a["coords"], b["coords"]), (ks, st)
+        assert np.array_equal(a["out_in_map"], b["out_in_map"]), (ks, st)
