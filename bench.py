@@ -10,12 +10,15 @@ points, 0.05 m voxels).  One step = voxelisation (sparse_quantize on the GPU) ->
 42 sparse convolutions (+ BN/ReLU/skip) -> logits.  With N GPUs every rank runs its own scan (weak
 scaling, scans are independent) and the logits are all-gathered over NCCL once per step.
 
-Prints ONE JSON line (rank 0).  `value` = scans/s with the points already resident in HBM;
-`e2e` = the same through the public API from pinned host memory (H2D of the points and D2H of the
-logits inside the timed region).  `roofline` describes the dominant kernel (the implicit-GEMM conv
-forward of the layer shape with the largest total time), timed with CUDA events on its own stream
-inside the timed region.  `cpu_baseline` = the reference project's own CPU convolution (oracle/_ref)
-driving the same network on a spatial crop of the same scan, scaled by voxel count.
+Prints ONE JSON line (rank 0).  Three passes over the same K steps, each after W warm-up steps:
+`value` = scans/s with the points already resident in HBM and `e2e` = the same through the public API
+from pinned host memory (H2D of the points and D2H of the logits inside the timed region) — both with
+alternate scans issued by two host threads on two streams, each thread waiting for its scan before it
+starts its next, one event pair around the K steps and a 256 MiB L2 flush before every step inside it;
+then a serial pass (one stream, one thread) with an event pair around every conv launch, from which
+`roofline` describes the dominant kernel (the implicit-GEMM conv forward of the layer shape with the
+largest total time).  `cpu_baseline` = the reference project's own CPU convolution (oracle/_ref) driving
+the same network on a spatial crop of the same scan, scaled by voxel count.
 """
 from __future__ import annotations
 
