@@ -192,6 +192,22 @@ int tsb_map_sorted_artefacts(const int32_t* out_in_map, int64_t rows, int32_t kv
                              int32_t* sorted_mask, int32_t* reorder_loc, int32_t* reordered_map,
                              int32_t* reduced_mask, void* workspace, size_t workspace_bytes, tsb_stream_t stream);
 
+/* The row order and map layout the tensor-core convolution is fastest on, for a map that is used by
+ * several launches (every submanifold layer of a resolution level shares one map): rows sorted by their
+ * neighbour mask (stable, descending, padding rows last) so that the 128 rows of a tile share their
+ * offsets, the reordered map stored column-major (map_cm int32 [kvol][rows], entry of sorted row r and
+ * offset k at map_cm[k * rows + r]), and the per-tile offset masks (tile_mask uint32 [rows / 128]).
+ * reorder_loc int32 [rows]: sorted row r is map row reorder_loc[r] (the row its output is stored at).
+ * rows = padded row count of out_in_map (a multiple of 128); valid_n rows are real; valid_n_dev (int32,
+ * device, nullable) overrides valid_n with a count in device memory (valid_n is then its upper bound).
+ * The same idea as the reference's derive_bitmask -> torch.sort -> reorder_out_in_map -> reduce_bitmask
+ * chain (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:92-107); the layout and the
+ * sort key are this library's own, so the results are not interchangeable with that chain's. */
+size_t tsb_map_sorted_cm_workspace_bytes(int64_t rows);
+int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n,
+                      const int32_t* valid_n_dev, int32_t* reorder_loc, int32_t* map_cm, uint32_t* tile_mask,
+                      void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+
 /* Pair lists for the GatherScatter / FetchOnDemand dataflows.
  * tsb_pairs_count: nbsizes int32 [kvol] = valid entries per column; also writes the
  * exclusive scans nbaddrs / qnbaddrs int32 [kvol+1] (q = 128 rounding).
@@ -223,24 +239,90 @@ int tsb_build_masks(int64_t n_in, int64_t n_out, const int32_t* nbmaps, const in
 
 /* Implicit GEMM over an out_in_map [pad128(n_out), kvol].  If reorder_loc != NULL the map
  * is the row-sorted one and output row r is stored at reorder_loc[r] (sorted dataflow).
- * Empty (tile, offset) blocks are skipped in either case.  Optional fused epilogue, applied to the
+ * Empty (tile, offset) blocks are skipped in either case: tile_mask (uint32 [ceil(n_out / 128)], from
+ * tsb_map_tile_mask) names the offsets present in each 128-row tile; with tile_mask == NULL the call
+ * derives the masks into its workspace first (one more launch).  Optional fused epilogue, applied to the
  * fp32 accumulator before the single rounding: y = acc * scale[n] + bias[n] + residual[m][n], then
  * ReLU; scale / bias fp32 [cout], residual [n_out,cout] of `dtype`, each may be NULL (an
  * inference-mode BatchNorm folds into scale and bias).
  * fp16 / bf16 tensors, and fp32 tensors with math == TSB_MATH_TF32, run on the tensor cores when the
  * feature rows are 16-byte multiples, cout is a multiple of 8 and kvol <= 32; every other case
  * (exact fp32 arithmetic included) runs on the CUDA cores with the same results up to rounding.
+ * Workspace: tsb_conv_igemm_workspace_bytes(...) bytes (packed weights + a status word), plus
+ * tsb_map_tile_mask_bytes(n_out) when tile_mask == NULL; none is needed when packed_weight,
+ * dev_status and tile_mask are all supplied.
  * Replaces conv_forward_implicit_gemm_cuda
  * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987) and
  * conv_forward_implicit_gemm_sorted_cuda
  * (torchsparse/backend/convolution/convolution_forward_implicit_gemm_sorted_cuda.cu:1755-2230). */
 size_t tsb_conv_igemm_workspace_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype);
 int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* packed_weight,
-                       const int32_t* out_in_map, const int32_t* reorder_loc, void* out_feats,
-                       int64_t n_in, int64_t n_out, int32_t kvol, int32_t cin, int32_t cout,
+                       const int32_t* out_in_map, const int32_t* reorder_loc, const uint32_t* tile_mask,
+                       void* out_feats, int64_t n_in, int64_t n_out, int32_t kvol, int32_t cin, int32_t cout,
                        int32_t dtype, int32_t math, const float* scale, const float* bias,
                        const void* residual, int32_t relu, int32_t* dev_status, void* workspace,
                        size_t workspace_bytes, tsb_stream_t stream);
+
+/* Offsets present in each 128-row tile of a kernel map: out[t] has bit k set when some row of tile t has
+ * an entry >= 0 in column k.  The entry of (row, k) is read at map[row * row_stride + k * col_stride]
+ * (element strides: (kvol, 1) for the reference's row-major layout, (1, padded rows) for a
+ * column-major copy).  n_rows_dev (int32, device, nullable) overrides n_rows with a count held in device
+ * memory (n_rows is then its upper bound).  The reference computes the same word as the OR of the sorted
+ * row masks, reduce_bitmask_cuda (torchsparse/backend/others/reduce_bitmask_cuda.cu:60-87), for sorted
+ * maps only; here every implicit-GEMM launch uses it. */
+size_t tsb_map_tile_mask_bytes(int64_t n_rows);
+int tsb_map_tile_mask(const int32_t* map, int64_t n_rows, int32_t kvol, int64_t row_stride, int64_t col_stride,
+                      const int32_t* n_rows_dev, uint32_t* out, tsb_stream_t stream);
+
+/* The full form of the implicit-GEMM forward: every argument of tsb_conv_igemm_fwd plus the options
+ * below, in one descriptor (zero / NULL = option not used).  A caller fills `struct_bytes` with
+ * sizeof(tsb_igemm_desc); a library built against another layout refuses the call with TSB_ERR_BAD_ARG.
+ *   in_feats2 / c1     the input channels are the concatenation of in_feats [n_in, c1] and in_feats2
+ *                      [n_in, cin - c1]; the concatenated matrix is never written (replaces the
+ *                      torchsparse.cat in front of a convolution, torchsparse/operators.py:12-16)
+ *   map_row_stride / map_col_stride   element strides of the map (0, 0: row-major [rows][kvol]);
+ *                      out_in_map == NULL with kvol == 1: output row m reads input row m (a 1x1x1
+ *                      convolution, torchsparse/nn/functional/conv/conv.py:65-74, on the same kernel)
+ *   n_out_dev          int32 in device memory holding the number of output rows; n_out is then only an
+ *                      upper bound (it sizes the launch), so the same launch can be replayed for inputs of
+ *                      other sizes, e.g. inside a CUDA graph
+ *   k_lo, k_hi         only the kernel offsets [k_lo, k_hi) are multiplied (0, 0: all)
+ *   acc_in / acc_out   fp32 [rows of out_feats, cout]: acc_in is added to the accumulator; with acc_out
+ *                      the sum is stored there in fp32 and out_feats / the epilogue are skipped.  A group
+ *                      of launches over disjoint offset ranges, chained through these buffers, is the
+ *                      split-mask form of the sorted dataflow
+ *                      (convolution_forward_implicit_gemm_sorted_cuda.cu:42-86, 2226-2229) with the
+ *                      partial sums kept in fp32 instead of being rounded per split
+ *   cfg_*              launch-configuration overrides for tuning runs (N tile, 128-byte channel chunks
+ *                      per pipeline stage, stages, CTAs per SM); 0 = chosen by the library
+ * Tensor-core shapes only (see above); other shapes return TSB_ERR_UNSUPPORTED. */
+typedef struct tsb_igemm_desc {
+  uint32_t struct_bytes;
+  int32_t dtype, math, relu;
+  const void* in_feats;
+  const void* in_feats2;
+  const void* weight;
+  const void* packed_weight;
+  const int32_t* out_in_map;
+  const int32_t* reorder_loc;
+  const uint32_t* tile_mask;
+  void* out_feats;
+  const float* scale;
+  const float* bias;
+  const void* residual;
+  const float* acc_in;
+  float* acc_out;
+  const int32_t* n_out_dev;
+  int32_t* dev_status;
+  void* workspace;
+  size_t workspace_bytes;
+  int64_t n_in, n_out, dst_rows;
+  int64_t map_row_stride, map_col_stride;
+  int32_t kvol, cin, cout, c1;
+  int32_t k_lo, k_hi;
+  int32_t cfg_n_tile, cfg_cpb, cfg_stages, cfg_ctas;
+} tsb_igemm_desc;
+int tsb_conv_igemm_run(const tsb_igemm_desc* desc, tsb_stream_t stream);
 
 /* The tensor-core kernel reads the weights K-major ([kvol, cout, cin]).  A caller whose weights
  * do not change between calls (inference) packs them once and passes the result as

@@ -32,8 +32,8 @@ def test_status_strings_and_argument_checks():
     # null pointers / bad sizes are refused before any CUDA call
     assert lib.tsb_coord_hash(None, 5, None, None) == 1
     assert lib.tsb_coord_hash(None, 0, None, None) == 0
-    assert lib.tsb_conv_igemm_fwd(None, None, None, None, None, None, 1, 1, 27, 0, 8, 0, 0, None, None, None, 0, None, None, 0, None) == 1
-    assert lib.tsb_conv_igemm_fwd(None, None, None, None, None, None, 1, 1, 27, 8, 8, 9, 0, None, None, None, 0, None, None, 0, None) == 2
+    assert lib.tsb_conv_igemm_fwd(None, None, None, None, None, None, None, 1, 1, 27, 0, 8, 0, 0, None, None, None, 0, None, None, 0, None) == 1
+    assert lib.tsb_conv_igemm_fwd(None, None, None, None, None, None, None, 1, 1, 27, 8, 8, 9, 0, None, None, None, 0, None, None, 0, None) == 2
     assert lib.tsb_bitmask_reduce(None, 10, 1, 6, None, None) == 1
     assert lib.tsb_kmap_down_slots(i32x((2, 2, 2)), i32x((2, 2, 2))) == 1
     assert lib.tsb_kmap_down_slots(i32x((3, 3, 3)), i32x((2, 2, 2))) == 8

@@ -1,0 +1,177 @@
+"""GPU parity of the options of the tensor-core implicit-GEMM entry point (tsb_conv_igemm_run) against the
+fp64 oracle: per-tile offset masks, the row-sorted column-major map, a two-matrix input (unwritten channel
+concatenation), the map-less 1x1x1 form, chained offset ranges with fp32 partial sums, a row count held in
+device memory, and the launch-configuration overrides.
+
+Tolerance: relative L2 <= 2e-3 for fp16 operands (fp32 accumulation, one rounding), as for every fp16
+convolution test of this suite."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import random_coords, rel_l2
+from oracle import kmap_oracle as ko
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _case(n=5000, shape=(40, 40, 40), cin=64, cout=96, seed=0, ks=3):
+    rng = np.random.default_rng(seed)
+    coords = random_coords(rng, n, shape)
+    feats = rng.standard_normal((n, cin)).astype(np.float32)
+    kvol = ks ** 3
+    w = (rng.standard_normal((kvol, cin, cout)) / np.sqrt(kvol * cin)).astype(np.float32)
+    km = ko.build_kmap(coords, ks, 1, (ks - 1) // 2)
+    f16 = torch.from_numpy(feats).half()
+    w16 = torch.from_numpy(w).half()
+    want = ko.conv_from_map(f16.float().numpy(), w16.float().numpy(), km["out_in_map"], n)
+    return coords, f16.cuda(), w16.cuda(), km, want
+
+
+def test_tile_mask_matches_oracle():
+    from torchsparse_b200 import backend
+
+    _, _, _, km, _ = _case(n=3000)
+    m = km["out_in_map"]
+    n = km["sizes"][1]
+    got = backend.tile_mask_cuda(torch.from_numpy(m).cuda(), n).cpu().numpy().astype(np.uint32)
+    valid = (m >= 0)
+    valid[n:] = False
+    tiles = (n + 127) // 128
+    want = np.array([sum(1 << k for k in np.nonzero(valid[t * 128:(t + 1) * 128].any(0))[0]) for t in range(tiles)],
+                    dtype=np.uint32)
+    assert np.array_equal(got[:tiles], want)
+    # the same masks from a column-major copy of the map
+    cm = torch.from_numpy(np.ascontiguousarray(m.T)).cuda()
+    got_cm = backend.tile_mask_cuda(cm, n, 1, m.shape[0]).cpu().numpy().astype(np.uint32)
+    assert np.array_equal(got_cm[:tiles], want)
+
+
+def test_sorted_cm_artefacts_are_a_permutation_of_the_map():
+    from torchsparse_b200 import backend
+
+    _, _, _, km, _ = _case(n=3000)
+    m = km["out_in_map"]
+    n = km["sizes"][1]
+    map_cm, loc, tmask = backend.sorted_cm_artefacts_cuda(torch.from_numpy(m).cuda(), n)
+    map_cm, loc, tmask = map_cm.cpu().numpy(), loc.cpu().numpy(), tmask.cpu().numpy().astype(np.uint32)
+    assert sorted(loc[:n].tolist()) == list(range(n))               # the valid rows, each once
+    assert np.array_equal(map_cm[:, :n], m[loc[:n]].T)               # row r of the sorted map is map row loc[r]
+    assert (map_cm[:, n:] == -1).all()
+    masks = ((m[:n] >= 0) * (1 << np.arange(m.shape[1]))).sum(1)
+    assert (np.diff(masks[loc[:n]]) <= 0).all()                      # descending neighbour masks
+    same = masks[loc[:n]][1:] == masks[loc[:n]][:-1]
+    assert (np.diff(loc[:n])[same] > 0).all()                        # stable: equal masks keep row order
+    valid = map_cm >= 0
+    want = np.array([sum(1 << k for k in np.nonzero(valid[:, t * 128:(t + 1) * 128].any(1))[0])
+                     for t in range(m.shape[0] // 128)], dtype=np.uint32)
+    assert np.array_equal(tmask, want)
+
+
+@pytest.mark.parametrize("cin,cout", [(64, 96), (96, 96), (32, 32), (256, 128), (8, 32)])
+def test_sorted_cm_conv(cin, cout):
+    from torchsparse_b200 import backend
+
+    _, f, w, km, want = _case(cin=cin, cout=cout)
+    n = km["sizes"][1]
+    map_cm, loc, tmask = backend.sorted_cm_artefacts_cuda(torch.from_numpy(km["out_in_map"]).cuda(), n)
+    y = backend.conv_forward_implicit_gemm_cuda(f, w, map_cm, n, cout, reorder_loc=loc, tile_mask=tmask,
+                                                map_strides=(1, map_cm.shape[1]))
+    assert rel_l2(y.float().cpu().numpy(), want) < TOL
+
+
+@pytest.mark.parametrize("c1,c2,cout", [(64, 32, 96), (96, 32, 96), (256, 128, 256), (8, 8, 16)])
+def test_two_matrix_input_equals_concatenation(c1, c2, cout):
+    from torchsparse_b200 import backend
+
+    _, f, w, km, want = _case(cin=c1 + c2, cout=cout, n=3000)
+    n = km["sizes"][1]
+    m = torch.from_numpy(km["out_in_map"]).cuda()
+    fa, fb = f[:, :c1].contiguous(), f[:, c1:].contiguous()
+    y = backend.conv_forward_implicit_gemm_cuda(fa, w, m, n, cout, in_feats2=fb)
+    assert rel_l2(y.float().cpu().numpy(), want) < TOL
+    y_cat = backend.conv_forward_implicit_gemm_cuda(f, w, m, n, cout)
+    assert torch.equal(y, y_cat)     # the same arithmetic on the same operands
+
+
+def test_pointwise_without_a_map():
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(1)
+    n, cin, cout = 4001, 192, 128
+    f = torch.from_numpy(rng.standard_normal((n, cin)).astype(np.float32)).half()
+    w = torch.from_numpy((rng.standard_normal((1, cin, cout)) / np.sqrt(cin)).astype(np.float32)).half()
+    scale = torch.from_numpy(rng.uniform(0.5, 1.5, cout).astype(np.float32))
+    bias = torch.from_numpy(rng.standard_normal(cout).astype(np.float32))
+    res = torch.from_numpy(rng.standard_normal((n, cout)).astype(np.float32)).half()
+    want = np.maximum(f.double().numpy() @ w[0].double().numpy() * scale.double().numpy() + bias.double().numpy()
+                      + res.double().numpy(), 0)
+    y = backend.conv_forward_implicit_gemm_cuda(f.cuda(), w.cuda(), None, n, cout, scale=scale.cuda(), bias=bias.cuda(),
+                                                residual=res.cuda(), relu=True)
+    assert rel_l2(y.float().cpu().numpy(), want) < TOL
+    # and from two matrices
+    y2 = backend.conv_forward_implicit_gemm_cuda(f[:, :128].contiguous().cuda(), w.cuda(), None, n, cout,
+                                                 scale=scale.cuda(), bias=bias.cuda(), residual=res.cuda(), relu=True,
+                                                 in_feats2=f[:, 128:].contiguous().cuda())
+    assert torch.equal(y, y2)
+
+
+def test_offset_ranges_chained_through_fp32_partial_sums():
+    from torchsparse_b200 import backend
+
+    _, f, w, km, want = _case(cin=64, cout=64, n=3000)
+    n = km["sizes"][1]
+    m = torch.from_numpy(km["out_in_map"]).cuda()
+    acc = torch.empty((n, 64), dtype=torch.float32, device="cuda")
+    bias = torch.linspace(-1, 1, 64, device="cuda")
+    backend.conv_forward_implicit_gemm_cuda(f, w, m, n, 64, k_range=(0, 9), acc_out=acc)
+    backend.conv_forward_implicit_gemm_cuda(f, w, m, n, 64, k_range=(9, 18), acc_in=acc, acc_out=acc)
+    y = backend.conv_forward_implicit_gemm_cuda(f, w, m, n, 64, k_range=(18, 27), acc_in=acc, bias=bias)
+    assert rel_l2(y.float().cpu().numpy(), want + bias.cpu().numpy()) < TOL
+
+
+def test_row_count_in_device_memory():
+    from torchsparse_b200 import backend
+
+    _, f, w, km, want = _case(cin=64, cout=64, n=3000)
+    n = km["sizes"][1]
+    m = torch.from_numpy(km["out_in_map"]).cuda()
+    rows_max = 4096                                   # upper bound the launch is sized for
+    m_big = torch.full((rows_max, 27), -1, dtype=torch.int32, device="cuda")
+    m_big[: m.shape[0]] = m
+    out = torch.full((rows_max, 64), 7.0, dtype=torch.float16, device="cuda")
+    n_dev = torch.tensor([n], dtype=torch.int32, device="cuda")
+    backend.conv_forward_implicit_gemm_cuda(f, w, m_big, rows_max, 64, n_out_dev=n_dev, out=out)
+    assert rel_l2(out[:n].float().cpu().numpy(), want) < TOL
+    assert (out[(n + 127) // 128 * 128:] == 7.0).all()        # tiles beyond the device-side count are not touched
+
+
+@pytest.mark.parametrize("cfg", [dict(cpb=2), dict(cpb=2, ctas=1), dict(n_tile=64), dict(ctas=1, stages=3),
+                                 dict(n_tile=32, cpb=2, ctas=2)])
+def test_launch_configuration_overrides(cfg):
+    from torchsparse_b200 import backend
+
+    _, f, w, km, want = _case(cin=96, cout=128, n=3000)
+    n = km["sizes"][1]
+    m = torch.from_numpy(km["out_in_map"]).cuda()
+    old = dict(backend.igemm_tuning)
+    try:
+        backend.igemm_tuning.update(cfg)
+        y = backend.conv_forward_implicit_gemm_cuda(f, w, m, n, 128)
+    finally:
+        backend.igemm_tuning.update(old)
+    assert rel_l2(y.float().cpu().numpy(), want) < TOL
+
+
+def test_split_sorted_on_tensor_cores_fp16():
+    """F.set_conv_mode(2)'s configuration (row-sorted map, 3 mask splits) through F.conv3d."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    coords, f, w, km, want = _case(cin=64, cout=64, n=4000)
+    cfg = F.conv_config.get_default_conv_config()
+    cfg.ifsort, cfg.split_mask_num = True, 3
+    x = ts.SparseTensor(f, torch.from_numpy(coords).cuda())
+    y = F.conv3d(x, w, 3, None, 1, 1, config=cfg)
+    assert rel_l2(y.feats.float().cpu().numpy(), want) < TOL

@@ -39,14 +39,14 @@ def _randomise_bn(model):
 
 
 def _gpu_forward(model, coords, feats, dtype, engine):
-    """engine: False = the module graph as written, True = fused inference engine,
-    "sorted" = the engine with row-sorted kernel maps at every level."""
+    """engine: False = the module graph as written, True = fused inference engine (row-sorted
+    column-major kernel maps, the default), "unsorted" = the engine on the maps as built."""
     import torchsparse_b200 as ts
     from torchsparse_b200.nn import InferenceEngine
 
     m = model.cuda().to(dtype).eval()
     if engine:
-        m = InferenceEngine(m, sort_max_stride=16 if engine == "sorted" else 0)
+        m = InferenceEngine(m, sorted_maps=engine != "unsorted")
     x = ts.SparseTensor(torch.from_numpy(feats).cuda().to(dtype), torch.from_numpy(coords).cuda())
     with torch.no_grad():
         out = m(x)
@@ -58,7 +58,7 @@ def _gpu_forward(model, coords, feats, dtype, engine):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3)])
-@pytest.mark.parametrize("engine", [False, True, "sorted"])
+@pytest.mark.parametrize("engine", [False, True, "unsorted"])
 def test_unet_matches_cpu_oracle(dtype, tol, engine):
     import copy
     from torchsparse_b200.backbones import SparseResUNet42

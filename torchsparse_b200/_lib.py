@@ -48,7 +48,12 @@ SIGNATURES = {
     "tsb_scan_quantified": (C.c_int, [I32, P, P, P, P]),
     "tsb_build_masks": (C.c_int, [I64, I64, P, P, I32, I64, P, P, P]),
     "tsb_conv_igemm_workspace_bytes": (SZ, [I32, I32, I32, I32]),
-    "tsb_conv_igemm_fwd": (C.c_int, [P, P, P, P, P, P, I64, I64, I32, I32, I32, I32, I32, P, P, P, I32, P, P, SZ, P]),
+    "tsb_conv_igemm_fwd": (C.c_int, [P, P, P, P, P, P, P, I64, I64, I32, I32, I32, I32, I32, P, P, P, I32, P, P, SZ, P]),
+    "tsb_map_tile_mask_bytes": (SZ, [I64]),
+    "tsb_map_tile_mask": (C.c_int, [P, I64, I32, I64, I64, P, P, P]),
+    "tsb_conv_igemm_run": (C.c_int, [P, P]),
+    "tsb_map_sorted_cm_workspace_bytes": (SZ, [I64]),
+    "tsb_map_sorted_cm": (C.c_int, [P, I64, I32, I64, P, P, P, P, P, SZ, P]),
     "tsb_conv_packed_weight_bytes": (SZ, [I32, I32, I32, I32]),
     "tsb_conv_pack_weight": (C.c_int, [P, I32, I32, I32, I32, P, P]),
     "tsb_conv_gs_workspace_bytes": (SZ, [I64, I32, I32, I32, I32]),
@@ -64,6 +69,26 @@ SIGNATURES = {
     "tsb_quantize_unique": (C.c_int, [P, I32, I64, P, P, P, P, P, P, P, SZ, P]),
     "tsb_to_dense_fwd": (C.c_int, [P, P, I64, I32, P, I32, P, P]),
 }
+
+class IgemmDesc(C.Structure):
+    """tsb_igemm_desc of include/tsb200.h, field for field."""
+    _fields_ = [
+        ("struct_bytes", C.c_uint32), ("dtype", I32), ("math", I32), ("relu", I32),
+        ("in_feats", P), ("in_feats2", P), ("weight", P), ("packed_weight", P), ("out_in_map", P),
+        ("reorder_loc", P), ("tile_mask", P), ("out_feats", P), ("scale", P), ("bias", P), ("residual", P),
+        ("acc_in", P), ("acc_out", P), ("n_out_dev", P), ("dev_status", P), ("workspace", P),
+        ("workspace_bytes", SZ), ("n_in", I64), ("n_out", I64), ("dst_rows", I64),
+        ("map_row_stride", I64), ("map_col_stride", I64),
+        ("kvol", I32), ("cin", I32), ("cout", I32), ("c1", I32), ("k_lo", I32), ("k_hi", I32),
+        ("cfg_n_tile", I32), ("cfg_cpb", I32), ("cfg_stages", I32), ("cfg_ctas", I32),
+    ]
+
+
+def new_igemm_desc() -> "IgemmDesc":
+    d = IgemmDesc()
+    d.struct_bytes = C.sizeof(IgemmDesc)
+    return d
+
 
 TSB_OK = 0
 TSB_F32, TSB_F16, TSB_BF16 = 0, 1, 2

@@ -32,7 +32,7 @@ __all__ = [
     "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
     "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
-    "pairs_from_out_in_map", "quantize_unique_cuda",
+    "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda",
 ]
 
 _DTYPES = {torch.float32: _lib.TSB_F32, torch.float16: _lib.TSB_F16, torch.bfloat16: _lib.TSB_BF16}
@@ -327,6 +327,22 @@ def sorted_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, m_tile: int):
     return masks[0], masks[1], reordered, reduced
 
 
+def sorted_cm_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, valid_n_dev: Optional[torch.Tensor] = None):
+    """The row order and layout the tensor-core convolution is fastest on (tsb_map_sorted_cm): returns
+    (map_cm int32 [Kvol, rows] column-major and row-sorted, reorder_loc int32 [rows], tile_mask int32
+    [rows / 128]).  Launch with ``map_strides=(1, rows)``."""
+    _need_cuda(out_in_map)
+    rows, kvol = out_in_map.shape
+    dev = out_in_map.device
+    map_cm = torch.empty((kvol, rows), dtype=torch.int32, device=dev)
+    loc = torch.empty(rows, dtype=torch.int32, device=dev)
+    tile_mask = torch.empty(max(rows // 128, 1), dtype=torch.int32, device=dev)
+    ws = _workspace(lib.tsb_map_sorted_cm_workspace_bytes(rows), dev)
+    check(lib.tsb_map_sorted_cm(_p(out_in_map), rows, kvol, int(valid_n), _p(valid_n_dev), _p(loc), _p(map_cm),
+                                _p(tile_mask), _p(ws), ws.numel(), _stream()), "sorted_cm_artefacts_cuda")
+    return map_cm, loc, tile_mask
+
+
 def reduce_bitmask_cuda(bitmask: torch.Tensor, m_tile: int) -> torch.Tensor:
     """int32 [split, ceil(rows/tile)] (torchsparse/backend/others/reduce_bitmask_cuda.cu:60-87)."""
     _need_cuda(bitmask)
@@ -449,6 +465,14 @@ def _padded_kernel(kernel: torch.Tensor) -> torch.Tensor:
     return padded
 
 
+def _tensor_core_shape(in_feats: torch.Tensor, kernel: torch.Tensor, allow_tf32: bool) -> bool:
+    """Shapes the tcgen05 kernel takes (include/tsb200.h, tsb_conv_igemm_fwd)."""
+    kvol, cin, cout = kernel.shape
+    if in_feats.dtype == torch.float32 and not allow_tf32:
+        return False
+    return (cin * in_feats.element_size()) % 16 == 0 and cout % 8 == 0 and kvol <= 32
+
+
 def _math_mode(t: torch.Tensor, allow_tf32: bool) -> int:
     return _lib.TSB_MATH_TF32 if (t.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
 
@@ -466,116 +490,255 @@ def _prep_feats(in_feats: torch.Tensor, kernel: torch.Tensor, allow_fp16: bool):
     return in_feats.contiguous(), kernel.contiguous()
 
 
-def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,
+# Launch-configuration overrides of the tensor-core kernel for tuning runs (0 = chosen by the library):
+# N tile, 128-byte channel chunks per pipeline stage, stages, CTAs per SM.
+igemm_tuning = {"n_tile": 0, "cpb": 0, "stages": 0, "ctas": 0}
+
+
+def tile_mask_cuda(out_in_map: torch.Tensor, n_rows: int, row_stride: Optional[int] = None,
+                   col_stride: Optional[int] = None, n_rows_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """uint32-as-int32 [ceil(n_rows / 128)]: the kernel offsets present in each 128-row tile of a map whose
+    entry (row, k) lies at ``row * row_stride + k * col_stride`` (default: row-major [rows, Kvol])."""
+    _need_cuda(out_in_map)
+    kvol = out_in_map.shape[1] if row_stride is None else None
+    if row_stride is None:
+        row_stride, col_stride = out_in_map.shape[1], 1
+    else:
+        kvol = out_in_map.shape[0] if col_stride != 1 else out_in_map.shape[1]
+    out = torch.empty(max(1, (n_rows + 127) // 128), dtype=torch.int32, device=out_in_map.device)
+    check(lib.tsb_map_tile_mask(_p(out_in_map), n_rows, kvol, row_stride, col_stride, _p(n_rows_dev), _p(out), _stream()),
+          "tile_mask_cuda")
+    return out
+
+
+def _tile_mask_of(out_in_map: torch.Tensor, n_rows: int) -> Optional[torch.Tensor]:
+    """Tile masks of a row-major map, derived once and kept on the map tensor (a kernel map is shared
+    by the layers of a resolution level; the masks are rebuilt if the tensor is modified in place)."""
+    if out_in_map.shape[1] > 32 or not out_in_map.is_contiguous():
+        return None
+    tag = (out_in_map._version, out_in_map.data_ptr(), n_rows)
+    hit = getattr(out_in_map, "_tsb_tile_mask", None)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    mask = tile_mask_cuda(out_in_map, n_rows)
+    try:
+        out_in_map._tsb_tile_mask = (tag, mask)
+    except (AttributeError, RuntimeError):
+        pass
+    return mask
+
+
+def _apply_tuning(d) -> None:
+    d.cfg_n_tile, d.cfg_cpb = igemm_tuning["n_tile"], igemm_tuning["cpb"]
+    d.cfg_stages, d.cfg_ctas = igemm_tuning["stages"], igemm_tuning["ctas"]
+
+
+def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: Optional[torch.Tensor],
                                     num_out_feats: int, num_out_channels: int, allow_tf32: bool = False,
                                     allow_fp16: bool = True, *, scale: Optional[torch.Tensor] = None,
                                     bias: Optional[torch.Tensor] = None,
                                     residual: Optional[torch.Tensor] = None, relu: bool = False,
-                                    reorder_loc: Optional[torch.Tensor] = None) -> torch.Tensor:
+                                    reorder_loc: Optional[torch.Tensor] = None,
+                                    tile_mask: Optional[torch.Tensor] = None,
+                                    in_feats2: Optional[torch.Tensor] = None,
+                                    map_strides: Optional[Tuple[int, int]] = None,
+                                    k_range: Optional[Tuple[int, int]] = None,
+                                    acc_in: Optional[torch.Tensor] = None, acc_out: Optional[torch.Tensor] = None,
+                                    n_out_dev: Optional[torch.Tensor] = None,
+                                    out: Optional[torch.Tensor] = None, dst_rows: int = 0) -> Optional[torch.Tensor]:
     """Implicit-GEMM forward
     (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987).
     ``scale`` / ``bias`` (fp32 [Cout]), ``residual`` and ``relu`` are an optional fused epilogue
-    (y = relu(acc * scale + bias + residual), one rounding) that the reference does not have."""
-    in_feats, kernel = _prep_feats(in_feats, kernel, allow_fp16)
-    _need_cuda(out_in_map)
+    (y = relu(acc * scale + bias + residual), one rounding) that the reference does not have.
+    The remaining keywords are the options of ``tsb_conv_igemm_run`` (include/tsb200.h): a second feature
+    matrix whose channels follow those of ``in_feats``, a map with other strides (or ``None`` with a
+    1x1x1 kernel: row m reads input row m), a range of kernel offsets, fp32 partial sums in / out, a
+    device-side row count and a caller-owned output."""
+    in_feats, kernel = _prep_feats_cat(in_feats, in_feats2, kernel, allow_fp16)
+    if in_feats2 is not None:
+        in_feats2 = in_feats2.contiguous()
     kvol, cin, cout = kernel.shape
     if num_out_channels != cout:
         raise ValueError("num_out_channels does not match the kernel")
-    if in_feats.dtype != torch.float32 and cin % 8 != 0 and cout % 8 == 0 and kvol <= 32:
+    if in_feats.dtype != torch.float32 and cin % 8 != 0 and cout % 8 == 0 and kvol <= 32 and in_feats2 is None:
         # rows that are not 16-byte multiples (the 4- or 5-channel input layer): zero-pad the channels
         # once so that the layer takes the tensor-core kernel instead of the CUDA-core one
         kernel = _padded_kernel(kernel)
         in_feats = torch.nn.functional.pad(in_feats, (0, kernel.shape[1] - cin))
         cin = kernel.shape[1]
-    if out_in_map.shape[1] != kvol or out_in_map.shape[0] < num_out_feats:
-        raise ValueError("out_in_map shape does not match kernel volume / output rows")
-    out = torch.empty((num_out_feats, cout), dtype=in_feats.dtype, device=in_feats.device)
+    if out_in_map is None:
+        if kvol != 1:
+            raise ValueError("a convolution without a kernel map needs a 1x1x1 kernel")
+    else:
+        _need_cuda(out_in_map)
+        if map_strides is None and (out_in_map.shape[1] != kvol or out_in_map.shape[0] < num_out_feats):
+            raise ValueError("out_in_map shape does not match kernel volume / output rows")
     code = _dtype_code(in_feats)
+    if out is None and acc_out is None:
+        out = torch.empty((num_out_feats if not dst_rows else dst_rows, cout), dtype=in_feats.dtype,
+                          device=in_feats.device)
     if bias is not None:
         bias = bias.float().contiguous()
     if scale is not None:
         scale = scale.float().contiguous()
     if residual is not None:
         residual = residual.to(in_feats.dtype).contiguous()
-    packed = _packed_weight(kernel, code, bool(allow_tf32)) if cache_packed_weights else None
+    tensor_cores = code != _lib.TSB_F32 or bool(allow_tf32)
+    packed = _packed_weight(kernel, code, bool(allow_tf32)) if (cache_packed_weights and tensor_cores) else None
     if check_kernel_status:
         status = torch.zeros(1, dtype=torch.int32, device=in_feats.device)
     else:
         status = _status_word(in_feats.device)
-    # with packed weights and a status word supplied the kernel needs no workspace
-    ws = None if packed is not None else _workspace(lib.tsb_conv_igemm_workspace_bytes(kvol, cin, cout, code),
-                                                    in_feats.device)
+    if tile_mask is None and tensor_cores and out_in_map is not None and map_strides is None and kvol > 1:
+        tile_mask = _tile_mask_of(out_in_map, num_out_feats)
+    # what is not supplied is made in the workspace: packed weights, tile masks
+    ws = None
+    if packed is None or (tile_mask is None and out_in_map is not None):
+        ws = _workspace(lib.tsb_conv_igemm_workspace_bytes(kvol, cin, cout, code)
+                        + lib.tsb_map_tile_mask_bytes(num_out_feats), in_feats.device)
     if _observer is not None:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
-    check(lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(packed), _p(out_in_map), _p(reorder_loc), _p(out),
-                                 in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
-                                 _math_mode(in_feats, allow_tf32), _p(scale), _p(bias), _p(residual), int(relu),
-                                 _p(status),
-                                 _p(ws), 0 if ws is None else ws.numel(), _stream()),
-          "conv_forward_implicit_gemm_cuda")
+    d = _lib.new_igemm_desc()
+    d.dtype, d.math, d.relu = code, _math_mode(in_feats, allow_tf32), int(relu)
+    d.in_feats, d.in_feats2, d.weight, d.packed_weight = _p(in_feats), _p(in_feats2), _p(kernel), _p(packed)
+    d.out_in_map, d.reorder_loc, d.tile_mask, d.out_feats = _p(out_in_map), _p(reorder_loc), _p(tile_mask), _p(out)
+    d.scale, d.bias, d.residual = _p(scale), _p(bias), _p(residual)
+    d.acc_in, d.acc_out, d.n_out_dev, d.dev_status = _p(acc_in), _p(acc_out), _p(n_out_dev), _p(status)
+    d.workspace, d.workspace_bytes = _p(ws), 0 if ws is None else ws.numel()
+    d.n_in, d.n_out, d.dst_rows = in_feats.shape[0], num_out_feats, int(dst_rows)
+    if map_strides is not None:
+        d.map_row_stride, d.map_col_stride = map_strides
+    d.kvol, d.cin, d.cout = kvol, cin, cout
+    d.c1 = in_feats.shape[1] if in_feats2 is not None else 0
+    if k_range is not None:
+        d.k_lo, d.k_hi = k_range
+    _apply_tuning(d)
+    rc = lib.tsb_conv_igemm_run(_lib.C.byref(d), _stream())
+    if rc == 2:
+        # shapes the tensor-core kernel does not take (exact fp32, odd row sizes): the CUDA-core kernel
+        # behind the flat entry point, which has none of the options above
+        if (in_feats2 is not None or map_strides is not None or k_range is not None or acc_in is not None
+                or acc_out is not None or n_out_dev is not None or out_in_map is None):
+            check(rc, "conv_forward_implicit_gemm_cuda (these options need a tensor-core shape)")
+        rc = lib.tsb_conv_igemm_fwd(_p(in_feats), _p(kernel), _p(packed), _p(out_in_map), _p(reorder_loc),
+                                    _p(tile_mask), _p(out), in_feats.shape[0], num_out_feats, kvol, cin, cout, code,
+                                    _math_mode(in_feats, allow_tf32), _p(scale), _p(bias), _p(residual), int(relu),
+                                    _p(status), _p(ws), 0 if ws is None else ws.numel(), _stream())
+    check(rc, "conv_forward_implicit_gemm_cuda")
     if _observer is not None:
         ev1.record()
-        _observer("igemm", (in_feats.shape[0], num_out_feats, kvol, cin, cout, code, out_in_map), ev0, ev1)
+        _observer("igemm", (in_feats.shape[0], num_out_feats, kvol, cin, cout, code, out_in_map,
+                            tile_mask, k_range), ev0, ev1)
     if check_kernel_status and int(status.item()) != 0:
         raise RuntimeError(f"conv_forward_implicit_gemm_cuda: a bounded wait inside the kernel ran out "
                            f"(code {int(status.item())}); the output is undefined")
     return out
 
 
-class IgemmLayerPlan:
-    """The arguments of tsb_conv_igemm_fwd that do not change between calls of one inference layer
-    (weights, packed weights, fp32 scale / shift, sizes), resolved once.  :func:`igemm_plan_launch` then
-    costs one output allocation and one foreign call; argument checks happened when the plan was made.
-    The plan keeps the tensors alive and is remade when the weights are replaced or modified."""
+def _prep_feats_cat(in_feats, in_feats2, kernel, allow_fp16):
+    """_prep_feats for an input that may be the channel concatenation of two matrices."""
+    if in_feats2 is None:
+        return _prep_feats(in_feats, kernel, allow_fp16)
+    _need_cuda(in_feats, in_feats2, kernel)
+    if in_feats.dtype != kernel.dtype or in_feats2.dtype != kernel.dtype:
+        raise RuntimeError("input features and kernel must share a dtype")
+    if in_feats.shape[0] != in_feats2.shape[0]:
+        raise ValueError("the two feature matrices must have the same rows")
+    if kernel.dim() != 3 or in_feats.shape[1] + in_feats2.shape[1] != kernel.shape[1]:
+        raise ValueError("Input feature size and kernel size mismatch")
+    return in_feats.contiguous(), kernel.contiguous()
 
-    __slots__ = ("kernel", "packed", "scale", "bias", "tag", "args_head", "args_tail", "cout", "dtype", "device")
+
+class IgemmLayerPlan:
+    """The arguments of tsb_conv_igemm_run that do not change between calls of one inference layer
+    (weights, packed weights, fp32 scale / shift, sizes), resolved once into a descriptor.
+    :func:`igemm_plan_launch` then costs one output allocation and one foreign call; argument checks
+    happened when the plan was made.  The plan keeps the tensors alive and is remade when the weights
+    are replaced or modified."""
+
+    __slots__ = ("kernel", "packed", "scale", "bias", "tag", "desc", "cin", "cout", "dtype", "device", "allow_tf32")
 
     def __init__(self, kernel: torch.Tensor, scale: Optional[torch.Tensor], bias: Optional[torch.Tensor],
-                 allow_tf32: bool):
+                 allow_tf32: bool, relu: bool = False):
         _need_cuda(kernel)
         if kernel.dim() != 3:
             raise ValueError("kernel must be [Kvol, Cin, Cout]")
         kernel = kernel.contiguous()
         kvol, cin, cout = kernel.shape
         code = _dtype_code(kernel)
-        if kernel.dtype != torch.float32 and cin % 8 != 0:
-            raise ValueError("IgemmLayerPlan needs feature rows that are 16-byte multiples")
+        if (cin * kernel.element_size()) % 16 != 0 or cout % 8 != 0 or kvol > 32:
+            raise ValueError("IgemmLayerPlan needs feature rows that are 16-byte multiples and Cout % 8 == 0")
+        if code == _lib.TSB_F32 and not allow_tf32:
+            raise ValueError("IgemmLayerPlan is for the tensor-core kernel (16-bit tensors or TF32)")
         self.tag = (kernel._version, kernel.data_ptr(), bool(allow_tf32))
+        self.allow_tf32 = bool(allow_tf32)
         self.kernel = kernel
         self.packed = _packed_weight(kernel, code, bool(allow_tf32))
         self.scale = None if scale is None else scale.float().contiguous()
         self.bias = None if bias is None else bias.float().contiguous()
-        self.cout, self.dtype = cout, kernel.dtype
+        self.cin, self.cout, self.dtype = cin, cout, kernel.dtype
         self.device = kernel.device if kernel.device.index is not None else torch.device("cuda", kernel.get_device())
-        math = _lib.TSB_MATH_TF32 if (kernel.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
-        self.args_head = (kernel.data_ptr(), _p(self.packed))
-        self.args_tail = (kvol, cin, cout, code, math, _p(self.scale), _p(self.bias))
+        d = self.desc = _lib.new_igemm_desc()
+        d.dtype = code
+        d.math = _lib.TSB_MATH_TF32 if (kernel.dtype == torch.float32 and allow_tf32) else _lib.TSB_MATH_FP32
+        d.relu = int(relu)
+        d.weight, d.packed_weight = kernel.data_ptr(), _p(self.packed)
+        d.scale, d.bias = _p(self.scale), _p(self.bias)
+        d.dev_status = _status_word(self.device).data_ptr()
+        d.kvol, d.cin, d.cout = kvol, cin, cout
 
     def valid_for(self, kernel: torch.Tensor, allow_tf32: bool) -> bool:
         return self.tag == (kernel._version, kernel.data_ptr(), bool(allow_tf32))
 
 
-def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: torch.Tensor, num_out_feats: int,
-                      residual: Optional[torch.Tensor], relu: bool,
-                      reorder_loc: Optional[torch.Tensor] = None) -> torch.Tensor:
+def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: Optional[torch.Tensor],
+                      num_out_feats: int, residual: Optional[torch.Tensor], relu: bool,
+                      reorder_loc: Optional[torch.Tensor] = None, tile_mask: Optional[torch.Tensor] = None,
+                      in_feats2: Optional[torch.Tensor] = None, map_strides: Optional[Tuple[int, int]] = None,
+                      n_out_dev: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """conv_forward_implicit_gemm_cuda for a layer with an :class:`IgemmLayerPlan` (same kernel launch).
     Falls back to the checked entry point when launches are being observed or their status read back."""
-    if _observer is not None or check_kernel_status or plan.packed is None:
+    if _observer is not None or check_kernel_status:
         return conv_forward_implicit_gemm_cuda(in_feats, plan.kernel, out_in_map, num_out_feats, plan.cout,
-                                               plan.tag[2], True, scale=plan.scale, bias=plan.bias,
-                                               residual=residual, relu=relu, reorder_loc=reorder_loc)
-    if in_feats.dtype != plan.dtype or not in_feats.is_contiguous() or in_feats.shape[1] != plan.args_tail[1]:
-        raise ValueError("input features do not match the layer plan (dtype, layout or channel count)")
+                                               plan.allow_tf32, True, scale=plan.scale, bias=plan.bias,
+                                               residual=residual, relu=relu, reorder_loc=reorder_loc,
+                                               tile_mask=tile_mask, in_feats2=in_feats2, map_strides=map_strides,
+                                               n_out_dev=n_out_dev, out=out)
+    c1 = in_feats.shape[1]
+    if in_feats.dtype != plan.dtype or not in_feats.is_contiguous():
+        raise ValueError("input features do not match the layer plan (dtype or layout)")
+    if in_feats2 is not None:
+        if in_feats2.dtype != plan.dtype or not in_feats2.is_contiguous() or c1 + in_feats2.shape[1] != plan.cin:
+            raise ValueError("input features do not match the layer plan (second matrix)")
+    elif c1 != plan.cin:
+        raise ValueError("input features do not match the layer plan (channel count)")
     if residual is not None and (residual.dtype != plan.dtype or not residual.is_contiguous()):
         residual = residual.to(plan.dtype).contiguous()
-    out = torch.empty((num_out_feats, plan.cout), dtype=plan.dtype, device=plan.device)
-    rc = lib.tsb_conv_igemm_fwd(in_feats.data_ptr(), plan.args_head[0], plan.args_head[1], out_in_map.data_ptr(),
-                                None if reorder_loc is None else reorder_loc.data_ptr(), out.data_ptr(),
-                                in_feats.shape[0], num_out_feats, *plan.args_tail,
-                                None if residual is None else residual.data_ptr(), int(relu),
-                                _status_word(plan.device).data_ptr(), None, 0,
-                                torch._C._cuda_getCurrentRawStream(plan.device.index))
+    if out is None:
+        out = torch.empty((num_out_feats, plan.cout), dtype=plan.dtype, device=plan.device)
+    ws = None
+    if tile_mask is None and out_in_map is not None and plan.desc.kvol > 1:
+        if map_strides is None:
+            tile_mask = _tile_mask_of(out_in_map, num_out_feats)
+        if tile_mask is None:
+            ws = _workspace(lib.tsb_conv_igemm_workspace_bytes(plan.desc.kvol, plan.cin, plan.cout, plan.desc.dtype)
+                            + lib.tsb_map_tile_mask_bytes(num_out_feats), plan.device)
+    d = plan.desc
+    d.relu = int(relu)
+    d.in_feats, d.in_feats2 = in_feats.data_ptr(), (None if in_feats2 is None else in_feats2.data_ptr())
+    d.c1 = c1 if in_feats2 is not None else 0
+    d.out_in_map = None if out_in_map is None else out_in_map.data_ptr()
+    d.reorder_loc = None if reorder_loc is None else reorder_loc.data_ptr()
+    d.tile_mask = None if tile_mask is None else tile_mask.data_ptr()
+    d.out_feats = out.data_ptr()
+    d.residual = None if residual is None else residual.data_ptr()
+    d.n_out_dev = None if n_out_dev is None else n_out_dev.data_ptr()
+    d.workspace, d.workspace_bytes = (None, 0) if ws is None else (ws.data_ptr(), ws.numel())
+    d.n_in, d.n_out = in_feats.shape[0], num_out_feats
+    d.map_row_stride, d.map_col_stride = map_strides if map_strides is not None else (0, 0)
+    _apply_tuning(d)
+    rc = lib.tsb_conv_igemm_run(_lib.C.byref(d), torch._C._cuda_getCurrentRawStream(plan.device.index))
     if rc != 0:
         check(rc, "conv_forward_implicit_gemm_cuda")
     return out
@@ -622,23 +785,30 @@ def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch
                                                allow_tf32, allow_fp16, reorder_loc=loc[0], **epilogue)
     kvol = kernel.shape[0]
     split_len = (kvol + split - 1) // split
-    acc = None
+    if not _tensor_core_shape(in_feats, kernel, allow_tf32):
+        # exact fp32 (CUDA cores): one launch per split over a slice of the map, summed in fp32
+        acc = None
+        for s in range(split):
+            lo, hi = s * split_len, min(kvol, (s + 1) * split_len)
+            part = conv_forward_implicit_gemm_cuda(in_feats, kernel[lo:hi].contiguous(),
+                                                   out_in_map[:, lo:hi].contiguous(), num_out_feats,
+                                                   num_out_channels, allow_tf32, allow_fp16, reorder_loc=loc[s])
+            acc = part if acc is None else acc + part
+        from .nn.functional.conv.conv import _epilogue_torch
+        return _epilogue_torch(acc, epilogue) if epilogue else acc
+    # one launch per split over its own columns and row order; the partial sums stay in fp32 and the
+    # last launch applies the epilogue and rounds once
+    acc = torch.empty((num_out_feats, num_out_channels), dtype=torch.float32, device=in_feats.device)
+    masks = _tile_mask_of(out_in_map, out_in_map.shape[0])
+    out = None
     for s in range(split):
         lo, hi = s * split_len, min(kvol, (s + 1) * split_len)
-        part = conv_forward_implicit_gemm_cuda(in_feats.float(), kernel[lo:hi].float(),
-                                               out_in_map[:, lo:hi].contiguous(), num_out_feats, num_out_channels,
-                                               False, allow_fp16, reorder_loc=loc[s])
-        acc = part if acc is None else acc + part
-    bias, residual, relu = epilogue.get("bias"), epilogue.get("residual"), epilogue.get("relu", False)
-    if epilogue.get("scale") is not None:
-        acc = acc * epilogue["scale"]
-    if bias is not None:
-        acc = acc + bias
-    if residual is not None:
-        acc = acc + residual
-    if relu:
-        acc = torch.relu(acc)
-    return acc.to(in_feats.dtype)
+        last = s == split - 1
+        out = conv_forward_implicit_gemm_cuda(
+            in_feats, kernel, out_in_map, num_out_feats, num_out_channels, allow_tf32, allow_fp16,
+            reorder_loc=loc[s], tile_mask=masks, k_range=(lo, hi), acc_in=acc if s > 0 else None,
+            acc_out=None if last else acc, **(epilogue if last else {}))
+    return out
 
 
 def conv_forward_gather_scatter_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, nbmaps: torch.Tensor,

@@ -15,7 +15,17 @@ extern "C" {
 
 size_t tsb_conv_igemm_workspace_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {
   if (kvol < 1 || cin < 1 || cout < 1 || !valid_dtype(dtype)) return 0;
-  return igemm_umma_workspace_bytes(kvol, cin, cout, dtype);
+  return igemm_umma_workspace_bytes(kvol, cin, cout, dtype, 0);
+}
+
+size_t tsb_map_tile_mask_bytes(int64_t n_rows) { return n_rows < 0 ? 0 : tile_mask_bytes(n_rows); }
+
+int tsb_map_tile_mask(const int32_t* map, int64_t n_rows, int32_t kvol, int64_t row_stride, int64_t col_stride,
+                      const int32_t* n_rows_dev, uint32_t* out, tsb_stream_t stream) {
+  if (n_rows < 0 || kvol < 1 || kvol > 32 || row_stride < 1 || col_stride < 1) return TSB_ERR_BAD_ARG;
+  if (n_rows == 0) return TSB_OK;
+  if (!map || !out) return TSB_ERR_BAD_ARG;
+  return tile_masks(map, row_stride, col_stride, kvol, n_rows, n_rows_dev, out, as_stream(stream));
 }
 
 size_t tsb_conv_packed_weight_bytes(int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {
@@ -31,10 +41,11 @@ int tsb_conv_pack_weight(const void* weight, int32_t kvol, int32_t cin, int32_t 
 }
 
 int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* packed_weight,
-                       const int32_t* out_in_map, const int32_t* reorder_loc, void* out_feats, int64_t n_in,
-                       int64_t n_out, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype, int32_t math,
-                       const float* scale, const float* bias, const void* residual, int32_t relu,
-                       int32_t* dev_status, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+                       const int32_t* out_in_map, const int32_t* reorder_loc, const uint32_t* tile_mask,
+                       void* out_feats, int64_t n_in, int64_t n_out, int32_t kvol, int32_t cin, int32_t cout,
+                       int32_t dtype, int32_t math, const float* scale, const float* bias, const void* residual,
+                       int32_t relu, int32_t* dev_status, void* workspace, size_t workspace_bytes,
+                       tsb_stream_t stream) {
   if (n_in < 0 || n_out < 0 || kvol < 1 || cin < 1 || cout < 1) return TSB_ERR_BAD_ARG;
   if (!valid_dtype(dtype)) return TSB_ERR_UNSUPPORTED;
   if (n_out == 0) return TSB_OK;
@@ -42,8 +53,34 @@ int tsb_conv_igemm_fwd(const void* in_feats, const void* weight, const void* pac
   if (n_in > INT32_MAX || n_out > INT32_MAX) return TSB_ERR_LIMIT;
   IgemmArgs a{in_feats, weight, packed_weight, out_in_map, reorder_loc, out_feats, n_in, n_out, kvol, cin, cout,
               dtype, math, scale, bias, residual, relu, dev_status, workspace, workspace_bytes};
+  a.tile_mask = tile_mask;
   if (igemm_umma_supported(a)) return igemm_umma(a, as_stream(stream));
   return igemm_simt(a, as_stream(stream));
+}
+
+int tsb_conv_igemm_run(const tsb_igemm_desc* d, tsb_stream_t stream) {
+  if (!d || d->struct_bytes != sizeof(tsb_igemm_desc)) return TSB_ERR_BAD_ARG;
+  if (d->n_in < 0 || d->n_out < 0 || d->kvol < 1 || d->cin < 1 || d->cout < 1) return TSB_ERR_BAD_ARG;
+  if (!valid_dtype(d->dtype)) return TSB_ERR_UNSUPPORTED;
+  if (d->n_out == 0) return TSB_OK;
+  if (!d->weight || !d->in_feats || (!d->out_feats && !d->acc_out)) return TSB_ERR_BAD_ARG;
+  if (!d->out_in_map && d->kvol != 1) return TSB_ERR_BAD_ARG;
+  if (d->n_in > INT32_MAX || d->n_out > INT32_MAX || d->dst_rows > INT32_MAX) return TSB_ERR_LIMIT;
+  if (d->in_feats2 && (d->c1 <= 0 || d->c1 >= d->cin)) return TSB_ERR_BAD_ARG;
+  if ((d->map_row_stride == 0) != (d->map_col_stride == 0) || d->map_row_stride < 0 || d->map_col_stride < 0)
+    return TSB_ERR_BAD_ARG;
+  IgemmArgs a{d->in_feats, d->weight, d->packed_weight, d->out_in_map, d->reorder_loc, d->out_feats, d->n_in, d->n_out,
+              d->kvol, d->cin, d->cout, d->dtype, d->math, d->scale, d->bias, d->residual, d->relu, d->dev_status,
+              d->workspace, d->workspace_bytes};
+  a.dst_rows = d->dst_rows;
+  a.x2 = d->in_feats2; a.c1 = d->c1;
+  a.map_rs = d->map_row_stride; a.map_cs = d->map_col_stride;
+  a.tile_mask = d->tile_mask; a.n_out_dev = d->n_out_dev;
+  a.acc_in = d->acc_in; a.acc_out = d->acc_out;
+  a.k_lo = d->k_lo; a.k_hi = d->k_hi;
+  a.cfg_n_tile = d->cfg_n_tile; a.cfg_cpb = d->cfg_cpb; a.cfg_stages = d->cfg_stages; a.cfg_ctas = d->cfg_ctas;
+  if (!igemm_umma_supported(a)) return TSB_ERR_UNSUPPORTED;
+  return igemm_umma(a, as_stream(stream));
 }
 
 size_t tsb_conv_gs_workspace_bytes(int64_t n_pairs, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {

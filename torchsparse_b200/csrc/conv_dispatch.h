@@ -30,6 +30,17 @@ struct IgemmArgs {
   int out_fp32;     // 16-bit operands, fp32 output rows
   int atomic_out;   // fp32 output rows accumulated with atomic adds
   int64_t dst_rows; // rows of y when they are addressed through reorder_loc (0: n_out)
+  // ---- optional extensions of the tensor-core kernel (zero / null: not used)
+  const void* x2;            // second feature matrix [n_in, cin - c1]: input channels [c1, cin) come from it
+  int c1;                    // channels held by x when x2 is given
+  int64_t map_rs, map_cs;    // element strides of the map, entry (row, k) at map[row * map_rs + k * map_cs]
+                             // (0, 0: row-major [rows][kvol]); a null map with kvol = 1 means row m reads input row m
+  const unsigned* tile_mask; // [ceil(n_out / 128)] offsets present in each 128-row tile (null: derived in the workspace)
+  const int* n_out_dev;      // number of output rows in device memory (n_out is then its upper bound)
+  const float* acc_in;       // fp32 [dst_rows, cout] partial sums added to the accumulator before the epilogue
+  float* acc_out;            // fp32 [dst_rows, cout]: store the accumulator (+ acc_in) here instead of y, no epilogue
+  int k_lo, k_hi;            // kernel offsets [k_lo, k_hi) covered by this launch (0, 0: all)
+  int cfg_n_tile, cfg_cpb, cfg_stages, cfg_ctas;   // tuning overrides of the launch configuration (0: automatic)
 };
 
 struct GsArgs {
@@ -66,7 +77,11 @@ size_t gs_workspace_bytes(int64_t n_pairs, int kvol, int cin, int cout, int dtyp
 
 // tcgen05 kernels (conv_umma.cu)
 bool igemm_umma_supported(const IgemmArgs& a);
-size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype);
+size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype, int64_t n_out);
+size_t tile_mask_bytes(int64_t n_out);
+// offset mask of every 128-row tile of a map (entry (row, k) at map[row * rs + k * cs])
+int tile_masks(const int* map, long long rs, long long cs, int kvol, int64_t n_rows, const int* n_rows_dev,
+               unsigned* out, cudaStream_t s);
 int igemm_umma(const IgemmArgs& a, cudaStream_t s);
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype);
 int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* packed, cudaStream_t s);

@@ -3,40 +3,46 @@
 //   Y[m, :] = sum_k  X[map[m][k], :] . W[k]      (fp16 / bf16 operands, or fp32 operands multiplied
 //                                                  as TF32; fp32 accumulation in every case)
 //
-// One CTA owns 128 consecutive output rows (the rows of one map tile) and an N-tile of at most
-// 256 output channels.  The reduction runs over "K blocks": one kernel offset k x one 128-byte
-// chunk of Cin (64 16-bit or 32 32-bit channels).  K blocks whose offset has no neighbour in the
-// whole tile are skipped (the tile's 128 x Kvol map slice is staged in shared memory first and
-// OR-reduced into an offset mask), so the issued MMA work follows the sparsity of the map; with a
-// row-sorted map the skipping gets coarser-grained and the output rows are scattered through
-// reorder_loc.
+// A work item is a tile of 128 consecutive map rows times an N tile of at most 256 output channels.
+// Its reduction runs over "K blocks": one kernel offset k times a group of 128-byte channel chunks
+// (64 16-bit or 32 32-bit channels per chunk).  Which offsets a tile needs is given by a per-tile
+// bit mask (tile_mask, built once per kernel map): offsets without a neighbour in the whole tile are
+// never touched, so the issued work follows the sparsity of the map.  With a row-sorted map the rows
+// of a tile share their neighbour pattern, the masks get sparse, and the output rows are scattered
+// through reorder_loc.
 //
-// Operands of a K block (one pipeline stage, both 128B-swizzled K-major tiles):
-//   A  128 gathered feature-row slices of 128 bytes (zeros for a missing neighbour), copied by
-//      all eight gather warps with 16-byte cp.async, four per thread; each thread's arrival on the
-//      stage's "full" barrier is attached to its copies (cp.async.mbarrier.arrive.noinc), so no
-//      thread ever blocks on data.  The map entries are read into registers before the wait for
-//      the stage, so the copies go out back to back once it is released.
-//   B  one TMA tile copy of N_tile rows of the K-major packed weights, counted in bytes on the
-//      same barrier.
+// Operands of a K block (one pipeline stage; every chunk is a 128B-swizzled K-major tile):
+//   A  128 gathered feature-row slices of 128 bytes per chunk (zeros for a missing neighbour), copied
+//      by all eight gather warps with 16-byte cp.async, four rows per thread.  The four map entries
+//      of an offset are read from global memory into registers one offset ahead (the map may be
+//      row-major [rows][kvol] or column-major [kvol][rows]: the entry of (row, k) is at
+//      map[row * rs + k * cs]), so the copies go out back to back once the stage is released; each
+//      thread's arrival on the stage's "full" barrier is attached to its copies
+//      (cp.async.mbarrier.arrive.noinc), so no thread ever blocks on data.  The channels may come from
+//      two feature matrices (a channel concatenation that is never materialised).
+//   B  one TMA tile copy per chunk of N_tile rows of the K-major packed weights, counted in bytes on
+//      the same barrier.
 //
 // Roles (480 threads, persistent CTAs, one or two per SM):
 //   warps 0-7   gather (A operand)
-//   warps 8-11  epilogue: tcgen05.ld of their TMEM lane quarter, scale / bias / residual / ReLU,
-//               rounding and 16-byte stores
+//   warps 8-11  epilogue: tcgen05.ld of their TMEM lane quarter, optional fp32 partial sum in/out,
+//               scale / bias / residual / ReLU, rounding and 16-byte stores
 //   warp 12     weight loader: one elected thread issues the TMA copies
 //   warp 13     allocates TMEM; one elected thread issues tcgen05.mma (M=128, N=N_tile, 32 bytes of K
-//               per instruction, 4 per stage) and releases stages / publishes accumulators with
-//               tcgen05.commit.  Warps 12 and 13 run their loops converged and elect the issuing
-//               lane per instruction, so that descriptors and coordinates stay warp-uniform.
+//               per instruction) and releases stages / publishes accumulators with tcgen05.commit
 //   warp 14     scheduler: takes the CTA's next work item from a global counter (tiles differ in how
-//               many offsets they hold, so a fixed assignment would leave CTAs idle at the end), stages
-//               its map slice and offset mask for the other roles
+//               many offsets they hold, so a fixed assignment would leave CTAs idle at the end) and
+//               publishes (item, offset mask) through a small ring; the counter read for the item
+//               after next is already in flight
 //
 // Pair-list mode (the GatherScatter / FetchOnDemand dataflows, conv_pairs.cu): the map is one column of
 // input rows, every 128-row tile belongs to one kernel offset (tile_k[tile] picks its weight block),
 // and the fp32 products are either stored as rows of a buffer or added to the output rows with
 // 16-byte atomic adds.
+//
+// The number of output rows may live in device memory (n_out_dev): then the host-side n_out is only
+// an upper bound that sizes the grid, and a launch sequence can be replayed as a CUDA graph for
+// inputs of any size up to that bound.
 //
 // Every wait on an mbarrier is bounded: when it runs out the thread records an error code and the
 // CTA stops issuing work, gives its copies in flight time to land, frees its TMEM and returns.
@@ -65,7 +71,7 @@ constexpr int kTmaWarp = 12;
 constexpr int kMmaWarp = 13;
 constexpr int kSchedWarp = 14;
 constexpr int kThreads = 480;
-constexpr int kMaxRing = 4;            // tile ring: map slices + offset masks staged ahead of the other roles
+constexpr int kRing = 4;               // scheduler ring: (work item, offset mask) published ahead of the other roles
 constexpr int kMaxStages = 8;
 constexpr int kMaxKvolUmma = 32;
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -254,26 +260,36 @@ __host__ __device__ inline uint32_t make_idesc(int ab_format, int n) {
 }
 
 struct UmmaParams {
-  const void* x;        // [n_in, cin]
-  const int* map;       // [pad128(n_out), kvol]
+  const void* x;        // [n_in, c1]   channels [0, c1) of the input features
+  const void* x2;       // nullable, [n_in, cin - c1]: channels [c1, cin) (a concatenation that is not materialised)
+  const int* map;       // entry (row, k) at map[row * map_rs + k * map_cs]; null: row m reads input row m (kvol = 1)
+  const unsigned* tile_mask;   // nullable, [tiles]: bit k set when some row of the tile has a neighbour at offset k
   const int* reorder;   // nullable
   void* y;              // [n_out, cout]
   const float* scale;   // nullable, fp32 [cout]: y = acc * scale + bias (+ residual), then ReLU
   const float* bias;    // nullable
   const void* residual; // nullable, [n_out, cout]
+  const float* acc_in;  // nullable, fp32 [dst_rows, cout]: partial sums of earlier launches, added to the accumulator
+  float* acc_out;       // nullable, fp32 [dst_rows, cout]: the accumulator (+ acc_in) is stored here, no epilogue
+  const int* n_out_dev; // nullable: the number of output rows, read on the device (n_out is then its upper bound)
   int* error;           // device error word (0 = fine)
   int* sched;           // {next work item, CTAs finished}: both zero at launch, reset by the last CTA
   const int* tile_k;    // nullable ("pair list" mode): weight offset of each 128-row tile; the map is one column
+  long long map_rs, map_cs;
+  int c1;               // channels taken from x (= cin without x2)
   int dst_rows;         // rows of y (bound of the reorder scatter)
   int out_fp32;         // 16-bit operands, fp32 output rows (no residual)
   int atomic_out;       // fp32 output accumulated with atomic adds (rows may repeat between tiles)
-  long long* trace;     // debugging aid (trace builds only)
+#ifdef TSB_TRACE_BUILD
+  long long* trace;     // debugging aid: per-block timestamps of one CTA
   int trace_cta;
+#endif
   int n_in, n_out, kvol, cin, cout;
+  unsigned k_range;     // bits of the kernel offsets this launch covers
   int n_tile;           // UMMA N of a full tile (multiple of 16, <= 256)
   int acc_cols;         // TMEM columns of one accumulator buffer (power of two >= n_tile, >= 32)
-  int ring;             // tile ring depth (2..kMaxRing)
   int stages;
+  int cpb;              // 128-byte channel chunks per K block (pipeline stage)
   int relu;
   int ab_format;        // kFmtF16 / kFmtBF16 / kFmtTF32
 };
@@ -301,7 +317,7 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
 
-// TMA tile load of the weight block: box = 128 bytes of channels x n_tile rows of the packed
+// TMA tile load of a weight chunk: box = 128 bytes of channels x n_tile rows of the packed
 // weights, written 128B-swizzled; completion is counted in bytes on the mbarrier.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -314,43 +330,61 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// The next (work item, offset mask) of the scheduler ring, read by lane 0 and handed to the whole warp; the
+// slot is released at once (its two words now live in registers).  false: a bounded wait ran out.
+__device__ __forceinline__ bool ring_take(uint64_t* s_full, uint64_t* s_empty, const int* s_tile, const uint32_t* s_kmask,
+                                          int it, int lane, int& w, uint32_t& kmask) {
+  const int slot = it % kRing;
+  int ww = -1;
+  uint32_t mm = 0, ok = 1;
+  if (lane == 0) {
+    ok = mbar_wait(smem_u32(&s_full[slot]), (uint32_t)(it / kRing) & 1u) ? 1u : 0u;
+    if (ok) {
+      ww = s_tile[slot];
+      mm = s_kmask[slot];
+      mbar_arrive(smem_u32(&s_empty[slot]));
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  w = __shfl_sync(0xffffffffu, ww, 0);
+  kmask = __shfl_sync(0xffffffffu, mm, 0);
+  return ok != 0;
+}
+
 // Persistent kernel: each CTA takes (row tile, N tile) work items from a shared counter until none is left.
 // Three rings decouple the roles so that the copies of the next tile are in flight while the
 // current tile is multiplied and the previous one is written out:
-//   stage ring   (p.stages)  A+B operands of one K block         full[] / empty[]
-//   tile ring    (p.ring)    work item, map slice + offset mask  sched_full[] / sched_empty[]
-//   accumulator  (2)         TMEM column ranges                   acc_full[] / acc_empty[]
+//   stage ring      (p.stages)  A+B operands of one K block      full[] / empty[]
+//   scheduler ring  (kRing)     work item + offset mask           sched_full[] / sched_empty[]
+//   accumulator     (2)         TMEM column ranges                acc_full[] / acc_empty[]
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 2)
 igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map) {
   constexpr bool kTF32 = sizeof(T) == 4;
-  constexpr int kChunk = kRowBytes / (int)sizeof(T);     // channels per stage row
+  constexpr int kChunk = kRowBytes / (int)sizeof(T);     // channels per 128-byte chunk
   constexpr int kStepK = 32 / (int)sizeof(T);            // channels per MMA instruction (32 bytes of K)
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t s_full[kMaxStages];
   __shared__ uint64_t s_empty[kMaxStages];
-  __shared__ uint64_t s_sched_full[kMaxRing];
-  __shared__ uint64_t s_sched_empty[kMaxRing];
+  __shared__ uint64_t s_sched_full[kRing];
+  __shared__ uint64_t s_sched_empty[kRing];
   __shared__ uint64_t s_acc_full[2];
   __shared__ uint64_t s_acc_empty[2];
-  __shared__ uint32_t s_kmask[kMaxRing];
-  __shared__ int s_tile[kMaxRing];       // work item of the ring slot; -1 = no more work
+  __shared__ uint32_t s_kmask[kRing];
+  __shared__ int s_tile[kRing];          // work item of the ring slot; -1 = no more work
   __shared__ uint32_t s_tmem;
   __shared__ volatile int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef TSB_TRACE_BUILD
   if (tid == 0) TSB_TRACE_HOT(7, 0);     // CTA entry
-  const int tiles_n = (p.cout + p.n_tile - 1) / p.n_tile;
-  const int tiles_m = (p.n_out + kTileM - 1) / kTileM;
-  const int n_work = tiles_m * tiles_n;
-  const int b_bytes = p.n_tile * kRowBytes;
-  const int stage_bytes = kABytes + b_bytes;
+#endif
+  const int b_bytes = p.n_tile * kRowBytes;              // one weight chunk
+  const int stage_bytes = p.cpb * (kABytes + b_bytes);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t map_smem = smem_base + (uint32_t)p.stages * stage_bytes;
-  const int map_ints = kTileM * p.kvol;
-  int* s_map0 = reinterpret_cast<int*>(smem_raw + (map_smem - smem_u32(smem_raw)));
   const uint32_t acc_cols = p.acc_cols;            // TMEM columns of one accumulator (power of two)
   const int chunks = (p.cin + kChunk - 1) / kChunk;
+  const int groups = (chunks + p.cpb - 1) / p.cpb;       // K blocks per kernel offset
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -358,7 +392,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       mbar_init(smem_u32(&s_full[s]), kGatherThreads + 1);
       mbar_init(smem_u32(&s_empty[s]), 1);   // tcgen05.commit
     }
-    for (int b = 0; b < p.ring; ++b) {
+    for (int b = 0; b < kRing; ++b) {
       mbar_init(smem_u32(&s_sched_full[b]), 1);
       // readers of a ring slot: gather warps, weight loader, MMA warp, epilogue warps
       mbar_init(smem_u32(&s_sched_empty[b]), kGatherWarps + 2 + kEpilogueWarps);
@@ -376,77 +410,110 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
 
+  // rows of this launch: a device-side count (bounded by the host-side one that sized the grid) or the host's
+  int n_out = p.n_out;
+  if (p.n_out_dev) n_out = max(0, min(__ldg(p.n_out_dev), p.n_out));
+  const int tiles_n = (p.cout + p.n_tile - 1) / p.n_tile;
+  const int tiles_m = (n_out + kTileM - 1) / kTileM;
+  const int n_work = tiles_m * tiles_n;
+
   if (warp < kGatherWarps) {
     // ------------------------------------------------------------ gather warps (A operand)
-    // Thread t copies the 16-byte granule (t & 7) of rows (t >> 3) + 32 j, j = 0..3, of every K block:
+    // Thread t copies the 16-byte granule (t & 7) of rows (t >> 3) + 32 j, j = 0..3, of every chunk:
     // a warp instruction covers four whole 128-byte row slices.  The four map entries of an offset
-    // are read once, before the wait for the stage, and serve all channel chunks of that offset.
+    // are read one offset ahead and serve all channel chunks of that offset.
     constexpr int kGran = 16 / (int)sizeof(T);                     // channels per 16-byte granule
-    const T* x = reinterpret_cast<const T*>(p.x);
+    const T* x1 = reinterpret_cast<const T*>(p.x);
+    const T* x2 = reinterpret_cast<const T*>(p.x2);
+    const int c2w = p.cin - p.c1;                                   // channels of x2
     const int gran = tid & 7;
     const int rbase = tid >> 3;
     const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
-    const int mrow = kRowsPerPass * p.kvol;                        // map ints between a thread's rows
     const int cin_mma = (p.cin + kStepK - 1) / kStepK * kStepK;     // K extent the MMAs read
     uint32_t stage = 0, phase = 0;      // stage of the current block; phase = parity of its use count
     bool first_pass = true;              // the first use of a stage needs no release
     bool ok = true;
-    int i = 0;
+    int it = 0;                          // work items taken from the ring so far
+    uint32_t km = 0;                     // offsets of the current item not yet fetched
+    int row0 = 0;
 #ifdef TSB_TRACE_BUILD
     int blk = 0;
 #endif
-    for (;; ++i) {
-      const int buf = i % p.ring;
-      const uint32_t use_parity = (uint32_t)(i / p.ring) & 1u;
-      const int* mp = s_map0 + buf * map_ints + rbase * p.kvol;
-      if (!mbar_wait_warp(smem_u32(&s_sched_full[buf]), use_parity, lane)) {
-        atomicExch(p.error, kErrSchedWait);
-        s_abort = 1;
-        break;
-      }
-      if (s_abort || s_tile[buf] < 0) break;
-      const uint32_t kmask = s_kmask[buf];
-      for (int k = 0; k < p.kvol && ok; ++k) {
-        if (!((kmask >> k) & 1u)) continue;
-        int src[kCopies];
-#pragma unroll
-        for (int j = 0; j < kCopies; ++j) src[j] = mp[j * mrow + k];
-        for (int c = 0; c < chunks; ++c) {
-          const int col = c * kChunk + gran * kGran;
-          const bool col_ok = col < p.cin;                          // rows are 16-byte multiples: all-in or all-out
-          const T* xc = x + col;
-          if (tid == 0) TSB_TRACE_HOT(0, blk);
-          if (!first_pass && !mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, lane)) {
-            atomicExch(p.error, kErrEmptyWait);
-            s_abort = 1;
-            ok = false;
-            break;
-          }
-          if (tid == 0) TSB_TRACE_HOT(1, blk);
-          const uint32_t a_dst = smem_base + stage * (uint32_t)stage_bytes + dst_off;
-          // granules beyond the K extent of the chunk's last MMA (Cin rounded up to one instruction's K) are
-          // never read: their threads copy nothing and only arrive; granules between Cin and that bound are
-          // zero-filled (the weights there are zero, but stale shared memory could hold NaN patterns)
-          if (col < cin_mma) {
-#pragma unroll
-            for (int j = 0; j < kCopies; ++j) {
-              const bool live = col_ok && src[j] >= 0;
-              cp_async16(a_dst + (uint32_t)(j * kRowsPerPass) * kRowBytes,
-                         live ? (const void*)(xc + (int64_t)src[j] * p.cin) : (const void*)x, live ? 16u : 0u);
-            }
-          }
-          cp_async_arrive_noinc(full0 + stage * 8);
-          if (tid == 0) TSB_TRACE_HOT(2, blk);
-#ifdef TSB_TRACE_BUILD
-          ++blk;
-#endif
-          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+    // fetches the map entries of this thread's four rows for the next offset of the item stream
+    auto next_offset = [&](int (&src)[kCopies]) -> bool {
+      while (km == 0) {
+        int w;
+        uint32_t m;
+        if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, m)) {
+          atomicExch(p.error, kErrSchedWait);
+          s_abort = 1;
+          ok = false;
+          return false;
         }
+        ++it;
+        if (w < 0 || s_abort) return false;
+        row0 = (w / tiles_n) * kTileM;
+        km = m;
       }
+      const int k = __ffs(km) - 1;
+      km &= km - 1;
+#pragma unroll
+      for (int j = 0; j < kCopies; ++j) {
+        const int r = row0 + rbase + j * kRowsPerPass;
+        if (p.map) src[j] = __ldg(p.map + (long long)r * p.map_rs + (long long)k * p.map_cs);
+        else src[j] = r < n_out ? r : -1;
+      }
+      return true;
+    };
+    int src[kCopies], nxt[kCopies];
+    bool have = next_offset(src);
+    while (have && ok) {
+      const bool have_next = next_offset(nxt);       // in flight while this offset is copied
       if (!ok) break;
-      __syncwarp();   // every lane has read its rows of the slice
-      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
+      for (int g = 0; g < groups && ok; ++g) {
+#ifdef TSB_TRACE_BUILD
+        if (tid == 0) TSB_TRACE_HOT(0, blk);
+#endif
+        if (!first_pass && !mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, lane)) {
+          atomicExch(p.error, kErrEmptyWait);
+          s_abort = 1;
+          ok = false;
+          break;
+        }
+#ifdef TSB_TRACE_BUILD
+        if (tid == 0) TSB_TRACE_HOT(1, blk);
+#endif
+        const uint32_t a_stage = smem_base + stage * (uint32_t)stage_bytes + dst_off;
+        for (int cc = 0; cc < p.cpb; ++cc) {
+          const int c = g * p.cpb + cc;
+          const int col = c * kChunk + gran * kGran;
+          // granules beyond the K extent of the chunk's last MMA (Cin rounded up to one instruction's K) are
+          // never read: their threads copy nothing; granules between Cin and that bound are zero-filled (the
+          // weights there are zero, but stale shared memory could hold NaN patterns)
+          if (col >= cin_mma) break;
+          const bool col_ok = col < p.cin;                  // rows are 16-byte multiples: all-in or all-out
+          const bool from2 = col >= p.c1;
+          const T* xc = from2 ? x2 + (col - p.c1) : x1 + col;
+          const int rstride = from2 ? c2w : p.c1;
+          const uint32_t a_dst = a_stage + (uint32_t)cc * kABytes;
+#pragma unroll
+          for (int j = 0; j < kCopies; ++j) {
+            const bool live = col_ok && (unsigned)src[j] < (unsigned)p.n_in;
+            cp_async16(a_dst + (uint32_t)(j * kRowsPerPass) * kRowBytes,
+                       live ? (const void*)(xc + (int64_t)src[j] * rstride) : (const void*)x1, live ? 16u : 0u);
+          }
+        }
+        cp_async_arrive_noinc(full0 + stage * 8);
+#ifdef TSB_TRACE_BUILD
+        if (tid == 0) TSB_TRACE_HOT(2, blk);
+        ++blk;
+#endif
+        if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+      }
+#pragma unroll
+      for (int j = 0; j < kCopies; ++j) src[j] = nxt[j];
+      have = have_next;
     }
     cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
   } else if (warp < kGatherWarps + kEpilogueWarps) {
@@ -455,21 +522,16 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     const int quarter = warp & 3;
     T* y = reinterpret_cast<T*>(p.y);
     const T* res = reinterpret_cast<const T*>(p.residual);
-    int i = 0;
     int acc_count = 0;   // tiles that used an accumulator so far (tiles with an empty mask use none)
-    bool ok = true;
-    for (;; ++i) {
-      const int buf = i % p.ring;
-      if (!mbar_wait_warp(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u, lane)) {
+    for (int it = 0;; ++it) {
+      int w;
+      uint32_t kmask;
+      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, kmask)) {
         atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
-      const int w = s_tile[buf];
       if (s_abort || w < 0) break;
-      const uint32_t kmask = s_kmask[buf];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
       const int row0 = (w / tiles_n) * kTileM;
       const int n0 = (w % tiles_n) * p.n_tile;
       const int n_valid = min(p.n_tile, p.cout - n0);
@@ -485,7 +547,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       const int r = quarter * 32 + lane;
       const int64_t grow = (int64_t)row0 + r;
       int64_t dst_row = -1;
-      if (grow < p.n_out) {
+      if (grow < n_out) {
         dst_row = p.reorder ? (int64_t)__ldg(&p.reorder[grow]) : grow;
         if (dst_row >= p.dst_rows) dst_row = -1;
       }
@@ -518,6 +580,19 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * h + e]);
+          if (p.acc_in) {    // partial sums of the launches that covered the other kernel offsets
+            const float* ap = p.acc_in + dst_row * p.cout + nh;
+            const float4 a = __ldg(reinterpret_cast<const float4*>(ap));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(ap) + 1);
+            f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+            f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+          }
+          if (p.acc_out) {   // this launch is not the last of its group: keep the sum in fp32
+            float* ao = p.acc_out + dst_row * p.cout + nh;
+            reinterpret_cast<float4*>(ao)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(ao)[1] = make_float4(f[4], f[5], f[6], f[7]);
+            continue;
+          }
           if (p.scale) {
             const float4 a = __ldg(reinterpret_cast<const float4*>(p.scale + nh));
             const float4 b = __ldg(reinterpret_cast<const float4*>(p.scale + nh) + 1);
@@ -569,7 +644,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           }
         }
       }
-      if (warp == kGatherWarps && lane == 0) TSB_TRACE_HOT(7, i + 1);   // tile i written out (first epilogue warp)
+#ifdef TSB_TRACE_BUILD
+      if (warp == kGatherWarps && lane == 0) TSB_TRACE_HOT(7, it + 1);   // item written out (first epilogue warp)
+#endif
       // this warp is done with the accumulator buffer
       tc_fence_before();
       __syncwarp();
@@ -578,91 +655,53 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     }
   } else if (warp == kSchedWarp) {
     // ------------------------------------------------------------ scheduler warp
-    // stages the map slice of each tile (128 rows x kvol ints, contiguous, 16-byte loads) into the
-    // tile ring and publishes its offset mask, up to `ring` tiles ahead of the other roles
-    const int n4 = map_ints / 4;
-    int i = 0;
-    for (;; ++i) {
-      const int buf = i % p.ring;
-      if (i >= p.ring && !mbar_wait_warp(smem_u32(&s_sched_empty[buf]), ((uint32_t)(i / p.ring) + 1u) & 1u, lane)) {
-        atomicExch(p.error, kErrSchedWait);
-        s_abort = 1;
-        break;
-      }
-      int w = 0;
-      if (lane == 0) w = atomicAdd(p.sched, 1);
-      w = __shfl_sync(0xffffffffu, w, 0);
-      if (w >= n_work || s_abort) {
-        // tell the other roles that the CTA is done
-        if (lane == 0) {
-          s_tile[buf] = -1;
-          mbar_arrive(smem_u32(&s_sched_full[buf]));
+    // one lane: counter read for the next item in flight while the current item's mask is fetched and
+    // published; the other roles run up to kRing items behind
+    if (lane == 0) {
+      int w_next = atomicAdd(p.sched, 1);
+      for (int i = 0;; ++i) {
+        const int slot = i % kRing;
+        if (i >= kRing && !mbar_wait(smem_u32(&s_sched_empty[slot]), ((uint32_t)(i / kRing) + 1u) & 1u)) {
+          atomicExch(p.error, kErrSchedWait);
+          s_abort = 1;
+          break;
         }
-        break;
-      }
-      const int row0 = (w / tiles_n) * kTileM;
-      // all 16-byte copies of the slice go out before any of them is waited for: the slice costs one
-      // memory round trip, not one per few loads
-      const int4* src = reinterpret_cast<const int4*>(p.map + (int64_t)row0 * p.kvol);
-      int4* dst = reinterpret_cast<int4*>(s_map0 + buf * map_ints);
-      const uint32_t dst_s = map_smem + (uint32_t)(buf * map_ints) * 4u;
-      for (int e = lane; e < n4; e += 32) cp_async16(dst_s + (uint32_t)e * 16u, src + e, 16u);
-      cp_async_wait_all();
-      __syncwarp();
-      uint32_t mine = 0;
-      int kk = (lane * 4) % p.kvol;                 // kernel offset of the first int of this lane's int4
-      const int kstep = 128 % p.kvol;               // advance of that offset per loop trip (32 lanes x 4 ints)
-#pragma unroll 4
-      for (int e = lane; e < n4; e += 32) {
-        int4 v = dst[e];
-        int* c = reinterpret_cast<int*>(&v);
-        int k = kk;
-        bool changed = false;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (c[j] >= p.n_in) { c[j] = -1; changed = true; }   // defensive: an index beyond the features reads nothing
-          if (c[j] >= 0) mine |= 1u << k;
-          k = (k + 1 == p.kvol) ? 0 : k + 1;
+        const int w = w_next;
+        if (w >= n_work || s_abort) {
+          s_tile[slot] = -1;                  // tells the other roles that the CTA is done
+          mbar_arrive(smem_u32(&s_sched_full[slot]));
+          break;
         }
-        if (changed) dst[e] = v;
-        kk += kstep;
-        if (kk >= p.kvol) kk -= p.kvol;
-      }
-      for (int o = 16; o; o >>= 1) mine |= __shfl_xor_sync(0xffffffffu, mine, o);
-      __syncwarp();
-      if (lane == 0) {
-        s_kmask[buf] = mine;
-        s_tile[buf] = w;
-        mbar_arrive(smem_u32(&s_sched_full[buf]));
+        w_next = atomicAdd(p.sched, 1);
+        uint32_t mask = p.k_range;
+        if (p.tile_mask) mask &= __ldg(&p.tile_mask[w / tiles_n]);
+        s_kmask[slot] = mask;
+        s_tile[slot] = w;
+        mbar_arrive(smem_u32(&s_sched_full[slot]));
       }
     }
   } else if (warp == kTmaWarp) {
     // ------------------------------------------------------------ weight loader (B operand)
-    // the whole warp walks the blocks converged; one elected lane posts the byte count and issues the copy
-    const uint32_t bytes = (uint32_t)b_bytes;
+    // the whole warp walks the blocks converged; one elected lane posts the byte count and issues the copies
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
     uint32_t stage = 0, phase = 0;
     bool first_pass = true;
-    int i = 0;
     bool ok = true;
-    for (; ok; ++i) {
-      const int buf = i % p.ring;
-      if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
+    for (int it = 0; ok; ++it) {
+      int w;
+      uint32_t kmask;
+      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, kmask)) {
         if (lane == 0) atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
-      const int w = s_tile[buf];
       if (s_abort || w < 0) break;
-      const uint32_t kmask = s_kmask[buf];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
       const int n0 = (w % tiles_n) * p.n_tile;
-      for (int k = 0; k < p.kvol && ok; ++k) {
-        if (!((kmask >> k) & 1u)) continue;
+      for (uint32_t km = kmask; km && ok; km &= km - 1) {
         // pair-list mode: the tile's rows all belong to one kernel offset, named by tile_k
-        const int wrow = (p.tile_k ? __ldg(&p.tile_k[w / tiles_n]) : k) * p.cout + n0;
-        for (int c = 0; c < chunks; ++c) {
+        const int k = p.tile_k ? __ldg(&p.tile_k[w / tiles_n]) : (__ffs(km) - 1);
+        const int wrow = k * p.cout + n0;
+        for (int g = 0; g < groups; ++g) {
           if (!first_pass && !mbar_wait(empty0 + stage * 8, phase ^ 1u)) {
             if (lane == 0) atomicExch(p.error, kErrEmptyWait);
             s_abort = 1;
@@ -670,9 +709,12 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             break;
           }
           const uint32_t bar = full0 + stage * 8;
+          const int c_lo = g * p.cpb, c_hi = min(c_lo + p.cpb, chunks);
           if (elect_one()) {
-            mbar_arrive_expect_tx(bar, bytes);
-            tma_load_2d(smem_base + stage * (uint32_t)stage_bytes + kABytes, &w_map, bar, c * kChunk, wrow);
+            mbar_arrive_expect_tx(bar, (uint32_t)((c_hi - c_lo) * b_bytes));
+            const uint32_t b_dst = smem_base + stage * (uint32_t)stage_bytes + (uint32_t)p.cpb * kABytes;
+            for (int c = c_lo; c < c_hi; ++c)
+              tma_load_2d(b_dst + (uint32_t)((c - c_lo) * b_bytes), &w_map, bar, c * kChunk, wrow);
           }
           __syncwarp();
           if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
@@ -681,33 +723,32 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
-    // The instruction stream of this warp is on the critical path of the whole CTA: stage index,
-    // barrier phase and descriptors are carried incrementally (no division, no 64-bit arithmetic per
-    // block), and the warp stays converged so that they are warp-uniform values.
+    // The instruction stream of this warp is on the critical path of the whole CTA: the warp stays
+    // converged so that stage index, barrier phase and descriptors are warp-uniform values.
     const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
     const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, SWIZZLE_128B
-    const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);  // stage 0, A operand
+    const uint32_t lo_flag = 1u << 16;
     const uint32_t stage_units = (uint32_t)stage_bytes >> 4;
-    const uint32_t b_units = (uint32_t)kABytes >> 4;
+    const uint32_t a_units = (uint32_t)kABytes >> 4;
+    const uint32_t b_units = (uint32_t)b_bytes >> 4;
+    const uint32_t b_first = (uint32_t)p.cpb * a_units;                 // first weight chunk of a stage
+    const uint32_t base_units = smem_base >> 4;
     const int last_steps = ((p.cin - (chunks - 1) * kChunk) + kStepK - 1) / kStepK;
-    uint32_t stage = 0, phase = 0, a_lo = a_lo0;
-    int i = 0, acc_count = 0;
+    uint32_t stage = 0, phase = 0;
+    int acc_count = 0;
     bool ok = true;
 #ifdef TSB_TRACE_BUILD
     int blk = 0;
 #endif
-    for (; ok; ++i) {
-      const int buf = i % p.ring;
-      if (!mbar_wait(smem_u32(&s_sched_full[buf]), (uint32_t)(i / p.ring) & 1u)) {
+    for (int it = 0; ok; ++it) {
+      int w;
+      uint32_t kmask;
+      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, kmask)) {
         if (lane == 0) atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
-      const int w = s_tile[buf];
       if (s_abort || w < 0) break;
-      const uint32_t kmask = s_kmask[buf];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&s_sched_empty[buf]));
       const int n0 = (w % tiles_n) * p.n_tile;
       const int n_mma = (min(p.n_tile, p.cout - n0) + 15) & ~15;
       const uint32_t idesc = make_idesc(p.ab_format, n_mma);
@@ -723,8 +764,10 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       const uint32_t acc = tmem_base + (uint32_t)ab * acc_cols;
       uint32_t accumulate = 0;
       for (uint32_t km = kmask; km && ok; km &= km - 1) {       // one trip per offset present in the tile
-        for (int c = 0; c < chunks; ++c) {
+        for (int g = 0; g < groups; ++g) {
+#ifdef TSB_TRACE_BUILD
           if (lane == 0) TSB_TRACE_HOT(4, blk);
+#endif
           if (!mbar_wait(full0 + stage * 8, phase)) {
             if (lane == 0) atomicExch(p.error, kErrFullWait);
             s_abort = 1;
@@ -732,16 +775,25 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             break;
           }
           tc_fence_after();
+#ifdef TSB_TRACE_BUILD
           if (lane == 0) TSB_TRACE_HOT(5, blk);
-          const int steps = (c == chunks - 1) ? last_steps : 4;
+#endif
+          const int c_lo = g * p.cpb, c_hi = min(c_lo + p.cpb, chunks);
           if (elect_one()) {
-            // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
+            const uint32_t st_units = base_units + stage * stage_units;
+            for (int c = c_lo; c < c_hi; ++c) {
+              const uint32_t a_lo = ((st_units + (uint32_t)(c - c_lo) * a_units) & 0x3FFFu) | lo_flag;
+              const uint32_t b_lo = ((st_units + b_first + (uint32_t)(c - c_lo) * b_units) & 0x3FFFu) | lo_flag;
+              const int steps = (c == chunks - 1) ? last_steps : 4;
+              // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
 #pragma unroll
-            for (int st = 0; st < 4; ++st) {
-              if (st < steps) {
-                const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_lo + 2u * st);
-                const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (a_lo + b_units + 2u * st);
-                umma<kTF32>(acc, a_desc, b_desc, idesc, (st == 0) ? accumulate : 1u);
+              for (int st = 0; st < 4; ++st) {
+                if (st < steps) {
+                  const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_lo + 2u * st);
+                  const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (b_lo + 2u * st);
+                  umma<kTF32>(acc, a_desc, b_desc, idesc, accumulate);
+                  accumulate = 1;
+                }
               }
             }
             umma_commit(empty0 + stage * 8);
@@ -752,8 +804,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           if (lane == 0) TSB_TRACE_HOT(6, blk);
           ++blk;
 #endif
-          a_lo += stage_units;
-          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
+          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; }
         }
       }
       // also on the error path: ends the epilogue's bounded wait early
@@ -773,7 +824,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * acc_cols);
   }
+#ifdef TSB_TRACE_BUILD
   if (tid == 0) TSB_TRACE_HOT(3, 0);     // CTA exit
+#endif
   // the last CTA to finish puts the scheduling words back to zero for a later launch
   if (tid == 0) {
     __threadfence();
@@ -785,10 +838,47 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   }
 }
 
+// Offset mask of every 128-row tile of a map: bit k = some row of the tile has an entry >= 0 in column k.
+// One warp per tile; entry (row, k) at map[row * rs + k * cs]; rows >= n_rows (a device-side count
+// when n_rows_dev is given) count as empty.
+__global__ void tile_mask_kernel(const int* __restrict__ map, long long rs, long long cs, int kvol, int64_t n_rows,
+                                 const int* __restrict__ n_rows_dev, int64_t tiles, unsigned* __restrict__ out) {
+  if (n_rows_dev) n_rows = max((int64_t)0, min((int64_t)__ldg(n_rows_dev), n_rows));
+  const int lane = threadIdx.x & 31;
+  int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (; warp < tiles; warp += nwarps) {
+    unsigned m = 0;
+    const int64_t row0 = warp * kTileM;
+    if (cs == 1) {
+      // row-major: the tile is one contiguous run of 128 * kvol ints
+      const int total = kTileM * kvol;
+      const int* base = map + row0 * rs;
+      for (int e = lane; e < total; e += 32) {
+        const int r = e / kvol;
+        if (row0 + r < n_rows && __ldg(base + e) >= 0) m |= 1u << (e - r * kvol);
+      }
+    } else {
+      for (int k = 0; k < kvol; ++k) {
+        bool any = false;
+#pragma unroll
+        for (int j = 0; j < kTileM / 32; ++j) {
+          const int64_t r = row0 + lane + 32 * j;
+          any = any || (r < n_rows && __ldg(map + r * rs + (long long)k * cs) >= 0);
+        }
+        if (any) m |= 1u << k;
+      }
+    }
+    for (int o = 16; o; o >>= 1) m |= __shfl_xor_sync(0xffffffffu, m, o);
+    if (lane == 0) out[warp] = m;
+  }
+}
+
 // Scheduling words, one slot per stream: launches on one stream run one after another, so they can share
 // a slot (zero-initialised, and every launch zeroes it again when its last CTA leaves); launches on
 // different streams may overlap and get different slots.
 constexpr int kSchedSlots = 1024;
+constexpr int kMaxDevices = 64;
 __device__ int g_sched_slots[kSchedSlots * 2];
 
 // W [kvol, cin, cout] -> Wt [kvol, cout, cin]
@@ -826,44 +916,60 @@ EncodeFn tensor_map_encoder() {
   return fn;
 }
 
-size_t smem_bytes_for(int n_tile, int stages, int kvol, int ring) {
-  return 1024 + (size_t)stages * (kABytes + (size_t)n_tile * kRowBytes) + (size_t)ring * kTileM * kvol * sizeof(int);
+size_t smem_bytes_for(int n_tile, int stages, int cpb) {
+  return 1024 + (size_t)stages * cpb * (kABytes + (size_t)n_tile * kRowBytes);
 }
 
-int usable_stages(int s) { return s > kMaxStages ? kMaxStages : s; }
+struct LaunchConfig {
+  int n_tile, cpb, stages, ctas;
+};
+
+int acc_cols_for(int n_tile) {
+  int c = 32;
+  while (c < n_tile) c <<= 1;
+  return c;
+}
+
+// Stages that fit `budget` bytes of dynamic shared memory (0: not even two).
+int stages_that_fit(int n_tile, int cpb, size_t budget) {
+  int best = 0;
+  for (int s = 2; s <= kMaxStages; ++s)
+    if (smem_bytes_for(n_tile, s, cpb) <= budget) best = s;
+  return best;
+}
 
 // Two persistent CTAs per SM when two double-buffered accumulators fit TMEM (N tile <= 128 columns)
-// and three stages fit half the shared memory: two MMA issuers per SM hide the per-block latency
-// of the narrow layers.  Otherwise one CTA per SM with as many stages as fit.
-void pick_config(int n_tile, int kvol, int* stages, int* ring, int* ctas) {
-  int acc_cols = 32;
-  while (acc_cols < n_tile) acc_cols <<= 1;
-  if (acc_cols <= 128) {
-    const size_t half = 112 * 1024;
-    int best = 0;
-    for (int s = 2; s <= kMaxStages; ++s)
-      if (smem_bytes_for(n_tile, s, kvol, 2) <= half) best = s;
-    if (best >= 3) { *stages = usable_stages(best); *ring = 2; *ctas = 2; return; }
-  }
-  const size_t budget = 226 * 1024;
-  int best[2] = {0, 0};
-  for (int r = 2; r <= 3; ++r)
-    for (int s = 2; s <= kMaxStages; ++s)
-      if (smem_bytes_for(n_tile, s, kvol, r) <= budget) best[r - 2] = usable_stages(s);
-  *ctas = 1;
-  if (best[0] > best[1]) { *stages = best[0]; *ring = 2; }
-  else { *stages = best[1]; *ring = 3; }
+// and at least three stages fit half the shared memory: two MMA issuers per SM hide the per-block
+// latency of the narrow layers.  Otherwise one CTA per SM with as many stages as fit.  Non-zero
+// fields of `want` override the choice (tuning runs).
+bool pick_config(int cout, int chunks, const LaunchConfig& want, LaunchConfig* out) {
+  LaunchConfig c;
+  c.n_tile = want.n_tile > 0 ? ((want.n_tile + 15) & ~15) : ((cout + 15) & ~15);
+  if (c.n_tile > 256) c.n_tile = 256;
+  if (c.n_tile > ((cout + 15) & ~15)) c.n_tile = (cout + 15) & ~15;
+  c.cpb = want.cpb > 0 ? want.cpb : 1;
+  if (c.cpb > chunks) c.cpb = chunks;
+  const size_t half = 112 * 1024, whole = 226 * 1024;
+  const int s2 = acc_cols_for(c.n_tile) <= 128 ? stages_that_fit(c.n_tile, c.cpb, half) : 0;
+  const int s1 = stages_that_fit(c.n_tile, c.cpb, whole);
+  c.ctas = want.ctas > 0 ? want.ctas : (s2 >= 3 ? 2 : 1);
+  if (c.ctas == 2 && s2 < 2) c.ctas = 1;
+  c.stages = c.ctas == 2 ? s2 : s1;
+  if (want.stages > 0 && want.stages < c.stages) c.stages = want.stages;
+  *out = c;
+  return c.stages >= 2;
 }
 
 // scheduling words of `stream` on the current device (the array's address is looked up once per device,
-// a stream gets the next free slot the first time it launches a convolution)
-int* sched_slot_of(cudaStream_t stream) {
+// a stream gets the next free slot the first time it launches a convolution).  When every slot of a
+// device has been handed out the call fails rather than letting two streams share a counter.
+int* sched_slot_of(cudaStream_t stream, int dev) {
   static std::mutex mu;
-  static int* addr[64] = {nullptr};
+  static int* addr[kMaxDevices] = {nullptr};
   static std::map<std::pair<int, cudaStream_t>, int> slot_of;
-  static int next_slot[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  static int next_slot[kMaxDevices] = {0};
+  // the per-thread default stream is one handle value for a different stream in every host thread
+  if (stream == cudaStreamPerThread) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   if (!addr[dev]) {
     void* ptr = nullptr;
@@ -871,53 +977,84 @@ int* sched_slot_of(cudaStream_t stream) {
     addr[dev] = reinterpret_cast<int*>(ptr);
   }
   auto it = slot_of.find({dev, stream});
-  if (it == slot_of.end()) it = slot_of.emplace(std::make_pair(dev, stream), next_slot[dev]++ % kSchedSlots).first;
+  if (it == slot_of.end()) {
+    if (next_slot[dev] >= kSchedSlots) return nullptr;
+    it = slot_of.emplace(std::make_pair(dev, stream), next_slot[dev]++).first;
+  }
   return addr[dev] + 2 * it->second;
 }
 
-int num_sms() {
-  static int n = []() {
-    int dev = 0, v = kSmCount;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : kSmCount;
-  }();
-  return n;
+// per-device facts and one-time settings, looked up / applied on first use under a lock
+struct DeviceState {
+  int sms = 0;
+  bool attr_set[3] = {false, false, false};
+};
+std::mutex g_dev_mu;
+DeviceState g_dev[kMaxDevices];
+
+template <typename T>
+int prepare_device(int dev, int fmt, int* sms) {
+  std::lock_guard<std::mutex> lock(g_dev_mu);
+  DeviceState& d = g_dev[dev];
+  if (!d.sms) {
+    int v = kSmCount;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = kSmCount;
+    d.sms = v;
+  }
+  if (!d.attr_set[fmt]) {
+    TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    d.attr_set[fmt] = true;
+  }
+  *sms = d.sms;
+  return TSB_OK;
 }
 
-int pick_n_tile(int cout) {
-  int n = (cout + 15) & ~15;
-  return n > 256 ? 256 : n;
-}
+int chunks_of(int cin, int dtype) { return (int)cdiv((int64_t)cin * (int64_t)dtype_size(dtype), kRowBytes); }
 
 }  // namespace
 
 bool igemm_umma_supported(const IgemmArgs& a) {
   if (!tensor_map_encoder()) return false;
-  if ((a.kvol * kTileM) % 4 || ((uintptr_t)a.map & 15)) return false;
   if (a.dtype == TSB_F32) {
     if (a.math != TSB_MATH_TF32) return false;       // exact fp32 stays on the CUDA cores
   } else if (a.dtype != TSB_F16 && a.dtype != TSB_BF16) {
     return false;
   }
-  // feature rows must be 16-byte multiples (tensor-map stride); outputs are written in 8-channel groups
-  if ((a.cin * (int)dtype_size(a.dtype)) % 16 || a.cout % 8) return false;
+  // feature rows must be 16-byte multiples; outputs are written in 8-channel groups
+  const int esz = (int)dtype_size(a.dtype);
+  if ((a.cin * esz) % 16 || a.cout % 8) return false;
+  if (a.x2 && (a.c1 <= 0 || a.c1 >= a.cin || (a.c1 * esz) % 16)) return false;
   if (a.n_in >= (int64_t)INT32_MAX || a.n_out >= (int64_t)INT32_MAX) return false;
   if (a.kvol > kMaxKvolUmma) return false;            // one bit per map column in a tile's offset mask
   if (a.tile_k && a.kvol != 1) return false;          // pair-list mode: one map column, weights chosen per tile
+  if (!a.map && a.kvol != 1) return false;            // identity rows: a 1x1x1 kernel
   if (a.out_fp32 && a.residual) return false;
-  if (((uintptr_t)a.x | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual | (uintptr_t)a.packed_w) & 15)
+  if ((a.acc_in || a.acc_out) && (a.atomic_out || a.out_fp32)) return false;
+  if (((uintptr_t)a.x | (uintptr_t)a.x2 | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual |
+       (uintptr_t)a.packed_w | (uintptr_t)a.acc_in | (uintptr_t)a.acc_out) & 15)
     return false;
-  int st = 0, rg = 0, ct = 0;
-  pick_config(pick_n_tile(a.cout), a.kvol, &st, &rg, &ct);
-  return st >= 2;
+  LaunchConfig want{a.cfg_n_tile, a.cfg_cpb, a.cfg_stages, a.cfg_ctas}, got;
+  return pick_config(a.cout, chunks_of(a.cin, a.dtype), want, &got);
 }
 
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype) {
   return align_up((size_t)kvol * cin * cout * dtype_size(dtype), 256);
 }
 
-size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype) {
-  return packed_weight_bytes(kvol, cin, cout, dtype) + 256;   // packed weights + error word
+size_t tile_mask_bytes(int64_t n_out) { return align_up((size_t)cdiv(n_out, kTileM) * sizeof(unsigned) + 4, 256); }
+
+size_t igemm_umma_workspace_bytes(int kvol, int cin, int cout, int dtype, int64_t n_out) {
+  // packed weights + error word + tile masks (each only used when the caller does not supply it)
+  return packed_weight_bytes(kvol, cin, cout, dtype) + 256 + tile_mask_bytes(n_out);
+}
+
+int tile_masks(const int* map, long long rs, long long cs, int kvol, int64_t n_rows, const int* n_rows_dev,
+               unsigned* out, cudaStream_t s) {
+  const int64_t tiles = cdiv(n_rows, kTileM);
+  if (tiles == 0) return TSB_OK;
+  tile_mask_kernel<<<grid_for(tiles * 32, 256, 8), 256, 0, s>>>(map, rs, cs, kvol, n_rows, n_rows_dev, tiles, out);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
 }
 
 template <typename T>
@@ -940,42 +1077,66 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   const size_t w_bytes = packed_weight_bytes(kvol_w, a.cin, a.cout, a.dtype);
   const T* wt = reinterpret_cast<const T*>(a.packed_w);
   int* err = a.dev_status;
-  if (!wt || !err) {
-    if (!a.workspace || a.workspace_bytes < w_bytes + 256) return TSB_ERR_WORKSPACE;
-  }
+  const unsigned* tmask = a.tile_mask;
+  const bool need_mask = !tmask && a.map && !a.tile_k && a.kvol > 1;
+  // workspace layout: [packed weights][error word, 256 bytes][tile masks]; only the parts the caller did
+  // not supply are used, and the workspace has to reach the end of the last one used
+  size_t need = 0;
+  if (!wt) need = w_bytes;
+  if (!err) need = w_bytes + 256;
+  if (need_mask) need = w_bytes + 256 + tile_mask_bytes(a.n_out);
+  char* ws = reinterpret_cast<char*>(a.workspace);
+  if (need && (!ws || a.workspace_bytes < need)) return TSB_ERR_WORKSPACE;
   if (!err) {
-    err = reinterpret_cast<int*>(reinterpret_cast<char*>(a.workspace) + w_bytes);
+    err = reinterpret_cast<int*>(ws + w_bytes);
     TSB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), s));
   }
   if (!wt) {
-    int rc = pack_launch<T>(a.w, kvol_w, a.cin, a.cout, a.workspace, s);
+    int rc = pack_launch<T>(a.w, kvol_w, a.cin, a.cout, ws, s);
     if (rc != TSB_OK) return rc;
-    wt = reinterpret_cast<const T*>(a.workspace);
+    wt = reinterpret_cast<const T*>(ws);
   }
+  const long long rs = a.map_rs ? a.map_rs : a.kvol, cs = a.map_cs ? a.map_cs : 1;
+  if (need_mask) {
+    unsigned* m = reinterpret_cast<unsigned*>(ws + w_bytes + 256);
+    int rc = tile_masks(a.map, rs, cs, a.kvol, a.n_out, a.n_out_dev, m, s);
+    if (rc != TSB_OK) return rc;
+    tmask = m;
+  }
+  int dev = 0;
+  TSB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TSB_ERR_LIMIT;
   UmmaParams p;
-  p.x = a.x; p.map = a.map; p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
-  p.residual = a.residual; p.error = err;
+  p.x = a.x; p.x2 = a.x2; p.c1 = a.x2 ? a.c1 : a.cin;
+  p.map = a.map; p.map_rs = rs; p.map_cs = cs; p.tile_mask = tmask;
+  p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
+  p.residual = a.residual; p.acc_in = a.acc_in; p.acc_out = a.acc_out; p.n_out_dev = a.n_out_dev; p.error = err;
   p.tile_k = a.tile_k; p.out_fp32 = a.out_fp32; p.atomic_out = a.atomic_out;
   p.dst_rows = (int)(a.dst_rows > 0 ? a.dst_rows : a.n_out);
-  p.sched = sched_slot_of(s);
-  if (!p.sched) return TSB_ERR_CUDA;
+  p.sched = sched_slot_of(s, dev);
+  if (!p.sched) return TSB_ERR_LIMIT;   // more distinct streams than scheduling slots, or the per-thread default stream
+#ifdef TSB_TRACE_BUILD
   p.trace = nullptr; p.trace_cta = 0;
   if (const char* tr = getenv("TSB_UMMA_TRACE")) {   // debugging aid: address of a 256x8 int64 device buffer
     p.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
     if (const char* tc = getenv("TSB_UMMA_TRACE_CTA")) p.trace_cta = atoi(tc);
   }
+#endif
   p.n_in = (int)a.n_in; p.n_out = (int)a.n_out; p.kvol = a.kvol; p.cin = a.cin; p.cout = a.cout;
-  p.n_tile = pick_n_tile(a.cout);
-  int ctas = 1;
-  pick_config(p.n_tile, a.kvol, &p.stages, &p.ring, &ctas);
+  const int k_lo = a.k_hi > a.k_lo ? a.k_lo : 0, k_hi = a.k_hi > a.k_lo ? a.k_hi : a.kvol;
+  if (k_lo < 0 || k_hi > a.kvol) return TSB_ERR_BAD_ARG;
+  p.k_range = (k_hi >= 32 ? 0xffffffffu : ((1u << k_hi) - 1u)) & ~((1u << k_lo) - 1u);
+  LaunchConfig want{a.cfg_n_tile, a.cfg_cpb, a.cfg_stages, a.cfg_ctas}, cfg;
+  if (!pick_config(a.cout, chunks_of(a.cin, a.dtype), want, &cfg)) return TSB_ERR_UNSUPPORTED;
+  p.n_tile = cfg.n_tile; p.cpb = cfg.cpb; p.stages = cfg.stages;
+  p.acc_cols = acc_cols_for(cfg.n_tile);
   p.relu = a.relu;
   p.ab_format = (a.dtype == TSB_BF16) ? kFmtBF16 : (a.dtype == TSB_F32) ? kFmtTF32 : kFmtF16;
-  const size_t smem = smem_bytes_for(p.n_tile, p.stages, a.kvol, p.ring);
-  static bool attr_set[3] = {false, false, false};
-  const int ti = p.ab_format;
-  if (!attr_set[ti]) {
-    TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    attr_set[ti] = true;
+  const size_t smem = smem_bytes_for(cfg.n_tile, cfg.stages, cfg.cpb);
+  int sms = kSmCount;
+  {
+    int rc = prepare_device<T>(dev, p.ab_format, &sms);
+    if (rc != TSB_OK) return rc;
   }
   CUtensorMap w_map;
   {
@@ -989,16 +1150,14 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     // packed weights as a 2-D tensor [kvol * cout rows, cin columns]; box = 128 bytes of columns x n_tile rows
     cuuint64_t gdim[2] = {(cuuint64_t)a.cin, (cuuint64_t)kvol_w * (cuuint64_t)a.cout};
     cuuint64_t gstride[1] = {(cuuint64_t)a.cin * sizeof(T)};
-    cuuint32_t box[2] = {chunk, (cuuint32_t)p.n_tile};
+    cuuint32_t box[2] = {chunk, (cuuint32_t)cfg.n_tile};
     CUresult r = encode(&w_map, dt, 2, const_cast<T*>(wt), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
   }
-  p.acc_cols = 32;
-  while (p.acc_cols < p.n_tile) p.acc_cols <<= 1;
-  const int64_t n_work = cdiv(a.n_out, kTileM) * cdiv(a.cout, p.n_tile);
-  const int64_t slots = (int64_t)ctas * num_sms();
+  const int64_t n_work = cdiv(a.n_out, kTileM) * cdiv(a.cout, cfg.n_tile);
+  const int64_t slots = (int64_t)cfg.ctas * sms;
   const int grid = (int)(n_work < slots ? n_work : slots);
   igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p, w_map);
   TSB_LAUNCH_CHECK();

@@ -397,6 +397,50 @@ __global__ void reorder_map_kernel(const int* __restrict__ map, int64_t rows, in
   }
 }
 
+// ------------------------------------------------------------------ conv-ready sorted map
+// Sort key of a map row: (neighbour mask << 1) | 1 for a valid row, 0 for a padding row, so that padding
+// rows sort last (descending) even behind valid rows without any neighbour.  iota[i] = i.
+__global__ void row_sort_key_kernel(const int* __restrict__ map, int64_t rows, int kvol, int64_t valid_n,
+                                    const int* __restrict__ valid_n_dev, unsigned* __restrict__ keys,
+                                    int* __restrict__ iota) {
+  if (valid_n_dev) valid_n = max((int64_t)0, min((int64_t)__ldg(valid_n_dev), valid_n));
+  for (int64_t row = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; row < rows; row += (int64_t)gridDim.x * blockDim.x) {
+    unsigned key = 0;
+    if (row < valid_n) {
+      const int* p = map + row * kvol;
+      unsigned m = 0;
+      for (int i = 0; i < kvol; ++i) m |= (unsigned)(__ldg(&p[i]) >= 0) << i;
+      key = (m << 1) | 1u;
+    }
+    keys[row] = key;
+    iota[row] = (int)row;
+  }
+}
+
+// One block per 128-row tile of the sorted order: row r of the tile is map row loc[tile * 128 + r]; its kvol
+// entries are written column-major (map_cm[k][tile * 128 + r], coalesced over r) and the tile's offset
+// mask is the OR over its rows.  Padding positions (sorted key 0 at or beyond the valid count) get -1.
+__global__ void __launch_bounds__(128)
+reorder_cm_kernel(const int* __restrict__ map, const int* __restrict__ loc, int64_t rows, int kvol, int64_t valid_n,
+                  const int* __restrict__ valid_n_dev, int* __restrict__ map_cm, unsigned* __restrict__ tile_mask) {
+  if (valid_n_dev) valid_n = max((int64_t)0, min((int64_t)__ldg(valid_n_dev), valid_n));
+  __shared__ unsigned s_mask[4];
+  const int64_t pos = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  const bool live = pos < valid_n;
+  const int src = live ? __ldg(&loc[pos]) : -1;
+  const int* p = map + (int64_t)(src < 0 ? 0 : src) * kvol;
+  unsigned mine = 0;
+  for (int k = 0; k < kvol; ++k) {
+    const int v = (live && src >= 0) ? __ldg(&p[k]) : -1;
+    map_cm[(int64_t)k * rows + pos] = v;
+    const unsigned bal = __ballot_sync(0xffffffffu, v >= 0);
+    if (bal) mine |= 1u << k;
+  }
+  if ((threadIdx.x & 31) == 0) s_mask[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) tile_mask[blockIdx.x] = s_mask[0] | s_mask[1] | s_mask[2] | s_mask[3];
+}
+
 // ------------------------------------------------------------------ pair lists
 constexpr int kMaxKvolSmem = 512;
 
@@ -928,6 +972,56 @@ int tsb_map_sorted_artefacts(const int32_t* out_in_map, int64_t rows, int32_t kv
   rc = tsb_map_reorder(out_in_map, rows, kvol, reorder_loc, 1, reordered_map, stream);
   if (rc != TSB_OK) return rc;
   return tsb_bitmask_reduce(sorted_mask, rows, 1, tile, reduced_mask, stream);
+}
+
+namespace {
+struct SortCmWs { size_t key_off, key2_off, iota_off, cub_off, total, cub_bytes; };
+SortCmWs sort_cm_layout(int64_t rows) {
+  SortCmWs w;
+  size_t cb = 0;
+  cub::DeviceRadixSort::SortPairsDescending(nullptr, cb, (const unsigned*)nullptr, (unsigned*)nullptr, (const int*)nullptr,
+                                            (int*)nullptr, rows, 0, 32);
+  w.cub_bytes = cb;
+  size_t off = 0;
+  w.key_off = off; off = align_up(off + (size_t)rows * 4, 256);
+  w.key2_off = off; off = align_up(off + (size_t)rows * 4, 256);
+  w.iota_off = off; off = align_up(off + (size_t)rows * 4, 256);
+  w.cub_off = off; off = align_up(off + cb, 256);
+  w.total = off;
+  return w;
+}
+}  // namespace
+
+size_t tsb_map_sorted_cm_workspace_bytes(int64_t rows) {
+  if (rows <= 0) return 256;
+  return sort_cm_layout(rows).total;
+}
+
+int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n,
+                      const int32_t* valid_n_dev, int32_t* reorder_loc, int32_t* map_cm, uint32_t* tile_mask,
+                      void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (rows < 0 || rows % 128 || kvol < 1 || kvol > 31 || valid_n < 0 || valid_n > rows) return TSB_ERR_BAD_ARG;
+  if (rows == 0) return TSB_OK;
+  if (rows > INT32_MAX) return TSB_ERR_LIMIT;
+  if (!out_in_map || !reorder_loc || !map_cm || !tile_mask) return TSB_ERR_BAD_ARG;
+  SortCmWs w = sort_cm_layout(rows);
+  if (!workspace || workspace_bytes < w.total) return TSB_ERR_WORKSPACE;
+  cudaStream_t s = as_stream(stream);
+  char* base = reinterpret_cast<char*>(workspace);
+  unsigned* keys = reinterpret_cast<unsigned*>(base + w.key_off);
+  unsigned* keys2 = reinterpret_cast<unsigned*>(base + w.key2_off);
+  int* iota = reinterpret_cast<int*>(base + w.iota_off);
+  row_sort_key_kernel<<<grid_for(rows, kBlock, 8), kBlock, 0, s>>>(out_in_map, rows, kvol, valid_n, valid_n_dev, keys, iota);
+  TSB_LAUNCH_CHECK();
+  size_t cb = w.cub_bytes;
+  // stable: rows with the same neighbour pattern keep their original order (neighbouring rows share inputs)
+  TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairsDescending(base + w.cub_off, cb, keys, keys2, iota, reorder_loc, rows, 0,
+                                                         kvol + 1, s));
+  count_launch();
+  reorder_cm_kernel<<<(unsigned)(rows / 128), 128, 0, s>>>(out_in_map, reorder_loc, rows, kvol, valid_n, valid_n_dev,
+                                                          map_cm, tile_mask);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
 }
 
 int tsb_scan_quantified(int32_t kvol, const int32_t* nbsizes, int32_t* nbaddrs, int32_t* qnbaddrs,

@@ -26,6 +26,7 @@ from ..tensor import SparseTensor
 from ..utils.utils import make_ntuple
 from . import functional as F
 from .functional.conv import conv as _conv_impl
+from .functional.conv.kmap import transpose_kernel_map
 from .modules.activation import ReLU
 from .modules.conv import Conv3d
 
@@ -52,7 +53,13 @@ def _fold_bn(conv: Conv3d, bn: Optional[nn.BatchNorm1d]):
 
 class FusedConv(nn.Module):
     """conv (+ folded BatchNorm) (+ ReLU); ``forward(x, residual=None)`` adds a residual feature
-    matrix before the ReLU."""
+    matrix before the ReLU.  Every kernel shape, the 1x1x1 kernels included, runs on the library's
+    implicit-GEMM kernel; an input that is a pending concatenation (CatSparseTensor) is read from its
+    two matrices."""
+
+    # set by InferenceEngine: run on row-sorted, column-major copies of the kernel maps (built once per
+    # map, shared by all layers that use it)
+    sorted_maps = False
 
     def __init__(self, conv: Conv3d, bn: Optional[nn.BatchNorm1d] = None, relu: bool = False) -> None:
         super().__init__()
@@ -65,11 +72,6 @@ class FusedConv(nn.Module):
         self.kernel = nn.Parameter(conv.kernel.detach(), requires_grad=False)
         scale, shift = _fold_bn(conv, bn)
         self.pointwise = self.kernel.dim() == 2
-        if self.pointwise:
-            # 1x1x1: a dense matmul; the scale goes into the weights (fp32 product, then one rounding)
-            self.kernel = nn.Parameter((self.kernel.float() * scale[None, :]).to(self.kernel.dtype),
-                                       requires_grad=False)
-            self.register_buffer("shift_lp", shift.to(self.kernel.dtype))
         self.register_buffer("scale", scale)
         self.register_buffer("shift", shift)
         self._plan = None      # per-layer constant launch arguments, made on first use
@@ -83,80 +85,89 @@ class FusedConv(nn.Module):
         self._plan = None
         return self
 
-    # set by InferenceEngine: layers whose input (output, for transposed convs) tensor stride is at most
-    # this value run on row-sorted kernel maps (fewer issued K blocks where the map is very sparse)
-    sort_max_stride = 0
+    def invalidate(self) -> None:
+        """Forget the cached launch plan and packed weights (call after changing the weights through
+        ``.data`` or a raw pointer, which the version counter does not see)."""
+        self._plan = None
+        for name in ("_tsb_packed", "_tsb_padded"):
+            if hasattr(self.kernel, name):
+                delattr(self.kernel, name)
 
-    def _layer_config(self, x: SparseTensor):
-        if self._config is not None or self.sort_max_stride <= 0:
-            return self._config
-        # only submanifold convolutions: their map is shared by every layer of the resolution level, so
-        # one sort serves many launches; a strided or transposed map is used once and not worth sorting
-        if self.transposed or any(s != 1 for s in self.stride) or max(x.stride) > self.sort_max_stride:
-            return None
-        cfg = _conv_impl.resolve_config(None).copy()
-        cfg["ifsort"] = True
-        cfg["split_mask_num"] = 1
-        return cfg
+    def _kernel3(self) -> torch.Tensor:
+        return self.kernel if self.kernel.dim() == 3 else self.kernel.view(1, *self.kernel.shape)
 
     def forward(self, x: SparseTensor, residual: Optional[torch.Tensor] = None) -> SparseTensor:
-        if self.pointwise:
-            out = torch.addmm(self.shift_lp, x.feats, self.kernel)
-            if residual is not None:
-                out = out + residual
-            if self.relu:
-                out = torch.relu_(out)
-            return SparseTensor._from_parts(out, x.coords, x.stride, x.spatial_range, x._caches)
-        layer_config = self._layer_config(x)
-        y = self._forward_cached_map(x, residual, layer_config)
+        y = self._forward_planned(x, residual)
         if y is not None:
             return y
+        epilogue = {"scale": self.scale, "bias": self.shift, "residual": residual, "relu": self.relu}
+        if self.pointwise:
+            feats = x.feats
+            out = backend.conv_forward_implicit_gemm_cuda(feats, self._kernel3().to(feats.dtype), None, feats.shape[0],
+                                                          self.out_channels, backends.allow_tf32, True, **epilogue) \
+                if backend._tensor_core_shape(feats, self._kernel3(), backends.allow_tf32) else \
+                _conv_impl._epilogue_torch(feats.matmul(self.kernel.to(feats.dtype)), epilogue)
+            return SparseTensor._from_parts(out, x.coords, x.stride, x.spatial_range, x._caches)
         return F.conv3d(x, self.kernel, self.kernel_size, None, self.stride, self.padding, self.dilation,
-                        layer_config, self.transposed, False, False,
-                        epilogue={"scale": self.scale, "bias": self.shift, "residual": residual, "relu": self.relu})
+                        self._config, self.transposed, False, False, epilogue=epilogue)
 
-    def _forward_cached_map(self, x: SparseTensor, residual, layer_config) -> Optional[SparseTensor]:
-        """Short path for the common case of a network's inner layers: implicit GEMM on a
-        kernel map that is already in the tensor's cache (built by an earlier layer of the level or by
-        the engine's prebuild).  Same launch as F.conv3d makes, without its per-call bookkeeping;
-        returns None when the case does not apply."""
-        config = _conv_impl.resolve_config(layer_config)
-        if config["dataflow"] != F.Dataflow.ImplicitGEMM:
+    def _forward_planned(self, x: SparseTensor, residual) -> Optional[SparseTensor]:
+        """The common case: implicit GEMM on the tensor cores through the layer's launch plan.  The kernel
+        map comes from the tensor's cache (built by an earlier layer of the level, by the engine's
+        prebuild, or here), optionally in its row-sorted column-major form.  Returns None when the case
+        does not apply (another dataflow, a shape the tensor-core kernel does not take)."""
+        config = _conv_impl.resolve_config(self._config)
+        if config["dataflow"] != F.Dataflow.ImplicitGEMM or config["ifsort"]:
             return None
-        ifsort = bool(config["ifsort"])
-        if ifsort and config["split_mask_num"] != 1:
+        parts = getattr(x, "parts", None)
+        feats, feats2 = (parts[0], parts[1]) if (parts is not None and len(parts) == 2) else (x.feats, None)
+        kernel = self._kernel3()
+        if feats.dtype != kernel.dtype or not feats.is_cuda or not feats.is_contiguous():
             return None
-        feats = x.feats
-        if feats.dtype != self.kernel.dtype or not feats.is_cuda:
+        if (feats.shape[1] * feats.element_size()) % 16 != 0:
+            return None     # the 4-channel input layer is padded by the general entry point
+        if feats2 is not None and (not feats2.is_contiguous() or feats2.dtype != kernel.dtype):
             return None
+        if feats.dtype == torch.float32 and not backends.allow_tf32:
+            return None
+        plan = self._plan
+        if plan is None or not plan.valid_for(kernel, backends.allow_tf32):
+            try:
+                plan = self._plan = backend.IgemmLayerPlan(kernel, self.scale, self.shift, backends.allow_tf32)
+            except ValueError:
+                return None
         caches = x._caches
+        if self.pointwise:
+            out = backend.igemm_plan_launch(plan, feats, None, feats.shape[0], residual, self.relu, in_feats2=feats2)
+            return SparseTensor._from_parts(out, x.coords, x.stride, x.spatial_range, caches)
         if self.transposed:
             out_stride = tuple(a // b for a, b in zip(x.stride, self.stride))
             kmap = caches.kmaps.get((out_stride, self.kernel_size, self.stride, self.dilation))
             target = caches.cmaps.get(out_stride)
-            if kmap is None or target is None or kmap.get("out_in_map_t") is None:
+            if kmap is None or target is None:
                 return None
-            if ifsort and (kmap.get("reorder_out_in_map_t") is None or kmap.get("_split_t") != 1):
-                return None
-            out_in_map, n_out = kmap["reorder_out_in_map_t" if ifsort else "out_in_map_t"], kmap["sizes"][0]
-            reorder_loc = kmap["reorder_loc_t"] if ifsort else None
+            if kmap.get("out_in_map_t") is None:
+                transpose_kernel_map(kmap)
+            sfx, n_out = "_t", kmap["sizes"][0]
             out_coords, out_range = target
         else:
-            kmap = caches.kmaps.get((x.stride, self.kernel_size, self.stride, self.dilation))
-            if kmap is None:
-                return None
-            if ifsort and (kmap.get("reorder_out_in_map") is None or kmap.get("_split") != 1):
-                return None
-            out_in_map, n_out = kmap["reorder_out_in_map" if ifsort else "out_in_map"], kmap["sizes"][1]
-            reorder_loc = kmap["reorder_loc"] if ifsort else None
+            caches.cmaps.setdefault(x.stride, (x.coords, x.spatial_range))
+            kmap = _conv_impl.acquire_kernel_map(caches, x.coords, feats.shape[0], x.stride, x.spatial_range,
+                                                 self.kernel_size, self.stride, make_ntuple(self.padding, 3),
+                                                 self.dilation, config, False)
+            sfx, n_out = "", kmap["sizes"][1]
             out_coords, out_range = kmap["coords"], kmap["spatial_range"]
             out_stride = tuple(a * b for a, b in zip(x.stride, self.stride))
-        if feats.shape[1] % 8 != 0 or not feats.is_contiguous():
-            return None     # the 4-channel input layer is padded by the general entry point
-        plan = self._plan
-        if plan is None or not plan.valid_for(self.kernel, backends.allow_tf32):
-            plan = self._plan = backend.IgemmLayerPlan(self.kernel, self.scale, self.shift, backends.allow_tf32)
-        out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu, reorder_loc)
+        out_in_map = kmap["out_in_map" + sfx]
+        if self.sorted_maps:
+            art = kmap.get("_cm" + sfx)
+            if art is None:
+                art = kmap["_cm" + sfx] = backend.sorted_cm_artefacts_cuda(out_in_map, n_out)
+            map_cm, loc, tile_mask = art
+            out = backend.igemm_plan_launch(plan, feats, map_cm, n_out, residual, self.relu, loc, tile_mask, feats2,
+                                            (1, map_cm.shape[1]))
+        else:
+            out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu, in_feats2=feats2)
         caches.cmaps.setdefault(out_stride, (out_coords, out_range))
         return SparseTensor._from_parts(out, out_coords, out_stride, out_range, caches)
 
@@ -236,18 +247,20 @@ def fuse_for_inference(model: nn.Module) -> nn.Module:
 
 
 class InferenceEngine(nn.Module):
-    """Eval-mode wrapper: fused modules, no autograd, strided kernel maps built ahead of the convs."""
+    """Eval-mode wrapper: fused modules, no autograd, strided kernel maps built ahead of the convs,
+    skip concatenations read in place by the layer that follows them."""
 
-    def __init__(self, model: nn.Module, sort_max_stride: int = 0) -> None:
-        """`sort_max_stride` > 0: convolutions at tensor strides up to that value use row-sorted kernel
-        maps (the reference's sorted implicit GEMM, chosen per resolution level instead of globally)."""
+    def __init__(self, model: nn.Module, sorted_maps: bool = True) -> None:
+        """`sorted_maps`: every kernel map gets a row-sorted, column-major copy with per-tile offset masks
+        the first time a layer uses it (tsb_map_sorted_cm), and all layers sharing the map run on that copy:
+        the 128 rows of a tile then share their neighbour pattern and few (tile, offset) blocks remain."""
         super().__init__()
         if model.training:
             raise ValueError("InferenceEngine needs a model in eval() mode (BatchNorm statistics are folded)")
         self.model = fuse_for_inference(model)
         for m in self.model.modules():
             if isinstance(m, FusedConv):
-                m.sort_max_stride = sort_max_stride
+                m.sorted_maps = bool(sorted_maps)
         self._plan = None   # strided conv keys in execution order, learnt on the first call
 
     def _prebuild(self, x: SparseTensor) -> None:
@@ -263,14 +276,20 @@ class InferenceEngine(nn.Module):
 
     @torch.no_grad()
     def forward(self, x: SparseTensor):
-        if self._plan is None:
-            _conv_impl.strided_build_log = []
-            try:
-                out = self.model(x)
-            finally:
-                log, _conv_impl.strided_build_log = _conv_impl.strided_build_log, None
-            cfg = _conv_impl.resolve_config(None)
-            self._plan = [entry + (cfg,) for entry in log]
-            return out
-        self._prebuild(x)
-        return self.model(x)
+        from .. import operators
+
+        was_lazy, operators.lazy = operators.lazy, True
+        try:
+            if self._plan is None:
+                _conv_impl.strided_build_log = []
+                try:
+                    out = self.model(x)
+                finally:
+                    log, _conv_impl.strided_build_log = _conv_impl.strided_build_log, None
+                cfg = _conv_impl.resolve_config(None)
+                self._plan = [entry + (cfg,) for entry in log]
+                return out
+            self._prebuild(x)
+            return self.model(x)
+        finally:
+            operators.lazy = was_lazy

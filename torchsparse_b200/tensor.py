@@ -12,7 +12,8 @@ from .utils.tensor_cache import TensorCache, TensorCacheMode, cache_for_new_tens
 from .utils.to_dense import to_dense
 from .utils.utils import make_ntuple
 
-__all__ = ["SparseTensor", "PointTensor", "get_allow_negative_coordinates", "set_allow_negative_coordinates"]
+__all__ = ["SparseTensor", "CatSparseTensor", "PointTensor", "get_allow_negative_coordinates",
+           "set_allow_negative_coordinates"]
 
 _negative_coordinates = {"allowed": False}
 
@@ -95,6 +96,27 @@ class SparseTensor:
     def __add__(self, other: "SparseTensor") -> "SparseTensor":
         return SparseTensor._from_parts(self.feats + other.feats, self.coords, self.stride, self.spatial_range,
                                         self._caches)
+
+
+class CatSparseTensor(SparseTensor):
+    """A channel concatenation of tensors on the same coordinates that is not written out: ``parts`` holds
+    the feature matrices, and ``feats`` concatenates them the first time something asks for it.  Layers
+    that can read their input from two matrices (the fused convolutions) take ``parts`` directly."""
+
+    def __init__(self, parts, coords, stride, spatial_range, caches) -> None:
+        self.parts = tuple(parts)
+        self._feats = None
+        self.coords, self.stride, self.spatial_range, self._caches = coords, stride, spatial_range, caches
+
+    @property
+    def feats(self) -> torch.Tensor:
+        if self._feats is None:
+            self._feats = torch.cat(self.parts, dim=1)
+        return self._feats
+
+    @feats.setter
+    def feats(self, value: torch.Tensor) -> None:
+        self._feats, self.parts = value, (value,)
 
 
 class PointTensor:
