@@ -40,7 +40,8 @@ enum { TSB_F32 = 0, TSB_F16 = 1, TSB_BF16 = 2 };
 enum { TSB_MATH_FP32 = 0, TSB_MATH_TF32 = 1 };
 
 /* bits of the device status word written by table kernels (0 = fine) */
-enum { TSB_DEV_TABLE_FULL = 1, TSB_DEV_BAD_INDEX = 2 };
+enum { TSB_DEV_TABLE_FULL = 1, TSB_DEV_BAD_INDEX = 2,
+       TSB_DEV_LIMIT = 4 /* a device-side size went beyond the bound the caller stated */ };
 
 const char* tsb_version(void);
 const char* tsb_status_string(int status);
@@ -181,6 +182,42 @@ int tsb_bitmask_reduce(const int32_t* bitmask, int64_t rows, int32_t split, int3
 int tsb_map_reorder(const int32_t* out_in_map, int64_t rows, int32_t kvol, const int32_t* reorder_loc,
                     int32_t split, int32_t* out, tsb_stream_t stream);
 
+/* ---------------------------------------------------------------- kernel maps with sizes in device memory
+ * The same maps as tsb_kmap_subm / tsb_kmap_down_*, for callers that must not read sizes back to the host
+ * (a sequence of builds and convolutions recorded once and replayed, e.g. as a CUDA graph).  The number of
+ * coordinates of a tensor stride and their bounds live in a "level record", int32[16] in device memory:
+ * [0] rows, [1..4] lower and [5..8] upper bound (b,x,y,z) of the key space of the level's hash table,
+ * [9..12] the largest coordinate present, rest reserved.  Launches are sized for n_max / m_max rows (the
+ * caller's upper bounds; buffers have that many rows); rows beyond the device-side count are not written,
+ * except that every map is -1 filled up to the next multiple of 128 rows.  Coordinates must be >= 0.
+ * No counterpart in the reference, whose builders read two sizes back per strided map
+ * (torchsparse/backend/others/sparsemapping_cuda.cu:435,477). */
+
+/* Level record of the finest level from the result record of tsb_quantize_unique (voxel count, min, max);
+ * all rows get batch index `batch`.  Negative voxel coordinates set TSB_DEV_LIMIT in *dev_status. */
+int tsb_level_record_from_quantize(const int32_t* quantize_result, int32_t batch, int32_t* rec, int32_t* dev_status,
+                                   tsb_stream_t stream);
+
+/* tsb_kmap_subm with the row count and bounds read from `rec`.  capacity >= 2 * n_max; with to_insert != 0
+ * the table keys are cleared first. */
+int tsb_kmap_subm_dyn(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n_max,
+                      const int32_t* rec, const int32_t* kernel_size, int32_t to_insert, int32_t* out_in_map,
+                      int32_t* dev_status, tsb_stream_t stream);
+
+/* The whole strided build in one call: candidates -> sort -> unique -> output coordinates + table insert ->
+ * map, and (out_in_map_t != NULL) the transposed map int32 [pad128(n_max), kvol] of the matching transposed
+ * convolution.  Writes the output level's record to rec_out (the table then holds the output coordinates,
+ * as tsb_kmap_down_finish leaves it).  key_bits: the candidate keys are sorted on this many bits, so the
+ * output key space (batch x X x Y x Z cells) must stay below 2^key_bits - 1: derive it from an upper bound
+ * of the coordinates; a larger space sets TSB_DEV_LIMIT in *dev_status.  m_max <= n_max * slots: rows of
+ * out_coords / out_in_map; capacity >= 2 * m_max. */
+size_t tsb_kmap_down_dyn_workspace_bytes(int64_t n_max, const int32_t* kernel_size, const int32_t* stride);
+int tsb_kmap_down_dyn(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n_max,
+                      const int32_t* rec_in, const int32_t* kernel_size, const int32_t* stride, const int32_t* padding,
+                      int32_t key_bits, int64_t m_max, int32_t* out_coords, int32_t* out_in_map, int32_t* out_in_map_t,
+                      int32_t* rec_out, int32_t* dev_status, void* workspace, size_t workspace_bytes,
+                      tsb_stream_t stream);
+
 /* The four steps above for one split in one call: bitmask of every row, stable descending sort,
  * row-reordered map, per-tile OR of the sorted masks.  sorted_mask / reorder_loc int32 [rows],
  * reordered_map int32 [rows, kvol], reduced_mask int32 [ceil(rows / tile)].  At batch 1 the host cost
@@ -204,9 +241,19 @@ int tsb_map_sorted_artefacts(const int32_t* out_in_map, int64_t rows, int32_t kv
  * chain (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:92-107); the layout and the
  * sort key are this library's own, so the results are not interchangeable with that chain's. */
 size_t tsb_map_sorted_cm_workspace_bytes(int64_t rows);
+/* Upper bound of the number of work items (below) of a map with `rows` padded rows. */
+int64_t tsb_map_items_max(int64_t rows, int32_t kvol, int32_t max_offsets);
+/* items (nullable) int32 [tsb_map_items_max(...)][4], 16-byte aligned, and n_items (int32, device): the
+ * work-item table of the sorted map.  A tile with more than max_offsets offsets (in a sorted map these are
+ * the first tiles, and they hold a large share of all the work) is listed as several consecutive items that
+ * each take an equal share of its offsets: {row tile, offset mask of the part, part | parts << 8 | first
+ * scratch slot << 16, 0} (third word 0 for a whole tile).  Each part of a split tile owns one slot (128 rows x
+ * cout fp32) of the convolution's scratch; tiles are split only while slots remain (max_slots, at most 32767).
+ * The convolution spreads the parts over its CTAs and adds their slots in part order (tsb_igemm_desc.items). */
 int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n,
                       const int32_t* valid_n_dev, int32_t* reorder_loc, int32_t* map_cm, uint32_t* tile_mask,
-                      void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+                      int32_t max_offsets, int32_t max_slots, int32_t* items, int32_t* n_items, void* workspace,
+                      size_t workspace_bytes, tsb_stream_t stream);
 
 /* Pair lists for the GatherScatter / FetchOnDemand dataflows.
  * tsb_pairs_count: nbsizes int32 [kvol] = valid entries per column; also writes the
@@ -293,6 +340,15 @@ int tsb_map_tile_mask(const int32_t* map, int64_t n_rows, int32_t kvol, int64_t 
  *                      split-mask form of the sorted dataflow
  *                      (convolution_forward_implicit_gemm_sorted_cuda.cu:42-86, 2226-2229) with the
  *                      partial sums kept in fp32 instead of being rounded per split
+ *   items / n_items_dev / n_items / split_scratch / split_flags
+ *                      the work-item table of tsb_map_sorted_cm in place of tile_mask: int32 [n_items][4],
+ *                      its length in device memory (n_items = upper bound, sizes the launch), fp32 scratch of
+ *                      max_slots x 128 x cout elements for the parts of split tiles, and int32 [row tiles *
+ *                      ceil(cout / N tile)] part counters that must be zero before the first launch (every
+ *                      launch leaves them zero).  Launches that share scratch and counters must not overlap on
+ *                      the GPU.  No part waits for another: each stores its accumulator in its slot and counts
+ *                      itself; the part that counts last adds the slots in part order and runs the epilogue,
+ *                      so results do not depend on the schedule
  *   cfg_*              launch-configuration overrides for tuning runs (N tile, 128-byte channel chunks
  *                      per pipeline stage, stages, CTAs per SM); 0 = chosen by the library
  * Tensor-core shapes only (see above); other shapes return TSB_ERR_UNSUPPORTED. */
@@ -321,6 +377,11 @@ typedef struct tsb_igemm_desc {
   int32_t kvol, cin, cout, c1;
   int32_t k_lo, k_hi;
   int32_t cfg_n_tile, cfg_cpb, cfg_stages, cfg_ctas;
+  const int32_t* items;
+  const int32_t* n_items_dev;
+  int64_t n_items;
+  float* split_scratch;
+  int32_t* split_flags;
 } tsb_igemm_desc;
 int tsb_conv_igemm_run(const tsb_igemm_desc* desc, tsb_stream_t stream);
 
@@ -392,6 +453,23 @@ int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const do
                         int32_t* q_all, int32_t* uniq_coords, int64_t* first_index,
                         int64_t* inverse, int32_t* result, void* workspace, size_t workspace_bytes,
                         tsb_stream_t stream);
+
+/* tsb_quantize_unique for a caller that knows an upper bound of the voxel grid: the ravel keys of a grid of
+ * X x Y x Z cells (extent of the voxel coordinates per axis) are below 2^key_bits, and only that many bits are
+ * sorted (the general entry sorts 64).  A grid that does not fit gives a wrong result, not an error: state a
+ * safe bound. */
+int tsb_quantize_unique_bits(const void* xyz, int32_t xyz_is_f64, int64_t n, const double* voxel, int32_t key_bits,
+                             int32_t* q_all, int32_t* uniq_coords, int64_t* first_index, int64_t* inverse,
+                             int32_t* result, void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+
+/* The network input of one scan from the outputs of tsb_quantize_unique, without the host knowing the voxel
+ * count: coords int32 [n_max,4] = (batch, x, y, z) and feats [n_max, c_pad] of `dtype` = the c_in fp32 values
+ * of each voxel's first point, zero-padded to c_pad channels; rows at or beyond the voxel count (read from
+ * quantize_result[0]) are not written.  Stands for the indexing and collating a caller of the reference does
+ * in numpy / torch (torchsparse/utils/collate.py:11-33). */
+int tsb_voxel_inputs(const float* points, int32_t c_in, const int64_t* first_index, const int32_t* uniq_coords,
+                     const int32_t* quantize_result, int32_t batch, int64_t n_max, int32_t* coords, void* feats,
+                     int32_t c_pad, int32_t dtype, tsb_stream_t stream);
 
 /* Dense scatter: out [B,X,Y,Z,C] (zeroed by the CALLER) <- feats[i] at coords[i] = (b,x,y,z).
  * range is HOST int32[4] = (B,X,Y,Z).

@@ -54,8 +54,8 @@ def test_sorted_cm_artefacts_are_a_permutation_of_the_map():
     _, _, _, km, _ = _case(n=3000)
     m = km["out_in_map"]
     n = km["sizes"][1]
-    map_cm, loc, tmask = backend.sorted_cm_artefacts_cuda(torch.from_numpy(m).cuda(), n)
-    map_cm, loc, tmask = map_cm.cpu().numpy(), loc.cpu().numpy(), tmask.cpu().numpy().astype(np.uint32)
+    sm = backend.sorted_cm_artefacts_cuda(torch.from_numpy(m).cuda(), n, max_offsets=4)
+    map_cm, loc, tmask = sm.map_cm.cpu().numpy(), sm.loc.cpu().numpy(), sm.tile_mask.cpu().numpy().astype(np.uint32)
     assert sorted(loc[:n].tolist()) == list(range(n))               # the valid rows, each once
     assert np.array_equal(map_cm[:, :n], m[loc[:n]].T)               # row r of the sorted map is map row loc[r]
     assert (map_cm[:, n:] == -1).all()
@@ -67,18 +67,52 @@ def test_sorted_cm_artefacts_are_a_permutation_of_the_map():
     want = np.array([sum(1 << k for k in np.nonzero(valid[:, t * 128:(t + 1) * 128].any(1))[0])
                      for t in range(m.shape[0] // 128)], dtype=np.uint32)
     assert np.array_equal(tmask, want)
+    # the work-item table: every tile once, its offsets divided among ceil(count / 4) consecutive parts
+    items = sm.items.cpu().numpy()[: int(sm.n_items.item())]
+    assert len(items) <= sm.n_items_max
+    pos = slot = 0
+    budget = m.shape[0] // 128                          # scratch slots: one per tile of the map
+    for t, mask in enumerate(want):
+        pc = bin(int(mask)).count("1")
+        parts = wanted = max(1, -(-pc // 4))
+        if parts > 1 and slot + parts > budget:        # beyond the scratch slots: the tile stays whole
+            parts = 1
+        rows = items[pos: pos + parts]
+        assert (rows[:, 0] == t).all()
+        got_mask = 0
+        for j, r in enumerate(rows):
+            pm = int(r[1]) & 0xffffffff
+            assert pm and (pm & got_mask) == 0 and (parts == 1 or bin(pm).count("1") <= 4)
+            got_mask |= pm
+            if parts > 1:
+                assert int(r[2]) & 0xffff == (j | (parts << 8)) and int(r[2]) >> 16 == slot
+            else:
+                assert int(r[2]) == 0
+        assert got_mask == int(mask)
+        pos += parts
+        slot += wanted if wanted > 1 else 0             # slots are numbered as if every heavy tile were split
+    assert pos == len(items)
 
 
 @pytest.mark.parametrize("cin,cout", [(64, 96), (96, 96), (32, 32), (256, 128), (8, 32)])
-def test_sorted_cm_conv(cin, cout):
+@pytest.mark.parametrize("max_offsets", [8, 3, 27])
+def test_sorted_cm_conv(cin, cout, max_offsets):
+    """The sorted map with its tiles split into parts of at most max_offsets offsets (27: no tile is split)
+    gives the result of the plain map; the split sums are formed in part order, so two runs agree bit for bit."""
     from torchsparse_b200 import backend
 
     _, f, w, km, want = _case(cin=cin, cout=cout)
     n = km["sizes"][1]
-    map_cm, loc, tmask = backend.sorted_cm_artefacts_cuda(torch.from_numpy(km["out_in_map"]).cuda(), n)
-    y = backend.conv_forward_implicit_gemm_cuda(f, w, map_cm, n, cout, reorder_loc=loc, tile_mask=tmask,
-                                                map_strides=(1, map_cm.shape[1]))
+    sm = backend.sorted_cm_artefacts_cuda(torch.from_numpy(km["out_in_map"]).cuda(), n, max_offsets=max_offsets)
+    y = backend.conv_forward_implicit_gemm_cuda(f, w, None, n, cout, smap=sm)
     assert rel_l2(y.float().cpu().numpy(), want) < TOL
+    y2 = backend.conv_forward_implicit_gemm_cuda(f, w, None, n, cout, smap=sm)
+    assert torch.equal(y, y2)
+    assert int(sm.flags.abs().sum().item()) == 0          # the part counters are back at zero
+    # without the item table (whole tiles): the same map through explicit arguments
+    y3 = backend.conv_forward_implicit_gemm_cuda(f, w, sm.map_cm, n, cout, reorder_loc=sm.loc, tile_mask=sm.tile_mask,
+                                                 map_strides=(1, sm.rows))
+    assert rel_l2(y3.float().cpu().numpy(), want) < TOL
 
 
 @pytest.mark.parametrize("c1,c2,cout", [(64, 32, 96), (96, 32, 96), (256, 128, 256), (8, 8, 16)])

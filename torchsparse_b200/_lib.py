@@ -53,7 +53,8 @@ SIGNATURES = {
     "tsb_map_tile_mask": (C.c_int, [P, I64, I32, I64, I64, P, P, P]),
     "tsb_conv_igemm_run": (C.c_int, [P, P]),
     "tsb_map_sorted_cm_workspace_bytes": (SZ, [I64]),
-    "tsb_map_sorted_cm": (C.c_int, [P, I64, I32, I64, P, P, P, P, P, SZ, P]),
+    "tsb_map_items_max": (I64, [I64, I32, I32]),
+    "tsb_map_sorted_cm": (C.c_int, [P, I64, I32, I64, P, P, P, P, I32, I32, P, P, P, SZ, P]),
     "tsb_conv_packed_weight_bytes": (SZ, [I32, I32, I32, I32]),
     "tsb_conv_pack_weight": (C.c_int, [P, I32, I32, I32, I32, P, P]),
     "tsb_conv_gs_workspace_bytes": (SZ, [I64, I32, I32, I32, I32]),
@@ -67,6 +68,12 @@ SIGNATURES = {
     "tsb_map_sorted_artefacts": (C.c_int, [P, I64, I32, I64, I32, P, P, P, P, P, SZ, P]),
     "tsb_quantize_workspace_bytes": (SZ, [I64]),
     "tsb_quantize_unique": (C.c_int, [P, I32, I64, P, P, P, P, P, P, P, SZ, P]),
+    "tsb_quantize_unique_bits": (C.c_int, [P, I32, I64, P, I32, P, P, P, P, P, P, SZ, P]),
+    "tsb_voxel_inputs": (C.c_int, [P, I32, P, P, P, I32, I64, P, P, I32, I32, P]),
+    "tsb_level_record_from_quantize": (C.c_int, [P, I32, P, P, P]),
+    "tsb_kmap_subm_dyn": (C.c_int, [P, P, I64, P, I64, P, P, I32, P, P, P]),
+    "tsb_kmap_down_dyn_workspace_bytes": (SZ, [I64, P, P]),
+    "tsb_kmap_down_dyn": (C.c_int, [P, P, I64, P, I64, P, P, P, P, I32, I64, P, P, P, P, P, P, SZ, P]),
     "tsb_to_dense_fwd": (C.c_int, [P, P, I64, I32, P, I32, P, P]),
 }
 
@@ -81,6 +88,7 @@ class IgemmDesc(C.Structure):
         ("map_row_stride", I64), ("map_col_stride", I64),
         ("kvol", I32), ("cin", I32), ("cout", I32), ("c1", I32), ("k_lo", I32), ("k_hi", I32),
         ("cfg_n_tile", I32), ("cfg_cpb", I32), ("cfg_stages", I32), ("cfg_ctas", I32),
+        ("items", P), ("n_items_dev", P), ("n_items", I64), ("split_scratch", P), ("split_flags", P),
     ]
 
 
@@ -93,7 +101,7 @@ def new_igemm_desc() -> "IgemmDesc":
 TSB_OK = 0
 TSB_F32, TSB_F16, TSB_BF16 = 0, 1, 2
 TSB_MATH_FP32, TSB_MATH_TF32 = 0, 1
-TSB_DEV_TABLE_FULL, TSB_DEV_BAD_INDEX = 1, 2
+TSB_DEV_TABLE_FULL, TSB_DEV_BAD_INDEX, TSB_DEV_LIMIT = 1, 2, 4
 
 
 class TsbError(RuntimeError):

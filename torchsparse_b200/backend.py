@@ -32,7 +32,7 @@ __all__ = [
     "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
     "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
-    "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda",
+    "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda", "SortedMap",
 ]
 
 _DTYPES = {torch.float32: _lib.TSB_F32, torch.float16: _lib.TSB_F16, torch.bfloat16: _lib.TSB_BF16}
@@ -327,20 +327,50 @@ def sorted_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, m_tile: int):
     return masks[0], masks[1], reordered, reduced
 
 
-def sorted_cm_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, valid_n_dev: Optional[torch.Tensor] = None):
-    """The row order and layout the tensor-core convolution is fastest on (tsb_map_sorted_cm): returns
-    (map_cm int32 [Kvol, rows] column-major and row-sorted, reorder_loc int32 [rows], tile_mask int32
-    [rows / 128]).  Launch with ``map_strides=(1, rows)``."""
+class SortedMap:
+    """A kernel map in the form the tensor-core convolution is fastest on (tsb_map_sorted_cm): rows sorted by
+    neighbour mask, stored column-major, with per-tile offset masks and the work-item table that splits tiles
+    with many offsets into parts.  Built once per kernel map and shared by every layer that uses the map
+    (their launches must not overlap on the GPU: they share the scratch of the split tiles)."""
+
+    __slots__ = ("map_cm", "loc", "tile_mask", "items", "n_items", "n_items_max", "rows", "kvol", "flags", "_scratch")
+
+    def scratch(self, cout: int) -> torch.Tensor:
+        buf = self._scratch.get(cout)
+        if buf is None:
+            buf = self._scratch[cout] = torch.empty((self.rows, cout), dtype=torch.float32, device=self.map_cm.device)
+        return buf
+
+
+# a tile of the sorted map with more offsets than this is split into parts that other CTAs can take
+# (32: no tile is split)
+split_max_offsets = 32
+
+
+def sorted_cm_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, valid_n_dev: Optional[torch.Tensor] = None,
+                             max_offsets: Optional[int] = None) -> SortedMap:
+    """Row-sorted, column-major copy of a row-major kernel map plus its work-item table (tsb_map_sorted_cm).
+    ``valid_n_dev`` (int32, device) overrides ``valid_n`` with a count the host does not know."""
     _need_cuda(out_in_map)
     rows, kvol = out_in_map.shape
     dev = out_in_map.device
-    map_cm = torch.empty((kvol, rows), dtype=torch.int32, device=dev)
-    loc = torch.empty(rows, dtype=torch.int32, device=dev)
-    tile_mask = torch.empty(max(rows // 128, 1), dtype=torch.int32, device=dev)
+    max_offsets = int(max_offsets or split_max_offsets)
+    m = SortedMap()
+    m.rows, m.kvol = rows, kvol
+    m.map_cm = torch.empty((kvol, rows), dtype=torch.int32, device=dev)
+    m.loc = torch.empty(rows, dtype=torch.int32, device=dev)
+    m.tile_mask = torch.empty(max(rows // 128, 1), dtype=torch.int32, device=dev)
+    m.n_items_max = int(lib.tsb_map_items_max(rows, kvol, max_offsets))
+    m.items = torch.empty((max(m.n_items_max, 1), 4), dtype=torch.int32, device=dev)
+    m.n_items = torch.zeros(1, dtype=torch.int32, device=dev)
+    m.flags = torch.zeros(max(rows // 128, 1) * 16, dtype=torch.int32, device=dev)
+    m._scratch = {}
     ws = _workspace(lib.tsb_map_sorted_cm_workspace_bytes(rows), dev)
-    check(lib.tsb_map_sorted_cm(_p(out_in_map), rows, kvol, int(valid_n), _p(valid_n_dev), _p(loc), _p(map_cm),
-                                _p(tile_mask), _p(ws), ws.numel(), _stream()), "sorted_cm_artefacts_cuda")
-    return map_cm, loc, tile_mask
+    check(lib.tsb_map_sorted_cm(_p(out_in_map), rows, kvol, int(valid_n), _p(valid_n_dev), _p(m.loc), _p(m.map_cm),
+                                _p(m.tile_mask), max_offsets, rows // 128, _p(m.items), _p(m.n_items), _p(ws),
+                                ws.numel(), _stream()),
+          "sorted_cm_artefacts_cuda")
+    return m
 
 
 def reduce_bitmask_cuda(bitmask: torch.Tensor, m_tile: int) -> torch.Tensor:
@@ -545,7 +575,8 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
                                     k_range: Optional[Tuple[int, int]] = None,
                                     acc_in: Optional[torch.Tensor] = None, acc_out: Optional[torch.Tensor] = None,
                                     n_out_dev: Optional[torch.Tensor] = None,
-                                    out: Optional[torch.Tensor] = None, dst_rows: int = 0) -> Optional[torch.Tensor]:
+                                    out: Optional[torch.Tensor] = None, dst_rows: int = 0,
+                                    smap: Optional["SortedMap"] = None) -> Optional[torch.Tensor]:
     """Implicit-GEMM forward
     (torchsparse/backend/convolution/convolution_forward_implicit_gemm_cuda.cu:1527-1987).
     ``scale`` / ``bias`` (fp32 [Cout]), ``residual`` and ``relu`` are an optional fused epilogue
@@ -553,7 +584,10 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     The remaining keywords are the options of ``tsb_conv_igemm_run`` (include/tsb200.h): a second feature
     matrix whose channels follow those of ``in_feats``, a map with other strides (or ``None`` with a
     1x1x1 kernel: row m reads input row m), a range of kernel offsets, fp32 partial sums in / out, a
-    device-side row count and a caller-owned output."""
+    device-side row count and a caller-owned output.  ``smap`` (a :class:`SortedMap`) stands for the map, its
+    strides, row order and work-item table in one argument."""
+    if smap is not None:
+        out_in_map, reorder_loc, tile_mask, map_strides = smap.map_cm, smap.loc, smap.tile_mask, (1, smap.rows)
     in_feats, kernel = _prep_feats_cat(in_feats, in_feats2, kernel, allow_fp16)
     if in_feats2 is not None:
         in_feats2 = in_feats2.contiguous()
@@ -613,6 +647,9 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     d.c1 = in_feats.shape[1] if in_feats2 is not None else 0
     if k_range is not None:
         d.k_lo, d.k_hi = k_range
+    if smap is not None and k_range is None:
+        d.items, d.n_items_dev, d.n_items = _p(smap.items), _p(smap.n_items), smap.n_items_max
+        d.split_scratch, d.split_flags = _p(smap.scratch(cout)), _p(smap.flags)
     _apply_tuning(d)
     rc = lib.tsb_conv_igemm_run(_lib.C.byref(d), _stream())
     if rc == 2:
@@ -696,7 +733,8 @@ def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: 
                       num_out_feats: int, residual: Optional[torch.Tensor], relu: bool,
                       reorder_loc: Optional[torch.Tensor] = None, tile_mask: Optional[torch.Tensor] = None,
                       in_feats2: Optional[torch.Tensor] = None, map_strides: Optional[Tuple[int, int]] = None,
-                      n_out_dev: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      n_out_dev: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                      smap: Optional["SortedMap"] = None) -> torch.Tensor:
     """conv_forward_implicit_gemm_cuda for a layer with an :class:`IgemmLayerPlan` (same kernel launch).
     Falls back to the checked entry point when launches are being observed or their status read back."""
     if _observer is not None or check_kernel_status:
@@ -704,7 +742,9 @@ def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: 
                                                plan.allow_tf32, True, scale=plan.scale, bias=plan.bias,
                                                residual=residual, relu=relu, reorder_loc=reorder_loc,
                                                tile_mask=tile_mask, in_feats2=in_feats2, map_strides=map_strides,
-                                               n_out_dev=n_out_dev, out=out)
+                                               n_out_dev=n_out_dev, out=out, smap=smap)
+    if smap is not None:
+        out_in_map, reorder_loc, tile_mask, map_strides = smap.map_cm, smap.loc, smap.tile_mask, (1, smap.rows)
     c1 = in_feats.shape[1]
     if in_feats.dtype != plan.dtype or not in_feats.is_contiguous():
         raise ValueError("input features do not match the layer plan (dtype or layout)")
@@ -737,6 +777,11 @@ def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: 
     d.workspace, d.workspace_bytes = (None, 0) if ws is None else (ws.data_ptr(), ws.numel())
     d.n_in, d.n_out = in_feats.shape[0], num_out_feats
     d.map_row_stride, d.map_col_stride = map_strides if map_strides is not None else (0, 0)
+    if smap is not None:
+        d.items, d.n_items_dev, d.n_items = smap.items.data_ptr(), smap.n_items.data_ptr(), smap.n_items_max
+        d.split_scratch, d.split_flags = smap.scratch(plan.cout).data_ptr(), smap.flags.data_ptr()
+    else:
+        d.items, d.n_items_dev, d.n_items, d.split_scratch, d.split_flags = None, None, 0, None, None
     _apply_tuning(d)
     rc = lib.tsb_conv_igemm_run(_lib.C.byref(d), torch._C._cuda_getCurrentRawStream(plan.device.index))
     if rc != 0:

@@ -41,6 +41,14 @@ struct IgemmArgs {
   float* acc_out;            // fp32 [dst_rows, cout]: store the accumulator (+ acc_in) here instead of y, no epilogue
   int k_lo, k_hi;            // kernel offsets [k_lo, k_hi) covered by this launch (0, 0: all)
   int cfg_n_tile, cfg_cpb, cfg_stages, cfg_ctas;   // tuning overrides of the launch configuration (0: automatic)
+  // work-item table of a map whose heavy tiles are split into parts (tsb_map_sorted_cm): int32 [n_items][4] =
+  // {row tile, offset mask, part | parts << 8, 0}, its length in device memory, the fp32 running sums
+  // [pad128(n_out), cout] and the per-(row tile, N tile) part counters (zero between launches)
+  const int* items;
+  const int* n_items_dev;
+  int64_t n_items;           // upper bound of *n_items_dev (sizes the launch)
+  float* split_scratch;
+  int* split_flags;
 };
 
 struct GsArgs {

@@ -31,9 +31,9 @@
 //   warp 13     allocates TMEM; one elected thread issues tcgen05.mma (M=128, N=N_tile, 32 bytes of K
 //               per instruction) and releases stages / publishes accumulators with tcgen05.commit
 //   warp 14     scheduler: takes the CTA's next work item from a global counter (tiles differ in how
-//               many offsets they hold, so a fixed assignment would leave CTAs idle at the end) and
-//               publishes (item, offset mask) through a small ring; the counter read for the item
-//               after next is already in flight
+//               many offsets they hold, so a fixed assignment would leave CTAs idle at the end) when the
+//               gather warps reach the last offset of the current item, and publishes (item, offset
+//               mask) through a small ring
 //
 // Pair-list mode (the GatherScatter / FetchOnDemand dataflows, conv_pairs.cu): the map is one column of
 // input rows, every 128-row tile belongs to one kernel offset (tile_k[tile] picks its weight block),
@@ -77,7 +77,7 @@ constexpr int kMaxKvolUmma = 32;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s
 
-enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3, kErrSchedWait = 4 };
+enum { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3, kErrSchedWait = 4, kErrSplitWait = 5 };
 enum { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -264,6 +264,12 @@ struct UmmaParams {
   const void* x2;       // nullable, [n_in, cin - c1]: channels [c1, cin) (a concatenation that is not materialised)
   const int* map;       // entry (row, k) at map[row * map_rs + k * map_cs]; null: row m reads input row m (kvol = 1)
   const unsigned* tile_mask;   // nullable, [tiles]: bit k set when some row of the tile has a neighbour at offset k
+  const int4* items;    // nullable work-item table {row tile, offset mask, part | parts << 8 | first slot << 16, 0}: tiles
+                        // with many offsets appear as several parts whose fp32 accumulators meet in split_scratch
+  const int* n_items_dev;      // number of entries of `items` (device memory); n_items is its upper bound
+  float* split_scratch;        // fp32 [slots][128][cout]: one slot per part of a split tile
+  int* split_flags;            // [row tiles * N tiles], zero between launches: parts of the tile finished so far
+  int n_items;
   const int* reorder;   // nullable
   void* y;              // [n_out, cout]
   const float* scale;   // nullable, fp32 [cout]: y = acc * scale + bias (+ residual), then ReLU
@@ -330,24 +336,33 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+// Map entries are fetched one offset ahead of their use; as plain loads the compiler would sink them to
+// the use and expose their latency, as volatile asm they are issued where they stand.
+__device__ __forceinline__ int ld_map_entry(const int* p) {
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
 // The next (work item, offset mask) of the scheduler ring, read by lane 0 and handed to the whole warp; the
 // slot is released at once (its two words now live in registers).  false: a bounded wait ran out.
 __device__ __forceinline__ bool ring_take(uint64_t* s_full, uint64_t* s_empty, const int* s_tile, const uint32_t* s_kmask,
-                                          int it, int lane, int& w, uint32_t& kmask) {
+                                          const int* s_aux, int it, int lane, int& w, uint32_t& kmask, int& aux) {
   const int slot = it % kRing;
-  int ww = -1;
+  int ww = -1, aa = 0;
   uint32_t mm = 0, ok = 1;
   if (lane == 0) {
     ok = mbar_wait(smem_u32(&s_full[slot]), (uint32_t)(it / kRing) & 1u) ? 1u : 0u;
     if (ok) {
       ww = s_tile[slot];
       mm = s_kmask[slot];
+      aa = s_aux[slot];
       mbar_arrive(smem_u32(&s_empty[slot]));
     }
   }
   ok = __shfl_sync(0xffffffffu, ok, 0);
   w = __shfl_sync(0xffffffffu, ww, 0);
   kmask = __shfl_sync(0xffffffffu, mm, 0);
+  aux = __shfl_sync(0xffffffffu, aa, 0);
   return ok != 0;
 }
 
@@ -370,14 +385,19 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   __shared__ uint64_t s_sched_empty[kRing];
   __shared__ uint64_t s_acc_full[2];
   __shared__ uint64_t s_acc_empty[2];
+  __shared__ uint64_t s_req;             // the gather warps ask the scheduler for the next work item
+  __shared__ uint64_t s_epi;             // the four epilogue warps meet here around the count of a split tile's parts
+  __shared__ volatile int s_split_last;  // this CTA counted the last part of the split tile at hand
   __shared__ uint32_t s_kmask[kRing];
-  __shared__ int s_tile[kRing];          // work item of the ring slot; -1 = no more work
+  __shared__ int s_tile[kRing];          // row tile * N tiles + N tile of the ring slot; -1 = no more work
+  __shared__ int s_aux[kRing];           // part | parts << 8 of a tile that is split into parts (0: whole tile)
   __shared__ uint32_t s_tmem;
   __shared__ volatile int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #ifdef TSB_TRACE_BUILD
   if (tid == 0) TSB_TRACE_HOT(7, 0);     // CTA entry
+  if (tid == 0 && p.trace && blockIdx.x < 1024) p.trace[2048 + 2 * blockIdx.x] = (long long)global_ns();   // every CTA: wall clock
 #endif
   const int b_bytes = p.n_tile * kRowBytes;              // one weight chunk
   const int stage_bytes = p.cpb * (kABytes + b_bytes);
@@ -401,6 +421,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       mbar_init(smem_u32(&s_acc_full[b]), 1);
       mbar_init(smem_u32(&s_acc_empty[b]), kEpilogueWarps);
     }
+    mbar_init(smem_u32(&s_epi), kEpilogueWarps);
+    mbar_init(smem_u32(&s_req), 1);
     s_abort = 0;
     fence_barrier_init();
   }
@@ -415,7 +437,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   if (p.n_out_dev) n_out = max(0, min(__ldg(p.n_out_dev), p.n_out));
   const int tiles_n = (p.cout + p.n_tile - 1) / p.n_tile;
   const int tiles_m = (n_out + kTileM - 1) / kTileM;
-  const int n_work = tiles_m * tiles_n;
+  int n_work = tiles_m * tiles_n;
+  if (p.items) n_work = max(0, min(__ldg(p.n_items_dev), p.n_items)) * tiles_n;
 
   if (warp < kGatherWarps) {
     // ------------------------------------------------------------ gather warps (A operand)
@@ -443,9 +466,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     // fetches the map entries of this thread's four rows for the next offset of the item stream
     auto next_offset = [&](int (&src)[kCopies]) -> bool {
       while (km == 0) {
-        int w;
+        int w, aux;
         uint32_t m;
-        if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, m)) {
+        if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, s_aux, it, lane, w, m, aux)) {
           atomicExch(p.error, kErrSchedWait);
           s_abort = 1;
           ok = false;
@@ -455,13 +478,18 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         if (w < 0 || s_abort) return false;
         row0 = (w / tiles_n) * kTileM;
         km = m;
+        if (km == 0 && tid == 0) mbar_arrive(smem_u32(&s_req));   // nothing to copy for this item: ask for the next
       }
       const int k = __ffs(km) - 1;
       km &= km - 1;
+      // The item's last offset is now being fetched: time to ask the scheduler for the next item, so that it
+      // arrives while the remaining copies of this one are issued.  Asking any earlier would let every CTA hold
+      // several items from the start, and with a few items per CTA the dynamic assignment would balance nothing.
+      if (km == 0 && tid == 0) mbar_arrive(smem_u32(&s_req));
 #pragma unroll
       for (int j = 0; j < kCopies; ++j) {
         const int r = row0 + rbase + j * kRowsPerPass;
-        if (p.map) src[j] = __ldg(p.map + (long long)r * p.map_rs + (long long)k * p.map_cs);
+        if (p.map) src[j] = ld_map_entry(p.map + (long long)r * p.map_rs + (long long)k * p.map_cs);
         else src[j] = r < n_out ? r : -1;
       }
       return true;
@@ -523,15 +551,97 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     T* y = reinterpret_cast<T*>(p.y);
     const T* res = reinterpret_cast<const T*>(p.residual);
     int acc_count = 0;   // tiles that used an accumulator so far (tiles with an empty mask use none)
+    uint32_t epi_uses = 0;
+    // all four epilogue warps have reached this point (bounded, like every other wait)
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&s_epi));
+      const bool met = mbar_wait_warp(smem_u32(&s_epi), epi_uses & 1u, lane);
+      ++epi_uses;
+      return met;
+    };
+    // eight fp32 sums of row dst_row, channels nh .. nh + 7  ->  partial sums in / out, scale, bias, residual,
+    // ReLU, one rounding, one 16-byte (or two, fp32) store
+    auto emit8 = [&](float (&f)[8], int nh, int64_t dst_row) {
+      if (p.acc_in) {    // partial sums of the launches that covered the other kernel offsets
+        const float* ap = p.acc_in + dst_row * p.cout + nh;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(ap));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(ap) + 1);
+        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+        f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+      }
+      if (p.acc_out) {   // this launch is not the last of its group: keep the sum in fp32
+        float* ao = p.acc_out + dst_row * p.cout + nh;
+        reinterpret_cast<float4*>(ao)[0] = make_float4(f[0], f[1], f[2], f[3]);
+        reinterpret_cast<float4*>(ao)[1] = make_float4(f[4], f[5], f[6], f[7]);
+        return;
+      }
+      if (p.scale) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p.scale + nh));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p.scale + nh) + 1);
+        f[0] *= a.x; f[1] *= a.y; f[2] *= a.z; f[3] *= a.w;
+        f[4] *= b.x; f[5] *= b.y; f[6] *= b.z; f[7] *= b.w;
+      }
+      if (p.bias) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(p.bias + nh));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + nh) + 1);
+        f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+        f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+      }
+      if (kTF32 || p.out_fp32) {
+        float* yo = reinterpret_cast<float*>(p.y) + dst_row * p.cout + nh;
+        if (kTF32 && res) {
+          const float* rp = reinterpret_cast<const float*>(res) + dst_row * p.cout + nh;
+          const float4 ra = __ldg(reinterpret_cast<const float4*>(rp));
+          const float4 rb = __ldg(reinterpret_cast<const float4*>(rp) + 1);
+          f[0] += ra.x; f[1] += ra.y; f[2] += ra.z; f[3] += ra.w;
+          f[4] += rb.x; f[5] += rb.y; f[6] += rb.z; f[7] += rb.w;
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
+        }
+        if (p.atomic_out) {
+          atomicAdd(reinterpret_cast<float4*>(yo), make_float4(f[0], f[1], f[2], f[3]));
+          atomicAdd(reinterpret_cast<float4*>(yo) + 1, make_float4(f[4], f[5], f[6], f[7]));
+        } else {
+          reinterpret_cast<float4*>(yo)[0] = make_float4(f[0], f[1], f[2], f[3]);
+          reinterpret_cast<float4*>(yo)[1] = make_float4(f[4], f[5], f[6], f[7]);
+        }
+      } else if constexpr (!kTF32) {
+        if (res) {
+          const uint4 rv = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + nh));
+          const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t = unpack2<T>(rw[e]);
+            f[2 * e] += t.x;
+            f[2 * e + 1] += t.y;
+          }
+        }
+        if (p.relu) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
+        }
+        *reinterpret_cast<uint4*>(y + dst_row * p.cout + nh) =
+            make_uint4(pack2<T>(f[0], f[1]), pack2<T>(f[2], f[3]), pack2<T>(f[4], f[5]), pack2<T>(f[6], f[7]));
+      }
+    };
     for (int it = 0;; ++it) {
-      int w;
+      int w, aux;
       uint32_t kmask;
-      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, kmask)) {
+      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, s_aux, it, lane, w, kmask, aux)) {
         atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
       }
       if (s_abort || w < 0) break;
+      // A tile with many offsets is worked on by several items ("parts", possibly on other CTAs).  Every part
+      // stores its fp32 accumulator in its own slot of split_scratch and counts itself in split_flags[tile];
+      // the part that counts last adds the slots in part order (so the sum does not depend on the schedule),
+      // runs the epilogue and puts the counter back to zero.  No part waits for another.
+      const int part = aux & 0xff, parts = (aux >> 8) & 0xff, slot0 = aux >> 16;
+      const bool split = parts > 1;
       const int row0 = (w / tiles_n) * kTileM;
       const int n0 = (w % tiles_n) * p.n_tile;
       const int n_valid = min(p.n_tile, p.cout - n0);
@@ -552,131 +662,113 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         if (dst_row >= p.dst_rows) dst_row = -1;
       }
       const uint32_t acc_addr = tmem_base + (uint32_t)ab * acc_cols + ((uint32_t)(quarter * 32) << 16);
+      const int64_t slot_elems = (int64_t)kTileM * p.cout;
+      float* my_slot = split ? p.split_scratch + (int64_t)(slot0 + part) * slot_elems + (int64_t)r * p.cout : nullptr;
       for (int j = 0; j < n_mma; j += 16) {
-        // the accumulator load is in flight while the per-channel constants and the residual are fetched
         uint32_t v[16];
         if (have_acc) {
           tmem_ld16(acc_addr + (uint32_t)j, v);
+          tmem_ld_wait16(v);
         } else {
 #pragma unroll
           for (int e = 0; e < 16; ++e) v[e] = 0u;
         }
         const int n = n0 + j;
-        const bool ok8[2] = {dst_row >= 0 && n < p.cout, dst_row >= 0 && n + 8 < p.cout};   // cout % 8 == 0
-        // residual of the 16 channels, still packed (fp32: fetched per half below)
-        uint4 rv[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-        if constexpr (!kTF32) {
-          if (res) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-              if (ok8[h]) rv[h] = __ldg(reinterpret_cast<const uint4*>(res + dst_row * p.cout + n) + h);
-          }
-        }
-        if (have_acc) tmem_ld_wait16(v);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          if (!ok8[h]) continue;
           const int nh = n + 8 * h;
+          if (dst_row < 0 || nh >= p.cout) continue;      // cout % 8 == 0
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * h + e]);
-          if (p.acc_in) {    // partial sums of the launches that covered the other kernel offsets
-            const float* ap = p.acc_in + dst_row * p.cout + nh;
-            const float4 a = __ldg(reinterpret_cast<const float4*>(ap));
-            const float4 b = __ldg(reinterpret_cast<const float4*>(ap) + 1);
-            f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-            f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+          if (split) {
+            reinterpret_cast<float4*>(my_slot + nh)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(my_slot + nh)[1] = make_float4(f[4], f[5], f[6], f[7]);
+          } else {
+            emit8(f, nh, dst_row);
           }
-          if (p.acc_out) {   // this launch is not the last of its group: keep the sum in fp32
-            float* ao = p.acc_out + dst_row * p.cout + nh;
-            reinterpret_cast<float4*>(ao)[0] = make_float4(f[0], f[1], f[2], f[3]);
-            reinterpret_cast<float4*>(ao)[1] = make_float4(f[4], f[5], f[6], f[7]);
-            continue;
-          }
-          if (p.scale) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(p.scale + nh));
-            const float4 b = __ldg(reinterpret_cast<const float4*>(p.scale + nh) + 1);
-            f[0] *= a.x; f[1] *= a.y; f[2] *= a.z; f[3] *= a.w;
-            f[4] *= b.x; f[5] *= b.y; f[6] *= b.z; f[7] *= b.w;
-          }
-          if (p.bias) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(p.bias + nh));
-            const float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + nh) + 1);
-            f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-            f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-          }
-          if (kTF32 || p.out_fp32) {
-            float* yo = reinterpret_cast<float*>(p.y) + dst_row * p.cout + nh;
-            if (kTF32 && res) {
-              const float* rp = reinterpret_cast<const float*>(res) + dst_row * p.cout + nh;
-              const float4 ra = __ldg(reinterpret_cast<const float4*>(rp));
-              const float4 rb = __ldg(reinterpret_cast<const float4*>(rp) + 1);
-              f[0] += ra.x; f[1] += ra.y; f[2] += ra.z; f[3] += ra.w;
-              f[4] += rb.x; f[5] += rb.y; f[6] += rb.z; f[7] += rb.w;
+        }
+      }
+      // this warp is done with the accumulator buffer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0 && have_acc) mbar_arrive(smem_u32(&s_acc_empty[ab]));
+      if (have_acc) ++acc_count;
+      if (split) {
+        __threadfence();                              // this thread's slot rows are visible before the count
+        if (!epi_sync()) {
+          atomicExch(p.error, kErrSplitWait);
+          s_abort = 1;
+          break;
+        }
+        if (warp == kGatherWarps && lane == 0) {
+          int* flag = p.split_flags + w;
+          const int before = atomicAdd(flag, 1);
+          __threadfence();
+          const int last = before == parts - 1;
+          if (last) atomicExch(flag, 0);             // no other part of this tile is left to count
+          s_split_last = last;
+        }
+        if (!epi_sync()) {
+          atomicExch(p.error, kErrSplitWait);
+          s_abort = 1;
+          break;
+        }
+        if (s_split_last) {
+          const float* slots = p.split_scratch + (int64_t)slot0 * slot_elems + (int64_t)r * p.cout;
+          for (int nh = n0; nh < n0 + n_mma; nh += 8) {
+            if (dst_row < 0 || nh >= p.cout) continue;
+            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < parts; ++q) {
+              const float4 a = __ldcg(reinterpret_cast<const float4*>(slots + q * slot_elems + nh));
+              const float4 b = __ldcg(reinterpret_cast<const float4*>(slots + q * slot_elems + nh) + 1);
+              f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+              f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
             }
-            if (p.relu) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
-            }
-            if (p.atomic_out) {
-              atomicAdd(reinterpret_cast<float4*>(yo), make_float4(f[0], f[1], f[2], f[3]));
-              atomicAdd(reinterpret_cast<float4*>(yo) + 1, make_float4(f[4], f[5], f[6], f[7]));
-            } else {
-              reinterpret_cast<float4*>(yo)[0] = make_float4(f[0], f[1], f[2], f[3]);
-              reinterpret_cast<float4*>(yo)[1] = make_float4(f[4], f[5], f[6], f[7]);
-            }
-          } else if constexpr (!kTF32) {
-            if (res) {
-              const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rv[h]);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 t = unpack2<T>(rw[e]);
-                f[2 * e] += t.x;
-                f[2 * e + 1] += t.y;
-              }
-            }
-            if (p.relu) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = fmaxf(f[e], 0.f);
-            }
-            *reinterpret_cast<uint4*>(y + dst_row * p.cout + nh) =
-                make_uint4(pack2<T>(f[0], f[1]), pack2<T>(f[2], f[3]), pack2<T>(f[4], f[5]), pack2<T>(f[6], f[7]));
+            emit8(f, nh, dst_row);
           }
         }
       }
 #ifdef TSB_TRACE_BUILD
       if (warp == kGatherWarps && lane == 0) TSB_TRACE_HOT(7, it + 1);   // item written out (first epilogue warp)
 #endif
-      // this warp is done with the accumulator buffer
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0 && have_acc) mbar_arrive(smem_u32(&s_acc_empty[ab]));
-      if (have_acc) ++acc_count;
     }
   } else if (warp == kSchedWarp) {
     // ------------------------------------------------------------ scheduler warp
-    // one lane: counter read for the next item in flight while the current item's mask is fetched and
-    // published; the other roles run up to kRing items behind
+    // one lane: takes the next item from the global counter each time the gather warps ask for one (the
+    // first without being asked), reads its table entry and publishes it through the ring
     if (lane == 0) {
-      int w_next = atomicAdd(p.sched, 1);
       for (int i = 0;; ++i) {
         const int slot = i % kRing;
+        if (i >= 1 && !mbar_wait(smem_u32(&s_req), (uint32_t)(i - 1) & 1u)) {
+          atomicExch(p.error, kErrSchedWait);
+          s_abort = 1;
+          break;
+        }
         if (i >= kRing && !mbar_wait(smem_u32(&s_sched_empty[slot]), ((uint32_t)(i / kRing) + 1u) & 1u)) {
           atomicExch(p.error, kErrSchedWait);
           s_abort = 1;
           break;
         }
-        const int w = w_next;
+        const int w = atomicAdd(p.sched, 1);
         if (w >= n_work || s_abort) {
           s_tile[slot] = -1;                  // tells the other roles that the CTA is done
           mbar_arrive(smem_u32(&s_sched_full[slot]));
           break;
         }
-        w_next = atomicAdd(p.sched, 1);
         uint32_t mask = p.k_range;
-        if (p.tile_mask) mask &= __ldg(&p.tile_mask[w / tiles_n]);
+        int item = w, aux = 0;
+        if (p.items) {
+          const int4 e = __ldg(&p.items[w / tiles_n]);
+          item = e.x * tiles_n + (w % tiles_n);
+          mask &= (uint32_t)e.y;
+          aux = e.z;
+        } else if (p.tile_mask) {
+          mask &= __ldg(&p.tile_mask[w / tiles_n]);
+        }
         s_kmask[slot] = mask;
-        s_tile[slot] = w;
+        s_tile[slot] = item;
+        s_aux[slot] = aux;
         mbar_arrive(smem_u32(&s_sched_full[slot]));
       }
     }
@@ -688,9 +780,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     bool first_pass = true;
     bool ok = true;
     for (int it = 0; ok; ++it) {
-      int w;
+      int w, aux;
       uint32_t kmask;
-      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, kmask)) {
+      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, s_aux, it, lane, w, kmask, aux)) {
         if (lane == 0) atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
@@ -741,9 +833,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     int blk = 0;
 #endif
     for (int it = 0; ok; ++it) {
-      int w;
+      int w, aux;
       uint32_t kmask;
-      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, it, lane, w, kmask)) {
+      if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, s_aux, it, lane, w, kmask, aux)) {
         if (lane == 0) atomicExch(p.error, kErrSchedWait);
         s_abort = 1;
         break;
@@ -826,6 +918,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   }
 #ifdef TSB_TRACE_BUILD
   if (tid == 0) TSB_TRACE_HOT(3, 0);     // CTA exit
+  if (tid == 0 && p.trace && blockIdx.x < 1024) p.trace[2048 + 2 * blockIdx.x + 1] = (long long)global_ns();
 #endif
   // the last CTA to finish puts the scheduling words back to zero for a later launch
   if (tid == 0) {
@@ -1030,6 +1123,9 @@ bool igemm_umma_supported(const IgemmArgs& a) {
   if (!a.map && a.kvol != 1) return false;            // identity rows: a 1x1x1 kernel
   if (a.out_fp32 && a.residual) return false;
   if ((a.acc_in || a.acc_out) && (a.atomic_out || a.out_fp32)) return false;
+  if (a.items && (!a.n_items_dev || !a.split_scratch || !a.split_flags || a.tile_k || a.n_items < 0 ||
+                  ((uintptr_t)a.items & 15) || ((uintptr_t)a.split_scratch & 15)))
+    return false;
   if (((uintptr_t)a.x | (uintptr_t)a.x2 | (uintptr_t)a.y | (uintptr_t)a.w | (uintptr_t)a.residual |
        (uintptr_t)a.packed_w | (uintptr_t)a.acc_in | (uintptr_t)a.acc_out) & 15)
     return false;
@@ -1078,7 +1174,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   const T* wt = reinterpret_cast<const T*>(a.packed_w);
   int* err = a.dev_status;
   const unsigned* tmask = a.tile_mask;
-  const bool need_mask = !tmask && a.map && !a.tile_k && a.kvol > 1;
+  const bool need_mask = !tmask && !a.items && a.map && !a.tile_k && a.kvol > 1;
   // workspace layout: [packed weights][error word, 256 bytes][tile masks]; only the parts the caller did
   // not supply are used, and the workspace has to reach the end of the last one used
   size_t need = 0;
@@ -1111,6 +1207,8 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   p.map = a.map; p.map_rs = rs; p.map_cs = cs; p.tile_mask = tmask;
   p.reorder = a.reorder_loc; p.y = a.y; p.bias = a.bias; p.scale = a.scale;
   p.residual = a.residual; p.acc_in = a.acc_in; p.acc_out = a.acc_out; p.n_out_dev = a.n_out_dev; p.error = err;
+  p.items = reinterpret_cast<const int4*>(a.items); p.n_items_dev = a.n_items_dev; p.n_items = (int)a.n_items;
+  p.split_scratch = a.split_scratch; p.split_flags = a.split_flags;
   p.tile_k = a.tile_k; p.out_fp32 = a.out_fp32; p.atomic_out = a.atomic_out;
   p.dst_rows = (int)(a.dst_rows > 0 ? a.dst_rows : a.n_out);
   p.sched = sched_slot_of(s, dev);
@@ -1156,7 +1254,7 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
   }
-  const int64_t n_work = cdiv(a.n_out, kTileM) * cdiv(a.cout, cfg.n_tile);
+  const int64_t n_work = (a.items ? a.n_items : cdiv(a.n_out, kTileM)) * cdiv(a.cout, cfg.n_tile);
   const int64_t slots = (int64_t)cfg.ctas * sms;
   const int grid = (int)(n_work < slots ? n_work : slots);
   igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p, w_map);

@@ -327,6 +327,238 @@ down_stage3_rows_kernel(TableView t, const int4* __restrict__ coords, int64_t n,
   }
 }
 
+// ------------------------------------------------------------------ builds with device-side sizes
+// A "level record" (int32[16], device memory) describes the coordinates of one tensor stride when the host
+// does not know their number: [0] rows, [1..4] lower and [5..8] upper bound (b,x,y,z) of the key space of the
+// level's hash table, [9..12] the largest coordinate present.  The kernels below read sizes and bounds from
+// records, are launched for the largest size the caller allows, and never report a size to the host, so a
+// whole sequence of map builds and convolutions can be replayed (e.g. as a CUDA graph) for any input.
+enum { kRecRows = 0, kRecMin = 1, kRecMax = 5, kRecActMax = 9, kRecInts = 16 };
+
+__device__ __forceinline__ Bounds rec_bounds(const int* __restrict__ rec) {
+  Bounds b;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    b.mn[i] = rec[kRecMin + i];
+    b.mx[i] = rec[kRecMax + i];
+    b.sz[i] = b.mx[i] - b.mn[i] + 1;
+  }
+  return b;
+}
+__device__ __forceinline__ int64_t rec_rows(const int* __restrict__ rec, int64_t cap) {
+  return max((int64_t)0, min((int64_t)rec[kRecRows], cap));
+}
+__device__ __forceinline__ int floor_div(int a, int b) {   // b > 0
+  int q = a / b;
+  return (a % b != 0 && a < 0) ? q - 1 : q;
+}
+
+__global__ void subm_insert_fill_dyn_kernel(TableView t, const int4* __restrict__ coords, int64_t n_max,
+                                            const int* __restrict__ rec, int kvol, int to_insert,
+                                            int* __restrict__ map, int* status) {
+  const int64_t n = rec_rows(rec, n_max);
+  const int64_t rows_pad = (n + 127) / 128 * 128;
+  const int64_t row0 = (int64_t)blockIdx.x * kBlock;
+  if (row0 >= rows_pad) return;
+  const int64_t row = row0 + threadIdx.x;
+  if (to_insert && row < n) {
+    const Bounds b = rec_bounds(rec);
+    const int4 c = __ldg(&coords[row]);
+    const int64_t key = ravel4(b, c.x, c.y, c.z, c.w);
+    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+  }
+  const int64_t lo = row0 * kvol;
+  const int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kBlock) map[i] = -1;
+}
+
+// rows x offset lanes (blockDim = (lanes, rows per block)); odd kernel volume: lanes cover k < kvol / 2 and
+// write the mirrored entry as well; even: lanes cover every k.  Offset digits are precomputed on the host.
+struct SubmOffsets {
+  signed char d[3][32];
+};
+__global__ void __launch_bounds__(256)
+subm_query_dyn_kernel(TableView t, const int4* __restrict__ coords, int64_t n_max, const int* __restrict__ rec,
+                      int kvol, int odd, SubmOffsets off, int* __restrict__ map) {
+  const int64_t n = rec_rows(rec, n_max);
+  const int64_t row = blockIdx.x * (int64_t)blockDim.y + threadIdx.y;
+  if (row >= n) return;
+  const Bounds b = rec_bounds(rec);
+  const int4 c = __ldg(&coords[row]);
+  const int half = kvol / 2;
+  const int k_end = odd ? half : kvol;
+  if (odd && threadIdx.x == 0) map[row * kvol + half] = (int)row;
+  for (int k = threadIdx.x; k < k_end; k += blockDim.x) {
+    const int x = c.y + off.d[0][k], y = c.z + off.d[1][k], z = c.w + off.d[2][k];
+    if (!in_bounds_xyz(b, x, y, z)) continue;
+    const int64_t key = ravel4(b, c.x, x, y, z);
+    const int nbr = table_lookup(t, (unsigned long long)(key + 1)) - 1;
+    if (nbr >= 0) {
+      map[row * kvol + k] = nbr;
+      if (odd) map[(int64_t)nbr * kvol + (kvol - 1 - k)] = (int)row;
+    }
+  }
+}
+
+// Output record of a strided build from the input record: key space [0, (max + 2 pad - (k - 1)) // stride]
+// per axis (the reference's bound, torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:33-37);
+// rows and the largest output coordinate are filled in by the later kernels.  Extents beyond the caller's
+// static bound (which fixed the number of key bits that get sorted) set TSB_DEV_LIMIT in *status.
+__global__ void down_prepare_kernel(const int* __restrict__ rec_in, KernelGeom g, long long max_key_space,
+                                    int* __restrict__ rec_out, int* status) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  rec_out[kRecRows] = 0;
+  rec_out[kRecMin] = rec_in[kRecMin];          // batch index: unchanged
+  rec_out[kRecMax] = rec_in[kRecActMax];
+  long long space = (long long)(rec_out[kRecMax] - rec_out[kRecMin] + 1);
+  for (int i = 0; i < 3; ++i) {
+    rec_out[kRecMin + 1 + i] = 0;
+    const int mx = floor_div(rec_in[kRecActMax + 1 + i] + 2 * g.pd[i] - (g.ks[i] - 1), g.st[i]);
+    rec_out[kRecMax + 1 + i] = mx;
+    space *= (long long)max(mx + 1, 0);
+  }
+  for (int i = 0; i < 4; ++i) rec_out[kRecActMax + i] = INT_MIN;
+  for (int i = 13; i < kRecInts; ++i) rec_out[i] = 0;
+  if (space >= max_key_space && status) atomicOr(status, TSB_DEV_LIMIT);
+}
+
+__global__ void down_candidates_dyn_kernel(const int4* __restrict__ coords, int64_t n_max, const int* __restrict__ rec_in,
+                                           const int* __restrict__ rec_out, KernelGeom g, SlotGeom sg, int64_t sentinel,
+                                           int64_t* __restrict__ cand) {
+  const int64_t n = rec_rows(rec_in, n_max);
+  const Bounds b = rec_bounds(rec_out);
+  const bool empty = b.sz[0] < 1 || b.sz[1] < 1 || b.sz[2] < 1 || b.sz[3] < 1;
+  const int64_t total = n_max * (int64_t)sg.slots;
+  for (int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; tid < total;
+       tid += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = tid / sg.slots;
+    int j = (int)(tid - row * sg.slots);
+    int64_t key = sentinel;
+    if (row < n && !empty) {
+      const int4 c = __ldg(&coords[row]);
+      const int in[3] = {c.y, c.z, c.w};
+      int o[3];
+      bool ok = true;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int t = j % sg.per[i];
+        j /= sg.per[i];
+        const int base = in[i] + g.pd[i] - (g.ks[i] - 1);
+        const int d = pos_mod(-base, g.st[i]) + t * g.st[i];
+        ok = ok && (d < g.ks[i]);
+        o[i] = (base + d) / g.st[i];  // exact when ok
+      }
+      ok = ok && in_bounds_xyz(b, o[0], o[1], o[2]);
+      if (ok) key = ravel4(b, c.x, o[0], o[1], o[2]);
+    }
+    cand[tid] = key;
+  }
+}
+
+// rec_out[0] = number of outputs (unique keys minus the sentinel)
+__global__ void down_count_dyn_kernel(const int64_t* __restrict__ uniq, const int* __restrict__ n_selected,
+                                      int64_t sentinel, int64_t m_max, int* __restrict__ rec_out, int* status) {
+  const int ns = *n_selected;
+  int m = ns;
+  if (ns > 0 && uniq[ns - 1] == sentinel) m = ns - 1;
+  if (m > m_max) {
+    m = (int)m_max;
+    if (status) atomicOr(status, TSB_DEV_LIMIT);
+  }
+  rec_out[kRecRows] = m;
+}
+
+// unravel + insert the outputs, fill the map with -1 (block owns kBlock rows), and find the largest coordinate
+__global__ void down_insert_fill_dyn_kernel(TableView t, const int64_t* __restrict__ uniq, int64_t m_max,
+                                            int* __restrict__ rec_out, int kvol, int4* __restrict__ out_coords,
+                                            int* __restrict__ map, int* status) {
+  const int64_t m = rec_rows(rec_out, m_max);
+  const int64_t rows_pad = (m + 127) / 128 * 128;
+  const int64_t row0 = (int64_t)blockIdx.x * kBlock;
+  if (row0 >= rows_pad) return;
+  const int64_t row = row0 + threadIdx.x;
+  int mx[4] = {INT_MIN, INT_MIN, INT_MIN, INT_MIN};
+  if (row < m) {
+    const Bounds b = rec_bounds(rec_out);
+    const int64_t key = uniq[row];
+    int4 c;
+    unravel4(b, key, c.x, c.y, c.z, c.w);
+    out_coords[row] = c;
+    mx[0] = c.x; mx[1] = c.y; mx[2] = c.z; mx[3] = c.w;
+    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+  }
+#pragma unroll
+  for (int d = 0; d < 4; ++d) {
+    int v = mx[d];
+    for (int o = 16; o; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0 && v != INT_MIN) atomicMax(&rec_out[kRecActMax + d], v);
+  }
+  const int64_t lo = row0 * kvol;
+  const int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
+  for (int64_t i = lo + threadIdx.x; i < hi; i += kBlock) map[i] = -1;
+}
+
+// input rows x offset lanes: map[out][kvol-1-k] = in, and (optionally) the transposed map [in][kvol-1-k] = out
+__global__ void __launch_bounds__(256)
+down_stage3_dyn_kernel(TableView t, const int4* __restrict__ coords, int64_t n_max, const int* __restrict__ rec_in,
+                       int64_t m_max, const int* __restrict__ rec_out, KernelGeom g, DownOffsets off,
+                       int* __restrict__ map, int* __restrict__ map_t, int* status) {
+  const int64_t n = rec_rows(rec_in, n_max);
+  const int64_t row = blockIdx.x * (int64_t)blockDim.y + threadIdx.y;
+  const int64_t rows_pad_t = (n + 127) / 128 * 128;
+  if (row >= rows_pad_t) return;
+  if (row >= n) {   // padding rows of the transposed map
+    if (map_t) for (int k = threadIdx.x; k < g.kvol; k += blockDim.x) map_t[row * g.kvol + k] = -1;
+    return;
+  }
+  const int64_t m = rec_rows(rec_out, m_max);
+  const Bounds b = rec_bounds(rec_out);
+  const int4 c = __ldg(&coords[row]);
+  const int in[3] = {c.y, c.z, c.w};
+  for (int k = threadIdx.x; k < g.kvol; k += blockDim.x) {
+    int o[3];
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int v = in[i] + off.d[i][k];
+      if (off.shift[i] >= 0) {
+        ok = ok && ((v & ((1 << off.shift[i]) - 1)) == 0);
+        o[i] = v >> off.shift[i];
+      } else {
+        ok = ok && (v % g.st[i] == 0);
+        o[i] = v / g.st[i];
+      }
+    }
+    int orow = -1;
+    if (ok && in_bounds_xyz(b, o[0], o[1], o[2])) {
+      const int64_t key = ravel4(b, c.x, o[0], o[1], o[2]);
+      orow = table_lookup(t, (unsigned long long)(key + 1)) - 1;
+      if (orow >= 0 && orow < m) {
+        map[(int64_t)orow * g.kvol + (g.kvol - 1 - k)] = (int)row;
+      } else {
+        orow = -1;
+        if (status) atomicOr(status, TSB_DEV_BAD_INDEX);
+      }
+    }
+    if (map_t) map_t[row * g.kvol + (g.kvol - 1 - k)] = orow;
+  }
+}
+
+// level record of the finest level from the result of tsb_quantize_unique
+// ({voxels, min x,y,z, max x,y,z}), batch index `batch`; voxel coordinates must be >= 0
+__global__ void level0_record_kernel(const int* __restrict__ qresult, int batch, int* __restrict__ rec, int* status) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  rec[kRecRows] = qresult[0];
+  rec[kRecMin] = 0; rec[kRecMax] = batch; rec[kRecActMax] = batch;
+  for (int i = 0; i < 3; ++i) {
+    rec[kRecMin + 1 + i] = 0;
+    rec[kRecMax + 1 + i] = qresult[4 + i];
+    rec[kRecActMax + 1 + i] = qresult[4 + i];
+    if (qresult[0] > 0 && qresult[1 + i] < 0 && status) atomicOr(status, TSB_DEV_LIMIT);
+  }
+  for (int i = 13; i < kRecInts; ++i) rec[i] = 0;
+}
+
 // ------------------------------------------------------------------ transpose / bitmask / reorder
 __global__ void fill_i32_kernel(int* __restrict__ p, int64_t n, int v) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
@@ -439,6 +671,58 @@ reorder_cm_kernel(const int* __restrict__ map, const int* __restrict__ loc, int6
   if ((threadIdx.x & 31) == 0) s_mask[threadIdx.x >> 5] = mine;
   __syncthreads();
   if (threadIdx.x == 0) tile_mask[blockIdx.x] = s_mask[0] | s_mask[1] | s_mask[2] | s_mask[3];
+}
+
+// Work-item table of a map's tiles: a tile with more than `max_offsets` offsets becomes several consecutive
+// items ("parts") that each take an equal share of its offsets, so that no single item is much longer than
+// the others; every part of a split tile owns one slot of the convolution's fp32 scratch, and tiles are split
+// only while slots are left (at most max_slots, < 32768).  items[i] = {row tile, offset mask of the part,
+// part | parts << 8 | first slot of the tile << 16 (0 for a whole tile), 0}; *n_items = their number.
+// One block; tiles are taken in chunks of the block size with running prefixes.
+__global__ void __launch_bounds__(1024)
+build_items_kernel(const unsigned* __restrict__ tile_mask, int64_t valid_n, const int* __restrict__ valid_n_dev,
+                   int max_offsets, int max_slots, int4* __restrict__ items, int* __restrict__ n_items) {
+  typedef cub::BlockScan<int, 1024> Scan;
+  __shared__ typename Scan::TempStorage tmp;
+  __shared__ int s_items, s_slots;
+  if (valid_n_dev) valid_n = max((int64_t)0, min((int64_t)__ldg(valid_n_dev), valid_n));
+  const int tiles = (int)((valid_n + 127) / 128);
+  if (threadIdx.x == 0) { s_items = 0; s_slots = 0; }
+  __syncthreads();
+  for (int t0 = 0; t0 < tiles; t0 += 1024) {
+    const int t = t0 + threadIdx.x;
+    const unsigned m = t < tiles ? tile_mask[t] : 0u;
+    const int pc = __popc(m);
+    int parts = t < tiles ? max(1, (pc + max_offsets - 1) / max_offsets) : 0;
+    // slots: a tile is split only if its slots fit below max_slots
+    int slot_first, slot_total;
+    Scan(tmp).ExclusiveSum(parts > 1 ? parts : 0, slot_first, slot_total);
+    const int slot_base = s_slots;
+    __syncthreads();
+    const int slot0 = slot_base + slot_first;
+    if (parts > 1 && slot0 + parts > max_slots) parts = 1;
+    int first, total;
+    Scan(tmp).ExclusiveSum(parts, first, total);
+    const int base = s_items;
+    if (t < tiles) {
+      const int per = (pc + parts - 1) / parts;      // offsets per part (the last part may hold fewer)
+      unsigned rest = m;
+      for (int j = 0; j < parts; ++j) {
+        unsigned mj = 0;
+        for (int c = 0; c < per && rest; ++c) {
+          const unsigned low = rest & (0u - rest);
+          mj |= low;
+          rest ^= low;
+        }
+        if (parts == 1) mj = m;
+        items[base + first + j] = make_int4(t, (int)mj, parts > 1 ? (j | (parts << 8) | (slot0 << 16)) : 0, 0);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { s_items = base + total; s_slots = slot_base + slot_total; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *n_items = s_items;
 }
 
 // ------------------------------------------------------------------ pair lists
@@ -997,10 +1281,17 @@ size_t tsb_map_sorted_cm_workspace_bytes(int64_t rows) {
   return sort_cm_layout(rows).total;
 }
 
+int64_t tsb_map_items_max(int64_t rows, int32_t kvol, int32_t max_offsets) {
+  if (rows <= 0 || kvol < 1 || max_offsets < 1) return 0;
+  return cdiv(rows, 128) * cdiv(kvol, max_offsets);
+}
+
 int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n,
                       const int32_t* valid_n_dev, int32_t* reorder_loc, int32_t* map_cm, uint32_t* tile_mask,
-                      void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+                      int32_t max_offsets, int32_t max_slots, int32_t* items, int32_t* n_items, void* workspace,
+                      size_t workspace_bytes, tsb_stream_t stream) {
   if (rows < 0 || rows % 128 || kvol < 1 || kvol > 31 || valid_n < 0 || valid_n > rows) return TSB_ERR_BAD_ARG;
+  if (items && (!n_items || max_offsets < 1 || max_slots < 0 || ((uintptr_t)items & 15))) return TSB_ERR_BAD_ARG;
   if (rows == 0) return TSB_OK;
   if (rows > INT32_MAX) return TSB_ERR_LIMIT;
   if (!out_in_map || !reorder_loc || !map_cm || !tile_mask) return TSB_ERR_BAD_ARG;
@@ -1020,6 +1311,139 @@ int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int
   count_launch();
   reorder_cm_kernel<<<(unsigned)(rows / 128), 128, 0, s>>>(out_in_map, reorder_loc, rows, kvol, valid_n, valid_n_dev,
                                                           map_cm, tile_mask);
+  TSB_LAUNCH_CHECK();
+  if (items) {
+    build_items_kernel<<<1, 1024, 0, s>>>(tile_mask, valid_n, valid_n_dev, max_offsets,
+                                          max_slots > 32767 ? 32767 : max_slots, reinterpret_cast<int4*>(items), n_items);
+    TSB_LAUNCH_CHECK();
+  }
+  return TSB_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel-map builds whose sizes live in device memory (level records, see the kernels above).
+namespace {
+int fill_down_offsets(const KernelGeom& g, DownOffsets* off) {
+  if (g.kvol > kMaxStage3Offsets) return TSB_ERR_LIMIT;
+  for (int i = 0; i < 3; ++i) if (g.ks[i] > 64 || g.pd[i] < 0 || g.pd[i] > 63) return TSB_ERR_LIMIT;
+  for (int k = 0; k < g.kvol; ++k) {
+    int d[3];
+    if (g.odd) { d[0] = k % g.ks[0]; d[1] = (k / g.ks[0]) % g.ks[1]; d[2] = k / (g.ks[0] * g.ks[1]); }
+    else { d[2] = k % g.ks[2]; d[1] = (k / g.ks[2]) % g.ks[1]; d[0] = k / (g.ks[2] * g.ks[1]); }
+    for (int i = 0; i < 3; ++i) off->d[i][k] = (signed char)(g.pd[i] + d[i] - (g.ks[i] - 1));
+  }
+  for (int i = 0; i < 3; ++i) {
+    off->shift[i] = -1;
+    for (int sh = 0; sh < 16; ++sh) if (g.st[i] == (1 << sh)) off->shift[i] = sh;
+  }
+  return TSB_OK;
+}
+}  // namespace
+
+int tsb_level_record_from_quantize(const int32_t* quantize_result, int32_t batch, int32_t* rec, int32_t* dev_status,
+                                   tsb_stream_t stream) {
+  if (!quantize_result || !rec || batch < 0) return TSB_ERR_BAD_ARG;
+  level0_record_kernel<<<1, 32, 0, as_stream(stream)>>>(quantize_result, batch, rec, dev_status);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_kmap_subm_dyn(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n_max,
+                      const int32_t* rec, const int32_t* kernel_size, int32_t to_insert, int32_t* out_in_map,
+                      int32_t* dev_status, tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n_max < 0 || !rec || !kernel_size) return TSB_ERR_BAD_ARG;
+  if (n_max == 0) return TSB_OK;
+  if (!coords || !out_in_map) return TSB_ERR_BAD_ARG;
+  for (int i = 0; i < 3; ++i) if (kernel_size[i] < 1 || kernel_size[i] > 64) return TSB_ERR_BAD_ARG;
+  KernelGeom g = make_geom(kernel_size, nullptr, nullptr);
+  if (g.kvol > 32) return TSB_ERR_LIMIT;
+  if (capacity < 2 * n_max) return TSB_ERR_LIMIT;
+  TableView t = make_table(table_keys, table_vals, capacity);
+  cudaStream_t s = as_stream(stream);
+  const int64_t rows_pad = pad128(n_max);
+  const int4* c4 = reinterpret_cast<const int4*>(coords);
+  if (to_insert) TSB_CUDA_TRY(cudaMemsetAsync(table_keys, 0, (size_t)capacity * sizeof(int64_t), s));
+  subm_insert_fill_dyn_kernel<<<(int)cdiv(rows_pad, kBlock), kBlock, 0, s>>>(t, c4, n_max, rec, g.kvol, to_insert,
+                                                                            out_in_map, dev_status);
+  TSB_LAUNCH_CHECK();
+  SubmOffsets off;
+  for (int k = 0; k < g.kvol; ++k) {
+    int d[3];
+    if (g.odd) { d[0] = k % g.ks[0]; d[1] = (k / g.ks[0]) % g.ks[1]; d[2] = k / (g.ks[0] * g.ks[1]); }
+    else { d[2] = k % g.ks[2]; d[1] = (k / g.ks[2]) % g.ks[1]; d[0] = k / (g.ks[2] * g.ks[1]); }
+    // odd volumes are centred, even ones take the raw digits
+    for (int i = 0; i < 3; ++i) off.d[i][k] = (signed char)(g.odd ? d[i] - (g.ks[i] - 1) / 2 : d[i]);
+  }
+  const int k_end = g.odd ? g.kvol / 2 : g.kvol;
+  const int lanes = k_end <= 1 ? 1 : (k_end <= 8 ? 8 : 16), rows = 256 / lanes;
+  subm_query_dyn_kernel<<<(unsigned)cdiv(n_max, rows), dim3(lanes, rows), 0, s>>>(t, c4, n_max, rec, g.kvol, g.odd, off,
+                                                                                 out_in_map);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+size_t tsb_kmap_down_dyn_workspace_bytes(int64_t n_max, const int32_t* kernel_size, const int32_t* stride) {
+  int slots = tsb_kmap_down_slots(kernel_size, stride);
+  if (n_max <= 0 || slots <= 0) return 256;
+  DownWs w = down_ws_layout(n_max, slots);
+  return w.total + align_up((size_t)n_max * slots * 8, 256);   // + the unique keys
+}
+
+int tsb_kmap_down_dyn(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n_max,
+                      const int32_t* rec_in, const int32_t* kernel_size, const int32_t* stride, const int32_t* padding,
+                      int32_t key_bits, int64_t m_max, int32_t* out_coords, int32_t* out_in_map, int32_t* out_in_map_t,
+                      int32_t* rec_out, int32_t* dev_status, void* workspace, size_t workspace_bytes,
+                      tsb_stream_t stream) {
+  if (!table_keys || !table_vals || capacity <= 0 || n_max < 0 || m_max < 0 || !rec_in || !rec_out || !kernel_size ||
+      !stride || !padding || key_bits < 1 || key_bits > 62)
+    return TSB_ERR_BAD_ARG;
+  if (n_max == 0) return TSB_OK;
+  if (!coords || !out_coords || !out_in_map) return TSB_ERR_BAD_ARG;
+  const int slots = tsb_kmap_down_slots(kernel_size, stride);
+  if (slots <= 0) return TSB_ERR_BAD_ARG;
+  const int64_t items = n_max * (int64_t)slots;
+  if (items > (int64_t)INT32_MAX || m_max > items) return TSB_ERR_LIMIT;
+  if (capacity < 2 * m_max) return TSB_ERR_LIMIT;
+  DownWs w = down_ws_layout(n_max, slots);
+  if (!workspace || workspace_bytes < tsb_kmap_down_dyn_workspace_bytes(n_max, kernel_size, stride)) return TSB_ERR_WORKSPACE;
+  char* base = reinterpret_cast<char*>(workspace);
+  int64_t* cand = reinterpret_cast<int64_t*>(base + w.cand_off);
+  int64_t* sorted = reinterpret_cast<int64_t*>(base + w.sorted_off);
+  int* nsel = reinterpret_cast<int*>(base + w.nsel_off);
+  void* cub_ws = base + w.cub_off;
+  int64_t* uniq = reinterpret_cast<int64_t*>(base + w.total);
+  KernelGeom g = make_geom(kernel_size, stride, padding);
+  SlotGeom sg = make_slots(kernel_size, stride);
+  DownOffsets off;
+  {
+    int rc = fill_down_offsets(g, &off);
+    if (rc != TSB_OK) return rc;
+  }
+  cudaStream_t s = as_stream(stream);
+  // keys are sorted on key_bits bits: the key space must stay below 2^key_bits - 1, which is the sentinel
+  const int64_t sentinel = ((int64_t)1 << key_bits) - 1;
+  const int4* c4 = reinterpret_cast<const int4*>(coords);
+  TableView t = make_table(table_keys, table_vals, capacity);
+  TSB_CUDA_TRY(cudaMemsetAsync(table_keys, 0, (size_t)capacity * sizeof(int64_t), s));
+  down_prepare_kernel<<<1, 32, 0, s>>>(rec_in, g, (long long)sentinel, rec_out, dev_status);
+  TSB_LAUNCH_CHECK();
+  down_candidates_dyn_kernel<<<grid_for(items, kBlock, 32), kBlock, 0, s>>>(c4, n_max, rec_in, rec_out, g, sg, sentinel,
+                                                                           cand);
+  TSB_LAUNCH_CHECK();
+  size_t cb = w.cub_bytes;
+  TSB_CUDA_TRY(cub::DeviceRadixSort::SortKeys(cub_ws, cb, cand, sorted, items, 0, key_bits, s));
+  count_launch();
+  cb = w.cub_bytes;
+  TSB_CUDA_TRY(cub::DeviceSelect::Unique(cub_ws, cb, sorted, uniq, nsel, items, s));
+  count_launch();
+  down_count_dyn_kernel<<<1, 1, 0, s>>>(uniq, nsel, sentinel, m_max, rec_out, dev_status);
+  TSB_LAUNCH_CHECK();
+  down_insert_fill_dyn_kernel<<<(int)cdiv(pad128(m_max), kBlock), kBlock, 0, s>>>(
+      t, uniq, m_max, rec_out, g.kvol, reinterpret_cast<int4*>(out_coords), out_in_map, dev_status);
+  TSB_LAUNCH_CHECK();
+  const int lanes = g.kvol <= 8 ? 8 : 16, rows = 256 / lanes;
+  down_stage3_dyn_kernel<<<(unsigned)cdiv(pad128(n_max), rows), dim3(lanes, rows), 0, s>>>(
+      t, c4, n_max, rec_in, m_max, rec_out, g, off, out_in_map, out_in_map_t, dev_status);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }

@@ -94,6 +94,21 @@ __global__ void to_dense_kernel(const T* __restrict__ feats, const int4* __restr
   }
 }
 
+// One thread per voxel: batch column + voxel coordinates, and the features of the voxel's first point cast
+// to T and zero-padded to c_pad channels.  The voxel count is read from the quantisation result on the device.
+template <typename T>
+__global__ void voxel_inputs_kernel(const float* __restrict__ points, int c_in, const int64_t* __restrict__ first,
+                                    const int* __restrict__ uniq, const int* __restrict__ qresult, int batch,
+                                    int64_t n_max, int4* __restrict__ coords, T* __restrict__ feats, int c_pad) {
+  const int64_t nv = max((int64_t)0, min((int64_t)qresult[0], n_max));
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nv; i += (int64_t)gridDim.x * blockDim.x) {
+    coords[i] = make_int4(batch, uniq[i * 3], uniq[i * 3 + 1], uniq[i * 3 + 2]);
+    const float* src = points + first[i] * c_in;
+    T* dst = feats + i * c_pad;
+    for (int c = 0; c < c_pad; ++c) dst[c] = from_f32<T>(c < c_in ? __ldg(&src[c]) : 0.f);
+  }
+}
+
 }  // namespace
 }  // namespace tsb
 
@@ -169,6 +184,35 @@ int tsb_to_dense_fwd(const void* feats, const int32_t* coords, int64_t n, int32_
     case TSB_F16: to_dense_kernel<__half><<<grid, kBlock, 0, st>>>((const __half*)feats, c4, n, c, range[0], range[1], range[2], range[3], (__half*)out); break;
     case TSB_BF16: to_dense_kernel<__nv_bfloat16><<<grid, kBlock, 0, st>>>((const __nv_bfloat16*)feats, c4, n, c, range[0], range[1], range[2], range[3], (__nv_bfloat16*)out); break;
     default: return TSB_ERR_UNSUPPORTED;
+  }
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_voxel_inputs(const float* points, int32_t c_in, const int64_t* first_index, const int32_t* uniq_coords,
+                     const int32_t* quantize_result, int32_t batch, int64_t n_max, int32_t* coords, void* feats,
+                     int32_t c_pad, int32_t dtype, tsb_stream_t stream) {
+  if (n_max < 0 || c_in < 1 || c_pad < c_in || batch < 0 || !quantize_result) return TSB_ERR_BAD_ARG;
+  if (n_max == 0) return TSB_OK;
+  if (!points || !first_index || !uniq_coords || !coords || !feats) return TSB_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  const int grid = grid_for(n_max, kBlock);
+  int4* c4 = reinterpret_cast<int4*>(coords);
+  switch (dtype) {
+    case TSB_F32:
+      voxel_inputs_kernel<float><<<grid, kBlock, 0, s>>>(points, c_in, first_index, uniq_coords, quantize_result, batch,
+                                                         n_max, c4, (float*)feats, c_pad);
+      break;
+    case TSB_F16:
+      voxel_inputs_kernel<__half><<<grid, kBlock, 0, s>>>(points, c_in, first_index, uniq_coords, quantize_result, batch,
+                                                          n_max, c4, (__half*)feats, c_pad);
+      break;
+    case TSB_BF16:
+      voxel_inputs_kernel<__nv_bfloat16><<<grid, kBlock, 0, s>>>(points, c_in, first_index, uniq_coords, quantize_result,
+                                                                 batch, n_max, c4, (__nv_bfloat16*)feats, c_pad);
+      break;
+    default:
+      return TSB_ERR_UNSUPPORTED;
   }
   TSB_LAUNCH_CHECK();
   return TSB_OK;

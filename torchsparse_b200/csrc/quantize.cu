@@ -124,7 +124,14 @@ size_t tsb_quantize_workspace_bytes(int64_t n) {
 int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const double* voxel, int32_t* q_all,
                         int32_t* uniq_coords, int64_t* first_index, int64_t* inverse, int32_t* result,
                         void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
-  if (n < 0 || !voxel || !result) return TSB_ERR_BAD_ARG;
+  return tsb_quantize_unique_bits(xyz, xyz_is_f64, n, voxel, 64, q_all, uniq_coords, first_index, inverse, result,
+                                  workspace, workspace_bytes, stream);
+}
+
+int tsb_quantize_unique_bits(const void* xyz, int32_t xyz_is_f64, int64_t n, const double* voxel, int32_t key_bits,
+                             int32_t* q_all, int32_t* uniq_coords, int64_t* first_index, int64_t* inverse,
+                             int32_t* result, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (n < 0 || !voxel || !result || key_bits < 1 || key_bits > 64) return TSB_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
   if (n == 0) {
     TSB_CUDA_TRY(cudaMemsetAsync(result, 0, 8 * sizeof(int32_t), s));
@@ -155,7 +162,7 @@ int tsb_quantize_unique(const void* xyz, int32_t xyz_is_f64, int64_t n, const do
   size_t cb = w.cub_bytes;
   // radix sort is stable: inside a run the original indices stay ascending, so the head of a
   // run is the first occurrence
-  TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairs(base + w.cub, cb, keys_in, keys_out, idx_in, idx_out, n, 0, 64, s));
+  TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairs(base + w.cub, cb, keys_in, keys_out, idx_in, idx_out, n, 0, key_bits, s));
   count_launch();
   int* flags = idx_in;  // idx_in is free after the sort
   head_flags_kernel<<<grid, kBlock, 0, s>>>(keys_out, n, flags);

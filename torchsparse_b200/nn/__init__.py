@@ -1,3 +1,4 @@
 from . import functional
 from .modules import *
 from .fused import *
+from .static_engine import *

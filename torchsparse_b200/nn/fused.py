@@ -97,6 +97,9 @@ class FusedConv(nn.Module):
         return self.kernel if self.kernel.dim() == 3 else self.kernel.view(1, *self.kernel.shape)
 
     def forward(self, x: SparseTensor, residual: Optional[torch.Tensor] = None) -> SparseTensor:
+        if getattr(x, "dyn", None) is not None:      # a tensor of the static (CUDA graph) engine
+            from .static_engine import dyn_conv
+            return dyn_conv(self, x, residual)
         y = self._forward_planned(x, residual)
         if y is not None:
             return y
@@ -163,9 +166,7 @@ class FusedConv(nn.Module):
             art = kmap.get("_cm" + sfx)
             if art is None:
                 art = kmap["_cm" + sfx] = backend.sorted_cm_artefacts_cuda(out_in_map, n_out)
-            map_cm, loc, tile_mask = art
-            out = backend.igemm_plan_launch(plan, feats, map_cm, n_out, residual, self.relu, loc, tile_mask, feats2,
-                                            (1, map_cm.shape[1]))
+            out = backend.igemm_plan_launch(plan, feats, None, n_out, residual, self.relu, in_feats2=feats2, smap=art)
         else:
             out = backend.igemm_plan_launch(plan, feats, out_in_map, n_out, residual, self.relu, in_feats2=feats2)
         caches.cmaps.setdefault(out_stride, (out_coords, out_range))
@@ -280,6 +281,8 @@ class InferenceEngine(nn.Module):
 
         was_lazy, operators.lazy = operators.lazy, True
         try:
+            if getattr(x, "dyn", None) is not None:
+                return self.model(x)
             if self._plan is None:
                 _conv_impl.strided_build_log = []
                 try:

@@ -17,8 +17,12 @@ def cat(inputs: List[SparseTensor]) -> SparseTensor:
     (torchsparse/operators.py:12-16); used by the U-Net skip connections."""
     first = inputs[0]
     if lazy and len(inputs) == 2 and not torch.is_grad_enabled():
-        return CatSparseTensor([inp.feats for inp in inputs], first.coords, first.stride, first.spatial_range,
-                               first._caches)
+        out = CatSparseTensor([inp.feats for inp in inputs], first.coords, first.stride, first.spatial_range,
+                              first._caches)
+        dyn = getattr(first, "dyn", None)      # a tensor of the static engine: sizes live in device memory
+        if dyn is not None:
+            out.dyn = dyn
+        return out
     feats = torch.cat([inp.feats for inp in inputs], dim=1)
     output = SparseTensor(coords=first.coords, feats=feats, stride=first.stride, spatial_range=first.spatial_range)
     output._caches = first._caches
