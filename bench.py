@@ -1,24 +1,32 @@
 #!/usr/bin/env python
 """Benchmark of the sparse-convolution hot path on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4]
 
-Workload (BASELINE config 2, the one the metric is quoted on): a MinkUNet-class residual sparse
-U-Net (the reference's own SparseResUNet42, width 1.0, plus a 19-way linear head) in fp16 inference
-on one synthetic LiDAR-like scan per GPU per step (64 rings x 2048 azimuths, 120k rays + 20% box
-points, 0.05 m voxels).  One step = voxelisation (sparse_quantize on the GPU) -> 9 kernel maps ->
-42 sparse convolutions (+ BN/ReLU/skip) -> logits.  With N GPUs every rank runs its own scan (weak
-scaling, scans are independent) and the logits are all-gathered over NCCL once per step.
+Workload c2 (BASELINE config 2, the one the metric is quoted on): a MinkUNet-class residual sparse U-Net (the
+reference's own SparseResUNet42, width 1.0, plus a 19-way linear head) in fp16 inference on one synthetic
+LiDAR-like scan per GPU per step (64 rings x 2048 azimuths, 120k rays + 20% box points, 0.05 m voxels).
+One step = voxelisation (sparse_quantize on the GPU) -> 9 kernel maps -> 42 sparse convolutions + 7 pointwise
+ones (BatchNorm / ReLU / skip folded in) -> logits.  The whole step is one CUDA graph (StaticEngine: every
+size lives in device memory), replayed per scan; consecutive scans alternate between two engines on two
+streams.  With N GPUs every rank runs its own scans (weak scaling, scans are independent) and the logits are
+all-gathered over NCCL once per step.
 
-Prints ONE JSON line (rank 0).  Three passes over the same K steps, each after W warm-up steps:
-`value` = scans/s with the points already resident in HBM and `e2e` = the same through the public API
-from pinned host memory (H2D of the points and D2H of the logits inside the timed region) — both with
-alternate scans issued by two host threads on two streams, each thread waiting for its scan before it
-starts its next, one event pair around the K steps and a 256 MiB L2 flush before every step inside it;
-then a serial pass (one stream, one thread) with an event pair around every conv launch, from which
-`roofline` describes the dominant kernel (the implicit-GEMM conv forward of the layer shape with the
-largest total time).  `cpu_baseline` = the reference project's own CPU convolution (oracle/_ref) driving
-the same network on a spatial crop of the same scan, scaled by voxel count.
+Prints ONE JSON line (rank 0):
+  value     scans/s with the points already resident in HBM: median over `--repeats` timed passes of K steps
+            (one CUDA-event pair around each pass, barrier + synchronize on both sides, max over ranks)
+  e2e       the same from pinned host memory: H2D copy of the points and D2H copy of the logits + their row
+            count inside the timed region
+  roofline  over ALL convolution launches of a step, timed one by one (event pair per launch) in a serial
+            eager pass over the same scans: useful FLOPs, algorithmic bytes, sum of the per-launch roofline
+            minima; `dominant` = the layer shape with the largest total time; `levels` = per resolution level
+  step_roofline  roofline-minimum time of a whole step / measured time of a step
+  kmap_build_ms  the kernel-map builds of one scan (5 submanifold, 4 strided + transposed) and the row-sorted
+            copies, timed in isolation
+  batch32   BASELINE config 3 as written: 32 scans, 32 / N per rank collated into one batch, one gather
+  cpu_baseline   the reference project's own CPU convolution (oracle/_ref) driving the same network on the full
+            scan, at one thread and at all host threads
+`--workload c4` runs BASELINE config 4 (SparseResNet21D, batch 16 sharded 16 / N per rank) and prints its line.
 """
 from __future__ import annotations
 
@@ -29,7 +37,6 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 import numpy as np
@@ -42,21 +49,28 @@ if ROOT not in sys.path:
 VOXEL = 0.05
 NUM_CLASSES = 19
 METRIC = "minkunet_fp16_scans_per_sec"
-SCAN_POOL = 4          # distinct scans rotated through the timed steps
-MAX_VOXELS = 144_000   # upper bound of the voxels of one scan (every point its own voxel): row bound of the output gather
+SCAN_POOL = 4           # distinct scans rotated through the timed steps
+MAX_POINTS = 144_000    # points of one scan (120k rays + 20 % box points): bound of every level's rows
+# voxel grid bound at 0.05 m: 2 x 80 m range in x and y, 25 m in z (sensor range of the generator, with margin)
+MAX_EXTENT = (3328, 3328, 512)
 L2_FLUSH_BYTES = 256 << 20
+C4_VOXEL = (0.1, 0.1, 0.2)
+C4_RANGE = (1080, 1080, 40)
 
 
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return {"hbm_gbs": p["hbm_gbs"], "tensor_tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
-                "source": "measured (MEASURED_PEAKS.json; sustained 16-bit GEMM, copy bandwidth)"}
-    return {"hbm_gbs": 6650.0, "tensor_tflops": 1400.0, "source": "fallback (6.65 TB/s, 1.4 PFLOP/s sustained)"}
+        return {"hbm_gbs": p["hbm_gbs"], "tensor_tflops": p["bf16_tflops"],
+                "tensor_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured (MEASURED_PEAKS.json: copy bandwidth; 16-bit GEMM burst figure for kernels "
+                          "timed one by one, sustained figure for the whole step)"}
+    return {"hbm_gbs": 6650.0, "tensor_tflops": 1590.0, "tensor_tflops_sustained": 1400.0,
+            "source": "fallback (6.65 TB/s, 1.59 PFLOP/s burst, 1.4 sustained)"}
 
 
-# --------------------------------------------------------------------------------------- model
+# --------------------------------------------------------------------------------------- models
 class SegNet(torch.nn.Module):
     """SparseResUNet42 + linear classifier on the finest decoder output."""
 
@@ -71,9 +85,21 @@ class SegNet(torch.nn.Module):
         return self.head(self.backbone(x)[-1].feats)
 
 
-def make_model(device=None, half=True, engine=True, sort_max_stride=0):
+class DetNet(torch.nn.Module):
+    """SparseResNet21D (BASELINE config 4): the output is the coarsest stage's feature matrix."""
+
+    def __init__(self):
+        super().__init__()
+        from torchsparse_b200.backbones import SparseResNet21D
+
+        self.backbone = SparseResNet21D(in_channels=5)
+
+    def forward(self, x):
+        return self.backbone(x)[-1].feats
+
+
+def init_model(model):
     torch.manual_seed(0)
-    model = SegNet()
     for m in model.modules():   # random Kaiming-style init, non-trivial BN statistics
         if hasattr(m, "kernel"):
             fan_in = m.kernel.shape[-2] * (m.kernel.shape[0] if m.kernel.dim() == 3 else 1)
@@ -83,14 +109,19 @@ def make_model(device=None, half=True, engine=True, sort_max_stride=0):
             torch.nn.init.uniform_(m.bias, -0.1, 0.1)
             m.running_mean.uniform_(-0.1, 0.1)
             m.running_var.uniform_(0.8, 1.2)
-    model.eval()
+    return model.eval()
+
+
+def make_model(device=None, half=True, engine=True, sorted_maps=True, kind="seg"):
+    torch.manual_seed(0)
+    model = init_model(SegNet() if kind == "seg" else DetNet())
     if device is not None:
         model = model.to(device)
         if half:
             model = model.half()
         if engine:
             from torchsparse_b200.nn import InferenceEngine
-            model.backbone = InferenceEngine(model.backbone, sort_max_stride=sort_max_stride)
+            model.backbone = InferenceEngine(model.backbone, sorted_maps=sorted_maps)
     return model
 
 
@@ -102,17 +133,51 @@ def scan_points(seed: int) -> np.ndarray:
     return pts
 
 
+def c4_points(seed: int) -> np.ndarray:
+    """Multi-sweep detection scan cropped to the config-4 region, shifted so that the region starts at 0."""
+    from torchsparse_b200.utils.synthetic import multisweep_scan
+
+    pts = multisweep_scan(seed)
+    pts[:, 0] += 54.0
+    pts[:, 1] += 54.0
+    pts[:, 2] += 5.0
+    return pts
+
+
 # --------------------------------------------------------------------------------------- our arm
-def forward_scan(model, pts_dev: torch.Tensor):
-    """points [Np,4] on the device -> logits [Nv, 19] (the public-API path a user runs)."""
-    import torchsparse_b200 as ts
+def scan_tensor(pts_dev: torch.Tensor, voxel=VOXEL, pad_to: int = 8):
+    """points [Np, C] on the device -> (voxel coords int32 [Nv,3], features fp16 [Nv, C padded], max coords)."""
     from torchsparse_b200.utils import sparse_quantize
 
-    vox, idx, (vmin, vmax) = sparse_quantize(pts_dev[:, :3], VOXEL, return_index=True, return_bounds=True)
-    coords = torch.nn.functional.pad(vox, (1, 0))              # batch index 0 in front
+    vox, idx, (vmin, vmax) = sparse_quantize(pts_dev[:, :3], voxel, return_index=True, return_bounds=True)
     feats = torch.index_select(pts_dev, 0, idx).half()
+    if feats.shape[1] % pad_to:
+        feats = torch.nn.functional.pad(feats, (0, (-feats.shape[1]) % pad_to))
+    return vox, feats, vmax
+
+
+def forward_scan(model, pts_dev: torch.Tensor):
+    """One scan through the eager engine (the public-API path without graph capture) -> logits [Nv, 19]."""
+    import torchsparse_b200 as ts
+
+    vox, feats, vmax = scan_tensor(pts_dev)
+    coords = torch.nn.functional.pad(vox, (1, 0))              # batch index 0 in front
     bounds = ((0, 0, 0, 0), (0,) + tuple(vmax))                # the points were shifted to start at the origin
     return model(ts.SparseTensor(feats, coords, coord_bounds=bounds))
+
+
+def forward_batch(model, scans_dev, voxel, spatial_range):
+    """A batch of scans collated into one tensor with a common spatial range -> the model's output matrix."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.utils.collate import sparse_collate
+
+    items = []
+    for p in scans_dev:
+        vox, feats, _ = scan_tensor(p, voxel)
+        items.append(ts.SparseTensor(feats, vox))
+    x = sparse_collate(items)
+    x.spatial_range = (len(scans_dev),) + tuple(spatial_range)
+    return model(x)
 
 
 class ClockSampler:
@@ -125,10 +190,9 @@ class ClockSampler:
     def __init__(self, gpu_index: int):
         self.path = tempfile.mktemp(suffix=".csv")
         self.proc = None
-        self.idx = gpu_index
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "250", "-i", str(gpu_index)],
+                                          "-lms", "200", "-i", str(gpu_index)],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -165,29 +229,49 @@ class ClockSampler:
 
 def conv_algorithmic(dims, pairs: int):
     """Algorithmic work of one conv launch: useful FLOPs and bytes (features, weights, map once)."""
-    n_in, n_out, kvol, cin, cout, code, _ = dims
+    n_in, n_out, kvol, cin, cout, code = dims[:6]
     e = 4 if code == 0 else 2
     flops = 2.0 * pairs * cin * cout
     m_pad = (n_out + 127) // 128 * 128
-    byts = n_in * cin * e + n_out * cout * e + kvol * cin * cout * e + m_pad * kvol * 4
+    byts = n_in * cin * e + n_out * cout * e + kvol * cin * cout * e + (m_pad * kvol * 4 if kvol > 1 else 0)
     return flops, byts
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one conv launch from the ncu captures
-# summarised under profiles/ (igemm_umma_256x256_31k_rows.md, igemm_umma_96x96_110k_rows.md):
-# (kvol, cin, cout) -> (bytes, output rows of the captured launch).  Feature, output and map bytes grow with
-# the rows and the weights are small beside them, so the figure is scaled by the row count.
-NCU_TRAFFIC = {(27, 256, 256): (23.3e6, 31788), (27, 96, 96): (33.6e6, 110000)}
-
-
-def map_counts(dims):
-    """(valid (row, offset) pairs, issued (128-row tile, offset) blocks) of one conv launch's map."""
-    m = dims[6]
-    valid = m[: dims[1]] >= 0
-    pairs = int(valid.sum().item())
-    rows = (m.shape[0] // 128) * 128
-    blocks = int((m[:rows].reshape(-1, 128, m.shape[1]) >= 0).any(1).sum().item()) if rows else 0
+def launch_counts(dims):
+    """(valid (row, offset) pairs, issued (128-row tile, offset) blocks) of one observed conv launch."""
+    n_out, kvol, m, tmask = dims[1], dims[2], dims[6], dims[7]
+    if m is None:                       # 1x1x1: every row reads itself
+        return n_out, (n_out + 127) // 128
+    if tmask is not None:
+        tm = tmask.cpu().numpy().astype(np.uint32)
+        blocks = int(sum(bin(int(v)).count("1") for v in tm))
+    else:
+        blocks = ((n_out + 127) // 128) * kvol
+    pairs = int((m >= 0).sum().item())      # pad rows / columns hold -1 in either layout
     return pairs, blocks
+
+
+def make_engines(model, device, n_eng, sorted_maps=True):
+    from torchsparse_b200.nn import StaticEngine
+
+    head = model.head
+    return [StaticEngine(model.backbone, lambda outs: head(outs[-1].feats), max_points=MAX_POINTS, point_channels=4,
+                         voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device, sorted_maps=sorted_maps).capture()
+            for _ in range(n_eng)]
+
+
+def event_ms(fn, stream, reps, barrier):
+    """`reps` calls of fn(), each bracketed by a barrier + synchronize and one CUDA-event pair on `stream`."""
+    out = []
+    for _ in range(reps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        fn(e0)
+        e1.record(stream)
+        barrier()
+        out.append(e0.elapsed_time(e1))
+    return out
 
 
 def run_ours(args, rank: int, world: int, device: torch.device):
@@ -196,250 +280,225 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     from torchsparse_b200 import backend
     from torchsparse_b200.sharding import PaddedGather
 
-    from torchsparse_b200.nn import functional as F
-    F.set_conv_mode(args.conv_mode)
-    model = make_model(device, engine=not args.unfused, sort_max_stride=args.sort_max_stride)
+    model = make_model(device, sorted_maps=not args.unsorted)
     scans = [scan_points(1000 * rank + i) for i in range(SCAN_POOL)]
     host = [torch.from_numpy(s).pin_memory() for s in scans]
     resident = [h.to(device) for h in host]
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
-    stream = torch.cuda.current_stream()
+    main = torch.cuda.current_stream()
+    n_eng = max(1, args.streams)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step(i, e2e: bool, gather_inline: bool = True):
-        h = host[i % SCAN_POOL]
-        pts = h.to(device, non_blocking=True) if e2e else resident[i % SCAN_POOL]
-        logits = forward_scan(model, pts)      # scans are independent: the only exchange is the gather of outputs
-        if world > 1 and gather_inline:
-            gather(logits)
-        out = logits.cpu() if e2e else logits
-        return logits, h.numel() * h.element_size(), (logits.numel() * logits.element_size() if e2e else 0)
-
-    # useful-FLOP bookkeeping: the number of valid (row, offset) pairs of every conv launch of every
-    # pooled scan, taken in an untimed pass (the timed pass must not keep maps alive or sync)
-    pairs_of_scan = []
-    with torch.no_grad():
-        for i in range(SCAN_POOL):
-            plist = []
-            backend.set_launch_observer(lambda name, dims, e0, e1, plist=plist: plist.append(map_counts(dims)))
-            forward_scan(model, resident[i])
-            backend.set_launch_observer(None)
-            pairs_of_scan.append(plist)
-    torch.cuda.synchronize()
-
-    records = []
-    cur = threading.local()     # (step, launch index within the step) of the scan the calling thread is issuing
-
-    def observer(name, dims, ev0, ev1):
-        records.append((cur.step, cur.k, dims[:6], ev0, ev1))
-        cur.k += 1
-
-    n_streams = max(1, args.streams)
-    # host threads that issue scans (each on its own stream); collectives of a sharded run stay on one thread
-    n_threads = max(1, min(args.host_threads, n_streams))
-    side = [torch.cuda.Stream(device) for _ in range(n_streams)] if n_streams > 1 else [stream]
+    engines = make_engines(model, device, n_eng, not args.unsorted)
+    # kernels of this library per replay: a further capture (weights are packed by now) runs the forward twice
+    launches0 = backend.launch_count()
+    make_engines(model, device, 1, not args.unsorted)
+    launches_per_step = (backend.launch_count() - launches0) // 2
     comm_stream = torch.cuda.Stream(device) if world > 1 else None
-    gather = PaddedGather(MAX_VOXELS, 19, torch.float16, device) if world > 1 else None   # used on comm_stream only
+    gather = PaddedGather(MAX_POINTS, NUM_CLASSES, torch.float16, device) if world > 1 else None
+    pinned_out = [torch.empty((MAX_POINTS, NUM_CLASSES), dtype=torch.float16).pin_memory() for _ in range(n_eng)]
+    pinned_rec = [torch.empty(16, dtype=torch.int32).pin_memory() for _ in range(n_eng)]
 
-    host_ms = {"issue": float("nan")}   # host wall time per step spent issuing the step (no final sync)
-
-    def pipelined(n_steps: int, e2e: bool, n_streams: int, n_threads: int):
-        """n_steps scans, consecutive ones on alternating streams, issued by n_threads host threads (thread t
-        issues scans t, t + T, ... : the Python part of one scan overlaps the native part -- launch calls,
-        allocator, readbacks -- of another).  In a sharded run the issuing threads hand each step's logits to
-        the calling (main) thread, which alone talks to NCCL, in step order on every rank, on its own stream."""
-        io_bytes = {}
-        outputs = [None] * n_steps
-        ready = [threading.Event() for _ in range(n_steps)]
-        t0 = time.perf_counter()
-
-        def issue(first, stride):
-            torch.cuda.set_device(device)    # the current device is per thread (a new thread starts on 0)
-            with torch.no_grad():
-                for i in range(first, n_steps, stride):
-                    with torch.cuda.stream(side[i % n_streams]):
-                        flush.fill_(i & 0xFF)
-                        cur.step, cur.k = i, 0
-                        logits, bi, bo = step(i, e2e, gather_inline=False)
-                        io_bytes["h2d"], io_bytes["d2h"] = bi, bo
-                        if not e2e:
-                            # an issuing thread keeps one scan in flight: it waits for its scan's result (as
-                            # the e2e pass does by reading the logits back) before it starts its next one
-                            torch.cuda.current_stream().synchronize()
-                        if world > 1:
-                            produced = torch.cuda.Event()
-                            produced.record()
-                            outputs[i] = (logits, produced)
-                    ready[i].set()
-                    if os.environ.get("TSB_BENCH_DEBUG"):
-                        sys.stderr.write(f"[dbg rank {rank}] issued step {i} at {(time.perf_counter() - t0) * 1e3:.2f} ms\n")
-
-        def gather_outputs():
-            for i in range(n_steps):
-                if not ready[i].wait(timeout=300) or outputs[i] is None:
-                    raise RuntimeError(f"step {i} produced no output (an issuing thread failed)")
-                logits, produced = outputs[i]
-                outputs[i] = None
-                comm_stream.wait_event(produced)
+    def steps(e0, n_steps, e2e):
+        """n_steps scans, consecutive ones on alternating engines / streams; every stream first waits for e0."""
+        for eng in engines:
+            eng.stream.wait_event(e0)
+        if comm_stream is not None:
+            comm_stream.wait_event(e0)
+        for i in range(n_steps):
+            eng = engines[i % n_eng]
+            with torch.cuda.stream(eng.stream):
+                flush.fill_(i & 0xFF)                      # L2 flush between steps, inside the timed region
+            eng.load(host[i % SCAN_POOL] if e2e else resident[i % SCAN_POOL])
+            out, rec = eng.run()
+            if world > 1:
+                done = torch.cuda.Event()
+                done.record(eng.stream)
+                comm_stream.wait_event(done)
                 with torch.cuda.stream(comm_stream):
-                    logits.record_stream(comm_stream)
-                    gather(logits)
+                    gather(out, rec[:1])                   # rows padded to the bound, the count travels with them
+                    back = torch.cuda.Event()
+                    back.record(comm_stream)
+                eng.stream.wait_event(back)                # the engine's output buffer is free again
+            if e2e:
+                with torch.cuda.stream(eng.stream):
+                    pinned_out[i % n_eng].copy_(out, non_blocking=True)
+                    pinned_rec[i % n_eng].copy_(rec, non_blocking=True)
+        for s in [e.stream for e in engines] + ([comm_stream] if comm_stream is not None else []):
+            done = torch.cuda.Event()
+            done.record(s)
+            main.wait_event(done)
 
-        if n_threads == 1:
-            issue(0, 1)
-            if world > 1:
-                gather_outputs()
-        else:
-            workers = [threading.Thread(target=issue, args=(t, n_threads)) for t in range(n_threads)]
-            for wk in workers:
-                wk.start()
-            if world > 1:
-                gather_outputs()
-            for wk in workers:
-                wk.join()
-        return io_bytes.get("h2d", 0), io_bytes.get("d2h", 0)
-
-    def timed(e2e: bool, observe: bool, n_streams: int = n_streams, n_threads: int = n_threads):
+    def timed(e2e: bool, reps: int):
         with torch.no_grad():
-            if n_streams == 1:
-                for i in range(args.warmup):
-                    step(i, e2e)
-            else:
-                # warm-up through the same threads-and-streams path as the timed steps (a thread's first
-                # library calls create per-thread handles)
-                pipelined(args.warmup, e2e, n_streams, n_threads)
             barrier()
-            evs = []
-            launches0 = backend.launch_count()
-            backend.set_launch_observer(observer if observe else None)
-            h2d = d2h = 0
+            e = torch.cuda.Event(); e.record(main)
+            steps(e, args.warmup, e2e)
             t_host0 = time.perf_counter()
-            if n_streams == 1:
-                for i in range(args.steps):
-                    flush.fill_(i & 0xFF)       # evict L2 between steps (outside the timed events)
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record(stream)
-                    cur.step, cur.k = i, 0
-                    _, bi, bo = step(i, e2e)
-                    e1.record(stream)
-                    h2d, d2h = bi, bo
-                    evs.append((e0, e1))
-            else:
-                # the whole K-step region is timed with one event pair and the L2 flushes are INSIDE it
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for s in side:
-                    s.wait_event(e0)
-                h2d, d2h = pipelined(args.steps, e2e, n_streams, n_threads)
-                for s in side + ([comm_stream] if world > 1 else []):
-                    done = torch.cuda.Event()
-                    done.record(s)
-                    stream.wait_event(done)
-                e1.record(stream)
-                evs.append((e0, e1))
-            host_ms["issue"] = (time.perf_counter() - t_host0) * 1e3 / max(1, args.steps)
-            backend.set_launch_observer(None)
-            barrier()
-            launches = backend.launch_count() - launches0
-        total_ms = sum(a.elapsed_time(b) for a, b in evs)
-        t = torch.tensor([total_ms], dtype=torch.float64, device=device)
+            ms = event_ms(lambda e0: steps(e0, args.steps, e2e), main, reps, barrier)
+            host_ms = (time.perf_counter() - t_host0) * 1e3 / max(1, reps * args.steps)
+        t = torch.tensor(ms, dtype=torch.float64, device=device)
         if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), launches, h2d, d2h
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)       # per pass: the slowest rank
+        return [float(v) for v in t.tolist()], host_ms
 
     sampler = ClockSampler(device.index or 0) if rank == 0 else None
-    ms_total, launches, _, _ = timed(False, False)
-    host_issue_ms = host_ms["issue"]
-    e2e_ms, h2d, d2h = float("nan"), 0, 0
+    passes, host_wall_ms = timed(False, args.repeats)
+    e2e_passes = []
     if not args.no_e2e:
-        e2e_ms, _, h2d, d2h = timed(True, False)
+        e2e_passes, _ = timed(True, args.repeats)
     clocks = sampler.stop() if sampler else None     # sampled over both timed passes
-    # per-launch durations for the roofline: the same K steps once more, issued serially on one stream
-    # with an event pair around every convolution launch (under concurrent streams an event pair would
-    # also time the other stream's kernels)
-    observed_ms, _, _, _ = timed(False, True, 1, 1)
+    for eng in engines:
+        eng.check()
+
+    # ---- batch of 32 scans sharded over the ranks (BASELINE config 3 as written)
+    batch32 = None
+    if not args.no_batch32:
+        batch32 = run_batch(args, rank, world, device, model, barrier, kind="seg", total=32)
+
+    # ---- per-launch durations: the same scans through the eager engine, serially on one stream, with an event
+    # pair around every convolution launch
+    records = []
+    cur = {"step": 0, "k": 0}
+
+    def observer(name, dims, ev0, ev1):
+        records.append((cur["step"], cur["k"], dims, ev0, ev1))
+        cur["k"] += 1
+
+    with torch.no_grad():
+        for i in range(3):
+            forward_scan(model, resident[i % SCAN_POOL])
+        torch.cuda.synchronize()
+        backend.set_launch_observer(observer)
+        serial_ms = 0.0
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            cur["step"], cur["k"] = i, 0
+            forward_scan(model, resident[i % SCAN_POOL])
+            e1.record()
+            torch.cuda.synchronize()
+            serial_ms += e0.elapsed_time(e1)
+        backend.set_launch_observer(None)
+    kmap_ms = None if args.no_kmap else kmap_build_ms(model, resident[0], device)
 
     if rank != 0:
         return None
-    scans_per_step = world
-    value = scans_per_step * args.steps / (ms_total / 1e3)
-    e2e_value = scans_per_step * args.steps / (e2e_ms / 1e3)
-
-    # ---- roofline of the dominant kernel (largest total time among conv layer shapes)
     pk = peaks()
-    by_shape = {}
-    for step_i, k_i, key, ev0, ev1 in records:
-        pairs, blocks = pairs_of_scan[step_i % SCAN_POOL][k_i]
-        d = by_shape.setdefault(key, {"ms": 0.0, "n": 0, "flops": 0.0, "bytes": 0.0, "issued": 0.0})
-        fl, by = conv_algorithmic(key + (None,), pairs)
-        d["ms"] += ev0.elapsed_time(ev1); d["n"] += 1; d["flops"] += fl; d["bytes"] += by
-        d["issued"] += 2.0 * blocks * 128 * key[3] * key[4]     # what the tensor pipe executes (padded tiles)
-    roof = None
-    conv_ms = sum(d["ms"] for d in by_shape.values())
-    if args.dump_layers:
-        for key, d in sorted(by_shape.items(), key=lambda kv: -kv[1]["ms"]):
-            sys.stderr.write(f"layer n_in={key[0]:7d} n_out={key[1]:7d} kvol={key[2]:2d} {key[3]:3d}->{key[4]:3d}  "
-                             f"launches/step={d['n'] / args.steps:4.1f} avg_us={d['ms'] * 1e3 / d['n']:8.1f} "
-                             f"total_us/step={d['ms'] * 1e3 / args.steps:8.1f} useful_TF={d['flops'] / d['ms'] / 1e9:7.1f} "
-                             f"GB/s={d['bytes'] / d['ms'] / 1e6:7.1f}\n")
-    if by_shape:
-        key, d = max(by_shape.items(), key=lambda kv: kv[1]["ms"])
+    med = statistics.median(passes)
+    value = world * args.steps / (med / 1e3)
+    e2e_med = statistics.median(e2e_passes) if e2e_passes else float("nan")
+    e2e_value = world * args.steps / (e2e_med / 1e3) if e2e_passes else float("nan")
+    ms_per_step = med / args.steps
+
+    # ---- roofline over all conv launches
+    counts_cache = {}
+    agg = {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "issued": 0.0, "roof_ms": 0.0, "n": 0}
+    by_shape, by_level = {}, {}
+    for step_i, k_i, dims, ev0, ev1 in records:
+        key_c = (step_i % SCAN_POOL, k_i)
+        if key_c not in counts_cache:
+            counts_cache[key_c] = launch_counts(dims)
+        pairs, blocks = counts_cache[key_c]
+        ms = ev0.elapsed_time(ev1)
+        fl, by = conv_algorithmic(dims, pairs)
+        issued = 2.0 * blocks * 128 * dims[3] * dims[4]
+        roof = max(fl / (pk["tensor_tflops"] * 1e12), by / (pk["hbm_gbs"] * 1e9)) * 1e3
+        shape = (dims[2], dims[3], dims[4], round(dims[1], -4))      # kvol, cin, cout, rows to the nearest 10k
+        level = f"rows~{round(dims[1], -4) // 1000}k"
+        for d in (agg, by_shape.setdefault(shape, dict.fromkeys(agg, 0.0)), by_level.setdefault(level, dict.fromkeys(agg, 0.0))):
+            d["ms"] += ms; d["flops"] += fl; d["bytes"] += by; d["issued"] += issued; d["roof_ms"] += roof; d["n"] += 1
+
+    def summary(d):
         sec = d["ms"] / 1e3
-        tf, gb = d["flops"] / sec / 1e12, d["bytes"] / sec / 1e9
-        t_tensor, t_hbm = d["flops"] / (pk["tensor_tflops"] * 1e12), d["bytes"] / (pk["hbm_gbs"] * 1e9)
+        return {"launches_per_step": round(d["n"] / args.steps, 2), "ms_per_step": round(d["ms"] / args.steps, 4),
+                "useful_tflops": round(d["flops"] / sec / 1e12, 2), "issued_tflops": round(d["issued"] / sec / 1e12, 2),
+                "algorithmic_gbs": round(d["bytes"] / sec / 1e9, 1),
+                "roofline_min_ms_per_step": round(d["roof_ms"] / args.steps, 4),
+                "frac_of_roofline": round(d["roof_ms"] / d["ms"], 4)}
+
+    roof = None
+    if agg["n"]:
+        sec = agg["ms"] / 1e3
+        tf, gb = agg["flops"] / sec / 1e12, agg["bytes"] / sec / 1e9
+        t_tensor, t_hbm = agg["flops"] / (pk["tensor_tflops"] * 1e12), agg["bytes"] / (pk["hbm_gbs"] * 1e9)
         if t_tensor >= t_hbm:
-            roof = {"bound": "tensor", "achieved": round(tf, 3), "peak": pk["tensor_tflops"], "unit": "TFLOP/s",
+            roof = {"bound": "tensor", "achieved": round(tf, 2), "peak": pk["tensor_tflops"], "unit": "TFLOP/s",
                     "frac": round(tf / pk["tensor_tflops"], 4)}
         else:
             roof = {"bound": "hbm", "achieved": round(gb, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": round(gb / pk["hbm_gbs"], 4)}
-        cap = NCU_TRAFFIC.get((key[2], key[3], key[4]))
-        roof.update({"traffic": None if cap is None else round(cap[0] * key[1] / cap[1]),
-                     "traffic_source": None if cap is None else
-                     f"ncu capture of the same kernel on {cap[1]} rows (profiles/), scaled by rows; bytes per launch",
-                     "kernel": "igemm conv forward",
-                     "layer": {"n_in": key[0], "n_out": key[1], "kvol": key[2], "cin": key[3], "cout": key[4]},
-                     "launches": d["n"], "avg_us": round(d["ms"] * 1e3 / d["n"], 2),
-                     "useful_flops_per_launch": d["flops"] / d["n"], "algorithmic_bytes_per_launch": d["bytes"] / d["n"],
-                     "issued_flops_per_launch": d["issued"] / d["n"],
-                     "issued_tflops": round(d["issued"] / sec / 1e12, 2),
-                     "issued_frac_of_peak": round(d["issued"] / sec / 1e12 / pk["tensor_tflops"], 4),
-                     "note": "achieved/frac count useful FLOPs (2 * valid pairs * Cin * Cout); issued_* count the "
-                             "128-row blocks the tensor pipe executes, zero rows of absent neighbours included",
-                     "share_of_step": round(d["ms"] / observed_ms, 4),
-                     "all_conv_share_of_step": round(conv_ms / observed_ms, 4),
-                     "measured_in": "a serial pass over the same steps (one stream, one host thread, an event "
-                                    f"pair around every conv launch): {observed_ms / args.steps:.3f} ms per step",
-                     "peak_source": pk["source"]})
+        dom_key, dom = max(by_shape.items(), key=lambda kv: kv[1]["ms"])
+        roof.update({
+            "traffic": None,
+            "kernel": "igemm_umma_kernel (implicit-GEMM conv forward), all launches of a step",
+            "scope": summary(agg),
+            "note": "achieved / frac: useful FLOPs (2 * valid pairs * Cin * Cout) or algorithmic bytes (features, "
+                    "weights, map once) of all conv launches over the sum of their durations; issued_* counts the "
+                    "128-row blocks the tensor pipe executes, zero rows included; frac_of_roofline = sum over "
+                    "launches of max(bytes / HBM peak, FLOPs / tensor peak) over the measured time",
+            "dominant": dict(summary(dom), layer={"kvol": dom_key[0], "cin": dom_key[1], "cout": dom_key[2],
+                                                  "rows_about": dom_key[3]}),
+            "levels": {k: summary(v) for k, v in sorted(by_level.items())},
+            "measured_in": f"a serial eager pass over the same scans (one stream, an event pair around every conv "
+                           f"launch): {serial_ms / args.steps:.3f} ms per step",
+            "peak_source": pk["source"]})
+    # roofline-minimum time of a whole step: convs as above + the kernel-map bytes + quantisation bytes
+    step_roof = None
+    if agg["n"]:
+        n_vox = int(forward_voxels(scans[0]))
+        kmap_bytes = 0.0
+        rows = n_vox
+        for lvl in range(5):      # rough level sizes: each stride-2 level keeps the measured share of its rows
+            kmap_bytes += rows * 16 * 2 + rows * 2 * 12 + rows * 27 * 4 + 13 * rows * 8
+            if lvl < 4:
+                kmap_bytes += rows * 16 + 4 * rows * 8 + rows * 8 * 4 * 2
+            rows = int(rows * 0.72)
+        quant_bytes = MAX_POINTS * (12 + 12 + 8 + 8 + 8)
+        min_ms = agg["roof_ms"] / args.steps + (kmap_bytes + quant_bytes) / (pk["hbm_gbs"] * 1e9) * 1e3
+        step_roof = {"roofline_min_ms": round(min_ms, 4), "measured_ms": round(ms_per_step, 4),
+                     "frac": round(min_ms / ms_per_step, 4),
+                     "parts_ms": {"convs": round(agg["roof_ms"] / args.steps, 4),
+                                  "kernel_maps_and_quantize": round((kmap_bytes + quant_bytes) / (pk["hbm_gbs"] * 1e9) * 1e3, 4)}}
 
     out = {
         "metric": METRIC, "value": round(value, 3), "unit": "scans/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "BASELINE config 2: SparseResUNet42 (MinkUNet-class, cr=1.0) + 19-class head, fp16 "
                                "inference, one synthetic 64-ring LiDAR scan (144k points, 0.05 m voxels) per GPU per step",
-                   "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": scans_per_step,
-                   "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written between steps"
-                         + (" (inside the timed region)" if n_streams > 1 else " (outside the timed events)")
-                         + f"; {SCAN_POOL} scans rotated",
-                   "streams": n_streams, "host_threads": n_threads,
-                   "conv_mode": args.conv_mode, "fused_inference_engine": not args.unfused,
-                   "sort_max_stride": args.sort_max_stride,
+                   "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": world,
+                   "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written before every step (inside the timed region); "
+                         f"{SCAN_POOL} scans rotated",
+                   "engine": "one CUDA graph per scan (sizes in device memory), row-sorted column-major kernel maps"
+                             if not args.unsorted else "one CUDA graph per scan, kernel maps as built",
+                   "streams": n_eng,
                    "parallelism": (f"scan-sharded x{world}, NCCL all-gather of the logits of every step"
                                    if world > 1 else "single GPU")},
-        "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(d2h)},
-        "gpu_launches": int(launches),
-        "host_issue_ms_per_step": round(host_issue_ms, 4),
+        "timing": {"passes": len(passes), "steps_per_pass": args.steps,
+                   "ms_per_step_min": round(min(passes) / args.steps, 4),
+                   "ms_per_step_max": round(max(passes) / args.steps, 4),
+                   "timed_seconds": round(sum(passes) / 1e3, 3),
+                   "host_ms_per_step": round(host_wall_ms, 4)},
+        "e2e": {"value": round(e2e_value, 3), "unit": "scans/s", "h2d_bytes_per_step": int(host[0].numel() * 4),
+                "d2h_bytes_per_step": int(MAX_POINTS * NUM_CLASSES * 2 + 64),
+                "ms_per_step_min": round(min(e2e_passes) / args.steps, 4) if e2e_passes else None,
+                "ms_per_step_max": round(max(e2e_passes) / args.steps, 4) if e2e_passes else None},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "gpu_launches_per_step": int(launches_per_step),
         "clocks": clocks,
         "roofline": roof,
+        "step_roofline": step_roof,
+        "kmap_build_ms": kmap_ms,
+        "batch32": batch32,
     }
     if world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline(budget_s=20.0)
+        out["cpu_baseline"] = cpu_baseline()
     return out
 
 
@@ -448,21 +507,136 @@ def forward_voxels(pts: np.ndarray) -> int:
     return len(np.unique((q[:, 0] * 100003 + q[:, 1]) * 100003 + q[:, 2]))
 
 
+def kmap_build_ms(model, pts_dev, device):
+    """The kernel maps of one scan built in isolation through the size-in-device-memory builders (the ones the
+    graph replays): per map the build and, separately, its row-sorted column-major copy.  Median of 5, events on
+    the launching stream, L2 flushed before each."""
+    from torchsparse_b200.nn import static_engine as se
+    from torchsparse_b200.nn.static_engine import StaticEngine
+
+    eng = StaticEngine(model.backbone, lambda outs: outs[-1].feats, max_points=MAX_POINTS, point_channels=4,
+                       voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    result = {}
+
+    class Stop(Exception):
+        pass
+
+    def front(post):
+        eng.post = post
+        eng.points.copy_(pts_dev)
+        return eng._forward()
+
+    times = {}
+
+    def timed(name, fn):
+        flush.fill_(1)
+        torch.cuda._sleep(300000)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); r = fn(); e1.record()
+        torch.cuda.synchronize()
+        times.setdefault(name, []).append(e0.elapsed_time(e1))
+        return r
+
+    class Probe(torch.nn.Module):
+        def forward(self, x):
+            for lvl in range(5):
+                km = timed(f"subm_k3_level{lvl}", lambda: se._subm_map(x, (3, 3, 3)))
+                timed(f"sorted_copy_subm_level{lvl}", lambda: se._sorted(km, "", x.dyn))
+                if lvl == 4:
+                    break
+                kd = timed(f"strided_k2s2_level{lvl}_with_transposed", lambda: se._down_map(x, (2, 2, 2), (2, 2, 2), (0, 0, 0)))
+                timed(f"sorted_copy_strided_level{lvl}", lambda: se._sorted(kd, "", kd["dyn_out"]))
+                timed(f"sorted_copy_transposed_level{lvl}", lambda: se._sorted(kd, "_t", x.dyn))
+                x = se._out_tensor(x.feats, kd["coords"], tuple(2 * s for s in x.stride), kd["dyn_out"], x._caches)
+            return [x]
+
+    probe = Probe()
+    eng.model = probe
+    with torch.no_grad():
+        for _ in range(6):
+            front(lambda outs: outs[-1].feats)
+    med = {k: round(statistics.median(v[1:]), 4) for k, v in times.items()}
+    total_build = sum(v for k, v in med.items() if not k.startswith("sorted_copy"))
+    total_sorted = sum(v for k, v in med.items() if k.startswith("sorted_copy"))
+    return {"maps_total": round(total_build, 4), "sorted_copies_total": round(total_sorted, 4), "per_map": med,
+            "note": "5 submanifold k3 maps + 4 strided k2 s2 maps (each with its transposed map) of one scan; "
+                    "sizes stay on the device, no host read; median of 5 isolated builds, host launch cost hidden "
+                    "behind a spin kernel"}
+
+
+def run_batch(args, rank, world, device, model, barrier, kind, total):
+    """`total` scans sharded total / world per rank, each rank's shard collated into ONE batch with a common
+    spatial range and run through the eager engine, outputs gathered once (NCCL).  Median of 5 passes; one event
+    pair around quantisation + collation + forward + gather, max over ranks."""
+    import torch.distributed as dist
+    from torchsparse_b200.sharding import shard_range, gather_rows_padded
+
+    lo, hi = shard_range(total, world, rank)
+    if kind == "seg":
+        pts = [torch.from_numpy(scan_points(5000 + i)).to(device) for i in range(lo, hi)]
+        voxel, srange = VOXEL, MAX_EXTENT
+    else:
+        pts = [torch.from_numpy(c4_points(7000 + i)).to(device) for i in range(lo, hi)]
+        voxel, srange = C4_VOXEL, C4_RANGE
+    rows_bound = 2 * sum(p.shape[0] for p in pts)       # voxels of any level of the shard (k3 s2 can add rows)
+    if world > 1:
+        t = torch.tensor([rows_bound], dtype=torch.int64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rows_bound = int(t.item())
+    times = []
+    out = None
+    with torch.no_grad():
+        for i in range(7):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = forward_batch(model, pts, voxel, srange)
+            if world > 1:
+                gather_rows_padded(out, rows_bound)
+            e1.record()
+            barrier()
+            if i >= 2:
+                times.append(e0.elapsed_time(e1))
+    t = torch.tensor(times, dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = statistics.median([float(v) for v in t.tolist()])
+    return {"scans": total, "scans_per_rank": hi - lo, "ms_per_batch": round(ms, 3),
+            "value": round(total / (ms / 1e3), 3), "unit": "scans/s", "scaling": "strong",
+            "output_rows_this_rank": int(out.shape[0]),
+            "note": "eager engine (one collated batch per rank, common spatial range), quantisation of every scan, "
+                    "forward and the one output gather inside the timed region; median of 5"}
+
+
+def run_c4(args, rank, world, device):
+    """BASELINE config 4: SparseResNet21D, fp16, batch 16 of multi-sweep scans, 16 / N per rank."""
+    import torch.distributed as dist
+    import torchsparse_b200  # noqa: F401
+
+    model = make_model(device, kind="det")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(device.index or 0) if rank == 0 else None
+    b = run_batch(args, rank, world, device, model, barrier, kind="det", total=16)
+    clocks = sampler.stop() if sampler else None
+    if rank != 0:
+        return None
+    return {"metric": "sparseresnet21d_fp16_scans_per_sec", "value": b["value"], "unit": "scans/s", "n_gpus": world,
+            "steps": 5, "warmup": 2, "ms_per_step": b["ms_per_batch"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "BASELINE config 4: SparseResNet21D detection backbone, fp16, batch 16 of synthetic "
+                                   "10-sweep scans (region 108 x 108 x 8 m, voxel 0.1 x 0.1 x 0.2 m, 5 input channels), "
+                                   f"{b['scans_per_rank']} scans per rank, a step = the whole batch",
+                       "parallelism": f"scan-sharded x{world}" if world > 1 else "single GPU"},
+            "detail": b, "clocks": clocks}
+
+
 # --------------------------------------------------------------------------------------- CPU arm
-def _crop(pts: np.ndarray, n_target: int):
-    """Spatial crop around the sensor holding about n_target voxels; returns (coords, feats, n_vox, n_full)."""
-    from oracle import kmap_oracle as ko
-
-    vox, idx = ko.sparse_quantize(pts[:, :3], VOXEL, return_index=True)
-    n_full = vox.shape[0]
-    centre = np.median(vox, axis=0)
-    d = np.abs(vox - centre).max(axis=1)
-    order = np.argsort(d, kind="stable")
-    keep = np.sort(order[: min(n_target, n_full)])
-    coords = np.concatenate([np.zeros((len(keep), 1), np.int32), vox[keep]], 1).astype(np.int32)
-    return coords, pts[idx[keep]], len(keep), n_full
-
-
 def cpu_forward_seconds(model, coords, feats, threads):
     from oracle import net_cpu
 
@@ -471,105 +645,140 @@ def cpu_forward_seconds(model, coords, feats, threads):
     return time.perf_counter() - t0
 
 
-def cpu_baseline(budget_s: float = 20.0, steps: int = 1, warmup: int = 0):
-    """The network on the host cores through the reference's own CPU convolution (oracle/_ref),
-    on a crop of the scan sized for about `budget_s` seconds per pass; scans/s scaled by voxel count."""
+def cpu_scan():
+    from oracle import kmap_oracle as ko
+
+    pts = scan_points(0)
+    vox, idx = ko.sparse_quantize(pts[:, :3], VOXEL, return_index=True)
+    coords = np.concatenate([np.zeros((len(vox), 1), np.int32), vox], 1).astype(np.int32)
+    return coords, pts[idx]
+
+
+def cpu_baseline(passes_one: int = 1, with_all_threads: bool = True):
+    """The network on the host cores through the reference's own CPU convolution (oracle/_ref) on the FULL scan:
+    one thread (its OpenMP loops fork per row, so more threads make it slower) and all host threads."""
     from oracle import net_cpu
 
-    threads = net_cpu.host_threads()
     kind = "reference" if net_cpu.reference_conv_module() is not None else "port"
     model = make_model(None)
-    pts = scan_points(0)
-    c, f, n, n_full = _crop(pts, 8000)
-    cpu_forward_seconds(model, c, f, threads)            # warm caches / thread pools
-    probe = cpu_forward_seconds(model, c, f, threads)
-    n_target = int(max(3000, min(n_full, 0.7 * n * budget_s / max(probe, 1e-3))))
-    c, f, n, n_full = _crop(pts, n_target)
-    for _ in range(warmup):
-        cpu_forward_seconds(model, c, f, threads)
-    times = [cpu_forward_seconds(model, c, f, threads) for _ in range(max(steps, 1))]
-    per_pass = sum(times) / len(times)
-    value = 1.0 / (per_pass * n_full / n)
-    return {"value": round(value, 5), "unit": "scans/s", "cores": threads, "kind": kind,
-            "sample": f"full network forward (fp32) on a {n}-voxel crop of the {n_full}-voxel scan, "
-                      f"{per_pass:.2f} s per pass, scaled by voxel count",
-            "seconds_per_pass": round(per_pass, 3), "crop_voxels": n, "scan_voxels": n_full}
+    coords, feats = cpu_scan()
+    n = coords.shape[0]
+    all_threads = net_cpu.host_threads()
+    small = coords[:2000]
+    cpu_forward_seconds(model, small, feats[:2000], 1)        # warm caches / thread pools
+    one = [cpu_forward_seconds(model, coords, feats, 1) for _ in range(max(passes_one, 1))]
+    t_one = statistics.median(one)
+    res = {"value": round(1.0 / t_one, 5), "unit": "scans/s", "cores": 1, "kind": kind,
+           "sample": f"full network forward (fp32) on the full {n}-voxel scan, {t_one:.2f} s per pass at 1 thread",
+           "seconds_per_pass": round(t_one, 3), "scan_voxels": n,
+           "one_thread": {"seconds_per_pass": round(t_one, 3), "scans_per_sec": round(1.0 / t_one, 5)}}
+    if with_all_threads and all_threads > 1:
+        t_all = cpu_forward_seconds(model, coords, feats, all_threads)
+        res["all_threads"] = {"threads": all_threads, "seconds_per_pass": round(t_all, 3),
+                              "scans_per_sec": round(1.0 / t_all, 5)}
+        if t_all < t_one:
+            res.update({"value": round(1.0 / t_all, 5), "cores": all_threads, "seconds_per_pass": round(t_all, 3)})
+        res["sample"] += f", {t_all:.2f} s at {all_threads} threads; value = the faster of the two"
+    return res
 
 
 def run_reference(args):
-    total_budget = 150.0
-    per_step = max(2.0, total_budget / max(args.steps + args.warmup, 1))
-    b = cpu_baseline(budget_s=per_step, steps=args.steps, warmup=args.warmup)
+    """The reference's CPU path on the same workload: every step is one full-scan forward at the faster thread
+    setting; the number of timed steps is cut so that the run ends within a few minutes."""
+    from oracle import net_cpu
+
+    first = cpu_baseline(1, True)
+    threads = first["cores"]
+    per = first["seconds_per_pass"]
+    budget = 150.0
+    n_steps = int(max(1, min(args.steps, budget / max(per, 1e-3))))
+    model = make_model(None)
+    coords, feats = cpu_scan()
+    for _ in range(min(args.warmup, 1)):
+        cpu_forward_seconds(model, coords, feats, threads)
+    times = [cpu_forward_seconds(model, coords, feats, threads) for _ in range(n_steps)]
+    sec = statistics.median(times)
+    first.update({"value": round(1.0 / sec, 5), "seconds_per_pass": round(sec, 3),
+                  "sample": first["sample"] + f"; {n_steps} timed full-scan passes at {threads} thread(s)"})
     return {
-        "impl": "reference", "metric": METRIC, "value": b["value"], "unit": "scans/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(b["seconds_per_pass"] * 1e3, 2),
+        "impl": "reference", "metric": METRIC, "value": first["value"], "unit": "scans/s", "n_gpus": args.gpus,
+        "steps": n_steps, "warmup": min(args.warmup, 1), "ms_per_step": round(sec * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "BASELINE config 2 network on the host CPU through the reference's CPU convolution "
-                               "(fp32 gather-matmul-scatter; the reference has no fp16 / implicit-GEMM CPU path)"},
-        "cpu_baseline": b,
-        "e2e": {"value": b["value"], "unit": "scans/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                               "(fp32 gather-matmul-scatter; the reference has no fp16 / implicit-GEMM CPU path), "
+                               "full scan"},
+        "cpu_baseline": first,
+        "e2e": {"value": first["value"], "unit": "scans/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
 
 
+# --------------------------------------------------------------------------------------- single layers / maps
 def run_layer(args, device):
     """Single sparse Conv3d layer (BASELINE config 5 cell): --layer N,Cin,Cout,kernel,stride,occupancy
-    [--dataflow ImplicitGEMM|GatherScatter|FetchOnDemand] [--dtype f16|bf16|f32|tf32] [--sorted].
+    [--dataflow ImplicitGEMM|GatherScatter|FetchOnDemand] [--dtype f16|bf16|f32|tf32] [--sorted] [--transposed].
     Prints one JSON line with time, useful TFLOP/s and algorithmic GB/s of the conv launch."""
     import torchsparse_b200 as ts
-    from torchsparse_b200 import backend
+    from torchsparse_b200 import backend, backends
     from torchsparse_b200.nn import functional as F
     from torchsparse_b200.utils.synthetic import uniform_voxels
 
     n, cin, cout, ks, st = [int(v) for v in args.layer.split(",")[:5]]
     occ = float(args.layer.split(",")[5]) if len(args.layer.split(",")) > 5 else 0.05
     dtype = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32, "tf32": torch.float32}[args.dtype]
-    from torchsparse_b200 import backends
     backends.allow_tf32 = args.dtype == "tf32"     # "f32" = exact fp32 arithmetic on the CUDA cores
     coords_np, side = uniform_voxels(0, n, occ)
     coords = torch.from_numpy(coords_np).to(device)
     g = torch.Generator(device=device).manual_seed(0)
-    feats = torch.randn(n, cin, device=device, generator=g).to(dtype)
     kvol = ks ** 3
     w = (torch.randn(kvol, cin, cout, device=device, generator=g) * (2.0 / (kvol * cin)) ** 0.5).to(dtype)
     cfg = F.conv_config.get_default_conv_config()
     cfg.dataflow = getattr(F.Dataflow, args.dataflow)
     cfg.ifsort = bool(args.sorted)
     pad = (ks - 1) // 2 if (ks % 2 == 1 and st == 1) else 0
-    x = ts.SparseTensor(feats, coords)
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    t0.record(); y = F.conv3d(x, w, ks, None, st, pad, config=cfg); t1.record()
+    x = ts.SparseTensor(torch.randn(n, cin, device=device, generator=g).to(dtype), coords)
+    if args.transposed:
+        # the strided conv first (it builds the map), then the transposed conv back to the input coordinates
+        mid = F.conv3d(x, w, ks, None, st, pad, config=cfg)
+        wt = (torch.randn(kvol, cout, cin, device=device, generator=g) * (2.0 / (kvol * cout)) ** 0.5).to(dtype)
+        run = lambda: F.conv3d(mid, wt, ks, None, st, pad, config=cfg, transposed=True)
+    else:
+        run = lambda: F.conv3d(x, w, ks, None, st, pad, config=cfg)
+    run()
     torch.cuda.synchronize()
-    first_ms = t0.elapsed_time(t1)          # includes the kernel-map build
     kmap = x._caches.kmaps[((1, 1, 1), (ks,) * 3, (st,) * 3, (1, 1, 1))]
-    n_out = kmap["sizes"][1]
-    pairs = int((kmap["out_in_map"][:n_out] >= 0).sum().item())
+    n_out = kmap["sizes"][0] if args.transposed else kmap["sizes"][1]
+    n_in = kmap["sizes"][1] if args.transposed else n
+    pairs = int((kmap["out_in_map"][:kmap["sizes"][1]] >= 0).sum().item())
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     times = []
     with torch.no_grad():
         for i in range(args.warmup + args.steps):
             flush.fill_(i & 0xFF)
+            torch.cuda._sleep(300000)          # the host finishes queueing behind this spin
             e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-            e0.record(); F.conv3d(x, w, ks, None, st, pad, config=cfg); e1.record()
+            e0.record(); run(); e1.record()
             torch.cuda.synchronize()
             if i >= args.warmup:
                 times.append(e0.elapsed_time(e1))
     ms = statistics.median(times)
     code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
-    fl, by = conv_algorithmic((n, n_out, kvol, cin, cout, code, None), pairs)
+    ci, co = (cout, cin) if args.transposed else (cin, cout)
+    fl, by = conv_algorithmic((n_in, n_out, kvol, ci, co, code), pairs)
     pk = peaks()
     return {"metric": "sparse_conv3d_layer_ms", "value": round(ms, 4), "unit": "ms", "higher_is_better": False,
-            "config": {"workload": f"single Conv3d N={n} {cin}->{cout} k{ks} s{st} occupancy {occ} (grid side {side})",
+            "config": {"workload": f"single Conv3d N={n} {cin}->{cout} k{ks} s{st}{' transposed' if args.transposed else ''} "
+                                   f"occupancy {occ} (grid side {side})",
                        "dataflow": args.dataflow, "sorted": bool(args.sorted), "dtype": args.dtype},
             "n_out": n_out, "pairs": pairs, "neighbours_per_row": round(pairs / max(n_out, 1), 2),
             "useful_tflops": round(fl / ms / 1e9, 2), "algorithmic_gbs": round(by / ms / 1e6, 1),
             "frac_tensor_peak": round(fl / ms / 1e9 / pk["tensor_tflops"], 4),
-            "frac_hbm_peak": round(by / ms / 1e6 / pk["hbm_gbs"], 4),
-            "first_call_ms_incl_kmap": round(first_ms, 3), "steps": args.steps, "warmup": args.warmup}
+            "frac_hbm_peak": round(by / ms / 1e6 / pk["hbm_gbs"], 4), "steps": args.steps, "warmup": args.warmup}
 
 
 def run_kmap(args, device):
-    """Kernel-map build timing (--kmap N,kernel,stride[,occupancy|lidar]): median ms of a cold build (caches
-    cleared every iteration, as torchsparse/utils/tune.py:67-71 does), algorithmic bytes and GB/s."""
+    """Kernel-map build timing (--kmap N,kernel,stride[,occupancy|lidar]): median ms of a cold build through the
+    eager builders (caches cleared every iteration, as torchsparse/utils/tune.py:67-71 does; includes the one
+    size readback of a strided build), algorithmic bytes and GB/s."""
     from torchsparse_b200.nn import functional as F
     from torchsparse_b200.utils.synthetic import uniform_voxels
 
@@ -622,23 +831,21 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
+    ap.add_argument("--repeats", type=int, default=15, help="timed passes of --steps steps each (the median is reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
-    ap.add_argument("--dump-layers", action="store_true", help="per-layer-shape conv timings to stderr")
+    ap.add_argument("--no-batch32", action="store_true", help="skip the 32-scan batch (profiling runs)")
+    ap.add_argument("--no-kmap", action="store_true", help="skip the isolated kernel-map timings")
     ap.add_argument("--layer", default=None, help="N,Cin,Cout,kernel,stride[,occupancy]: single-layer mode")
     ap.add_argument("--kmap", default=None, help="N,kernel,stride[,occupancy|lidar]: kernel-map build timing")
     ap.add_argument("--dataflow", default="ImplicitGEMM")
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
+    ap.add_argument("--transposed", action="store_true")
     ap.add_argument("--streams", type=int, default=2,
-                    help="CUDA streams the scans of consecutive steps alternate between (1 = strictly serial steps)")
-    ap.add_argument("--host-threads", type=int, default=2,
-                    help="host threads issuing scans, each on its own stream (<= --streams)")
-    ap.add_argument("--unfused", action="store_true", help="run the module graph as written (no InferenceEngine)")
-    ap.add_argument("--sort-max-stride", type=int, default=0,
-                    help="row-sorted kernel maps for convolutions at tensor strides <= this value (0 = none)")
-    ap.add_argument("--conv-mode", type=int, default=0, choices=[0, 1, 2],
-                    help="0 unsorted, 1 row-sorted maps, 2 sorted with 3 mask splits (F.set_conv_mode)")
+                    help="engines (each with its own stream and graph) that consecutive scans alternate between")
+    ap.add_argument("--unsorted", action="store_true", help="run on the kernel maps as built (no row-sorted copies)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -663,7 +870,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     try:
-        out = run_ours(args, rank, world, device)
+        out = run_c4(args, rank, world, device) if args.workload == "c4" else run_ours(args, rank, world, device)
         if rank == 0:
             print(json.dumps(out), flush=True)
     finally:

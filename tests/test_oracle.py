@@ -153,3 +153,41 @@ def test_oracle_hashmap_mode_agrees_with_on_the_fly_mode_where_both_are_defined(
         b = ko.build_kmap_hashmap_mode(coords, ks, st, pd)
         assert np.array_equal(a["coords"], b["coords"]), (ks, st)
         assert np.array_equal(a["out_in_map"], b["out_in_map"]), (ks, st)
+
+
+def _dense_conv_at(coords, feats, w, ks, st, pd, out_coords):
+    """Dense torch conv3d (fp64) of the scattered input with kernel `ks`, stride `st`, zero padding `pd`,
+    sampled at out_coords; the weight of kernel index k sits at the digits the oracle assigns to k."""
+    import torch
+
+    ks3, st3, pd3 = ko._as3(ks), ko._as3(st), ko._as3(pd)
+    b = int(coords[:, 0].max()) + 1
+    size = [int(coords[:, 1 + i].max()) + 1 for i in range(3)]
+    cin, cout = feats.shape[1], w.shape[2]
+    dense = torch.zeros((b, cin, *size), dtype=torch.float64)
+    dense[coords[:, 0], :, coords[:, 1], coords[:, 2], coords[:, 3]] = torch.from_numpy(feats)
+    wd = torch.zeros((cout, cin, *ks3), dtype=torch.float64)
+    for k, (dx, dy, dz) in enumerate(ko.kernel_digits(ks3)):
+        wd[:, :, dx, dy, dz] = torch.from_numpy(w[k]).T
+    out = torch.nn.functional.conv3d(dense, wd, stride=st3, padding=pd3)
+    oc = out_coords
+    return out[oc[:, 0], :, oc[:, 1], oc[:, 2], oc[:, 3]].numpy()
+
+
+@pytest.mark.parametrize("ks,st,pd", [(3, 2, 1), ((1, 3, 1), (1, 2, 1), (0, 1, 0)), (3, 1, 1), (3, 3, 1)])
+def test_oracle_hashmap_mode_pinned_by_dense_conv(ks, st, pd):
+    """kmap_mode="hashmap" with stride != kernel looks neighbours up at  out * stride + digit - (kernel - 1) / 2
+    (torchsparse/backend/hashmap/hashmap_cuda.cuh:213-232), which is a dense convolution with padding
+    (kernel - 1) / 2: the restatement of that mode is pinned against torch's conv3d, the way the reference's
+    own test pins its kernels (tests/python/test_single_layer_conv.py:111-220)."""
+    rng = np.random.default_rng(21)
+    coords = random_coords(rng, 900, (13, 12, 11), 2)
+    feats = rng.standard_normal((coords.shape[0], 3))
+    kvol = int(np.prod(ko._as3(ks)))
+    w = rng.standard_normal((kvol, 3, 4))
+    km = ko.build_kmap_hashmap_mode(coords, ks, st, pd)
+    m = km["sizes"][1]
+    assert m > 0
+    y = ko.conv_from_map(feats, w, km["out_in_map"], m)
+    want = _dense_conv_at(coords, feats, w, ks, st, pd, km["coords"])
+    assert np.abs(y - want).max() < 1e-12

@@ -362,7 +362,7 @@ def sorted_cm_artefacts_cuda(out_in_map: torch.Tensor, valid_n: int, valid_n_dev
     m.tile_mask = torch.empty(max(rows // 128, 1), dtype=torch.int32, device=dev)
     m.n_items_max = int(lib.tsb_map_items_max(rows, kvol, max_offsets))
     m.items = torch.empty((max(m.n_items_max, 1), 4), dtype=torch.int32, device=dev)
-    m.n_items = torch.zeros(1, dtype=torch.int32, device=dev)
+    m.n_items = torch.empty(1, dtype=torch.int32, device=dev)
     m.flags = torch.zeros(max(rows // 128, 1) * 16, dtype=torch.int32, device=dev)
     m._scratch = {}
     ws = _workspace(lib.tsb_map_sorted_cm_workspace_bytes(rows), dev)

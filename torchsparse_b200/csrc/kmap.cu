@@ -379,7 +379,7 @@ struct SubmOffsets {
 };
 __global__ void __launch_bounds__(256)
 subm_query_dyn_kernel(TableView t, const int4* __restrict__ coords, int64_t n_max, const int* __restrict__ rec,
-                      int kvol, int odd, SubmOffsets off, int* __restrict__ map) {
+                      int kvol, int odd, const __grid_constant__ SubmOffsets off, int* __restrict__ map) {
   const int64_t n = rec_rows(rec, n_max);
   const int64_t row = blockIdx.x * (int64_t)blockDim.y + threadIdx.y;
   if (row >= n) return;
@@ -501,8 +501,9 @@ __global__ void down_insert_fill_dyn_kernel(TableView t, const int64_t* __restri
 // input rows x offset lanes: map[out][kvol-1-k] = in, and (optionally) the transposed map [in][kvol-1-k] = out
 __global__ void __launch_bounds__(256)
 down_stage3_dyn_kernel(TableView t, const int4* __restrict__ coords, int64_t n_max, const int* __restrict__ rec_in,
-                       int64_t m_max, const int* __restrict__ rec_out, KernelGeom g, DownOffsets off,
-                       int* __restrict__ map, int* __restrict__ map_t, int* status) {
+                       int64_t m_max, const int* __restrict__ rec_out, KernelGeom g,
+                       const __grid_constant__ DownOffsets off, int* __restrict__ map, int* __restrict__ map_t,
+                       int* status) {
   const int64_t n = rec_rows(rec_in, n_max);
   const int64_t row = blockIdx.x * (int64_t)blockDim.y + threadIdx.y;
   const int64_t rows_pad_t = (n + 127) / 128 * 128;
@@ -630,21 +631,20 @@ __global__ void reorder_map_kernel(const int* __restrict__ map, int64_t rows, in
 }
 
 // ------------------------------------------------------------------ conv-ready sorted map
-// Sort key of a map row: (neighbour mask << 1) | 1 for a valid row, 0 for a padding row, so that padding
-// rows sort last (descending) even behind valid rows without any neighbour.  iota[i] = i.
+// Sort key of a map row: its neighbour mask (bit k = offset k has a neighbour); padding rows get 0.  The sort is
+// stable and padding rows have the largest row numbers, so in descending order they end up behind every
+// valid row, including valid rows without any neighbour.  iota[i] = i.
 __global__ void row_sort_key_kernel(const int* __restrict__ map, int64_t rows, int kvol, int64_t valid_n,
                                     const int* __restrict__ valid_n_dev, unsigned* __restrict__ keys,
                                     int* __restrict__ iota) {
   if (valid_n_dev) valid_n = max((int64_t)0, min((int64_t)__ldg(valid_n_dev), valid_n));
   for (int64_t row = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; row < rows; row += (int64_t)gridDim.x * blockDim.x) {
-    unsigned key = 0;
+    unsigned m = 0;
     if (row < valid_n) {
       const int* p = map + row * kvol;
-      unsigned m = 0;
       for (int i = 0; i < kvol; ++i) m |= (unsigned)(__ldg(&p[i]) >= 0) << i;
-      key = (m << 1) | 1u;
     }
-    keys[row] = key;
+    keys[row] = m;
     iota[row] = (int)row;
   }
 }
@@ -1305,9 +1305,13 @@ int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int
   row_sort_key_kernel<<<grid_for(rows, kBlock, 8), kBlock, 0, s>>>(out_in_map, rows, kvol, valid_n, valid_n_dev, keys, iota);
   TSB_LAUNCH_CHECK();
   size_t cb = w.cub_bytes;
-  // stable: rows with the same neighbour pattern keep their original order (neighbouring rows share inputs)
-  TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairsDescending(base + w.cub_off, cb, keys, keys2, iota, reorder_loc, rows, 0,
-                                                         kvol + 1, s));
+  // Stable: rows with the same neighbour pattern keep their original order (neighbouring rows share inputs).
+  // Only the top 24 bits of the mask are sorted (three 8-bit passes instead of four): on LiDAR scans the
+  // lowest offsets of a 3x3x3 kernel are the rarest, and leaving them out of the order costs about a tenth
+  // more (tile, offset) blocks at the finest levels and nothing at the coarse ones.
+  const int begin_bit = kvol > 24 ? kvol - 24 : 0;
+  TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairsDescending(base + w.cub_off, cb, keys, keys2, iota, reorder_loc, rows,
+                                                         begin_bit, kvol, s));
   count_launch();
   reorder_cm_kernel<<<(unsigned)(rows / 128), 128, 0, s>>>(out_in_map, reorder_loc, rows, kvol, valid_n, valid_n_dev,
                                                           map_cm, tile_mask);

@@ -57,9 +57,16 @@ class FusedConv(nn.Module):
     implicit-GEMM kernel; an input that is a pending concatenation (CatSparseTensor) is read from its
     two matrices."""
 
-    # set by InferenceEngine: run on row-sorted, column-major copies of the kernel maps (built once per
-    # map, shared by all layers that use it)
+    # set by InferenceEngine: submanifold layers at tensor strides up to sorted_max_stride run on row-sorted,
+    # column-major copies of their kernel maps (built once per map, shared by all layers that use it).  Strided
+    # and transposed maps serve one layer each and the coarsest level has few rows: there the copy costs more
+    # than the offset blocks it saves.
     sorted_maps = False
+    sorted_max_stride = 8
+
+    def _wants_sorted(self, stride) -> bool:
+        return (self.sorted_maps and not self.transposed and all(s == 1 for s in self.stride)
+                and max(stride) <= self.sorted_max_stride)
 
     def __init__(self, conv: Conv3d, bn: Optional[nn.BatchNorm1d] = None, relu: bool = False) -> None:
         super().__init__()
@@ -96,6 +103,16 @@ class FusedConv(nn.Module):
     def _kernel3(self) -> torch.Tensor:
         return self.kernel if self.kernel.dim() == 3 else self.kernel.view(1, *self.kernel.shape)
 
+    def _input_kernel(self, channels: int) -> torch.Tensor:
+        """[Kvol, Cin, Cout] weights for an input of `channels` channels: the layer's own, or, for an input
+        whose channels were zero-padded to the next multiple of 8 (the 4- or 5-channel network input, so that
+        its rows are 16-byte multiples), the weights with zero rows for the padding (made once)."""
+        kernel = self._kernel3()
+        cin = kernel.shape[1]
+        if channels != cin and channels == (cin + 7) // 8 * 8:
+            return backend._padded_kernel(kernel)
+        return kernel
+
     def forward(self, x: SparseTensor, residual: Optional[torch.Tensor] = None) -> SparseTensor:
         if getattr(x, "dyn", None) is not None:      # a tensor of the static (CUDA graph) engine
             from .static_engine import dyn_conv
@@ -124,7 +141,7 @@ class FusedConv(nn.Module):
             return None
         parts = getattr(x, "parts", None)
         feats, feats2 = (parts[0], parts[1]) if (parts is not None and len(parts) == 2) else (x.feats, None)
-        kernel = self._kernel3()
+        kernel = self._input_kernel(feats.shape[1] + (0 if feats2 is None else feats2.shape[1]))
         if feats.dtype != kernel.dtype or not feats.is_cuda or not feats.is_contiguous():
             return None
         if (feats.shape[1] * feats.element_size()) % 16 != 0:
@@ -162,7 +179,7 @@ class FusedConv(nn.Module):
             out_coords, out_range = kmap["coords"], kmap["spatial_range"]
             out_stride = tuple(a * b for a, b in zip(x.stride, self.stride))
         out_in_map = kmap["out_in_map" + sfx]
-        if self.sorted_maps:
+        if self._wants_sorted(x.stride):
             art = kmap.get("_cm" + sfx)
             if art is None:
                 art = kmap["_cm" + sfx] = backend.sorted_cm_artefacts_cuda(out_in_map, n_out)
@@ -251,10 +268,11 @@ class InferenceEngine(nn.Module):
     """Eval-mode wrapper: fused modules, no autograd, strided kernel maps built ahead of the convs,
     skip concatenations read in place by the layer that follows them."""
 
-    def __init__(self, model: nn.Module, sorted_maps: bool = True) -> None:
-        """`sorted_maps`: every kernel map gets a row-sorted, column-major copy with per-tile offset masks
-        the first time a layer uses it (tsb_map_sorted_cm), and all layers sharing the map run on that copy:
-        the 128 rows of a tile then share their neighbour pattern and few (tile, offset) blocks remain."""
+    def __init__(self, model: nn.Module, sorted_maps: bool = True, sorted_max_stride: int = 8) -> None:
+        """`sorted_maps`: the kernel map of the submanifold layers of a resolution level (tensor stride up to
+        `sorted_max_stride`) gets a row-sorted, column-major copy with per-tile offset masks the first time a
+        layer uses it (tsb_map_sorted_cm), and all layers sharing the map run on that copy: the 128 rows of a
+        tile then share their neighbour pattern and few (tile, offset) blocks remain."""
         super().__init__()
         if model.training:
             raise ValueError("InferenceEngine needs a model in eval() mode (BatchNorm statistics are folded)")
@@ -262,6 +280,7 @@ class InferenceEngine(nn.Module):
         for m in self.model.modules():
             if isinstance(m, FusedConv):
                 m.sorted_maps = bool(sorted_maps)
+                m.sorted_max_stride = int(sorted_max_stride)
         self._plan = None   # strided conv keys in execution order, learnt on the first call
 
     def _prebuild(self, x: SparseTensor) -> None:

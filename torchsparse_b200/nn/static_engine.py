@@ -159,7 +159,7 @@ def dyn_conv(layer, x: DynSparseTensor, residual: Optional[torch.Tensor]) -> Dyn
     dyn, caches = x.dyn, x._caches
     parts = getattr(x, "parts", None)
     feats, feats2 = (parts[0], parts[1]) if (parts is not None and len(parts) == 2) else (x.feats, None)
-    kernel = layer._kernel3()
+    kernel = layer._input_kernel(feats.shape[1] + (0 if feats2 is None else feats2.shape[1]))
     plan = layer._plan
     if plan is None or not plan.valid_for(kernel, backends.allow_tf32):
         plan = layer._plan = backend.IgemmLayerPlan(kernel, layer.scale, layer.shift, backends.allow_tf32)
@@ -186,7 +186,7 @@ def dyn_conv(layer, x: DynSparseTensor, residual: Optional[torch.Tensor]) -> Dyn
         kmap = _subm_map(x, ks)
         sfx, dyn_out, out_coords, out_stride = "", dyn, x.coords, x.stride
     out = torch.empty((dyn_out.n_max, plan.cout), dtype=plan.dtype, device=plan.device)
-    if dyn.ctx.sorted_maps:
+    if dyn.ctx.sorted_maps and layer._wants_sorted(x.stride):
         backend.igemm_plan_launch(plan, feats, None, dyn_out.n_max, residual, layer.relu, in_feats2=feats2,
                                   smap=_sorted(kmap, sfx, dyn_out), n_out_dev=dyn_out.rec, out=out)
     else:

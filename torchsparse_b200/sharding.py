@@ -83,7 +83,11 @@ class PaddedGather:
     """gather_rows_padded with its buffers allocated once: for a loop that gathers the output of every
     step, where the per-call allocations and small host calls would otherwise be paid each time.
     All calls must be made on the same stream (the buffers are reused in stream order).  Returns views
-    of the internal buffers, valid until the next call."""
+    of the internal buffers, valid until the next call.
+
+    The row count never passes through reused host memory (a queued host-to-device copy reads its source
+    when it runs, not when it is queued, so a later call could overwrite it first): a count the host knows
+    travels as a kernel argument (`fill_`), a count the host does not know is given as a device tensor."""
 
     def __init__(self, max_rows: int, cols: int, dtype: torch.dtype, device,
                  group: Optional[dist.ProcessGroup] = None) -> None:
@@ -92,22 +96,28 @@ class PaddedGather:
         self.max_rows = max_rows
         self.padded = torch.zeros((max_rows, cols), dtype=dtype, device=device)
         self.buf = torch.empty((self.world, max_rows, cols), dtype=dtype, device=device)
-        self.n_host = torch.zeros(1, dtype=torch.int64).pin_memory() if torch.cuda.is_available() else \
-            torch.zeros(1, dtype=torch.int64)
         self.n_dev = torch.zeros(1, dtype=torch.int64, device=device)
         self.counts = torch.zeros(self.world, dtype=torch.int64, device=device)
 
-    def __call__(self, local: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    def __call__(self, local: torch.Tensor, n_dev: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """`local`: this rank's rows.  Without `n_dev` all of them count; with `n_dev` (an integer tensor of one
+        element on the device) `local` holds `max_rows` rows of which the first `n_dev[0]` count."""
         rows = local.shape[0]
         if rows > self.max_rows:
             raise ValueError(f"{rows} rows exceed max_rows={self.max_rows}")
-        self.n_host[0] = rows
-        self.n_dev.copy_(self.n_host, non_blocking=True)
-        self.padded[:rows].copy_(local)
+        if n_dev is None:
+            self.n_dev.fill_(rows)
+        else:
+            self.n_dev.copy_(n_dev.reshape(1))
+        if rows == self.max_rows and local.is_contiguous():
+            src = local                       # already padded: gathered in place
+        else:
+            self.padded[:rows].copy_(local)
+            src = self.padded
         if self.world == 1:
             self.counts.copy_(self.n_dev)
-            self.buf[0].copy_(self.padded)
+            self.buf[0].copy_(src)
         else:
             dist.all_gather_into_tensor(self.counts, self.n_dev, group=self.group)
-            dist.all_gather_into_tensor(self.buf.view(self.world * self.max_rows, -1), self.padded, group=self.group)
+            dist.all_gather_into_tensor(self.buf.view(self.world * self.max_rows, -1), src, group=self.group)
         return self.buf, self.counts
