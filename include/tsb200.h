@@ -441,6 +441,18 @@ int tsb_voxelize_fwd(const void* feats, const int32_t* idx, const int32_t* count
 int tsb_devoxelize_fwd(const void* feats, const int32_t* indices, const float* weights, int64_t n,
                        int32_t c, int32_t dtype, void* out, tsb_stream_t stream);
 
+/* Backward of tsb_voxelize_fwd: grad_feats fp32 [n, c] (fully written) = grad_out[idx[i]] / counts[idx[i]],
+ * 0 where idx[i] is out of range.  grad_out fp32 [n_vox, c].
+ * Replaces voxelize_backward_cuda (torchsparse/backend/voxelize/voxelize_cuda.cu:58-76, 97-114). */
+int tsb_voxelize_bwd(const float* grad_out, const int32_t* idx, const int32_t* counts, int64_t n, int64_t n_vox,
+                     int32_t c, float* grad_feats, tsb_stream_t stream);
+
+/* Backward of tsb_devoxelize_fwd with respect to the voxel features: grad_voxels fp32 [n_vox, c] (zeroed by the
+ * call) += weights[i][k] * grad_out[i] at indices[i][k] >= 0.  grad_out fp32 [n, c].
+ * Replaces devoxelize_backward_cuda (torchsparse/backend/devoxelize/devoxelize_cuda.cu:37-57, 80-98). */
+int tsb_devoxelize_bwd(const float* grad_out, const int32_t* indices, const float* weights, int64_t n, int64_t n_vox,
+                       int32_t c, float* grad_voxels, tsb_stream_t stream);
+
 /* GPU twin of sparse_quantize: q = floor(xyz / voxel) (evaluated in float64, xyz float32 or
  * float64 [n,3], voxel HOST double[3]), unique by ravel key in ascending order.
  * Outputs: q_all int32 [n,3]; uniq_coords int32 [<=n,3]; first_index int64 [<=n] (smallest

@@ -201,8 +201,15 @@ def test_baseline_config1_all_dataflows():
 
 def test_reference_style_dense_equivalence_fp16():
     """The reference's own test (tests/python/test_single_layer_conv.py:111-220, thresholds
-    tests/test.py:40-41): 5^3 grid, 20 voxels, 16->32, fp16, kernel {2,3,5} x stride {1,2,3},
-    against dense conv3d; mean-abs-diff <= 1e-4 and max-rel-diff <= 1e-2 averaged over the runs."""
+    tests/test.py:40-41): 5^3 grid, 20 voxels, 16->32, fp16, kernel {2,3,5} x stride {1,2,3}, against a dense
+    convolution whose output is rounded to fp16 as the reference's dense fp16 model rounds it; its metrics,
+    averaged over the runs: sum |diff| / rows <= 1e-4 and max |diff| / mean |out| <= 1e-2.
+
+    Both sides round the same sums (fp32 accumulation here, fp64 there) to fp16, so they differ only where a sum
+    sits within accumulation error of an fp16 rounding boundary: a handful of 1-ulp flips (ulp 2^-9..2^-7 at these
+    magnitudes) over the 9 x 640 outputs.  The reference's bound on the first metric allows about five such flips;
+    the bound asserted here is 1e-3 (about fifty), stated rather than borrowed, because the count of flips
+    depends on the accumulation order of the tensor cores, which is not specified."""
     rng = np.random.default_rng(0)
     madiffs, rdiffs = [], []
     for ks in (2, 3, 5):
@@ -216,10 +223,11 @@ def test_reference_style_dense_equivalence_fp16():
             want = ko.conv_from_map(feats, w, km["out_in_map"], km["sizes"][1])
             if want.shape[0] == 0:
                 continue
+            want = want.astype(np.float16).astype(np.float64)          # the dense fp16 model's output
             got = y.feats.float().cpu().numpy()
-            madiffs.append(np.abs(got - want).sum() / want.shape[0] / 32)
+            madiffs.append(np.abs(got - want).sum() / want.shape[0])
             rdiffs.append(np.abs(got - want).max() / max(np.abs(got).mean(), 1e-9))
-    assert np.mean(madiffs) <= 1e-2 and np.mean(rdiffs) <= 1e-2
+    assert np.mean(madiffs) <= 1e-3 and np.mean(rdiffs) <= 1e-2, (np.mean(madiffs), np.mean(rdiffs))
 
 
 def test_fused_epilogue_and_bias():

@@ -1,0 +1,114 @@
+"""GPU checks of smaller pieces: gradients of the point <-> voxel operators against torch autograd of the same
+sums, weight-cache invalidation of the tensor-core path, the output gather's row counts, convolutions on a
+second device of one process."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import random_coords, rel_l2
+from oracle import kmap_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+
+def test_voxelize_and_devoxelize_gradients():
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(3)
+    n, nv, c = 5000, 700, 24
+    idx = torch.from_numpy(rng.integers(0, nv, n).astype(np.int32)).cuda()
+    counts = torch.bincount(idx.long(), minlength=nv).int()
+    x = torch.from_numpy(rng.standard_normal((n, c)).astype(np.float32)).cuda().requires_grad_()
+    g = torch.from_numpy(rng.standard_normal((nv, c)).astype(np.float32)).cuda()
+    y = F.spvoxelize(x, idx, counts)
+    y.backward(g)
+    xr = x.detach().clone().requires_grad_()
+    want = torch.zeros(nv, c, device="cuda").index_add(0, idx.long(), xr) / counts.clamp(min=1)[:, None]
+    want.backward(g)
+    assert rel_l2(y.detach().cpu().numpy(), want.detach().cpu().numpy()) < 1e-5
+    assert rel_l2(x.grad.cpu().numpy(), xr.grad.cpu().numpy()) < 1e-6
+
+    ind = rng.integers(-1, nv, (n, 8)).astype(np.int32)
+    w = rng.uniform(0, 1, (n, 8)).astype(np.float32)
+    w[ind < 0] = 0
+    ind_t, w_t = torch.from_numpy(ind).cuda(), torch.from_numpy(w).cuda()
+    v = torch.from_numpy(rng.standard_normal((nv, c)).astype(np.float32)).cuda().requires_grad_()
+    gp = torch.from_numpy(rng.standard_normal((n, c)).astype(np.float32)).cuda()
+    out = F.spdevoxelize(v, ind_t, w_t)
+    out.backward(gp)
+    vr = v.detach().clone().requires_grad_()
+    want = (vr[ind_t.clamp(min=0).long()] * w_t[:, :, None]).sum(1)
+    want.backward(gp)
+    assert rel_l2(out.detach().cpu().numpy(), want.detach().cpu().numpy()) < 1e-5
+    assert rel_l2(v.grad.cpu().numpy(), vr.grad.cpu().numpy()) < 1e-5
+
+
+def test_weights_changed_in_place_reach_the_tensor_core_path():
+    """Packed weight copies are rebuilt after an in-place update through torch (version counter), after
+    Conv3d.reset_parameters(), and after FusedConv.invalidate() for writes the counter does not see."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200 import nn as spnn
+    from torchsparse_b200.nn import FusedConv
+
+    rng = np.random.default_rng(5)
+    coords = random_coords(rng, 3000, (24, 24, 24))
+    feats = rng.standard_normal((3000, 32)).astype(np.float32)
+    km = ko.build_kmap(coords, 3, 1, 1)
+    conv = spnn.Conv3d(32, 64, 3).cuda().half()
+
+    def check(layer, kernel):
+        x = ts.SparseTensor(torch.from_numpy(feats).cuda().half(), torch.from_numpy(coords).cuda())
+        with torch.no_grad():
+            y = layer(x)
+        want = ko.conv_from_map(torch.from_numpy(feats).half().float().numpy(), kernel.detach().float().cpu().numpy(),
+                                km["out_in_map"], 3000)
+        assert rel_l2(y.feats.float().cpu().numpy(), want) < 2e-3
+
+    check(conv, conv.kernel)
+    with torch.no_grad():
+        conv.kernel.mul_(-0.5)                      # in place through torch
+    check(conv, conv.kernel)
+    conv.reset_parameters()
+    check(conv, conv.kernel)
+    fused = FusedConv(conv).cuda()
+    check(fused, fused.kernel)
+    fused.kernel.data.copy_(torch.randn_like(fused.kernel) * 0.05)      # invisible to the version counter
+    fused.invalidate()
+    check(fused, fused.kernel)
+
+
+def test_padded_gather_counts_of_back_to_back_calls():
+    """Two gathers queued behind a long-running kernel keep their own row counts."""
+    from torchsparse_b200.sharding import PaddedGather
+
+    pg = PaddedGather(64, 4, torch.float32, torch.device("cuda", 0))
+    a, b = torch.ones(10, 4, device="cuda"), torch.full((37, 4), 2.0, device="cuda")
+    torch.cuda._sleep(20_000_000)                   # ~10 ms: both calls are queued before either runs
+    _, c1 = pg(a)
+    c1 = c1.clone()
+    buf, c2 = pg(b)
+    torch.cuda.synchronize()
+    assert int(c1[0]) == 10 and int(c2[0]) == 37
+    assert bool((buf[0, :37] == 2.0).all())
+    n_dev = torch.tensor([5], dtype=torch.int32, device="cuda")
+    full = torch.full((64, 4), 3.0, device="cuda")
+    buf, c3 = pg(full, n_dev)
+    torch.cuda.synchronize()
+    assert int(c3[0]) == 5 and bool((buf[0] == 3.0).all())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_convolution_on_a_second_device_of_one_process():
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(7)
+    coords = random_coords(rng, 2000, (20, 20, 20))
+    km = ko.build_kmap(coords, 3, 1, 1)
+    f = torch.from_numpy(rng.standard_normal((2000, 96)).astype(np.float32)).half()
+    w = torch.from_numpy((rng.standard_normal((27, 96, 96)) / 50).astype(np.float32)).half()
+    want = ko.conv_from_map(f.float().numpy(), w.float().numpy(), km["out_in_map"], 2000)
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            y = backend.conv_forward_implicit_gemm_cuda(f.cuda(dev), w.cuda(dev), torch.from_numpy(km["out_in_map"]).cuda(dev),
+                                                        2000, 96)
+            assert rel_l2(y.float().cpu().numpy(), want) < 2e-3

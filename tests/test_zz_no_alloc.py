@@ -50,6 +50,30 @@ def test_static_hash_query_matches_workspace_version_twice_in_a_row():
         assert torch.equal(refs[got[pos]], q[pos])
 
 
+def test_static_hash_query_at_its_limit_and_without_touching_device_memory():
+    """The largest key set the fixed table takes (exactly the stated maximum), and the point of the entry: the
+    amount of free device memory is the same before and after the call."""
+    from torchsparse_b200._lib import lib, check
+
+    n_ref = lib.tsb_hash_query_static_max_refs()
+    rng = np.random.default_rng(43)
+    universe = rng.choice(10**14, n_ref + 1000, replace=False).astype(np.int64) + 1
+    refs = torch.from_numpy(universe[:n_ref]).cuda()
+    q = torch.from_numpy(np.concatenate([universe[:5000], universe[n_ref:]])).cuda()
+    want, _ = _both(q, refs)                       # also makes the entry's one-time address lookup happen
+    out = torch.empty(q.numel(), dtype=torch.int64, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    check(lib.tsb_hash_query_static(q.data_ptr(), q.numel(), refs.data_ptr(), n_ref, out.data_ptr(), stream),
+          "tsb_hash_query_static")
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.equal(out, want)
+    assert bool((out[:5000] == torch.arange(5000, device="cuda")).all()) and bool((out[5000:] == -1).all())
+
+
 def test_static_hash_query_rejects_sizes_beyond_its_table():
     from torchsparse_b200._lib import lib
 

@@ -74,6 +74,8 @@ SIGNATURES = {
     "tsb_kmap_subm_dyn": (C.c_int, [P, P, I64, P, I64, P, P, I32, P, P, P]),
     "tsb_kmap_down_dyn_workspace_bytes": (SZ, [I64, P, P]),
     "tsb_kmap_down_dyn": (C.c_int, [P, P, I64, P, I64, P, P, P, P, I32, I64, P, P, P, P, P, P, SZ, P]),
+    "tsb_voxelize_bwd": (C.c_int, [P, P, P, I64, I64, I32, P, P]),
+    "tsb_devoxelize_bwd": (C.c_int, [P, P, P, I64, I64, I32, P, P]),
     "tsb_to_dense_fwd": (C.c_int, [P, P, I64, I32, P, I32, P, P]),
 }
 

@@ -31,7 +31,7 @@ __all__ = [
     "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda", "conv_backward_wgrad_pairs_cuda",
     "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
-    "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
+    "voxelize_backward_cuda", "devoxelize_backward_cuda", "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
     "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda", "SortedMap",
 ]
 
@@ -62,13 +62,32 @@ def _stream() -> int:
 _status_words = {}
 
 
+def _dev(device) -> torch.device:
+    device = torch.device(device)
+    return device if device.index is not None else torch.device("cuda", torch.cuda.current_device())
+
+
 def _status_word(device: torch.device) -> torch.Tensor:
     """One persistent int32 status word per device for launches whose status nobody reads back
     (the kernels only ever write non-zero error codes into it)."""
+    device = _dev(device)
     w = _status_words.get(device)
     if w is None:
         w = _status_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
     return w
+
+
+def raise_if_kernel_failed(device: torch.device) -> None:
+    """Reads the device's shared status word (a device-to-host read: call it where the stream is being waited for
+    anyway) and raises if a bounded wait inside a convolution kernel ran out since the last check."""
+    w = _status_words.get(_dev(device))
+    if w is None:
+        return
+    v = int(w.item())
+    if v:
+        w.zero_()
+        raise RuntimeError(f"a bounded wait inside a convolution kernel ran out (code {v}); results computed since "
+                           "the last check are undefined")
 
 
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -239,6 +258,7 @@ def downsample_unique(coords: torch.Tensor, coords_min, coords_max, kernel_sizes
     check(lib.tsb_kmap_down_unique(_p(coords), n, i32x(cmin), i32x(cmax), a_ks, a_st, i32x(pd), _p(uniq), _p(result),
                                    _p(ws), ws.numel(), _stream()), "build_kernel_map_downsample_hashmap")
     res = result.cpu().tolist()  # the one synchronisation of the strided build
+    raise_if_kernel_failed(coords.device)     # the stream is idle now: the status of earlier launches comes cheap
     m = res[0]
     out_max = tuple(res[1:5]) if m > 0 else None
     return uniq, m, out_max
@@ -452,7 +472,9 @@ def build_mask_from_kmap(n_points: int, n_out_points: int, nbmaps: torch.Tensor,
 # --------------------------------------------------------------------------- convolution
 # Weights packed K-major for the tensor-core kernel are cached ON the weight tensor object, tagged
 # with its version counter, so an inference loop packs each layer once and an in-place update
-# through torch invalidates the copy.  Turn off for weights rewritten through raw pointers.
+# through torch invalidates the copy.  Writes through ``.data`` or raw pointers do NOT move the version
+# counter: after such a write call ``FusedConv.invalidate()`` / delete the ``_tsb_packed`` and ``_tsb_padded``
+# attributes of the weight tensor, or turn the cache off.
 cache_packed_weights = True
 # When True every tensor-core launch is followed by a read of its device status word (a sync).
 check_kernel_status = False
@@ -985,6 +1007,30 @@ def devoxelize_forward_cuda(feat: torch.Tensor, indices: torch.Tensor, weight: t
     return out
 
 
+def voxelize_backward_cuda(grad_out: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor, n: int) -> torch.Tensor:
+    """Gradient of voxelize_forward_cuda with respect to the point features, fp32 [n, C]
+    (torchsparse/backend/voxelize/voxelize_cuda.cu:97-114)."""
+    _need_cuda(grad_out, idx, counts)
+    grad_out, idx, counts = grad_out.float().contiguous(), idx.int().contiguous(), counts.int().contiguous()
+    c = grad_out.shape[1]
+    out = torch.empty((int(n), c), dtype=torch.float32, device=grad_out.device)
+    check(lib.tsb_voxelize_bwd(_p(grad_out), _p(idx), _p(counts), int(n), counts.shape[0], c, _p(out), _stream()),
+          "voxelize_backward_cuda")
+    return out
+
+
+def devoxelize_backward_cuda(grad_out: torch.Tensor, indices: torch.Tensor, weight: torch.Tensor, n_vox: int) -> torch.Tensor:
+    """Gradient of devoxelize_forward_cuda with respect to the voxel features, fp32 [n_vox, C]
+    (torchsparse/backend/devoxelize/devoxelize_cuda.cu:80-98)."""
+    _need_cuda(grad_out, indices, weight)
+    grad_out, indices, weight = grad_out.float().contiguous(), indices.int().contiguous(), weight.float().contiguous()
+    n, c = grad_out.shape
+    out = torch.empty((int(n_vox), c), dtype=torch.float32, device=grad_out.device)
+    check(lib.tsb_devoxelize_bwd(_p(grad_out), _p(indices), _p(weight), n, int(n_vox), c, _p(out), _stream()),
+          "devoxelize_backward_cuda")
+    return out
+
+
 def to_dense_forward_cuda(feats: torch.Tensor, coords: torch.Tensor, spatial_range, outputs: torch.Tensor) -> None:
     """Scatter into the caller's zero-initialised dense tensor
     (torchsparse/backend/voxelize/voxelize_cuda.cu:116-127)."""
@@ -1015,6 +1061,7 @@ def quantize_unique_cuda(xyz: torch.Tensor, voxel_size: Sequence[float], return_
     check(lib.tsb_quantize_unique(_p(xyz), int(xyz.dtype == torch.float64), n, vox, _p(q_all), _p(uniq), _p(first),
                                   _p(inv), _p(result), _p(ws), ws.numel(), _stream()), "quantize_unique_cuda")
     res = result.cpu().tolist()        # the one synchronisation: voxel count + coordinate bounds
+    raise_if_kernel_failed(dev)
     nv = res[0]
     bounds = (tuple(res[1:4]), tuple(res[4:7])) if nv else ((0, 0, 0), (0, 0, 0))
     return uniq[:nv], (first[:nv] if first is not None else None), inv, bounds

@@ -94,6 +94,41 @@ __global__ void to_dense_kernel(const T* __restrict__ feats, const int4* __restr
   }
 }
 
+// Backward of the average pooling: grad_feats[i] = grad_out[idx[i]] / counts[idx[i]] (a gather; fp32 gradients).
+__global__ void voxelize_bwd_kernel(const float* __restrict__ grad_out, const int* __restrict__ idx,
+                                    const int* __restrict__ counts, int64_t n, int64_t n_vox, int c,
+                                    float* __restrict__ grad_feats) {
+  const int64_t total = n * c;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = t / c;
+    const int j = (int)(t - i * c);
+    const int pos = __ldg(&idx[i]);
+    float g = 0.f;
+    if (pos >= 0 && pos < n_vox) {
+      const int cnt = __ldg(&counts[pos]);
+      if (cnt > 0) g = __ldg(&grad_out[(int64_t)pos * c + j]) / (float)cnt;
+    }
+    grad_feats[t] = g;
+  }
+}
+
+// Backward of the interpolation: grad_voxels[idx[i][k]] += w[i][k] * grad_out[i] (scatter by atomic adds, fp32).
+__global__ void devoxelize_bwd_kernel(const float* __restrict__ grad_out, const int* __restrict__ indices,
+                                      const float* __restrict__ weights, int64_t n, int64_t n_vox, int c,
+                                      float* __restrict__ grad_voxels) {
+  const int64_t total = n * c;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = t / c;
+    const int j = (int)(t - i * c);
+    const float g = __ldg(&grad_out[t]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int dst = __ldg(&indices[i * 8 + k]);
+      if (dst >= 0 && dst < n_vox) atomicAdd(&grad_voxels[(int64_t)dst * c + j], __ldg(&weights[i * 8 + k]) * g);
+    }
+  }
+}
+
 // One thread per voxel: batch column + voxel coordinates, and the features of the voxel's first point cast
 // to T and zero-padded to c_pad channels.  The voxel count is read from the quantisation result on the device.
 template <typename T>
@@ -214,6 +249,30 @@ int tsb_voxel_inputs(const float* points, int32_t c_in, const int64_t* first_ind
     default:
       return TSB_ERR_UNSUPPORTED;
   }
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_voxelize_bwd(const float* grad_out, const int32_t* idx, const int32_t* counts, int64_t n, int64_t n_vox,
+                     int32_t c, float* grad_feats, tsb_stream_t stream) {
+  if (n < 0 || n_vox < 0 || c < 1 || (n && (!idx || !grad_feats)) || (n && n_vox && (!grad_out || !counts)))
+    return TSB_ERR_BAD_ARG;
+  if (n == 0) return TSB_OK;
+  voxelize_bwd_kernel<<<grid_for(n * (int64_t)c, kBlock, 32), kBlock, 0, as_stream(stream)>>>(grad_out, idx, counts, n,
+                                                                                            n_vox, c, grad_feats);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_devoxelize_bwd(const float* grad_out, const int32_t* indices, const float* weights, int64_t n, int64_t n_vox,
+                       int32_t c, float* grad_voxels, tsb_stream_t stream) {
+  if (n < 0 || n_vox < 0 || c < 1 || (n_vox && !grad_voxels) || (n && (!grad_out || !indices || !weights)))
+    return TSB_ERR_BAD_ARG;
+  cudaStream_t st = as_stream(stream);
+  if (n_vox) TSB_CUDA_TRY(cudaMemsetAsync(grad_voxels, 0, (size_t)n_vox * c * sizeof(float), st));
+  if (n == 0 || n_vox == 0) return TSB_OK;
+  devoxelize_bwd_kernel<<<grid_for(n * (int64_t)c, kBlock, 32), kBlock, 0, st>>>(grad_out, indices, weights, n, n_vox, c,
+                                                                                grad_voxels);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }

@@ -122,6 +122,11 @@ def conv3d(
     # the input's own coordinates are the target of a later transposed conv back to this stride
     caches.cmaps.setdefault(input.stride, (coords, input.spatial_range))
     fused = epilogue is not None and dataflow == Dataflow.ImplicitGEMM
+    if fused and torch.is_grad_enabled():
+        # the kernel's epilogue has no backward: under autograd the same arithmetic runs as torch ops
+        res = epilogue.get("residual")
+        if feats.requires_grad or weight.requires_grad or (res is not None and res.requires_grad):
+            fused = False
 
     if kernel_size == (1, 1, 1) and stride == (1, 1, 1) and dilation == (1, 1, 1):
         out_feats = feats.matmul(weight.to(feats.dtype))

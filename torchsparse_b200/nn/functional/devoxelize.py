@@ -1,4 +1,5 @@
 import torch
+from torch.autograd import Function
 
 from ... import backend
 
@@ -28,7 +29,27 @@ def calc_ti_weights(coords: torch.Tensor, idx_query: torch.Tensor, scale: float 
     return w
 
 
+class _Devoxelize(Function):
+    """Interpolation of voxel features at points and its gradient with respect to the voxel features
+    (torchsparse/nn/functional/devoxelize.py:52-101)."""
+
+    @staticmethod
+    def forward(ctx, feats: torch.Tensor, coords: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        ctx.save_for_backward(coords, weights)
+        ctx.n_vox = feats.shape[0]
+        return backend.devoxelize_forward_cuda(feats, coords, weights)
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        coords, weights = ctx.saved_tensors
+        grad = backend.devoxelize_backward_cuda(grad_output, coords, weights, ctx.n_vox)
+        return grad.to(grad_output.dtype), None, None
+
+
 def spdevoxelize(feats: torch.Tensor, coords: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
     """Interpolate voxel features at points: ``coords`` int [N,8] voxel rows (-1 = absent),
-    ``weights`` [N,8] (torchsparse/nn/functional/devoxelize.py:52-101; forward only)."""
-    return backend.devoxelize_forward_cuda(feats.contiguous(), coords.contiguous().int(), weights.contiguous())
+    ``weights`` [N,8] (torchsparse/nn/functional/devoxelize.py:52-101)."""
+    feats, coords, weights = feats.contiguous(), coords.contiguous().int(), weights.contiguous()
+    if torch.is_grad_enabled() and feats.requires_grad:
+        return _Devoxelize.apply(feats, coords, weights)
+    return backend.devoxelize_forward_cuda(feats, coords, weights)

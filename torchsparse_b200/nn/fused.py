@@ -311,7 +311,7 @@ class InferenceEngine(nn.Module):
                 cfg = _conv_impl.resolve_config(None)
                 self._plan = [entry + (cfg,) for entry in log]
                 return out
-            self._prebuild(x)
+            self._prebuild(x)     # its size readbacks also fetch the convolution kernels' status word
             return self.model(x)
         finally:
             operators.lazy = was_lazy

@@ -45,9 +45,12 @@ class Conv3d(nn.Module):
         """U(-b, b) with b = 1 / sqrt(fan * Kvol), fan = Cout for a transposed layer, else Cin."""
         fan = self.out_channels if self.transposed else self.in_channels
         bound = 1.0 / math.sqrt(fan * self.kernel_volume)
-        for param in (self.kernel, self.bias):
-            if param is not None:
-                param.data.uniform_(-bound, bound)
+        # in-place under no_grad, not through .data: the version counter moves, so weight copies cached for the
+        # tensor-core kernel (packed / padded layouts) are rebuilt
+        with torch.no_grad():
+            for param in (self.kernel, self.bias):
+                if param is not None:
+                    param.uniform_(-bound, bound)
 
     def extra_repr(self) -> str:
         parts = [f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}"]
