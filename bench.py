@@ -8,7 +8,7 @@ reference's own SparseResUNet42, width 1.0, plus a 19-way linear head) in fp16 i
 LiDAR-like scan per GPU per step (64 rings x 2048 azimuths, 120k rays + 20% box points, 0.05 m voxels).
 One step = voxelisation (sparse_quantize on the GPU) -> 9 kernel maps -> 42 sparse convolutions + 7 pointwise
 ones (BatchNorm / ReLU / skip folded in) -> logits.  The whole step is one CUDA graph (StaticEngine: every
-size lives in device memory), replayed per scan; consecutive scans alternate between two engines on two
+size lives in device memory), replayed per scan; consecutive scans rotate over four engines on four
 streams.  With N GPUs every rank runs its own scans (weak scaling, scans are independent) and the logits are
 all-gathered over NCCL once per step.
 
@@ -726,8 +726,17 @@ def run_layer(args, device):
     occ = float(args.layer.split(",")[5]) if len(args.layer.split(",")) > 5 else 0.05
     dtype = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32, "tf32": torch.float32}[args.dtype]
     backends.allow_tf32 = args.dtype == "tf32"     # "f32" = exact fp32 arithmetic on the CUDA cores
-    coords_np, side = uniform_voxels(0, n, occ)
-    coords = torch.from_numpy(coords_np).to(device)
+    if args.lidar_level >= 0:
+        # rows of the benchmark scan at tensor stride 2^level instead of uniformly scattered voxels
+        from torchsparse_b200.utils import sparse_quantize
+        vox = sparse_quantize(torch.from_numpy(scan_points(0)).to(device)[:, :3], VOXEL)
+        coords = torch.cat([torch.zeros((vox.shape[0], 1), dtype=torch.int32, device=device), vox], 1)
+        for _ in range(args.lidar_level):
+            coords = F.build_kernel_map(coords, coords.shape[0], 2, 2, 0, None, None, None, "hashmap_on_the_fly")["coords"]
+        n, side, occ = coords.shape[0], 0, f"lidar level {args.lidar_level}"
+    else:
+        coords_np, side = uniform_voxels(0, n, occ)
+        coords = torch.from_numpy(coords_np).to(device)
     g = torch.Generator(device=device).manual_seed(0)
     kvol = ks ** 3
     w = (torch.randn(kvol, cin, cout, device=device, generator=g) * (2.0 / (kvol * cin)) ** 0.5).to(dtype)
@@ -746,6 +755,16 @@ def run_layer(args, device):
     run()
     torch.cuda.synchronize()
     kmap = x._caches.kmaps[((1, 1, 1), (ks,) * 3, (st,) * 3, (1, 1, 1))]
+    if args.smap:
+        # the engine's form of the map: row-sorted, column-major, per-tile masks (tsb_map_sorted_cm)
+        sfx = "_t" if args.transposed else ""
+        rows_valid = kmap["sizes"][0] if args.transposed else kmap["sizes"][1]
+        sm = backend.sorted_cm_artefacts_cuda(kmap["out_in_map" + sfx], rows_valid)
+        xin, wk = (mid.feats, wt) if args.transposed else (x.feats, w)
+        run = lambda: backend.conv_forward_implicit_gemm_cuda(xin, wk, None, rows_valid, wk.shape[2], backends.allow_tf32,
+                                                              True, smap=sm)
+        run()
+        torch.cuda.synchronize()
     n_out = kmap["sizes"][0] if args.transposed else kmap["sizes"][1]
     n_in = kmap["sizes"][1] if args.transposed else n
     pairs = int((kmap["out_in_map"][:kmap["sizes"][1]] >= 0).sum().item())
@@ -768,7 +787,8 @@ def run_layer(args, device):
     return {"metric": "sparse_conv3d_layer_ms", "value": round(ms, 4), "unit": "ms", "higher_is_better": False,
             "config": {"workload": f"single Conv3d N={n} {cin}->{cout} k{ks} s{st}{' transposed' if args.transposed else ''} "
                                    f"occupancy {occ} (grid side {side})",
-                       "dataflow": args.dataflow, "sorted": bool(args.sorted), "dtype": args.dtype},
+                       "dataflow": args.dataflow, "sorted": bool(args.sorted), "engine_sorted_map": bool(args.smap),
+                       "dtype": args.dtype},
             "n_out": n_out, "pairs": pairs, "neighbours_per_row": round(pairs / max(n_out, 1), 2),
             "useful_tflops": round(fl / ms / 1e9, 2), "algorithmic_gbs": round(by / ms / 1e6, 1),
             "frac_tensor_peak": round(fl / ms / 1e9 / pk["tensor_tflops"], 4),
@@ -843,7 +863,9 @@ def main():
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
     ap.add_argument("--transposed", action="store_true")
-    ap.add_argument("--streams", type=int, default=2,
+    ap.add_argument("--smap", action="store_true", help="layer mode: run on the row-sorted column-major map of the engines")
+    ap.add_argument("--lidar-level", type=int, default=-1, help="layer mode: rows of the benchmark scan at stride 2^L")
+    ap.add_argument("--streams", type=int, default=4,
                     help="engines (each with its own stream and graph) that consecutive scans alternate between")
     ap.add_argument("--unsorted", action="store_true", help="run on the kernel maps as built (no row-sorted copies)")
     args = ap.parse_args()

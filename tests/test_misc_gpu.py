@@ -112,3 +112,34 @@ def test_convolution_on_a_second_device_of_one_process():
             y = backend.conv_forward_implicit_gemm_cuda(f.cuda(dev), w.cuda(dev), torch.from_numpy(km["out_in_map"]).cuda(dev),
                                                         2000, 96)
             assert rel_l2(y.float().cpu().numpy(), want) < 2e-3
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_gather_scatter_backward_entry_fills_callers_buffers(transpose):
+    """`conv_backward_gather_scatter_cuda` with the reference's argument list
+    (torchsparse/nn/functional/conv/func/gather_scatter.py:116): the caller's zero-filled gradient tensors are
+    written in place; checked against the fp64 oracle."""
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(91)
+    coords = random_coords(rng, 900, (12, 12, 12))
+    n, cin, cout = coords.shape[0], 16, 24
+    km = ko.build_kmap(coords, 2, 2, 0)
+    m = km["sizes"][1]
+    nbmaps, nbsizes = ko.pairs_from_map(km["out_in_map"])
+    if transpose:                       # the pair list of the strided layer, used from its outputs to its inputs
+        n_in, n_out, omap = m, n, ko.transpose_map(km["out_in_map"], ko.pad_rows(n))
+    else:
+        n_in, n_out, omap = n, m, km["out_in_map"]
+    feats = rng.standard_normal((n_in, cin)).astype(np.float32)
+    w = (rng.standard_normal((8, cin, cout)) * 0.2).astype(np.float32)
+    gy = rng.standard_normal((n_out, cout)).astype(np.float32)
+    want_dx, want_dw = ko.conv_backward_from_map(feats, w, omap, n_out, gy)
+
+    x = torch.from_numpy(feats).cuda()
+    wt = torch.from_numpy(w).cuda()
+    gx, gw = torch.zeros_like(x), torch.zeros_like(wt)
+    backend.conv_backward_gather_scatter_cuda(x, gx, torch.from_numpy(gy).cuda(), wt, gw,
+                                              torch.from_numpy(nbmaps).cuda(), torch.from_numpy(nbsizes), transpose)
+    assert rel_l2(gx.cpu().numpy(), want_dx) < 1e-5
+    assert rel_l2(gw.cpu().numpy(), want_dw) < 1e-5

@@ -29,7 +29,7 @@ __all__ = [
     "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "sorted_artefacts_cuda",
     "exclusive_scan_quantified_wrapper",
     "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda", "conv_backward_wgrad_pairs_cuda",
-    "conv_forward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
+    "conv_forward_gather_scatter_cuda", "conv_backward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
     "voxelize_backward_cuda", "devoxelize_backward_cuda", "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
     "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda", "SortedMap",
@@ -834,6 +834,25 @@ def conv_backward_wgrad_pairs_cuda(grad_out: torch.Tensor, in_feats: torch.Tenso
             torch.mm(xg[start:start + size].t(), yg[start:start + size], out=dw[k])
         start += size
     return dw
+
+
+def conv_backward_gather_scatter_cuda(in_feat: torch.Tensor, grad_in_feat: torch.Tensor, grad_out_feat: torch.Tensor,
+                                      kernel: torch.Tensor, grad_kernel: torch.Tensor, neighbor_map: torch.Tensor,
+                                      neighbor_offset, transpose: bool = False) -> None:
+    """Gradients of the gather-scatter convolution, written into ``grad_in_feat`` and ``grad_kernel``
+    (torchsparse/backend/convolution/convolution_gather_scatter_cuda.cu:640-800): the input gradient is the
+    same pair-list convolution run from the outputs back to the inputs with every W[k] transposed, the weight
+    gradient is X[in_k]^T . dY[out_k] per offset."""
+    _need_cuda(in_feat, grad_in_feat, grad_out_feat, kernel, grad_kernel, neighbor_map)
+    sizes = [int(v) for v in (neighbor_offset.tolist() if isinstance(neighbor_offset, torch.Tensor) else neighbor_offset)]
+    nbmaps = neighbor_map.int().contiguous()
+    n_a, n_b = (grad_out_feat.shape[0], in_feat.shape[0]) if transpose else (in_feat.shape[0], grad_out_feat.shape[0])
+    masks = build_mask_from_kmap(n_a, n_b, nbmaps, torch.tensor(sizes, dtype=torch.int32, device=nbmaps.device))
+    gx = conv_forward_gather_scatter_cuda(grad_out_feat.to(kernel.dtype), kernel.transpose(1, 2).contiguous(), nbmaps,
+                                          sizes, masks[0], masks[1], in_feat.shape[0], transpose=not transpose,
+                                          allow_tf32=False)
+    grad_in_feat.copy_(gx)
+    grad_kernel.copy_(conv_backward_wgrad_pairs_cuda(grad_out_feat, in_feat, nbmaps, sizes, transpose))
 
 
 def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,
