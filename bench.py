@@ -868,7 +868,17 @@ def main():
     ap.add_argument("--streams", type=int, default=4,
                     help="engines (each with its own stream and graph) that consecutive scans alternate between")
     ap.add_argument("--unsorted", action="store_true", help="run on the kernel maps as built (no row-sorted copies)")
+    ap.add_argument("--gather", type=int, default=0, choices=[0, 2],
+                    help="gathered operand of the conv kernel: 0 = cp.async by the gather warps (default), 2 = copy engine (TMA gather4)")
+    ap.add_argument("--max-offsets", type=int, default=0,
+                    help="split tiles of the sorted maps with more kernel offsets than this into parts (0: library default)")
     args = ap.parse_args()
+    if args.max_offsets:
+        from torchsparse_b200 import backend as _backend
+        _backend.split_max_offsets = args.max_offsets
+    if args.gather:
+        from torchsparse_b200 import backend as _backend
+        _backend.igemm_tuning["gather"] = args.gather
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

@@ -249,6 +249,8 @@ int64_t tsb_map_items_max(int64_t rows, int32_t kvol, int32_t max_offsets);
  * each take an equal share of its offsets: {row tile, offset mask of the part, part | parts << 8 | first
  * scratch slot << 16, 0} (third word 0 for a whole tile).  Each part of a split tile owns one slot (128 rows x
  * cout fp32) of the convolution's scratch; tiles are split only while slots remain (max_slots, at most 32767).
+ * The table lists the items by weight class (offsets per item >= 14, >= 7, >= 3, fewer), heaviest class first and
+ * in tile order inside a class: the convolution's CTAs take items in table order, so the long ones start first.
  * The convolution spreads the parts over its CTAs and adds their slots in part order (tsb_igemm_desc.items). */
 int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int64_t valid_n,
                       const int32_t* valid_n_dev, int32_t* reorder_loc, int32_t* map_cm, uint32_t* tile_mask,
@@ -350,7 +352,11 @@ int tsb_map_tile_mask(const int32_t* map, int64_t n_rows, int32_t kvol, int64_t 
  *                      itself; the part that counts last adds the slots in part order and runs the epilogue,
  *                      so results do not depend on the schedule
  *   cfg_*              launch-configuration overrides for tuning runs (N tile, 128-byte channel chunks
- *                      per pipeline stage, stages, CTAs per SM); 0 = chosen by the library
+ *                      per pipeline stage, stages, CTAs per SM); 0 = chosen by the library.  cfg_gather picks
+ *                      how the gathered operand reaches shared memory: 0 or 1 = by 16-byte cp.async of eight
+ *                      gather warps (the default: faster on B200), 2 = by the copy engine (TMA gather4, four
+ *                      feature rows per copy, zeros for a missing neighbour; same results up to the order of
+ *                      the fp32 sums when a two-matrix input is not cut at a multiple of 128 bytes)
  * Tensor-core shapes only (see above); other shapes return TSB_ERR_UNSUPPORTED. */
 typedef struct tsb_igemm_desc {
   uint32_t struct_bytes;
@@ -382,6 +388,8 @@ typedef struct tsb_igemm_desc {
   int64_t n_items;
   float* split_scratch;
   int32_t* split_flags;
+  int32_t cfg_gather;
+  int32_t reserved0;
 } tsb_igemm_desc;
 int tsb_conv_igemm_run(const tsb_igemm_desc* desc, tsb_stream_t stream);
 

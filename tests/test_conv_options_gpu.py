@@ -68,30 +68,38 @@ def test_sorted_cm_artefacts_are_a_permutation_of_the_map():
     want = np.array([sum(1 << k for k in np.nonzero(valid[:, t * 128:(t + 1) * 128].any(1))[0])
                      for t in range(m.shape[0] // 128)], dtype=np.uint32)
     assert np.array_equal(tmask, want)
-    # the work-item table: every tile once, its offsets divided among ceil(count / 4) consecutive parts
+    # the work-item table: every tile once, its offsets divided among ceil(count / 4) consecutive parts; the
+    # items are grouped by weight class (offsets per item: >= 14, >= 7, >= 3, fewer), heaviest class first, and
+    # keep the tile order inside a class
     items = sm.items.cpu().numpy()[: int(sm.n_items.item())]
     assert len(items) <= sm.n_items_max
-    pos = slot = 0
+    slot = 0
     budget = m.shape[0] // 128                          # scratch slots: one per tile of the map
+    expected = []                                       # (class, tile, parts, first slot)
     for t, mask in enumerate(want):
         pc = bin(int(mask)).count("1")
         parts = wanted = max(1, -(-pc // 4))
         if parts > 1 and slot + parts > budget:        # beyond the scratch slots: the tile stays whole
             parts = 1
+        per = -(-pc // parts)
+        cls = 0 if per >= 14 else 1 if per >= 7 else 2 if per >= 3 else 3
+        expected.append((cls, t, parts, slot))
+        slot += wanted if wanted > 1 else 0             # slots are numbered as if every heavy tile were split
+    pos = 0
+    for cls, t, parts, slot0 in sorted(expected, key=lambda e: e[0]):      # a stable sort
         rows = items[pos: pos + parts]
         assert (rows[:, 0] == t).all()
         got_mask = 0
         for j, r in enumerate(rows):
             pm = int(r[1]) & 0xffffffff
-            assert pm and (pm & got_mask) == 0 and (parts == 1 or bin(pm).count("1") <= 4)
+            assert (pm or not want[t]) and (pm & got_mask) == 0 and (parts == 1 or bin(pm).count("1") <= 4)
             got_mask |= pm
             if parts > 1:
-                assert int(r[2]) & 0xffff == (j | (parts << 8)) and int(r[2]) >> 16 == slot
+                assert int(r[2]) & 0xffff == (j | (parts << 8)) and int(r[2]) >> 16 == slot0
             else:
                 assert int(r[2]) == 0
-        assert got_mask == int(mask)
+        assert got_mask == int(want[t])
         pos += parts
-        slot += wanted if wanted > 1 else 0             # slots are numbered as if every heavy tile were split
     assert pos == len(items)
 
 
@@ -210,3 +218,37 @@ def test_split_sorted_on_tensor_cores_fp16():
     x = ts.SparseTensor(f, torch.from_numpy(coords).cuda())
     y = F.conv3d(x, w, 3, None, 1, 1, config=cfg)
     assert rel_l2(y.feats.float().cpu().numpy(), want) < TOL
+
+
+@pytest.mark.parametrize("cin,cout,c1", [(64, 64, 0), (96, 96, 0), (8, 32, 0), (128, 96, 96), (384, 256, 256), (40, 48, 24)])
+def test_copy_engine_gather_equals_cp_async_gather(cin, cout, c1):
+    """The two ways the gathered operand reaches shared memory (TMA gather4 by one producer warp, 16-byte cp.async by
+    eight gather warps) give the same rows: bit-identical for one feature matrix (same K order), within fp16
+    rounding for a two-matrix input whose first part is not a multiple of 64 channels (the chunks are cut per
+    matrix with the copy engine, so the fp32 sums are added in another order)."""
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(cin + cout + c1)
+    coords = random_coords(rng, 3000, (20, 20, 20), 2)
+    n = coords.shape[0]
+    km = ko.build_kmap(coords, 3, 1, 1)
+    omap = torch.from_numpy(km["out_in_map"]).cuda()
+    x = torch.from_numpy(rng.standard_normal((n, cin)).astype(np.float32)).cuda().half()
+    w = torch.from_numpy((rng.standard_normal((27, cin, cout)) * 0.1).astype(np.float32)).cuda().half()
+    kw = {}
+    feats = x
+    if c1:
+        feats, kw = x[:, :c1].contiguous(), {"in_feats2": x[:, c1:].contiguous()}
+    outs = []
+    try:
+        for mode in (2, 1):
+            backend.igemm_tuning["gather"] = mode
+            outs.append(backend.conv_forward_implicit_gemm_cuda(feats, w, omap, n, cout, **kw))
+    finally:
+        backend.igemm_tuning["gather"] = 0
+    want = ko.conv_from_map(x.float().cpu().numpy(), w.float().cpu().numpy(), km["out_in_map"], n)
+    assert rel_l2(outs[0].float().cpu().numpy(), want) < TOL
+    if c1 % 64 == 0:
+        assert torch.equal(outs[0], outs[1])
+    else:
+        assert rel_l2(outs[0].float().cpu().numpy(), outs[1].float().cpu().numpy()) < 1e-3

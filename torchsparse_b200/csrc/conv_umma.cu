@@ -49,6 +49,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -67,10 +68,10 @@ constexpr int kGatherThreads = kGatherWarps * 32;
 constexpr int kRowsPerPass = kGatherThreads / 8;   // rows covered by one copy of every gather thread (32)
 constexpr int kCopies = kTileM / kRowsPerPass;     // copies per gather thread per K block (4)
 constexpr int kEpilogueWarps = 4;      // warps 8..11: warp % 4 = TMEM lane quarter
-constexpr int kTmaWarp = 12;
-constexpr int kMmaWarp = 13;
-constexpr int kSchedWarp = 14;
 constexpr int kThreads = 480;
+// The TMA-gather variant keeps the role order with a gather group of four warps (one producer, three spares):
+constexpr int kGatherWarpsTma = 4;
+constexpr int kThreadsTma = (kGatherWarpsTma + kEpilogueWarps + 3) * 32;   // 352
 constexpr int kRing = 4;               // scheduler ring: (work item, offset mask) published ahead of the other roles
 constexpr int kMaxStages = 8;
 constexpr int kMaxKvolUmma = 32;
@@ -100,14 +101,18 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread is parked in hardware until the phase completes (it resumes at
+// once then) or the hint runs out.  Without the hint a failed try comes back after ~100 cycles, and the dozen
+// waiting roles of a CTA spend more issue slots on polling than the working roles get for their instructions.
+constexpr uint32_t kSuspendHintNs = 1000000u;   // 1 ms
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -332,6 +337,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       : "r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+// TMA gather of four rows of a 2-D tensor (box = 128 bytes of columns x 1 row): the rows land one after the other,
+// 128B-swizzled by their shared-memory address; a row index outside the tensor (-1: no neighbour) is filled with
+// zeros and still counted in bytes on the mbarrier.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, uint32_t bar, int col, int4 rows) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :
+      : "r"(dst), "l"(tmap), "r"(bar), "r"(col), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w)
+      : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -341,6 +356,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ int ld_map_entry(const int* p) {
   int v;
   asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int4 ld_map_entry4(const int* p) {
+  int4 v;
+  asm volatile("ld.global.nc.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
 // The next (work item, offset mask) of the scheduler ring, read by lane 0 and handed to the whole warp; the
@@ -372,10 +392,13 @@ __device__ __forceinline__ bool ring_take(uint64_t* s_full, uint64_t* s_empty, c
 //   stage ring      (p.stages)  A+B operands of one K block      full[] / empty[]
 //   scheduler ring  (kRing)     work item + offset mask           sched_full[] / sched_empty[]
 //   accumulator     (2)         TMEM column ranges                acc_full[] / acc_empty[]
-template <typename T>
-__global__ void __launch_bounds__(kThreads, 2)
-igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map) {
+template <typename T, bool kTma>
+__global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 2)
+igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+                  const __grid_constant__ CUtensorMap x2_map) {
   constexpr bool kTF32 = sizeof(T) == 4;
+  constexpr int kGW = kTma ? kGatherWarpsTma : kGatherWarps;     // warps of the gather group
+  constexpr int kTmaWarp = kGW + kEpilogueWarps, kMmaWarp = kTmaWarp + 1, kSchedWarp = kTmaWarp + 2;
   constexpr int kChunk = kRowBytes / (int)sizeof(T);     // channels per 128-byte chunk
   constexpr int kStepK = 32 / (int)sizeof(T);            // channels per MMA instruction (32 bytes of K)
   extern __shared__ uint8_t smem_raw[];
@@ -403,19 +426,37 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   const int stage_bytes = p.cpb * (kABytes + b_bytes);
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t acc_cols = p.acc_cols;            // TMEM columns of one accumulator (power of two)
-  const int chunks = (p.cin + kChunk - 1) / kChunk;
+  // Channel chunks of a kernel offset.  cp.async gather: the concatenated channels cut every 128 bytes.  TMA gather:
+  // the chunks of the first feature matrix, then those of the second (a box never spans both), the last chunk
+  // of each possibly narrower; the weight columns of a chunk start where its channels start in the concatenation.
+  const int chunks1 = kTma ? (p.c1 + kChunk - 1) / kChunk : 0;
+  const int chunks = kTma ? chunks1 + (p.cin - p.c1 + kChunk - 1) / kChunk : (p.cin + kChunk - 1) / kChunk;
   const int groups = (chunks + p.cpb - 1) / p.cpb;       // K blocks per kernel offset
+  // chunk c: first column inside its feature matrix, first weight column, MMA instructions (32 bytes of K each)
+  auto chunk_geometry = [&](int c, int& col_src, int& col_w, int& steps) {
+    if constexpr (kTma) {
+      const bool second = c >= chunks1;
+      col_src = (second ? c - chunks1 : c) * kChunk;
+      col_w = second ? p.c1 + col_src : col_src;
+      const int width = min(kChunk, (second ? p.cin - p.c1 : p.c1) - col_src);
+      steps = (width + kStepK - 1) / kStepK;
+    } else {
+      col_src = col_w = c * kChunk;
+      steps = (min(kChunk, p.cin - col_src) + kStepK - 1) / kStepK;
+    }
+  };
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
       // every gather thread (attached to its copies) + the weight loader's arrive.expect_tx
-      mbar_init(smem_u32(&s_full[s]), kGatherThreads + 1);
+      // TMA gather: the producer's and the weight loader's arrive.expect_tx
+      mbar_init(smem_u32(&s_full[s]), kTma ? 2 : kGatherThreads + 1);
       mbar_init(smem_u32(&s_empty[s]), 1);   // tcgen05.commit
     }
     for (int b = 0; b < kRing; ++b) {
       mbar_init(smem_u32(&s_sched_full[b]), 1);
       // readers of a ring slot: gather warps, weight loader, MMA warp, epilogue warps
-      mbar_init(smem_u32(&s_sched_empty[b]), kGatherWarps + 2 + kEpilogueWarps);
+      mbar_init(smem_u32(&s_sched_empty[b]), (kTma ? 1 : kGatherWarps) + 2 + kEpilogueWarps);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&s_acc_full[b]), 1);
@@ -440,7 +481,89 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
   int n_work = tiles_m * tiles_n;
   if (p.items) n_work = max(0, min(__ldg(p.n_items_dev), p.n_items)) * tiles_n;
 
-  if (warp < kGatherWarps) {
+  if (kTma && warp < kGW) {
+    // ------------------------------------------------------------ TMA producer (A operand), warp 0 of the group
+    // Lane l owns rows 4 l .. 4 l + 3 of the tile: it reads their four map entries (one 16-byte load from a
+    // column-major map) one offset ahead and issues one gather4 copy per channel chunk; the copy engine fetches
+    // the 128-byte row slices and writes zeros for a missing neighbour.  One warp instruction moves a whole
+    // 16 KiB chunk, so the A operand costs the SM a handful of issue slots per K block.
+    if (warp == 0) {
+      const uint32_t full0 = smem_u32(&s_full[0]), empty0 = smem_u32(&s_empty[0]);
+      const bool vec_map = p.map && p.map_rs == 1 && (p.map_cs & 3) == 0 && (reinterpret_cast<uintptr_t>(p.map) & 15) == 0;
+      uint32_t stage = 0, phase = 0;
+      bool first_pass = true, ok = true;
+      int it = 0;
+      uint32_t km = 0;
+      int row0 = 0;
+#ifdef TSB_TRACE_BUILD
+      int blk = 0;
+#endif
+      auto next_offset = [&](int4& src) -> bool {
+        while (km == 0) {
+          int w, aux;
+          uint32_t m;
+          if (!ring_take(s_sched_full, s_sched_empty, s_tile, s_kmask, s_aux, it, lane, w, m, aux)) {
+            if (lane == 0) atomicExch(p.error, kErrSchedWait);
+            s_abort = 1;
+            ok = false;
+            return false;
+          }
+          ++it;
+          if (w < 0 || s_abort) return false;
+          row0 = (w / tiles_n) * kTileM;
+          km = m;
+          if (km == 0 && lane == 0) mbar_arrive(smem_u32(&s_req));   // nothing to copy for this item: ask for the next
+        }
+        const int k = __ffs(km) - 1;
+        km &= km - 1;
+        // the item's last offset is being fetched: ask the scheduler for the next item (see the cp.async variant)
+        if (km == 0 && lane == 0) mbar_arrive(smem_u32(&s_req));
+        const int r = row0 + 4 * lane;
+        if (!p.map) {
+          src = make_int4(r < n_out ? r : -1, r + 1 < n_out ? r + 1 : -1, r + 2 < n_out ? r + 2 : -1, r + 3 < n_out ? r + 3 : -1);
+        } else if (vec_map) {
+          src = ld_map_entry4(p.map + (long long)k * p.map_cs + r);
+        } else {
+          const int* e = p.map + (long long)r * p.map_rs + (long long)k * p.map_cs;
+          src = make_int4(ld_map_entry(e), ld_map_entry(e + p.map_rs), ld_map_entry(e + 2 * p.map_rs), ld_map_entry(e + 3 * p.map_rs));
+        }
+        return true;
+      };
+      int4 src, nxt = make_int4(-1, -1, -1, -1);
+      bool have = next_offset(src);
+      while (have && ok) {
+        const bool have_next = next_offset(nxt);       // in flight while this offset is copied
+        if (!ok) break;
+        for (int g = 0; g < groups && ok; ++g) {
+          if (lane == 0) TSB_TRACE_HOT(0, blk);
+          if (!first_pass && !mbar_wait_warp(empty0 + stage * 8, phase ^ 1u, lane)) {
+            if (lane == 0) atomicExch(p.error, kErrEmptyWait);
+            s_abort = 1;
+            ok = false;
+            break;
+          }
+          if (lane == 0) TSB_TRACE_HOT(1, blk);
+          const int c_lo = g * p.cpb, c_hi = min(c_lo + p.cpb, chunks);
+          const uint32_t bar = full0 + stage * 8;
+          if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)((c_hi - c_lo) * kABytes));
+          __syncwarp();
+          const uint32_t a_dst = smem_base + stage * (uint32_t)stage_bytes + (uint32_t)lane * (4u * kRowBytes);
+          for (int c = c_lo; c < c_hi; ++c) {
+            int col_src, col_w, steps;
+            chunk_geometry(c, col_src, col_w, steps);
+            tma_gather4(a_dst + (uint32_t)(c - c_lo) * kABytes, c >= chunks1 ? &x2_map : &x_map, bar, col_src, src);
+          }
+          if (lane == 0) TSB_TRACE_HOT(2, blk);
+#ifdef TSB_TRACE_BUILD
+          ++blk;
+#endif
+          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+        }
+        src = nxt;
+        have = have_next;
+      }
+    }
+  } else if (!kTma && warp < kGW) {
     // ------------------------------------------------------------ gather warps (A operand)
     // Thread t copies the 16-byte granule (t & 7) of rows (t >> 3) + 32 j, j = 0..3, of every chunk:
     // a warp instruction covers four whole 128-byte row slices.  The four map entries of an offset
@@ -485,6 +608,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       // The item's last offset is now being fetched: time to ask the scheduler for the next item, so that it
       // arrives while the remaining copies of this one are issued.  Asking any earlier would let every CTA hold
       // several items from the start, and with a few items per CTA the dynamic assignment would balance nothing.
+      // (Measured: asking two offsets earlier, or fetching map entries two offsets ahead, changes nothing.)
       if (km == 0 && tid == 0) mbar_arrive(smem_u32(&s_req));
 #pragma unroll
       for (int j = 0; j < kCopies; ++j) {
@@ -544,7 +668,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
       have = have_next;
     }
     cp_async_wait_all();   // nothing of this thread may still be writing shared memory at exit
-  } else if (warp < kGatherWarps + kEpilogueWarps) {
+  } else if (warp < kGW + kEpilogueWarps) {
     // ------------------------------------------------------------ epilogue warps
     // warp q reads TMEM lanes 32 q .. 32 q + 31 = its 32 output rows, all columns of the tile
     const int quarter = warp & 3;
@@ -654,6 +778,9 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         break;
       }
       tc_fence_after();
+#ifdef TSB_TRACE_BUILD
+      if (warp == kGW && lane == 0 && p.trace && (int)blockIdx.x == p.trace_cta && it < 256) p.trace[5120 + it] = clk();
+#endif
       const int r = quarter * 32 + lane;
       const int64_t grow = (int64_t)row0 + r;
       int64_t dst_row = -1;
@@ -701,7 +828,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           s_abort = 1;
           break;
         }
-        if (warp == kGatherWarps && lane == 0) {
+        if (warp == kGW && lane == 0) {
           int* flag = p.split_flags + w;
           const int before = atomicAdd(flag, 1);
           __threadfence();
@@ -730,7 +857,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         }
       }
 #ifdef TSB_TRACE_BUILD
-      if (warp == kGatherWarps && lane == 0) TSB_TRACE_HOT(7, it + 1);   // item written out (first epilogue warp)
+      if (warp == kGW && lane == 0) TSB_TRACE_HOT(7, it + 1);   // item written out (first epilogue warp)
 #endif
     }
   } else if (warp == kSchedWarp) {
@@ -750,7 +877,13 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           s_abort = 1;
           break;
         }
+#ifdef TSB_TRACE_BUILD
+        if (p.trace && (int)blockIdx.x == p.trace_cta && i < 256) p.trace[4096 + i * 4] = clk();       // asked
+#endif
         const int w = atomicAdd(p.sched, 1);
+#ifdef TSB_TRACE_BUILD
+        if (p.trace && (int)blockIdx.x == p.trace_cta && i < 256) p.trace[4096 + i * 4 + 1] = clk() + (w & 0);   // counted
+#endif
         if (w >= n_work || s_abort) {
           s_tile[slot] = -1;                  // tells the other roles that the CTA is done
           mbar_arrive(smem_u32(&s_sched_full[slot]));
@@ -770,6 +903,19 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
         s_tile[slot] = item;
         s_aux[slot] = aux;
         mbar_arrive(smem_u32(&s_sched_full[slot]));
+#ifdef TSB_TRACE_BUILD
+        if (p.trace && blockIdx.x < 1024) {       // every CTA: items taken, offsets taken, wall clock of the last claim
+          p.trace[6144 + 4 * blockIdx.x] += 1;
+          p.trace[6144 + 4 * blockIdx.x + 1] += __popc(mask);
+          p.trace[6144 + 4 * blockIdx.x + 2] = (long long)global_ns();
+        }
+#endif
+#ifdef TSB_TRACE_BUILD
+        if (p.trace && (int)blockIdx.x == p.trace_cta && i < 256) {
+          p.trace[4096 + i * 4 + 2] = clk();       // published
+          p.trace[4096 + i * 4 + 3] = (long long)mask;
+        }
+#endif
       }
     }
   } else if (warp == kTmaWarp) {
@@ -805,8 +951,11 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
           if (elect_one()) {
             mbar_arrive_expect_tx(bar, (uint32_t)((c_hi - c_lo) * b_bytes));
             const uint32_t b_dst = smem_base + stage * (uint32_t)stage_bytes + (uint32_t)p.cpb * kABytes;
-            for (int c = c_lo; c < c_hi; ++c)
-              tma_load_2d(b_dst + (uint32_t)((c - c_lo) * b_bytes), &w_map, bar, c * kChunk, wrow);
+            for (int c = c_lo; c < c_hi; ++c) {
+              int col_src, col_w, steps;
+              chunk_geometry(c, col_src, col_w, steps);
+              tma_load_2d(b_dst + (uint32_t)((c - c_lo) * b_bytes), &w_map, bar, col_w, wrow);
+            }
           }
           __syncwarp();
           if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
@@ -825,7 +974,6 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
     const uint32_t b_units = (uint32_t)b_bytes >> 4;
     const uint32_t b_first = (uint32_t)p.cpb * a_units;                 // first weight chunk of a stage
     const uint32_t base_units = smem_base >> 4;
-    const int last_steps = ((p.cin - (chunks - 1) * kChunk) + kStepK - 1) / kStepK;
     uint32_t stage = 0, phase = 0;
     int acc_count = 0;
     bool ok = true;
@@ -876,7 +1024,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map)
             for (int c = c_lo; c < c_hi; ++c) {
               const uint32_t a_lo = ((st_units + (uint32_t)(c - c_lo) * a_units) & 0x3FFFu) | lo_flag;
               const uint32_t b_lo = ((st_units + b_first + (uint32_t)(c - c_lo) * b_units) & 0x3FFFu) | lo_flag;
-              const int steps = (c == chunks - 1) ? last_steps : 4;
+              int col_src, col_w, steps;
+              chunk_geometry(c, col_src, col_w, steps);
               // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
 #pragma unroll
               for (int st = 0; st < 4; ++st) {
@@ -1080,12 +1229,12 @@ int* sched_slot_of(cudaStream_t stream, int dev) {
 // per-device facts and one-time settings, looked up / applied on first use under a lock
 struct DeviceState {
   int sms = 0;
-  bool attr_set[3] = {false, false, false};
+  bool attr_set[2][3] = {{false, false, false}, {false, false, false}};
 };
 std::mutex g_dev_mu;
 DeviceState g_dev[kMaxDevices];
 
-template <typename T>
+template <typename T, bool kTma>
 int prepare_device(int dev, int fmt, int* sms) {
   std::lock_guard<std::mutex> lock(g_dev_mu);
   DeviceState& d = g_dev[dev];
@@ -1094,15 +1243,26 @@ int prepare_device(int dev, int fmt, int* sms) {
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = kSmCount;
     d.sms = v;
   }
-  if (!d.attr_set[fmt]) {
-    TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    d.attr_set[fmt] = true;
+  if (!d.attr_set[kTma][fmt]) {
+    TSB_CUDA_TRY(cudaFuncSetAttribute(igemm_umma_kernel<T, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    d.attr_set[kTma][fmt] = true;
   }
   *sms = d.sms;
   return TSB_OK;
 }
 
 int chunks_of(int cin, int dtype) { return (int)cdiv((int64_t)cin * (int64_t)dtype_size(dtype), kRowBytes); }
+
+// The A operand is copied by the gather warps (cp.async) unless the caller asks for the copy engine
+// (cfg_gather == 2, TMA gather4).  Measured on B200: the copy engine delivers one 128-byte row slice per ~9 cycles
+// per SM whatever the number of issuing warps, CTAs per SM or chunks in flight (0.6 us per 16 KiB chunk), the
+// gather warps one per ~2-3 cycles, and whole layers run 2.0-2.4x slower on the copy engine; it stays as an option.
+bool use_tma_gather(const IgemmArgs& a) { return a.cfg_gather == 2 && a.n_in > 0; }
+// channel chunks of a kernel offset: per feature matrix with the TMA gather (a box reads one matrix)
+int chunks_for(const IgemmArgs& a) {
+  if (use_tma_gather(a) && a.x2) return chunks_of(a.c1, a.dtype) + chunks_of(a.cin - a.c1, a.dtype);
+  return chunks_of(a.cin, a.dtype);
+}
 
 }  // namespace
 
@@ -1130,7 +1290,7 @@ bool igemm_umma_supported(const IgemmArgs& a) {
        (uintptr_t)a.packed_w | (uintptr_t)a.acc_in | (uintptr_t)a.acc_out) & 15)
     return false;
   LaunchConfig want{a.cfg_n_tile, a.cfg_cpb, a.cfg_stages, a.cfg_ctas}, got;
-  return pick_config(a.cout, chunks_of(a.cin, a.dtype), want, &got);
+  return pick_config(a.cout, chunks_for(a), want, &got);
 }
 
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype) {
@@ -1225,7 +1385,8 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   if (k_lo < 0 || k_hi > a.kvol) return TSB_ERR_BAD_ARG;
   p.k_range = (k_hi >= 32 ? 0xffffffffu : ((1u << k_hi) - 1u)) & ~((1u << k_lo) - 1u);
   LaunchConfig want{a.cfg_n_tile, a.cfg_cpb, a.cfg_stages, a.cfg_ctas}, cfg;
-  if (!pick_config(a.cout, chunks_of(a.cin, a.dtype), want, &cfg)) return TSB_ERR_UNSUPPORTED;
+  if (!pick_config(a.cout, chunks_for(a), want, &cfg)) return TSB_ERR_UNSUPPORTED;
+  const bool tma = use_tma_gather(a);
   p.n_tile = cfg.n_tile; p.cpb = cfg.cpb; p.stages = cfg.stages;
   p.acc_cols = acc_cols_for(cfg.n_tile);
   p.relu = a.relu;
@@ -1233,10 +1394,12 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
   const size_t smem = smem_bytes_for(cfg.n_tile, cfg.stages, cfg.cpb);
   int sms = kSmCount;
   {
-    int rc = prepare_device<T>(dev, p.ab_format, &sms);
+    int rc = tma ? prepare_device<T, true>(dev, p.ab_format, &sms) : prepare_device<T, false>(dev, p.ab_format, &sms);
     if (rc != TSB_OK) return rc;
   }
-  CUtensorMap w_map;
+  CUtensorMap w_map, x_map, x2_map;
+  memset(&x_map, 0, sizeof(x_map));
+  memset(&x2_map, 0, sizeof(x2_map));
   {
     auto encode = tensor_map_encoder();
     if (!encode) return TSB_ERR_UNSUPPORTED;
@@ -1253,11 +1416,30 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
+    if (tma) {
+      // feature matrices as 2-D tensors [n_in rows, channels]; box = 128 bytes of channels x 1 row (gather4 takes
+      // four row coordinates); columns past the matrix and rows outside it read as zeros
+      cuuint32_t xbox[2] = {chunk, 1};
+      const int c2 = a.cin - p.c1;
+      cuuint64_t xdim[2] = {(cuuint64_t)p.c1, (cuuint64_t)a.n_in};
+      cuuint64_t xstride[1] = {(cuuint64_t)p.c1 * sizeof(T)};
+      r = encode(&x_map, dt, 2, const_cast<void*>(a.x), xdim, xstride, xbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
+      if (a.x2) {
+        cuuint64_t x2dim[2] = {(cuuint64_t)c2, (cuuint64_t)a.n_in};
+        cuuint64_t x2stride[1] = {(cuuint64_t)c2 * sizeof(T)};
+        r = encode(&x2_map, dt, 2, const_cast<void*>(a.x2), x2dim, x2stride, xbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
+      }
+    }
   }
   const int64_t n_work = (a.items ? a.n_items : cdiv(a.n_out, kTileM)) * cdiv(a.cout, cfg.n_tile);
   const int64_t slots = (int64_t)cfg.ctas * sms;
   const int grid = (int)(n_work < slots ? n_work : slots);
-  igemm_umma_kernel<T><<<grid, kThreads, smem, s>>>(p, w_map);
+  if (tma) igemm_umma_kernel<T, true><<<grid, kThreadsTma, smem, s>>>(p, w_map, x_map, x2_map);
+  else igemm_umma_kernel<T, false><<<grid, kThreads, smem, s>>>(p, w_map, x_map, x2_map);
   TSB_LAUNCH_CHECK();
   return TSB_OK;
 }

@@ -673,6 +673,12 @@ reorder_cm_kernel(const int* __restrict__ map, const int* __restrict__ loc, int6
   if (threadIdx.x == 0) tile_mask[blockIdx.x] = s_mask[0] | s_mask[1] | s_mask[2] | s_mask[3];
 }
 
+// Weight classes of work items (offsets of the item): 0 = heaviest.  Four classes order the table closely enough to
+// "longest first" and cost four block scans per 1024 tiles.
+constexpr int kItemClasses = 4;
+__device__ __forceinline__ int item_class(int offsets) { return offsets >= 14 ? 0 : offsets >= 7 ? 1 : offsets >= 3 ? 2 : 3; }
+
+
 // Work-item table of a map's tiles: a tile with more than `max_offsets` offsets becomes several consecutive
 // items ("parts") that each take an equal share of its offsets, so that no single item is much longer than
 // the others; every part of a split tile owns one slot of the convolution's fp32 scratch, and tiles are split
@@ -684,45 +690,67 @@ build_items_kernel(const unsigned* __restrict__ tile_mask, int64_t valid_n, cons
                    int max_offsets, int max_slots, int4* __restrict__ items, int* __restrict__ n_items) {
   typedef cub::BlockScan<int, 1024> Scan;
   __shared__ typename Scan::TempStorage tmp;
-  __shared__ int s_items, s_slots;
+  __shared__ int s_slots;
+  __shared__ int s_class_items[kItemClasses];   // pass 1: items of each weight class; pass 2: next free entry of the class
   if (valid_n_dev) valid_n = max((int64_t)0, min((int64_t)__ldg(valid_n_dev), valid_n));
   const int tiles = (int)((valid_n + 127) / 128);
-  if (threadIdx.x == 0) { s_items = 0; s_slots = 0; }
-  __syncthreads();
-  for (int t0 = 0; t0 < tiles; t0 += 1024) {
-    const int t = t0 + threadIdx.x;
-    const unsigned m = t < tiles ? tile_mask[t] : 0u;
-    const int pc = __popc(m);
-    int parts = t < tiles ? max(1, (pc + max_offsets - 1) / max_offsets) : 0;
-    // slots: a tile is split only if its slots fit below max_slots
-    int slot_first, slot_total;
-    Scan(tmp).ExclusiveSum(parts > 1 ? parts : 0, slot_first, slot_total);
-    const int slot_base = s_slots;
-    __syncthreads();
-    const int slot0 = slot_base + slot_first;
-    if (parts > 1 && slot0 + parts > max_slots) parts = 1;
-    int first, total;
-    Scan(tmp).ExclusiveSum(parts, first, total);
-    const int base = s_items;
-    if (t < tiles) {
-      const int per = (pc + parts - 1) / parts;      // offsets per part (the last part may hold fewer)
-      unsigned rest = m;
-      for (int j = 0; j < parts; ++j) {
-        unsigned mj = 0;
-        for (int c = 0; c < per && rest; ++c) {
-          const unsigned low = rest & (0u - rest);
-          mj |= low;
-          rest ^= low;
-        }
-        if (parts == 1) mj = m;
-        items[base + first + j] = make_int4(t, (int)mj, parts > 1 ? (j | (parts << 8) | (slot0 << 16)) : 0, 0);
+  // Items are written heaviest class first (the persistent CTAs take them in table order, and a long item that
+  // starts last leaves every other CTA idle while it runs); inside a class they keep the tile order, so the table
+  // is the same on every run.  Pass 1 decides how every tile is split and counts the items of each class, pass 2
+  // writes them.
+  for (int pass = 0; pass < 2; ++pass) {
+    if (threadIdx.x == 0) s_slots = 0;
+    if (pass == 1 && threadIdx.x == 0) {
+      int at = 0;
+      for (int c = 0; c < kItemClasses; ++c) {   // class 0 = heaviest
+        const int cnt = s_class_items[c];
+        s_class_items[c] = at;
+        at += cnt;
       }
+      *n_items = at;
+    }
+    if (pass == 0 && threadIdx.x < kItemClasses) s_class_items[threadIdx.x] = 0;
+    __syncthreads();
+    for (int t0 = 0; t0 < tiles; t0 += 1024) {
+      const int t = t0 + threadIdx.x;
+      const unsigned m = t < tiles ? tile_mask[t] : 0u;
+      const int pc = __popc(m);
+      int parts = t < tiles ? max(1, (pc + max_offsets - 1) / max_offsets) : 0;
+      // slots: a tile is split only if its slots fit below max_slots
+      int slot_first, slot_total;
+      Scan(tmp).ExclusiveSum(parts > 1 ? parts : 0, slot_first, slot_total);
+      const int slot_base = s_slots;
+      __syncthreads();
+      const int slot0 = slot_base + slot_first;
+      if (parts > 1 && slot0 + parts > max_slots) parts = 1;
+      const int per = parts ? (pc + parts - 1) / parts : 0;      // offsets per part (the last part may hold fewer)
+      const int cls = item_class(per);
+      for (int c = 0; c < kItemClasses; ++c) {
+        int first, total;
+        Scan(tmp).ExclusiveSum(cls == c ? parts : 0, first, total);
+        const int base = s_class_items[c];
+        __syncthreads();
+        if (pass == 1 && t < tiles && cls == c) {
+          unsigned rest = m;
+          for (int j = 0; j < parts; ++j) {
+            unsigned mj = 0;
+            for (int q = 0; q < per && rest; ++q) {
+              const unsigned low = rest & (0u - rest);
+              mj |= low;
+              rest ^= low;
+            }
+            if (parts == 1) mj = m;
+            items[base + first + j] = make_int4(t, (int)mj, parts > 1 ? (j | (parts << 8) | (slot0 << 16)) : 0, 0);
+          }
+        }
+        if (threadIdx.x == 0) s_class_items[c] = base + total;
+        __syncthreads();
+      }
+      if (threadIdx.x == 0) s_slots = slot_base + slot_total;
+      __syncthreads();
     }
     __syncthreads();
-    if (threadIdx.x == 0) { s_items = base + total; s_slots = slot_base + slot_total; }
-    __syncthreads();
   }
-  if (threadIdx.x == 0) *n_items = s_items;
 }
 
 // ------------------------------------------------------------------ pair lists
