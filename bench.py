@@ -54,6 +54,7 @@ MAX_POINTS = 144_000    # points of one scan (120k rays + 20 % box points): boun
 # voxel grid bound at 0.05 m: 2 x 80 m range in x and y, 25 m in z (sensor range of the generator, with margin)
 MAX_EXTENT = (3328, 3328, 512)
 L2_FLUSH_BYTES = 256 << 20
+CONV_GRID_SHARED = 56   # persistent CTAs per convolution launch when several engines keep the GPU busy (of 296 slots)
 C4_VOXEL = (0.1, 0.1, 0.2)
 C4_RANGE = (1080, 1080, 40)
 
@@ -251,12 +252,13 @@ def launch_counts(dims):
     return pairs, blocks
 
 
-def make_engines(model, device, n_eng, sorted_maps=True):
+def make_engines(model, device, n_eng, sorted_maps=True, conv_grid=0):
     from torchsparse_b200.nn import StaticEngine
 
     head = model.head
     return [StaticEngine(model.backbone, lambda outs: head(outs[-1].feats), max_points=MAX_POINTS, point_channels=4,
-                         voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device, sorted_maps=sorted_maps).capture()
+                         voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device, sorted_maps=sorted_maps,
+                         conv_grid=conv_grid).capture()
             for _ in range(n_eng)]
 
 
@@ -293,10 +295,10 @@ def run_ours(args, rank: int, world: int, device: torch.device):
             dist.barrier()
         torch.cuda.synchronize()
 
-    engines = make_engines(model, device, n_eng, not args.unsorted)
+    engines = make_engines(model, device, n_eng, not args.unsorted, args.conv_grid)
     # kernels of this library per replay: a further capture (weights are packed by now) runs the forward twice
     launches0 = backend.launch_count()
-    make_engines(model, device, 1, not args.unsorted)
+    make_engines(model, device, 1, not args.unsorted, args.conv_grid)
     launches_per_step = (backend.launch_count() - launches0) // 2
     comm_stream = torch.cuda.Stream(device) if world > 1 else None
     gather = PaddedGather(MAX_POINTS, NUM_CLASSES, torch.float16, device) if world > 1 else None
@@ -478,6 +480,8 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                    "engine": "one CUDA graph per scan (sizes in device memory), row-sorted column-major kernel maps"
                              if not args.unsorted else "one CUDA graph per scan, kernel maps as built",
                    "streams": n_eng,
+                   "conv_grid": (f"{args.conv_grid} persistent CTAs per convolution launch (of {2 * 148} resident slots): "
+                                 "launches of different engines run side by side" if args.conv_grid else "all resident slots"),
                    "parallelism": (f"scan-sharded x{world}, NCCL all-gather of the logits of every step"
                                    if world > 1 else "single GPU")},
         "timing": {"passes": len(passes), "steps_per_pass": args.steps,
@@ -865,14 +869,22 @@ def main():
     ap.add_argument("--transposed", action="store_true")
     ap.add_argument("--smap", action="store_true", help="layer mode: run on the row-sorted column-major map of the engines")
     ap.add_argument("--lidar-level", type=int, default=-1, help="layer mode: rows of the benchmark scan at stride 2^L")
-    ap.add_argument("--streams", type=int, default=4,
+    ap.add_argument("--streams", type=int, default=8,
                     help="engines (each with its own stream and graph) that consecutive scans alternate between")
     ap.add_argument("--unsorted", action="store_true", help="run on the kernel maps as built (no row-sorted copies)")
     ap.add_argument("--gather", type=int, default=0, choices=[0, 2],
                     help="gathered operand of the conv kernel: 0 = cp.async by the gather warps (default), 2 = copy engine (TMA gather4)")
     ap.add_argument("--max-offsets", type=int, default=0,
                     help="split tiles of the sorted maps with more kernel offsets than this into parts (0: library default)")
+    ap.add_argument("--conv-grid", type=int, default=-1,
+                    help="upper bound of the persistent CTAs of a convolution launch (0: every resident slot; "
+                         "-1: 56 when several engines share the GPU, else every slot)")
     args = ap.parse_args()
+    if args.conv_grid < 0:
+        args.conv_grid = CONV_GRID_SHARED if (args.streams > 1 and not args.layer and not args.kmap) else 0
+    if args.conv_grid and args.layer:      # the engines of the step benchmark get it as their own setting
+        from torchsparse_b200 import backend as _backend
+        _backend.igemm_tuning["grid"] = args.conv_grid
     if args.max_offsets:
         from torchsparse_b200 import backend as _backend
         _backend.split_max_offsets = args.max_offsets

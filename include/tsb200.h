@@ -356,7 +356,10 @@ int tsb_map_tile_mask(const int32_t* map, int64_t n_rows, int32_t kvol, int64_t 
  *                      how the gathered operand reaches shared memory: 0 or 1 = by 16-byte cp.async of eight
  *                      gather warps (the default: faster on B200), 2 = by the copy engine (TMA gather4, four
  *                      feature rows per copy, zeros for a missing neighbour; same results up to the order of
- *                      the fp32 sums when a two-matrix input is not cut at a multiple of 128 bytes)
+ *                      the fp32 sums when a two-matrix input is not cut at a multiple of 128 bytes).  cfg_grid
+ *                      bounds the persistent CTAs of the launch (0: every resident slot of the device); a caller
+ *                      that keeps several streams busy gives each launch a share of the device, so that launches
+ *                      of different streams run side by side instead of waiting for each other's last CTAs
  * Tensor-core shapes only (see above); other shapes return TSB_ERR_UNSUPPORTED. */
 typedef struct tsb_igemm_desc {
   uint32_t struct_bytes;
@@ -389,7 +392,7 @@ typedef struct tsb_igemm_desc {
   float* split_scratch;
   int32_t* split_flags;
   int32_t cfg_gather;
-  int32_t reserved0;
+  int32_t cfg_grid;
 } tsb_igemm_desc;
 int tsb_conv_igemm_run(const tsb_igemm_desc* desc, tsb_stream_t stream);
 

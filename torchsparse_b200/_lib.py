@@ -91,7 +91,7 @@ class IgemmDesc(C.Structure):
         ("kvol", I32), ("cin", I32), ("cout", I32), ("c1", I32), ("k_lo", I32), ("k_hi", I32),
         ("cfg_n_tile", I32), ("cfg_cpb", I32), ("cfg_stages", I32), ("cfg_ctas", I32),
         ("items", P), ("n_items_dev", P), ("n_items", I64), ("split_scratch", P), ("split_flags", P),
-        ("cfg_gather", I32), ("reserved0", I32),
+        ("cfg_gather", I32), ("cfg_grid", I32),
     ]
 
 

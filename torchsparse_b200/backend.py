@@ -544,7 +544,7 @@ def _prep_feats(in_feats: torch.Tensor, kernel: torch.Tensor, allow_fp16: bool):
 
 # Launch-configuration overrides of the tensor-core kernel for tuning runs (0 = chosen by the library):
 # N tile, 128-byte channel chunks per pipeline stage, stages, CTAs per SM.
-igemm_tuning = {"n_tile": 0, "cpb": 0, "stages": 0, "ctas": 0, "gather": 0}
+igemm_tuning = {"n_tile": 0, "cpb": 0, "stages": 0, "ctas": 0, "gather": 0, "grid": 0}
 
 
 def tile_mask_cuda(out_in_map: torch.Tensor, n_rows: int, row_stride: Optional[int] = None,
@@ -583,7 +583,7 @@ def _tile_mask_of(out_in_map: torch.Tensor, n_rows: int) -> Optional[torch.Tenso
 def _apply_tuning(d) -> None:
     d.cfg_n_tile, d.cfg_cpb = igemm_tuning["n_tile"], igemm_tuning["cpb"]
     d.cfg_stages, d.cfg_ctas = igemm_tuning["stages"], igemm_tuning["ctas"]
-    d.cfg_gather = igemm_tuning["gather"]
+    d.cfg_gather, d.cfg_grid = igemm_tuning["gather"], igemm_tuning["grid"]
 
 
 def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: Optional[torch.Tensor],

@@ -79,7 +79,7 @@ int tsb_conv_igemm_run(const tsb_igemm_desc* d, tsb_stream_t stream) {
   a.acc_in = d->acc_in; a.acc_out = d->acc_out;
   a.k_lo = d->k_lo; a.k_hi = d->k_hi;
   a.cfg_n_tile = d->cfg_n_tile; a.cfg_cpb = d->cfg_cpb; a.cfg_stages = d->cfg_stages; a.cfg_ctas = d->cfg_ctas;
-  a.cfg_gather = d->cfg_gather;
+  a.cfg_gather = d->cfg_gather; a.cfg_grid = d->cfg_grid;
   a.items = d->items; a.n_items_dev = d->n_items_dev; a.n_items = d->n_items;
   a.split_scratch = d->split_scratch; a.split_flags = d->split_flags;
   if (a.items && a.n_items > INT32_MAX) return TSB_ERR_LIMIT;

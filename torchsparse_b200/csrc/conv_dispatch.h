@@ -41,6 +41,7 @@ struct IgemmArgs {
   float* acc_out;            // fp32 [dst_rows, cout]: store the accumulator (+ acc_in) here instead of y, no epilogue
   int k_lo, k_hi;            // kernel offsets [k_lo, k_hi) covered by this launch (0, 0: all)
   int cfg_n_tile, cfg_cpb, cfg_stages, cfg_ctas;   // tuning overrides of the launch configuration (0: automatic)
+  int cfg_grid;         // upper bound of the persistent CTAs of a launch (0: every resident slot of the device)
   int cfg_gather;       // A operand: 0 / 1 = cp.async by the gather warps (default), 2 = TMA gather4 by the copy engine
   // work-item table of a map whose heavy tiles are split into parts (tsb_map_sorted_cm): int32 [n_items][4] =
   // {row tile, offset mask, part | parts << 8, 0}, its length in device memory, the fp32 running sums

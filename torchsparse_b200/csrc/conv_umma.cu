@@ -1436,7 +1436,8 @@ static int umma_launch(const IgemmArgs& a, cudaStream_t s) {
     }
   }
   const int64_t n_work = (a.items ? a.n_items : cdiv(a.n_out, kTileM)) * cdiv(a.cout, cfg.n_tile);
-  const int64_t slots = (int64_t)cfg.ctas * sms;
+  int64_t slots = (int64_t)cfg.ctas * sms;
+  if (a.cfg_grid > 0 && a.cfg_grid < slots) slots = a.cfg_grid;
   const int grid = (int)(n_work < slots ? n_work : slots);
   if (tma) igemm_umma_kernel<T, true><<<grid, kThreadsTma, smem, s>>>(p, w_map, x_map, x2_map);
   else igemm_umma_kernel<T, false><<<grid, kThreads, smem, s>>>(p, w_map, x_map, x2_map);

@@ -211,12 +211,16 @@ class StaticEngine:
     the voxel deduplication removes again.
 
     The captured launches carry the stream's scheduling slot of the convolution kernel: replays of one engine
-    must not overlap on the GPU (use one engine per stream)."""
+    must not overlap on the GPU (use one engine per stream).  `conv_grid` bounds the persistent CTAs of every
+    convolution launch (0: all resident slots of the device): with several engines kept busy on their own streams
+    a share of the device per launch (e.g. 56 of 296 slots with eight engines on a B200) lets launches of different
+    engines run side by side, where full-device launches would wait for each other's last CTAs."""
 
     def __init__(self, model: torch.nn.Module, post: Callable, *, max_points: int, point_channels: int,
                  voxel_size: float, max_extent: Sequence[int], device: torch.device,
                  dtype: torch.dtype = torch.float16, pad_channels: int = 8, sorted_maps: bool = True,
-                 stream: Optional[torch.cuda.Stream] = None, row_cap: Optional[int] = None) -> None:
+                 stream: Optional[torch.cuda.Stream] = None, row_cap: Optional[int] = None,
+                 conv_grid: int = 0) -> None:
         self.model, self.post = model, post
         self.max_points, self.c_in, self.c_pad = int(max_points), int(point_channels), int(pad_channels)
         self.voxel = (float(voxel_size),) * 3 if isinstance(voxel_size, (int, float)) else tuple(voxel_size)
@@ -225,6 +229,7 @@ class StaticEngine:
         # a strided convolution whose kernel is larger than its stride can create more outputs than inputs
         # (up to 8x for k3 s2); buffers of the coarser levels are bounded by this many rows
         self.row_cap = int(row_cap) if row_cap is not None else 2 * self.max_points
+        self.conv_grid = int(conv_grid)
         self.max_extent = tuple(int(v) for v in max_extent)
         self.stream = stream if stream is not None else torch.cuda.Stream(device)
         self.points = torch.zeros((self.max_points, self.c_in), dtype=torch.float32, device=device)
@@ -274,6 +279,7 @@ class StaticEngine:
         # no per-launch status reads or observers while recording (they would synchronise)
         was_checked, backend.check_kernel_status = backend.check_kernel_status, False
         observer, backend._observer = backend._observer, None
+        grid, backend.igemm_tuning["grid"] = backend.igemm_tuning["grid"], self.conv_grid or backend.igemm_tuning["grid"]
         try:
             with torch.no_grad(), torch.cuda.stream(self.stream):
                 self._forward()
@@ -285,6 +291,7 @@ class StaticEngine:
         finally:
             operators.lazy = was_lazy
             backend.check_kernel_status, backend._observer = was_checked, observer
+            backend.igemm_tuning["grid"] = grid
         torch.cuda.synchronize(self.device)
         return self
 
