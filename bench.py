@@ -849,6 +849,63 @@ def run_kmap(args, device):
             "steps": args.steps, "warmup": args.warmup}
 
 
+def run_pointops(args, device):
+    """Point <-> voxel operators on N points (--pointops N): median ms, algorithmic bytes and GB/s of the coordinate
+    hash, the hash join, the voxel quantisation, average-pool voxelisation and trilinear devoxelisation.  Inputs are
+    larger than L2 at the default N; a 256 MiB fill separates the timed calls."""
+    from torchsparse_b200 import backend
+
+    n = int(args.pointops)
+    g = torch.Generator(device=device).manual_seed(0)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+    side = max(8, int(round((n / 0.05) ** (1 / 3))))                 # ~5 % occupancy of a cube
+    coords = torch.randint(0, side, (n, 4), generator=g, device=device, dtype=torch.int32)
+    coords[:, 0] = 0
+    xyz = torch.rand((n, 3), generator=g, device=device) * (side * 0.05)
+    c_pt, c_vox = 4, 32
+    feats = torch.randn((n, c_pt), generator=g, device=device)
+    uniq, inverse = torch.unique(backend.hash_cuda(coords), return_inverse=True)
+    nv = uniq.numel()
+    counts = torch.bincount(inverse, minlength=nv).int()
+    idx = inverse.int()
+    vfeat = torch.randn((nv, c_vox), generator=g, device=device).half()
+    nbr = torch.randint(-1, nv, (n, 8), generator=g, device=device, dtype=torch.int32)
+    wts = torch.rand((n, 8), generator=g, device=device)
+    refs = uniq[torch.randperm(nv, generator=g, device=device)]
+    queries = backend.hash_cuda(coords)
+    cap = 512
+    while cap < 2 * nv:
+        cap *= 2
+    cases = {
+        # name: (callable, algorithmic bytes)
+        "coord_hash": (lambda: backend.hash_cuda(coords), n * 16 + n * 8),
+        "hash_query": (lambda: backend.hash_query_cuda(queries, refs), nv * 8 + cap * 16 + n * 8 + n * 8),
+        "quantize_unique": (lambda: backend.quantize_unique_cuda(xyz, (0.05, 0.05, 0.05), False, True), n * 12 + n * 8),
+        "voxelize": (lambda: backend.voxelize_forward_cuda(feats, idx, counts), n * c_pt * 4 + n * 4 + nv * (c_pt * 4 + 4)),
+        "devoxelize": (lambda: backend.devoxelize_forward_cuda(vfeat, nbr, wts), n * 64 + n * c_vox * 2 + nv * c_vox * 2),
+    }
+    pk = peaks()
+    out = {"metric": "pointops_ms", "unit": "ms", "higher_is_better": False,
+           "config": {"workload": f"point ops on N={n} points, {nv} voxels, {c_pt} point channels (fp32), "
+                                  f"{c_vox} voxel channels (fp16)"}, "steps": args.steps, "warmup": args.warmup, "ops": {}}
+    for name, (fn, byts) in cases.items():
+        times = []
+        for i in range(args.warmup + args.steps):
+            flush.fill_(i & 0xFF)
+            e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        out["ops"][name] = {"ms": round(ms, 4), "algorithmic_bytes": int(byts), "algorithmic_gbs": round(byts / ms / 1e6, 1),
+                            "frac_hbm_peak": round(byts / ms / 1e6 / pk["hbm_gbs"], 4)}
+    out["value"] = round(sum(v["ms"] for v in out["ops"].values()), 4)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -863,6 +920,7 @@ def main():
     ap.add_argument("--no-kmap", action="store_true", help="skip the isolated kernel-map timings")
     ap.add_argument("--layer", default=None, help="N,Cin,Cout,kernel,stride[,occupancy]: single-layer mode")
     ap.add_argument("--kmap", default=None, help="N,kernel,stride[,occupancy|lidar]: kernel-map build timing")
+    ap.add_argument("--pointops", default=None, help="N: timings of the point <-> voxel operators on N points")
     ap.add_argument("--dataflow", default="ImplicitGEMM")
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
@@ -879,9 +937,15 @@ def main():
     ap.add_argument("--conv-grid", type=int, default=-1,
                     help="upper bound of the persistent CTAs of a convolution launch (0: every resident slot; "
                          "-1: 56 when several engines share the GPU, else every slot)")
+    ap.add_argument("--tune", default="", help="launch-configuration overrides of the conv kernel, e.g. stages=3,ctas=2,cpb=2")
     args = ap.parse_args()
+    if args.tune:
+        from torchsparse_b200 import backend as _backend
+        for kv in args.tune.split(","):
+            k, v = kv.split("=")
+            _backend.igemm_tuning[k] = int(v)
     if args.conv_grid < 0:
-        args.conv_grid = CONV_GRID_SHARED if (args.streams > 1 and not args.layer and not args.kmap) else 0
+        args.conv_grid = CONV_GRID_SHARED if (args.streams > 1 and not args.layer and not args.kmap and not args.pointops) else 0
     if args.conv_grid and args.layer:      # the engines of the step benchmark get it as their own setting
         from torchsparse_b200 import backend as _backend
         _backend.igemm_tuning["grid"] = args.conv_grid
@@ -906,9 +970,10 @@ def main():
 
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if args.layer or args.kmap:
+    if args.layer or args.kmap or args.pointops:
         if rank == 0:
-            print(json.dumps(run_layer(args, device) if args.layer else run_kmap(args, device)), flush=True)
+            fn = run_layer if args.layer else run_kmap if args.kmap else run_pointops
+            print(json.dumps(fn(args, device)), flush=True)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

@@ -1092,13 +1092,24 @@ __global__ void tile_mask_kernel(const int* __restrict__ map, long long rs, long
   for (; warp < tiles; warp += nwarps) {
     unsigned m = 0;
     const int64_t row0 = warp * kTileM;
-    if (cs == 1) {
-      // row-major: the tile is one contiguous run of 128 * kvol ints
-      const int total = kTileM * kvol;
+    if (cs == 1 && rs == kvol) {
+      // row-major: the valid rows of the tile are one contiguous run of ints; eight loads in flight per lane
+      // (the pass is bound by load latency, not by bytes), the column of an element tracked incrementally
+      const int64_t rows_here = min((int64_t)kTileM, n_rows - row0);
+      const int total = rows_here > 0 ? (int)rows_here * kvol : 0;
       const int* base = map + row0 * rs;
-      for (int e = lane; e < total; e += 32) {
-        const int r = e / kvol;
-        if (row0 + r < n_rows && __ldg(base + e) >= 0) m |= 1u << (e - r * kvol);
+      const int step = 32 % kvol;
+      int c = lane % kvol;
+      for (int e = lane; e < total; e += 32 * 8) {
+        int v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = (e + 32 * u < total) ? __ldg(base + e + 32 * u) : -1;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (v[u] >= 0) m |= 1u << c;
+          c += step;
+          if (c >= kvol) c -= kvol;
+        }
       }
     } else {
       for (int k = 0; k < kvol; ++k) {
