@@ -771,6 +771,19 @@ def run_layer(args, device):
         torch.cuda.synchronize()
     n_out = kmap["sizes"][0] if args.transposed else kmap["sizes"][1]
     n_in = kmap["sizes"][1] if args.transposed else n
+    if args.backward:
+        # one gradient launch of the layer (not transposed): the weight gradient on the tensor cores (fp32 result), or
+        # the input gradient = the forward kernel on the transposed map with W transposed per offset
+        from torchsparse_b200.nn.functional.conv.kmap import transpose_kernel_map
+        dy = torch.randn(n_out, cout, device=device, generator=g).to(dtype)
+        fmap = kmap["out_in_map"]
+        if args.backward == "wgrad":
+            run = lambda: backend.conv_wgrad_implicit_gemm_cuda(x.feats, dy, fmap)
+        else:
+            tmap, wt_ = transpose_kernel_map(kmap)["out_in_map_t"], w.transpose(1, 2).contiguous()
+            run = lambda: backend.conv_forward_implicit_gemm_cuda(dy, wt_, tmap, n, cin, backends.allow_tf32, True)
+        run()
+        torch.cuda.synchronize()
     pairs = int((kmap["out_in_map"][:kmap["sizes"][1]] >= 0).sum().item())
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     times = []
@@ -792,6 +805,7 @@ def run_layer(args, device):
             "config": {"workload": f"single Conv3d N={n} {cin}->{cout} k{ks} s{st}{' transposed' if args.transposed else ''} "
                                    f"occupancy {occ} (grid side {side})",
                        "dataflow": args.dataflow, "sorted": bool(args.sorted), "engine_sorted_map": bool(args.smap),
+                       "pass": args.backward or "forward",
                        "dtype": args.dtype},
             "n_out": n_out, "pairs": pairs, "neighbours_per_row": round(pairs / max(n_out, 1), 2),
             "useful_tflops": round(fl / ms / 1e9, 2), "algorithmic_gbs": round(by / ms / 1e6, 1),
@@ -925,6 +939,8 @@ def main():
     ap.add_argument("--dtype", default="f16")
     ap.add_argument("--sorted", action="store_true")
     ap.add_argument("--transposed", action="store_true")
+    ap.add_argument("--backward", default="", choices=["", "wgrad", "dgrad"],
+                    help="layer mode: time the weight-gradient or the input-gradient launch instead of the forward")
     ap.add_argument("--smap", action="store_true", help="layer mode: run on the row-sorted column-major map of the engines")
     ap.add_argument("--lidar-level", type=int, default=-1, help="layer mode: rows of the benchmark scan at stride 2^L")
     ap.add_argument("--streams", type=int, default=8,

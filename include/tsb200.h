@@ -405,6 +405,23 @@ size_t tsb_conv_packed_weight_bytes(int32_t kvol, int32_t cin, int32_t cout, int
 int tsb_conv_pack_weight(const void* weight, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype,
                          void* packed, tsb_stream_t stream);
 
+/* Weight gradient of the implicit-GEMM dataflow on the tensor cores (fp16 / bf16 operands, fp32 accumulation):
+ *   grad_weight[k][a][b] = sum over map rows m of  gathered_feats[out_in_map[m][k]][a] * row_feats[m][b]
+ * grad_weight is fp32 [kvol, c_gathered, c_rows]; the call zeroes it first.  With the forward map
+ * (gathered = input features, rows = output gradients) this is dW [kvol, cin, cout]; with the transposed map
+ * (gathered = output gradients, rows = input features) it is the [kvol, cout, cin] tensor that
+ * conv_backward_wgrad_implicit_gemm_cuda returns
+ * (torchsparse/backend/convolution/convolution_backward_wgrad_implicit_gemm_cuda.cu:1614-1700; its split_k_iters
+ * argument has no counterpart: the row range is divided among CTAs by the library, and the shares meet in
+ * grad_weight through fp32 atomic adds, so the last bits of a sum depend on the order in which CTAs finish).
+ * tile_mask (nullable) = tsb_map_tile_mask of the map.  c_gathered % 8 == 0, c_rows % 16 == 0, kvol <= 32;
+ * other shapes and fp32 tensors return TSB_ERR_UNSUPPORTED (the caller falls back to pair-list GEMMs). */
+size_t tsb_conv_wgrad_igemm_workspace_bytes(int64_t n_rows);
+int tsb_conv_wgrad_igemm(const void* gathered_feats, const void* row_feats, const int32_t* out_in_map,
+                         const uint32_t* tile_mask, float* grad_weight, int64_t n_gathered, int64_t n_rows,
+                         int64_t map_row_stride, int64_t map_col_stride, int32_t kvol, int32_t c_gathered, int32_t c_rows,
+                         int32_t dtype, int32_t* dev_status, void* workspace, size_t workspace_bytes, tsb_stream_t stream);
+
 /* Gather -> grouped GEMM -> scatter over pair lists (nbmaps [P,2], HOST nbsizes [kvol]).
  * 16-bit tensors (and fp32 under TSB_MATH_TF32) whose rows are 16-byte multiples run the GEMM on the
  * tensor cores over the 128-padded pair list, fetching the input rows straight from in_feats.

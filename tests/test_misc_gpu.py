@@ -143,3 +143,32 @@ def test_gather_scatter_backward_entry_fills_callers_buffers(transpose):
                                               torch.from_numpy(nbmaps).cuda(), torch.from_numpy(nbsizes), transpose)
     assert rel_l2(gx.cpu().numpy(), want_dx) < 1e-5
     assert rel_l2(gw.cpu().numpy(), want_dw) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,cg,cd,ks", [(1500, 32, 48, 3), (4000, 96, 96, 3), (3000, 64, 256, 3), (2500, 256, 128, 3),
+                                        (3000, 136, 320, 2), (900, 8, 16, 3)])
+def test_tensor_core_weight_gradient_vs_oracle(dtype, n, cg, cd, ks):
+    """tsb_conv_wgrad_igemm (tcgen05, both operands MN-major, row range divided among CTAs, fp32 atomic adds)
+    against the fp64 oracle on 16-bit-rounded operands.  Tolerance: relative L2 <= 1e-5 on the fp32 result (fp32
+    accumulation of exact 16-bit products; the order of the atomic adds moves the last bits only)."""
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(n + cg + cd)
+    coords = random_coords(rng, n, (24, 24, 24), 2)
+    n = coords.shape[0]
+    st, pad = (1, 1) if ks == 3 else (2, 0)
+    km = ko.build_kmap(coords, ks, st, pad)
+    m = km["sizes"][1]
+    x = torch.from_numpy(rng.standard_normal((n, cg)).astype(np.float32)).to(dtype)
+    dy = torch.from_numpy(rng.standard_normal((m, cd)).astype(np.float32)).to(dtype)
+    w0 = np.zeros((ks ** 3, cg, cd), dtype=np.float32)
+    _, want = ko.conv_backward_from_map(x.float().numpy(), w0, km["out_in_map"], m, dy.float().numpy())
+    got = backend.conv_wgrad_implicit_gemm_cuda(x.cuda(), dy.cuda(), torch.from_numpy(km["out_in_map"]).cuda())
+    assert got.dtype == torch.float32 and got.shape == want.shape
+    assert rel_l2(got.cpu().numpy(), want) < 1e-5
+    # the reference-named entry on the transposed map returns the [Kvol, Cout, Cin] form
+    map_t = torch.from_numpy(ko.transpose_map(km["out_in_map"], ko.pad_rows(n))).cuda()
+    got_t = backend.conv_backward_wgrad_implicit_gemm_cuda(dy.cuda(), x.cuda(), map_t, 32)
+    assert got_t.dtype == dtype and got_t.numel() == want.size
+    assert rel_l2(got_t.float().reshape(ks ** 3, cd, cg).transpose(1, 2).cpu().numpy(), want) < 4e-3

@@ -57,6 +57,8 @@ SIGNATURES = {
     "tsb_map_sorted_cm": (C.c_int, [P, I64, I32, I64, P, P, P, P, I32, I32, P, P, P, SZ, P]),
     "tsb_conv_packed_weight_bytes": (SZ, [I32, I32, I32, I32]),
     "tsb_conv_pack_weight": (C.c_int, [P, I32, I32, I32, I32, P, P]),
+    "tsb_conv_wgrad_igemm_workspace_bytes": (SZ, [I64]),
+    "tsb_conv_wgrad_igemm": (I32, [P, P, P, P, P, I64, I64, I64, I64, I32, I32, I32, I32, P, P, SZ, P]),
     "tsb_conv_gs_workspace_bytes": (SZ, [I64, I32, I32, I32, I32]),
     "tsb_conv_gs_fwd": (C.c_int, [P, P, P, P, P, P, I64, I64, I32, I32, I32, I32, I32, I32, P, SZ, P]),
     "tsb_conv_fod_workspace_bytes": (SZ, [I64, I64, I32, I32, I32, I32]),

@@ -29,7 +29,9 @@ __all__ = [
     "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "sorted_artefacts_cuda",
     "exclusive_scan_quantified_wrapper",
     "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda", "conv_backward_wgrad_pairs_cuda",
-    "conv_forward_gather_scatter_cuda", "conv_backward_gather_scatter_cuda", "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
+    "conv_forward_gather_scatter_cuda", "conv_backward_gather_scatter_cuda", "conv_wgrad_implicit_gemm_cuda",
+    "conv_backward_wgrad_implicit_gemm_cuda", "conv_backward_wgrad_implicit_gemm_sorted_cuda",
+    "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
     "voxelize_backward_cuda", "devoxelize_backward_cuda", "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
     "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda", "SortedMap",
@@ -835,6 +837,78 @@ def conv_backward_wgrad_pairs_cuda(grad_out: torch.Tensor, in_feats: torch.Tenso
             torch.mm(xg[start:start + size].t(), yg[start:start + size], out=dw[k])
         start += size
     return dw
+
+
+def _wgrad_by_offsets(gathered: torch.Tensor, rows: torch.Tensor, out_in_map: torch.Tensor) -> torch.Tensor:
+    """fp32 [Kvol, Cg, Cd] of the sums below, one masked product per kernel offset (shapes the tensor-core kernel
+    does not take, and exact fp32)."""
+    n_rows, kvol = rows.shape[0], out_in_map.shape[1]
+    out = torch.zeros((kvol, gathered.shape[1], rows.shape[1]), dtype=torch.float32, device=rows.device)
+    for k in range(kvol):
+        idx = out_in_map[:n_rows, k].long()
+        valid = idx >= 0
+        if bool(valid.any()):
+            out[k] = gathered.index_select(0, idx[valid]).float().t() @ rows[valid].float()
+    return out
+
+
+def conv_wgrad_implicit_gemm_cuda(gathered: torch.Tensor, rows: torch.Tensor, out_in_map: torch.Tensor,
+                                  tile_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[k][a][b] = sum over map rows m of gathered[out_in_map[m][k]][a] * rows[m][b], fp32 [Kvol, Cg, Cd]
+    (tsb_conv_wgrad_igemm: tcgen05 with both operands read MN-major, fp32 accumulators in TMEM, the row range
+    divided among CTAs).  With the forward map, gathered = input features and rows = output gradients give dW."""
+    _need_cuda(gathered, rows, out_in_map)
+    n_rows, kvol = rows.shape[0], out_in_map.shape[1]
+    cg, cd = gathered.shape[1], rows.shape[1]
+    if out_in_map.shape[0] < n_rows:
+        raise ValueError("the map has fewer rows than the row matrix")
+    dev = rows.device
+    tensor_cores = (gathered.dtype in (torch.float16, torch.bfloat16) and rows.dtype == gathered.dtype
+                    and cg % 8 == 0 and cd % 16 == 0 and kvol <= 32 and n_rows > 0 and gathered.shape[0] > 0)
+    if not tensor_cores:
+        return _wgrad_by_offsets(gathered, rows, out_in_map)
+    gathered, rows, out_in_map = gathered.contiguous(), rows.contiguous(), out_in_map.contiguous()
+    if tile_mask is None:
+        tile_mask = _tile_mask_of(out_in_map, n_rows)
+    out = torch.empty((kvol, cg, cd), dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if check_kernel_status else _status_word(dev)
+    ws = _workspace(lib.tsb_conv_wgrad_igemm_workspace_bytes(n_rows), dev)
+    rc = lib.tsb_conv_wgrad_igemm(_p(gathered), _p(rows), _p(out_in_map), _p(tile_mask), _p(out), gathered.shape[0],
+                                  n_rows, 0, 0, kvol, cg, cd, _dtype_code(gathered), _p(status), _p(ws), ws.numel(),
+                                  _stream())
+    if rc == 2:      # TSB_ERR_UNSUPPORTED
+        return _wgrad_by_offsets(gathered, rows, out_in_map)
+    check(rc, "conv_wgrad_implicit_gemm_cuda")
+    if check_kernel_status and int(status.item()) != 0:
+        raise RuntimeError(f"conv_wgrad_implicit_gemm_cuda: a bounded wait inside the kernel ran out "
+                           f"(code {int(status.item())}); the output is undefined")
+    return out
+
+
+def conv_backward_wgrad_implicit_gemm_cuda(_in_feats: torch.Tensor, _kernel: torch.Tensor, _out_in_map: torch.Tensor,
+                                           split_k_iters: int = 32, allow_tf32: bool = False,
+                                           allow_fp16: bool = True) -> torch.Tensor:
+    """The reference's entry (torchsparse/backend/convolution/convolution_backward_wgrad_implicit_gemm_cuda.cu:1614,
+    called at torchsparse/nn/functional/conv/func/implicit_gemm.py:178 with grad_output, input and the map of the
+    input rows): returns [Kvol * Cout, Cin] = sum over input rows n of grad_output[map[n][k]]^T . input[n].
+    ``split_k_iters`` is accepted and ignored (the library divides the row range itself)."""
+    if torch.float16 in (_in_feats.dtype, _kernel.dtype) and allow_fp16:
+        _in_feats, _kernel = _in_feats.half(), _kernel.half()
+    out = conv_wgrad_implicit_gemm_cuda(_in_feats, _kernel, _out_in_map)
+    return out.reshape(-1, _kernel.shape[1]).to(_kernel.dtype)
+
+
+def conv_backward_wgrad_implicit_gemm_sorted_cuda(_in_feats: torch.Tensor, _kernel: torch.Tensor,
+                                                  _out_in_map: torch.Tensor, _reduced_mask: torch.Tensor,
+                                                  _reorder_loc: torch.Tensor, split_k_iters: int = 32,
+                                                  allow_tf32: bool = False, allow_fp16: bool = True) -> torch.Tensor:
+    """The sorted form (convolution_backward_wgrad_implicit_gemm_sorted_cuda.cu:1744): row r of the reordered map
+    belongs to input row ``_reorder_loc[0][r]``.  The input rows are put in map order once and the unsorted entry
+    does the rest; ``_reduced_mask`` is not needed (the per-tile offset masks are derived from the map)."""
+    loc = (_reorder_loc[0] if _reorder_loc.dim() == 2 else _reorder_loc).long()
+    n = _kernel.shape[0]
+    rows = _kernel.index_select(0, loc[:n].clamp(min=0))
+    return conv_backward_wgrad_implicit_gemm_cuda(_in_feats, rows, _out_in_map, split_k_iters, allow_tf32, allow_fp16)
 
 
 def conv_backward_gather_scatter_cuda(in_feat: torch.Tensor, grad_in_feat: torch.Tensor, grad_out_feat: torch.Tensor,

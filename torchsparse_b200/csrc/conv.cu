@@ -87,6 +87,27 @@ int tsb_conv_igemm_run(const tsb_igemm_desc* d, tsb_stream_t stream) {
   return igemm_umma(a, as_stream(stream));
 }
 
+size_t tsb_conv_wgrad_igemm_workspace_bytes(int64_t n_rows) { return n_rows < 0 ? 0 : wgrad_umma_workspace_bytes(n_rows); }
+
+int tsb_conv_wgrad_igemm(const void* gathered_feats, const void* row_feats, const int32_t* out_in_map,
+                         const uint32_t* tile_mask, float* grad_weight, int64_t n_gathered, int64_t n_rows,
+                         int64_t map_row_stride, int64_t map_col_stride, int32_t kvol, int32_t c_gathered, int32_t c_rows,
+                         int32_t dtype, int32_t* dev_status, void* workspace, size_t workspace_bytes, tsb_stream_t stream) {
+  if (n_gathered < 0 || n_rows < 0 || kvol < 1 || c_gathered < 1 || c_rows < 1) return TSB_ERR_BAD_ARG;
+  if (!valid_dtype(dtype)) return TSB_ERR_UNSUPPORTED;
+  if (!grad_weight) return TSB_ERR_BAD_ARG;
+  if ((map_row_stride == 0) != (map_col_stride == 0) || map_row_stride < 0 || map_col_stride < 0) return TSB_ERR_BAD_ARG;
+  if (n_gathered == 0 || n_rows == 0) {      // no pair: the gradient is zero
+    TSB_CUDA_TRY(cudaMemsetAsync(grad_weight, 0, (size_t)kvol * c_gathered * c_rows * sizeof(float), as_stream(stream)));
+    return TSB_OK;
+  }
+  if (!gathered_feats || !row_feats || !out_in_map) return TSB_ERR_BAD_ARG;
+  WgradArgs a{gathered_feats, row_feats, out_in_map, map_row_stride, map_col_stride, tile_mask, grad_weight, n_gathered,
+              n_rows, kvol, c_gathered, c_rows, dtype, dev_status, workspace, workspace_bytes};
+  if (!wgrad_umma_supported(a)) return TSB_ERR_UNSUPPORTED;
+  return wgrad_umma(a, as_stream(stream));
+}
+
 size_t tsb_conv_gs_workspace_bytes(int64_t n_pairs, int32_t kvol, int32_t cin, int32_t cout, int32_t dtype) {
   if (n_pairs < 0 || kvol < 1 || cin < 1 || cout < 1 || !valid_dtype(dtype)) return 0;
   const size_t simt = gs_workspace_bytes(n_pairs, kvol, cin, cout, dtype);

@@ -93,6 +93,24 @@ size_t tile_mask_bytes(int64_t n_out);
 int tile_masks(const int* map, long long rs, long long cs, int kvol, int64_t n_rows, const int* n_rows_dev,
                unsigned* out, cudaStream_t s);
 int igemm_umma(const IgemmArgs& a, cudaStream_t s);
+// Weight gradient on the tensor cores: out[k][a][b] = sum over map rows m of g[map[m][k]][a] * p[m][b].
+struct WgradArgs {
+  const void* g;             // [n_g, cg]: the matrix addressed through the map
+  const void* p;             // [n_rows, cd]: the matrix whose rows are the map's rows
+  const int* map;            // entry (row, k) at map[row * map_rs + k * map_cs] (0, 0: row-major [rows][kvol])
+  int64_t map_rs, map_cs;
+  const unsigned* tile_mask; // nullable: offsets present in each 128-row tile (derived in the workspace when null)
+  float* out;                // fp32 [kvol, cg, cd]; zeroed by the call
+  int64_t n_g, n_rows;
+  int kvol, cg, cd, dtype;
+  int* dev_status;           // nullable
+  void* workspace;
+  size_t workspace_bytes;
+};
+bool wgrad_umma_supported(const WgradArgs& a);
+size_t wgrad_umma_workspace_bytes(int64_t n_rows);
+int wgrad_umma(const WgradArgs& a, cudaStream_t s);
+
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype);
 int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* packed, cudaStream_t s);
 

@@ -1275,6 +1275,223 @@ int chunks_for(const IgemmArgs& a) {
   return chunks_of(a.cin, a.dtype);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Weight gradient on the tensor cores.
+//
+//   D[k][a][b] = sum over map rows m of  G[map[m][k]][a] * P[m][b]        (fp32 accumulation)
+//
+// G = the matrix addressed through the map ("gathered"), P = the matrix whose rows are the map's rows.  With the
+// forward map, G = input features and P = output gradients gives dW[k][cin][cout]; with the transposed map,
+// G = output gradients and P = input features gives the [kvol][cout][cin] form the reference returns
+// (torchsparse/backend/convolution/convolution_backward_wgrad_implicit_gemm_cuda.cu:1614).
+//
+// The reduction runs over map rows, so both operands are read "MN-major": a stage holds 128 map rows, every
+// row one 128-byte slice of 64 channels, 128B-swizzled by row - byte for byte the layout the forward kernel
+// gathers its A operand into.  The shared-memory descriptors name it as canonical MN-major SWIZZLE_128B:
+// 8-row groups 1024 bytes apart (stride byte offset), 64-channel blocks one chunk (16 KiB) apart (leading byte
+// offset), and the instruction descriptor marks A and B as MN-major.  One tcgen05.mma covers 16 rows.
+//
+// A CTA owns (offset k, 128-channel tile of G, N tile of P, a share of the 128-row tiles) and keeps the 128 x N
+// fp32 tile in TMEM over its whole share; tiles whose offset mask lacks k are skipped.  G rows are gathered by
+// the eight gather warps (cp.async, zeros for a missing neighbour), P tiles are fetched by TMA.  At the end the
+// four epilogue warps add the tile to the fp32 result with 16-byte atomic adds (the shares of the row range
+// meet there).  Waits are bounded as in the forward kernel.
+struct WgradParams {
+  const void* g;         // [n_g, cg]
+  const int* map;        // entry (row, k) at map[row * map_rs + k * map_cs]
+  long long map_rs, map_cs;
+  const unsigned* tile_mask;   // [tiles]
+  float* out;            // [kvol, cg, cd], zero before the launch
+  int* error;
+  int n_g, n_rows, kvol, cg, cd;
+  int m_tiles, n_tiles, splits, tiles;
+  int n_tile;            // channels of P per CTA (multiple of 16, <= 256)
+  int acc_cols, stages, ab_format;
+};
+
+constexpr int kWgradThreads = (kGatherWarps + kEpilogueWarps + 2) * 32;   // 448
+
+template <typename T>
+__global__ void __launch_bounds__(kWgradThreads, 1)
+wgrad_umma_kernel(const WgradParams p, const __grid_constant__ CUtensorMap p_map) {
+  constexpr int kChunk = kRowBytes / (int)sizeof(T);     // channels per 128-byte slice (64)
+  constexpr int kGran = 16 / (int)sizeof(T);
+  constexpr int kTmaW = kGatherWarps + kEpilogueWarps, kMmaW = kTmaW + 1;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t s_full[kMaxStages];
+  __shared__ uint64_t s_empty[kMaxStages];
+  __shared__ uint64_t s_acc_full;
+  __shared__ uint32_t s_tmem;
+  __shared__ volatile int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // work item of this CTA
+  int w = blockIdx.x;
+  const int split = w % p.splits; w /= p.splits;
+  const int nt = w % p.n_tiles; w /= p.n_tiles;
+  const int mt = w % p.m_tiles;
+  const int k = w / p.m_tiles;
+  const int t_lo = (int)((long long)p.tiles * split / p.splits), t_hi = (int)((long long)p.tiles * (split + 1) / p.splits);
+  const int n0 = nt * p.n_tile;
+  const int n_mma = (min(p.n_tile, p.cd - n0) + 15) & ~15;
+  const int b_chunks = (n_mma + kChunk - 1) / kChunk;
+  const int a_bytes = 2 * kABytes;                           // two 64-channel blocks of G (M = 128)
+  const int stage_bytes = a_bytes + b_chunks * kABytes;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&s_full[s]), kGatherThreads + 1);
+      mbar_init(smem_u32(&s_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_acc_full), 1);
+    s_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == kMmaW) tmem_alloc(smem_u32(&s_tmem), p.acc_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem;
+  auto tile_live = [&](int t) -> bool { return (__ldg(&p.tile_mask[t]) >> k) & 1u; };
+
+  if (warp < kGatherWarps) {
+    // ------------------------------------------------------------ gather warps: rows of G named by the map
+    const T* g = reinterpret_cast<const T*>(p.g);
+    const int gran = tid & 7, rbase = tid >> 3;
+    const uint32_t dst_off = (uint32_t)rbase * kRowBytes + (uint32_t)((gran ^ (rbase & 7)) << 4);
+    uint32_t stage = 0, phase = 0;
+    bool first_pass = true;
+    for (int t = t_lo; t < t_hi; ++t) {
+      if (!tile_live(t)) continue;
+      int src[kCopies];
+#pragma unroll
+      for (int j = 0; j < kCopies; ++j) {
+        const long long r = (long long)t * kTileM + rbase + j * kRowsPerPass;
+        src[j] = r < p.n_rows ? ld_map_entry(p.map + r * p.map_rs + (long long)k * p.map_cs) : -1;
+      }
+      if (!first_pass && !mbar_wait_warp(smem_u32(&s_empty[stage]), phase ^ 1u, lane)) {
+        if (lane == 0) atomicExch(p.error, kErrEmptyWait);
+        s_abort = 1;
+        break;
+      }
+      const uint32_t a_stage = smem_base + stage * (uint32_t)stage_bytes + dst_off;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col = mt * 2 * kChunk + c * kChunk + gran * kGran;
+        const bool col_ok = col < p.cg;
+#pragma unroll
+        for (int j = 0; j < kCopies; ++j) {
+          const bool live = col_ok && (unsigned)src[j] < (unsigned)p.n_g;
+          cp_async16(a_stage + (uint32_t)c * kABytes + (uint32_t)(j * kRowsPerPass) * kRowBytes,
+                     live ? (const void*)(g + (int64_t)src[j] * p.cg + col) : (const void*)g, live ? 16u : 0u);
+        }
+      }
+      cp_async_arrive_noinc(smem_u32(&s_full[stage]));
+      if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+    }
+    cp_async_wait_all();
+  } else if (warp < kGatherWarps + kEpilogueWarps) {
+    // ------------------------------------------------------------ epilogue warps: D rows = channels of G
+    bool any = false;
+    for (int t = t_lo; t < t_hi && !any; ++t) any = tile_live(t);
+    if (any) {
+      if (!mbar_wait_warp(smem_u32(&s_acc_full), 0u, lane)) {
+        if (lane == 0) atomicExch(p.error, kErrAccWait);
+        s_abort = 1;
+      } else {
+        tc_fence_after();
+        const int quarter = warp & 3;
+        const int a = mt * 2 * kChunk + quarter * 32 + lane;      // channel of G
+        const uint32_t acc_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float* orow = p.out + ((int64_t)k * p.cg + a) * p.cd + n0;
+        for (int j = 0; j < n_mma; j += 16) {
+          uint32_t v[16];
+          tmem_ld16(acc_addr + (uint32_t)j, v);
+          tmem_ld_wait16(v);
+          if (a < p.cg) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (n0 + j + 4 * q < p.cd)
+                atomicAdd(reinterpret_cast<float4*>(orow + j) + q,
+                          make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                      __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3])));
+            }
+          }
+        }
+        tc_fence_before();
+      }
+    }
+  } else if (warp == kTmaW) {
+    // ------------------------------------------------------------ P tiles by TMA (128 rows x 64 channels per chunk)
+    uint32_t stage = 0, phase = 0;
+    bool first_pass = true;
+    for (int t = t_lo; t < t_hi; ++t) {
+      if (!tile_live(t)) continue;
+      if (!first_pass && !mbar_wait(smem_u32(&s_empty[stage]), phase ^ 1u)) {
+        if (lane == 0) atomicExch(p.error, kErrEmptyWait);
+        s_abort = 1;
+        break;
+      }
+      if (elect_one()) {
+        const uint32_t bar = smem_u32(&s_full[stage]);
+        mbar_arrive_expect_tx(bar, (uint32_t)(b_chunks * kABytes));
+        const uint32_t b_dst = smem_base + stage * (uint32_t)stage_bytes + (uint32_t)a_bytes;
+        for (int c = 0; c < b_chunks; ++c) tma_load_2d(b_dst + (uint32_t)(c * kABytes), &p_map, bar, n0 + c * kChunk, t * kTileM);
+      }
+      __syncwarp();
+      if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+    }
+  } else if (warp == kMmaW) {
+    // ------------------------------------------------------------ MMA issuer
+    // descriptors: SBO = 1024 (8-row groups), LBO = one chunk (the next 64 channels), version 1, SWIZZLE_128B
+    const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const uint32_t lbo = ((uint32_t)kABytes >> 4) << 16;
+    const uint32_t idesc = make_idesc(p.ab_format, n_mma) | (1u << 15) | (1u << 16);    // A and B MN-major
+    uint32_t stage = 0, phase = 0, accumulate = 0;
+    bool ok = true, any = false;
+    for (int t = t_lo; t < t_hi && ok; ++t) {
+      if (!tile_live(t)) continue;
+      any = true;
+      if (!mbar_wait(smem_u32(&s_full[stage]), phase)) {
+        if (lane == 0) atomicExch(p.error, kErrFullWait);
+        s_abort = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      if (elect_one()) {
+        const uint32_t a_units = (smem_base + stage * (uint32_t)stage_bytes) >> 4;
+        const uint32_t b_units = a_units + ((uint32_t)a_bytes >> 4);
+#pragma unroll
+        for (int ks = 0; ks < kTileM / 16; ++ks) {      // 16 map rows per instruction = 2048 bytes = 128 address units
+          const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (((a_units + 128u * ks) & 0x3FFFu) | lbo);
+          const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (((b_units + 128u * ks) & 0x3FFFu) | lbo);
+          umma<false>(tmem_base, a_desc, b_desc, idesc, accumulate);
+          accumulate = 1;
+        }
+        umma_commit(smem_u32(&s_empty[stage]));
+      }
+      __syncwarp();
+      accumulate = 1;
+      if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; }
+    }
+    if (any) {
+      if (elect_one()) umma_commit(smem_u32(&s_acc_full));
+      __syncwarp();
+    }
+    tc_fence_before();
+  }
+  if (s_abort) {
+    for (int t = 0; t < 1000; ++t) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == kMmaW) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.acc_cols);
+  }
+}
+
 }  // namespace
 
 bool igemm_umma_supported(const IgemmArgs& a) {
@@ -1460,6 +1677,102 @@ int igemm_umma(const IgemmArgs& a, cudaStream_t s) {
   if (a.dtype == TSB_F16) return umma_launch<__half>(a, s);
   if (a.dtype == TSB_BF16) return umma_launch<__nv_bfloat16>(a, s);
   if (a.dtype == TSB_F32 && a.math == TSB_MATH_TF32) return umma_launch<float>(a, s);
+  return TSB_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Weight gradient (see wgrad_umma_kernel)
+bool wgrad_umma_supported(const WgradArgs& a) {
+  if (!tensor_map_encoder()) return false;
+  if (a.dtype != TSB_F16 && a.dtype != TSB_BF16) return false;
+  if (a.cg % 8 || a.cd % 16 || a.kvol < 1 || a.kvol > kMaxKvolUmma) return false;
+  if (a.n_g <= 0 || a.n_rows <= 0 || a.n_g >= (int64_t)INT32_MAX || a.n_rows >= (int64_t)INT32_MAX) return false;
+  if (((uintptr_t)a.g | (uintptr_t)a.p | (uintptr_t)a.out) & 15) return false;
+  return true;
+}
+
+size_t wgrad_umma_workspace_bytes(int64_t n_rows) { return 256 + tile_mask_bytes(n_rows); }
+
+template <typename T>
+static int wgrad_launch(const WgradArgs& a, cudaStream_t s) {
+  char* ws = reinterpret_cast<char*>(a.workspace);
+  int* err = a.dev_status;
+  const unsigned* tmask = a.tile_mask;
+  const size_t need = (!tmask ? 256 + tile_mask_bytes(a.n_rows) : (!err ? 256 : 0));
+  if (need && (!ws || a.workspace_bytes < need)) return TSB_ERR_WORKSPACE;
+  if (!err) {
+    err = reinterpret_cast<int*>(ws);
+    TSB_CUDA_TRY(cudaMemsetAsync(err, 0, sizeof(int), s));
+  }
+  const long long rs = a.map_rs ? a.map_rs : a.kvol, cs = a.map_cs ? a.map_cs : 1;
+  if (!tmask) {
+    unsigned* m = reinterpret_cast<unsigned*>(ws + 256);
+    int rc = tile_masks(a.map, rs, cs, a.kvol, a.n_rows, nullptr, m, s);
+    if (rc != TSB_OK) return rc;
+    tmask = m;
+  }
+  int dev = 0;
+  TSB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TSB_ERR_LIMIT;
+  int sms = kSmCount;
+  {
+    static std::mutex mu;
+    static bool attr_set[kMaxDevices][2] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    const int f = a.dtype == TSB_BF16 ? 1 : 0;
+    if (!attr_set[dev][f]) {
+      TSB_CUDA_TRY(cudaFuncSetAttribute(wgrad_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+      attr_set[dev][f] = true;
+    }
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sms = v;
+  }
+  WgradParams p;
+  p.g = a.g; p.map = a.map; p.map_rs = rs; p.map_cs = cs; p.tile_mask = tmask; p.out = a.out; p.error = err;
+  p.n_g = (int)a.n_g; p.n_rows = (int)a.n_rows; p.kvol = a.kvol; p.cg = a.cg; p.cd = a.cd;
+  p.n_tile = a.cd < 256 ? a.cd : 256;
+  p.n_tiles = (a.cd + p.n_tile - 1) / p.n_tile;
+  p.m_tiles = (a.cg + 127) / 128;
+  p.tiles = (int)cdiv(a.n_rows, kTileM);
+  // shares of the row range: enough CTAs for two per SM, never more shares than row tiles
+  const int64_t base = (int64_t)a.kvol * p.m_tiles * p.n_tiles;
+  int64_t splits = (2 * (int64_t)sms + base - 1) / base;
+  if (splits < 1) splits = 1;
+  if (splits > p.tiles) splits = p.tiles;
+  p.splits = (int)splits;
+  p.acc_cols = acc_cols_for(p.n_tile);
+  p.ab_format = a.dtype == TSB_BF16 ? kFmtBF16 : kFmtF16;
+  const int b_chunks = (p.n_tile + 63) / 64;
+  const size_t stage_bytes = (size_t)(2 + b_chunks) * kABytes;
+  int stages = (int)((225 * 1024) / stage_bytes);
+  if (stages > 4) stages = 4;
+  if (stages < 2) return TSB_ERR_UNSUPPORTED;
+  p.stages = stages;
+  const size_t smem = 1024 + (size_t)stages * stage_bytes;
+  CUtensorMap p_map;
+  {
+    auto encode = tensor_map_encoder();
+    if (!encode) return TSB_ERR_UNSUPPORTED;
+    const CUtensorMapDataType dt = a.dtype == TSB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    cuuint32_t estride[2] = {1, 1};
+    cuuint64_t gdim[2] = {(cuuint64_t)a.cd, (cuuint64_t)a.n_rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)a.cd * sizeof(T)};
+    cuuint32_t box[2] = {(cuuint32_t)(kRowBytes / sizeof(T)), (cuuint32_t)kTileM};
+    CUresult r = encode(&p_map, dt, 2, const_cast<void*>(a.p), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return TSB_ERR_BAD_ARG;
+  }
+  TSB_CUDA_TRY(cudaMemsetAsync(a.out, 0, (size_t)a.kvol * a.cg * a.cd * sizeof(float), s));
+  const int64_t grid = base * p.splits;
+  if (grid > INT32_MAX) return TSB_ERR_LIMIT;
+  wgrad_umma_kernel<T><<<(unsigned)grid, kWgradThreads, smem, s>>>(p, p_map);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int wgrad_umma(const WgradArgs& a, cudaStream_t s) {
+  if (a.dtype == TSB_F16) return wgrad_launch<__half>(a, s);
+  if (a.dtype == TSB_BF16) return wgrad_launch<__nv_bfloat16>(a, s);
   return TSB_ERR_UNSUPPORTED;
 }
 

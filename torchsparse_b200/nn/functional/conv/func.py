@@ -31,7 +31,9 @@ class _SparseConvFunction(Function):
 
     * dgrad: the implicit-GEMM *forward* kernel run on grad_output with W transposed per offset and the
       transposed kernel map (input row -> output rows), as the reference does;
-    * wgrad: dW[k] = X[in_k]^T . dY[out_k] over the pair lists (gathers + one GEMM per offset)."""
+    * wgrad: dW[k] = sum over output rows m of X[map[m][k]]^T . dY[m] on the tensor cores (tcgen05, both operands
+      read row-major = MN-major; torchsparse/backend/convolution/convolution_backward_wgrad_implicit_gemm_cuda.cu);
+      exact fp32 and odd channel counts as one masked product per offset."""
 
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
@@ -52,11 +54,11 @@ class _SparseConvFunction(Function):
                 dy, w.transpose(1, 2).contiguous(), bwd_map, x.shape[0], cin, backends.allow_tf32,
                 backends.allow_fp16).to(input.dtype)
         if ctx.needs_input_grad[1]:
-            pairs = kmap.get("_bwd_pairs")
-            if pairs is None:
-                nbmaps, _, sizes_host, _, _, _ = backend.pairs_from_out_in_map(kmap["out_in_map"], False)
-                pairs = kmap["_bwd_pairs"] = (nbmaps, sizes_host)
-            grad_weight = backend.conv_backward_wgrad_pairs_cuda(dy, x, pairs[0], pairs[1], transposed).to(weight.dtype)
+            # dW[k] = sum over output rows m of X[map[m][k]]^T . dY[m] on the map the forward used
+            fwd_map = kmap.get("out_in_map_t") if transposed else kmap["out_in_map"]
+            if fwd_map is None:
+                fwd_map = transpose_kernel_map(kmap)["out_in_map_t"]
+            grad_weight = backend.conv_wgrad_implicit_gemm_cuda(x, dy, fwd_map).to(weight.dtype)
         return grad_input, grad_weight, None, None, None, None
 
 
