@@ -510,6 +510,38 @@ def build_kmap_hashmap_mode(coords, kernel_size, stride=1, padding=0, spatial_ra
     return {"out_in_map": out, "coords": out_coords, "sizes": (coords.shape[0], m)}
 
 
+def build_kmap_generative(coords, kernel_size, stride, padding, spatial_range):
+    """The kernel map of a generative transposed convolution
+    (torchsparse/nn/functional/conv/kmap/upsample.py:12-38, kmap/func/hashmap.py:37-40, 58-64, 74-83,
+    kmap/build_kmap.py:65-72).  ``spatial_range`` is the INPUT tensor's (batch, x, y, z) range; as in the reference the
+    generated coordinates are clamped to the range the strided-convolution formula derives from it.  Output rows:
+    unique (lexicographic) rows of clamp(coords * stride + cell offset) over the cells of a stride-1 kernel; entry
+    (row, k) = the input whose coords * stride equals output + digit_k - (kernel - 1) // 2, else -1."""
+    ks, st, pd = _as3(kernel_size), _as3(stride), _as3(padding)
+    coords = np.asarray(coords, dtype=np.int32)
+    new_range = (spatial_range[0],) + tuple(
+        (spatial_range[i + 1] + 2 * pd[i] - (ks[i] - 1) - 1) // st[i] + 1 for i in range(3))
+    digits = kernel_digits(ks)
+    offs = digits.astype(np.int64) - np.array([(k - 1) // 2 for k in ks], dtype=np.int64)
+    scaled = coords.astype(np.int64).copy()
+    scaled[:, 1:] *= np.array(st, dtype=np.int64)
+    gen = np.repeat(scaled[:, None, :], offs.shape[0], axis=1)
+    gen[:, :, 1:] += offs[None, :, :]
+    for i in range(1, 4):
+        gen[:, :, i] = np.clip(gen[:, :, i], 0, new_range[i] - 1)
+    out_coords = np.unique(gen.reshape(-1, 4), axis=0).astype(np.int32)
+    index = {tuple(int(v) for v in row): i for i, row in enumerate(scaled)}
+    kvol = offs.shape[0]
+    m = out_coords.shape[0]
+    out = np.full(((m + 127) // 128 * 128, kvol), -1, dtype=np.int32)
+    for i in range(m):
+        b, x, y, z = (int(v) for v in out_coords[i])
+        for k in range(kvol):
+            dx, dy, dz = (int(v) for v in offs[k])
+            out[i, k] = index.get((b, x + dx, y + dy, z + dz), -1)
+    return {"out_in_map": out, "coords": out_coords, "sizes": (coords.shape[0], m), "spatial_range": new_range}
+
+
 def build_kmap(coords, kernel_size, stride=1, padding=0, spatial_range=None, allow_negative=False):
     """The ``hashmap_on_the_fly`` kernel map as a dict with the reference's keys
     (torchsparse/nn/functional/conv/kmap/func/hashmap_on_the_fly.py:10-109)."""

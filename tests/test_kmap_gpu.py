@@ -252,3 +252,49 @@ def test_spdownsample_and_downsample_cuda():
     got3 = F.spdownsample(c, 2, 3, 1).cpu().numpy()                 # stride != kernel: native enumeration
     want3 = ko.build_kmap(coords, 3, 2, 1)["coords"]
     assert np.array_equal(got3, want3)
+
+
+@pytest.mark.parametrize("ks,st", [(2, 2), (3, 2)])
+def test_generative_transposed_convolution(ks, st):
+    """Generative transposed convolution (kmap_mode="hashmap"): generated output coordinates and the kernel map
+    bit-exact against the oracle, the features against the oracle convolution, gradients flow, the kernel-map
+    caches are emptied afterwards (torchsparse/nn/functional/conv/conv.py:161-203), and `generative_add` of the
+    result with a tensor on other coordinates sums over the union."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.nn import functional as F
+
+    rng = np.random.default_rng(21)
+    coords = random_coords(rng, 1500, (12, 12, 12), 2)
+    srange = (2, 32, 32, 32)
+    want = ko.build_kmap_generative(coords, ks, st, 0, srange)
+    cfg = F.conv_config.get_default_conv_config()
+    cfg.kmap_mode = "hashmap"
+    kvol = ks ** 3
+    feats = rng.standard_normal((coords.shape[0], 16)).astype(np.float32)
+    w = (rng.standard_normal((kvol, 16, 24)) * 0.1).astype(np.float32)
+    xf = torch.from_numpy(feats).cuda().requires_grad_(True)
+    wt = torch.from_numpy(w).cuda().requires_grad_(True)
+    x = ts.SparseTensor(xf, torch.from_numpy(coords).cuda(), stride=(st,) * 3, spatial_range=srange)
+    y = F.conv3d(x, wt, ks, None, st, 0, config=cfg, transposed=True, generative=True)
+    assert y.stride == (1, 1, 1) and tuple(y.spatial_range) == tuple(want["spatial_range"])
+    assert np.array_equal(y.coords.cpu().numpy(), want["coords"])
+    m = want["sizes"][1]
+    ref = ko.conv_from_map(feats, w, want["out_in_map"], m)
+    assert rel_l2(y.feats.detach().cpu().numpy(), ref) < 1e-5
+    assert x._caches.kmaps == {} and x._caches.hashmaps == {}
+    gy = rng.standard_normal((m, 24)).astype(np.float32)
+    y.feats.backward(torch.from_numpy(gy).cuda())
+    want_dx, want_dw = ko.conv_backward_from_map(feats, w, want["out_in_map"], m, gy)
+    assert rel_l2(xf.grad.cpu().numpy(), want_dx) < 1e-5 and rel_l2(wt.grad.cpu().numpy(), want_dw) < 1e-5
+    # generative_add: union of coordinates, equal coordinates summed
+    other_c = np.unique(np.concatenate([want["coords"][::3], random_coords(rng, 200, (20, 20, 20), 2)]), axis=0)
+    other_f = rng.standard_normal((other_c.shape[0], 24)).astype(np.float32)
+    z = ts.generative_add(ts.SparseTensor(y.feats.detach(), y.coords), ts.SparseTensor(torch.from_numpy(other_f).cuda(),
+                                                                                      torch.from_numpy(other_c).cuda()))
+    union = np.unique(np.concatenate([want["coords"], other_c]), axis=0)
+    assert np.array_equal(z.coords.cpu().numpy(), union)
+    dense = {tuple(c): f.copy() for c, f in zip(want["coords"].tolist(), y.feats.detach().cpu().numpy())}
+    for c, f in zip(other_c.tolist(), other_f):
+        dense[tuple(c)] = dense.get(tuple(c), 0) + f
+    want_z = np.stack([dense[tuple(c)] for c in union.tolist()])
+    assert rel_l2(z.feats.cpu().numpy(), want_z) < 1e-6

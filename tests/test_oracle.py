@@ -191,3 +191,22 @@ def test_oracle_hashmap_mode_pinned_by_dense_conv(ks, st, pd):
     y = ko.conv_from_map(feats, w, km["out_in_map"], m)
     want = _dense_conv_at(coords, feats, w, ks, st, pd, km["coords"])
     assert np.abs(y - want).max() < 1e-12
+
+
+def test_generative_kernel_map_small_case():
+    """One input voxel at (1, 1, 1) of a stride-2 tensor, kernel 2, stride 2, input range 16 per axis: the range the
+    strided formula derives is 8, the eight generated voxels are (2..3)^3, and only the one that equals the scaled
+    input is linked to it (the lookup adds the cell offset to the OUTPUT coordinate, hashmap_cuda.cuh:215-232)."""
+    km = ko.build_kmap_generative(np.array([[0, 1, 1, 1]], dtype=np.int32), 2, 2, 0, (1, 16, 16, 16))
+    assert km["spatial_range"] == (1, 8, 8, 8)
+    want = np.array([[0, x, y, z] for x in (2, 3) for y in (2, 3) for z in (2, 3)], dtype=np.int32)
+    assert np.array_equal(km["coords"], want)
+    m = km["out_in_map"][:8]
+    assert m[0, 0] == 0 and (m.ravel() >= 0).sum() == 1
+    # two inputs one cell apart along z: the output between them (2, 2, 3) sees the second input at cell (0, 0, 1)
+    km = ko.build_kmap_generative(np.array([[0, 1, 1, 1], [0, 1, 1, 2]], dtype=np.int32), 2, 2, 0, (1, 16, 16, 16))
+    row = [tuple(c) for c in km["coords"].tolist()].index((0, 2, 2, 3))
+    assert km["out_in_map"][row].tolist() == [-1, 1, -1, -1, -1, -1, -1, -1]
+    # clamping: the generated coordinates never leave the derived range
+    km = ko.build_kmap_generative(np.array([[0, 3, 3, 3]], dtype=np.int32), 2, 2, 0, (1, 8, 8, 8))
+    assert km["spatial_range"] == (1, 4, 4, 4) and km["coords"].tolist() == [[0, 3, 3, 3]]

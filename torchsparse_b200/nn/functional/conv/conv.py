@@ -141,18 +141,33 @@ def conv3d(
         out_stride = tuple(input.stride[k] * stride[k] for k in range(3))
         out_range = kmap["spatial_range"]
     else:
-        if generative:
-            raise NotImplementedError("generative transposed convolution is not built")
         tensor_stride = tuple(input.stride[k] // stride[k] for k in range(3))
-        kmap = caches.kmaps.get((tensor_stride, kernel_size, stride, dilation))
-        kmap = transpose_kernel_map(kmap, config["ifsort"], training=training,
-                                    split_mask_num=config["split_mask_num"],
-                                    split_mask_num_bwd=config["split_mask_num_bwd"])
-        if dataflow != Dataflow.ImplicitGEMM and kmap.get("nbmaps") is None:
-            raise ValueError("the cached kernel map was built for another dataflow")
-        out_feats = _apply(fn, feats, weight, kmap, config, True, epilogue if fused else None)
-        out_coords, out_range = caches.cmaps[tensor_stride]
-        out_stride = tensor_stride
+        if generative:
+            # new coordinates are generated from the inputs; the map is built afresh (no table is reused) and the
+            # convolution runs as a plain (not transposed) one on it
+            # (torchsparse/nn/functional/conv/conv.py:161-203)
+            from .kmap import build_kernel_map
+            padding = make_ntuple(padding, ndim=3)
+            kmap = build_kernel_map(coords, feats.shape[0], kernel_size, stride, padding, None, None,
+                                    input.spatial_range, config["kmap_mode"], dataflow,
+                                    downsample_mode=config["downsample_mode"], training=training,
+                                    ifsort=config["ifsort"], generative=True)
+            out_feats = _apply(fn, feats, weight, kmap, config, False, epilogue if fused else None)
+            caches.cmaps[tensor_stride] = (kmap["coords"], kmap.get("spatial_range"))
+            out_coords, out_range = caches.cmaps[tensor_stride]
+            out_stride = tensor_stride
+            caches.kmaps = dict()
+            caches.hashmaps = dict()
+        else:
+            kmap = caches.kmaps.get((tensor_stride, kernel_size, stride, dilation))
+            kmap = transpose_kernel_map(kmap, config["ifsort"], training=training,
+                                        split_mask_num=config["split_mask_num"],
+                                        split_mask_num_bwd=config["split_mask_num_bwd"])
+            if dataflow != Dataflow.ImplicitGEMM and kmap.get("nbmaps") is None:
+                raise ValueError("the cached kernel map was built for another dataflow")
+            out_feats = _apply(fn, feats, weight, kmap, config, True, epilogue if fused else None)
+            out_coords, out_range = caches.cmaps[tensor_stride]
+            out_stride = tensor_stride
 
     if bias is not None:
         out_feats += bias

@@ -95,9 +95,7 @@ def build_kernel_map(
     the ravel bounds of a reused table be looked up instead of recomputed."""
     if mode not in ("hashmap_on_the_fly", "hashmap"):
         raise ValueError(f"unknown kmap_mode {mode!r}")
-    if generative and mode == "hashmap":
-        raise NotImplementedError("generative transposed convolution is not built")
-    if generative:
+    if generative and mode != "hashmap":
         raise ValueError(
             f"Unsupported kmap_mode: {mode} for generative convolution (please switch to kmap_mode=hashmap).")
     kmap = dict.fromkeys(
@@ -115,8 +113,11 @@ def build_kernel_map(
     coords = _coords.contiguous()
     n = coords.shape[0]
     if mode == "hashmap":
-        hashmap_keys, hashmap_vals = _hashmap_mode_map(kmap, coords, kernel_size, stride, padding, new_range,
-                                                       subm, downsample_mode, caches, tensor_stride)
+        if generative:
+            hashmap_keys, hashmap_vals = _generative_map(kmap, coords, kernel_size, stride, padding, new_range)
+        else:
+            hashmap_keys, hashmap_vals = _hashmap_mode_map(kmap, coords, kernel_size, stride, padding, new_range,
+                                                           subm, downsample_mode, caches, tensor_stride)
         return _finish_kernel_map(kmap, n, input_node_num, hashmap_keys, hashmap_vals, dataflow, ifsort,
                                   split_mask_num)
     cmin_act, cmax_act = _actual_bounds(coords, caches, tensor_stride)
@@ -202,6 +203,30 @@ def _hashmap_mode_map(kmap, coords, kernel_size, stride, padding, spatial_range,
     kmap["out_in_map"] = table.lookup_coords(out_coords[:, [1, 2, 3, 0]], kernel_size, stride, kvol) - 1
     kmap["coords"] = out_coords
     kmap["table_stride"] = tensor_stride
+    kmap["table_bounds"] = _FNV_TABLE
+    return keys, vals
+
+
+def _generative_map(kmap, coords, kernel_size, stride, padding, spatial_range):
+    """Kernel map of a generative transposed convolution
+    (torchsparse/nn/functional/conv/kmap/func/hashmap.py:37-40, 58-64, 74-83): the output coordinates are generated
+    from the inputs (``spupsample_generative``, clamped to ``spatial_range`` - the range the caller derived with the
+    strided-convolution formula, as the reference does), the inputs are inserted at ``coords * stride``, and every
+    (output row, kernel cell) looks up ``output + cell offset`` with stride 1."""
+    from .upsample import spupsample_generative
+
+    out_coords = spupsample_generative(coords, stride, kernel_size, padding, spatial_range)
+    cap = _table_capacity(coords.shape[0])
+    keys = torch.zeros(cap, dtype=torch.int64, device=coords.device)
+    vals = torch.zeros(cap, dtype=torch.int32, device=coords.device)
+    table = backend.GPUHashTable(keys, vals)
+    scaled = coords.clone()
+    scaled[:, 1:] *= torch.tensor(stride, dtype=coords.dtype, device=coords.device)
+    table.insert_coords(scaled[:, [1, 2, 3, 0]])
+    kvol = kernel_size[0] * kernel_size[1] * kernel_size[2]
+    kmap["out_in_map"] = table.lookup_coords(out_coords[:, [1, 2, 3, 0]].contiguous(), kernel_size, (1, 1, 1), kvol) - 1
+    kmap["coords"] = out_coords
+    kmap["table_stride"] = None
     kmap["table_bounds"] = _FNV_TABLE
     return keys, vals
 

@@ -4,7 +4,7 @@ import torch
 
 from .tensor import CatSparseTensor, SparseTensor
 
-__all__ = ["cat"]
+__all__ = ["cat", "generative_add"]
 
 # When True (set by the inference engine around its forward), `cat` of two tensors returns a
 # CatSparseTensor: the concatenated matrix is only written if a layer asks for `.feats`; the fused
@@ -27,3 +27,19 @@ def cat(inputs: List[SparseTensor]) -> SparseTensor:
     output = SparseTensor(coords=first.coords, feats=feats, stride=first.stride, spatial_range=first.spatial_range)
     output._caches = first._caches
     return output
+
+
+def generative_add(a: SparseTensor, b: SparseTensor) -> SparseTensor:
+    """Sum of two tensors over the union of their coordinates (torchsparse/operators.py:53-64): rows with equal
+    coordinates are added, the rest are kept; the output rows are in lexicographic coordinate order
+    (``torch.unique(dim=0)``), stride, spatial range and caches are those of the operand with more rows."""
+    first, second = (a, b) if a.feats.shape[0] >= b.feats.shape[0] else (b, a)
+    union_coords = torch.cat([first.coords, second.coords], dim=0)
+    union_feats = torch.cat([first.feats, second.feats], dim=0)
+    unique_coords, inverse = torch.unique(union_coords, dim=0, return_inverse=True)
+    out_feats = torch.zeros((unique_coords.shape[0], union_feats.shape[1]), dtype=union_feats.dtype,
+                            device=union_feats.device)
+    out_feats.index_add_(0, inverse, union_feats)
+    out = SparseTensor(out_feats, unique_coords, first.stride, spatial_range=first.spatial_range)
+    out._caches = first._caches
+    return out
