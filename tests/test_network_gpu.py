@@ -193,12 +193,12 @@ def test_training_step_through_a_unet():
 
 @pytest.mark.parametrize("fused", [False, True])
 def test_tune_assigns_a_config_per_group_and_keeps_results(fused):
-    """utils.tune.tune: every group of convolutions sharing a kernel map gets one of the candidates,
+    """utils.tune.tune_candidates: every group of convolutions sharing a kernel map gets one of the candidates,
     and the tuned model computes the same function."""
     import torchsparse_b200 as ts
     from torchsparse_b200.backbones import SparseResUNet42
     from torchsparse_b200.nn import InferenceEngine
-    from torchsparse_b200.utils.tune import default_candidates, tune
+    from torchsparse_b200.utils.tune import default_candidates, tune_candidates as tune
 
     torch.manual_seed(0)
     model = SparseResUNet42(in_channels=4, width_multiplier=0.5)
@@ -218,3 +218,47 @@ def test_tune_assigns_a_config_per_group_and_keeps_results(fused):
     with torch.no_grad():
         after = model(ts.SparseTensor(f, c))[-1].feats.float()
     assert rel_l2(after.cpu().numpy(), before.cpu().numpy()) < 2e-3
+
+
+def test_tuner_searches_the_reference_space_saves_and_reloads(tmp_path):
+    """utils.tune.tune with the reference's arguments (torchsparse/utils/tune.py:373-386): the three dataflows with
+    pruning, the table saved under save_dir/tune_tag in the reference's format, applied to the layers, the model
+    unchanged in what it computes; a second call loads the table instead of measuring."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200.backbones import SparseResUNet42
+    from torchsparse_b200.nn import functional as F
+    from torchsparse_b200.nn.modules.conv import Conv3d
+    from torchsparse_b200.utils.tune import search_space, tune
+
+    torch.manual_seed(0)
+    model = SparseResUNet42(in_channels=4, width_multiplier=0.5)
+    _randomise_bn(model)
+    model = model.cuda().half().eval()
+    coords, feats = _scan_crop()
+    x = ts.SparseTensor(torch.from_numpy(feats).half(), torch.from_numpy(coords))
+    loader = [{"input": x}, {"input": x}]
+    with torch.no_grad():
+        before = model(ts.SparseTensor(x.feats.cuda(), x.coords.cuda()))[-1].feats.float()
+    flows = [F.Dataflow.ImplicitGEMM, F.Dataflow.FetchOnDemand, F.Dataflow.GatherScatter]
+    assert len(search_space(flows)) == 8
+    table = tune(model, loader, n_samples=1, collect_fn=lambda d: d["input"], enable_fp16=True, save_dir=str(tmp_path),
+                 tune_tag="unet", dataflow_range=flows, dataflow_prune=True, verbose=False, skip_warning=True)
+    assert len(table) >= 5
+    fields = {"epsilon", "mm_thresh", "split_mask_num", "split_mask_num_bwd", "dataflow", "ifsort", "FOD_fusion"}
+    assert all(set(cfg) == fields and cfg["dataflow"] in flows for cfg in table.values())
+    name_to_group, saved = torch.load(tmp_path / "unet", weights_only=False)
+    assert saved == table and all(g in table for g in name_to_group.values())
+    convs = {n: m for n, m in model.named_modules() if isinstance(m, Conv3d) and m.kernel.dim() == 3}
+    assert set(name_to_group) == set(convs)
+    for n, m in convs.items():
+        assert m._config["dataflow"] == table[name_to_group[n]]["dataflow"]
+        assert m._config["ifsort"] == table[name_to_group[n]]["ifsort"]
+    with torch.no_grad():
+        after = model(ts.SparseTensor(x.feats.cuda(), x.coords.cuda()))[-1].feats.float()
+    assert rel_l2(after.cpu().numpy(), before.cpu().numpy()) < 2e-3
+    # the table on disk is applied to a fresh model without measuring (an empty loader would otherwise raise)
+    fresh = SparseResUNet42(in_channels=4, width_multiplier=0.5).cuda().half().eval()
+    again = tune(fresh, [], save_dir=str(tmp_path), tune_tag="unet", verbose=False, skip_warning=True)
+    assert again == table
+    got = {n: m._config["dataflow"] for n, m in fresh.named_modules() if isinstance(m, Conv3d) and m.kernel.dim() == 3}
+    assert got == {n: table[name_to_group[n]]["dataflow"] for n in convs}
