@@ -516,6 +516,10 @@ int tsb_voxel_inputs(const float* points, int32_t c_in, const int64_t* first_ind
  * Replaces to_dense_forward_cuda (torchsparse/backend/voxelize/voxelize_cuda.cu:116-127). */
 int tsb_to_dense_fwd(const void* feats, const int32_t* coords, int64_t n, int32_t c,
                      const int32_t* range, int32_t dtype, void* out, tsb_stream_t stream);
+/* grad_feats[i][:] = grad_dense[cell of coords[i]][:] (zeros for a row outside `range`).
+ * Replaces to_dense_backward_cuda (torchsparse/backend/voxelize/voxelize_cuda.cu:26-37, 129-141). */
+int tsb_to_dense_bwd(const void* grad_dense, const int32_t* coords, int64_t n, int32_t c,
+                     const int32_t* range, int32_t dtype, void* grad_feats, tsb_stream_t stream);
 
 #ifdef __cplusplus
 }

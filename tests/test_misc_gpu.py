@@ -172,3 +172,34 @@ def test_tensor_core_weight_gradient_vs_oracle(dtype, n, cg, cd, ks):
     got_t = backend.conv_backward_wgrad_implicit_gemm_cuda(dy.cuda(), x.cuda(), map_t, 32)
     assert got_t.dtype == dtype and got_t.numel() == want.size
     assert rel_l2(got_t.float().reshape(ks ** 3, cd, cg).transpose(1, 2).cpu().numpy(), want) < 4e-3
+
+
+def test_to_dense_gradient_and_group_norm():
+    """`to_dense` is differentiable (gather of the dense gradient, torchsparse/utils/to_dense.py:41-64) and `GroupNorm`
+    normalises every batch sample on its own (torchsparse/nn/modules/norm.py:25-57)."""
+    import torchsparse_b200 as ts
+    from torchsparse_b200 import nn as spnn
+    from torchsparse_b200.utils.to_dense import to_dense
+
+    rng = np.random.default_rng(5)
+    coords = random_coords(rng, 800, (10, 9, 8), 2)
+    n, c = coords.shape[0], 12
+    feats = torch.from_numpy(rng.standard_normal((n, c)).astype(np.float32)).cuda().requires_grad_()
+    ct = torch.from_numpy(coords).cuda()
+    dense = to_dense(feats, ct, (2, 10, 9, 8))
+    g = torch.from_numpy(rng.standard_normal(tuple(dense.shape)).astype(np.float32)).cuda()
+    dense.backward(g)
+    idx = ct.long()
+    want = g[idx[:, 0], idx[:, 1], idx[:, 2], idx[:, 3]]
+    assert torch.equal(feats.grad, want)
+    assert torch.equal(dense[idx[:, 0], idx[:, 1], idx[:, 2], idx[:, 3]], feats.detach())
+
+    gn = spnn.GroupNorm(4, c).cuda()
+    with torch.no_grad():
+        gn.weight.uniform_(0.5, 1.5)
+        gn.bias.uniform_(-0.5, 0.5)
+    y = gn(ts.SparseTensor(feats.detach(), ct)).feats
+    for b in range(2):
+        rows = ct[:, 0] == b
+        ref = torch.nn.functional.group_norm(feats.detach()[rows].t().unsqueeze(0), 4, gn.weight, gn.bias, gn.eps)
+        assert rel_l2(y[rows].cpu().numpy(), ref.squeeze(0).t().cpu().numpy()) < 1e-6

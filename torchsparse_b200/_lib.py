@@ -79,6 +79,7 @@ SIGNATURES = {
     "tsb_voxelize_bwd": (C.c_int, [P, P, P, I64, I64, I32, P, P]),
     "tsb_devoxelize_bwd": (C.c_int, [P, P, P, I64, I64, I32, P, P]),
     "tsb_to_dense_fwd": (C.c_int, [P, P, I64, I32, P, I32, P, P]),
+    "tsb_to_dense_bwd": (C.c_int, [P, P, I64, I32, P, I32, P, P]),
 }
 
 class IgemmDesc(C.Structure):

@@ -33,7 +33,7 @@ __all__ = [
     "conv_backward_wgrad_implicit_gemm_cuda", "conv_backward_wgrad_implicit_gemm_sorted_cuda",
     "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
     "conv_forward_fetch_on_demand_no_fusion_cuda", "voxelize_forward_cuda", "devoxelize_forward_cuda",
-    "voxelize_backward_cuda", "devoxelize_backward_cuda", "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda",
+    "voxelize_backward_cuda", "devoxelize_backward_cuda", "hash_cuda", "kernel_hash_cuda", "hash_query_cuda", "count_cuda", "to_dense_forward_cuda", "to_dense_backward_cuda",
     "pairs_from_out_in_map", "quantize_unique_cuda", "tile_mask_cuda", "sorted_cm_artefacts_cuda", "SortedMap",
 ]
 
@@ -1133,6 +1133,16 @@ def to_dense_forward_cuda(feats: torch.Tensor, coords: torch.Tensor, spatial_ran
     feats, coords = feats.contiguous(), coords.int().contiguous()
     check(lib.tsb_to_dense_fwd(_p(feats), _p(coords), feats.shape[0], feats.shape[1], i32x(rng), _dtype_code(feats),
                                _p(outputs), _stream()), "to_dense_forward_cuda")
+
+
+def to_dense_backward_cuda(top_grad: torch.Tensor, coords: torch.Tensor, spatial_range, bottom_grad: torch.Tensor) -> None:
+    """Gather of the dense gradient into the caller's [N, C] tensor
+    (torchsparse/backend/voxelize/voxelize_cuda.cu:129-141)."""
+    _need_cuda(top_grad, coords, bottom_grad)
+    rng = _host_ints(spatial_range, 4)
+    top_grad, coords = top_grad.contiguous(), coords.int().contiguous()
+    check(lib.tsb_to_dense_bwd(_p(top_grad), _p(coords), bottom_grad.shape[0], bottom_grad.shape[1], i32x(rng),
+                               _dtype_code(bottom_grad), _p(bottom_grad), _stream()), "to_dense_backward_cuda")
 
 
 def quantize_unique_cuda(xyz: torch.Tensor, voxel_size: Sequence[float], return_index: bool, return_inverse: bool):

@@ -94,6 +94,24 @@ __global__ void to_dense_kernel(const T* __restrict__ feats, const int4* __restr
   }
 }
 
+// Backward of to_dense: grad_feats[i] = grad_dense[cell of coords[i]] (zero for a row outside the range).
+template <typename T>
+__global__ void to_dense_bwd_kernel(const T* __restrict__ grad_dense, const int4* __restrict__ coords, int64_t n, int c,
+                                    int r0, int r1, int r2, int r3, T* __restrict__ grad_feats) {
+  const int64_t total = n * c;
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    int64_t i = t / c;
+    int j = (int)(t - i * c);
+    int4 p = __ldg(&coords[i]);
+    if (p.x < 0 || p.x >= r0 || p.y < 0 || p.y >= r1 || p.z < 0 || p.z >= r2 || p.w < 0 || p.w >= r3) {
+      grad_feats[t] = T(0.f);
+      continue;
+    }
+    int64_t pos = (((int64_t)p.x * r1 + p.y) * r2 + p.z) * r3 + p.w;
+    grad_feats[t] = grad_dense[pos * c + j];
+  }
+}
+
 // Backward of the average pooling: grad_feats[i] = grad_out[idx[i]] / counts[idx[i]] (a gather; fp32 gradients).
 __global__ void voxelize_bwd_kernel(const float* __restrict__ grad_out, const int* __restrict__ idx,
                                     const int* __restrict__ counts, int64_t n, int64_t n_vox, int c,
@@ -218,6 +236,23 @@ int tsb_to_dense_fwd(const void* feats, const int32_t* coords, int64_t n, int32_
     case TSB_F32: to_dense_kernel<float><<<grid, kBlock, 0, st>>>((const float*)feats, c4, n, c, range[0], range[1], range[2], range[3], (float*)out); break;
     case TSB_F16: to_dense_kernel<__half><<<grid, kBlock, 0, st>>>((const __half*)feats, c4, n, c, range[0], range[1], range[2], range[3], (__half*)out); break;
     case TSB_BF16: to_dense_kernel<__nv_bfloat16><<<grid, kBlock, 0, st>>>((const __nv_bfloat16*)feats, c4, n, c, range[0], range[1], range[2], range[3], (__nv_bfloat16*)out); break;
+    default: return TSB_ERR_UNSUPPORTED;
+  }
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int tsb_to_dense_bwd(const void* grad_dense, const int32_t* coords, int64_t n, int32_t c, const int32_t* range,
+                     int32_t dtype, void* grad_feats, tsb_stream_t stream) {
+  if (n < 0 || c < 1 || !range || (n && (!grad_dense || !coords || !grad_feats))) return TSB_ERR_BAD_ARG;
+  if (n == 0) return TSB_OK;
+  cudaStream_t st = as_stream(stream);
+  int grid = grid_for(n * (int64_t)c, kBlock, 32);
+  const int4* c4 = reinterpret_cast<const int4*>(coords);
+  switch (dtype) {
+    case TSB_F32: to_dense_bwd_kernel<float><<<grid, kBlock, 0, st>>>((const float*)grad_dense, c4, n, c, range[0], range[1], range[2], range[3], (float*)grad_feats); break;
+    case TSB_F16: to_dense_bwd_kernel<__half><<<grid, kBlock, 0, st>>>((const __half*)grad_dense, c4, n, c, range[0], range[1], range[2], range[3], (__half*)grad_feats); break;
+    case TSB_BF16: to_dense_bwd_kernel<__nv_bfloat16><<<grid, kBlock, 0, st>>>((const __nv_bfloat16*)grad_dense, c4, n, c, range[0], range[1], range[2], range[3], (__nv_bfloat16*)grad_feats); break;
     default: return TSB_ERR_UNSUPPORTED;
   }
   TSB_LAUNCH_CHECK();
