@@ -182,7 +182,7 @@ def test_to_dense_gradient_and_group_norm():
     from torchsparse_b200.utils.to_dense import to_dense
 
     rng = np.random.default_rng(5)
-    coords = random_coords(rng, 800, (10, 9, 8), 2)
+    coords = random_coords(rng, 300, (10, 9, 8), 2)
     n, c = coords.shape[0], 12
     feats = torch.from_numpy(rng.standard_normal((n, c)).astype(np.float32)).cuda().requires_grad_()
     ct = torch.from_numpy(coords).cuda()
