@@ -252,3 +252,37 @@ def test_copy_engine_gather_equals_cp_async_gather(cin, cout, c1):
         assert torch.equal(outs[0], outs[1])
     else:
         assert rel_l2(outs[0].float().cpu().numpy(), outs[1].float().cpu().numpy()) < 1e-3
+
+
+@pytest.mark.parametrize("cin,cout", [(32, 48), (96, 96), (4, 16)])
+def test_exact_fp32_by_three_tf32_passes(cin, cout):
+    """fp32 operands with allow_tf32 = False: the three-pass TF32 split on the tensor cores and the CUDA-core kernel
+    both stay within relative L2 1e-5 of the fp64 oracle (the tolerance of every exact-fp32 test of this suite),
+    while a single TF32 pass does not."""
+    from torchsparse_b200 import backend, backends
+
+    rng = np.random.default_rng(cin * 7 + cout)
+    coords = random_coords(rng, 4000, (30, 30, 30))
+    n = coords.shape[0]
+    km = ko.build_kmap(coords, 3, 1, 1)
+    x = rng.standard_normal((n, cin)).astype(np.float32)
+    w = (rng.standard_normal((27, cin, cout)) / np.sqrt(27 * cin)).astype(np.float32)
+    want = ko.conv_from_map(x, w, km["out_in_map"], n)
+    xt, wt, m = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), torch.from_numpy(km["out_in_map"]).cuda()
+    errs = {}
+    try:
+        for name, split, tf32 in (("split", True, False), ("cuda_cores", False, False), ("tf32", True, True)):
+            backends.fp32_by_split_tf32 = split
+            y = backend.conv_forward_implicit_gemm_cuda(xt, wt, m, n, cout, tf32)
+            assert y.dtype == torch.float32
+            errs[name] = rel_l2(y.cpu().numpy(), want)
+    finally:
+        backends.fp32_by_split_tf32 = True
+    assert errs["split"] < 1e-5 and errs["cuda_cores"] < 1e-5, errs
+    assert errs["tf32"] > 1e-5, errs                       # one pass rounds the operands to 10 mantissa bits
+    # the fused epilogue rides on the last pass
+    scale = torch.rand(cout, device="cuda") + 0.5
+    bias = torch.randn(cout, device="cuda")
+    y = backend.conv_forward_implicit_gemm_cuda(xt, wt, m, n, cout, False, scale=scale, bias=bias, relu=True)
+    ref = np.maximum(want * scale.cpu().numpy() + bias.cpu().numpy(), 0)
+    assert rel_l2(y.cpu().numpy(), ref) < 1e-5

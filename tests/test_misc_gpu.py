@@ -198,8 +198,9 @@ def test_to_dense_gradient_and_group_norm():
     with torch.no_grad():
         gn.weight.uniform_(0.5, 1.5)
         gn.bias.uniform_(-0.5, 0.5)
-    y = gn(ts.SparseTensor(feats.detach(), ct)).feats
-    for b in range(2):
-        rows = ct[:, 0] == b
-        ref = torch.nn.functional.group_norm(feats.detach()[rows].t().unsqueeze(0), 4, gn.weight, gn.bias, gn.eps)
-        assert rel_l2(y[rows].cpu().numpy(), ref.squeeze(0).t().cpu().numpy()) < 1e-6
+    with torch.no_grad():
+        y = gn(ts.SparseTensor(feats.detach(), ct)).feats
+        for b in range(2):
+            rows = ct[:, 0] == b
+            ref = torch.nn.functional.group_norm(feats.detach()[rows].t().unsqueeze(0), 4, gn.weight, gn.bias, gn.eps)
+            assert rel_l2(y[rows].cpu().numpy(), ref.squeeze(0).t().cpu().numpy()) < 1e-6

@@ -611,6 +611,16 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
     1x1x1 kernel: row m reads input row m), a range of kernel offsets, fp32 partial sums in / out, a
     device-side row count and a caller-owned output.  ``smap`` (a :class:`SortedMap`) stands for the map, its
     strides, row order and work-item table in one argument."""
+    from . import backends
+    if (in_feats.dtype == torch.float32 and kernel.dtype == torch.float32 and not allow_tf32
+            and backends.fp32_by_split_tf32 and in_feats2 is None and acc_in is None and acc_out is None
+            and k_range is None and kernel.dim() == 3 and kernel.shape[1] % 4 == 0 and kernel.shape[2] % 8 == 0
+            and kernel.shape[0] <= 32 and in_feats.shape[0] > 0 and num_out_feats > 0
+            and in_feats.shape[1] == kernel.shape[1]):
+        return _conv_fp32_by_split_tf32(in_feats, kernel, out_in_map, num_out_feats, num_out_channels,
+                                        dict(scale=scale, bias=bias, residual=residual, relu=relu, out=out),
+                                        dict(reorder_loc=reorder_loc, tile_mask=tile_mask, map_strides=map_strides,
+                                             n_out_dev=n_out_dev, dst_rows=dst_rows, smap=smap))
     if smap is not None:
         out_in_map, reorder_loc, tile_mask, map_strides = smap.map_cm, smap.loc, smap.tile_mask, (1, smap.rows)
     in_feats, kernel = _prep_feats_cat(in_feats, in_feats2, kernel, allow_fp16)
@@ -696,6 +706,28 @@ def conv_forward_implicit_gemm_cuda(in_feats: torch.Tensor, kernel: torch.Tensor
         raise RuntimeError(f"conv_forward_implicit_gemm_cuda: a bounded wait inside the kernel ran out "
                            f"(code {int(status.item())}); the output is undefined")
     return out
+
+
+def _split_tf32(t: torch.Tensor):
+    """t = hi + lo with hi exactly representable in TF32 (the low 13 mantissa bits cleared)."""
+    hi = (t.contiguous().view(torch.int32) & -8192).view(torch.float32)
+    return hi, t - hi
+
+
+def _conv_fp32_by_split_tf32(in_feats, kernel, out_in_map, num_out_feats, cout, epilogue, common):
+    """fp32 convolution of fp32 operands on the tensor cores: three TF32 launches over the split operands, the
+    partial sums kept in fp32 between them (smallest terms first), the epilogue in the last launch.  Every product
+    of two TF32 numbers is exact in fp32, so what is dropped is x_lo * w_lo (relative 2^-22) and the rounding of
+    x_lo, w_lo to TF32 (relative 2^-21): the result stays within the 1e-5 relative error asked of fp32 paths."""
+    x_hi, x_lo = _split_tf32(in_feats)
+    w_hi, w_lo = _split_tf32(kernel)
+    rows = int(common.get("dst_rows") or 0) or num_out_feats
+    acc1 = torch.empty((rows, cout), dtype=torch.float32, device=in_feats.device)
+    acc2 = torch.empty_like(acc1)
+    conv_forward_implicit_gemm_cuda(x_lo, w_hi, out_in_map, num_out_feats, cout, True, acc_out=acc1, **common)
+    conv_forward_implicit_gemm_cuda(x_hi, w_lo, out_in_map, num_out_feats, cout, True, acc_in=acc1, acc_out=acc2, **common)
+    return conv_forward_implicit_gemm_cuda(x_hi, w_hi, out_in_map, num_out_feats, cout, True, acc_in=acc2, **epilogue,
+                                           **common)
 
 
 def _prep_feats_cat(in_feats, in_feats2, kernel, allow_fp16):

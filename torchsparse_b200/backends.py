@@ -9,6 +9,10 @@ allow_tf32 = False
 allow_fp16 = True
 device_capability = 0
 hash_rsv_ratio = 2  # table slots reserved per input point (>= 2)
+# Exact-fp32 convolutions (allow_tf32 = False) of tensor-core shapes: three TF32 passes over the split operands
+# (x_hi w_hi + x_hi w_lo + x_lo w_hi, fp32 accumulation) instead of the CUDA-core kernel; no counterpart in the
+# reference, whose fp32 path runs on the CUDA cores
+fp32_by_split_tf32 = True
 
 
 def init():
