@@ -717,6 +717,9 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------------------- single layers / maps
+_VOXEL_CACHE: dict = {}
+
+
 def run_layer(args, device):
     """Single sparse Conv3d layer (BASELINE config 5 cell): --layer N,Cin,Cout,kernel,stride,occupancy
     [--dataflow ImplicitGEMM|GatherScatter|FetchOnDemand] [--dtype f16|bf16|f32|tf32] [--sorted] [--transposed].
@@ -739,7 +742,11 @@ def run_layer(args, device):
             coords = F.build_kernel_map(coords, coords.shape[0], 2, 2, 0, None, None, None, "hashmap_on_the_fly")["coords"]
         n, side, occ = coords.shape[0], 0, f"lidar level {args.lidar_level}"
     else:
-        coords_np, side = uniform_voxels(0, n, occ)
+        key = (n, occ)
+        if key not in _VOXEL_CACHE:
+            _VOXEL_CACHE.clear()                       # one set at a time (a sweep visits equal keys in a row)
+            _VOXEL_CACHE[key] = uniform_voxels(0, n, occ)
+        coords_np, side = _VOXEL_CACHE[key]
         coords = torch.from_numpy(coords_np).to(device)
     g = torch.Generator(device=device).manual_seed(0)
     kvol = ks ** 3
@@ -920,6 +927,61 @@ def run_pointops(args, device):
     return out
 
 
+def run_sweep(args, device):
+    """BASELINE config 5 (--sweep reduced|full): single-layer cells through `run_layer` in one process.
+    reduced: {k3 s1, k2 s2, k2 s2 transposed} x {16, 64, 128, 256} channels x {10k, 100k, 1M} voxels at 5 % occupancy
+    x the three dataflows x {f16, tf32, f32}, plus the 1 % and 20 % occupancies at 100k voxels and the 2M-voxel cells
+    for the implicit GEMM in f16.  full: every cell of the grid.  One JSON line with a list of cells."""
+    import copy
+
+    kinds = [(3, 1, False), (2, 2, False), (2, 2, True)]
+    chans = [16, 64, 128, 256]
+    flows = ["ImplicitGEMM", "GatherScatter", "FetchOnDemand"]
+    dtypes = ["f16", "tf32", "f32"]
+    cells = []
+    if args.sweep == "full":
+        for n in (10_000, 100_000, 1_000_000, 2_000_000):
+            for occ in (0.01, 0.05, 0.2):
+                for kind in kinds:
+                    for c in chans:
+                        for fl in flows:
+                            for dt in dtypes:
+                                cells.append((n, occ, kind, c, fl, dt))
+    else:
+        for n in (10_000, 100_000, 1_000_000):
+            for kind in kinds:
+                for c in chans:
+                    for fl in flows:
+                        for dt in dtypes:
+                            cells.append((n, 0.05, kind, c, fl, dt))
+        for occ in (0.01, 0.2):
+            for kind in kinds:
+                for c in chans:
+                    cells.append((100_000, occ, kind, c, "ImplicitGEMM", "f16"))
+        for kind in kinds:
+            for c in chans:
+                cells.append((2_000_000, 0.05, kind, c, "ImplicitGEMM", "f16"))
+    out = []
+    for n, occ, (ks, st, tr), c, fl, dt in cells:
+        a = copy.copy(args)
+        a.layer, a.dataflow, a.dtype, a.transposed = f"{n},{c},{c},{ks},{st},{occ}", fl, dt, tr
+        a.sorted, a.smap, a.lidar_level, a.backward = False, False, -1, ""
+        try:
+            r = run_layer(a, device)
+            out.append({"n": n, "occupancy": occ, "kernel": ks, "stride": st, "transposed": tr, "channels": c,
+                        "dataflow": fl, "dtype": dt, "ms": r["value"], "pairs": r["pairs"], "n_out": r["n_out"],
+                        "useful_tflops": r["useful_tflops"], "algorithmic_gbs": r["algorithmic_gbs"],
+                        "frac_tensor_peak": r["frac_tensor_peak"], "frac_hbm_peak": r["frac_hbm_peak"]})
+        except Exception as e:      # a cell that does not fit or is not supported is reported, not fatal
+            out.append({"n": n, "occupancy": occ, "kernel": ks, "stride": st, "transposed": tr, "channels": c,
+                        "dataflow": fl, "dtype": dt, "error": f"{type(e).__name__}: {e}"[:200]})
+        torch.cuda.empty_cache()
+    pk = peaks()
+    return {"metric": "layer_sweep", "unit": "ms", "higher_is_better": False, "steps": args.steps, "warmup": args.warmup,
+            "config": {"workload": f"BASELINE config 5 layer sweep ({args.sweep}), {len(out)} cells"},
+            "peaks": pk, "cells": out}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -934,6 +996,7 @@ def main():
     ap.add_argument("--no-kmap", action="store_true", help="skip the isolated kernel-map timings")
     ap.add_argument("--layer", default=None, help="N,Cin,Cout,kernel,stride[,occupancy]: single-layer mode")
     ap.add_argument("--kmap", default=None, help="N,kernel,stride[,occupancy|lidar]: kernel-map build timing")
+    ap.add_argument("--sweep", default=None, choices=["reduced", "full"], help="BASELINE config 5: single-layer cells")
     ap.add_argument("--pointops", default=None, help="N: timings of the point <-> voxel operators on N points")
     ap.add_argument("--dataflow", default="ImplicitGEMM")
     ap.add_argument("--dtype", default="f16")
@@ -961,7 +1024,7 @@ def main():
             k, v = kv.split("=")
             _backend.igemm_tuning[k] = int(v)
     if args.conv_grid < 0:
-        args.conv_grid = CONV_GRID_SHARED if (args.streams > 1 and not args.layer and not args.kmap and not args.pointops) else 0
+        args.conv_grid = CONV_GRID_SHARED if (args.streams > 1 and not args.layer and not args.kmap and not args.pointops and not args.sweep) else 0
     if args.conv_grid and args.layer:      # the engines of the step benchmark get it as their own setting
         from torchsparse_b200 import backend as _backend
         _backend.igemm_tuning["grid"] = args.conv_grid
@@ -986,9 +1049,9 @@ def main():
 
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if args.layer or args.kmap or args.pointops:
+    if args.layer or args.kmap or args.pointops or args.sweep:
         if rank == 0:
-            fn = run_layer if args.layer else run_kmap if args.kmap else run_pointops
+            fn = run_sweep if args.sweep else run_layer if args.layer else run_kmap if args.kmap else run_pointops
             print(json.dumps(fn(args, device)), flush=True)
         return
     if world > 1:
