@@ -776,6 +776,18 @@ def run_layer(args, device):
                                                               True, smap=sm)
         run()
         torch.cuda.synchronize()
+    if args.cmap:
+        # the map as built, stored column-major ([kvol][rows]): the per-offset reads of the kernel become contiguous
+        sfx = "_t" if args.transposed else ""
+        rows_valid = kmap["sizes"][0] if args.transposed else kmap["sizes"][1]
+        rm = kmap["out_in_map" + sfx]
+        cm = rm.t().contiguous()
+        tmask = backend.tile_mask_cuda(cm, rows_valid, 1, cm.shape[1])
+        xin, wk = (mid.feats, wt) if args.transposed else (x.feats, w)
+        run = lambda: backend.conv_forward_implicit_gemm_cuda(xin, wk, cm, rows_valid, wk.shape[2], backends.allow_tf32,
+                                                              True, tile_mask=tmask, map_strides=(1, cm.shape[1]))
+        run()
+        torch.cuda.synchronize()
     n_out = kmap["sizes"][0] if args.transposed else kmap["sizes"][1]
     n_in = kmap["sizes"][1] if args.transposed else n
     if args.backward:
@@ -989,7 +1001,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c4"])
-    ap.add_argument("--repeats", type=int, default=15, help="timed passes of --steps steps each (the median is reported)")
+    ap.add_argument("--repeats", type=int, default=25, help="timed passes of --steps steps each (the median is reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass (profiling runs)")
     ap.add_argument("--no-batch32", action="store_true", help="skip the 32-scan batch (profiling runs)")
@@ -1004,6 +1016,7 @@ def main():
     ap.add_argument("--transposed", action="store_true")
     ap.add_argument("--backward", default="", choices=["", "wgrad", "dgrad"],
                     help="layer mode: time the weight-gradient or the input-gradient launch instead of the forward")
+    ap.add_argument("--cmap", action="store_true", help="layer mode: run on a column-major copy of the map as built")
     ap.add_argument("--smap", action="store_true", help="layer mode: run on the row-sorted column-major map of the engines")
     ap.add_argument("--lidar-level", type=int, default=-1, help="layer mode: rows of the benchmark scan at stride 2^L")
     ap.add_argument("--streams", type=int, default=8,
