@@ -619,6 +619,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
       return true;
     };
     int src[kCopies], nxt[kCopies];
+    const uint32_t a_stage0 = smem_base + dst_off;     // this thread's first destination in stage 0
+    uint32_t a_stage = a_stage0;
     bool have = next_offset(src);
     while (have && ok) {
       const bool have_next = next_offset(nxt);       // in flight while this offset is copied
@@ -636,7 +638,6 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
 #ifdef TSB_TRACE_BUILD
         if (tid == 0) TSB_TRACE_HOT(1, blk);
 #endif
-        const uint32_t a_stage = smem_base + stage * (uint32_t)stage_bytes + dst_off;
         for (int cc = 0; cc < p.cpb; ++cc) {
           const int c = g * p.cpb + cc;
           const int col = c * kChunk + gran * kGran;
@@ -661,7 +662,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
         if (tid == 0) TSB_TRACE_HOT(2, blk);
         ++blk;
 #endif
-        if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; }
+        a_stage += (uint32_t)stage_bytes;
+        if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; first_pass = false; a_stage = a_stage0; }
       }
 #pragma unroll
       for (int j = 0; j < kCopies; ++j) src[j] = nxt[j];
@@ -973,8 +975,11 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
     const uint32_t a_units = (uint32_t)kABytes >> 4;
     const uint32_t b_units = (uint32_t)b_bytes >> 4;
     const uint32_t b_first = (uint32_t)p.cpb * a_units;                 // first weight chunk of a stage
-    const uint32_t base_units = smem_base >> 4;
-    uint32_t stage = 0, phase = 0;
+    // stage index, barrier phase and descriptor words are carried incrementally: no multiplication per block
+    // in the instruction stream that every other role of the CTA waits for
+    const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | lo_flag;      // stage 0, first A chunk
+    const int last_steps = ((p.cin - (chunks - 1) * kChunk) + kStepK - 1) / kStepK;   // cp.async variant
+    uint32_t stage = 0, phase = 0, a_lo = a_lo0;
     int acc_count = 0;
     bool ok = true;
 #ifdef TSB_TRACE_BUILD
@@ -1004,7 +1009,7 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
       const uint32_t acc = tmem_base + (uint32_t)ab * acc_cols;
       uint32_t accumulate = 0;
       for (uint32_t km = kmask; km && ok; km &= km - 1) {       // one trip per offset present in the tile
-        for (int g = 0; g < groups; ++g) {
+        for (int c_lo = 0; c_lo < chunks; c_lo += p.cpb) {
 #ifdef TSB_TRACE_BUILD
           if (lane == 0) TSB_TRACE_HOT(4, blk);
 #endif
@@ -1018,20 +1023,23 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
 #ifdef TSB_TRACE_BUILD
           if (lane == 0) TSB_TRACE_HOT(5, blk);
 #endif
-          const int c_lo = g * p.cpb, c_hi = min(c_lo + p.cpb, chunks);
+          const int c_hi = min(c_lo + p.cpb, chunks);
           if (elect_one()) {
-            const uint32_t st_units = base_units + stage * stage_units;
-            for (int c = c_lo; c < c_hi; ++c) {
-              const uint32_t a_lo = ((st_units + (uint32_t)(c - c_lo) * a_units) & 0x3FFFu) | lo_flag;
-              const uint32_t b_lo = ((st_units + b_first + (uint32_t)(c - c_lo) * b_units) & 0x3FFFu) | lo_flag;
-              int col_src, col_w, steps;
-              chunk_geometry(c, col_src, col_w, steps);
+            uint32_t a_c = a_lo, b_c = a_lo + b_first;          // shared memory stays below 2^18 bytes: no carry
+            for (int c = c_lo; c < c_hi; ++c, a_c += a_units, b_c += b_units) {
+              int steps;
+              if constexpr (kTma) {
+                int col_src, col_w;
+                chunk_geometry(c, col_src, col_w, steps);
+              } else {
+                steps = (c == chunks - 1) ? last_steps : 4;
+              }
               // +32 bytes along K inside the swizzle atom = +2 in the descriptor's 16-byte address units
 #pragma unroll
               for (int st = 0; st < 4; ++st) {
                 if (st < steps) {
-                  const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_lo + 2u * st);
-                  const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (b_lo + 2u * st);
+                  const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (a_c + 2u * st);
+                  const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (b_c + 2u * st);
                   umma<kTF32>(acc, a_desc, b_desc, idesc, accumulate);
                   accumulate = 1;
                 }
@@ -1045,7 +1053,8 @@ igemm_umma_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap w_map,
           if (lane == 0) TSB_TRACE_HOT(6, blk);
           ++blk;
 #endif
-          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; }
+          a_lo += stage_units;
+          if (++stage == (uint32_t)p.stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; }
         }
       }
       // also on the error path: ends the epilogue's bounded wait early
