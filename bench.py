@@ -436,8 +436,16 @@ def run_ours(args, rank: int, world: int, device: torch.device):
             roof = {"bound": "hbm", "achieved": round(gb, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                     "frac": round(gb / pk["hbm_gbs"], 4)}
         dom_key, dom = max(by_shape.items(), key=lambda kv: kv[1]["ms"])
+        # DRAM bytes per launch of the dominant layer shape, from an ncu capture of that layer (small case, one launch:
+        # 21.7 MB at 30 912 rows 256 -> 256 k3, 23.9 MB at 110 387 rows 96 -> 96 k3), scaled by rows
+        captured = {(27, 256, 256): (21.7e6, 30912), (27, 96, 96): (23.9e6, 110387)}
+        cap = captured.get(dom_key[:3])
+        traffic = int(cap[0] * dom_key[3] / cap[1]) if cap else None
         roof.update({
-            "traffic": None,
+            "traffic": traffic,
+            "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant layer shape "
+                               "(ncu capture of `bench.py --layer ... --lidar-level L --smap`), scaled by rows; per launch"
+                               if cap else None),
             "kernel": "igemm_umma_kernel (implicit-GEMM conv forward), all launches of a step",
             "scope": summary(agg),
             "note": "achieved / frac: useful FLOPs (2 * valid pairs * Cin * Cout) or algorithmic bytes (features, "
