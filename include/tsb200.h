@@ -414,8 +414,9 @@ int tsb_conv_pack_weight(const void* weight, int32_t kvol, int32_t cin, int32_t 
  * (torchsparse/backend/convolution/convolution_backward_wgrad_implicit_gemm_cuda.cu:1614-1700; its split_k_iters
  * argument has no counterpart: the row range is divided among CTAs by the library, and the shares meet in
  * grad_weight through fp32 atomic adds, so the last bits of a sum depend on the order in which CTAs finish).
- * tile_mask (nullable) = tsb_map_tile_mask of the map.  c_gathered % 8 == 0, c_rows % 16 == 0, kvol <= 32;
- * other shapes and fp32 tensors return TSB_ERR_UNSUPPORTED (the caller falls back to pair-list GEMMs). */
+ * tile_mask (nullable) = tsb_map_tile_mask of the map.  Tensor cores: fp16 / bf16, c_gathered % 8 == 0,
+ * c_rows % 16 == 0, kvol <= 32; other shapes and fp32 tensors run a CUDA-core kernel (fp32 FMA, exact products) on
+ * row-major maps. */
 size_t tsb_conv_wgrad_igemm_workspace_bytes(int64_t n_rows);
 int tsb_conv_wgrad_igemm(const void* gathered_feats, const void* row_feats, const int32_t* out_in_map,
                          const uint32_t* tile_mask, float* grad_weight, int64_t n_gathered, int64_t n_rows,

@@ -28,7 +28,7 @@ __all__ = [
     "build_mask_from_kmap", "convert_transposed_out_in_map", "derive_bitmask_from_out_in_map",
     "reduce_bitmask_cuda", "reorder_out_in_map_cuda", "sort_bitmask_cuda", "sorted_artefacts_cuda",
     "exclusive_scan_quantified_wrapper",
-    "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda", "conv_backward_wgrad_pairs_cuda",
+    "conv_forward_implicit_gemm_cuda", "conv_forward_implicit_gemm_sorted_cuda",
     "conv_forward_gather_scatter_cuda", "conv_backward_gather_scatter_cuda", "conv_wgrad_implicit_gemm_cuda",
     "conv_backward_wgrad_implicit_gemm_cuda", "conv_backward_wgrad_implicit_gemm_sorted_cuda",
     "conv_forward_fetch_on_demand_cuda", "downsample_cuda",
@@ -852,59 +852,24 @@ def igemm_plan_launch(plan: IgemmLayerPlan, in_feats: torch.Tensor, out_in_map: 
     return out
 
 
-def conv_backward_wgrad_pairs_cuda(grad_out: torch.Tensor, in_feats: torch.Tensor, nbmaps: torch.Tensor,
-                                   nbsizes_host, transposed: bool = False) -> torch.Tensor:
-    """Weight gradient dW[k] = X[in_k]^T . dY[out_k] over the pair list of every kernel offset
-    (nbmaps int32 [P,2] = (input row, output row), segments of nbsizes_host[k] pairs; the columns swap
-    roles for a transposed convolution).  Returns [Kvol, Cin, Cout] in the dtype of in_feats.
-    The rows are gathered once and the per-offset products are plain GEMMs on torch's cuBLAS handle,
-    as in the reference's gather-scatter backward
-    (torchsparse/backend/convolution/convolution_gather_scatter_cuda.cu:640-800); the reference's
-    implicit-GEMM wgrad kernels (convolution_backward_wgrad_implicit_gemm_cuda.cu) compute the same sums."""
-    _need_cuda(grad_out, in_feats, nbmaps)
-    kvol = len(nbsizes_host)
-    cin, cout = in_feats.shape[1], grad_out.shape[1]
-    x_col, y_col = (1, 0) if transposed else (0, 1)
-    pairs = nbmaps.long()
-    xg = in_feats.index_select(0, pairs[:, x_col])
-    yg = grad_out.to(in_feats.dtype).index_select(0, pairs[:, y_col])
-    dw = torch.zeros((kvol, cin, cout), dtype=in_feats.dtype, device=in_feats.device)
-    start = 0
-    for k, size in enumerate(nbsizes_host):
-        if size:
-            torch.mm(xg[start:start + size].t(), yg[start:start + size], out=dw[k])
-        start += size
-    return dw
-
-
-def _wgrad_by_offsets(gathered: torch.Tensor, rows: torch.Tensor, out_in_map: torch.Tensor) -> torch.Tensor:
-    """fp32 [Kvol, Cg, Cd] of the sums below, one masked product per kernel offset (shapes the tensor-core kernel
-    does not take, and exact fp32)."""
-    n_rows, kvol = rows.shape[0], out_in_map.shape[1]
-    out = torch.zeros((kvol, gathered.shape[1], rows.shape[1]), dtype=torch.float32, device=rows.device)
-    for k in range(kvol):
-        idx = out_in_map[:n_rows, k].long()
-        valid = idx >= 0
-        if bool(valid.any()):
-            out[k] = gathered.index_select(0, idx[valid]).float().t() @ rows[valid].float()
-    return out
-
-
 def conv_wgrad_implicit_gemm_cuda(gathered: torch.Tensor, rows: torch.Tensor, out_in_map: torch.Tensor,
                                   tile_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[k][a][b] = sum over map rows m of gathered[out_in_map[m][k]][a] * rows[m][b], fp32 [Kvol, Cg, Cd]
     (tsb_conv_wgrad_igemm: tcgen05 with both operands read MN-major, fp32 accumulators in TMEM, the row range
-    divided among CTAs).  With the forward map, gathered = input features and rows = output gradients give dW."""
+    divided among CTAs; fp32 tensors and channel counts that are not multiples of 8 / 16 run the CUDA-core kernel
+    behind the same entry).  With the forward map, gathered = input features and rows = output gradients give dW."""
     _need_cuda(gathered, rows, out_in_map)
     n_rows, kvol = rows.shape[0], out_in_map.shape[1]
     cg, cd = gathered.shape[1], rows.shape[1]
     if out_in_map.shape[0] < n_rows:
         raise ValueError("the map has fewer rows than the row matrix")
     dev = rows.device
-    tensor_cores = (gathered.dtype in (torch.float16, torch.bfloat16) and rows.dtype == gathered.dtype
-                    and cg % 8 == 0 and cd % 16 == 0 and kvol <= 32 and n_rows > 0 and gathered.shape[0] > 0)
-    if not tensor_cores:
-        return _wgrad_by_offsets(gathered, rows, out_in_map)
+    if rows.dtype != gathered.dtype:
+        rows = rows.to(gathered.dtype)
+    if gathered.dtype not in _DTYPES:
+        raise RuntimeError("unsupported dtype")
+    if n_rows == 0 or gathered.shape[0] == 0:
+        return torch.zeros((kvol, cg, cd), dtype=torch.float32, device=dev)
     gathered, rows, out_in_map = gathered.contiguous(), rows.contiguous(), out_in_map.contiguous()
     if tile_mask is None:
         tile_mask = _tile_mask_of(out_in_map, n_rows)
@@ -914,8 +879,6 @@ def conv_wgrad_implicit_gemm_cuda(gathered: torch.Tensor, rows: torch.Tensor, ou
     rc = lib.tsb_conv_wgrad_igemm(_p(gathered), _p(rows), _p(out_in_map), _p(tile_mask), _p(out), gathered.shape[0],
                                   n_rows, 0, 0, kvol, cg, cd, _dtype_code(gathered), _p(status), _p(ws), ws.numel(),
                                   _stream())
-    if rc == 2:      # TSB_ERR_UNSUPPORTED
-        return _wgrad_by_offsets(gathered, rows, out_in_map)
     check(rc, "conv_wgrad_implicit_gemm_cuda")
     if check_kernel_status and int(status.item()) != 0:
         raise RuntimeError(f"conv_wgrad_implicit_gemm_cuda: a bounded wait inside the kernel ran out "
@@ -955,7 +918,7 @@ def conv_backward_gather_scatter_cuda(in_feat: torch.Tensor, grad_in_feat: torch
     """Gradients of the gather-scatter convolution, written into ``grad_in_feat`` and ``grad_kernel``
     (torchsparse/backend/convolution/convolution_gather_scatter_cuda.cu:640-800): the input gradient is the
     same pair-list convolution run from the outputs back to the inputs with every W[k] transposed, the weight
-    gradient is X[in_k]^T . dY[out_k] per offset."""
+    gradient is X[in_k]^T . dY[out_k] per offset (the pair list turned into a map of the output rows)."""
     _need_cuda(in_feat, grad_in_feat, grad_out_feat, kernel, grad_kernel, neighbor_map)
     sizes = [int(v) for v in (neighbor_offset.tolist() if isinstance(neighbor_offset, torch.Tensor) else neighbor_offset)]
     nbmaps = neighbor_map.int().contiguous()
@@ -965,7 +928,16 @@ def conv_backward_gather_scatter_cuda(in_feat: torch.Tensor, grad_in_feat: torch
                                           sizes, masks[0], masks[1], in_feat.shape[0], transpose=not transpose,
                                           allow_tf32=False)
     grad_in_feat.copy_(gx)
-    grad_kernel.copy_(conv_backward_wgrad_pairs_cuda(grad_out_feat, in_feat, nbmaps, sizes, transpose))
+    # weight gradient: the pair list as a map of the output rows (entry (row, k) = the input row paired with it at
+    # offset k), then the kernel behind tsb_conv_wgrad_igemm
+    x_col, y_col = (1, 0) if transpose else (0, 1)
+    kvol = len(sizes)
+    offset_of_pair = torch.repeat_interleave(torch.arange(kvol, device=nbmaps.device),
+                                             torch.tensor(sizes, device=nbmaps.device))
+    rows_pad = (grad_out_feat.shape[0] + 127) // 128 * 128
+    as_map = torch.full((rows_pad, kvol), -1, dtype=torch.int32, device=nbmaps.device)
+    as_map[nbmaps[:, y_col].long(), offset_of_pair] = nbmaps[:, x_col]
+    grad_kernel.copy_(conv_wgrad_implicit_gemm_cuda(in_feat, grad_out_feat, as_map))
 
 
 def conv_forward_implicit_gemm_sorted_cuda(in_feats: torch.Tensor, kernel: torch.Tensor, out_in_map: torch.Tensor,

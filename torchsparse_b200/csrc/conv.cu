@@ -104,7 +104,7 @@ int tsb_conv_wgrad_igemm(const void* gathered_feats, const void* row_feats, cons
   if (!gathered_feats || !row_feats || !out_in_map) return TSB_ERR_BAD_ARG;
   WgradArgs a{gathered_feats, row_feats, out_in_map, map_row_stride, map_col_stride, tile_mask, grad_weight, n_gathered,
               n_rows, kvol, c_gathered, c_rows, dtype, dev_status, workspace, workspace_bytes};
-  if (!wgrad_umma_supported(a)) return TSB_ERR_UNSUPPORTED;
+  if (!wgrad_umma_supported(a)) return wgrad_simt(a, as_stream(stream));
   return wgrad_umma(a, as_stream(stream));
 }
 

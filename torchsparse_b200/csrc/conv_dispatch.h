@@ -110,6 +110,7 @@ struct WgradArgs {
 bool wgrad_umma_supported(const WgradArgs& a);
 size_t wgrad_umma_workspace_bytes(int64_t n_rows);
 int wgrad_umma(const WgradArgs& a, cudaStream_t s);
+int wgrad_simt(const WgradArgs& a, cudaStream_t s);   // CUDA cores: every dtype and channel count, row-major maps
 
 size_t packed_weight_bytes(int kvol, int cin, int cout, int dtype);
 int pack_weight(const void* w, int kvol, int cin, int cout, int dtype, void* packed, cudaStream_t s);

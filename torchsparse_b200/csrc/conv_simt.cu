@@ -122,6 +122,64 @@ igemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const int* _
   }
 }
 
+// ------------------------------------------------------------------ weight gradient on the CUDA cores
+// out[k][a][b] += sum over the block's share of the map rows m of g[map[m][k]][a] * p[m][b]  (fp32 accumulation).
+// Grid: (row shares, 32 x 32 tiles of (a, b), kernel offsets); a block walks its rows 32 at a time: the 32 gathered
+// rows of g and the 32 rows of p are staged in shared memory, every thread owns a 2 x 2 patch of the tile.  For the
+// shapes the tensor-core kernel does not take (fp32 tensors, channel counts that are not multiples of 8 / 16).
+constexpr int kWgTile = 32, kWgRows = 32;
+template <typename T>
+__global__ void __launch_bounds__(256)
+wgrad_simt_kernel(const T* __restrict__ g, const T* __restrict__ pm, const int* __restrict__ map, float* __restrict__ out,
+                  int64_t n_g, int64_t n_rows, int kvol, int cg, int cd, int64_t rows_per_block) {
+  __shared__ float s_g[kWgRows][kWgTile + 1];
+  __shared__ float s_p[kWgRows][kWgTile + 1];
+  __shared__ int s_src[kWgRows];
+  const int k = blockIdx.z;
+  const int tiles_b = (cd + kWgTile - 1) / kWgTile;
+  const int a0 = (blockIdx.y / tiles_b) * kWgTile, b0 = (blockIdx.y % tiles_b) * kWgTile;
+  const int64_t r_lo = (int64_t)blockIdx.x * rows_per_block;
+  const int64_t r_hi = min(r_lo + rows_per_block, n_rows);
+  const int ta = (threadIdx.x >> 4) * 2, tb = (threadIdx.x & 15) * 2;      // this thread's patch
+  float acc[2][2] = {};
+  for (int64_t r0 = r_lo; r0 < r_hi; r0 += kWgRows) {
+    int any = 0;
+    if (threadIdx.x < kWgRows) {
+      const int64_t r = r0 + threadIdx.x;
+      int v = -1;
+      if (r < r_hi) {
+        v = __ldg(&map[r * kvol + k]);
+        if (v >= n_g) v = -1;
+      }
+      s_src[threadIdx.x] = v;
+      any = v >= 0;
+    }
+    if (!__syncthreads_or(any)) continue;            // no pair of this offset among these rows
+    for (int e = threadIdx.x; e < kWgRows * kWgTile; e += 256) {
+      const int rr = e / kWgTile, cc = e % kWgTile;
+      const int src = s_src[rr];
+      const int64_t r = r0 + rr;
+      s_g[rr][cc] = (src >= 0 && a0 + cc < cg) ? to_f32(__ldg(&g[(int64_t)src * cg + a0 + cc])) : 0.f;
+      s_p[rr][cc] = (src >= 0 && r < r_hi && b0 + cc < cd) ? to_f32(__ldg(&pm[r * cd + b0 + cc])) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int rr = 0; rr < kWgRows; ++rr) {
+      const float g0 = s_g[rr][ta], g1 = s_g[rr][ta + 1], p0 = s_p[rr][tb], p1 = s_p[rr][tb + 1];
+      acc[0][0] = fmaf(g0, p0, acc[0][0]); acc[0][1] = fmaf(g0, p1, acc[0][1]);
+      acc[1][0] = fmaf(g1, p0, acc[1][0]); acc[1][1] = fmaf(g1, p1, acc[1][1]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int a = a0 + ta + i, b = b0 + tb + j;
+      if (a < cg && b < cd && acc[i][j] != 0.f) atomicAdd(&out[((int64_t)k * cg + a) * cd + b], acc[i][j]);
+    }
+}
+
 // ------------------------------------------------------------------ gather-scatter
 // in_buffer[p] = X[src(p)], 16-byte chunks when rows allow it (vec = elements per chunk)
 template <typename T, int VEC>
@@ -290,6 +348,35 @@ int igemm_simt(const IgemmArgs& a, cudaStream_t s) {
     case TSB_F32: return igemm_simt_launch<float>(a, s);
     case TSB_F16: return igemm_simt_launch<__half>(a, s);
     case TSB_BF16: return igemm_simt_launch<__nv_bfloat16>(a, s);
+  }
+  return TSB_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+static int wgrad_simt_launch(const WgradArgs& a, cudaStream_t s) {
+  TSB_CUDA_TRY(cudaMemsetAsync(a.out, 0, (size_t)a.kvol * a.cg * a.cd * sizeof(float), s));
+  const int tiles = (int)(cdiv(a.cg, kWgTile) * cdiv(a.cd, kWgTile));
+  // shares of the row range: about four blocks per SM over all (tile, offset) pairs, at least 256 rows each
+  int64_t shares = cdiv((int64_t)4 * kSmCount, (int64_t)tiles * a.kvol);
+  const int64_t max_shares = cdiv(a.n_rows, 256);
+  if (shares > max_shares) shares = max_shares;
+  if (shares < 1) shares = 1;
+  const int64_t rows_per_block = cdiv(cdiv(a.n_rows, shares), kWgRows) * kWgRows;
+  dim3 grid((unsigned)cdiv(a.n_rows, rows_per_block), (unsigned)tiles, (unsigned)a.kvol);
+  wgrad_simt_kernel<T><<<grid, 256, 0, s>>>((const T*)a.g, (const T*)a.p, a.map, a.out, a.n_g, a.n_rows, a.kvol, a.cg, a.cd,
+                                            rows_per_block);
+  TSB_LAUNCH_CHECK();
+  return TSB_OK;
+}
+
+int wgrad_simt(const WgradArgs& a, cudaStream_t s) {
+  if (a.map_rs != 0 || a.map_cs != 0) {
+    if (a.map_rs != a.kvol || a.map_cs != 1) return TSB_ERR_UNSUPPORTED;      // row-major maps only
+  }
+  switch (a.dtype) {
+    case TSB_F32: return wgrad_simt_launch<float>(a, s);
+    case TSB_F16: return wgrad_simt_launch<__half>(a, s);
+    case TSB_BF16: return wgrad_simt_launch<__nv_bfloat16>(a, s);
   }
   return TSB_ERR_UNSUPPORTED;
 }
