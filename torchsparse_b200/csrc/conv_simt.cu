@@ -356,10 +356,10 @@ template <typename T>
 static int wgrad_simt_launch(const WgradArgs& a, cudaStream_t s) {
   TSB_CUDA_TRY(cudaMemsetAsync(a.out, 0, (size_t)a.kvol * a.cg * a.cd * sizeof(float), s));
   const int tiles = (int)(cdiv(a.cg, kWgTile) * cdiv(a.cd, kWgTile));
-  // shares of the row range: about four blocks per SM over all (tile, offset) pairs, at least 256 rows each
-  int64_t shares = cdiv((int64_t)4 * kSmCount, (int64_t)tiles * a.kvol);
-  const int64_t max_shares = cdiv(a.n_rows, 256);
-  if (shares > max_shares) shares = max_shares;
+  // shares of the row range: a block walks its rows 32 at a time with three dependent memory round trips per step,
+  // so the row range is cut into many short shares (about 1024 rows) rather than a few long ones
+  int64_t shares = cdiv(a.n_rows, 1024);
+  if (shares > 8192) shares = 8192;
   if (shares < 1) shares = 1;
   const int64_t rows_per_block = cdiv(cdiv(a.n_rows, shares), kWgRows) * kWgRows;
   dim3 grid((unsigned)cdiv(a.n_rows, rows_per_block), (unsigned)tiles, (unsigned)a.kvol);
