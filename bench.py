@@ -113,7 +113,8 @@ def init_model(model):
     return model.eval()
 
 
-def make_model(device=None, half=True, engine=True, sorted_maps=True, kind="seg"):
+def make_model(device=None, half=True, engine=True, sorted_maps=True, kind="seg", sorted_max_stride=8,
+               sorted_strided=False):
     torch.manual_seed(0)
     model = init_model(SegNet() if kind == "seg" else DetNet())
     if device is not None:
@@ -122,7 +123,8 @@ def make_model(device=None, half=True, engine=True, sorted_maps=True, kind="seg"
             model = model.half()
         if engine:
             from torchsparse_b200.nn import InferenceEngine
-            model.backbone = InferenceEngine(model.backbone, sorted_maps=sorted_maps)
+            model.backbone = InferenceEngine(model.backbone, sorted_maps=sorted_maps, sorted_max_stride=sorted_max_stride,
+                                             sorted_strided=sorted_strided)
     return model
 
 
@@ -282,7 +284,8 @@ def run_ours(args, rank: int, world: int, device: torch.device):
     from torchsparse_b200 import backend
     from torchsparse_b200.sharding import PaddedGather
 
-    model = make_model(device, sorted_maps=not args.unsorted)
+    model = make_model(device, sorted_maps=not args.unsorted, sorted_max_stride=args.sorted_max_stride,
+                       sorted_strided=args.sorted_strided)
     scans = [scan_points(1000 * rank + i) for i in range(SCAN_POOL)]
     host = [torch.from_numpy(s).pin_memory() for s in scans]
     resident = [h.to(device) for h in host]
@@ -485,7 +488,7 @@ def run_ours(args, rank: int, world: int, device: torch.device):
                    "voxels_per_scan": int(forward_voxels(scans[0])), "scans_per_step": world,
                    "l2": f"{L2_FLUSH_BYTES >> 20} MiB buffer written before every step (inside the timed region); "
                          f"{SCAN_POOL} scans rotated",
-                   "engine": "one CUDA graph per scan (sizes in device memory), row-sorted column-major kernel maps"
+                   "engine": "one CUDA graph per scan (sizes in device memory), row-sorted column-major copies of every kernel map"
                              if not args.unsorted else "one CUDA graph per scan, kernel maps as built",
                    "streams": n_eng,
                    "conv_grid": (f"{args.conv_grid} persistent CTAs per convolution launch (of {2 * 148} resident slots): "
@@ -1037,6 +1040,9 @@ def main():
     ap.add_argument("--conv-grid", type=int, default=-1,
                     help="upper bound of the persistent CTAs of a convolution launch (0: every resident slot; "
                          "-1: 56 when several engines share the GPU, else every slot)")
+    ap.add_argument("--sorted-max-stride", type=int, default=16, help="row-sorted map copies up to this tensor stride")
+    ap.add_argument("--no-sorted-strided", dest="sorted_strided", action="store_false",
+                    help="no row-sorted copies of the strided / transposed maps (only of the submanifold ones)")
     ap.add_argument("--tune", default="", help="launch-configuration overrides of the conv kernel, e.g. stages=3,ctas=2,cpb=2")
     args = ap.parse_args()
     if args.tune:

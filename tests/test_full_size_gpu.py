@@ -42,14 +42,19 @@ def config2():
 
 
 def _gpu_model(model, sorted_maps=True):
+    """sorted_maps: False, True (submanifold maps up to stride 8) or "all" (every map of every level: the
+    benchmark's setting)."""
     from torchsparse_b200.nn import InferenceEngine
 
     m = copy.deepcopy(model).cuda().half()
-    m.backbone = InferenceEngine(m.backbone, sorted_maps=sorted_maps)
+    if sorted_maps == "all":
+        m.backbone = InferenceEngine(m.backbone, sorted_maps=True, sorted_max_stride=16, sorted_strided=True)
+    else:
+        m.backbone = InferenceEngine(m.backbone, sorted_maps=sorted_maps)
     return m
 
 
-@pytest.mark.parametrize("sorted_maps", [True, False])
+@pytest.mark.parametrize("sorted_maps", [True, False, "all"])
 def test_config2_full_scan_eager_engine(config2, sorted_maps):
     """The benchmark's public-API path (bench.forward_scan without the head) at full size."""
     import torchsparse_b200 as ts
@@ -75,7 +80,7 @@ def test_config2_full_scan_eager_engine(config2, sorted_maps):
 def test_config2_full_scan_graph_engine(config2):
     """What bench.py times: the CUDA-graph engine with the benchmark's bounds, on the benchmark's scan."""
     b = _bench()
-    m = _gpu_model(config2["model"])
+    m = _gpu_model(config2["model"], "all")
     eng = b.make_engines(m, torch.device("cuda", 0), 1)[0]
     out, rec = eng(torch.from_numpy(config2["pts"]).cuda())
     eng.stream.synchronize()

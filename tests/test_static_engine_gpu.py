@@ -48,7 +48,7 @@ def _eager(engine, head, pts):
         return coords, outs[-1].feats
 
 
-@pytest.mark.parametrize("sorted_maps", [True, False])
+@pytest.mark.parametrize("sorted_maps", [True, False, "all"])
 def test_static_engine_equals_eager_engine(sorted_maps):
     from torchsparse_b200.nn import InferenceEngine, StaticEngine
 
@@ -57,7 +57,11 @@ def test_static_engine_equals_eager_engine(sorted_maps):
     conv0 = net.stem[0]
     conv0.kernel = torch.nn.Parameter(torch.nn.functional.pad(conv0.kernel.data, (0, 0, 0, 4)), requires_grad=False)
     conv0.in_channels = 8
-    engine = InferenceEngine(net, sorted_maps=sorted_maps)
+    if sorted_maps == "all":       # row-sorted copies of every map: strided, transposed and the coarsest level too
+        engine = InferenceEngine(net, sorted_maps=True, sorted_max_stride=16, sorted_strided=True)
+        sorted_maps = True
+    else:
+        engine = InferenceEngine(net, sorted_maps=sorted_maps)
     scans = [_scan(s, n) for s, n in ((0, 20000), (1, 12000), (2, 20000))]
     max_points = max(p.shape[0] for p in scans)
     ext = [int(max(float(p[:, d].max()) for p in scans) / VOXEL) + 8 for d in range(3)]

@@ -63,10 +63,12 @@ class FusedConv(nn.Module):
     # than the offset blocks it saves.
     sorted_maps = False
     sorted_max_stride = 8
+    sorted_strided = False      # also the strided and transposed maps (one sorted copy per map and direction)
 
     def _wants_sorted(self, stride) -> bool:
-        return (self.sorted_maps and not self.transposed and all(s == 1 for s in self.stride)
-                and max(stride) <= self.sorted_max_stride)
+        if not self.sorted_maps or max(stride) > self.sorted_max_stride:
+            return False
+        return self.sorted_strided or (not self.transposed and all(s == 1 for s in self.stride))
 
     def __init__(self, conv: Conv3d, bn: Optional[nn.BatchNorm1d] = None, relu: bool = False) -> None:
         super().__init__()
@@ -268,7 +270,8 @@ class InferenceEngine(nn.Module):
     """Eval-mode wrapper: fused modules, no autograd, strided kernel maps built ahead of the convs,
     skip concatenations read in place by the layer that follows them."""
 
-    def __init__(self, model: nn.Module, sorted_maps: bool = True, sorted_max_stride: int = 8) -> None:
+    def __init__(self, model: nn.Module, sorted_maps: bool = True, sorted_max_stride: int = 8,
+                 sorted_strided: bool = False) -> None:
         """`sorted_maps`: the kernel map of the submanifold layers of a resolution level (tensor stride up to
         `sorted_max_stride`) gets a row-sorted, column-major copy with per-tile offset masks the first time a
         layer uses it (tsb_map_sorted_cm), and all layers sharing the map run on that copy: the 128 rows of a
@@ -281,6 +284,7 @@ class InferenceEngine(nn.Module):
             if isinstance(m, FusedConv):
                 m.sorted_maps = bool(sorted_maps)
                 m.sorted_max_stride = int(sorted_max_stride)
+                m.sorted_strided = bool(sorted_strided)
         self._plan = None   # strided conv keys in execution order, learnt on the first call
 
     def _prebuild(self, x: SparseTensor) -> None:
