@@ -1334,10 +1334,10 @@ int tsb_map_sorted_cm(const int32_t* out_in_map, int64_t rows, int32_t kvol, int
   TSB_LAUNCH_CHECK();
   size_t cb = w.cub_bytes;
   // Stable: rows with the same neighbour pattern keep their original order (neighbouring rows share inputs).
-  // Only the top 24 bits of the mask are sorted (three 8-bit passes instead of four): on LiDAR scans the
-  // lowest offsets of a 3x3x3 kernel are the rarest, and leaving them out of the order costs about a tenth
-  // more (tile, offset) blocks at the finest levels and nothing at the coarse ones.
-  const int begin_bit = kvol > 24 ? kvol - 24 : 0;
+  // Every bit of the mask is sorted (four 8-bit passes for a 3x3x3 kernel).  Leaving the lowest three offsets
+  // out of the order saves a pass but costs about a tenth more (tile, offset) blocks at the finest levels of a
+  // LiDAR scan; with several scans in flight the extra pass is hidden and the blocks are not.
+  const int begin_bit = 0;
   TSB_CUDA_TRY(cub::DeviceRadixSort::SortPairsDescending(base + w.cub_off, cb, keys, keys2, iota, reorder_loc, rows,
                                                          begin_bit, kvol, s));
   count_launch();
