@@ -1043,8 +1043,13 @@ def main():
     ap.add_argument("--sorted-max-stride", type=int, default=16, help="row-sorted map copies up to this tensor stride")
     ap.add_argument("--no-sorted-strided", dest="sorted_strided", action="store_false",
                     help="no row-sorted copies of the strided / transposed maps (only of the submanifold ones)")
+    ap.add_argument("--hash64", action="store_true",
+                    help="kernel-map tables with 64-bit keys even where the level's key space fits 32 bits")
     ap.add_argument("--tune", default="", help="launch-configuration overrides of the conv kernel, e.g. stages=3,ctas=2,cpb=2")
     args = ap.parse_args()
+    if args.hash64:
+        from torchsparse_b200 import backends as _backends
+        _backends.hash_keys_32bit = False
     if args.tune:
         from torchsparse_b200 import backend as _backend
         for kv in args.tune.split(","):

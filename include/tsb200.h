@@ -69,7 +69,17 @@ int tsb_kernel_hash(const int32_t* coords, int64_t n, const int32_t* offsets, in
  * TSB_DEV_TABLE_FULL in *dev_status (int32, device, may be NULL) instead of
  * spinning.  Replaces class GPUHashTable
  * (torchsparse/backend/hashmap/hashmap_cuda.cuh:65-118) and its kernels
- * (hashmap_cuda.cuh:124-196, 316-347). */
+ * (hashmap_cuda.cuh:124-196, 316-347).
+ *
+ * 32-bit keys: table_vals == NULL selects the packed layout, in which table_keys holds `capacity`
+ * 8-byte slots, value << 32 | key (0 = empty), for keys below 2^32.  Insert is one compare-and-swap
+ * of the slot and a probe one 8-byte load.  tsb_hash_insert / tsb_hash_lookup, tsb_kmap_subm,
+ * tsb_kmap_down_finish and the *_dyn builders take either layout and give the same maps; a key that
+ * does not fit returns TSB_ERR_LIMIT where the host knows the key space (bounds, key_bits) and sets
+ * TSB_DEV_LIMIT in *dev_status where only the device does.  Replaces the hashtable32 instantiation
+ * behind build_kernel_map_subm_hashmap_int32 / build_kernel_map_downsample_hashmap_int32
+ * (torchsparse/backend/others/sparsemapping_cuda.cu:259-300, 347-426;
+ * torchsparse/backend/hashmap/hashmap_cuda.cuh). */
 int tsb_hash_insert(int64_t* table_keys, int32_t* table_vals, int64_t capacity,
                     const int64_t* keys, int64_t n, int32_t* dev_status, tsb_stream_t stream);
 int tsb_hash_lookup(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity,

@@ -161,6 +161,67 @@ def test_hash_table_api_and_full_table_error():
         small.insert_vals(keys[:200])
 
 
+def test_32bit_key_table_api_and_limits():
+    """The packed layout (reference: hashtable32, sparsemapping_cuda.cu:259-300, 347-426): same stored values as the
+    64-bit layout, full-table and key-range errors reported instead of wrong answers."""
+    from torchsparse_b200 import backend
+
+    rng = np.random.default_rng(23)
+    keys = torch.from_numpy(rng.choice(2**32 - 2, 5000, replace=False).astype(np.int64) + 1).cuda()
+    table = backend.GPUHashTable32(torch.zeros(10007, dtype=torch.int64, device="cuda"))
+    table.insert_vals(keys)
+    got = table.lookup_vals(keys)
+    assert bool((got[:5000] == torch.arange(1, 5001, device="cuda")).all()) and bool((got[5000:] == 0).all())
+    absent = torch.from_numpy(np.setdiff1d(np.arange(1, 20000), keys.cpu().numpy())[:100].astype(np.int64)).cuda()
+    assert bool((table.lookup_vals(absent) == 0).all())
+    assert bool((table.lookup_vals(keys[:100] + 2**32) == 0).all())      # beyond the key range: never found
+    with pytest.raises(ValueError):
+        backend.GPUHashTable32(64).insert_vals(keys[:200])                # full
+    with pytest.raises(ValueError):
+        backend.GPUHashTable32(1024).insert_vals(keys[:10] + 2**32)       # key does not fit a packed slot
+    # a box of 2^32 cells or more is refused by the builders before anything is launched
+    coords = torch.from_numpy(random_coords(rng, 50, (8, 8, 8))).cuda()
+    with pytest.raises(Exception):
+        backend.build_kernel_map_subm_hashmap_int32(backend.GPUHashTable32(256), coords, (0, 0, 0, 0),
+                                                    (0, 70000, 70000, 8), (3, 3, 3))
+    with pytest.raises(ValueError):
+        backend.build_kernel_map_subm_hashmap_int32(backend.GPUHashTable(256), coords, (0, 0, 0, 0), (0, 7, 7, 7), (3, 3, 3))
+
+
+@pytest.mark.parametrize("ks,st", [(3, 1), (2, 2), (3, 2), ((1, 3, 1), (1, 2, 1)), (2, 1), (5, 1)])
+def test_32bit_and_64bit_key_tables_build_the_same_maps(ks, st):
+    from torchsparse_b200 import backend, backends
+
+    rng = np.random.default_rng(29)
+    coords_np = random_coords(rng, 3000, (40, 33, 17), 2)
+    pad = _pad(ks, st)
+    want = ko.build_kmap(coords_np, ks, st, pad)
+    seen = {}
+    for flag in (True, False):
+        backends.hash_keys_32bit = flag
+        try:
+            got = _build(coords_np, ks, st, pad)
+        finally:
+            backends.hash_keys_32bit = True
+        assert (got["hashmap_vals"] is None) == flag
+        assert np.array_equal(got["coords"].cpu().numpy(), want["coords"])
+        assert np.array_equal(got["out_in_map"].cpu().numpy(), want["out_in_map"])
+        seen[flag] = got
+    # the reference-named entry points over an explicit table
+    ks3, st3 = ko._as3(ks), ko._as3(st)
+    coords = torch.from_numpy(coords_np).cuda()
+    cmax = tuple(int(v) for v in coords_np.max(0))
+    if all(s == 1 for s in st3):
+        m = backend.build_kernel_map_subm_hashmap_int32(backend.GPUHashTable32(8192), coords, (0, 0, 0, 0), cmax, ks3)[0]
+        assert np.array_equal(m.cpu().numpy(), want["out_in_map"])
+    else:
+        cmax_out = (cmax[0],) + tuple((cmax[1 + i] + 2 * pad[i] - (ks3[i] - 1)) // st3[i] for i in range(3))
+        m, oc = backend.build_kernel_map_downsample_hashmap_int32(backend.GPUHashTable32(8192), coords, (0, 0, 0, 0),
+                                                                  cmax_out, ks3, st3, pad)
+        assert np.array_equal(oc.cpu().numpy(), want["coords"])
+        assert np.array_equal(m.cpu().numpy(), want["out_in_map"])
+
+
 def test_duplicate_free_determinism():
     rng = np.random.default_rng(19)
     coords = random_coords(rng, 4000, (30, 30, 30), 2)

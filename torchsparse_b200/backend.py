@@ -133,6 +133,9 @@ def _check_dev_status(status: torch.Tensor, what: str) -> None:
             "(torchsparse_b200.backends.hash_rsv_ratio)")
     if v & _lib.TSB_DEV_BAD_INDEX:
         raise RuntimeError(f"{what}: inconsistent hash table (an output coordinate was not found)")
+    if v & _lib.TSB_DEV_LIMIT:
+        raise ValueError(f"{what}: a key does not fit the table's 32-bit keys, or a device-side size went beyond "
+                         "the bound stated by the caller")
 
 
 def pad128(n: int) -> int:
@@ -201,6 +204,57 @@ class GPUHashTable:
         check(lib.tsb_hash_lookup_coords(_p(self.keys), _p(self.vals), self.capacity, _p(coords), n, _lib.i32x(ks),
                                          _lib.i32x(st), _p(out), _stream()), "GPUHashTable.lookup_coords")
         return out
+
+
+class GPUHashTable32(GPUHashTable):
+    """The table with 32-bit keys (class hashtable32 of torchsparse/backend/hashmap/hashmap_cuda.cuh, the table type of
+    build_kernel_map_subm_hashmap_int32 / build_kernel_map_downsample_hashmap_int32,
+    torchsparse/backend/others/sparsemapping_cuda.cu:259-300, 347-426): one 8-byte slot per entry, value << 32 | key,
+    so an insert is one compare-and-swap and a probe one load.  Every builder that takes a ``GPUHashTable`` takes
+    this one too and returns the same maps; key spaces of 2^32 or more raise."""
+
+    def __init__(self, slots_or_capacity, device=None):
+        if isinstance(slots_or_capacity, int):
+            dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+            self.keys = torch.zeros(slots_or_capacity, dtype=torch.int64, device=dev)
+        else:
+            self.keys = slots_or_capacity
+            _need_cuda(self.keys)
+            if self.keys.dtype != torch.int64 or not self.keys.is_contiguous():
+                raise ValueError("GPUHashTable32 expects a contiguous int64 tensor of packed slots")
+        self.vals = None
+        self.capacity = self.keys.numel()
+        self.divisor = 128
+
+    def insert_coords(self, coords: torch.Tensor) -> None:
+        raise NotImplementedError("coordinate hashes are 64-bit: the hashmap kernel-map mode needs a GPUHashTable")
+
+    def lookup_coords(self, coords, kernel_sizes, strides, kernel_volume):
+        raise NotImplementedError("coordinate hashes are 64-bit: the hashmap kernel-map mode needs a GPUHashTable")
+
+
+def fits_32bit_keys(coords_min, coords_max) -> bool:
+    """True when every ravel key (index + 1) of the box [coords_min, coords_max] fits a 32-bit-key table."""
+    total = 1
+    for lo, hi in zip(coords_min, coords_max):
+        total *= max(int(hi) - int(lo) + 1, 1)
+    return total < 0xFFFFFFFF
+
+
+def new_table(capacity: int, device, coords_min=None, coords_max=None):
+    """Zeroed ``(keys, vals)`` of a table for ravel keys over the given box: packed 32-bit-key slots (``vals`` is None)
+    when ``backends.hash_keys_32bit`` is set and the box allows it, else int64 keys + int32 values."""
+    from . import backends
+
+    keys = torch.zeros(capacity, dtype=torch.int64, device=device)
+    if backends.hash_keys_32bit and coords_min is not None and fits_32bit_keys(coords_min, coords_max):
+        return keys, None
+    return keys, torch.zeros(capacity, dtype=torch.int32, device=device)
+
+
+def table_of(keys: torch.Tensor, vals: Optional[torch.Tensor]):
+    """The table object over ``(keys, vals)`` as ``new_table`` returns them."""
+    return GPUHashTable32(keys) if vals is None else GPUHashTable(keys, vals)
 
 
 # --------------------------------------------------------------------------- kernel maps
@@ -298,6 +352,28 @@ def build_kernel_map_downsample_hashmap(table: GPUHashTable, coords: torch.Tenso
     out_in_map, out_coords = downsample_finish(table, coords, uniq, m, coords_min, coords_max, kernel_sizes, stride,
                                                padding)
     return [out_in_map, out_coords]
+
+
+def build_kernel_map_subm_hashmap_int32(table: GPUHashTable32, coords: torch.Tensor, coords_min, coords_max,
+                                        kernel_sizes, stride=None, padding=None,
+                                        to_insert: bool = True) -> List[torch.Tensor]:
+    """``build_kernel_map_subm_hashmap`` over a table of 32-bit keys
+    (torchsparse/backend/others/sparsemapping_cuda.cu:259-300): same map, half the bytes per probe."""
+    if table.vals is not None:
+        raise ValueError("build_kernel_map_subm_hashmap_int32 expects a GPUHashTable32")
+    return build_kernel_map_subm_hashmap(table, coords, coords_min, coords_max, kernel_sizes, stride, padding,
+                                         to_insert)
+
+
+def build_kernel_map_downsample_hashmap_int32(table: GPUHashTable32, coords: torch.Tensor, coords_min, coords_max,
+                                              kernel_sizes, stride, padding,
+                                              to_insert: bool = True) -> List[torch.Tensor]:
+    """``build_kernel_map_downsample_hashmap`` over a table of 32-bit keys
+    (torchsparse/backend/others/sparsemapping_cuda.cu:347-426)."""
+    if table.vals is not None:
+        raise ValueError("build_kernel_map_downsample_hashmap_int32 expects a GPUHashTable32")
+    return build_kernel_map_downsample_hashmap(table, coords, coords_min, coords_max, kernel_sizes, stride, padding,
+                                               to_insert)
 
 
 def convert_transposed_out_in_map(out_in_map: torch.Tensor, out_in_map_t: torch.Tensor, fill: bool = False) -> None:

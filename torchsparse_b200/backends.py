@@ -13,6 +13,11 @@ hash_rsv_ratio = 2  # table slots reserved per input point (>= 2)
 # (x_hi w_hi + x_hi w_lo + x_lo w_hi, fp32 accumulation) instead of the CUDA-core kernel; no counterpart in the
 # reference, whose fp32 path runs on the CUDA cores
 fp32_by_split_tf32 = True
+# Kernel-map builds keyed by the ravel index of a coordinate use a table of 32-bit keys (one 8-byte slot per entry)
+# whenever the key space of the level stays below 2^32, and the 64-bit layout otherwise; False always takes the
+# 64-bit layout.  The maps are the same either way (the reference's *_hashmap_int32 builders make the same choice
+# by name).
+hash_keys_32bit = True
 
 
 def init():

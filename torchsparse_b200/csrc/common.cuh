@@ -78,7 +78,10 @@ __host__ __device__ inline bool in_bounds_xyz(const Bounds& b, int x, int y, int
 }
 
 // ---------------------------------------------------------------------------
-// Open-addressing table over caller-owned arrays (keys int64, 0 = empty; vals int32).
+// Open-addressing table over caller-owned arrays, in one of two layouts:
+//   64-bit keys   keys int64[cap] (0 = empty) + vals int32[cap]; a probe reads the key word and, on a hit, the value
+//   32-bit keys   vals == nullptr: keys[] holds cap packed slots, value << 32 | key (0 = empty), for key spaces below
+//                 2^32; insert is one compare-and-swap of the whole slot, a probe one 8-byte load
 struct TableView {
   unsigned long long* keys;
   int* vals;
@@ -94,6 +97,9 @@ inline TableView make_table(int64_t* keys, int32_t* vals, int64_t cap) {
   t.mask = ((cap & (cap - 1)) == 0) ? (unsigned long long)(cap - 1) : 0ull;
   return t;
 }
+
+// largest key a table of packed slots can hold
+constexpr unsigned long long kPackedKeyMax = 0xffffffffull;
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long k) {
   k ^= k >> 33;
@@ -114,23 +120,48 @@ __device__ __forceinline__ unsigned long long table_next(const TableView& t, uns
   return slot == t.cap ? 0ull : slot;
 }
 
-// Returns false when every slot was probed without finding room.
-__device__ __forceinline__ bool table_insert(const TableView& t, unsigned long long key, int val) {
+// 0 = stored; TSB_DEV_TABLE_FULL when every slot was probed without finding room; TSB_DEV_LIMIT when the key does
+// not fit a packed slot.  key > 0.
+__device__ __forceinline__ int table_insert(const TableView& t, unsigned long long key, int val) {
   unsigned long long slot = table_slot(t, key);
+  if (!t.vals) {
+    if (key > kPackedKeyMax) return TSB_DEV_LIMIT;
+    const unsigned long long word = ((unsigned long long)(unsigned)val << 32) | key;
+    for (unsigned long long probe = 0; probe < t.cap; ++probe) {
+      const unsigned long long prev = atomicCAS(&t.keys[slot], 0ull, word);
+      if (prev == 0ull) return 0;
+      if ((prev & kPackedKeyMax) == key) {     // the key is there already: the later value stays, as in the other layout
+        t.keys[slot] = word;
+        return 0;
+      }
+      slot = table_next(t, slot);
+    }
+    return TSB_DEV_TABLE_FULL;
+  }
   for (unsigned long long probe = 0; probe < t.cap; ++probe) {
     unsigned long long prev = atomicCAS(&t.keys[slot], 0ull, key);
     if (prev == 0ull || prev == key) {
       t.vals[slot] = val;
-      return true;
+      return 0;
     }
     slot = table_next(t, slot);
   }
-  return false;
+  return TSB_DEV_TABLE_FULL;
 }
 
 // 0 = not found.
 __device__ __forceinline__ int table_lookup(const TableView& t, unsigned long long key) {
   unsigned long long slot = table_slot(t, key);
+  if (!t.vals) {
+    if (key > kPackedKeyMax) return 0;
+    for (unsigned long long probe = 0; probe < t.cap; ++probe) {
+      const unsigned long long cur = __ldg(&t.keys[slot]);
+      if ((cur & kPackedKeyMax) == key) return (int)(cur >> 32);
+      if (cur == 0ull) return 0;
+      slot = table_next(t, slot);
+    }
+    return 0;
+  }
   for (unsigned long long probe = 0; probe < t.cap; ++probe) {
     unsigned long long cur = __ldg(&t.keys[slot]);
     if (cur == key) return __ldg(&t.vals[slot]);

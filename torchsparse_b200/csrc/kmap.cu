@@ -51,7 +51,7 @@ __global__ void kernel_hash_kernel(const int4* __restrict__ coords, int64_t n, c
 // ------------------------------------------------------------------ table
 __global__ void table_insert_kernel(TableView t, const int64_t* __restrict__ keys, int64_t n, int* status) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    if (!table_insert(t, (unsigned long long)keys[i], (int)(i + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+    { const int e = table_insert(t, (unsigned long long)keys[i], (int)(i + 1)); if (e && status) atomicOr(status, e); }
   }
 }
 
@@ -78,7 +78,7 @@ __global__ void subm_insert_fill_kernel(TableView t, const int4* __restrict__ co
   if (to_insert && row < n) {
     int4 c = __ldg(&coords[row]);
     int64_t key = ravel4(b, c.x, c.y, c.z, c.w);
-    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+    { const int e = table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)); if (e && status) atomicOr(status, e); }
   }
   int64_t lo = row0 * kvol;
   int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
@@ -249,7 +249,7 @@ __global__ void down_insert_fill_kernel(TableView t, const int64_t* __restrict__
     int4 c;
     unravel4(b, key, c.x, c.y, c.z, c.w);
     out_coords[row] = c;
-    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+    { const int e = table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)); if (e && status) atomicOr(status, e); }
   }
   int64_t lo = row0 * kvol;
   int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
@@ -365,7 +365,7 @@ __global__ void subm_insert_fill_dyn_kernel(TableView t, const int4* __restrict_
     const Bounds b = rec_bounds(rec);
     const int4 c = __ldg(&coords[row]);
     const int64_t key = ravel4(b, c.x, c.y, c.z, c.w);
-    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+    { const int e = table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)); if (e && status) atomicOr(status, e); }
   }
   const int64_t lo = row0 * kvol;
   const int64_t hi = min(row0 + kBlock, rows_pad) * (int64_t)kvol;
@@ -485,7 +485,7 @@ __global__ void down_insert_fill_dyn_kernel(TableView t, const int64_t* __restri
     unravel4(b, key, c.x, c.y, c.z, c.w);
     out_coords[row] = c;
     mx[0] = c.x; mx[1] = c.y; mx[2] = c.z; mx[3] = c.w;
-    if (!table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)) && status) atomicOr(status, TSB_DEV_TABLE_FULL);
+    { const int e = table_insert(t, (unsigned long long)(key + 1), (int)(row + 1)); if (e && status) atomicOr(status, e); }
   }
 #pragma unroll
   for (int d = 0; d < 4; ++d) {
@@ -890,7 +890,7 @@ int tsb_kernel_hash(const int32_t* coords, int64_t n, const int32_t* offsets, in
 
 int tsb_hash_insert(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int64_t* keys, int64_t n,
                     int32_t* dev_status, tsb_stream_t stream) {
-  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || (n && !keys)) return TSB_ERR_BAD_ARG;
+  if (!table_keys || capacity <= 0 || n < 0 || (n && !keys)) return TSB_ERR_BAD_ARG;
   if (n == 0) return TSB_OK;
   table_insert_kernel<<<grid_for(n, kBlock), kBlock, 0, as_stream(stream)>>>(make_table(table_keys, table_vals, capacity),
                                                                              keys, n, dev_status);
@@ -900,7 +900,7 @@ int tsb_hash_insert(int64_t* table_keys, int32_t* table_vals, int64_t capacity, 
 
 int tsb_hash_lookup(const int64_t* table_keys, const int32_t* table_vals, int64_t capacity, const int64_t* keys,
                     int64_t n, int32_t* out_vals, tsb_stream_t stream) {
-  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || (n && (!keys || !out_vals))) return TSB_ERR_BAD_ARG;
+  if (!table_keys || capacity <= 0 || n < 0 || (n && (!keys || !out_vals))) return TSB_ERR_BAD_ARG;
   if (n == 0) return TSB_OK;
   table_lookup_kernel<<<grid_for(n, kBlock), kBlock, 0, as_stream(stream)>>>(
       make_table(const_cast<int64_t*>(table_keys), const_cast<int32_t*>(table_vals), capacity), keys, n, out_vals);
@@ -1014,16 +1014,24 @@ int tsb_hash_lookup_coords(const int64_t* table_keys, const int32_t* table_vals,
   return TSB_OK;
 }
 
+// keys are ravel index + 1 over the bounds: do they all fit the 32-bit half of a packed slot?
+static bool fits_packed_keys(const Bounds& b) {
+  unsigned __int128 total = 1;
+  for (int i = 0; i < 4; ++i) total *= (unsigned __int128)(uint64_t)b.sz[i];
+  return total < (unsigned __int128)kPackedKeyMax;
+}
+
 int tsb_kmap_subm(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n,
                   const int32_t* cmin, const int32_t* cmax, const int32_t* kernel_size, int32_t to_insert,
                   int32_t* out_in_map, int32_t* dev_status, tsb_stream_t stream) {
-  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || !cmin || !cmax || !kernel_size) return TSB_ERR_BAD_ARG;
+  if (!table_keys || capacity <= 0 || n < 0 || !cmin || !cmax || !kernel_size) return TSB_ERR_BAD_ARG;
   if (n && (!coords || !out_in_map)) return TSB_ERR_BAD_ARG;
   if (n == 0) return TSB_OK;
   for (int i = 0; i < 3; ++i) if (kernel_size[i] < 1) return TSB_ERR_BAD_ARG;
   KernelGeom g = make_geom(kernel_size, nullptr, nullptr);
   Bounds b = make_bounds(cmin, cmax);
   for (int i = 0; i < 4; ++i) if (b.sz[i] < 1) return TSB_ERR_BAD_ARG;
+  if (!table_vals && !fits_packed_keys(b)) return TSB_ERR_LIMIT;
   TableView t = make_table(table_keys, table_vals, capacity);
   cudaStream_t s = as_stream(stream);
   const int64_t rows_pad = pad128(n);
@@ -1128,13 +1136,13 @@ int tsb_kmap_down_finish(int64_t* table_keys, int32_t* table_vals, int64_t capac
                          const int64_t* uniq_keys, int64_t m, const int32_t* cmin, const int32_t* cmax_out,
                          const int32_t* kernel_size, const int32_t* stride, const int32_t* padding,
                          int32_t* out_coords, int32_t* out_in_map, int32_t* dev_status, tsb_stream_t stream) {
-  if (!table_keys || !table_vals || capacity <= 0 || n < 0 || m < 0 || !cmin || !cmax_out || !kernel_size ||
-      !stride || !padding)
+  if (!table_keys || capacity <= 0 || n < 0 || m < 0 || !cmin || !cmax_out || !kernel_size || !stride || !padding)
     return TSB_ERR_BAD_ARG;
   if (m == 0) return TSB_OK;
   if (!coords || !uniq_keys || !out_coords || !out_in_map) return TSB_ERR_BAD_ARG;
   if (capacity < m) return TSB_ERR_LIMIT;
   Bounds b = make_bounds(cmin, cmax_out);
+  if (!table_vals && !fits_packed_keys(b)) return TSB_ERR_LIMIT;
   KernelGeom g = make_geom(kernel_size, stride, padding);
   TableView t = make_table(table_keys, table_vals, capacity);
   cudaStream_t s = as_stream(stream);
@@ -1383,7 +1391,7 @@ int tsb_level_record_from_quantize(const int32_t* quantize_result, int32_t batch
 int tsb_kmap_subm_dyn(int64_t* table_keys, int32_t* table_vals, int64_t capacity, const int32_t* coords, int64_t n_max,
                       const int32_t* rec, const int32_t* kernel_size, int32_t to_insert, int32_t* out_in_map,
                       int32_t* dev_status, tsb_stream_t stream) {
-  if (!table_keys || !table_vals || capacity <= 0 || n_max < 0 || !rec || !kernel_size) return TSB_ERR_BAD_ARG;
+  if (!table_keys || capacity <= 0 || n_max < 0 || !rec || !kernel_size) return TSB_ERR_BAD_ARG;
   if (n_max == 0) return TSB_OK;
   if (!coords || !out_in_map) return TSB_ERR_BAD_ARG;
   for (int i = 0; i < 3; ++i) if (kernel_size[i] < 1 || kernel_size[i] > 64) return TSB_ERR_BAD_ARG;
@@ -1426,9 +1434,10 @@ int tsb_kmap_down_dyn(int64_t* table_keys, int32_t* table_vals, int64_t capacity
                       int32_t key_bits, int64_t m_max, int32_t* out_coords, int32_t* out_in_map, int32_t* out_in_map_t,
                       int32_t* rec_out, int32_t* dev_status, void* workspace, size_t workspace_bytes,
                       tsb_stream_t stream) {
-  if (!table_keys || !table_vals || capacity <= 0 || n_max < 0 || m_max < 0 || !rec_in || !rec_out || !kernel_size ||
-      !stride || !padding || key_bits < 1 || key_bits > 62)
+  if (!table_keys || capacity <= 0 || n_max < 0 || m_max < 0 || !rec_in || !rec_out || !kernel_size || !stride ||
+      !padding || key_bits < 1 || key_bits > 62)
     return TSB_ERR_BAD_ARG;
+  if (!table_vals && key_bits > 32) return TSB_ERR_LIMIT;     // keys + 1 must fit the 32-bit half of a packed slot
   if (n_max == 0) return TSB_OK;
   if (!coords || !out_coords || !out_in_map) return TSB_ERR_BAD_ARG;
   const int slots = tsb_kmap_down_slots(kernel_size, stride);

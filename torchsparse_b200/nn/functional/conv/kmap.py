@@ -143,10 +143,8 @@ def build_kernel_map(
             cmin, cmax = cmin_key, cmax_act
         to_insert = hashmap_keys is None or table_bounds is None
         if to_insert:
-            cap = _table_capacity(n)
-            hashmap_keys = torch.zeros(cap, dtype=torch.int64, device=coords.device)
-            hashmap_vals = torch.zeros(cap, dtype=torch.int32, device=coords.device)
-        table = backend.GPUHashTable(hashmap_keys, hashmap_vals)
+            hashmap_keys, hashmap_vals = backend.new_table(_table_capacity(n), coords.device, cmin, cmax)
+        table = backend.table_of(hashmap_keys, hashmap_vals)
         kmap["out_in_map"] = backend.build_kernel_map_subm_hashmap(
             table, coords, cmin, cmax, kernel_size, stride, padding, to_insert, check_status=False)[0]
         kmap["coords"] = _coords
@@ -160,10 +158,8 @@ def build_kernel_map(
                 (cmax_act[1 + i] + 2 * padding[i] - (kernel_size[i] - 1)) // stride[i] for i in range(3))
         cmin_out = cmin_key
         uniq, m, out_max = backend.downsample_unique(coords, cmin_out, cmax_out, kernel_size, stride, padding)
-        cap = _table_capacity(max(n, m))
-        hashmap_keys = torch.zeros(cap, dtype=torch.int64, device=coords.device)
-        hashmap_vals = torch.zeros(cap, dtype=torch.int32, device=coords.device)
-        table = backend.GPUHashTable(hashmap_keys, hashmap_vals)
+        hashmap_keys, hashmap_vals = backend.new_table(_table_capacity(max(n, m)), coords.device, cmin_out, cmax_out)
+        table = backend.table_of(hashmap_keys, hashmap_vals)
         out_in_map, out_coords = backend.downsample_finish(table, coords, uniq, m, cmin_out, cmax_out, kernel_size,
                                                            stride, padding, check_status=False)
         kmap["out_in_map"] = out_in_map

@@ -83,17 +83,24 @@ def _out_tensor(feats, coords, stride, dyn: DynInfo, caches) -> DynSparseTensor:
     return out
 
 
-def _level_table(caches, stride, n_max: int, device):
-    """(keys, vals, capacity, fresh) of the hash table of a tensor stride."""
+def _level_table(caches, stride, n_max: int, device, key_bits: int):
+    """(keys, vals, capacity, fresh) of the hash table of a tensor stride; vals is None for a table of 32-bit keys
+    (packed slots), taken whenever the level's key space allows it."""
+    from .. import backends
+
     tables = caches.__dict__.setdefault("dyn_tables", {})
     hit = tables.get(stride)
     if hit is not None:
         return hit + (False,)
     cap = _next_pow2(max(512, 2 * n_max))
     keys = torch.empty(cap, dtype=torch.int64, device=device)
-    vals = torch.empty(cap, dtype=torch.int32, device=device)
+    vals = None if (backends.hash_keys_32bit and key_bits <= 32) else torch.empty(cap, dtype=torch.int32, device=device)
     tables[stride] = (keys, vals, cap)
     return keys, vals, cap, True
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
 
 
 def _subm_map(x: DynSparseTensor, kernel_size) -> Dict:
@@ -104,9 +111,9 @@ def _subm_map(x: DynSparseTensor, kernel_size) -> Dict:
         return kmap
     dev = x.coords.device
     kvol = kernel_size[0] * kernel_size[1] * kernel_size[2]
-    keys, vals, cap, fresh = _level_table(caches, x.stride, dyn.n_max, dev)
+    keys, vals, cap, fresh = _level_table(caches, x.stride, dyn.n_max, dev, dyn.ctx.key_bits(x.stride))
     out_in_map = torch.empty((backend.pad128(dyn.n_max), kvol), dtype=torch.int32, device=dev)
-    check(lib.tsb_kmap_subm_dyn(keys.data_ptr(), vals.data_ptr(), cap, x.coords.data_ptr(), dyn.n_max,
+    check(lib.tsb_kmap_subm_dyn(keys.data_ptr(), _ptr(vals), cap, x.coords.data_ptr(), dyn.n_max,
                                 dyn.rec.data_ptr(), i32x(kernel_size), int(fresh), out_in_map.data_ptr(),
                                 dyn.ctx.status.data_ptr(), backend._stream()), "tsb_kmap_subm_dyn")
     kmap = {"out_in_map": out_in_map, "coords": x.coords, "dyn_in": dyn, "dyn_out": dyn}
@@ -127,14 +134,14 @@ def _down_map(x: DynSparseTensor, kernel_size, stride, padding) -> Dict:
         raise ValueError("bad kernel size / stride")
     m_max = min(dyn.n_max * slots, dyn.ctx.row_cap)     # more outputs than this are reported (TSB_DEV_LIMIT)
     out_stride = tuple(a * b for a, b in zip(x.stride, stride))
-    keys, vals, cap, _ = _level_table(caches, out_stride, m_max, dev)
+    keys, vals, cap, _ = _level_table(caches, out_stride, m_max, dev, dyn.ctx.key_bits(out_stride))
     out_coords = torch.empty((m_max, 4), dtype=torch.int32, device=dev)
     out_in_map = torch.empty((backend.pad128(m_max), kvol), dtype=torch.int32, device=dev)
     map_t = torch.empty((backend.pad128(dyn.n_max), kvol), dtype=torch.int32, device=dev)
     rec_out = torch.empty(16, dtype=torch.int32, device=dev)
     nbytes = lib.tsb_kmap_down_dyn_workspace_bytes(dyn.n_max, i32x(kernel_size), i32x(stride))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-    check(lib.tsb_kmap_down_dyn(keys.data_ptr(), vals.data_ptr(), cap, x.coords.data_ptr(), dyn.n_max,
+    check(lib.tsb_kmap_down_dyn(keys.data_ptr(), _ptr(vals), cap, x.coords.data_ptr(), dyn.n_max,
                                 dyn.rec.data_ptr(), i32x(kernel_size), i32x(stride), i32x(padding),
                                 dyn.ctx.key_bits(out_stride), m_max, out_coords.data_ptr(), out_in_map.data_ptr(),
                                 map_t.data_ptr(), rec_out.data_ptr(), dyn.ctx.status.data_ptr(), ws.data_ptr(),
