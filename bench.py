@@ -54,7 +54,10 @@ MAX_POINTS = 144_000    # points of one scan (120k rays + 20 % box points): boun
 # voxel grid bound at 0.05 m: 2 x 80 m range in x and y, 25 m in z (sensor range of the generator, with margin)
 MAX_EXTENT = (3328, 3328, 512)
 L2_FLUSH_BYTES = 256 << 20
-CONV_GRID_SHARED = 56   # persistent CTAs per convolution launch when several engines keep the GPU busy (of 296 slots)
+# persistent CTAs per convolution launch (of 296 slots) when several engines keep the GPU busy.  Measured with 20 scans
+# per timed pass: 8 engines x 56 CTAs 510 scans/s, 7 to 14 engines x 40-56 CTAs 500-506, 20 x 28 485; with 24 scans per
+# pass 12 engines x 40 CTAs reach 520 (the last round of a pass is then full)
+CONV_GRID_SHARED = 56
 C4_VOXEL = (0.1, 0.1, 0.2)
 C4_RANGE = (1080, 1080, 40)
 
@@ -254,13 +257,13 @@ def launch_counts(dims):
     return pairs, blocks
 
 
-def make_engines(model, device, n_eng, sorted_maps=True, conv_grid=0):
+def make_engines(model, device, n_eng, sorted_maps=True, conv_grid=0, overlap_maps=True):
     from torchsparse_b200.nn import StaticEngine
 
     head = model.head
     return [StaticEngine(model.backbone, lambda outs: head(outs[-1].feats), max_points=MAX_POINTS, point_channels=4,
                          voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device, sorted_maps=sorted_maps,
-                         conv_grid=conv_grid).capture()
+                         conv_grid=conv_grid, overlap_maps=overlap_maps).capture()
             for _ in range(n_eng)]
 
 
@@ -298,10 +301,10 @@ def run_ours(args, rank: int, world: int, device: torch.device):
             dist.barrier()
         torch.cuda.synchronize()
 
-    engines = make_engines(model, device, n_eng, not args.unsorted, args.conv_grid)
+    engines = make_engines(model, device, n_eng, not args.unsorted, args.conv_grid, not args.serial_maps)
     # kernels of this library per replay: a further capture (weights are packed by now) runs the forward twice
     launches0 = backend.launch_count()
-    make_engines(model, device, 1, not args.unsorted, args.conv_grid)
+    make_engines(model, device, 1, not args.unsorted, args.conv_grid, not args.serial_maps)
     launches_per_step = (backend.launch_count() - launches0) // 2
     comm_stream = torch.cuda.Stream(device) if world > 1 else None
     gather = PaddedGather(MAX_POINTS, NUM_CLASSES, torch.float16, device) if world > 1 else None
@@ -530,7 +533,7 @@ def kmap_build_ms(model, pts_dev, device):
     from torchsparse_b200.nn.static_engine import StaticEngine
 
     eng = StaticEngine(model.backbone, lambda outs: outs[-1].feats, max_points=MAX_POINTS, point_channels=4,
-                       voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device)
+                       voxel_size=VOXEL, max_extent=MAX_EXTENT, device=device, overlap_maps=False)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
     result = {}
 
@@ -1043,6 +1046,9 @@ def main():
     ap.add_argument("--sorted-max-stride", type=int, default=16, help="row-sorted map copies up to this tensor stride")
     ap.add_argument("--no-sorted-strided", dest="sorted_strided", action="store_false",
                     help="no row-sorted copies of the strided / transposed maps (only of the submanifold ones)")
+    ap.add_argument("--serial-maps", action="store_true",
+                    help="record every scan as one chain of launches (kernel maps built between the convolutions, "
+                         "not on a second branch of the graph)")
     ap.add_argument("--hash64", action="store_true",
                     help="kernel-map tables with 64-bit keys even where the level's key space fits 32 bits")
     ap.add_argument("--tune", default="", help="launch-configuration overrides of the conv kernel, e.g. stages=3,ctas=2,cpb=2")

@@ -57,6 +57,11 @@ class _Context:
         self.status = status
         self.sorted_maps = sorted_maps
         self.row_cap = int(row_cap)      # no level is given buffers for more rows than this
+        # Kernel maps depend on coordinates only, so they can be built ahead of the convolutions, on a stream of
+        # their own.  `log` (a list, or None) collects the map requests of a forward in network order; a later
+        # forward that was given them as its plan builds every map on the side stream first and lets each
+        # convolution wait for the event recorded behind the map it reads.
+        self.log: Optional[List[Tuple]] = None
 
     def key_bits(self, tensor_stride: Sequence[int]) -> int:
         cells = self.batch
@@ -161,6 +166,65 @@ def _sorted(kmap: Dict, sfx: str, valid: DynInfo) -> "backend.SortedMap":
     return art
 
 
+def _map_for(coords: torch.Tensor, stride, dyn: DynInfo, caches, request):
+    """The kernel map a layer asks for (built on first use, cached on the tensor cache) together with the form the
+    convolution reads it in: the row-sorted column-major copy, or the per-tile offset masks of the map as built.
+    request = (tensor stride, kernel size, conv stride, padding, dilation, transposed, sorted)."""
+    _, ks, st, pad, dil, transposed, want_sorted = request
+    if transposed:
+        out_stride = tuple(a // b for a, b in zip(stride, st))
+        kmap = caches.kmaps.get((out_stride, ks, st, dil))
+        if kmap is None:
+            raise ValueError("transposed convolution needs the kernel map of the matching strided convolution")
+        sfx, dyn_out = "_t", kmap["dyn_in"]
+        out_coords = caches.cmaps[out_stride][0]
+    else:
+        level = _out_tensor(None, coords, stride, dyn, caches)
+        if any(v != 1 for v in st):
+            kmap = _down_map(level, ks, st, pad)
+            sfx, dyn_out = "", kmap["dyn_out"]
+            out_coords, out_stride = kmap["coords"], tuple(a * b for a, b in zip(stride, st))
+        else:
+            kmap = _subm_map(level, ks)
+            sfx, dyn_out, out_coords, out_stride = "", dyn, coords, stride
+    if want_sorted:
+        art = _sorted(kmap, sfx, dyn_out)
+    else:
+        art = kmap.get("_tmask" + sfx)
+        if art is None:
+            art = kmap["_tmask" + sfx] = backend.tile_mask_cuda(kmap["out_in_map" + sfx], dyn_out.n_max,
+                                                                n_rows_dev=dyn_out.rec)
+    return kmap, sfx, dyn_out, out_coords, out_stride, art
+
+
+def _prebuild_maps(x: DynSparseTensor, plan: Sequence[Tuple], side: torch.cuda.Stream) -> torch.cuda.Event:
+    """Builds every kernel map of `plan` (the requests of an earlier forward, in network order) on `side`, which
+    branches off the current stream here; behind each map an event is recorded that its first reader waits for.
+    Returns the event that closes the branch: the caller's stream must wait for it before it ends."""
+    caches, main = x._caches, torch.cuda.current_stream(x.coords.device)
+    caches.__dict__.setdefault("dyn_levels", {}).setdefault(x.stride, x.dyn)
+    caches.cmaps.setdefault(x.stride, (x.coords, None))
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        seen = set()
+        for request in plan:
+            stride, transposed = request[0], request[5]
+            level = caches.cmaps.get(stride)
+            dyn = caches.__dict__["dyn_levels"].get(stride)
+            if level is None or dyn is None:
+                break                       # not the network the plan was taken from: the layers build on demand
+            kmap, sfx, *_ = _map_for(level[0], stride, dyn, caches, request)
+            key = (id(kmap), sfx, request[6])
+            if key not in seen:
+                seen.add(key)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                kmap["_ready" + sfx] = ev    # a later form of the same map (sorted / masks) moves the event back
+        done = torch.cuda.Event()
+        done.record(side)
+    return done
+
+
 def dyn_conv(layer, x: DynSparseTensor, residual: Optional[torch.Tensor]) -> DynSparseTensor:
     """A fused convolution layer (torchsparse_b200.nn.fused.FusedConv) on a tensor of the static mode."""
     dyn, caches = x.dyn, x._caches
@@ -177,32 +241,22 @@ def dyn_conv(layer, x: DynSparseTensor, residual: Optional[torch.Tensor]) -> Dyn
         backend.igemm_plan_launch(plan, feats, None, dyn.n_max, residual, layer.relu, in_feats2=feats2,
                                   n_out_dev=dyn.rec, out=out)
         return _out_tensor(out, x.coords, x.stride, dyn, caches)
-    ks, st = layer.kernel_size, layer.stride
-    if layer.transposed:
-        out_stride = tuple(a // b for a, b in zip(x.stride, st))
-        kmap = caches.kmaps.get((out_stride, ks, st, layer.dilation))
-        if kmap is None:
-            raise ValueError("transposed convolution needs the kernel map of the matching strided convolution")
-        sfx, dyn_out = "_t", kmap["dyn_in"]
-        out_coords = caches.cmaps[out_stride][0]
-    elif any(s != 1 for s in st):
-        kmap = _down_map(x, ks, st, make_ntuple(layer.padding, 3))
-        sfx, dyn_out = "", kmap["dyn_out"]
-        out_coords, out_stride = kmap["coords"], tuple(a * b for a, b in zip(x.stride, st))
-    else:
-        kmap = _subm_map(x, ks)
-        sfx, dyn_out, out_coords, out_stride = "", dyn, x.coords, x.stride
+    want_sorted = bool(dyn.ctx.sorted_maps and layer._wants_sorted(x.stride))
+    request = (x.stride, layer.kernel_size, layer.stride, make_ntuple(layer.padding, 3), layer.dilation,
+               bool(layer.transposed), want_sorted)
+    if dyn.ctx.log is not None:
+        dyn.ctx.log.append(request)
+    kmap, sfx, dyn_out, out_coords, out_stride, art = _map_for(x.coords, x.stride, dyn, caches, request)
+    ready = kmap.pop("_ready" + sfx, None)
+    if ready is not None:                  # built on the side stream: its first reader waits, later ones follow it
+        torch.cuda.current_stream(plan.device).wait_event(ready)
     out = torch.empty((dyn_out.n_max, plan.cout), dtype=plan.dtype, device=plan.device)
-    if dyn.ctx.sorted_maps and layer._wants_sorted(x.stride):
+    if want_sorted:
         backend.igemm_plan_launch(plan, feats, None, dyn_out.n_max, residual, layer.relu, in_feats2=feats2,
-                                  smap=_sorted(kmap, sfx, dyn_out), n_out_dev=dyn_out.rec, out=out)
+                                  smap=art, n_out_dev=dyn_out.rec, out=out)
     else:
-        m = kmap["out_in_map" + sfx]
-        tm = kmap.get("_tmask" + sfx)
-        if tm is None:
-            tm = kmap["_tmask" + sfx] = backend.tile_mask_cuda(m, dyn_out.n_max, n_rows_dev=dyn_out.rec)
-        backend.igemm_plan_launch(plan, feats, m, dyn_out.n_max, residual, layer.relu, tile_mask=tm,
-                                  in_feats2=feats2, n_out_dev=dyn_out.rec, out=out)
+        backend.igemm_plan_launch(plan, feats, kmap["out_in_map" + sfx], dyn_out.n_max, residual, layer.relu,
+                                  tile_mask=art, in_feats2=feats2, n_out_dev=dyn_out.rec, out=out)
     return _out_tensor(out, out_coords, out_stride, dyn_out, caches)
 
 
@@ -221,13 +275,14 @@ class StaticEngine:
     must not overlap on the GPU (use one engine per stream).  `conv_grid` bounds the persistent CTAs of every
     convolution launch (0: all resident slots of the device): with several engines kept busy on their own streams
     a share of the device per launch (e.g. 56 of 296 slots with eight engines on a B200) lets launches of different
-    engines run side by side, where full-device launches would wait for each other's last CTAs."""
+    engines run side by side, where full-device launches would wait for each other's last CTAs.
+    `overlap_maps=False` records the forward as one chain (maps built where the first layer needs them)."""
 
     def __init__(self, model: torch.nn.Module, post: Callable, *, max_points: int, point_channels: int,
                  voxel_size: float, max_extent: Sequence[int], device: torch.device,
                  dtype: torch.dtype = torch.float16, pad_channels: int = 8, sorted_maps: bool = True,
                  stream: Optional[torch.cuda.Stream] = None, row_cap: Optional[int] = None,
-                 conv_grid: int = 0) -> None:
+                 conv_grid: int = 0, overlap_maps: bool = True) -> None:
         self.model, self.post = model, post
         self.max_points, self.c_in, self.c_pad = int(max_points), int(point_channels), int(pad_channels)
         self.voxel = (float(voxel_size),) * 3 if isinstance(voxel_size, (int, float)) else tuple(voxel_size)
@@ -239,6 +294,11 @@ class StaticEngine:
         self.conv_grid = int(conv_grid)
         self.max_extent = tuple(int(v) for v in max_extent)
         self.stream = stream if stream is not None else torch.cuda.Stream(device)
+        # kernel maps are built on a second stream that branches off `stream` behind the quantisation and joins it
+        # again before the forward ends: in the recorded graph the map builds of the deeper levels (about a hundred
+        # short, latency-bound launches) run beside the convolutions of the earlier ones instead of between them
+        self.side = torch.cuda.Stream(device) if overlap_maps else None
+        self._map_plan: Optional[List[Tuple]] = None
         self.points = torch.zeros((self.max_points, self.c_in), dtype=torch.float32, device=device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.out: Optional[torch.Tensor] = None
@@ -275,7 +335,17 @@ class StaticEngine:
         check(lib.tsb_level_record_from_quantize(result.data_ptr(), 0, rec.data_ptr(), status.data_ptr(), stream),
               "tsb_level_record_from_quantize")
         x = DynSparseTensor(feats, coords, 1, DynInfo(rec, n, ctx))
-        return self.post(self.model(x)), rec, status
+        done = None
+        if self.side is not None and self._map_plan is not None:
+            done = _prebuild_maps(x, self._map_plan, self.side)
+        elif self.side is not None:
+            ctx.log = []
+        out = self.post(self.model(x))
+        if done is not None:
+            torch.cuda.current_stream(dev).wait_event(done)      # the branch joins: nothing of it outlives the forward
+        elif ctx.log is not None:
+            self._map_plan = ctx.log
+        return out, rec, status
 
     def capture(self) -> "StaticEngine":
         """One eager pass (packs weights, makes launch plans, loads kernels), then the recording."""
@@ -291,6 +361,9 @@ class StaticEngine:
             with torch.no_grad(), torch.cuda.stream(self.stream):
                 self._forward()
                 self.stream.synchronize()
+                if self.side is not None:       # once more with the maps on their own stream, as it will be recorded
+                    self._forward()
+                    torch.cuda.synchronize(self.device)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=self.stream):
                     self.out, self.rec, self.status = self._forward()
