@@ -302,10 +302,11 @@ def run_ours(args, rank: int, world: int, device: torch.device):
         torch.cuda.synchronize()
 
     engines = make_engines(model, device, n_eng, not args.unsorted, args.conv_grid, not args.serial_maps)
-    # kernels of this library per replay: a further capture (weights are packed by now) runs the forward twice
+    # kernels of this library per replay: a further capture (weights are packed by now) runs the forward twice, or
+    # three times when the maps go to a side branch (eager, eager with the branch, recording)
     launches0 = backend.launch_count()
     make_engines(model, device, 1, not args.unsorted, args.conv_grid, not args.serial_maps)
-    launches_per_step = (backend.launch_count() - launches0) // 2
+    launches_per_step = (backend.launch_count() - launches0) // (2 if args.serial_maps else 3)
     comm_stream = torch.cuda.Stream(device) if world > 1 else None
     gather = PaddedGather(MAX_POINTS, NUM_CLASSES, torch.float16, device) if world > 1 else None
     pinned_out = [torch.empty((MAX_POINTS, NUM_CLASSES), dtype=torch.float16).pin_memory() for _ in range(n_eng)]
