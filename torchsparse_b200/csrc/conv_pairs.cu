@@ -8,8 +8,9 @@
 // column of input rows (fetched on demand by the kernel's gather warps, no gathered copy of the
 // features is made), the weight block of a tile is chosen by tile_k[tile], one K block per 128 bytes
 // of input channels, fp32 accumulation in TMEM.
-//   GatherScatter   products written as fp32 rows of a [P_pad, Cout] buffer, then summed per output
-//                   row in fixed offset order through the scatter mask (no atomics, deterministic)
+//   GatherScatter   products written as rows of a [P_pad, Cout] buffer in the tensors' own type (what the
+//                   reference's per-offset GEMMs produce), then summed in fp32 per output row in fixed
+//                   offset order through the scatter mask (no atomics, deterministic)
 //   FetchOnDemand   products added straight into an fp32 [M, Cout] accumulator with vector atomic
 //                   adds from the kernel's epilogue, then rounded once
 #include <vector>
@@ -43,9 +44,24 @@ __global__ void pairs_pad_kernel(const int* __restrict__ in_list, int in_stride,
   }
 }
 
-// y[o, n..n+3] = sum_k buf[qaddrs[k] + mask[k*M + o], n..n+3]   (fixed k order, fp32)
-template <typename T>
-__global__ void pairs_scatter_kernel(const float* __restrict__ buf, const int* __restrict__ mask,
+__device__ __forceinline__ float4 load4_f32(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4_f32(const __half* p) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ float4 load4_f32(const __nv_bfloat16* p) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// y[o, n..n+3] = sum_k buf[qaddrs[k] + mask[k*M + o], n..n+3]   (fixed k order, fp32 sums; the product rows are
+// fp32 for fp32 tensors and 16-bit for 16-bit tensors, as the reference's per-offset GEMM outputs are)
+template <typename T, typename B>
+__global__ void pairs_scatter_kernel(const B* __restrict__ buf, const int* __restrict__ mask,
                                      const int* __restrict__ qaddrs, int kvol, int centre_k, int64_t n_out, int cout,
                                      T* __restrict__ y) {
   const int vecs = cout >> 2;
@@ -58,7 +74,7 @@ __global__ void pairs_scatter_kernel(const float* __restrict__ buf, const int* _
       // the masks leave out the centre offset of an odd submanifold map: its pair list is the identity
       const int pos = (k == centre_k) ? (int)o : __ldg(&mask[(int64_t)k * n_out + o]);
       if (pos >= 0) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(buf + ((int64_t)__ldg(&qaddrs[k]) + pos) * cout + n));
+        const float4 v = load4_f32(buf + ((int64_t)__ldg(&qaddrs[k]) + pos) * cout + n);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
     }
@@ -156,13 +172,13 @@ static int gs_umma_launch(const GsArgs& a, cudaStream_t s) {
     IgemmArgs ia = pair_mode_args(a.x, a.w, a.n_in, q_total, a.kvol, a.cin, a.cout, a.dtype, a.math);
     ia.map = in_pad; ia.tile_k = tile_k; ia.y = buf; ia.dev_status = err;
     ia.workspace = base + w.w_off; ia.workspace_bytes = w.total - w.w_off;     // packed weights
-    ia.out_fp32 = 1;
+    ia.out_fp32 = 0;           // product rows in the tensors' own type: half the bytes written and read again
     int rc = igemm_umma(ia, s);
     if (rc != TSB_OK) return rc;
   }
   if (a.n_out) {
-    pairs_scatter_kernel<T><<<grid_for(a.n_out * (a.cout / 4), 256, 16), 256, 0, s>>>(
-        buf, a.scatter_mask, qaddrs, a.kvol, (a.n_in == a.n_out && (a.kvol & 1)) ? a.kvol / 2 : -1, a.n_out, a.cout,
+    pairs_scatter_kernel<T, T><<<grid_for(a.n_out * (a.cout / 4), 256, 16), 256, 0, s>>>(
+        reinterpret_cast<const T*>(buf), a.scatter_mask, qaddrs, a.kvol, (a.n_in == a.n_out && (a.kvol & 1)) ? a.kvol / 2 : -1, a.n_out, a.cout,
         (T*)a.y);
     TSB_LAUNCH_CHECK();
   }
