@@ -48,8 +48,10 @@ def _eager(engine, head, pts):
         return coords, outs[-1].feats
 
 
+@pytest.mark.parametrize("overlap_maps", [True, False])
 @pytest.mark.parametrize("sorted_maps", [True, False, "all"])
-def test_static_engine_equals_eager_engine(sorted_maps):
+def test_static_engine_equals_eager_engine(sorted_maps, overlap_maps):
+    """Bit-equal to the eager engine, with the kernel maps recorded on a side branch of the graph or in line."""
     from torchsparse_b200.nn import InferenceEngine, StaticEngine
 
     net, head = _net()
@@ -66,7 +68,8 @@ def test_static_engine_equals_eager_engine(sorted_maps):
     max_points = max(p.shape[0] for p in scans)
     ext = [int(max(float(p[:, d].max()) for p in scans) / VOXEL) + 8 for d in range(3)]
     static = StaticEngine(engine, lambda outs: outs[-1].feats, max_points=max_points, point_channels=4,
-                          voxel_size=VOXEL, max_extent=ext, device=torch.device("cuda", 0), sorted_maps=sorted_maps)
+                          voxel_size=VOXEL, max_extent=ext, device=torch.device("cuda", 0), sorted_maps=sorted_maps,
+                          overlap_maps=overlap_maps)
     static.capture()
     for pts in scans:
         coords, want = _eager(engine, head, pts)
