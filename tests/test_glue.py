@@ -75,3 +75,13 @@ def test_sparse_collate_prepends_batch_index():
     assert out.feats.shape == (5, 2) and out.stride == (1, 1, 1)
     batch = sparse_collate_fn([{"x": a, "y": np.zeros(2), "meta": {"n": 1}}, {"x": b, "y": np.ones(2), "meta": {"n": 2}}])
     assert batch["x"].coords.shape == (5, 4) and batch["y"].shape == (2, 2) and batch["meta"]["n"] == [1, 2]
+
+
+def test_32bit_key_tables_are_taken_only_where_every_ravel_key_fits():
+    from torchsparse_b200 import backend
+
+    assert backend.fits_32bit_keys((0, 0, 0, 0), (0, 2399, 2399, 159))            # a LiDAR grid at 5 cm: 9.2e8 cells
+    assert backend.fits_32bit_keys((0, -100, -100, -10), (3, 1500, 1500, 100))    # 4 scans: 1.1e9 cells
+    assert not backend.fits_32bit_keys((0, 0, 0, 0), (0, 70000, 70000, 8))        # 4.4e10 cells
+    assert not backend.fits_32bit_keys((0, 0, 0, 0), (0, 65535, 65535, 0))        # exactly 2^32 cells
+    assert backend.fits_32bit_keys((0, 0, 0, 0), (0, 65535, 65534, 0))

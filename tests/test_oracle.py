@@ -210,3 +210,30 @@ def test_generative_kernel_map_small_case():
     # clamping: the generated coordinates never leave the derived range
     km = ko.build_kmap_generative(np.array([[0, 3, 3, 3]], dtype=np.int32), 2, 2, 0, (1, 8, 8, 8))
     assert km["spatial_range"] == (1, 4, 4, 4) and km["coords"].tolist() == [[0, 3, 3, 3]]
+
+
+def test_bev_restatement_on_a_case_checked_by_hand():
+    """Three voxels, two of them in one column along y: the four bird's-eye-view heads on numbers small enough to
+    verify on paper (oracle/bev_oracle.py restates torchsparse/nn/modules/bev.py:17-222 on batch-first rows)."""
+    from oracle import bev_oracle as bo
+
+    coords = np.array([[0, 1, 0, 2], [0, 1, 3, 2], [0, 2, 1, 0]], dtype=np.int32)      # (batch, x, y, z)
+    feats = np.array([[1.0, 2.0], [3.0, 6.0], [10.0, 20.0]], dtype=np.float32)
+    c, f = bo.bev_reduction(coords, feats, dim=1)
+    assert c.tolist() == [[0, 1, 0, 2], [0, 2, 0, 0]]
+    assert f.tolist() == [[2.0, 4.0], [10.0, 20.0]]                                    # mean over the column
+    kernel = np.zeros((4, 2, 1), dtype=np.float32)                                    # layer y: f . (y + 1, 0)
+    kernel[:, 0, 0] = [1.0, 2.0, 3.0, 4.0]
+    c, f, stride = bo.bev_convolution(coords, feats, (1, 1, 1), kernel, None, dim=1, stride=1)
+    assert c.tolist() == [[0, 1, 0, 2], [0, 2, 0, 0]] and stride == (1, 1, 1)
+    assert f.tolist() == [[1.0 * 1 + 3.0 * 4], [10.0 * 2]]
+    c, f, stride = bo.bev_convolution(coords, feats, (1, 1, 1), kernel, np.array([[0.5]]), dim=1, stride=4)
+    assert c.tolist() == [[0, 0, 0, 0]] and stride == (4, 4, 4)                        # one 4 x 4 column left
+    assert f.tolist() == [[13.0 + 20.0 + 3 * 0.5]]                                     # the bias once per voxel
+    dense = bo.dense_bev_convolution(coords, feats, (1, 1, 1), kernel, None, (3, 4, 3), (0, 0, 0), dim=1)
+    assert dense.shape == (1, 1, 3, 3) and dense[0, 0, 1, 2] == 13.0 and dense[0, 0, 2, 0] == 20.0
+    assert dense.sum() == 33.0
+    hc = bo.bev_height_compression(coords, feats, (1, 1, 1), (3, 2, 3), (0, 0, 0), dim=1)
+    assert hc.shape == (1, 4, 3, 3)                                                    # 2 layers x 2 channels
+    assert hc[0, :, 1, 2].tolist() == [1.0, 2.0, 3.0, 6.0]                             # y = 3 clamped into layer 1
+    assert hc[0, :, 2, 0].tolist() == [0.0, 0.0, 10.0, 20.0]
