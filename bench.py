@@ -642,16 +642,23 @@ def kmap_build_ms(model, pts_dev, device):
         times.setdefault(name, []).append(e0.elapsed_time(e1))
         return r
 
+    sizes = {}     # name -> (kind, row-count tensors on the device): read after the last pass
+
     class Probe(torch.nn.Module):
         def forward(self, x):
             for lvl in range(5):
                 km = timed(f"subm_k3_level{lvl}", lambda: se._subm_map(x, (3, 3, 3)))
+                sizes[f"subm_k3_level{lvl}"] = ("subm", x.dyn.rec, x.dyn.rec, 27)
                 timed(f"sorted_copy_subm_level{lvl}", lambda: se._sorted(km, "", x.dyn))
+                sizes[f"sorted_copy_subm_level{lvl}"] = ("sorted", x.dyn.rec, x.dyn.rec, 27)
                 if lvl == 4:
                     break
                 kd = timed(f"strided_k2s2_level{lvl}_with_transposed", lambda: se._down_map(x, (2, 2, 2), (2, 2, 2), (0, 0, 0)))
+                sizes[f"strided_k2s2_level{lvl}_with_transposed"] = ("down", x.dyn.rec, kd["dyn_out"].rec, 8)
                 timed(f"sorted_copy_strided_level{lvl}", lambda: se._sorted(kd, "", kd["dyn_out"]))
+                sizes[f"sorted_copy_strided_level{lvl}"] = ("sorted", kd["dyn_out"].rec, kd["dyn_out"].rec, 8)
                 timed(f"sorted_copy_transposed_level{lvl}", lambda: se._sorted(kd, "_t", x.dyn))
+                sizes[f"sorted_copy_transposed_level{lvl}"] = ("sorted", x.dyn.rec, x.dyn.rec, 8)
                 x = se._out_tensor(x.feats, kd["coords"], tuple(2 * s for s in x.stride), kd["dyn_out"], x._caches)
             return [x]
 
@@ -663,10 +670,29 @@ def kmap_build_ms(model, pts_dev, device):
     med = {k: round(statistics.median(v[1:]), 4) for k, v in times.items()}
     total_build = sum(v for k, v in med.items() if not k.startswith("sorted_copy"))
     total_sorted = sum(v for k, v in med.items() if k.startswith("sorted_copy"))
+    # algorithmic bytes of each build (every array read or written once; probes 8 bytes each) over its time
+    hbm = peaks()["hbm_gbs"]
+    gbs = {}
+    for name, (kind, rec_in, rec_out, kvol) in sizes.items():
+        n, m = int(rec_in[0].item()), int(rec_out[0].item())
+        cap = 512
+        while cap < 2 * MAX_POINTS:
+            cap *= 2
+        pad = lambda r: (r + 127) // 128 * 128
+        if kind == "subm":      # coords (insert) + table + coords again + map + one probe per (row, offset pair)
+            byts = 16 * n + 8 * cap + 16 * n + pad(n) * kvol * 4 + (kvol // 2) * n * 8
+        elif kind == "down":    # coords + candidate keys (written, read) + unique keys + table + output coords +
+            byts = 16 * n + 16 * n + 8 * m + 8 * cap + 16 * m + pad(m) * kvol * 4 + pad(n) * kvol * 4 + 8 * n   # both maps + probes
+        else:                   # the map read for the keys and for the copy, the copy written, 8-byte (key, row) pairs
+            byts = 3 * pad(n) * kvol * 4 + 8 * n
+        rate = byts / (med[name] * 1e-3) / 1e9
+        gbs[name] = {"rows": n, "algorithmic_gbs": round(rate, 1), "frac_of_hbm": round(rate / hbm, 4)}
     return {"maps_total": round(total_build, 4), "sorted_copies_total": round(total_sorted, 4), "per_map": med,
+            "per_map_bandwidth": gbs,
             "note": "5 submanifold k3 maps + 4 strided k2 s2 maps (each with its transposed map) of one scan; "
                     "sizes stay on the device, no host read; median of 5 isolated builds, host launch cost hidden "
-                    "behind a spin kernel"}
+                    "behind a spin kernel; per_map_bandwidth: algorithmic bytes over that time against the measured "
+                    "copy bandwidth (110 k rows or fewer per build: these launches are latency-bound)"}
 
 
 def run_batch(args, rank, world, device, model, barrier, kind, total):
