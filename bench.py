@@ -1173,6 +1173,10 @@ def main():
         for kv in args.tune.split(","):
             k, v = kv.split("=")
             _backend.igemm_tuning[k] = int(v)
+    if not (args.layer or args.kmap or args.pointops or args.sweep) and args.steps < args.streams:
+        args.streams = max(1, args.steps)        # a pass of fewer scans than engines keeps only that many in flight
+    if args.conv_grid < 0 and 1 < args.streams < 6:
+        args.conv_grid = 296 // args.streams       # few scans in flight: each convolution launch gets a larger share
     if args.conv_grid < 0:
         args.conv_grid = CONV_GRID_SHARED if (args.streams > 1 and not args.layer and not args.kmap and not args.pointops and not args.sweep) else 0
     if args.conv_grid and args.layer:      # the engines of the step benchmark get it as their own setting
