@@ -24,6 +24,27 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert sorted(_lib.SIGNATURES) == names
 
 
+def test_ctypes_table_matches_the_header_prototypes():
+    """Every prototype of include/tsb200.h has as many parameters as its entry in the ctypes table, pointer
+    parameters are bound as pointers and 64-bit sizes as 64-bit integers: a drifted binding would pass garbage."""
+    from torchsparse_b200 import _lib
+
+    text = open(os.path.join(ROOT, "include", "tsb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = re.findall(r"\b(tsb_[a-z0-9_]+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S)
+    assert sorted(n for n, _ in protos) == sorted(_lib.SIGNATURES)
+    wide = (ctypes.c_int64, ctypes.c_uint64, ctypes.c_size_t, ctypes.c_longlong, ctypes.c_ulonglong)
+    for name, args in protos:
+        params = [] if args.strip() in ("", "void") else [a.strip() for a in args.split(",")]
+        bound = _lib.SIGNATURES[name][1]
+        assert len(params) == len(bound), f"{name}: {len(params)} parameters declared, {len(bound)} bound"
+        for decl, ctype in zip(params, bound):
+            if "*" in decl or decl.startswith("tsb_stream_t"):
+                assert ctype in (ctypes.c_void_p, ctypes.c_char_p) or issubclass(ctype, ctypes._Pointer), (name, decl)
+            elif decl.startswith(("int64_t", "size_t", "uint64_t")):
+                assert ctype in wide, (name, decl, ctype)
+
+
 def test_status_strings_and_argument_checks():
     from torchsparse_b200._lib import lib, i32x
 
