@@ -171,6 +171,29 @@ __device__ __forceinline__ int table_lookup(const TableView& t, unsigned long lo
   return 0;
 }
 
+// The rest of a lookup whose first probe (slot = table_slot(t, key), cur = the word read there) the caller has
+// already made, so that several lookups of one thread can have their first loads in flight together.
+__device__ __forceinline__ int table_lookup_after(const TableView& t, unsigned long long key, unsigned long long slot,
+                                                  unsigned long long cur) {
+  if (!t.vals) {
+    if (key > kPackedKeyMax) return 0;
+    for (unsigned long long probe = 0; probe < t.cap; ++probe) {
+      if ((cur & kPackedKeyMax) == key) return (int)(cur >> 32);
+      if (cur == 0ull) return 0;
+      slot = table_next(t, slot);
+      cur = __ldg(&t.keys[slot]);
+    }
+    return 0;
+  }
+  for (unsigned long long probe = 0; probe < t.cap; ++probe) {
+    if (cur == key) return __ldg(&t.vals[slot]);
+    if (cur == 0ull) return 0;
+    slot = table_next(t, slot);
+    cur = __ldg(&t.keys[slot]);
+  }
+  return 0;
+}
+
 // Kernel geometry passed by value to the map kernels.
 struct KernelGeom {
   int ks[3];
