@@ -8,8 +8,9 @@ reference's own SparseResUNet42, width 1.0, plus a 19-way linear head) in fp16 i
 LiDAR-like scan per GPU per step (64 rings x 2048 azimuths, 120k rays + 20% box points, 0.05 m voxels).
 One step = voxelisation (sparse_quantize on the GPU) -> 9 kernel maps -> 42 sparse convolutions + 7 pointwise
 ones (BatchNorm / ReLU / skip folded in) -> logits.  The whole step is one CUDA graph (StaticEngine: every
-size lives in device memory), replayed per scan; consecutive scans rotate over four engines on four
-streams.  With N GPUs every rank runs its own scans (weak scaling, scans are independent) and the logits are
+size lives in device memory, the kernel maps on a second branch of the graph), replayed per scan; consecutive
+scans rotate over eight engines on eight streams whose convolution launches are bounded to 56 CTAs each, so that
+several scans are in flight on the GPU.  With N GPUs every rank runs its own scans (weak scaling, scans are independent) and the logits are
 all-gathered over NCCL once per step.
 
 Prints ONE JSON line (rank 0):
@@ -17,12 +18,13 @@ Prints ONE JSON line (rank 0):
             (one CUDA-event pair around each pass, barrier + synchronize on both sides, max over ranks)
   e2e       the same from pinned host memory: H2D copy of the points and D2H copy of the logits + their row
             count inside the timed region
-  roofline  over ALL convolution launches of a step, timed one by one (event pair per launch) in a serial
-            eager pass over the same scans: useful FLOPs, algorithmic bytes, sum of the per-launch roofline
-            minima; `dominant` = the layer shape with the largest total time; `levels` = per resolution level
+  roofline  over ALL convolution launches of a step, timed one by one (event pair per launch, queued behind a spin
+            kernel) in a serial eager pass over the same scans: useful FLOPs, algorithmic bytes, sum of the
+            per-launch roofline minima; `dominant` = the layer shape with the largest total time; `levels` = per
+            resolution level; `side_by_side` = the same launches alone with eight scans in flight
   step_roofline  roofline-minimum time of a whole step / measured time of a step
   kmap_build_ms  the kernel-map builds of one scan (5 submanifold, 4 strided + transposed) and the row-sorted
-            copies, timed in isolation
+            copies, timed in isolation, with the algorithmic bandwidth of each
   batch32   BASELINE config 3 as written: 32 scans, 32 / N per rank collated into one batch, one gather
   cpu_baseline   the reference project's own CPU convolution (oracle/_ref) driving the same network on the full
             scan, at one thread and at all host threads
